@@ -1,0 +1,87 @@
+"""Cosmos3-Nano-shaped network family: layers, towers, attention policies, streaming.
+
+``GEN_KEYS`` / ``TEXT_ENCODER_KEYS`` are the regular expressions that select the
+generation-tower and text-tower tensors of the released transformer checkpoint.
+
+Parity: reference ``wm/networks/cosmos3/__init__.py:16-68``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import asdict, is_dataclass
+from typing import Any
+
+import torch
+
+from .layers import Cosmos3Config
+from .network import Cosmos3Condition, Cosmos3Network, Cosmos3TextEncoder
+
+__all__ = [
+    "COSMOS3_EMPTY_PROMPT_IDS",
+    "GEN_KEYS",
+    "LORA_ATTENTION_MLP_MODULES",
+    "LORA_ATTENTION_MODULES",
+    "TEXT_ENCODER_KEYS",
+    "Cosmos3Condition",
+    "Cosmos3Conditioner",
+    "Cosmos3Config",
+    "Cosmos3Network",
+    "Cosmos3TextEncoder",
+    "build_network",
+]
+
+_GEN_ATTN = r"layers\.\d+\.self_attn\.(add_q_proj|add_k_proj|add_v_proj|to_add_out|norm_added_q|norm_added_k)\.weight"
+GEN_KEYS = (
+    _GEN_ATTN,
+    r"layers\.\d+\.(input_layernorm_moe_gen|post_attention_layernorm_moe_gen)\.weight",
+    r"layers\.\d+\.mlp_moe_gen\.(gate|up|down)_proj\.weight",
+    r"norm_moe_gen\.weight",
+    r"proj_(in|out)\.(weight|bias)",
+    r"time_embedder\.linear_[12]\.(weight|bias)",
+    r"geometry_modality_embed",
+    r"first_frame_reference_embed",
+)
+TEXT_ENCODER_KEYS = (
+    r"embed_tokens\.weight",
+    r"layers\.\d+\.self_attn\.(to_q|to_k|to_v|to_out|norm_q|norm_k)\.weight",
+    r"layers\.\d+\.(input_layernorm|post_attention_layernorm)\.weight",
+    r"layers\.\d+\.mlp\.(gate|up|down)_proj\.weight",
+)
+LORA_ATTENTION_MODULES = (
+    r"layers\.\d+\.self_attn\.(add_q_proj|add_k_proj|add_v_proj|to_add_out)",
+)
+LORA_ATTENTION_MLP_MODULES = (
+    *LORA_ATTENTION_MODULES,
+    r"layers\.\d+\.mlp_moe_gen\.(gate|up|down)_proj",
+)
+# Token ids of the empty prompt after the chat template (used for text dropout / CFG).
+COSMOS3_EMPTY_PROMPT_IDS: tuple[int, ...] = ()
+
+
+def _as_config(config: Any) -> Cosmos3Config:
+    if isinstance(config, Cosmos3Config):
+        return config
+    if is_dataclass(config):
+        return Cosmos3Config(**asdict(config))
+    data = {k: v for k, v in dict(config).items() if not str(k).startswith("_")}
+    return Cosmos3Config(**data)
+
+
+def build_network(config: Any, *, init_device: str | torch.device = "meta",
+                  lora: dict | None = None) -> Cosmos3Network:
+    """Construct the generation tower on ``init_device`` and optionally inject LoRA."""
+    with torch.device(init_device):
+        network = Cosmos3Network(_as_config(config))
+    if lora:
+        from agentgarten_b200.networks.lora import inject_lora
+
+        inject_lora(network, lora)
+    return network
+
+
+def __getattr__(name: str):
+    if name == "Cosmos3Conditioner":
+        from .conditioner import Cosmos3Conditioner
+
+        return Cosmos3Conditioner
+    raise AttributeError(name)

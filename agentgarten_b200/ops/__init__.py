@@ -1,0 +1,45 @@
+"""Operator facade.
+
+Every operator has two implementations that compute the same function:
+
+* the sm_100a CUDA kernels of ``agentgarten_b200/csrc`` (loaded through
+  :mod:`agentgarten_b200.ops.native`), used for bf16 tensors on a CUDA device, and
+* the PyTorch definitions in :mod:`agentgarten_b200.ops.reference`, used on CPU and for
+  other dtypes, and as the numerical oracle in the tests.
+
+On a CUDA device a missing extension is an error, never a silent fallback.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.autograd.forward_ad as fwAD
+
+from . import native, reference
+from .attention import attention, attention_jvp, planned_attention
+from .linear import linear
+from .pointwise import (
+    head_norm_rope,
+    rf_interpolate,
+    rf_x0,
+    rms_norm,
+    rms_norm_add,
+    rotary,
+    silu_mul,
+)
+
+__all__ = [
+    "attention",
+    "attention_jvp",
+    "head_norm_rope",
+    "linear",
+    "native",
+    "planned_attention",
+    "reference",
+    "rf_interpolate",
+    "rf_x0",
+    "rms_norm",
+    "rms_norm_add",
+    "rotary",
+    "silu_mul",
+]

@@ -1,0 +1,200 @@
+"""Attention operators: dense, planned (segment lists) and forward-mode JVP.
+
+``planned_attention`` is the single entry used by the attention policies.  A *plan* lists,
+for every query chunk, the key/value chunks it may attend to; text keys (masked to each
+sample's prompt length) always come first.  On a B200 the chunks are laid out back to back
+and one flash kernel walks, per 128-row query tile, the list of key *segments* of its
+chunk.  Key tiles never straddle segments, so the softmax of a query row is accumulated
+over the same tile partition no matter how many other chunks are processed in the same
+launch (bitwise replay between teacher-forced training and the cached rollout).
+
+Parity: reference ``wm/networks/cosmos3/attention.py:56-217`` (SDPA per block with
+concatenated keys and a boolean key mask; FP64 JVP oracle; autograd glue for tangents).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.autograd.forward_ad as fwAD
+
+from . import native, reference
+
+__all__ = ["AttentionSchedule", "attention", "attention_jvp", "build_schedule",
+           "planned_attention"]
+
+TILE = 128
+
+
+def _has_tangent(*tensors: torch.Tensor) -> bool:
+    return any(fwAD.unpack_dual(t).tangent is not None for t in tensors)
+
+
+# --------------------------------------------------------------------------- JVP
+def attention_jvp(q, k, v, dq, dk, dv, key_mask=None):
+    """Primal and tangent of softmax attention, ``[B, N, H, D]`` layout → ``(O, dO)`` FP32."""
+    if native.use(q) and q.shape[-1] == 128:
+        from .attention_native import jvp_dense
+
+        return jvp_dense(q, k, v, dq, dk, dv, key_mask)
+    o, do = reference.attention_jvp(q, k, v, dq, dk, dv, key_mask)
+    return o.float(), do.float()
+
+
+class _AttentionWithJVP(torch.autograd.Function):
+    """Dense attention that also defines its forward-mode derivative."""
+
+    @staticmethod
+    def forward(q, k, v, key_mask):
+        return reference.attention(q, k, v, key_mask)
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        q, k, v, key_mask = inputs
+        ctx.save_for_forward(q, k, v)
+        ctx.save_for_backward(q, k, v)
+        ctx.key_mask = key_mask
+
+    @staticmethod
+    def backward(ctx, grad):
+        q, k, v = ctx.saved_tensors
+        with torch.enable_grad():
+            q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
+            out = reference.attention(q_, k_, v_, ctx.key_mask)
+            gq, gk, gv = torch.autograd.grad(out, (q_, k_, v_), grad)
+        return gq, gk, gv, None
+
+    @staticmethod
+    def jvp(ctx, dq, dk, dv, _dmask):
+        q, k, v = ctx.saved_tensors
+        tangents = [torch.zeros_like(x) if dx is None else dx
+                    for x, dx in ((q, dq), (k, dk), (v, dv))]
+        _, tangent = attention_jvp(q, k, v, *tangents, key_mask=ctx.key_mask)
+        return tangent.to(q.dtype)
+
+
+# ------------------------------------------------------------------------- dense
+def attention(q, k, v, key_mask=None, causal: bool = False):
+    """Softmax attention on ``[B, N, H, D]`` tensors with grouped KV heads.
+
+    ``key_mask`` ``[B, NK]`` (True = visible) must describe a prefix-valid text segment
+    followed by visible keys for the kernel path; arbitrary masks use the PyTorch path.
+    """
+    if _has_tangent(q, k, v):
+        if causal:
+            raise NotImplementedError("forward-mode causal attention is not used by any recipe")
+        return _AttentionWithJVP.apply(q, k, v, key_mask)
+    if native.use(q) and q.shape[-1] == 128 and key_mask is None:
+        from .attention_native import dense
+
+        return dense(q, k, v, causal=causal)
+    return reference.attention(q, k, v, key_mask, causal)
+
+
+# ----------------------------------------------------------------------- planned
+@dataclass
+class AttentionSchedule:
+    """Device-side work lists for the segment flash kernels (all int32).
+
+    ``q_tiles[t] = (q_row, rows, first_entry, entries)``; ``entries[e] = (source, k_row,
+    k_len)`` with source 0 = text (valid length per sample), 1 = visual.  ``k_tiles`` and
+    ``q_lists`` are the transposed lists used by the dK/dV pass.
+    """
+
+    q_tiles: torch.Tensor
+    entries: torch.Tensor
+    k_tiles: torch.Tensor
+    q_lists: torch.Tensor
+    total_q: int
+    total_k: int
+    text_len: int
+
+
+_schedule_cache: dict = {}
+
+
+def build_schedule(q_sizes: list[int], k_sizes: list[int], plan: list[list[int]],
+                   text_len: int, device: torch.device) -> AttentionSchedule:
+    key = (tuple(q_sizes), tuple(k_sizes), tuple(map(tuple, plan)), text_len, str(device))
+    cached = _schedule_cache.get(key)
+    if cached is not None:
+        return cached
+    k_start = [0]
+    for size in k_sizes:
+        k_start.append(k_start[-1] + size)
+    q_tiles, entries = [], []
+    q_row = 0
+    readers: dict[int, list[tuple[int, int]]] = {j: [] for j in range(len(k_sizes))}
+    for chunk, size in enumerate(q_sizes):
+        first = len(entries)
+        if text_len:
+            entries.append((0, 0, text_len))
+        for j in plan[chunk]:
+            entries.append((1, k_start[j], k_sizes[j]))
+            readers[j].append((q_row, size))
+        count = len(entries) - first
+        for offset in range(0, size, TILE):
+            q_tiles.append((q_row + offset, min(TILE, size - offset), first, count))
+        q_row += size
+    k_tiles, q_lists = [], []
+    for j, size in enumerate(k_sizes):
+        first = len(q_lists)
+        q_lists.extend(readers[j])
+        count = len(q_lists) - first
+        if count == 0:
+            continue
+        for offset in range(0, size, TILE):
+            k_tiles.append((k_start[j] + offset, min(TILE, size - offset), first, count))
+
+    def tensor(rows, width):
+        data = torch.tensor(rows or [[0] * width], dtype=torch.int32).reshape(-1, width)
+        return data.to(device)
+
+    schedule = AttentionSchedule(
+        q_tiles=tensor(q_tiles, 4), entries=tensor(entries, 3), k_tiles=tensor(k_tiles, 4),
+        q_lists=tensor(q_lists, 2), total_q=q_row, total_k=k_start[-1], text_len=text_len)
+    if len(_schedule_cache) > 256:
+        _schedule_cache.clear()
+    _schedule_cache[key] = schedule
+    return schedule
+
+
+def _text_mask(text_valid, text_len: int, visual: int, device) -> torch.Tensor:
+    valid = torch.arange(text_len, device=device)[None] < text_valid.to(device)[:, None]
+    ones = torch.ones(valid.shape[0], visual, dtype=torch.bool, device=device)
+    return torch.cat((valid, ones), dim=1)
+
+
+def planned_attention(queries, keys, values, plan, *, text_keys=None, text_values=None,
+                      text_valid=None):
+    """Run a plan; returns one output per query chunk (``[B, N_c, H, D]``)."""
+    q0 = queries[0]
+    use_kernel = (native.use(q0) and q0.shape[-1] == 128
+                  and not _has_tangent(*queries, *keys, *values))
+    if use_kernel:
+        from .attention_native import planned
+
+        return planned(queries, keys, values, plan, text_keys, text_values, text_valid)
+    text_len = 0 if text_keys is None else text_keys.shape[1]
+    # Queries with identical key lists share one softmax call.
+    groups: dict[tuple[int, ...], list[int]] = {}
+    for index, visible in enumerate(plan):
+        groups.setdefault(tuple(visible), []).append(index)
+    outputs: list[torch.Tensor | None] = [None] * len(queries)
+    for visible, members in groups.items():
+        ks = [keys[j] for j in visible]
+        vs = [values[j] for j in visible]
+        if text_len:
+            ks, vs = [text_keys, *ks], [text_values, *vs]
+        key = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
+        value = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]
+        mask = None
+        if text_len:
+            mask = _text_mask(text_valid, text_len, key.shape[1] - text_len, key.device)
+        query = torch.cat([queries[i] for i in members], dim=1) if len(members) > 1 \
+            else queries[members[0]]
+        out = attention(query, key, value, mask)
+        for i, piece in zip(members, out.split([queries[i].shape[1] for i in members], dim=1)):
+            outputs[i] = piece
+    return outputs

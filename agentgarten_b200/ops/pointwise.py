@@ -1,0 +1,145 @@
+"""Row-wise and element-wise operators with hand-written forward/backward kernels.
+
+Parity: the fused serving kernels of the reference (``wm/kernels/gen_layer.py:29-119``:
+RMSNorm with optional residual add, per-head RMSNorm + rotary, SiLU·mul) and the
+rectified-flow pointwise steps (``wm/models/flow.py:49-59``).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import native, reference
+
+__all__ = ["head_norm_rope", "rf_interpolate", "rf_x0", "rms_norm", "rms_norm_add", "rotary",
+           "silu_mul"]
+
+
+def _plain(*tensors: torch.Tensor) -> bool:
+    """Kernels handle the ordinary reverse-mode/no-grad case; exotic autograd modes
+    (forward-mode duals, double backward) go through the PyTorch definitions."""
+    import torch.autograd.forward_ad as fwAD
+
+    return not any(fwAD.unpack_dual(t).tangent is not None for t in tensors)
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        C = native.ext()
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        out, rstd = C.rms_norm_fwd(x2, weight.contiguous(), float(eps))
+        native.count()
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return out.view(x.shape)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        C = native.ext()
+        x2, weight, rstd = ctx.saved_tensors
+        g2 = grad.reshape(-1, grad.shape[-1]).contiguous()
+        dx, dw = C.rms_norm_bwd(g2, x2, weight.contiguous(), rstd)
+        native.count(2)
+        return dx.view(ctx.shape), dw.to(weight.dtype), None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if native.use(x) and weight.dtype == x.dtype and _plain(x, weight) and x.shape[-1] % 8 == 0:
+        return _RMSNorm.apply(x, weight, eps)
+    return reference.rms_norm(x, weight, eps)
+
+
+def rms_norm_add(x, addend, weight, eps):
+    if native.use(x) and not torch.is_grad_enabled() and weight.dtype == x.dtype:
+        C = native.ext()
+        shape = x.shape
+        total, out = C.rms_norm_add_fwd(
+            x.reshape(-1, shape[-1]).contiguous(), addend.reshape(-1, shape[-1]).contiguous(),
+            weight.contiguous(), float(eps))
+        native.count()
+        return total.view(shape), out.view(shape)
+    total = x + addend
+    return total, rms_norm(total, weight, eps)
+
+
+def rotary(value, cos, sin):
+    return reference.rotary(value, cos, sin)
+
+
+class _HeadNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, value, weight, cos, sin, eps):
+        C = native.ext()
+        value = value.contiguous()
+        out, rstd = C.head_norm_rope_fwd(value, weight.contiguous(), cos.contiguous(),
+                                         sin.contiguous(), float(eps))
+        native.count()
+        ctx.save_for_backward(value, weight, cos, sin, rstd)
+        return out
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        C = native.ext()
+        value, weight, cos, sin, rstd = ctx.saved_tensors
+        dx, dw = C.head_norm_rope_bwd(grad.contiguous(), value, weight.contiguous(),
+                                      cos.contiguous(), sin.contiguous(), rstd)
+        native.count(2)
+        return dx, dw.to(weight.dtype), None, None, None
+
+
+def head_norm_rope(value, weight, cos, sin, eps):
+    """Per-head RMSNorm over ``D`` then rotate-half RoPE; ``value`` is ``[B, N, H, D]``."""
+    if (native.use(value) and value.shape[-1] == 128 and weight.dtype == value.dtype
+            and cos.dtype == value.dtype and _plain(value, weight)):
+        return _HeadNormRope.apply(value, weight, cos, sin, eps)
+    return reference.head_norm_rope(value, weight, cos, sin, eps)
+
+
+class _SiluMul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        C = native.ext()
+        gate, up = gate.contiguous(), up.contiguous()
+        ctx.save_for_backward(gate, up)
+        native.count()
+        return C.silu_mul_fwd(gate, up)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        C = native.ext()
+        gate, up = ctx.saved_tensors
+        native.count()
+        dgate, dup = C.silu_mul_bwd(grad.contiguous(), gate, up)
+        return dgate, dup
+
+
+def silu_mul(gate, up):
+    if native.use(gate) and _plain(gate, up) and gate.numel() % 8 == 0:
+        return _SiluMul.apply(gate, up)
+    return reference.silu_mul(gate, up)
+
+
+def rf_interpolate(x0, noise, sigma):
+    """``(1 - sigma) * x0 + sigma * noise`` with ``sigma`` ``[B]`` or ``[B, T]``."""
+    if (native.use(x0, dtypes=(torch.float32, torch.bfloat16)) and x0.ndim == 5
+            and not torch.is_grad_enabled() and x0.dtype == noise.dtype and _plain(x0, noise)):
+        C = native.ext()
+        native.count()
+        return C.rf_combine(x0.contiguous(), noise.contiguous(), sigma.float().contiguous(), 0)
+    return reference.rf_interpolate(x0, noise, sigma)
+
+
+def rf_x0(noisy, sigma, velocity):
+    """``noisy - sigma * velocity``."""
+    if (native.use(noisy, dtypes=(torch.float32, torch.bfloat16)) and noisy.ndim == 5
+            and not torch.is_grad_enabled() and noisy.dtype == velocity.dtype
+            and _plain(noisy, velocity)):
+        C = native.ext()
+        native.count()
+        return C.rf_combine(noisy.contiguous(), velocity.contiguous(),
+                            sigma.float().contiguous(), 1)
+    return reference.rf_x0(noisy, sigma, velocity)

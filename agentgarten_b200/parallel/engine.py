@@ -1,0 +1,168 @@
+"""Placement of a network on the job's GPUs.
+
+``parallelize_network`` casts a network to its parameter dtype, materialises meta
+parameters on the device, enables context parallelism, installs activation recomputation
+and records the data-parallel group the network's gradients are reduced over.
+
+Data parallelism is *sharded-optimizer replication*: on a B200 (180 GB) the bf16
+parameters of a 7 B tower are kept whole on every GPU, so no parameter all-gather sits in
+front of every layer; gradients are reduce-scattered once per update, each rank runs Adam
+on its shard of the FP32 master/moment state, and the updated bf16 shards are written
+straight into every peer's parameter buffer.  The three steps are one peer-memory kernel
+pair (see :mod:`agentgarten_b200.parallel.zero`).  Shard ownership follows the
+"chunk dim 0 per parameter" rule of FSDP2, so sharded checkpoints are interchangeable.
+
+Parity: reference ``wm/infra/parallel.py:58-254`` (``ParallelConfig``, meshes, activation
+checkpointing, FSDP2 wrapping, meta materialisation).
+"""
+
+from __future__ import annotations
+
+from collections.abc import Mapping
+from dataclasses import dataclass, field
+from enum import StrEnum
+from math import prod
+from typing import Any
+
+import torch
+import torch.distributed as dist
+from torch import nn
+from torch.utils.checkpoint import checkpoint
+
+from agentgarten_b200.infra.distributed import get_local_world_size
+
+from .network import ParallelNetwork
+
+__all__ = [
+    "ATTENTION_SAVE_OPS",
+    "ActivationCheckpointing",
+    "ParallelConfig",
+    "ParallelNetwork",
+    "init_meshes",
+    "parallelize_network",
+]
+
+# Names of the operators whose outputs are kept under selective recomputation.
+ATTENTION_SAVE_OPS = (r"scaled_dot_product", r"flash_attn", r"fmha")
+
+
+class ActivationCheckpointing(StrEnum):
+    NONE = "none"
+    SELECTIVE = "selective"
+    FULL = "full"
+
+
+@dataclass(frozen=True)
+class ParallelConfig:
+    parameter_dtype: str = "bfloat16"
+    fully_shard: bool = True
+    # None: one shard group over all ranks of a node; (nodes, local) on several nodes.
+    fsdp_mesh_shape: tuple[int, ...] | None = None
+    context_parallel_size: int = 1
+    activation_checkpointing: ActivationCheckpointing = ActivationCheckpointing.SELECTIVE
+    selective_save_ops: tuple[str, ...] = ATTENTION_SAVE_OPS
+    # Accepted for recipe compatibility; kernels here are hand-written, nothing is traced.
+    compile: bool = True
+    compile_dynamic: bool = False
+    compile_options: Mapping[str, Any] = field(default_factory=dict)
+    reduce_dtype: str = "float32"
+    reshard_after_forward: bool = True
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "activation_checkpointing",
+                           ActivationCheckpointing(self.activation_checkpointing))
+        for name in ("parameter_dtype", "reduce_dtype"):
+            if not isinstance(getattr(torch, getattr(self, name), None), torch.dtype):
+                raise ValueError(f"{name} must name a torch dtype, got {getattr(self, name)!r}")
+        if self.context_parallel_size < 1:
+            raise ValueError("context_parallel_size must be positive")
+        if self.fsdp_mesh_shape is not None:
+            object.__setattr__(self, "fsdp_mesh_shape", tuple(int(v) for v in self.fsdp_mesh_shape))
+        object.__setattr__(self, "selective_save_ops", tuple(self.selective_save_ops))
+        object.__setattr__(self, "compile_options", dict(self.compile_options))
+
+
+_MESHES: dict[tuple, tuple[Any, Any]] = {}
+
+
+def init_meshes(config: ParallelConfig, device_type: str):
+    """Return ``(shard_mesh, cp_mesh)``; either may be ``None``.
+
+    The shard mesh spans every rank (1-D, or ``(replicate, shard)`` across nodes).  The CP
+    mesh is the inner dimension of a separate ``(world // cp, cp)`` mesh, so CP ranks are
+    also shard ranks.
+    """
+    if not (dist.is_available() and dist.is_initialized()):
+        return None, None
+    from torch.distributed.device_mesh import init_device_mesh
+
+    world = dist.get_world_size()
+    local = get_local_world_size()
+    shape = config.fsdp_mesh_shape
+    if shape is None and config.fully_shard and 0 < local < world and world % local == 0:
+        shape = (world // local, local)
+    key = (device_type, world, config.fully_shard, config.context_parallel_size, shape)
+    if key in _MESHES:
+        return _MESHES[key]
+    shard_mesh = None
+    if config.fully_shard:
+        shape = shape or (world,)
+        if prod(shape) != world:
+            raise ValueError(f"fsdp_mesh_shape {shape} does not cover {world} ranks")
+        names = ("shard",) if len(shape) == 1 else ("replicate", "shard")
+        shard_mesh = init_device_mesh(device_type, shape, mesh_dim_names=names)
+    cp_mesh = None
+    cp = config.context_parallel_size
+    if cp > 1:
+        if world % cp:
+            raise ValueError(f"context_parallel_size {cp} does not divide {world} ranks")
+        cp_mesh = init_device_mesh(device_type, (world // cp, cp),
+                                   mesh_dim_names=("rest", "cp"))["cp"]
+    _MESHES[key] = (shard_mesh, cp_mesh)
+    return shard_mesh, cp_mesh
+
+
+def _install_recompute(layer: nn.Module) -> None:
+    """Make ``layer(...)`` run under activation recomputation whenever grad is enabled.
+
+    Only the bound ``forward`` of the instance is replaced, so module names and state-dict
+    keys stay exactly those of the plain layer.
+    """
+    if getattr(layer, "_agb_recompute", False):
+        return
+    inner = layer.forward
+
+    def forward(*args, **kwargs):
+        if not torch.is_grad_enabled():
+            return inner(*args, **kwargs)
+        return checkpoint(inner, *args, use_reentrant=False, preserve_rng_state=True, **kwargs)
+
+    layer.forward = forward
+    layer._agb_recompute = True
+
+
+def parallelize_network(network: ParallelNetwork, config: ParallelConfig, device):
+    """Place ``network`` and return its context-parallel mesh (or ``None``)."""
+    device = torch.device(device)
+    dtype = getattr(torch, config.parameter_dtype)
+    on_meta = any(p.is_meta for p in network.parameters())
+    if on_meta:
+        network.to(dtype=dtype)
+    else:
+        network.to(device=device, dtype=dtype)
+    shard_mesh, cp_mesh = init_meshes(config, device.type)
+    if cp_mesh is not None:
+        network.enable_context_parallel(cp_mesh)
+    mode = config.activation_checkpointing
+    network.activation_checkpointing = mode
+    if mode is not ActivationCheckpointing.NONE:
+        # The fused CUDA layer keeps attention outputs and recomputes the rest by itself
+        # (= "selective"); the op-by-op path recomputes the whole layer.
+        for layer in network.layers:
+            _install_recompute(layer)
+    network.shard_mesh = shard_mesh
+    network.parallel_config = config
+    if on_meta:
+        network.to_empty(device=device)
+        network.initialize_after_materialization()
+    return cp_mesh

@@ -1,0 +1,115 @@
+"""Tensor-tree helpers, seeding and scoped module state.
+
+Parity: reference ``wm/infra/utils.py:30-138``.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import os
+import random
+from collections.abc import Callable, Iterator, Mapping
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+__all__ = [
+    "frozen_parameters",
+    "map_tensors",
+    "prefetch",
+    "preserve_training_mode",
+    "set_random_seed",
+    "to",
+]
+
+
+def map_tensors(value: Any, transform: Callable[[torch.Tensor], torch.Tensor]) -> Any:
+    """Apply ``transform`` to every tensor of a nested container.
+
+    Containers whose leaves all come back unchanged are returned as the same object, so
+    callers can test ``result is value`` to see whether anything moved.
+    """
+
+    def visit(item: Any) -> Any:
+        if isinstance(item, torch.Tensor):
+            return transform(item)
+        if isinstance(item, Mapping):
+            out = {key: visit(child) for key, child in item.items()}
+            same = all(out[key] is item[key] for key in item)
+            return item if same else type(item)(out) if isinstance(item, dict) else out
+        if isinstance(item, tuple) and hasattr(item, "_fields"):
+            out = [visit(child) for child in item]
+            return item if all(a is b for a, b in zip(out, item)) else type(item)(*out)
+        if isinstance(item, (list, tuple)):
+            out = [visit(child) for child in item]
+            return item if all(a is b for a, b in zip(out, item)) else type(item)(out)
+        return item
+
+    return visit(value)
+
+
+def to(value: Any, device: torch.device | str | None = None, dtype: torch.dtype | None = None,
+       non_blocking: bool = True) -> Any:
+    """Move tensors of a tree; ``dtype`` only applies to floating tensors."""
+
+    def move(tensor: torch.Tensor) -> torch.Tensor:
+        target = dtype if (dtype is not None and tensor.is_floating_point()) else None
+        return tensor.to(device=device, dtype=target, non_blocking=non_blocking)
+
+    return map_tensors(value, move)
+
+
+def set_random_seed(seed: int, by_rank: bool = False) -> None:
+    if by_rank and dist.is_available() and dist.is_initialized():
+        seed = seed + dist.get_rank()
+    random.seed(seed)
+    np.random.seed(seed % (2**32))
+    torch.manual_seed(seed)
+
+
+@contextlib.contextmanager
+def preserve_training_mode(model: torch.nn.Module) -> Iterator[None]:
+    modes = {module: module.training for module in model.modules()}
+    try:
+        yield
+    finally:
+        for module, mode in modes.items():
+            module.training = mode
+
+
+@contextlib.contextmanager
+def frozen_parameters(module: torch.nn.Module) -> Iterator[None]:
+    """Temporarily mark all parameters as not requiring grad."""
+    flags = [(p, p.requires_grad) for p in module.parameters()]
+    try:
+        for p, _ in flags:
+            p.requires_grad_(False)
+        yield
+    finally:
+        for p, flag in flags:
+            p.requires_grad_(flag)
+
+
+def prefetch(path: str | Path, *, threads: int = 16, chunk: int = 64 << 20) -> None:
+    """Warm the page cache of ``path`` with parallel positional reads."""
+    size = os.path.getsize(path)
+    fd = os.open(path, os.O_RDONLY)
+    try:
+        def read(start: int) -> None:
+            remaining = min(chunk, size - start)
+            offset = start
+            while remaining > 0:
+                got = os.preadv(fd, [bytearray(min(remaining, 8 << 20))], offset)
+                if got <= 0:
+                    break
+                offset += got
+                remaining -= got
+
+        with ThreadPoolExecutor(max_workers=threads) as pool:
+            list(pool.map(read, range(0, size, chunk)))
+    finally:
+        os.close(fd)
