@@ -1,0 +1,100 @@
+// Host-callable launchers of the sm_100a kernels (plain C++ interface, no torch types).
+// Every launcher enqueues on the given stream and returns a cudaError_t; none allocates.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace agb {
+
+// Human-readable reason of the last failure reported by a launcher on this host thread.
+void set_error_detail(const char* text);
+const char* error_detail();
+
+// ------------------------------------------------------------------------------- GEMM
+// out[M, N] (+)= op(A) * op(B)^T-style product with bf16 inputs and fp32 accumulation.
+//   a_mn_major = 0: A stored [M, K] (K contiguous);  1: A stored [K, M] (M contiguous)
+//   b_mn_major = 0: B stored [N, K] (K contiguous);  1: B stored [K, N] (N contiguous)
+// Strides (lda, ldb) are in elements of the stored row.  Epilogue, in this order:
+//   acc (+ bias[n]) (+ residual[m, n]) (+ out[m, n] if accumulate) -> out (bf16 or fp32)
+struct GemmArgs {
+  const void* a;
+  const void* b;
+  void* out;
+  const void* bias;      // bf16 [N] or null
+  const void* residual;  // bf16 [M, N] (ld = ldr) or null
+  int64_t lda, ldb, ldo, ldr;
+  int m, n, k;
+  int a_mn_major, b_mn_major;
+  int out_fp32;    // 1: out is float, 0: out is bf16
+  int accumulate;  // 1: add the previous contents of out
+  int* status;     // device status word (0 = ok) or null
+};
+cudaError_t gemm_bf16(const GemmArgs& args, int sm_count, cudaStream_t stream);
+
+
+// -------------------------------------------------------------------------- pointwise
+// All tensors bf16 unless stated.  `addend` may be null (plain RMSNorm); with it,
+// total_out = bf16(x + addend) is written and normalised.  rstd (fp32 [rows]) may be null.
+cudaError_t rms_norm_fwd(const void* x, const void* addend, const void* w, void* total_out,
+                         void* out, float* rstd, int64_t rows, int width, float eps,
+                         cudaStream_t stream);
+// dw_partial is fp32 [rms_norm_bwd_partials(rows), width]; the caller sums it over dim 0.
+int rms_norm_bwd_partials(int64_t rows);
+cudaError_t rms_norm_bwd(const void* grad, const void* x, const void* w, const float* rstd,
+                         void* dx, float* dw_partial, int64_t rows, int width,
+                         cudaStream_t stream);
+// x [rows, heads, 128]; cos/sin [rows, 128]; rstd fp32 [rows, heads] (may be null in fwd).
+cudaError_t head_norm_rope_fwd(const void* x, const void* w, const void* cosv, const void* sinv,
+                               void* out, float* rstd, int64_t rows, int heads, float eps,
+                               cudaStream_t stream);
+int head_norm_rope_bwd_partials(int64_t rows, int heads);  // rows of the fp32 [.,128] partial
+cudaError_t head_norm_rope_bwd(const void* grad, const void* x, const void* w, const void* cosv,
+                               const void* sinv, const float* rstd, void* dx, float* dw_partial,
+                               int64_t rows, int heads, cudaStream_t stream);
+cudaError_t silu_mul_fwd(const void* gate, const void* up, void* out, int64_t elements,
+                         cudaStream_t stream);
+cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, void* dgate,
+                         void* dup, int64_t elements, cudaStream_t stream);
+// mode 0: (1-s)*a + s*b; mode 1: a - s*b.  sigma fp32 [batch, sigma_frames]
+// (sigma_frames is 1 or frames); a/b/out are [batch, channels, frames, hw], fp32 or bf16.
+cudaError_t rf_combine(const void* a, const void* b, const float* sigma, void* out, int64_t batch,
+                       int64_t channels, int frames, int hw, int sigma_frames, int mode,
+                       int is_bf16, cudaStream_t stream);
+
+// -------------------------------------------------------------------------- attention
+// Segment-list flash attention, head_dim 128, bf16.  q [B, NQ, Hq, 128], k/v [B, NK, Hkv, 128]
+// and optional text k/v [B, text_len, Hkv, 128]; strides in elements.  out has the layout
+// of q (contiguous), lse is fp32 [B, Hq, NQ].  q_tiles is int32 [num_q_tiles, 5]
+// (q_row, rows, first_entry, entries, q_local); entries int32 [*, 3] (source, k_row, k_len)
+// with source 0 = text, 1 = visual, 2 = visual with a causal mask against the chunk.
+struct AttnArgs {
+  const void* q; const void* k; const void* v;
+  const void* text_k; const void* text_v;   // may be null
+  void* out; float* lse;
+  const int* q_tiles; const int* entries; const int* text_valid;
+  int64_t nq, nk, text_len, batch;
+  int64_t q_row_stride, q_batch_stride, kv_row_stride, kv_batch_stride;
+  int64_t text_row_stride, text_batch_stride;
+  int hq, hkv, num_q_tiles;
+  float scale;
+  int* status;
+};
+cudaError_t attention_fwd(const AttnArgs& args, cudaStream_t stream);
+
+// Backward of attention_fwd.  `fwd` carries the forward tensors (out and lse filled in);
+// grad_out/dq have the layout of out, dk/dv the dense layout [B, NK, Hkv, 128]; rows of
+// dk/dv that no query can see must be zeroed by the caller; delta is fp32 scratch
+// [B, Hq, NQ].  k_tiles int32 [num_k_tiles, 5] (k_row, rows, first_reader, readers, -1),
+// q_lists int32 [*, 2] (q_row, q_len).  Text keys receive no gradient.
+struct AttnBwdArgs {
+  AttnArgs fwd;
+  const void* grad_out;
+  void* dq; void* dk; void* dv;
+  float* delta;
+  const int* k_tiles; const int* q_lists;
+  int num_k_tiles;
+};
+cudaError_t attention_bwd(const AttnBwdArgs& args, cudaStream_t stream);
+
+}  // namespace agb

@@ -1,0 +1,617 @@
+// Flash-attention backward on tcgen05 (head_dim 128, bf16, grouped KV heads, segment lists).
+//
+// Three kernels, all deterministic (no atomics):
+//   attn_delta   delta[b, h, q] = sum_d dO * O                      (row-wise, HBM-bound)
+//   attn_dq      one CTA per (query tile, query head, sample) walks the key tiles of the
+//                tile's segments:  S = Q K^T, dP = dO V^T, dS = P o (dP - delta) * scale,
+//                dQ += dS K.  Text keys take part (they shape P) but get no gradient.
+//   attn_dkdv    one CTA per (visual key tile, KV head, sample) walks every query tile that
+//                sees it, for the query heads of its group, in a fixed order:
+//                S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q.
+// Probabilities are recomputed from the saved log-sum-exp.  P / dS are handed to the tensor
+// core as packed bf16 in TMEM (A operand), K/V/Q/dO tiles are read from shared memory both
+// K-major (for the score products) and MN-major (for the gradient products) without any
+// transposed copy: the same swizzled tile serves both descriptors.
+#include "agb.h"
+#include "attention_common.cuh"
+#include "tensormap.h"
+
+namespace agb {
+namespace {
+
+constexpr int TILE_BYTES = 128 * 128 * 2;
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int BWD_THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ---------------------------------------------------------------------------- delta
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ out,
+                                                         const __nv_bfloat16* __restrict__ grad,
+                                                         float* __restrict__ delta, int64_t nq,
+                                                         int hq, int64_t units) {
+  // one warp per (b, q, h); delta laid out [B, Hq, NQ]
+  const int64_t unit = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (unit >= units) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 a = *reinterpret_cast<const uint2*>(out + unit * 128 + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(grad + unit * 128 + lane * 4);
+  float s = bf16_lo(a.x) * bf16_lo(g.x) + bf16_hi(a.x) * bf16_hi(g.x) +
+            bf16_lo(a.y) * bf16_lo(g.y) + bf16_hi(a.y) * bf16_hi(g.y);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) {
+    const int h = int(unit % hq);
+    const int64_t bq = unit / hq;
+    const int64_t b = bq / nq, q = bq % nq;
+    delta[(b * hq + h) * nq + q] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------- dQ
+// smem: Q, dO (resident) + K, V rings (2 stages).  TMEM: S [0,128) dP [128,256)
+// dQ [256,384) dS0 [384,448) dS1 [448,512).
+constexpr int DQ_SMEM = 6 * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512;
+
+struct DqParams {
+  const int* q_tiles;
+  const int* entries;
+  const int* text_valid;
+  const float* lse;    // [B, Hq, NQ]
+  const float* delta;  // [B, Hq, NQ]
+  __nv_bfloat16* dq;   // [B, NQ, Hq, 128]
+  int nq, hq, group;
+  float scale, scale_log2;
+  int* status;
+};
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+               const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_vt,
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+               const DqParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sdO = smem + TILE_BYTES;
+  uint8_t* sK = smem + 2 * TILE_BYTES;
+  uint8_t* sV = smem + 4 * TILE_BYTES;
+  KeyTile* tiles = reinterpret_cast<KeyTile*>(smem + 6 * TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + ATT_MAX_TILES);
+  uint64_t* q_full = bars;        // Q and dO
+  uint64_t* kv_full = bars + 1;   // [2]
+  uint64_t* kv_empty = bars + 3;  // [2]
+  uint64_t* sp_full = bars + 5;   // S and dP of the current tile are in TMEM
+  uint64_t* sp_free = bars + 6;   // softmax has read them out (count 4)
+  uint64_t* ds_ready = bars + 7;  // [2] (count 4)
+  uint64_t* dq_done = bars + 9;   // [2] dQ product of a tile finished (dS buffer free)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* n_tiles_smem = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / p.group;
+  const int* qt = p.q_tiles + 5 * blockIdx.x;
+  const int q_row = qt[0], q_rows = qt[1], q_local = qt[4];
+  const WaitGuard guard{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    mbar_init(sp_full, 1);
+    mbar_init(sp_free, 4);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&ds_ready[i], 4);
+      mbar_init(&dq_done[i], 1);
+    }
+    mbar_fence_init();
+    int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
+    if (n < 0) {
+      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+      n = 0;
+    }
+    *n_tiles_smem = n;
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_tiles = *n_tiles_smem;
+  constexpr uint32_t C_S = 0, C_DP = 128, C_DQ = 256, C_DS = 384;
+
+  if (warp == 4) {
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(q_full, 2 * TILE_BYTES);
+      tma_load_3d(sQ, &tm_q, q_full, head * ATT_D, q_row, batch);
+      tma_load_3d(sQ + HALF_BYTES, &tm_q, q_full, head * ATT_D + 64, q_row, batch);
+      tma_load_3d(sdO, &tm_do, q_full, head * ATT_D, q_row, batch);
+      tma_load_3d(sdO + HALF_BYTES, &tm_do, q_full, head * ATT_D + 64, q_row, batch);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const KeyTile t = tiles[j];
+        const CUtensorMap* mk = t.source == 0 ? &tm_kt : &tm_k;
+        const CUtensorMap* mv = t.source == 0 ? &tm_vt : &tm_v;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+        tma_load_3d(sK + st * TILE_BYTES, mk, &kv_full[st], kv_head * ATT_D, t.row, batch);
+        tma_load_3d(sK + st * TILE_BYTES + HALF_BYTES, mk, &kv_full[st], kv_head * ATT_D + 64, t.row, batch);
+        tma_load_3d(sV + st * TILE_BYTES, mv, &kv_full[st], kv_head * ATT_D, t.row, batch);
+        tma_load_3d(sV + st * TILE_BYTES + HALF_BYTES, mv, &kv_full[st], kv_head * ATT_D + 64, t.row, batch);
+      }
+      if (!ok || *abort_flag) {
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 100000ull) {}
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && n_tiles > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both K-major
+      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);  // B MN-major
+      const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
+      bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma);
+      auto issue_scores = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
+        if (j >= 1 && !mbar_wait(sp_free, (j - 1) & 1, guard, kTimeoutMma)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_S, make_smem_desc(q_addr + off, 16, 1024),
+                    make_smem_desc(k_addr + off, 16, 1024), idesc_kk, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_DP, make_smem_desc(do_addr + off, 16, 1024),
+                    make_smem_desc(v_addr + off, 16, 1024), idesc_kk, kk != 0);
+        }
+        tc_commit(sp_full);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1, buf = j & 1;
+        // scores of the next tile run while the softmax warps still work on this one
+        if (j + 1 < n_tiles && !issue_scores(j + 1)) { ok = false; break; }
+        if (!mbar_wait(&ds_ready[buf], (j >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          tc_mma_ts(tmem_base + C_DQ, tmem_base + C_DS + buf * 64 + kk * 8,
+                    make_smem_desc(k_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn,
+                    (j | kk) != 0);
+        }
+        tc_commit(&kv_empty[st]);
+        tc_commit(&dq_done[buf]);
+      }
+    }
+  } else {
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const int my_row = warp * 32 + lane;
+    const bool row_ok = my_row < q_rows;
+    const int64_t stat_index = (int64_t(batch) * p.hq + head) * p.nq + q_row + my_row;
+    const bool in_range = q_row + my_row < p.nq;
+    const float lse2 = in_range ? p.lse[stat_index] * LOG2E : 0.f;
+    const float delta = in_range ? p.delta[stat_index] : 0.f;
+    bool ok = n_tiles > 0;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int buf = j & 1;
+      const KeyTile t = tiles[j];
+      if (!mbar_wait(sp_full, j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (j >= 2 && !mbar_wait(&dq_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutSoftmax)) {
+        ok = false;
+        break;
+      }
+      int valid = t.valid;
+      if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
+      if (!row_ok) valid = 0;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[2][32], d[2][32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32(tmem_base + lane_base + C_S + half * 64 + c * 32, s[c]);
+          tmem_ld_32x32(tmem_base + lane_base + C_DP + half * 64 + c * 32, d[c]);
+        }
+        tmem_ld_wait();
+        if (half == 1) {
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sp_free);
+        }
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float ds2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = 2 * i + e;  // within this half
+            const float sv = __uint_as_float(s[col >> 5][col & 31]);
+            const float dp = __uint_as_float(d[col >> 5][col & 31]);
+            const float prob = (half * 64 + col < valid) ? exp2f(sv * p.scale_log2 - lse2) : 0.f;
+            ds2[e] = prob * (dp - delta) * p.scale;
+          }
+          packed[i] = pack_bf16(ds2[0], ds2[1]);
+        }
+        tmem_st_32x32(tmem_base + lane_base + C_DS + buf * 64 + half * 32, packed);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_ready[buf]);
+    }
+    if (ok) {
+      const int last = n_tiles - 1;
+      ok = mbar_wait(&dq_done[last & 1], (last >> 1) & 1, guard, kTimeoutEpilogue);
+    }
+    if (n_tiles == 0 || ok) {
+      tc_fence_after_sync();
+      __nv_bfloat16* dst = p.dq + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32(tmem_base + lane_base + C_DQ + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+            v.y = pack_bf16(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+            v.z = pack_bf16(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+            v.w = pack_bf16(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------- dK / dV
+// smem: K, V (resident) + Q, dO rings (2 stages) + per-item lse/delta vectors.
+// TMEM: S^T [0,128) dP^T [128,256) dV [256,384) dK [384,512); the packed bf16 P^T / dS^T
+// overwrite the first 64 columns of S^T / dP^T once those have been read into registers.
+constexpr int DKV_MAX_ITEMS = 2048;
+constexpr int DKV_SMEM =
+    6 * TILE_BYTES + DKV_MAX_ITEMS * 8 + 2 * 2 * 128 * 4 + 1024 + 512;
+
+struct DkvParams {
+  const int* k_tiles;  // [tiles, 5]: k_row, rows, first_reader, readers, causal (unused)
+  const int* q_lists;  // [*, 2]: q_row, q_len
+  const float* lse;
+  const float* delta;
+  __nv_bfloat16* dk;  // [B, NK, Hkv, 128]
+  __nv_bfloat16* dv;
+  int nq, nk, hq, hkv, group;
+  float scale, scale_log2;
+  int* status;
+};
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                const DkvParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;   // [2 stages]
+  uint8_t* sdO = smem + 4 * TILE_BYTES;  // [2 stages]
+  int2* items = reinterpret_cast<int2*>(smem + 6 * TILE_BYTES);  // (q_row, rows | head << 8)
+  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);  // [2][2][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * 128);
+  uint64_t* kv_full = bars;
+  uint64_t* qd_full = bars + 1;    // [2]
+  uint64_t* qd_empty = bars + 3;   // [2]
+  uint64_t* st_full = bars + 5;    // S^T, dP^T ready
+  uint64_t* pt_ready = bars + 6;   // P^T, dS^T written (count 4)
+  uint64_t* grad_done = bars + 7;  // dV/dK products of an item finished
+  uint64_t* stats_bar = bars + 8;  // lse/delta of an item staged by all 128 threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* n_items_smem = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kv_head = blockIdx.y, batch = blockIdx.z;
+  const int* kt = p.k_tiles + 5 * blockIdx.x;
+  const int k_row = kt[0], k_rows = kt[1];
+  const WaitGuard guard{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(kv_full, 1);
+    mbar_init(st_full, 1);
+    mbar_init(pt_ready, 4);
+    mbar_init(grad_done, 1);
+    mbar_init(stats_bar, 128);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qd_full[i], 1);
+      mbar_init(&qd_empty[i], 1);
+    }
+    mbar_fence_init();
+    int n = 0;
+    bool overflow = false;
+    for (int g = 0; g < p.group && !overflow; ++g) {
+      const int head = kv_head * p.group + g;
+      for (int r = kt[2]; r < kt[2] + kt[3] && !overflow; ++r) {
+        const int q0 = p.q_lists[2 * r], len = p.q_lists[2 * r + 1];
+        for (int off = 0; off < len; off += ATT_BM) {
+          if (n >= DKV_MAX_ITEMS) { overflow = true; break; }
+          items[n++] = make_int2(q0 + off, min(ATT_BM, len - off) | (head << 8));
+        }
+      }
+    }
+    if (overflow) {
+      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+      n = 0;
+    }
+    *n_items_smem = n;
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_items = *n_items_smem;
+  constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
+
+  if (warp == 4) {
+    if (lane == 0 && n_items > 0) {
+      mbar_expect_tx(kv_full, 2 * TILE_BYTES);
+      tma_load_3d(sK, &tm_k, kv_full, kv_head * ATT_D, k_row, batch);
+      tma_load_3d(sK + HALF_BYTES, &tm_k, kv_full, kv_head * ATT_D + 64, k_row, batch);
+      tma_load_3d(sV, &tm_v, kv_full, kv_head * ATT_D, k_row, batch);
+      tma_load_3d(sV + HALF_BYTES, &tm_v, kv_full, kv_head * ATT_D + 64, k_row, batch);
+      bool ok = true;
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int st = i & 1;
+        const int2 it = items[i];
+        const int head = it.y >> 8;
+        if (!mbar_wait(&qd_empty[st], ((i >> 1) & 1) ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&qd_full[st], 2 * TILE_BYTES);
+        tma_load_3d(sQ + st * TILE_BYTES, &tm_q, &qd_full[st], head * ATT_D, it.x, batch);
+        tma_load_3d(sQ + st * TILE_BYTES + HALF_BYTES, &tm_q, &qd_full[st], head * ATT_D + 64, it.x, batch);
+        tma_load_3d(sdO + st * TILE_BYTES, &tm_do, &qd_full[st], head * ATT_D, it.x, batch);
+        tma_load_3d(sdO + st * TILE_BYTES + HALF_BYTES, &tm_do, &qd_full[st], head * ATT_D + 64, it.x, batch);
+      }
+      if (!ok || *abort_flag) {
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 100000ull) {}
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && n_items > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);
+      const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      bool ok = mbar_wait(kv_full, 0, guard, kTimeoutMma);
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(&qd_full[st], (i >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + st * TILE_BYTES);
+        // S^T = K Q^T and dP^T = V dO^T (all operands K-major over d).  MMAs of one thread
+        // execute in issue order, so these overwrite the P^T/dS^T columns only after the
+        // gradient products of the previous item have consumed them.
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_ST, make_smem_desc(k_addr + off, 16, 1024),
+                    make_smem_desc(q_addr + off, 16, 1024), idesc_kk, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_DPT, make_smem_desc(v_addr + off, 16, 1024),
+                    make_smem_desc(do_addr + off, 16, 1024), idesc_kk, kk != 0);
+        }
+        tc_commit(st_full);
+        if (!mbar_wait(pt_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after_sync();
+        // dV += P^T dO and dK += dS^T Q: A from TMEM (K-major over q), B MN-major (d contiguous)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + kk * 8,
+                    make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn, (i | kk) != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + kk * 8,
+                    make_smem_desc(q_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn, (i | kk) != 0);
+        }
+        tc_commit(&qd_empty[st]);
+        tc_commit(grad_done);
+      }
+    }
+  } else {
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const int tid = threadIdx.x;  // 0..127: key row of this thread, and the q column it stages
+    bool ok = n_items > 0;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const int2 it = items[i];
+      const int head = it.y >> 8, rows = it.y & 0xff;
+      float* my_stats = stats + (i & 1) * 256;
+      {
+        const int q = it.x + tid;
+        const bool valid = tid < rows && q < p.nq;
+        const int64_t idx = (int64_t(batch) * p.hq + head) * p.nq + q;
+        my_stats[tid] = valid ? p.lse[idx] * LOG2E : INFINITY;  // +inf => probability 0
+        my_stats[128 + tid] = valid ? p.delta[idx] : 0.f;
+      }
+      mbar_arrive(stats_bar);
+      if (!mbar_wait(stats_bar, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(st_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[2][32], d[2][32];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32(tmem_base + lane_base + C_ST + half * 64 + c * 32, s[c]);
+          tmem_ld_32x32(tmem_base + lane_base + C_DPT + half * 64 + c * 32, d[c]);
+        }
+        tmem_ld_wait();
+        uint32_t pp[32], dd[32];
+#pragma unroll
+        for (int k2 = 0; k2 < 32; ++k2) {
+          float pv[2], dv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int col = 2 * k2 + e;
+            const int qc = half * 64 + col;
+            const float sv = __uint_as_float(s[col >> 5][col & 31]);
+            const float dp = __uint_as_float(d[col >> 5][col & 31]);
+            const float prob = exp2f(sv * p.scale_log2 - my_stats[qc]);
+            pv[e] = prob;
+            dv[e] = prob * (dp - my_stats[128 + qc]) * p.scale;
+          }
+          pp[k2] = pack_bf16(pv[0], pv[1]);
+          dd[k2] = pack_bf16(dv[0], dv[1]);
+        }
+        // the packed halves land in columns this thread has already read
+        tmem_st_32x32(tmem_base + lane_base + C_ST + half * 32, pp);
+        tmem_st_32x32(tmem_base + lane_base + C_DPT + half * 32, dd);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pt_ready);
+    }
+    if (ok) ok = mbar_wait(grad_done, (n_items - 1) & 1, guard, kTimeoutEpilogue);
+    if (ok) {
+      tc_fence_after_sync();
+      const bool row_ok = tid < k_rows;
+      const int64_t base = ((int64_t(batch) * p.nk + k_row + tid) * p.hkv + kv_head) * ATT_D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + base;
+        const uint32_t col0 = which == 0 ? C_DV : C_DK;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32(tmem_base + lane_base + col0 + c * 32, o);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+              v.y = pack_bf16(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+              v.z = pack_bf16(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+              v.w = pack_bf16(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = v;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+bool make_rows_map_bwd(CUtensorMap* map, const void* base, int heads, int64_t rows, int64_t batch,
+                       int64_t row_stride, int64_t batch_stride) {
+  const uint64_t dims[3] = {uint64_t(heads) * ATT_D, uint64_t(rows), uint64_t(batch)};
+  const uint64_t strides[2] = {uint64_t(row_stride) * 2, uint64_t(batch_stride) * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  return make_tensor_map_bf16(map, base, 3, dims, strides, box);
+}
+
+cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
+  const AttnArgs& a = b.fwd;
+  if (a.num_q_tiles == 0 || a.batch == 0) return cudaSuccess;
+  CUtensorMap tq, tdo, tkt, tvt, tk, tv;
+  const int64_t dense_row = int64_t(a.hq) * ATT_D;
+  if (!make_rows_map_bwd(&tq, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride) ||
+      !make_rows_map_bwd(&tdo, b.grad_out, a.hq, a.nq, a.batch, dense_row, dense_row * a.nq) ||
+      !make_rows_map_bwd(&tk, a.k, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride) ||
+      !make_rows_map_bwd(&tv, a.v, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride)) {
+    set_error_detail("attention_bwd: tensor map refused by the driver");
+    return cudaErrorInvalidValue;
+  }
+  if (a.text_k) {
+    if (!make_rows_map_bwd(&tkt, a.text_k, a.hkv, a.text_len, a.batch, a.text_row_stride,
+                           a.text_batch_stride) ||
+        !make_rows_map_bwd(&tvt, a.text_v, a.hkv, a.text_len, a.batch, a.text_row_stride,
+                           a.text_batch_stride)) {
+      set_error_detail("attention_bwd: text tensor map refused by the driver");
+      return cudaErrorInvalidValue;
+    }
+  } else {
+    tkt = tk;
+    tvt = tv;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_dq_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               DKV_SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int64_t units = a.batch * a.nq * a.hq;
+  attn_delta_kernel<<<unsigned((units + 7) / 8), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(a.out), static_cast<const __nv_bfloat16*>(b.grad_out),
+      b.delta, a.nq, a.hq, units);
+  const float scale_log2 = a.scale * LOG2E;
+  {
+    DqParams p;
+    p.q_tiles = a.q_tiles; p.entries = a.entries; p.text_valid = a.text_valid;
+    p.lse = a.lse; p.delta = b.delta; p.dq = static_cast<__nv_bfloat16*>(b.dq);
+    p.nq = int(a.nq); p.hq = a.hq; p.group = a.hq / a.hkv;
+    p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
+    dim3 grid(a.num_q_tiles, a.hq, unsigned(a.batch));
+    attn_dq_kernel<<<grid, BWD_THREADS, DQ_SMEM, stream>>>(tq, tdo, tkt, tvt, tk, tv, p);
+  }
+  if (b.num_k_tiles > 0) {
+    DkvParams p;
+    p.k_tiles = b.k_tiles; p.q_lists = b.q_lists; p.lse = a.lse; p.delta = b.delta;
+    p.dk = static_cast<__nv_bfloat16*>(b.dk); p.dv = static_cast<__nv_bfloat16*>(b.dv);
+    p.nq = int(a.nq); p.nk = int(a.nk); p.hq = a.hq; p.hkv = a.hkv; p.group = a.hq / a.hkv;
+    p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
+    dim3 grid(b.num_k_tiles, a.hkv, unsigned(a.batch));
+    attn_dkv_kernel<<<grid, BWD_THREADS, DKV_SMEM, stream>>>(tq, tdo, tk, tv, p);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace agb

@@ -1,0 +1,367 @@
+// Flash-attention forward on tcgen05 for head_dim 128 with grouped KV heads and
+// segment-list keys (text prefix with per-sample valid length + visual segments).
+//
+// One CTA per (query tile of 128 rows, query head, sample):
+//   warps 0-3  softmax: one query row per thread; S tile TMEM -> registers, online softmax
+//              in the exp2 domain, probabilities written back to TMEM as packed bf16
+//   warp 4     TMA producer: Q once, then K and V tiles through 2-stage rings
+//   warp 5     MMA issuer:   S = Q K^T (operands in shared memory) and O += P V with P read
+//              from TMEM, both accumulating in TMEM
+// S is double-buffered so the tensor core computes S[j+1] while the softmax works on S[j].
+// The running output stays in TMEM and is rescaled lazily: only when a row maximum grows
+// by more than 2^8 does a warp rescale its 32 rows of O.
+//
+// TMEM columns: S0 [0,128) S1 [128,256) O [256,384) P0 [384,448) P1 [448,512).
+#include "agb.h"
+#include "attention_common.cuh"
+#include "tensormap.h"
+
+namespace agb {
+namespace {
+
+constexpr int KV_STAGES = 2;
+constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: a 128x128 bf16 tile (2 atoms of 16 KiB)
+constexpr int HALF_BYTES = TILE_BYTES / 2;
+constexpr int FWD_THREADS = 192;
+constexpr int SMEM_TILES = 1 + 2 * KV_STAGES;  // Q + K ring + V ring
+constexpr int FWD_SMEM = SMEM_TILES * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512;
+
+constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+struct FwdParams {
+  const int* q_tiles;     // [tiles, 5]: q_row, rows, first_entry, entries, q_local
+  const int* entries;     // [*, 3]
+  const int* text_valid;  // [B] or null
+  __nv_bfloat16* out;     // [B, NQ, Hq, 128]
+  float* lse;             // [B, Hq, NQ] natural-log LSE
+  int nq, hq, group;      // group = Hq / Hkv
+  float scale_log2;       // softmax scale * log2(e)
+  int* status;
+};
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kt,
+                const __grid_constant__ CUtensorMap tm_vt, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
+  KeyTile* tiles = reinterpret_cast<KeyTile*>(sV + KV_STAGES * TILE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + ATT_MAX_TILES);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2]
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [2] MMA -> softmax
+  uint64_t* s_free = bars + 11;       // [2] softmax -> MMA (S buffer read out)
+  uint64_t* p_ready = bars + 13;      // [2] softmax -> MMA
+  uint64_t* pv_done = bars + 15;      // [2] MMA -> softmax (P buffer free, O stable)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* n_tiles_smem = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / p.group;
+  const int* qt = p.q_tiles + 5 * blockIdx.x;
+  const int q_row = qt[0], q_rows = qt[1], q_local = qt[4];
+  const WaitGuard guard{abort_flag, p.status};
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 4);
+      mbar_init(&p_ready[i], 4);
+      mbar_init(&pv_done[i], 1);
+    }
+    mbar_fence_init();
+    int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
+    if (n < 0) {
+      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+      n = 0;
+    }
+    *n_tiles_smem = n;
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const int n_tiles = *n_tiles_smem;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_tiles > 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_3d(sQ, &tm_q, q_full, head * ATT_D, q_row, batch);
+      tma_load_3d(sQ + HALF_BYTES, &tm_q, q_full, head * ATT_D + 64, q_row, batch);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const uint32_t ph = (j / KV_STAGES) & 1;
+        const KeyTile t = tiles[j];
+        const CUtensorMap* mk = t.source == 0 ? &tm_kt : &tm_k;
+        const CUtensorMap* mv = t.source == 0 ? &tm_vt : &tm_v;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        tma_load_3d(sK + st * TILE_BYTES, mk, &k_full[st], kv_head * ATT_D, t.row, batch);
+        tma_load_3d(sK + st * TILE_BYTES + HALF_BYTES, mk, &k_full[st], kv_head * ATT_D + 64, t.row, batch);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        tma_load_3d(sV + st * TILE_BYTES, mv, &v_full[st], kv_head * ATT_D, t.row, batch);
+        tma_load_3d(sV + st * TILE_BYTES + HALF_BYTES, mv, &v_full[st], kv_head * ATT_D + 64, t.row, batch);
+      }
+      if (!ok || *abort_flag) {
+        // give in-flight copies time to land before shared memory is released
+        const uint64_t start = global_timer_ns();
+        while (global_timer_ns() - start < 100000ull) {}
+      }
+    }
+  } else if (warp == 5) {
+    // -------------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      // S = Q K^T: both K-major, 8 k-steps of 16 over d = 128 (two 64-wide atoms).
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
+      // O += P V: A = P from TMEM (K-major), B = V MN-major (d contiguous), 8 k-steps over keys.
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);
+      const uint32_t q_addr = smem_u32(sQ);
+      bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j % KV_STAGES, buf = j & 1;
+        if (!mbar_wait(&k_full[st], (j / KV_STAGES) & 1, guard, kTimeoutMma)) return false;
+        if (j >= 2 && !mbar_wait(&s_free[buf], ((j - 2) >> 1) & 1, guard, kTimeoutMma)) return false;
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + COL_S + buf * 128, make_smem_desc(q_addr + off, 16, 1024),
+                    make_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0);
+        }
+        tc_commit(&k_empty[st]);
+        tc_commit(&s_full[buf]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
+        const int st = j % KV_STAGES, buf = j & 1;
+        if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait(&p_ready[buf], (j >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          // 16 keys per step: P advances 8 packed columns, V advances 16 rows (2048 B).
+          tc_mma_ts(tmem_base + COL_O, tmem_base + COL_P + buf * 64 + kk * 8,
+                    make_smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), idesc_o,
+                    (j | kk) != 0);
+        }
+        tc_commit(&v_empty[st]);
+        tc_commit(&pv_done[buf]);
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------------- softmax
+    const uint32_t lane_base = uint32_t(warp * 32) << 16;
+    const int my_row = warp * 32 + lane;        // row within the query tile
+    float m_ref = -INFINITY;                    // reference maximum (log2 domain)
+    float l_sum = 0.f;
+    bool ok = n_tiles > 0;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int buf = j & 1;
+      const KeyTile t = tiles[j];
+      if (!mbar_wait(&s_full[buf], (j >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      tc_fence_after_sync();
+      uint32_t s[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_base + COL_S + buf * 128 + c * 32, s[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[buf]);
+
+      int valid = t.valid;
+      if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float v = __uint_as_float(s[c][i]) * p.scale_log2;
+          v = (c * 32 + i < valid) ? v : -INFINITY;
+          s[c][i] = __float_as_uint(v);
+          m_tile = fmaxf(m_tile, v);
+        }
+      // Lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform.
+      const bool grow = m_tile > m_ref + RESCALE_THRESHOLD;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, m_tile);
+        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+        if (j > 0) {
+          // O must be stable: the previous PV product has to be complete.
+          if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, guard, kTimeoutSoftmax)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(tmem_base + lane_base + COL_O + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(tmem_base + lane_base + COL_O + c * 32, o);
+          }
+          tmem_st_wait();
+        }
+        l_sum *= alpha;
+        m_ref = m_new;
+      }
+      // A fully masked row (causal tiles above the diagonal never occur, but rows past the
+      // chunk end may see valid <= 0) keeps m_ref = -inf: exponentials are forced to zero.
+      const float shift = (m_ref == -INFINITY) ? 0.f : m_ref;
+      if (j >= 2 && !mbar_wait(&pv_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutSoftmax)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t packed[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          // columns (2i, 2i+1) of the 64-key half c
+          const float a = exp2f(__uint_as_float(s[2 * c + (i >> 4)][(2 * i) & 31]) - shift);
+          const float b = exp2f(__uint_as_float(s[2 * c + (i >> 4)][(2 * i + 1) & 31]) - shift);
+          l_sum += a + b;
+          packed[i] = pack_bf16(a, b);
+        }
+        tmem_st_32x32(tmem_base + lane_base + COL_P + buf * 64 + c * 32, packed);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[buf]);
+    }
+    // ---------------------------------------------------------------------- epilogue
+    if (ok) {
+      const int last = n_tiles - 1;
+      ok = mbar_wait(&pv_done[last & 1], (last >> 1) & 1, guard, kTimeoutEpilogue);
+    }
+    if (n_tiles == 0 || ok) {
+      tc_fence_after_sync();
+      const float inv = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
+      const bool row_ok = my_row < q_rows;
+      __nv_bfloat16* dst =
+          p.out + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32(tmem_base + lane_base + COL_O + c * 32, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = v;
+          }
+        }
+      }
+      if (row_ok && p.lse) {
+        const float lse = (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+        p.lse[(int64_t(batch) * p.hq + head) * p.nq + q_row + my_row] = lse;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+bool make_rows_map(CUtensorMap* map, const void* base, int heads, int64_t rows, int64_t batch,
+                   int64_t row_stride, int64_t batch_stride) {
+  // dims (head*128 contiguous, rows, batch); box = 64 columns x 128 rows.
+  const uint64_t dims[3] = {uint64_t(heads) * ATT_D, uint64_t(rows), uint64_t(batch)};
+  const uint64_t strides[2] = {uint64_t(row_stride) * 2, uint64_t(batch_stride) * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  return make_tensor_map_bf16(map, base, 3, dims, strides, box);
+}
+
+cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t stream) {
+  if (a.num_q_tiles == 0 || a.batch == 0) return cudaSuccess;
+  CUtensorMap tq, tkt, tvt, tk, tv;
+  if (!make_rows_map(&tq, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride) ||
+      !make_rows_map(&tk, a.k, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride) ||
+      !make_rows_map(&tv, a.v, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride))
+    return cudaErrorInvalidValue;
+  if (a.text_k) {
+    if (!make_rows_map(&tkt, a.text_k, a.hkv, a.text_len, a.batch, a.text_row_stride,
+                       a.text_batch_stride) ||
+        !make_rows_map(&tvt, a.text_v, a.hkv, a.text_len, a.batch, a.text_row_stride,
+                       a.text_batch_stride))
+      return cudaErrorInvalidValue;
+  } else {
+    tkt = tk;
+    tvt = tv;
+  }
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  FwdParams p;
+  p.q_tiles = a.q_tiles;
+  p.entries = a.entries;
+  p.text_valid = a.text_valid;
+  p.out = static_cast<__nv_bfloat16*>(a.out);
+  p.lse = a.lse;
+  p.nq = int(a.nq);
+  p.hq = a.hq;
+  p.group = a.hq / a.hkv;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.status = a.status;
+  dim3 grid(a.num_q_tiles, a.hq, unsigned(a.batch));
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tkt, tvt, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace agb

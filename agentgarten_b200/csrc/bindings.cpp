@@ -1,0 +1,284 @@
+// Python bindings of the sm_100a kernels (torch tensors in, torch tensors out).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+
+#include "agb.h"
+
+namespace {
+
+using torch::Tensor;
+
+cudaStream_t stream_of(const Tensor& t) {
+  return at::cuda::getCurrentCUDAStream(t.device().index()).stream();
+}
+
+void check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e), " (", agb::error_detail(), ")");
+}
+
+// One int32 status word per device; kernels write a non-zero code when a bounded wait
+// ran out or an argument was rejected on the device.
+Tensor status_word(int device) {
+  static std::map<int, Tensor> words;
+  auto it = words.find(device);
+  if (it == words.end()) {
+    auto w = torch::zeros({1}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+    it = words.emplace(device, w).first;
+  }
+  return it->second;
+}
+
+int sm_count(int device) { return at::cuda::getDeviceProperties(device)->multiProcessorCount; }
+
+void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16, name, " must be a bf16 CUDA tensor");
+}
+
+// out = op(a) @ op(b) (+ bias) (+ residual) (+ out)
+Tensor gemm(const Tensor& a, const Tensor& b, bool trans_a, bool trans_b,
+            c10::optional<Tensor> out_opt, bool accumulate, c10::optional<Tensor> bias,
+            c10::optional<Tensor> residual, torch::ScalarType out_dtype) {
+  check_bf16(a, "a");
+  check_bf16(b, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm operands must be 2-D");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm operands must have unit inner stride");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int64_t m = trans_a ? a.size(1) : a.size(0);
+  const int64_t k = trans_a ? a.size(0) : a.size(1);
+  const int64_t n = trans_b ? b.size(0) : b.size(1);
+  TORCH_CHECK((trans_b ? b.size(1) : b.size(0)) == k, "gemm inner dimensions differ");
+  Tensor out;
+  if (out_opt.has_value()) {
+    out = *out_opt;
+    TORCH_CHECK(out.dim() == 2 && out.size(0) == m && out.size(1) == n && out.stride(1) == 1,
+                "gemm out has the wrong shape");
+  } else {
+    TORCH_CHECK(!accumulate, "accumulate needs out");
+    out = torch::empty({m, n}, a.options().dtype(out_dtype));
+  }
+  TORCH_CHECK(out.scalar_type() == torch::kBFloat16 || out.scalar_type() == torch::kFloat32,
+              "gemm out must be bf16 or fp32");
+  agb::GemmArgs g{};
+  g.a = a.data_ptr();
+  g.b = b.data_ptr();
+  g.out = out.data_ptr();
+  g.lda = a.stride(0);
+  g.ldb = b.stride(0);
+  g.ldo = out.stride(0);
+  if (bias.has_value()) {
+    check_bf16(*bias, "bias");
+    TORCH_CHECK(bias->numel() == n && bias->is_contiguous(), "bias must be [N]");
+    g.bias = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    TORCH_CHECK(residual->dim() == 2 && residual->size(0) == m && residual->size(1) == n &&
+                    residual->stride(1) == 1, "residual must be [M, N]");
+    g.residual = residual->data_ptr();
+    g.ldr = residual->stride(0);
+  }
+  g.m = int(m);
+  g.n = int(n);
+  g.k = int(k);
+  g.a_mn_major = trans_a ? 1 : 0;
+  g.b_mn_major = trans_b ? 0 : 1;
+  g.out_fp32 = out.scalar_type() == torch::kFloat32;
+  g.accumulate = accumulate;
+  g.status = status_word(a.device().index()).data_ptr<int>();
+  check(agb::gemm_bf16(g, sm_count(a.device().index()), stream_of(a)), "gemm_bf16");
+  return out;
+}
+
+std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const Tensor& w, double eps) {
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  auto rstd = torch::empty({x.size(0)}, x.options().dtype(torch::kFloat32));
+  check(agb::rms_norm_fwd(x.data_ptr(), nullptr, w.data_ptr(), nullptr, out.data_ptr(),
+                          rstd.data_ptr<float>(), x.size(0), int(x.size(1)), float(eps),
+                          stream_of(x)), "rms_norm_fwd");
+  return {out, rstd};
+}
+
+std::tuple<Tensor, Tensor> rms_norm_add_fwd(const Tensor& x, const Tensor& addend, const Tensor& w,
+                                            double eps) {
+  check_bf16(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto total = torch::empty_like(x);
+  auto out = torch::empty_like(x);
+  check(agb::rms_norm_fwd(x.data_ptr(), addend.data_ptr(), w.data_ptr(), total.data_ptr(),
+                          out.data_ptr(), nullptr, x.size(0), int(x.size(1)), float(eps),
+                          stream_of(x)), "rms_norm_add_fwd");
+  return {total, out};
+}
+
+std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& grad, const Tensor& x, const Tensor& w,
+                                        const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = torch::empty_like(x);
+  const int parts = agb::rms_norm_bwd_partials(x.size(0));
+  auto partial = torch::empty({parts, x.size(1)}, x.options().dtype(torch::kFloat32));
+  check(agb::rms_norm_bwd(grad.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                          dx.data_ptr(), partial.data_ptr<float>(), x.size(0), int(x.size(1)),
+                          stream_of(x)), "rms_norm_bwd");
+  return {dx, partial.sum(0)};
+}
+
+std::tuple<Tensor, Tensor> head_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& cosv,
+                                              const Tensor& sinv, double eps) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 4 && x.size(3) == 128, "x must be [B, N, H, 128]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0) * x.size(1);
+  const int heads = int(x.size(2));
+  auto out = torch::empty_like(x);
+  auto rstd = torch::empty({rows, heads}, x.options().dtype(torch::kFloat32));
+  check(agb::head_norm_rope_fwd(x.data_ptr(), w.data_ptr(), cosv.data_ptr(), sinv.data_ptr(),
+                                out.data_ptr(), rstd.data_ptr<float>(), rows, heads, float(eps),
+                                stream_of(x)), "head_norm_rope_fwd");
+  return {out, rstd};
+}
+
+std::tuple<Tensor, Tensor> head_norm_rope_bwd(const Tensor& grad, const Tensor& x, const Tensor& w,
+                                              const Tensor& cosv, const Tensor& sinv,
+                                              const Tensor& rstd) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = x.size(0) * x.size(1);
+  const int heads = int(x.size(2));
+  auto dx = torch::empty_like(x);
+  const int parts = agb::head_norm_rope_bwd_partials(rows, heads);
+  auto partial = torch::zeros({parts, 128}, x.options().dtype(torch::kFloat32));
+  check(agb::head_norm_rope_bwd(grad.data_ptr(), x.data_ptr(), w.data_ptr(), cosv.data_ptr(),
+                                sinv.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                                partial.data_ptr<float>(), rows, heads, stream_of(x)),
+        "head_norm_rope_bwd");
+  return {dx, partial.sum(0)};
+}
+
+Tensor silu_mul_fwd(const Tensor& gate, const Tensor& up) {
+  check_bf16(gate, "gate");
+  c10::cuda::CUDAGuard guard(gate.device());
+  auto out = torch::empty_like(gate);
+  check(agb::silu_mul_fwd(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(),
+                          stream_of(gate)), "silu_mul_fwd");
+  return out;
+}
+
+std::tuple<Tensor, Tensor> silu_mul_bwd(const Tensor& grad, const Tensor& gate, const Tensor& up) {
+  c10::cuda::CUDAGuard guard(gate.device());
+  auto dgate = torch::empty_like(gate);
+  auto dup = torch::empty_like(gate);
+  check(agb::silu_mul_bwd(grad.data_ptr(), gate.data_ptr(), up.data_ptr(), dgate.data_ptr(),
+                          dup.data_ptr(), gate.numel(), stream_of(gate)), "silu_mul_bwd");
+  return {dgate, dup};
+}
+
+Tensor rf_combine(const Tensor& a, const Tensor& b, const Tensor& sigma, int64_t mode) {
+  TORCH_CHECK(a.dim() == 5 && a.is_contiguous() && b.is_contiguous(), "expected [B,C,T,H,W]");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto out = torch::empty_like(a);
+  const int sigma_frames = sigma.dim() == 1 ? 1 : int(sigma.size(1));
+  check(agb::rf_combine(a.data_ptr(), b.data_ptr(), sigma.data_ptr<float>(), out.data_ptr(),
+                        a.size(0), a.size(1), int(a.size(2)), int(a.size(3) * a.size(4)),
+                        sigma_frames, int(mode), a.scalar_type() == torch::kBFloat16, stream_of(a)),
+        "rf_combine");
+  return out;
+}
+
+// q [B,NQ,Hq,128]; k/v [B,NK,Hkv,128]; optional text k/v [B,NT,Hkv,128]; returns (out, lse)
+std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v,
+                                    c10::optional<Tensor> text_k, c10::optional<Tensor> text_v,
+                                    c10::optional<Tensor> text_valid, const Tensor& q_tiles,
+                                    const Tensor& entries, double scale) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(v, "v");
+  TORCH_CHECK(q.dim() == 4 && q.size(3) == 128 && k.dim() == 4 && k.size(3) == 128, "head_dim must be 128");
+  TORCH_CHECK(q.stride(3) == 1 && q.stride(2) == 128 && k.stride(3) == 1 && k.stride(2) == 128 &&
+                  v.stride(3) == 1 && v.stride(2) == 128 && k.strides() == v.strides(),
+              "q/k/v must be dense over (head, dim)");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto out = torch::empty({q.size(0), q.size(1), q.size(2), 128}, q.options());
+  auto lse = torch::empty({q.size(0), q.size(2), q.size(1)}, q.options().dtype(torch::kFloat32));
+  agb::AttnArgs a{};
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.out = out.data_ptr(); a.lse = lse.data_ptr<float>();
+  a.q_tiles = q_tiles.data_ptr<int>(); a.entries = entries.data_ptr<int>();
+  a.nq = q.size(1); a.nk = k.size(1); a.batch = q.size(0);
+  a.q_row_stride = q.stride(1); a.q_batch_stride = q.stride(0);
+  a.kv_row_stride = k.stride(1); a.kv_batch_stride = k.stride(0);
+  if (text_k.has_value()) {
+    check_bf16(*text_k, "text_k");
+    TORCH_CHECK(text_k->strides() == text_v->strides() && text_k->stride(2) == 128, "text k/v layout");
+    a.text_k = text_k->data_ptr(); a.text_v = text_v->data_ptr();
+    a.text_len = text_k->size(1);
+    a.text_row_stride = text_k->stride(1); a.text_batch_stride = text_k->stride(0);
+  }
+  if (text_valid.has_value()) a.text_valid = text_valid->data_ptr<int>();
+  a.hq = int(q.size(2)); a.hkv = int(k.size(2)); a.num_q_tiles = int(q_tiles.size(0));
+  a.scale = float(scale);
+  a.status = status_word(q.device().index()).data_ptr<int>();
+  check(agb::attention_fwd(a, stream_of(q)), "attention_fwd");
+  return {out, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(
+    const Tensor& grad, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+    const Tensor& lse, c10::optional<Tensor> text_k, c10::optional<Tensor> text_v,
+    c10::optional<Tensor> text_valid, const Tensor& q_tiles, const Tensor& entries,
+    const Tensor& k_tiles, const Tensor& q_lists, double scale) {
+  check_bf16(grad, "grad");
+  TORCH_CHECK(grad.is_contiguous() && out.is_contiguous(), "grad/out must be contiguous");
+  TORCH_CHECK(q.stride(2) == 128 && k.stride(2) == 128 && k.strides() == v.strides(), "q/k/v layout");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto dq = torch::empty({q.size(0), q.size(1), q.size(2), 128}, q.options());
+  auto dk = torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
+  auto dv = torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
+  auto delta = torch::empty({q.size(0), q.size(2), q.size(1)}, q.options().dtype(torch::kFloat32));
+  agb::AttnBwdArgs b{};
+  agb::AttnArgs& a = b.fwd;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.out = out.data_ptr(); a.lse = lse.data_ptr<float>();
+  a.q_tiles = q_tiles.data_ptr<int>(); a.entries = entries.data_ptr<int>();
+  a.nq = q.size(1); a.nk = k.size(1); a.batch = q.size(0);
+  a.q_row_stride = q.stride(1); a.q_batch_stride = q.stride(0);
+  a.kv_row_stride = k.stride(1); a.kv_batch_stride = k.stride(0);
+  if (text_k.has_value()) {
+    a.text_k = text_k->data_ptr(); a.text_v = text_v->data_ptr();
+    a.text_len = text_k->size(1);
+    a.text_row_stride = text_k->stride(1); a.text_batch_stride = text_k->stride(0);
+  }
+  if (text_valid.has_value()) a.text_valid = text_valid->data_ptr<int>();
+  a.hq = int(q.size(2)); a.hkv = int(k.size(2)); a.num_q_tiles = int(q_tiles.size(0));
+  a.scale = float(scale);
+  a.status = status_word(q.device().index()).data_ptr<int>();
+  b.grad_out = grad.data_ptr();
+  b.dq = dq.data_ptr(); b.dk = dk.data_ptr(); b.dv = dv.data_ptr();
+  b.delta = delta.data_ptr<float>();
+  b.k_tiles = k_tiles.data_ptr<int>(); b.q_lists = q_lists.data_ptr<int>();
+  b.num_k_tiles = int(k_tiles.size(0));
+  check(agb::attention_bwd(b, stream_of(q)), "attention_bwd");
+  return {dq, dk, dv};
+}
+
+Tensor status(int64_t device) { return status_word(int(device)); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rms_norm_fwd", &rms_norm_fwd);
+  m.def("rms_norm_add_fwd", &rms_norm_add_fwd);
+  m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("head_norm_rope_fwd", &head_norm_rope_fwd);
+  m.def("head_norm_rope_bwd", &head_norm_rope_bwd);
+  m.def("silu_mul_fwd", &silu_mul_fwd);
+  m.def("silu_mul_bwd", &silu_mul_bwd);
+  m.def("rf_combine", &rf_combine);
+  m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
+  m.def("status", &status);
+}

@@ -1,0 +1,58 @@
+#include "tensormap.h"
+
+#include "agb.h"
+
+#include <mutex>
+
+namespace agb {
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) ==
+            cudaSuccess &&
+        result == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+}  // namespace
+
+namespace {
+thread_local const char* g_detail = "";
+}
+void set_error_detail(const char* text) { g_detail = text; }
+const char* error_detail() { return g_detail; }
+
+bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdims[3];
+  cuuint64_t gstrides[2];
+  cuuint32_t gbox[3];
+  cuuint32_t estrides[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) gstrides[i] = strides_bytes[i];
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                  const_cast<void*>(base), gdims, gstrides, gbox, estrides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace agb

@@ -97,9 +97,11 @@ def attention(q, k, v, key_mask=None, causal: bool = False):
 class AttentionSchedule:
     """Device-side work lists for the segment flash kernels (all int32).
 
-    ``q_tiles[t] = (q_row, rows, first_entry, entries)``; ``entries[e] = (source, k_row,
-    k_len)`` with source 0 = text (valid length per sample), 1 = visual.  ``k_tiles`` and
-    ``q_lists`` are the transposed lists used by the dK/dV pass.
+    ``q_tiles[t] = (q_row, rows, first_entry, entries, q_local)`` where ``q_local`` is the
+    tile's first row counted from its chunk start; ``entries[e] = (source, k_row, k_len)``
+    with source 0 = text (valid length per sample), 1 = visual, 2 = visual under a causal
+    mask against the chunk.  ``k_tiles[t] = (k_row, rows, first_reader, readers, causal)``
+    and ``q_lists[r] = (q_row, q_len)`` are the transposed lists used by the dK/dV pass.
     """
 
     q_tiles: torch.Tensor
@@ -115,8 +117,8 @@ _schedule_cache: dict = {}
 
 
 def build_schedule(q_sizes: list[int], k_sizes: list[int], plan: list[list[int]],
-                   text_len: int, device: torch.device) -> AttentionSchedule:
-    key = (tuple(q_sizes), tuple(k_sizes), tuple(map(tuple, plan)), text_len, str(device))
+                   text_len: int, device: torch.device, causal: bool = False) -> AttentionSchedule:
+    key = (tuple(q_sizes), tuple(k_sizes), tuple(map(tuple, plan)), text_len, str(device), causal)
     cached = _schedule_cache.get(key)
     if cached is not None:
         return cached
@@ -131,11 +133,11 @@ def build_schedule(q_sizes: list[int], k_sizes: list[int], plan: list[list[int]]
         if text_len:
             entries.append((0, 0, text_len))
         for j in plan[chunk]:
-            entries.append((1, k_start[j], k_sizes[j]))
+            entries.append((2 if causal else 1, k_start[j], k_sizes[j]))
             readers[j].append((q_row, size))
         count = len(entries) - first
         for offset in range(0, size, TILE):
-            q_tiles.append((q_row + offset, min(TILE, size - offset), first, count))
+            q_tiles.append((q_row + offset, min(TILE, size - offset), first, count, offset))
         q_row += size
     k_tiles, q_lists = [], []
     for j, size in enumerate(k_sizes):
@@ -145,14 +147,15 @@ def build_schedule(q_sizes: list[int], k_sizes: list[int], plan: list[list[int]]
         if count == 0:
             continue
         for offset in range(0, size, TILE):
-            k_tiles.append((k_start[j] + offset, min(TILE, size - offset), first, count))
+            k_tiles.append((k_start[j] + offset, min(TILE, size - offset), first, count,
+                            offset if causal else -1))
 
     def tensor(rows, width):
         data = torch.tensor(rows or [[0] * width], dtype=torch.int32).reshape(-1, width)
         return data.to(device)
 
     schedule = AttentionSchedule(
-        q_tiles=tensor(q_tiles, 4), entries=tensor(entries, 3), k_tiles=tensor(k_tiles, 4),
+        q_tiles=tensor(q_tiles, 5), entries=tensor(entries, 3), k_tiles=tensor(k_tiles, 5),
         q_lists=tensor(q_lists, 2), total_q=q_row, total_k=k_start[-1], text_len=text_len)
     if len(_schedule_cache) > 256:
         _schedule_cache.clear()

@@ -1,0 +1,250 @@
+"""sm_100a kernels against plain PyTorch fp32 references of the same operators."""
+
+import pytest
+import torch
+
+from agentgarten_b200 import ops
+from agentgarten_b200.ops import native, reference
+from agentgarten_b200.ops.linear import gemm
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _status_ok():
+    torch.cuda.synchronize()
+    assert int(native.ext().status(torch.cuda.current_device()).item()) == 0
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 520, 192), (1000, 1024, 4096), (514, 192, 4096)])
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
+def test_gemm_layouts(m, n, k, trans_a, trans_b):
+    torch.manual_seed(0)
+    if trans_a and m % 8:
+        m = (m + 7) // 8 * 8
+    a = torch.randn((k, m) if trans_a else (m, k), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((n, k) if trans_b else (k, n), device=DEV, dtype=torch.bfloat16)
+    out = gemm(a, b, trans_a=trans_a, trans_b=trans_b)
+    ref = (a.float().t() if trans_a else a.float()) @ (b.float().t() if trans_b else b.float())
+    _status_ok()
+    assert out.shape == ref.shape
+    assert _rel(out, ref) < 4e-3
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    m, n, k = 333, 384, 256
+    a = torch.randn(m, k, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(n, k, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ w.float().t()
+    out = gemm(a, w, bias=bias, residual=res)
+    assert _rel(out, ref + bias.float() + res.float()) < 4e-3
+    acc = torch.randn(m, n, device=DEV, dtype=torch.float32)
+    expect = acc + ref
+    gemm(a, w, out=acc, accumulate=True)
+    assert _rel(acc, expect) < 1e-3
+    accb = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    expect = accb.float() + ref
+    gemm(a, w, out=accb, accumulate=True)
+    assert _rel(accb, expect) < 4e-3
+    _status_ok()
+
+
+def test_gemm_row_invariance():
+    torch.manual_seed(2)
+    a = torch.randn(700, 512, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(768, 512, device=DEV, dtype=torch.bfloat16)
+    whole = gemm(a, w)
+    part = gemm(a[130:391].contiguous(), w)
+    assert torch.equal(whole[130:391], part)
+
+
+def test_linear_autograd():
+    torch.manual_seed(3)
+    x = torch.randn(2, 100, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(512, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = ops.linear(x, w, b)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 4e-3
+    assert _rel(x.grad, xr.grad) < 4e-3
+    assert _rel(w.grad, wr.grad) < 4e-3
+    assert _rel(b.grad, br.grad) < 1e-2
+    _status_ok()
+
+
+@pytest.mark.parametrize("rows,width", [(37, 256), (1000, 4096)])
+def test_rms_norm(rows, width):
+    torch.manual_seed(4)
+    x = torch.randn(rows, width, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(width, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    y = ops.rms_norm(x, w, 1e-6)
+    assert torch.equal(y, reference.rms_norm(x.detach(), w.detach(), 1e-6))
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = (t.detach().float().requires_grad_(True) for t in (x, w))
+    reference.rms_norm(xr, wr, 1e-6).backward(g.float())
+    assert _rel(x.grad, xr.grad) < 1e-2
+    assert _rel(w.grad, wr.grad) < 1e-2
+    total, normed = ops.rms_norm_add(x.detach(), g, w.detach(), 1e-6)
+    tr, nr = reference.rms_norm_add(x.detach(), g, w.detach(), 1e-6)
+    assert torch.equal(total, tr) and torch.equal(normed, nr)
+
+
+def test_head_norm_rope():
+    torch.manual_seed(5)
+    b, n, h = 2, 77, 4
+    x = torch.randn(b, n, h, 128, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(128, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    ang = torch.randn(b, n, 64, device=DEV) * 3
+    cos = torch.cat((ang, ang), -1).cos().to(torch.bfloat16)
+    sin = torch.cat((ang, ang), -1).sin().to(torch.bfloat16)
+    y = ops.head_norm_rope(x, w, cos, sin, 1e-6)
+    yr = reference.head_norm_rope(x.detach(), w.detach(), cos, sin, 1e-6)
+    assert (y.float() - yr.float()).abs().max() <= 2 * 2 ** -8 * yr.float().abs().max()
+    assert _rel(y, yr) < 3e-3
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr = (t.detach().float().requires_grad_(True) for t in (x, w))
+    reference.head_norm_rope(xr, wr, cos.float(), sin.float(), 1e-6).backward(g.float())
+    assert _rel(x.grad, xr.grad) < 1e-2
+    assert _rel(w.grad, wr.grad) < 1e-2
+
+
+def test_silu_mul():
+    torch.manual_seed(6)
+    a = torch.randn(123, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    b = torch.randn(123, 1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = ops.silu_mul(a, b)
+    yr = reference.silu_mul(a.detach(), b.detach())
+    assert _rel(y, yr) < 3e-3
+    g = torch.randn_like(y)
+    y.backward(g)
+    ar, br = (t.detach().float().requires_grad_(True) for t in (a, b))
+    reference.silu_mul(ar, br).backward(g.float())
+    assert _rel(a.grad, ar.grad) < 1e-2 and _rel(b.grad, br.grad) < 1e-2
+
+
+def test_rf_combine():
+    torch.manual_seed(7)
+    x0 = torch.randn(2, 48, 5, 6, 8, device=DEV)
+    noise = torch.randn_like(x0)
+    for sigma in (torch.rand(2, device=DEV), torch.rand(2, 5, device=DEV)):
+        with torch.no_grad():
+            assert torch.allclose(ops.rf_interpolate(x0, noise, sigma),
+                                  reference.rf_interpolate(x0, noise, sigma), atol=1e-6)
+            assert torch.allclose(ops.rf_x0(x0, sigma, noise), reference.rf_x0(x0, sigma, noise), atol=1e-6)
+
+
+def _attention_inputs(b, nq, nk, hq, hkv, seed):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    q = torch.randn(b, nq, hq, 128, device=DEV, dtype=torch.bfloat16, generator=g)
+    k = torch.randn(b, nk, hkv, 128, device=DEV, dtype=torch.bfloat16, generator=g)
+    v = torch.randn(b, nk, hkv, 128, device=DEV, dtype=torch.bfloat16, generator=g)
+    return q, k, v
+
+
+@pytest.mark.parametrize("nq,nk", [(128, 128), (200, 333), (517, 1100)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_attention_dense_forward(nq, nk, causal):
+    if causal:
+        nk = nq
+    q, k, v = _attention_inputs(2, nq, nk, 4, 2, 10)
+    with torch.no_grad():
+        out = ops.attention(q, k, v, causal=causal)
+        ref = reference.attention(q.float(), k.float(), v.float(), causal=causal)
+    _status_ok()
+    assert _rel(out, ref) < 6e-3
+    assert (out.float() - ref).abs().max() < 3e-2
+
+
+def test_attention_planned_forward_with_text():
+    torch.manual_seed(11)
+    b, hq, hkv = 2, 4, 2
+    sizes = [130, 260, 260, 96]
+    g = torch.Generator(device=DEV).manual_seed(12)
+    mk = lambda n, h: torch.randn(b, n, h, 128, device=DEV, dtype=torch.bfloat16, generator=g)
+    queries = [mk(n, hq) for n in sizes]
+    keys = [mk(n, hkv) for n in sizes]
+    values = [mk(n, hkv) for n in sizes]
+    text_k, text_v = mk(48, hkv), mk(48, hkv)
+    valid = torch.tensor([17, 48], device=DEV)
+    plan = [[0], [0, 1], [0, 1, 2], [0, 2, 3]]
+    with torch.no_grad():
+        outs = ops.planned_attention(queries, keys, values, plan, text_keys=text_k,
+                                     text_values=text_v, text_valid=valid)
+    _status_ok()
+    for i, visible in enumerate(plan):
+        kk = torch.cat([text_k, *[keys[j] for j in visible]], 1).float()
+        vv = torch.cat([text_v, *[values[j] for j in visible]], 1).float()
+        mask = torch.ones(b, kk.shape[1], dtype=torch.bool, device=DEV)
+        mask[:, :48] = torch.arange(48, device=DEV)[None] < valid[:, None]
+        ref = reference.attention(queries[i].float(), kk, vv, mask)
+        assert _rel(outs[i], ref) < 6e-3, i
+
+
+def test_attention_chunk_invariance():
+    """A query chunk gives bitwise the same output alone or next to other chunks."""
+    b, hq, hkv = 1, 4, 2
+    g = torch.Generator(device=DEV).manual_seed(13)
+    mk = lambda n, h: torch.randn(b, n, h, 128, device=DEV, dtype=torch.bfloat16, generator=g)
+    queries = [mk(150, hq), mk(300, hq)]
+    keys = [mk(150, hkv), mk(300, hkv)]
+    values = [mk(150, hkv), mk(300, hkv)]
+    with torch.no_grad():
+        both = ops.planned_attention(queries, keys, values, [[0], [0, 1]])
+        alone = ops.planned_attention([queries[1]], keys, values, [[0, 1]])
+    assert torch.equal(both[1], alone[0])
+
+
+def test_attention_backward_dense():
+    q, k, v = _attention_inputs(2, 300, 420, 4, 2, 20)
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+    out = ops.attention(q, k, v)
+    g = torch.randn_like(out)
+    out.backward(g)
+    _status_ok()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    reference.attention(qr, kr, vr).backward(g.float())
+    assert _rel(q.grad, qr.grad) < 2e-2
+    assert _rel(k.grad, kr.grad) < 2e-2
+    assert _rel(v.grad, vr.grad) < 2e-2
+
+
+def test_attention_backward_planned_with_text():
+    b, hq, hkv = 2, 4, 2
+    sizes = [130, 260, 96]
+    g = torch.Generator(device=DEV).manual_seed(21)
+    mk = lambda n, h: torch.randn(b, n, h, 128, device=DEV, dtype=torch.bfloat16, generator=g)
+    queries = [mk(n, hq).requires_grad_(True) for n in sizes]
+    keys = [mk(n, hkv).requires_grad_(True) for n in sizes]
+    values = [mk(n, hkv).requires_grad_(True) for n in sizes]
+    text_k, text_v = mk(48, hkv), mk(48, hkv)
+    valid = torch.tensor([17, 48], device=DEV)
+    plan = [[0], [0, 1], [0, 2]]
+    outs = ops.planned_attention(queries, keys, values, plan, text_keys=text_k,
+                                 text_values=text_v, text_valid=valid)
+    grads = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(outs, grads)
+    _status_ok()
+    qs = [t.detach().float().requires_grad_(True) for t in queries]
+    ks = [t.detach().float().requires_grad_(True) for t in keys]
+    vs = [t.detach().float().requires_grad_(True) for t in values]
+    for i, visible in enumerate(plan):
+        kk = torch.cat([text_k.float(), *[ks[j] for j in visible]], 1)
+        vv = torch.cat([text_v.float(), *[vs[j] for j in visible]], 1)
+        mask = torch.ones(b, kk.shape[1], dtype=torch.bool, device=DEV)
+        mask[:, :48] = torch.arange(48, device=DEV)[None] < valid[:, None]
+        reference.attention(qs[i], kk, vv, mask).backward(grads[i].float())
+    for mine, ref in zip([*queries, *keys, *values], [*qs, *ks, *vs]):
+        assert _rel(mine.grad, ref.grad) < 2e-2
