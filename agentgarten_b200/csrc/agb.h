@@ -97,4 +97,24 @@ struct AttnBwdArgs {
 };
 cudaError_t attention_bwd(const AttnBwdArgs& args, cudaStream_t stream);
 
+// ----------------------------------------------------------- sharded optimizer (ZeRO)
+// Base pointers of the same flat buffer on every rank of the node (index = rank).
+struct ZeroPeers {
+  void* ptr[8];
+  int world;
+};
+// units: int64 [num_units, 4] = (flat offset, state offset, count, hyper row).
+int zero_reduce_parts(int num_units, int sm_count);  // length of the partial buffers
+cudaError_t zero_reduce(const ZeroPeers& grads, const int64_t* units, int num_units,
+                        float* gshard, float* partial_sumsq, int* partial_bad, float* sumsq_out,
+                        float* bad_out, int sm_count, cudaStream_t stream);
+// hyper: fp32 [rows, 8] = lr, beta1, beta2, eps, weight_decay, 1-beta1^t, sqrt(1-beta2^t),
+// adam_w flag.  grad_scale / skip_flag: device scalars (may be null).
+// gshard may be null in both calls: zero_reduce then only produces the statistics and
+// zero_adam averages the peers' gradients itself.
+cudaError_t zero_adam(const ZeroPeers& params, const ZeroPeers& grads, const int64_t* units,
+                      int num_units, const float* gshard, float* master, float* exp_avg, float* exp_avg_sq,
+                      const float* hyper, const float* grad_scale, const float* skip_flag,
+                      int sm_count, cudaStream_t stream);
+
 }  // namespace agb

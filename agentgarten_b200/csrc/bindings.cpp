@@ -264,6 +264,48 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   return {dq, dk, dv};
 }
 
+agb::ZeroPeers peers_of(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 8, "1..8 peers supported");
+  agb::ZeroPeers p{};
+  p.world = int(ptrs.size());
+  for (size_t i = 0; i < ptrs.size(); ++i) p.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
+  return p;
+}
+
+// gshard <- mean over ranks of the owned gradient ranges; stats[0] = sum of squares,
+// stats[1] = 1 if any value is not finite.
+void zero_reduce(std::vector<int64_t> grad_ptrs, const Tensor& units,
+                 c10::optional<Tensor> gshard_opt, const Tensor& stats) {
+  c10::cuda::CUDAGuard guard(stats.device());
+  const int dev = stats.device().index();
+  float* gshard_ptr = gshard_opt.has_value() ? gshard_opt->data_ptr<float>() : nullptr;
+  const int n = int(units.size(0));
+  const int parts = agb::zero_reduce_parts(n, sm_count(dev));
+  auto psum = torch::empty({parts}, stats.options());
+  auto pbad = torch::empty({parts}, stats.options().dtype(torch::kInt32));
+  check(agb::zero_reduce(peers_of(grad_ptrs), units.data_ptr<int64_t>(), n, gshard_ptr,
+                         psum.data_ptr<float>(), pbad.data_ptr<int>(), stats.data_ptr<float>(),
+                         stats.data_ptr<float>() + 1, sm_count(dev), stream_of(stats)),
+        "zero_reduce");
+}
+
+void zero_adam(std::vector<int64_t> param_ptrs, std::vector<int64_t> grad_ptrs,
+               const Tensor& units, c10::optional<Tensor> gshard, const Tensor& master, const Tensor& exp_avg, const Tensor& exp_avg_sq,
+               const Tensor& hyper, c10::optional<Tensor> grad_scale,
+               c10::optional<Tensor> skip_flag) {
+  c10::cuda::CUDAGuard guard(master.device());
+  const int dev = master.device().index();
+  check(agb::zero_adam(peers_of(param_ptrs), peers_of(grad_ptrs), units.data_ptr<int64_t>(),
+                       int(units.size(0)),
+                       gshard.has_value() ? gshard->data_ptr<float>() : nullptr,
+                       master.data_ptr<float>(),
+                       exp_avg.data_ptr<float>(), exp_avg_sq.data_ptr<float>(),
+                       hyper.data_ptr<float>(),
+                       grad_scale.has_value() ? grad_scale->data_ptr<float>() : nullptr,
+                       skip_flag.has_value() ? skip_flag->data_ptr<float>() : nullptr,
+                       sm_count(dev), stream_of(master)), "zero_adam");
+}
+
 Tensor status(int64_t device) { return status_word(int(device)); }
 
 }  // namespace
@@ -280,5 +322,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rf_combine", &rf_combine);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("zero_reduce", &zero_reduce);
+  m.def("zero_adam", &zero_adam);
   m.def("status", &status);
 }

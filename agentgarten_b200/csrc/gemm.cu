@@ -330,7 +330,6 @@ cudaError_t gemm_bf16(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     const uint64_t strides[1] = {uint64_t(g.lda) * 2};
     const uint32_t box[2] = {64, uint32_t(g.a_mn_major ? BK : BM)};
     if (!make_tensor_map_bf16(&ta, g.a, 2, dims, strides, box)) {
-      set_error_detail("gemm: tensor map of A refused by the driver");
       return cudaErrorInvalidValue;
     }
   }
@@ -340,7 +339,6 @@ cudaError_t gemm_bf16(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     const uint64_t strides[1] = {uint64_t(g.ldb) * 2};
     const uint32_t box[2] = {64, uint32_t(g.b_mn_major ? BK : BN)};
     if (!make_tensor_map_bf16(&tb, g.b, 2, dims, strides, box)) {
-      set_error_detail("gemm: tensor map of B refused by the driver");
       return cudaErrorInvalidValue;
     }
   }

@@ -2,6 +2,7 @@
 
 #include "agb.h"
 
+#include <cstdio>
 #include <mutex>
 
 namespace agb {
@@ -39,6 +40,13 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const ui
                           const uint64_t* strides_bytes, const uint32_t* box) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
+  // The driver call needs a current context; a thread that has only used the runtime API
+  // lazily (e.g. an autograd worker) may not have bound the primary context yet.
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
   cuuint64_t gdims[3];
   cuuint64_t gstrides[2];
   cuuint32_t gbox[3];
@@ -52,6 +60,15 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const ui
                   const_cast<void*>(base), gdims, gstrides, gbox, estrides,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    static thread_local char text[256];
+    snprintf(text, sizeof(text),
+             "cuTensorMapEncodeTiled -> %d (base %p rank %d dims %llu %llu %llu stride0 %llu box %u %u)",
+             int(r), base, rank, (unsigned long long)dims[0],
+             (unsigned long long)(rank > 1 ? dims[1] : 0), (unsigned long long)(rank > 2 ? dims[2] : 0),
+             (unsigned long long)(rank > 1 ? strides_bytes[0] : 0), box[0], rank > 1 ? box[1] : 0);
+    set_error_detail(text);
+  }
   return r == CUDA_SUCCESS;
 }
 

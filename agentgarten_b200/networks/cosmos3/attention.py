@@ -97,9 +97,11 @@ class FullAttention:
 
     text: TextContext
 
+    def plan(self, chunks: int) -> list[list[int]]:
+        return [list(range(chunks))] * chunks
+
     def __call__(self, layer: int, queries: Chunks, keys: Chunks, values: Chunks) -> Chunks:
-        everything = list(range(len(keys)))
-        return _run(self.text, layer, queries, keys, values, [everything] * len(queries))
+        return _run(self.text, layer, queries, keys, values, self.plan(len(queries)))
 
 
 def block_causal_plan(chunks: int, teacher_forcing: bool, history: HistoryWindow,
@@ -128,9 +130,11 @@ class BlockCausalAttention:
     teacher_forcing: bool
     history: HistoryWindow = field(default_factory=HistoryWindow)
 
+    def plan(self, chunks: int) -> list[list[int]]:
+        return block_causal_plan(chunks, self.teacher_forcing, self.history)
+
     def __call__(self, layer: int, queries: Chunks, keys: Chunks, values: Chunks) -> Chunks:
-        plan = block_causal_plan(len(queries), self.teacher_forcing, self.history)
-        return _run(self.text, layer, queries, keys, values, plan)
+        return _run(self.text, layer, queries, keys, values, self.plan(len(queries)))
 
 
 @dataclass

@@ -302,7 +302,7 @@ class Cosmos3GenLayer(nn.Module):
     ) -> list[torch.Tensor]:
         from agentgarten_b200.ops import fused_layer
 
-        if time_embeddings is None and fused_layer.eligible(self, chunks):
+        if time_embeddings is None and fused_layer.eligible(self, chunks, attention):
             return fused_layer.run(self, chunks, ropes, attention, layer_index)
         mods = [None] * len(chunks) if time_embeddings is None else [
             self.modulation(e) for e in time_embeddings]

@@ -1,16 +1,180 @@
-"""Whole-layer execution of a generation layer on the CUDA kernels.
+"""Whole-layer execution of a generation layer on the CUDA kernels, with a hand-written
+backward.
 
-Placeholder gate: the op-by-op path in ``networks/cosmos3/layers.py`` is used until the
-fused layer (manual forward/backward over concatenated chunks, attention outputs kept,
-everything else recomputed) is enabled for a configuration.
+All chunks of a step are concatenated along tokens and pushed through the layer as one
+matrix (the GEMM and every row kernel are row-invariant, so per-row results equal those of
+chunk-by-chunk execution).  The forward keeps only the layer input, the attention output
+and its log-sum-exp; the backward recomputes the cheap parts (norms, projections, MLP
+activations) and runs the tcgen05 GEMMs for input and weight gradients, accumulating
+weight gradients straight into the parameters' ``.grad`` buffers (fp32-accumulated in
+TMEM, no temporary per microbatch).  This is the "selective" activation policy: attention
+outputs are kept, everything else is recomputed.
+
+Parity: reference ``wm/networks/cosmos3/layers.py:269-312`` (project / finish) run under
+``wm/infra/parallel.py:164-214`` (selective activation checkpointing).
 """
 
 from __future__ import annotations
 
+import torch
 
-def eligible(layer, chunks) -> bool:
-    return False
+from . import native
+from .attention import build_schedule
+
+__all__ = ["eligible", "run"]
+
+
+def _plain_linear(module) -> bool:
+    from agentgarten_b200.networks.lora import LoRALinear
+
+    return (isinstance(module, torch.nn.Linear) and not isinstance(module, LoRALinear)
+            and module.bias is None)
+
+
+def eligible(layer, chunks, attention=None) -> bool:
+    import os
+
+    if os.environ.get("AGB200_DISABLE_FUSED_LAYER") == "1":
+        return False
+    first = chunks[0]
+    if not (first.is_cuda and first.dtype == torch.bfloat16 and torch.is_grad_enabled()):
+        return False
+    if not native.available() or layer.head_dim != 128 or layer.adaln is not None:
+        return False
+    if attention is not None and not hasattr(attention, "plan"):
+        return False
+    attn, mlp = layer.self_attn, layer.mlp_moe_gen
+    linears = [*attn.parts()[:4], mlp.gate_proj, mlp.up_proj, mlp.down_proj]
+    if not all(_plain_linear(m) for m in linears):
+        return False
+    import torch.autograd.forward_ad as fwAD
+
+    return fwAD.unpack_dual(first).tangent is None
+
+
+def _gemm(a, w, **kw):
+    C = native.ext()
+    native.count()
+    return C.gemm(a, w, kw.get("trans_a", False), kw.get("trans_b", True), kw.get("out"),
+                  kw.get("accumulate", False), None, kw.get("residual"), torch.bfloat16)
+
+
+def _wgrad(weight: torch.Tensor, grad_rows: torch.Tensor, input_rows: torch.Tensor):
+    """dW[N, K] (+)= grad_rows[M, N]^T @ input_rows[M, K]; returns a tensor only when the
+    parameter has no gradient buffer yet."""
+    if not weight.requires_grad:
+        return None
+    if weight.grad is not None:
+        _gemm(grad_rows, input_rows, trans_a=True, trans_b=False, out=weight.grad, accumulate=True)
+        return None
+    return _gemm(grad_rows, input_rows, trans_a=True, trans_b=False)
+
+
+class _Layer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, layer, schedule, text_k, text_v, text_valid, *weights):
+        C = native.ext()
+        w_in, wq, wk, wv, wo, nq, nk, w_post, wg, wu, wd = weights
+        b, n, h = x.shape
+        eps, heads, kv_heads = layer.input_layernorm_moe_gen.variance_epsilon, \
+            layer.num_attention_heads, layer.num_key_value_heads
+        x2 = x.reshape(b * n, h)
+        n1, _ = C.rms_norm_fwd(x2, w_in, eps)
+        q, _ = C.head_norm_rope_fwd(_gemm(n1, wq).view(b, n, heads, 128), nq, cos, sin, eps)
+        k, _ = C.head_norm_rope_fwd(_gemm(n1, wk).view(b, n, kv_heads, 128), nk, cos, sin, eps)
+        v = _gemm(n1, wv).view(b, n, kv_heads, 128)
+        attn, lse = C.attn_fwd(q, k, v, text_k, text_v, text_valid, schedule.q_tiles,
+                               schedule.entries, 128 ** -0.5)
+        h1 = _gemm(attn.view(b * n, heads * 128), wo, residual=x2)
+        n2, _ = C.rms_norm_fwd(h1, w_post, eps)
+        act = C.silu_mul_fwd(_gemm(n2, wg), _gemm(n2, wu))
+        y = _gemm(act, wd, residual=h1)
+        native.count(7)
+        ctx.layer, ctx.schedule = layer, schedule
+        ctx.text = (text_k, text_v, text_valid)
+        ctx.params = weights  # the parameter objects themselves (their .grad buffers are used)
+        ctx.save_for_backward(x, cos, sin, attn, lse, *weights)
+        return y.view(b, n, h)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, dy):
+        C = native.ext()
+        x, cos, sin, attn, lse, *_ = ctx.saved_tensors
+        w_in, wq, wk, wv, wo, nq, nk, w_post, wg, wu, wd = ctx.params
+        layer, schedule = ctx.layer, ctx.schedule
+        text_k, text_v, text_valid = ctx.text
+        b, n, h = x.shape
+        eps, heads, kv_heads = layer.input_layernorm_moe_gen.variance_epsilon, \
+            layer.num_attention_heads, layer.num_key_value_heads
+        x2 = x.reshape(b * n, h)
+        dy2 = dy.reshape(b * n, h).contiguous()
+        attn2 = attn.view(b * n, heads * 128)
+        # ---- recompute the second half
+        h1 = _gemm(attn2, wo, residual=x2)
+        n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
+        gate, up = _gemm(n2, wg), _gemm(n2, wu)
+        act = C.silu_mul_fwd(gate, up)
+        # ---- MLP backward
+        dwd = _wgrad(wd, dy2, act)
+        dact = _gemm(dy2, wd, trans_b=False)
+        del act
+        dgate, dup = C.silu_mul_bwd(dact, gate, up)
+        del dact, gate, up
+        dwg, dwu = _wgrad(wg, dgate, n2), _wgrad(wu, dup, n2)
+        dn2 = _gemm(dgate, wg, trans_b=False)
+        _gemm(dup, wu, trans_b=False, out=dn2, accumulate=True)
+        del dgate, dup, n2
+        dh1, dw_post = C.rms_norm_bwd(dn2, h1, w_post, rstd2)
+        del dn2, h1
+        dh1.add_(dy2)
+        # ---- output projection backward
+        dwo = _wgrad(wo, dh1, attn2)
+        dattn = _gemm(dh1, wo, trans_b=False).view(b, n, heads, 128)
+        # ---- recompute the first half
+        n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
+        q_lin = _gemm(n1, wq).view(b, n, heads, 128)
+        k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
+        q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
+        k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
+        v = _gemm(n1, wv).view(b, n, kv_heads, 128)
+        dq, dk, dv = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
+                                schedule.q_tiles, schedule.entries, schedule.k_tiles,
+                                schedule.q_lists, 128 ** -0.5)
+        del dattn, q, k, v
+        dq_lin, dnq = C.head_norm_rope_bwd(dq, q_lin, nq, cos, sin, rq)
+        dk_lin, dnk = C.head_norm_rope_bwd(dk, k_lin, nk, cos, sin, rk)
+        del dq, dk, q_lin, k_lin
+        dq2, dk2, dv2 = dq_lin.view(b * n, -1), dk_lin.view(b * n, -1), dv.view(b * n, -1)
+        dwq, dwk, dwv = _wgrad(wq, dq2, n1), _wgrad(wk, dk2, n1), _wgrad(wv, dv2, n1)
+        dn1 = _gemm(dq2, wq, trans_b=False)
+        _gemm(dk2, wk, trans_b=False, out=dn1, accumulate=True)
+        _gemm(dv2, wv, trans_b=False, out=dn1, accumulate=True)
+        dx, dw_in = C.rms_norm_bwd(dn1, x2, w_in, rstd1)
+        dx.add_(dh1)
+        native.count(20)
+        cast = lambda g, w: None if g is None else g.to(w.dtype)  # noqa: E731
+        return (dx.view(b, n, h), None, None, None, None, None, None, None,
+                cast(dw_in, w_in), dwq, dwk, dwv, dwo, cast(dnq, nq), cast(dnk, nk),
+                cast(dw_post, w_post), dwg, dwu, dwd)
 
 
 def run(layer, chunks, ropes, attention, layer_index):
-    raise NotImplementedError
+    sizes = [c.shape[1] for c in chunks]
+    x = chunks[0] if len(chunks) == 1 else torch.cat(chunks, dim=1)
+    cos = ropes[0][0] if len(ropes) == 1 else torch.cat([r[0] for r in ropes], dim=1)
+    sin = ropes[0][1] if len(ropes) == 1 else torch.cat([r[1] for r in ropes], dim=1)
+    plan = attention.plan(len(chunks))
+    text = attention.text
+    text_k, text_v = text.keys[layer_index].contiguous(), text.values[layer_index].contiguous()
+    valid = text.valid_lengths.to(device=x.device, dtype=torch.int32)
+    schedule = build_schedule(sizes, sizes, plan, int(text_k.shape[1]), x.device)
+    attn, mlp = layer.self_attn, layer.mlp_moe_gen
+    to_q, to_k, to_v, to_out, norm_q, norm_k = attn.parts()
+    weights = (layer.input_layernorm_moe_gen.weight, to_q.weight, to_k.weight, to_v.weight,
+               to_out.weight, norm_q.weight, norm_k.weight,
+               layer.post_attention_layernorm_moe_gen.weight, mlp.gate_proj.weight,
+               mlp.up_proj.weight, mlp.down_proj.weight)
+    y = _Layer.apply(x.contiguous(), cos.contiguous(), sin.contiguous(), layer, schedule,
+                     text_k, text_v, valid, *weights)
+    return list(y.split(sizes, dim=1)) if len(sizes) > 1 else [y]

@@ -122,6 +122,19 @@ def init_meshes(config: ParallelConfig, device_type: str):
     return shard_mesh, cp_mesh
 
 
+def _recomputes_itself(layer: nn.Module, args, kwargs) -> bool:
+    """True when the call will take the fused CUDA layer, which keeps only the attention
+    output and recomputes the rest in its own backward."""
+    from agentgarten_b200.ops import fused_layer
+
+    if len(args) < 3 or kwargs.get("time_embeddings") is not None or len(args) > 4 and args[4] is not None:
+        return False
+    try:
+        return fused_layer.eligible(layer, args[0], args[2])
+    except Exception:
+        return False
+
+
 def _install_recompute(layer: nn.Module) -> None:
     """Make ``layer(...)`` run under activation recomputation whenever grad is enabled.
 
@@ -133,7 +146,7 @@ def _install_recompute(layer: nn.Module) -> None:
     inner = layer.forward
 
     def forward(*args, **kwargs):
-        if not torch.is_grad_enabled():
+        if not torch.is_grad_enabled() or _recomputes_itself(layer, args, kwargs):
             return inner(*args, **kwargs)
         return checkpoint(inner, *args, use_reentrant=False, preserve_rng_state=True, **kwargs)
 

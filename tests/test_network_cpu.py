@@ -1,0 +1,115 @@
+import torch
+
+from agentgarten_b200.models.diffusion import DiffusionModel
+from agentgarten_b200.models.flow import FlowUniPC, RectifiedFlowSchedule, invariant_randn, rf_interpolate, rf_x0
+from agentgarten_b200.networks.cosmos3.attention import block_causal_plan
+from agentgarten_b200.networks.cosmos3.network import patchify, unpatchify
+from agentgarten_b200.protocols import HistoryWindow
+from agentgarten_b200.infra.optim import FusedAdam
+
+from helpers import synthetic_batch, tiny_conditioner, tiny_config, tiny_network
+
+
+def test_patchify_roundtrip():
+    x = torch.randn(2, 6, 3, 4, 8)
+    p = patchify(x, 2)
+    assert p.shape == (2, 3, 8, 24)
+    assert torch.equal(unpatchify(p, channels=6, grid=(2, 4), patch_size=2), x)
+
+
+def test_flow_pointwise_and_schedule():
+    x0, noise = torch.randn(2, 4, 3, 2, 2), torch.randn(2, 4, 3, 2, 2)
+    s = torch.tensor([0.25, 1.0])
+    xt = rf_interpolate(x0, noise, s)
+    assert torch.allclose(rf_x0(xt, s, noise - x0), x0, atol=1e-6)
+    per_frame = torch.rand(2, 3)
+    xt = rf_interpolate(x0, noise, per_frame)
+    assert torch.allclose(xt[1, :, 2], (1 - per_frame[1, 2]) * x0[1, :, 2] + per_frame[1, 2] * noise[1, :, 2])
+    for kind in ("uniform", "logitnormal", "waver"):
+        sig = RectifiedFlowSchedule(shift=5.0, train_distribution=kind).sample(1000, device=torch.device("cpu"))
+        assert sig.min() >= 0 and sig.max() <= 1 and sig.mean() > 0.5
+
+
+def test_invariant_randn_is_batching_invariant():
+    ref = torch.zeros(3, 2, 2)
+    a = invariant_randn(ref, [5, 6, 7])
+    b = invariant_randn(ref[:1], [6])
+    assert torch.equal(a[1:2], b)
+    assert not torch.equal(invariant_randn(ref, [5, 6, 7], stream=1), a)
+
+
+def test_unipc_integrates_linear_flow_exactly():
+    # velocity of the straight path between fixed noise and data is constant: noise - x0
+    x0, noise = torch.randn(1, 2, 2, 2, 2), torch.randn(1, 2, 2, 2, 2)
+    solver = FlowUniPC(8, shift=3.0)
+    start = (1 - solver.sigmas[0]) * x0 + solver.sigmas[0] * noise
+    out = solver.run(start, lambda x, s: noise - x0)
+    assert torch.allclose(out, x0, atol=1e-4)
+
+
+def test_block_causal_plan_and_window():
+    assert block_causal_plan(4, False, HistoryWindow()) == [[0], [0, 1], [0, 1, 2], [0, 1, 2, 3]]
+    tf = block_causal_plan(5, True, HistoryWindow())
+    assert tf == [[0], [0, 1], [0, 2], [0, 2, 3], [0, 2, 4]]
+    windowed = block_causal_plan(5, False, HistoryWindow(sink_blocks=1, recent_blocks=1))
+    assert windowed[4] == [0, 1, 3, 4]
+
+
+def test_bidirectional_training_step_decreases_loss():
+    cfg = tiny_config()
+    model = DiffusionModel(net=tiny_network(cfg), conditioner=tiny_conditioner(cfg), text_dropout=0.0)
+    model.parallelize("cpu")
+    opt = FusedAdam(model._group_trainable_parameters(), lr=2e-3, use_te_capturable_kernel=True,
+                    master_weights=True)
+    batch = model.prepare_data_batch(synthetic_batch())
+    losses = []
+    for it in range(8):
+        g = torch.Generator().manual_seed(0)
+        _, loss = model._loss(batch, generator=g, drop_text=False)
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        losses.append(float(loss))
+    assert losses[-1] < losses[0] * 0.9
+
+
+def test_forward_ar_replays_cached_rollout_bitwise():
+    cfg = tiny_config()
+    net = tiny_network(cfg).eval()
+    cond = tiny_conditioner(cfg)
+    batch = cond.encode(synthetic_batch(frames=9), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    anchor, target = latent[:, :, :1], latent[:, :, 1:]
+    sigma = torch.tensor([[0.7] * 4 + [0.3] * 4])
+    noisy = rf_interpolate(target, torch.randn_like(target), sigma)
+    with torch.no_grad():
+        full = net.forward_ar(anchor, noisy, sigma, condition, block_frames=4, clean=target)
+        cache = net.prefill(anchor, condition)
+        outs = []
+        for b in range(2):
+            sl = slice(4 * b, 4 * b + 4)
+            outs.append(net.denoise(cache, noisy[:, :, sl], sigma[:, sl]))
+            cache = net.commit(cache, target[:, :, sl])
+        rolled = torch.cat(outs, dim=2)
+    assert torch.equal(full, rolled)
+    assert cache.frames_committed == 8
+
+
+def test_fused_adam_matches_torch_adamw():
+    torch.manual_seed(0)
+    a = torch.nn.Parameter(torch.randn(5, 4))
+    b = torch.nn.Parameter(a.detach().clone())
+    mine = FusedAdam([a], lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    ref = torch.optim.AdamW([b], lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    for _ in range(4):
+        g = torch.randn(5, 4)
+        a.grad, b.grad = g.clone(), g.clone()
+        mine.step()
+        ref.step()
+    assert torch.allclose(a, b, atol=1e-6)
+    zero = torch.nn.Parameter(torch.randn(3))
+    no_moment = FusedAdam([zero], lr=1e-2, betas=(0.0, 0.999))
+    zero.grad = torch.ones(3)
+    no_moment.step()
+    assert "exp_avg" not in no_moment.state[zero]
