@@ -1,0 +1,394 @@
+"""Update-counted training loop.
+
+One *iteration* is one optimizer update; it consumes ``grad_accum_steps`` microbatches, and
+each microbatch may run several loss closures (e.g. fake-score + discriminator).  Per
+update: gradients are combined across ranks (the sharded engine does this in its
+reduce-scatter kernel, DDP in its reducer), callbacks may clip, all ranks agree on whether
+the gradients are finite, the active optimizers and schedulers step (or the step is
+skipped everywhere), gradients are cleared.  Checkpoint and validation cadence are asked of
+the model, which may count something other than raw iterations.
+
+Exact resume: state is restored first, the loader's workers are started next, and only then
+is the checkpointed RNG put back, so worker start-up cannot shift the random streams.
+Validation runs with the training mode, loader cursor and RNG streams preserved.
+
+Parity: reference ``wm/infra/trainer.py:43-627``.
+"""
+
+from __future__ import annotations
+
+import warnings
+from collections.abc import Callable, Iterable, Iterator, Mapping
+from contextlib import contextmanager
+from copy import deepcopy
+from dataclasses import dataclass
+from functools import partial
+from pathlib import Path
+from typing import Any
+
+import torch
+
+from agentgarten_b200.utils.misc import preserve_training_mode, to
+
+from .batch_transport import fetch_batch, prepare_batch
+from .callbacks.base import CallbackGroup
+from .distributed import DistributedDataParallel, ddp_sync_grad, is_rank0
+from .model import Model
+from .nonfinite import synchronize_found_nonfinite
+from .rng_state import isolated_rng
+
+__all__ = ["Trainer", "TrainingStepResult"]
+
+Batch = dict[str, Any]
+
+
+@dataclass(frozen=True, slots=True)
+class TrainingStepResult:
+    output_batch: Batch
+    loss: torch.Tensor
+    grad_accum_step: int
+    did_update: bool
+    found_nonfinite: bool = False
+
+
+class _NoScaler:
+    """Stand-in for a disabled ``torch.amp.GradScaler``."""
+
+    def is_enabled(self) -> bool:
+        return False
+
+    def scale(self, loss):
+        return loss
+
+    def unscale_(self, optimizer) -> None:
+        return
+
+    def step(self, optimizer):
+        return optimizer.step()
+
+    def update(self) -> None:
+        return
+
+    def state_dict(self) -> dict:
+        return {}
+
+    def load_state_dict(self, state) -> None:
+        return
+
+
+@contextmanager
+def _keep_loader_cursor(loader) -> Iterator[None]:
+    get, put = getattr(loader, "state_dict", None), getattr(loader, "load_state_dict", None)
+    saved = deepcopy(get()) if callable(get) and callable(put) else None
+    try:
+        yield
+    finally:
+        if saved is not None:
+            put(saved)
+
+
+def _pick(registry: Mapping[str, Any], names, *, label: str) -> dict[str, Any]:
+    if names is None:
+        return dict(registry)
+    wanted = (names,) if isinstance(names, str) else tuple(names)
+    wanted = tuple(dict.fromkeys(str(n) for n in wanted))
+    unknown = [n for n in wanted if n not in registry]
+    if unknown:
+        raise ValueError(f"Unknown checkpoint {label} name(s): {', '.join(unknown)}; "
+                         f"available: {', '.join(sorted(registry)) or '<none>'}")
+    return {n: registry[n] for n in wanted}
+
+
+def _root(model: torch.nn.Module) -> Model:
+    if isinstance(model, DistributedDataParallel):
+        return model.training_model
+    if isinstance(model, torch.nn.parallel.DistributedDataParallel):
+        raise TypeError("Trainer closures cannot run through stock PyTorch DDP; use "
+                        "wrap_ddp(), whose forward_closure() enters the reducer lifecycle.")
+    if not isinstance(model, Model):
+        raise TypeError("Trainer requires a Model training root")
+    return model
+
+
+def _with_cp_topology(model: Model, metadata: Mapping[str, Any] | None):
+    topology = model.context_parallel_context.checkpoint_topology()
+    if topology is None:
+        return metadata
+    out = dict(metadata or {})
+    mesh = dict(out.get("mesh") or {})
+    mesh["context_parallel"] = topology
+    out["mesh"] = mesh
+    return out
+
+
+class Trainer:
+    def __init__(self, *, grad_accum_steps: int = 1, callbacks: CallbackGroup | None = None,
+                 device: torch.device | str | None = None) -> None:
+        if grad_accum_steps < 1:
+            raise ValueError("grad_accum_steps must be at least one")
+        self.grad_accum_steps = int(grad_accum_steps)
+        self.periodic_iteration_offset = 0
+        self.device = None if device is None else torch.device(device)
+        if callbacks is None or not isinstance(callbacks, CallbackGroup):
+            # a plain mapping/list from the config is turned into a group here
+            config = None if callbacks is None else {"trainer": {"callbacks": callbacks}}
+            callbacks = CallbackGroup(config=config, trainer=self)
+        self.callbacks = callbacks
+        self.callbacks.trainer = self
+        for callback in self.callbacks:
+            callback.trainer = self
+
+    # ------------------------------------------------------------------------ data
+    def _prepare(self, model: Model, batch: Batch) -> Batch:
+        if self.device is not None:
+            batch = to(batch, device=self.device)
+        return model.prepare_data_batch(batch)
+
+    def _next_batch(self, model: Model, iterator: Iterator[Batch], *, sequence_index: int):
+        context = model.context_parallel_context
+        batch, exhausted, owner = fetch_batch(context, iterator, sequence_index=sequence_index)
+        if exhausted:
+            return None
+        return prepare_batch(context, batch, owner_rank=owner, prepare=partial(self._prepare, model))
+
+    # ----------------------------------------------------------------------- train
+    def train(self, model: Model, dataloader_train: Iterable[Batch],
+              dataloader_val: Iterable[Batch] | None = None, *, grad_scaler: Any = None,
+              max_iterations: int | None, checkpointer: Any = None,
+              checkpoint_path: str | Path | None = None,
+              checkpoint_components: Iterable[str] | None = None,
+              checkpoint_optimizer_names: Iterable[str] | str | None = None,
+              checkpoint_scheduler_names: Iterable[str] | str | None = None,
+              checkpoint_model_key_prefix: str | None = None,
+              checkpoint_interval: int | None = None, validation_interval: int | None = None,
+              periodic_iteration_offset: int = 0, max_val_steps: int | None = None,
+              validate_at_start: bool = False, save_final_checkpoint: bool = True,
+              model_wrapper: Callable[[Model], torch.nn.Module] | None = None,
+              runtime_metadata: Mapping[str, Any] | None = None,
+              model_initializations: Any = None) -> int:
+        """Run the loop; keyword names follow the ``train`` section of the config."""
+        del model_initializations  # consumed by the entry point before training starts
+        if periodic_iteration_offset < 0:
+            raise ValueError("periodic_iteration_offset must be non-negative")
+        self.periodic_iteration_offset = int(periodic_iteration_offset)
+        scaler = grad_scaler if grad_scaler is not None else _NoScaler()
+        try:
+            iteration = self._loop(
+                model, dataloader_train, dataloader_val, scaler, max_iterations, checkpointer,
+                {"path": checkpoint_path, "components": checkpoint_components,
+                 "optimizer_names": checkpoint_optimizer_names,
+                 "scheduler_names": checkpoint_scheduler_names,
+                 "model_key_prefix": checkpoint_model_key_prefix},
+                checkpoint_interval, validation_interval, max_val_steps, validate_at_start,
+                save_final_checkpoint, model_wrapper, _with_cp_topology(model, runtime_metadata))
+        except BaseException as error:
+            self._close(checkpointer, error)
+            raise
+        self._close(checkpointer, None)
+        return iteration
+
+    def _close(self, checkpointer, failure: BaseException | None) -> None:
+        """Finish the pending checkpoint and release callbacks.  Nothing raised here may
+        hide the training error; without one, the first cleanup error is raised."""
+        problem: BaseException | None = None
+        if checkpointer is not None:
+            try:
+                if failure is None:
+                    checkpointer.finalize()
+                else:
+                    checkpointer.finalize_after_error()
+            except BaseException as error:
+                problem = error
+                if failure is not None:
+                    warnings.warn("Checkpoint finalization failed while handling a training "
+                                  f"error: {type(error).__name__}: {error}", stacklevel=2)
+        try:
+            self.callbacks.on_app_end()
+        except Exception as error:
+            if failure is not None or problem is not None:
+                warnings.warn(f"Callback cleanup failed: {type(error).__name__}: {error}",
+                              stacklevel=2)
+            else:
+                problem = error
+        if failure is None and problem is not None:
+            raise problem
+
+    def _restore(self, checkpointer, model, scaler, loader, options, metadata) -> int:
+        kwargs = {"path": options["path"], "components": options["components"],
+                  "dataloader": loader, "runtime_metadata": metadata}
+        if options["model_key_prefix"] is not None:
+            kwargs["model_key_prefix"] = options["model_key_prefix"]
+        result = checkpointer.load(
+            model,
+            _pick(model.optimizer_dict, options["optimizer_names"], label="optimizer"),
+            _pick(model.scheduler_dict, options["scheduler_names"], label="scheduler"),
+            scaler, **kwargs)
+        return result.iteration
+
+    def _loop(self, model, loader, loader_val, scaler, max_iterations, checkpointer, load_options,
+              checkpoint_interval, validation_interval, max_val_steps, validate_at_start,
+              save_final, model_wrapper, metadata) -> int:
+        iteration = 0
+        if checkpointer is not None:
+            iteration = self._restore(checkpointer, model, scaler, loader, load_options, metadata)
+
+        def running() -> bool:
+            return max_iterations is None or iteration < max_iterations
+
+        def start_epoch() -> Iterator[Batch]:
+            iterator = iter(loader)
+            if checkpointer is not None:
+                checkpointer.restore_pending_rng_state()  # after worker start-up
+            return iterator
+
+        def save() -> None:
+            checkpointer.save(model, model.optimizer_dict, model.scheduler_dict, scaler,
+                              iteration=iteration, dataloader=loader, runtime_metadata=metadata)
+
+        def due(interval) -> bool:
+            return model.is_cadence_due(iteration - self.periodic_iteration_offset, interval)
+
+        wrapped = model if model_wrapper is None else model_wrapper(model)
+        _root(wrapped)
+        wrapped.train()
+        self.callbacks.on_train_start(model, iteration=iteration)
+        # Start the first epoch's workers before validation: sinks may start threads on
+        # rank 0 and forking workers afterwards can deadlock that rank only.
+        iterator = start_epoch() if running() else None
+        if validate_at_start and loader_val is not None:
+            self.validate(model, loader_val, iteration=iteration, max_val_steps=max_val_steps)
+
+        accum, updates, last_saved = 0, 0, None
+        while running():
+            if iterator is None:
+                iterator = start_epoch()
+            saw_batch = False
+            while running():
+                self.callbacks.on_before_dataloading(iteration=iteration)
+                batch = self._next_batch(model, iterator,
+                                         sequence_index=iteration * self.grad_accum_steps + accum)
+                if batch is None:
+                    break
+                saw_batch = True
+                if not wrapped.training:
+                    wrapped.train()
+                result = self.training_step(wrapped, scaler, batch, iteration=iteration,
+                                            grad_accum_step=accum)
+                accum = result.grad_accum_step
+                if not result.did_update:
+                    continue
+                iteration += 1
+                updates += 1
+                if checkpointer is not None and due(checkpoint_interval):
+                    save()
+                    last_saved = iteration
+                if loader_val is not None and due(validation_interval):
+                    if checkpointer is not None:
+                        checkpointer.finalize()  # publish `latest` before a long evaluation
+                    self.validate(model, loader_val, iteration=iteration,
+                                  max_val_steps=max_val_steps)
+            iterator = None
+            if running() and not saw_batch:
+                if is_rank0():
+                    warnings.warn("Training dataloader produced no batches; ending training.",
+                                  stacklevel=2)
+                break
+        if checkpointer is not None and save_final and updates > 0 and last_saved != iteration:
+            save()
+        self.callbacks.on_train_end(model, iteration=iteration)
+        return iteration
+
+    # ------------------------------------------------------------------------ step
+    def training_step(self, model_ddp: torch.nn.Module, grad_scaler: Any, data_batch: Batch, *,
+                      iteration: int = 0, grad_accum_step: int = 0) -> TrainingStepResult:
+        if not 0 <= grad_accum_step < self.grad_accum_steps:
+            raise ValueError(f"grad_accum_step must be in [0, {self.grad_accum_steps}), "
+                             f"got {grad_accum_step}")
+        scaler = grad_scaler if grad_scaler is not None else _NoScaler()
+        model = _root(model_ddp)
+        bindings = model.get_optimizer_bindings(iteration)
+        optimizers = tuple(b.optimizer for b in bindings)
+        self.callbacks.on_training_step_start(model, data_batch, iteration=iteration)
+
+        final_microbatch = grad_accum_step == self.grad_accum_steps - 1
+        outputs: Batch = {}
+        total: torch.Tensor | None = None
+        finished, count = False, 0
+        for _name, closure, is_last in model.training_step_closures(data_batch, iteration):
+            if finished:
+                raise RuntimeError("training_step_closures() yielded a closure after "
+                                   "is_last=True; the final marker must be on the last closure")
+            if not isinstance(is_last, bool):
+                raise TypeError("training_step_closures() is_last must be a bool, got "
+                                f"{type(is_last).__name__}")
+            count += 1
+            finished = is_last
+            with ddp_sync_grad(model_ddp, final_microbatch and is_last):
+                if isinstance(model_ddp, DistributedDataParallel):
+                    out, loss = model_ddp.forward_closure(closure)
+                else:
+                    out, loss = closure()
+                outputs.update(out)
+                scaler.scale(loss / self.grad_accum_steps).backward()
+            total = loss.detach() if total is None else total + loss.detach()
+        if count == 0 or total is None:
+            raise RuntimeError("training_step_closures() yielded no closures")
+        if not finished:
+            raise RuntimeError("training_step_closures() must mark exactly its final closure "
+                               "with is_last=True")
+
+        if grad_accum_step + 1 < self.grad_accum_steps:
+            self.callbacks.on_training_step_batch_end(model, data_batch, outputs, total,
+                                                      iteration=iteration)
+            return TrainingStepResult(outputs, total, grad_accum_step + 1, False)
+
+        for optimizer in optimizers:
+            scaler.unscale_(optimizer)
+            reduce = getattr(optimizer, "reduce_gradients", None)
+            if callable(reduce):
+                reduce()  # data-parallel mean; a no-op when already done or single rank
+        for b in bindings:
+            self.callbacks.on_before_optimizer_step(model_ddp, b.optimizer, b.scheduler, scaler,
+                                                    iteration=iteration)
+        found = synchronize_found_nonfinite(scaler, optimizers, fallback_device=total.device)
+        if not found:
+            for b in bindings:
+                scaler.step(b.optimizer)
+                b.scheduler.step()
+                self.callbacks.on_after_optimizer_step(model_ddp, b.name, b.optimizer, b.scheduler,
+                                                       iteration=iteration)
+        else:
+            self.callbacks.on_optimizer_step_skipped(model_ddp, tuple(b.name for b in bindings),
+                                                     iteration=iteration)
+        for b in bindings:
+            self.callbacks.on_before_zero_grad(model_ddp, b.optimizer, b.scheduler,
+                                               iteration=iteration)
+            b.optimizer.zero_grad(set_to_none=True)
+            if hasattr(b.optimizer, "grad_scale"):
+                b.optimizer.grad_scale = 1.0
+        scaler.update()  # shared by all active optimizers: exactly once
+        self.callbacks.on_training_step_batch_end(model, data_batch, outputs, total,
+                                                  iteration=iteration)
+        if not found:
+            self.callbacks.on_training_step_end(model, data_batch, outputs, total,
+                                                iteration=iteration + 1)
+        return TrainingStepResult(outputs, total, 0, not found, found)
+
+    # -------------------------------------------------------------------- validate
+    @torch.no_grad()
+    def validate(self, model: Model, dataloader_val: Iterable[Batch], *, iteration: int = 0,
+                 max_val_steps: int | None = None) -> None:
+        with preserve_training_mode(model), _keep_loader_cursor(dataloader_val), isolated_rng():
+            self.callbacks.on_validation_start(model, dataloader_val, iteration=iteration)
+            model.eval()
+            iterator = iter(dataloader_val)
+            index = 0
+            while max_val_steps is None or index < max_val_steps:
+                batch = self._next_batch(model, iterator, sequence_index=index)
+                if batch is None:
+                    break
+                outputs, loss = model.validation_step(batch, iteration)
+                self.callbacks.on_validation_step_end(model, batch, outputs, loss,
+                                                      iteration=iteration)
+                index += 1
+            self.callbacks.on_validation_end(model, iteration=iteration)
