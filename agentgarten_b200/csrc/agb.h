@@ -97,6 +97,13 @@ struct AttnBwdArgs {
 };
 cudaError_t attention_bwd(const AttnBwdArgs& args, cudaStream_t stream);
 
+// ------------------------------------------------------------------ streaming cache
+// dst[t] = rotate(src[t < sink ? t : t + shift]) for t < kept_tokens; rows are
+// [token][heads][128] bf16; cos/sin fp32 [kept_tokens, 128] or null (plain move).
+cudaError_t relocate_rows(const void* src, void* dst, const float* cosv, const float* sinv,
+                          int64_t kept_tokens, int sink_tokens, int shift_tokens, int heads,
+                          cudaStream_t stream);
+
 // ----------------------------------------------------------- sharded optimizer (ZeRO)
 // Base pointers of the same flat buffer on every rank of the node (index = rank).
 struct ZeroPeers {

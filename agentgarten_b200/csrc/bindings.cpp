@@ -306,6 +306,28 @@ void zero_adam(std::vector<int64_t> param_ptrs, std::vector<int64_t> grad_ptrs,
                        sm_count(dev), stream_of(master)), "zero_adam");
 }
 
+// src/dst: [tokens, heads, 128] bf16 views (dst may be larger); cos/sin fp32 [kept, 128].
+void relocate(const Tensor& src, const Tensor& dst, int64_t kept_tokens, int64_t sink_tokens,
+              int64_t shift_tokens, c10::optional<Tensor> cosv, c10::optional<Tensor> sinv) {
+  check_bf16(src, "src");
+  check_bf16(dst, "dst");
+  TORCH_CHECK(src.dim() == 3 && src.size(2) == 128 && src.is_contiguous() && dst.is_contiguous(),
+              "cache rows must be contiguous [tokens, heads, 128]");
+  TORCH_CHECK(kept_tokens <= dst.size(0) && kept_tokens + shift_tokens <= src.size(0) + 0,
+              "relocate range exceeds the cache");
+  c10::cuda::CUDAGuard guard(src.device());
+  const float* c = nullptr;
+  const float* s = nullptr;
+  if (cosv.has_value()) {
+    TORCH_CHECK(cosv->scalar_type() == torch::kFloat32 && cosv->is_contiguous() &&
+                    cosv->size(0) >= kept_tokens && cosv->size(1) == 128, "cos must be fp32 [kept,128]");
+    c = cosv->data_ptr<float>();
+    s = sinv->data_ptr<float>();
+  }
+  check(agb::relocate_rows(src.data_ptr(), dst.data_ptr(), c, s, kept_tokens, int(sink_tokens),
+                           int(shift_tokens), int(src.size(1)), stream_of(src)), "relocate_rows");
+}
+
 Tensor status(int64_t device) { return status_word(int(device)); }
 
 }  // namespace
@@ -322,6 +344,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rf_combine", &rf_combine);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("relocate", &relocate);
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);
   m.def("status", &status);

@@ -1,0 +1,1 @@
+"""Inference: artifact IO, serving preparation, streaming."""

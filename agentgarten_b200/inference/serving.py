@@ -1,0 +1,36 @@
+"""Serving preparation of a generation tower.
+
+``prepare_serving`` switches the network to its inference configuration: parameters frozen
+and in eval mode, every layer routed through the CUDA kernels (they are the default
+operator path for bf16 CUDA tensors) and — with ``cuda_graphs=True`` — whole-step CUDA
+graph replay enabled for streams created from the network afterwards.  A stream captures
+one graph per (cache fill level, denoise|commit); in steady state a denoise call is a single
+graph launch covering all layers, the cache writes, attention and the output projection.
+``release_serving`` drops the option (streams created later run eagerly).
+
+Parity: reference ``wm/inference/serving.py:17-96`` (per-layer graphs around Triton
+``project``/``finish`` with attention left outside the graphs).
+"""
+
+from __future__ import annotations
+
+import torch
+
+__all__ = ["prepare_serving", "release_serving"]
+
+
+def prepare_serving(network: torch.nn.Module, *, dynamic: bool = False, cuda_graphs: bool = True,
+                    inductor: bool = False) -> torch.nn.Module:
+    """``dynamic`` and ``inductor`` are accepted for call compatibility: shapes are handled by
+    per-shape graphs and nothing is traced or compiled here."""
+    del dynamic, inductor
+    network.eval()
+    network.requires_grad_(False)
+    on_cuda = next(network.parameters()).is_cuda
+    network._serving_options = {"cuda_graphs": bool(cuda_graphs) and on_cuda}
+    return network
+
+
+def release_serving(network: torch.nn.Module) -> torch.nn.Module:
+    network._serving_options = None
+    return network

@@ -47,7 +47,8 @@ class _AttentionWithJVP(torch.autograd.Function):
 
     @staticmethod
     def forward(q, k, v, key_mask):
-        return reference.attention(q, k, v, key_mask)
+        # a fresh contiguous tensor: forward-mode AD rejects outputs that are views
+        return reference.attention(q, k, v, key_mask).contiguous()
 
     @staticmethod
     def setup_context(ctx, inputs, output):
@@ -71,7 +72,7 @@ class _AttentionWithJVP(torch.autograd.Function):
         tangents = [torch.zeros_like(x) if dx is None else dx
                     for x, dx in ((q, dq), (k, dk), (v, dv))]
         _, tangent = attention_jvp(q, k, v, *tangents, key_mask=ctx.key_mask)
-        return tangent.to(q.dtype)
+        return tangent.to(q.dtype).contiguous()
 
 
 # ------------------------------------------------------------------------- dense

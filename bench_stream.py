@@ -1,0 +1,94 @@
+"""Streaming-inference benchmark: Cosmos3Stream, batch 1, bf16, CUDA graphs.
+
+Anchor ``[1, 48, 1, 30, 52]``, then ``--blocks`` blocks of 4 latent frames, each with fresh
+depth/normal latents, 4 denoise steps at the sigma endpoints (1.0, 0.75, 0.5, 0.25) followed
+by a commit into a bounded cache of 6 blocks plus the anchor.  Prints one JSON line with the
+p50 / p99 milliseconds per block (device time, CUDA events around each block).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--blocks", type=int, default=32)
+    parser.add_argument("--layers", type=int, default=36)
+    parser.add_argument("--no-graphs", action="store_true")
+    args = parser.parse_args()
+
+    import torch
+
+    from agentgarten_b200.bench_support import random_init_
+    from agentgarten_b200.inference.serving import prepare_serving
+    from agentgarten_b200.models.flow import rf_interpolate, rf_x0
+    from agentgarten_b200.networks.cosmos3 import Cosmos3Config, build_network
+    from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
+    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+    from agentgarten_b200.ops import native
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    native.require()
+    config = Cosmos3Config(num_hidden_layers=args.layers)
+    net = build_network(config, init_device="meta").to(torch.bfloat16).to_empty(device=device)
+    random_init_(net, seed=0)
+    cond = Cosmos3Conditioner(config=config, codec=None, init_device="meta", geometry_noise_sigma=0.0)
+    cond.to(torch.bfloat16).to_empty(device=device)
+    random_init_(cond.text_encoder, seed=1)
+    prepare_serving(net, cuda_graphs=not args.no_graphs)
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=24, rope="top_aligned",
+                          train_frames=61)
+    g = torch.Generator(device=device).manual_seed(0)
+    shape = (1, 48, 4, 30, 52)
+    ids = torch.randint(1000, 150000, (1, 512), device=device, generator=g)
+    with torch.inference_mode():
+        text = cond.text_encoder(ids, None)
+
+    def condition(frames):
+        s = (1, 48, frames, 30, 52)
+        return Cosmos3Condition(text=text, depth=torch.randn(s, device=device, generator=g),
+                                normal=torch.randn(s, device=device, generator=g),
+                                fps=torch.full((1,), 16.0, device=device))
+
+    endpoints = (1.0, 0.75, 0.5, 0.25)
+    stream = Cosmos3Stream(net, policy)
+    stream.start(torch.randn((1, 48, 1, 30, 52), device=device, generator=g), condition(1))
+    times = []
+    launches_before = native.launches()
+    for block in range(args.blocks):
+        cond_block = condition(4)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        clean = None
+        for step, sigma in enumerate(endpoints):
+            s = torch.full((1,), sigma, device=device)
+            noise = torch.randn(shape, device=device, generator=g)
+            current = noise if clean is None else rf_interpolate(clean, noise, s)
+            velocity = stream.denoise(current, s, cond_block)
+            clean = rf_x0(current, s, velocity)
+        stream.commit(clean, cond_block)
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+    steady = times[8:] if len(times) > 12 else times
+    steady_sorted = sorted(steady)
+    print(json.dumps({
+        "metric": "Cosmos3Stream ms per 4-frame block (4 denoise + 1 commit)",
+        "p50_ms": statistics.median(steady),
+        "p99_ms": steady_sorted[min(len(steady_sorted) - 1, int(0.99 * len(steady_sorted)))],
+        "first_blocks_ms": times[:8], "blocks": args.blocks, "n_gpus": 1, "dtype": "bf16",
+        "cuda_graphs": not args.no_graphs, "layers": args.layers,
+        "cache": "anchor + 6 blocks (sink 1, history 24 frames), top-aligned RoPE",
+        "tokens_per_block": 4 * 2 * 390, "gpu_launches": native.launches() - launches_before,
+        "kernel_status": int(native.ext().status(0).item()),
+    }))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

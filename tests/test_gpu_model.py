@@ -120,3 +120,44 @@ def test_smoke_entry():
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+def test_stream_graph_replay_matches_eager():
+    from agentgarten_b200.inference.serving import prepare_serving
+    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+
+    config = _config()
+    net = tiny_network(config, device="cpu", seed=0).to(DEV, torch.bfloat16).eval()
+    cond = tiny_conditioner(config, device="cpu", seed=1).to(DEV, torch.bfloat16)
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=21, height=8, width=12, text=9, seed=5).items()}
+    encoded = cond.encode(batch, training=False)
+    condition = cond.condition(encoded)
+    latent = encoded["latent"]
+
+    def block(lo, hi):
+        return Cosmos3Condition(text=condition.text, depth=condition.depth[:, :, lo:hi],
+                                normal=condition.normal[:, :, lo:hi], fps=condition.fps)
+
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, rope="top_aligned",
+                          train_frames=13)
+    outputs = {}
+    for graphs in (False, True):
+        prepare_serving(net, cuda_graphs=graphs)
+        stream = Cosmos3Stream(net, policy)
+        stream.start(latent[:, :, :1], block(0, 1))
+        outs = []
+        gen = torch.Generator(device=DEV).manual_seed(3)
+        for b in range(5):
+            lo, hi = 1 + 4 * b, 5 + 4 * b
+            noisy = torch.randn(latent[:, :, lo:hi].shape, device=DEV, generator=gen)
+            for sigma in (1.0, 0.5):
+                outs.append(stream.denoise(noisy, torch.tensor([sigma], device=DEV), block(lo, hi)))
+            stream.commit(latent[:, :, lo:hi], block(lo, hi))
+        outputs[graphs] = outs
+        assert stream.layers[0].frames == policy.capacity
+    torch.cuda.synchronize()
+    assert int(native.ext().status(0).item()) == 0
+    for eager, replayed in zip(outputs[False], outputs[True]):
+        assert torch.isfinite(eager).all()
+        assert torch.equal(eager, replayed)

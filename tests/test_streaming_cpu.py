@@ -1,0 +1,93 @@
+import pytest
+import torch
+
+from agentgarten_b200.models.flow import rf_interpolate
+from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy, StreamRoPE
+from agentgarten_b200.ops import reference
+from agentgarten_b200.ops.kernels.stream_cache import relocate
+
+from helpers import synthetic_batch, tiny_conditioner, tiny_config, tiny_network
+
+
+def _block_condition(condition, lo, hi):
+    return Cosmos3Condition(text=condition.text, depth=condition.depth[:, :, lo:hi],
+                            normal=condition.normal[:, :, lo:hi], fps=condition.fps)
+
+
+def test_policy_positions():
+    p = StreamPolicy(block_frames=4, sink_frames=5, history_frames=8, rope="top_aligned", train_frames=21)
+    assert p.capacity == 13
+    assert p.positions((0, 1, 2, 3, 4, 9, 10), 17) == (0, 1, 2, 3, 4, 9, 10)
+    assert p.positions((0, 4, 9, 20), 21) == (0, 4, 5, 16)
+    c = StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, rope="contiguous")
+    assert c.positions((0, 5, 12), 13) == (0, 1, 8)
+    with pytest.raises(ValueError):
+        StreamPolicy(sink_frames=3)
+    with pytest.raises(ValueError):
+        StreamPolicy(history_frames=None, rope="top_aligned")
+
+
+def test_stream_matches_cached_rollout_with_absolute_positions():
+    cfg = tiny_config()
+    net = tiny_network(cfg).eval()
+    cond = tiny_conditioner(cfg)
+    batch = cond.encode(synthetic_batch(frames=9), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    anchor = latent[:, :, :1]
+    stream = Cosmos3Stream(net, StreamPolicy(block_frames=4, sink_frames=1, history_frames=None,
+                                             rope=StreamRoPE.ABSOLUTE))
+    stream.start(anchor, _block_condition(condition, 0, 1))
+    with torch.no_grad():
+        cache = net.prefill(anchor, condition)
+    for b in range(2):
+        lo, hi = 1 + 4 * b, 5 + 4 * b
+        clean = latent[:, :, lo:hi]
+        sigma = torch.tensor([0.6])
+        noisy = rf_interpolate(clean, torch.randn_like(clean), sigma)
+        block = _block_condition(condition, lo, hi)
+        with torch.no_grad():
+            expected = net.denoise(cache, noisy, sigma)
+            cache = net.commit(cache, clean)
+        got = stream.denoise(noisy, sigma, block)
+        assert torch.allclose(got, expected, atol=2e-5)
+        stream.commit(clean, block)
+    assert stream.frame_ids == tuple(range(9)) and stream.layers[0].frames == 9
+
+
+def test_bounded_stream_evicts_and_relocates():
+    cfg = tiny_config()
+    net = tiny_network(cfg).eval()
+    cond = tiny_conditioner(cfg)
+    batch = cond.encode(synthetic_batch(frames=21), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, rope="top_aligned",
+                          train_frames=13)
+    stream = Cosmos3Stream(net, policy)
+    stream.start(latent[:, :, :1], _block_condition(condition, 0, 1))
+    for b in range(5):
+        lo, hi = 1 + 4 * b, 5 + 4 * b
+        block = _block_condition(condition, lo, hi)
+        out = stream.denoise(torch.randn_like(latent[:, :, lo:hi]), torch.tensor([0.9]), block)
+        assert torch.isfinite(out).all() and out.shape == latent[:, :, lo:hi].shape
+        stream.commit(latent[:, :, lo:hi], block)
+        assert len(stream.frame_ids) <= policy.capacity
+    assert stream.frame_ids == (0, *range(13, 21))
+    assert stream.layers[0].frames == policy.capacity
+    # the block that follows sits at the top of the training range
+    assert policy.positions((21,), 21) == (9,)
+
+
+def test_relocate_matches_reference_rows():
+    torch.manual_seed(0)
+    rows = torch.randn(1, 12, 2, 8)
+    ang = torch.randn(1, 9, 4)
+    cos, sin = torch.cat((ang, ang), -1).cos(), torch.cat((ang, ang), -1).sin()
+    out = torch.zeros(1, 12, 2, 8)
+    relocate(rows, out, 2, 3, (cos, sin))
+    assert torch.equal(out[0, :2], rows[0, :2])
+    moved = rows[0, 5:12]
+    expect = moved * cos[0, 2:9, None] + reference.rotate_half(moved) * sin[0, 2:9, None]
+    assert torch.allclose(out[0, 2:9], expect, atol=1e-6)
