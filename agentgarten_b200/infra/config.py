@@ -480,6 +480,17 @@ def _target_string(target: Any) -> str:
 
 
 def _signature_defaults(target: Callable[..., Any]) -> dict[str, Any]:
+    if isinstance(target, type) and dataclasses.is_dataclass(target):
+        # A ``default_factory`` shows up in the signature as an opaque sentinel: call it instead.
+        defaults: dict[str, Any] = {}
+        for field in dataclasses.fields(target):
+            if not field.init:
+                continue
+            if field.default is not dataclasses.MISSING:
+                defaults[field.name] = field.default
+            elif field.default_factory is not dataclasses.MISSING:
+                defaults[field.name] = field.default_factory()
+        return defaults
     try:
         signature = inspect.signature(target)
     except (TypeError, ValueError):

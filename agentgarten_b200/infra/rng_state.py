@@ -150,7 +150,7 @@ def _decode(state: Mapping[str, Any]):
     random.Random(0).setstate(py)
     np.random.RandomState(0).set_state(npy)
     torch.Generator(device="cpu").set_state(cpu)
-    cuda_states = item["cuda_states"]
+    cuda_states = item.get("cuda_states", {})  # an empty mapping is not stored by DCP
     if not isinstance(cuda_states, Mapping):
         raise RuntimeError("RNG checkpoint CUDA state is not a mapping")
     ordered: list[torch.Tensor] = []

@@ -123,10 +123,14 @@ def _with_cp_topology(model: Model, metadata: Mapping[str, Any] | None):
 
 class Trainer:
     def __init__(self, *, grad_accum_steps: int = 1, callbacks: CallbackGroup | None = None,
-                 device: torch.device | str | None = None) -> None:
+                 device: torch.device | str | None = None,
+                 max_consecutive_skipped_updates: int | None = 64) -> None:
         if grad_accum_steps < 1:
             raise ValueError("grad_accum_steps must be at least one")
         self.grad_accum_steps = int(grad_accum_steps)
+        # A run whose gradients stay non-finite would otherwise consume data forever without
+        # advancing the iteration; None restores that behaviour.
+        self.max_consecutive_skipped_updates = max_consecutive_skipped_updates
         self.periodic_iteration_offset = 0
         self.device = None if device is None else torch.device(device)
         if callbacks is None or not isinstance(callbacks, CallbackGroup):
@@ -258,7 +262,7 @@ class Trainer:
         if validate_at_start and loader_val is not None:
             self.validate(model, loader_val, iteration=iteration, max_val_steps=max_val_steps)
 
-        accum, updates, last_saved = 0, 0, None
+        accum, updates, last_saved, skipped = 0, 0, None, 0
         while running():
             if iterator is None:
                 iterator = start_epoch()
@@ -276,7 +280,15 @@ class Trainer:
                                             grad_accum_step=accum)
                 accum = result.grad_accum_step
                 if not result.did_update:
+                    if result.found_nonfinite:
+                        skipped += 1
+                        limit = self.max_consecutive_skipped_updates
+                        if limit is not None and skipped >= limit:
+                            raise FloatingPointError(
+                                f"{skipped} consecutive optimizer updates were skipped for non-finite "
+                                f"gradients at iteration {iteration}")
                     continue
+                skipped = 0
                 iteration += 1
                 updates += 1
                 if checkpointer is not None and due(checkpoint_interval):

@@ -67,6 +67,10 @@ class ParallelConfig:
     compile_options: Mapping[str, Any] = field(default_factory=dict)
     reduce_dtype: str = "float32"
     reshard_after_forward: bool = True
+    # Not None: parameters created on the meta device get seeded N(0, 0.02) matrices, unit
+    # norms and zero biases before the network's own post-materialisation rules run, so
+    # synthetic recipes and benchmarks train from a well-defined state without a checkpoint.
+    random_init_seed: int | None = None
 
     def __post_init__(self) -> None:
         object.__setattr__(self, "activation_checkpointing",
@@ -177,5 +181,20 @@ def parallelize_network(network: ParallelNetwork, config: ParallelConfig, device
     network.parallel_config = config
     if on_meta:
         network.to_empty(device=device)
+        if config.random_init_seed is not None:
+            _random_init(network, int(config.random_init_seed))
         network.initialize_after_materialization()
     return cp_mesh
+
+
+@torch.no_grad()
+def _random_init(network: torch.nn.Module, seed: int) -> None:
+    """The same values on every rank and device: drawn on the CPU, one parameter at a time."""
+    generator = torch.Generator().manual_seed(seed)
+    for name, p in network.named_parameters():
+        if p.ndim >= 2 or not ("norm" in name or name.endswith("bias")):
+            p.copy_(torch.randn(p.shape, generator=generator) * 0.02)
+        elif "norm" in name:
+            p.fill_(1.0)
+        else:
+            p.zero_()

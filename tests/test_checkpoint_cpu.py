@@ -1,0 +1,105 @@
+import torch
+
+from agentgarten_b200.data.loader import StatefulDataLoader
+from agentgarten_b200.data.video import SyntheticLatentDataset
+from agentgarten_b200.infra.checkpoint import DistributedCheckpointer
+from agentgarten_b200.infra.checkpoint.plan import build_model_restore_plan, plan_model_initializations
+from agentgarten_b200.infra.optim import FusedAdam, LinearWarmup
+from agentgarten_b200.models.diffusion import DiffusionModel
+
+from helpers import synthetic_batch, tiny_conditioner, tiny_config, tiny_network
+
+
+def _job(seed=0):
+    cfg = tiny_config()
+    model = DiffusionModel(net=tiny_network(cfg, seed=seed), conditioner=tiny_conditioner(cfg),
+                           text_dropout=0.0)
+    model.parallelize("cpu")
+    opt = FusedAdam(model._group_trainable_parameters(), lr=1e-3, use_te_capturable_kernel=True,
+                    master_weights=True)
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, LinearWarmup(10, 0.1))
+    model.optimizer_dict, model.scheduler_dict = {"net": opt}, {"net": sched}
+    return model, opt, sched
+
+
+def _step(model, opt, sched, batch, seed):
+    g = torch.Generator().manual_seed(seed)
+    _, loss = model._loss(batch, generator=g, drop_text=False)
+    loss.backward()
+    opt.step()
+    sched.step()
+    opt.zero_grad()
+    return float(loss)
+
+
+def test_save_resume_continues_exactly(tmp_path):
+    model, opt, sched = _job()
+    batch = model.prepare_data_batch(synthetic_batch())
+    loader = StatefulDataLoader(SyntheticLatentDataset(length=8, latent_frames=5, latent_height=8,
+                                                       latent_width=8, text_tokens=6, vocab_size=100),
+                                batch_size=2, shuffle=True, seed=3)
+    it = iter(loader)
+    next(it)
+    for s in range(3):
+        _step(model, opt, sched, batch, s)
+    saver = DistributedCheckpointer(tmp_path / "ckpt", async_mode="thread")
+    torch.manual_seed(123)
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=3, dataloader=loader)
+    saver.finalize()
+    assert (tmp_path / "ckpt" / "latest").read_text().strip() == "iter_000000003"
+    assert (tmp_path / "ckpt" / "iter_000000003" / "tensor" / ".metadata").is_file()
+    assert (tmp_path / "ckpt" / "iter_000000003" / "metadata.json").is_file()
+    expected_rand = torch.rand(3)
+    reference = [_step(model, opt, sched, batch, 10 + s) for s in range(2)]
+
+    fresh, opt2, sched2 = _job(seed=5)
+    loader2 = StatefulDataLoader(loader.dataset, batch_size=2, shuffle=True, seed=3)
+    loader_ckpt = DistributedCheckpointer(tmp_path / "ckpt", async_mode=None)
+    result = loader_ckpt.load(fresh, {"net": opt2}, {"net": sched2}, None, dataloader=loader2)
+    assert result.iteration == 3 and "model" in result.loaded_components
+    assert not result.missing_model_keys and not result.unexpected_model_keys
+    assert loader2.state_dict() == {"epoch": 0, "batch_offset": 1}
+    assert sched2.last_epoch == 3 and abs(opt2.param_groups[0]["lr"] - 1e-3 * (0.1 + 0.9 * 0.3)) < 1e-12
+    assert loader_ckpt.restore_pending_rng_state()
+    assert torch.equal(torch.rand(3), expected_rand)
+    resumed = [_step(fresh, opt2, sched2, batch, 10 + s) for s in range(2)]
+    assert resumed == reference
+    # the frozen conditioner is not part of a checkpoint
+    keys = torch.distributed.checkpoint.FileSystemReader(
+        str(tmp_path / "ckpt" / "iter_000000003" / "tensor")).read_metadata().state_dict_metadata
+    assert not any(k.startswith("model.conditioner.") for k in keys)
+    assert any(k.startswith("optimizers.net.state.net.layers.0.") and k.endswith("master_param") for k in keys)
+
+
+def test_overlay_into_several_prefixes(tmp_path):
+    import torch.distributed.checkpoint as dcp
+
+    cfg = tiny_config()
+    donor = tiny_network(cfg, seed=9)
+    dcp.save({k: v for k, v in donor.state_dict().items()},
+             storage_writer=dcp.FileSystemWriter(str(tmp_path / "donor")))
+    model, *_ = _job(seed=1)
+    before = model.net.layers[1].mlp_moe_gen.up_proj.weight.clone()
+    inits = {"net": {"path": str(tmp_path / "donor"), "model_key_prefixes": ["net"],
+                     "source_model_key_prefix": "",
+                     "source_model_key_patterns": [r"layers\.0\..*", r"proj_(?:in|out)\.(?:weight|bias)"],
+                     "resume_model_key_prefixes": None}}
+    DistributedCheckpointer(tmp_path / "x", async_mode=None).initialize_model(model, inits)
+    bf16 = torch.bfloat16
+    assert torch.equal(model.net.layers[0].mlp_moe_gen.up_proj.weight, donor.layers[0].mlp_moe_gen.up_proj.weight.to(bf16))
+    assert torch.equal(model.net.proj_in.weight, donor.proj_in.weight.to(bf16))
+    assert torch.equal(model.net.layers[1].mlp_moe_gen.up_proj.weight, before)
+    assert plan_model_initializations(inits, resume=True) == ()
+
+
+def test_restore_plan_rules():
+    plan = build_model_restore_plan(live_keys=["a.w", "b.w", "c"], saved_keys=["w", "z"], overlay=True,
+                                    source_prefix="", destination_prefixes=["a", "b"],
+                                    source_patterns=[r"w"])
+    assert plan.entries[0].targets == ("a.w", "b.w") and plan.missing_model_keys == ()
+    strict = build_model_restore_plan(live_keys=["x", "y"], saved_keys=["y", "q"], overlay=False)
+    assert strict.missing_model_keys == ("x",) and strict.unexpected_model_keys == ("q",)
+    merged = plan_model_initializations(
+        {"s": {"path": "p", "model_key_prefixes": ["student"], "source_model_key_prefix": ""},
+         "f": {"path": "p", "model_key_prefixes": ["fake"], "source_model_key_prefix": ""}}, resume=False)
+    assert len(merged) == 1 and merged[0].destinations == ("student", "fake")
