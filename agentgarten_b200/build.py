@@ -22,6 +22,7 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 OBJ = ROOT / "csrc" / "build"
 TARGET = ROOT / "_C.so"
+IO_TARGET = ROOT / "_io.so"  # host-only helpers: no CUDA or torch libraries are linked
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
@@ -56,7 +57,23 @@ def _stale(obj: Path, source: Path, headers: list[Path]) -> bool:
     return obj.stat().st_mtime < newest
 
 
+def build_host(force: bool = False) -> Path:
+    """``csrc/host/*.cpp`` -> ``_io.so`` (plain pybind11 module, loadable on any machine)."""
+    sources = sorted((CSRC / "host").glob("*.cpp"))
+    newest = max(p.stat().st_mtime for p in [*sources, Path(__file__)])
+    if not force and IO_TARGET.exists() and IO_TARGET.stat().st_mtime >= newest:
+        return IO_TARGET
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-w",
+           *_include_flags(), *map(str, sources), "-o", str(IO_TARGET)]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("compilation of the host helpers failed")
+    return IO_TARGET
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
+    build_host(force)
     OBJ.mkdir(parents=True, exist_ok=True)
     headers = sorted([*CSRC.glob("*.h"), *CSRC.glob("*.cuh")])
     sources = sorted([*CSRC.glob("*.cu"), *CSRC.glob("*.cpp")])

@@ -63,6 +63,7 @@ class LoadResult:
     loaded_components: tuple[str, ...] = ()
     missing_model_keys: tuple[str, ...] = ()
     unexpected_model_keys: tuple[str, ...] = ()
+    loaded_model_keys: tuple[str, ...] = ()
 
 
 @dataclass
@@ -308,7 +309,9 @@ class DistributedCheckpointer:
         # ---- apply
         missing: tuple[str, ...] = ()
         unexpected: tuple[str, ...] = ()
+        restored: tuple[str, ...] = ()
         if plan is not None:
+            restored = tuple(target for entry in plan.entries for target in entry.targets)
             with torch.no_grad():
                 for entry in plan.entries:
                     value = template[head + entry.source_key]
@@ -355,7 +358,7 @@ class DistributedCheckpointer:
             sidecar.warn_runtime_metadata_changes(directory, runtime_metadata)
             if sidecar.restore_dataloader_snapshot(directory, dataloader, runtime_metadata):
                 loaded.append("dataloader")
-        return LoadResult(iteration, str(directory), tuple(loaded), missing, unexpected)
+        return LoadResult(iteration, str(directory), tuple(loaded), missing, unexpected, restored)
 
     def _read(self, dcp, planner_type, source: LoadSource, template: dict[str, Any],
               object_keys: list[str]) -> None:

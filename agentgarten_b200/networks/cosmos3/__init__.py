@@ -54,8 +54,8 @@ LORA_ATTENTION_MLP_MODULES = (
     *LORA_ATTENTION_MODULES,
     r"layers\.\d+\.mlp_moe_gen\.(gate|up|down)_proj",
 )
-# Token ids of the empty prompt after the chat template (used for text dropout / CFG).
-COSMOS3_EMPTY_PROMPT_IDS: tuple[int, ...] = ()
+# Token ids of an empty user message after the chat template (text dropout / default negative).
+COSMOS3_EMPTY_PROMPT_IDS: tuple[int, ...] = (151644, 872, 198, 151645, 198, 151644, 77091, 198)
 
 
 def _as_config(config: Any) -> Cosmos3Config:

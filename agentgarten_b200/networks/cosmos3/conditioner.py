@@ -31,7 +31,7 @@ __all__ = ["COSMOS3_EMPTY_PROMPT_IDS", "Cosmos3Conditioner"]
 
 # Chat template around an empty user message: used for text dropout and as the default
 # negative prompt.
-COSMOS3_EMPTY_PROMPT_IDS = (151644, 872, 198, 151645, 198, 151644, 77091, 198)
+from agentgarten_b200.networks.cosmos3 import COSMOS3_EMPTY_PROMPT_IDS  # noqa: E402
 # Validation geometry noise is seeded per modality and sample id, so it is identical across
 # guidance arms, solver steps, evaluation rounds and batchings.
 _EVAL_NOISE_SEED = {"depth": 23_071_996 + 0x1D3E7A11, "normal": 23_071_996 + 0x4A6F2C35}

@@ -1,0 +1,143 @@
+"""Per-kernel timings against the measured roofline.
+
+``python -m agentgarten_b200.ops.microbench [--op gemm attention ...] [--tokens N] [--json]``
+
+Each case is timed with CUDA events on the launching stream after three warm-up launches;
+between timed launches a 256 MB buffer is rewritten so nothing is served from the 126 MB
+L2. Throughput is reported in absolute units and, when ``MEASURED_PEAKS.json`` sits at the
+repository root, as a fraction of the measured cuBLAS bf16 rate (tensor-core kernels) or of
+the measured copy bandwidth (memory-bound kernels).  ``--launches N`` limits the timed
+launches (useful under a profiler, which wants few, small launches).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+
+import torch
+
+from agentgarten_b200 import ops
+from agentgarten_b200.ops import native
+
+_FLUSH = None
+
+
+def _flush_l2() -> None:
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _FLUSH.fill_(1)
+
+
+def _time(fn, launches: int) -> float:
+    """Median milliseconds of ``fn`` over ``launches`` timed calls."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(launches):
+        _flush_l2()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(stop))
+    return statistics.median(samples)
+
+
+def _peaks() -> dict:
+    path = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if path.is_file():
+        data = json.loads(path.read_text())
+        return {"tflops": float(data.get("bf16_tflops", 0) or 0), "gbs": float(data.get("hbm_gbs", 0) or 0),
+                "source": "measured"}
+    return {"tflops": 1590.0, "gbs": 6650.0, "source": "fallback"}
+
+
+def bench_gemm(tokens: int, launches: int) -> list[dict]:
+    out = []
+    for name, (n, k) in {"qkv 4096->6144": (6144, 4096), "mlp up 4096->12288": (12288, 4096),
+                         "mlp down 12288->4096": (4096, 12288)}.items():
+        a = torch.randn(tokens, k, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+        ms = _time(lambda: ops.linear(a, w), launches)
+        out.append({"kernel": "gemm_kernel", "case": f"{name}, {tokens} rows", "ms": ms,
+                    "tflops": 2.0 * tokens * n * k / ms / 1e9})
+    return out
+
+
+def bench_attention(tokens: int, launches: int, heads: int = 32, kv_heads: int = 8) -> list[dict]:
+    from agentgarten_b200.ops import attention_native
+
+    q = torch.randn(1, tokens, heads, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(1, tokens, kv_heads, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(1, tokens, kv_heads, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    flops = 4.0 * tokens * tokens * heads * 128
+    with torch.no_grad():
+        fwd = _time(lambda: attention_native.dense(q, k, v), launches)
+    result = attention_native.dense(q, k, v)
+    grad = torch.randn_like(result)
+
+    def backward():
+        torch.autograd.grad(result, (q, k, v), grad, retain_graph=True)
+
+    bwd = _time(backward, launches)
+    case = f"{tokens} tokens, {heads}/{kv_heads} heads x 128, dense"
+    return [{"kernel": "attn_fwd_kernel", "case": case, "ms": fwd, "tflops": flops / fwd / 1e9},
+            {"kernel": "attn_delta + attn_dq + attn_dkv", "case": case, "ms": bwd,
+             "tflops": 2.5 * flops / bwd / 1e9}]
+
+
+def bench_pointwise(tokens: int, launches: int) -> list[dict]:
+    out = []
+    x = torch.randn(tokens, 4096, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(4096, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: ops.rms_norm(x, w, 1e-6), launches)
+    out.append({"kernel": "rms_norm_fwd", "case": f"{tokens} x 4096", "ms": ms,
+                "gbs": 2 * x.numel() * 2 / ms / 1e6})
+    gate = torch.randn(tokens, 12288, device="cuda", dtype=torch.bfloat16)
+    up = torch.randn_like(gate)
+    ms = _time(lambda: ops.silu_mul(gate, up), launches)
+    out.append({"kernel": "silu_mul_fwd", "case": f"{tokens} x 12288", "ms": ms,
+                "gbs": 3 * gate.numel() * 2 / ms / 1e6})
+    return out
+
+
+CASES = {"gemm": bench_gemm, "attention": bench_attention, "pointwise": bench_pointwise}
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    parser.add_argument("--op", nargs="*", default=list(CASES), choices=list(CASES))
+    parser.add_argument("--tokens", type=int, default=8192)
+    parser.add_argument("--launches", type=int, default=10)
+    parser.add_argument("--json", action="store_true")
+    args = parser.parse_args(argv)
+    native.require()
+    peaks = _peaks()
+    rows = []
+    for name in args.op:
+        rows += CASES[name](args.tokens, args.launches)
+    for row in rows:
+        if "tflops" in row and peaks["tflops"]:
+            row["fraction"] = row["tflops"] / peaks["tflops"]
+        if "gbs" in row and peaks["gbs"]:
+            row["fraction"] = row["gbs"] / peaks["gbs"]
+        row["of"] = f"of {peaks['source']}"
+    if args.json:
+        print(json.dumps({"peaks": peaks, "rows": rows, "launches": native.launches()}))
+    else:
+        for row in rows:
+            rate = f"{row['tflops']:8.1f} TFLOP/s" if "tflops" in row else f"{row['gbs']:8.1f} GB/s   "
+            print(f"{row['kernel']:34s} {row['case']:46s} {row['ms']:8.3f} ms {rate} "
+                  f"{row.get('fraction', 0):5.2f} {row['of']}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
