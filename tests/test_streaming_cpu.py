@@ -91,3 +91,35 @@ def test_relocate_matches_reference_rows():
     moved = rows[0, 5:12]
     expect = moved * cos[0, 2:9, None] + reference.rotate_half(moved) * sin[0, 2:9, None]
     assert torch.allclose(out[0, 2:9], expect, atol=1e-6)
+
+
+def test_reference_images_condition_a_block_without_touching_the_cache():
+    from agentgarten_b200.networks.cosmos3.reference import denoise_with_references
+
+    cfg = tiny_config()
+    net = tiny_network(cfg).eval()
+    cond = tiny_conditioner(cfg)
+    batch = cond.encode(synthetic_batch(frames=5), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    stream = Cosmos3Stream(net, StreamPolicy(block_frames=4, sink_frames=1, history_frames=None,
+                                             rope=StreamRoPE.ABSOLUTE))
+    block = _block_condition(condition, 1, 5)
+    sigma = torch.tensor([0.7])
+    noisy = rf_interpolate(latent[:, :, 1:5], torch.randn_like(latent[:, :, 1:5]), sigma)
+    with pytest.raises(RuntimeError):
+        denoise_with_references(stream, noisy, sigma, block, [latent[:, :, :1]])
+    stream.start(latent[:, :, :1], _block_condition(condition, 0, 1))
+    plain = stream.denoise(noisy, sigma, block)
+    assert torch.equal(denoise_with_references(stream, noisy, sigma, block, []), plain)
+    before = [(layer.frames, layer.key.clone()) for layer in stream.layers]
+    image = torch.randn(1, 48, 1, 8, 8)
+    guided = denoise_with_references(stream, noisy, sigma, block, [image, image * 0.5])
+    assert guided.shape == plain.shape and torch.isfinite(guided).all()
+    assert not torch.allclose(guided, plain, atol=1e-4)
+    for layer, (frames, key) in zip(stream.layers, before):
+        end = layer.text_tokens + frames * layer.frame_tokens
+        assert layer.frames == frames and torch.equal(layer.key[:, :end], key[:, :end])
+    assert torch.allclose(stream.denoise(noisy, sigma, block), plain, atol=1e-6)
+    with pytest.raises(ValueError):
+        denoise_with_references(stream, noisy, sigma, block, [torch.randn(1, 48, 2, 8, 8)])
