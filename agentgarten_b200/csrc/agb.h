@@ -29,8 +29,71 @@ struct GemmArgs {
   int out_fp32;    // 1: out is float, 0: out is bf16
   int accumulate;  // 1: add the previous contents of out
   int* status;     // device status word (0 = ok) or null
+  const struct TpLink* tp;  // tensor-parallel coupling of this GEMM to its peers, or null
+};
+
+// Tensor-parallel coupling of one GEMM (bf16 output, K-major operands).
+//
+// Rows are grouped in tiles of 128; tile t is owned by rank t % world and is that rank's
+// local tile t / world.  Counters are monotonic and never reset: the consumer keeps, in its
+// own device memory, how much of each counter it has already consumed (`*_seen`, one entry
+// per tile) and the last CTA of the consuming kernel advances it, so the same captured launch
+// sequence can be replayed and steps with different row counts can be mixed.
+//
+//   wait_a:  the TMA producer loads rows of A tile t only after a_ready[t] (local counter,
+//            incremented by the peers that push rows of A into this GPU's memory) shows that
+//            all valid rows of the tile have arrived for the current use.
+//   push:    the epilogue stores output tile t into the owner's partial-sum slot
+//            slot[owner][(rank * tiles_owned + t / world) * 128 + row][n] with plain stores
+//            through the peer mapping, then adds 1 (release, system scope) per epilogue warp
+//            to arrive[owner][t / world].
+struct TpLink {
+  int rank, world;
+  int wait_a;
+  const int* a_ready;  // [ceil(m / 128)] rows received so far, per tile
+  int* a_seen;         // [ceil(m / 128)] rows consumed so far, per tile
+  int* ticket;         // scratch for last-CTA detection, zero between launches; null: this
+                       // GEMM does not close the use (another GEMM on the same rows follows)
+  int push;
+  int tiles_owned;     // local tiles per rank: ceil(ceil(m / 128) / world)
+  void* slot[8];       // bf16 [world, tiles_owned, 128, n] on every rank
+  int* arrive[8];      // int32 [tiles_owned] on every rank
 };
 cudaError_t gemm_bf16(const GemmArgs& args, int sm_count, cudaStream_t stream);
+
+// Owner side of the tensor-parallel residual stream, one CTA per owned row:
+//   h = bf16(residual_row + sum over source ranks (in rank order) of slot[src][row])
+//   hidden_own[row] = h;  x = weight * bf16(h * rsqrt(mean(h^2) + eps))
+//   x is stored into xbuf[peer][global_row] on every rank (peer stores), then ready[peer][tile]
+//   is advanced by one row (release, system scope).
+// With seed != null the slots are not read and residual_row = seed[global_row] (first layer).
+// The kernel waits (bounded) until arrive[local tile] exceeds arrive_seen[local tile] by
+// world * arrivals_per_source.
+struct TpReduceArgs {
+  int rank, world;
+  int m, width;            // rows of the full activation, hidden size (multiple of 8, <= 8192)
+  int tiles_owned;
+  const void* slot;        // local bf16 [world, tiles_owned, 128, width]
+  const int* arrive;       // local int32 [tiles_owned]
+  int* arrive_seen;        // local int32 [tiles_owned]
+  int* ticket;
+  int arrivals_per_source; // 4 * ceil(width / 256): one per epilogue warp and column tile
+  void* hidden_own;        // local bf16 [tiles_owned * 128, width], in/out
+  const void* seed;        // local bf16 [m, width] or null
+  // Seed mode starts a new step: it overwrites every rank's input buffer, so it first waits
+  // until all ranks have signalled the end of their previous step (tp_signal_done):
+  // done >= world * (*done_uses); the last CTA then advances done_uses.
+  const int* done;         // local int32 counter
+  int* done_uses;
+  const void* weight;      // bf16 [width]
+  float eps;
+  void* xbuf[8];           // bf16 [ceil(m/128)*128, width] on every rank
+  int* ready[8];           // int32 [ceil(m/128)] on every rank
+  int* status;
+};
+cudaError_t tp_reduce_norm(const TpReduceArgs& args, cudaStream_t stream);
+// End of a step: adds 1 (release, system scope) to the `done` counter of every rank.
+cudaError_t tp_signal_done(int* const done[8], int world, cudaStream_t stream);
 
 
 // -------------------------------------------------------------------------- pointwise

@@ -264,6 +264,110 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   return {dq, dk, dv};
 }
 
+// ---------------------------------------------------------------- tensor-parallel serving
+// out = a @ b^T coupled to the peers (see agb::TpLink).  With a_ready the producer waits for
+// pushed rows of `a`; with slot_ptrs the output goes to the owners' partial-sum slots and
+// `out` is not used.
+void tp_gemm(const Tensor& a, const Tensor& b, c10::optional<Tensor> out, int64_t rank, int64_t world,
+             c10::optional<Tensor> a_ready, c10::optional<Tensor> a_seen, c10::optional<Tensor> ticket,
+             std::vector<int64_t> slot_ptrs, std::vector<int64_t> arrive_ptrs, int64_t tiles_owned) {
+  check_bf16(a, "a");
+  check_bf16(b, "b");
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1 &&
+                  a.size(1) == b.size(1), "tp_gemm operands must be [M, K] and [N, K]");
+  c10::cuda::CUDAGuard guard(a.device());
+  agb::TpLink link{};
+  link.rank = int(rank);
+  link.world = int(world);
+  if (a_ready.has_value()) {
+    TORCH_CHECK(a_seen.has_value(), "a_ready needs a_seen");
+    TORCH_CHECK(a_ready->numel() >= (a.size(0) + 127) / 128 && a_seen->numel() >= (a.size(0) + 127) / 128,
+                "a_ready / a_seen are too short");
+    link.wait_a = 1;
+    link.a_ready = a_ready->data_ptr<int>();
+    link.a_seen = a_seen->data_ptr<int>();
+    link.ticket = ticket.has_value() ? ticket->data_ptr<int>() : nullptr;  // null: use stays open
+  }
+  agb::GemmArgs g{};
+  g.a = a.data_ptr();
+  g.b = b.data_ptr();
+  g.lda = a.stride(0);
+  g.ldb = b.stride(0);
+  g.m = int(a.size(0));
+  g.n = int(b.size(0));
+  g.k = int(a.size(1));
+  if (!slot_ptrs.empty()) {
+    TORCH_CHECK(int64_t(slot_ptrs.size()) == world && int64_t(arrive_ptrs.size()) == world,
+                "one slot and one arrival pointer per rank");
+    link.push = 1;
+    link.tiles_owned = int(tiles_owned);
+    for (int64_t i = 0; i < world; ++i) {
+      link.slot[i] = reinterpret_cast<void*>(slot_ptrs[i]);
+      link.arrive[i] = reinterpret_cast<int*>(arrive_ptrs[i]);
+    }
+    g.ldo = g.n;
+  } else {
+    TORCH_CHECK(out.has_value() && out->dim() == 2 && out->size(0) == a.size(0) &&
+                    out->size(1) == b.size(0) && out->stride(1) == 1, "tp_gemm out has the wrong shape");
+    check_bf16(*out, "out");
+    g.out = out->data_ptr();
+    g.ldo = out->stride(0);
+  }
+  g.status = status_word(a.device().index()).data_ptr<int>();
+  g.tp = &link;
+  check(agb::gemm_bf16(g, sm_count(a.device().index()), stream_of(a)), "tp_gemm");
+}
+
+void tp_reduce_norm(int64_t rank, int64_t world, int64_t m, const Tensor& slot, const Tensor& arrive,
+                    const Tensor& arrive_seen, const Tensor& ticket, int64_t arrivals_per_source,
+                    const Tensor& hidden_own, c10::optional<Tensor> seed, const Tensor& weight,
+                    double eps, std::vector<int64_t> xbuf_ptrs, std::vector<int64_t> ready_ptrs,
+                    int64_t tiles_owned, const Tensor& done, const Tensor& done_uses) {
+  check_bf16(hidden_own, "hidden_own");
+  check_bf16(weight, "weight");
+  c10::cuda::CUDAGuard guard(hidden_own.device());
+  TORCH_CHECK(int64_t(xbuf_ptrs.size()) == world && int64_t(ready_ptrs.size()) == world,
+              "one buffer and one counter pointer per rank");
+  TORCH_CHECK(hidden_own.dim() == 2 && hidden_own.size(0) >= tiles_owned * 128 &&
+                  hidden_own.is_contiguous(), "hidden_own must be [tiles_owned * 128, width]");
+  agb::TpReduceArgs a{};
+  a.rank = int(rank);
+  a.world = int(world);
+  a.m = int(m);
+  a.width = int(hidden_own.size(1));
+  a.tiles_owned = int(tiles_owned);
+  a.slot = slot.data_ptr();
+  a.arrive = arrive.data_ptr<int>();
+  TORCH_CHECK(arrive_seen.numel() >= tiles_owned, "arrive_seen is too short");
+  a.arrive_seen = arrive_seen.data_ptr<int>();
+  a.ticket = ticket.data_ptr<int>();
+  a.arrivals_per_source = int(arrivals_per_source);
+  a.hidden_own = hidden_own.data_ptr();
+  if (seed.has_value()) {
+    check_bf16(*seed, "seed");
+    TORCH_CHECK(seed->is_contiguous() && seed->numel() == m * hidden_own.size(1), "seed must be [m, width]");
+    a.seed = seed->data_ptr();
+  }
+  a.done = done.data_ptr<int>();
+  a.done_uses = done_uses.data_ptr<int>();
+  a.weight = weight.data_ptr();
+  a.eps = float(eps);
+  for (int64_t i = 0; i < world; ++i) {
+    a.xbuf[i] = reinterpret_cast<void*>(xbuf_ptrs[i]);
+    a.ready[i] = reinterpret_cast<int*>(ready_ptrs[i]);
+  }
+  a.status = status_word(hidden_own.device().index()).data_ptr<int>();
+  check(agb::tp_reduce_norm(a, stream_of(hidden_own)), "tp_reduce_norm");
+}
+
+void tp_signal_done(std::vector<int64_t> done_ptrs, const Tensor& anchor) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  TORCH_CHECK(!done_ptrs.empty() && done_ptrs.size() <= 8, "1..8 ranks");
+  int* done[8] = {};
+  for (size_t i = 0; i < done_ptrs.size(); ++i) done[i] = reinterpret_cast<int*>(done_ptrs[i]);
+  check(agb::tp_signal_done(done, int(done_ptrs.size()), stream_of(anchor)), "tp_signal_done");
+}
+
 agb::ZeroPeers peers_of(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 8, "1..8 peers supported");
   agb::ZeroPeers p{};
@@ -347,5 +451,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relocate", &relocate);
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);
+  m.def("tp_gemm", &tp_gemm);
+  m.def("tp_reduce_norm", &tp_reduce_norm);
+  m.def("tp_signal_done", &tp_signal_done);
   m.def("status", &status);
 }

@@ -39,7 +39,25 @@ struct Params {
   int tiles_m, tiles_n;
   int accumulate;
   int* status;
+  TpLink tp;   // tp.world == 0: not coupled
 };
+
+// Bounded wait until a monotonic counter written by peers reaches `target`.
+__device__ __forceinline__ bool wait_counter(const int* counter, int target, const WaitGuard& g) {
+  const uint64_t start = global_timer_ns();
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (seen - target >= 0) return true;
+    if (*g.abort_flag) return false;
+    if (global_timer_ns() - start > 2000000000ull) {
+      *g.abort_flag = 1;
+      if (g.status) atomicCAS(g.status, 0, kTimeoutPeer);
+      return false;
+    }
+    __nanosleep(64);
+  }
+}
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int per_group = GROUP_M * tiles_n;
@@ -109,6 +127,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         int tm, tn;
         tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
         const int m0 = tm * BM, n0 = tn * BN;
+        if (p.tp.wait_a) {
+          // Rows of this A tile are pushed into local memory by their owner; the counter
+          // counts rows.  The copy below reads them through the async proxy.
+          const int target = reinterpret_cast<volatile int*>(p.tp.a_seen)[tm] + min(BM, p.m - m0);
+          if (!wait_counter(p.tp.a_ready + tm, target, guard)) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, guard, kTimeoutProducer)) {
             ok = false;
@@ -211,6 +239,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       const int row = tm * BM + warp * 32 + lane;
       const bool row_ok = row < p.m;
       const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + acc * BN;
+      // Where this thread's output row lives: the local output, or (tensor parallel, push)
+      // the partial-sum slot of the tile's owner, reached through the peer mapping.
+      __nv_bfloat16* out_row = p.out_bf16 ? p.out_bf16 + int64_t(row) * p.ldo : nullptr;
+      const int owner = p.tp.push ? tm % p.tp.world : 0;
+      if (p.tp.push) {
+        const int64_t slot_row =
+            (int64_t(p.tp.rank) * p.tp.tiles_owned + tm / p.tp.world) * BM + warp * 32 + lane;
+        out_row = static_cast<__nv_bfloat16*>(p.tp.slot[owner]) + slot_row * p.ldo;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = tn * BN + c * 32;
@@ -255,7 +292,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
               dst[0] = make_float4(v[0], v[1], v[2], v[3]);
               dst[1] = make_float4(v[4], v[5], v[6], v[7]);
             } else {
-              uint4* dst = reinterpret_cast<uint4*>(p.out_bf16 + int64_t(row) * p.ldo + col);
+              uint4* dst = reinterpret_cast<uint4*>(out_row + col);
               if (p.accumulate) {
                 const uint4 o = *dst;
                 const uint32_t ow[4] = {o.x, o.y, o.z, o.w};
@@ -272,8 +309,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         }
       }
       tc_fence_before_sync();
+      if (p.tp.push) __threadfence_system();  // this lane's stores before the warp's arrival
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        mbar_arrive(&acc_empty[acc]);
+        if (p.tp.push) {
+          int* counter = p.tp.arrive[owner] + tm / p.tp.world;
+          asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(counter) : "memory");
+        }
+      }
     }
   }
 
@@ -282,6 +326,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
   if (warp == 5) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
+  }
+  if (p.tp.wait_a && p.tp.ticket && threadIdx.x == 0) {
+    // The last CTA to finish closes this use of the A buffer (not when more GEMMs of the
+    // same use follow: those pass no ticket).
+    __threadfence();
+    if (atomicAdd(p.tp.ticket, 1) == int(gridDim.x) - 1) {
+      *p.tp.ticket = 0;
+      volatile int* seen = reinterpret_cast<volatile int*>(p.tp.a_seen);
+      for (int t = 0; t < p.tiles_m; ++t) seen[t] = seen[t] + min(BM, p.m - t * BM);
+      __threadfence();
+    }
   }
 }
 
@@ -356,6 +411,15 @@ cudaError_t gemm_bf16(const GemmArgs& g, int sm_count, cudaStream_t stream) {
   p.tiles_n = (g.n + BN - 1) / BN;
   p.accumulate = g.accumulate;
   p.status = g.status;
+  p.tp = TpLink{};
+  if (g.tp) {
+    if (g.a_mn_major || g.b_mn_major || g.out_fp32 || g.accumulate || g.tp->world < 1 ||
+        g.tp->world > 8 || (g.tp->push && (g.residual || g.bias))) {
+      set_error_detail("gemm: a tensor-parallel GEMM is K-major, bf16, without accumulate; a pushing one has no bias/residual");
+      return cudaErrorInvalidValue;
+    }
+    p.tp = *g.tp;
+  }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
   if (g.a_mn_major == 0 && g.b_mn_major == 0) return launch<0, 0>(g, ta, tb, p, grid, stream);

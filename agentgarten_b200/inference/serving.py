@@ -20,17 +20,34 @@ __all__ = ["prepare_serving", "release_serving"]
 
 
 def prepare_serving(network: torch.nn.Module, *, dynamic: bool = False, cuda_graphs: bool = True,
-                    inductor: bool = False) -> torch.nn.Module:
+                    inductor: bool = False, tensor_parallel: object = None,
+                    max_tokens: int = 8192) -> torch.nn.Module:
     """``dynamic`` and ``inductor`` are accepted for call compatibility: shapes are handled by
-    per-shape graphs and nothing is traced or compiled here."""
+    per-shape graphs and nothing is traced or compiled here.
+
+    ``tensor_parallel``: ``True`` (all ranks of the default process group) or a process group
+    shards heads and MLP columns over those GPUs of one node; streams then run the fused
+    GEMM + peer-memory kernels of :mod:`agentgarten_b200.parallel.tensor_parallel`.  Every
+    rank must hold the full weights when this is called and must drive its stream with the
+    same inputs in the same order.  ``max_tokens`` bounds the tokens of one chunk.
+    """
     del dynamic, inductor
     network.eval()
     network.requires_grad_(False)
     on_cuda = next(network.parameters()).is_cuda
     network._serving_options = {"cuda_graphs": bool(cuda_graphs) and on_cuda}
+    network._tensor_parallel = None
+    if tensor_parallel is not None and tensor_parallel is not False:
+        if not on_cuda:
+            raise ValueError("tensor-parallel serving needs CUDA devices")
+        from agentgarten_b200.parallel.tensor_parallel import TensorParallelServing
+
+        group = None if tensor_parallel is True else tensor_parallel
+        network._tensor_parallel = TensorParallelServing(network, group, max_tokens=max_tokens)
     return network
 
 
 def release_serving(network: torch.nn.Module) -> torch.nn.Module:
     network._serving_options = None
+    network._tensor_parallel = None
     return network

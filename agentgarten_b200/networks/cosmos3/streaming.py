@@ -25,7 +25,7 @@ import torch
 
 from .attention import TextContext
 from .layers import apply_rotary
-from .network import Cosmos3Condition, Cosmos3Network, frame_sigma, rgb_tokens
+from .network import Cosmos3Condition, Cosmos3Network, frame_sigma, rgb_tokens, unpatchify
 from .streaming_attention import StreamAttentionCache
 
 __all__ = ["Cosmos3Stream", "StreamPolicy", "StreamRoPE"]
@@ -204,8 +204,9 @@ class Cosmos3Stream:
         for mine, theirs in pairs:
             mine.copy_(theirs)
         n = text.lengths[0]
+        heads = self._local_kv_heads()
         for layer, key, value in zip(self.layers, text.keys, text.values, strict=True):
-            layer.update_text(key[:, :n], value[:, :n])
+            layer.update_text(key[:, :n, heads], value[:, :n, heads])
 
     # -------------------------------------------------------------------- internals
     def embed_chunk(self, latent: torch.Tensor, sigma: torch.Tensor | None,
@@ -226,8 +227,9 @@ class Cosmos3Stream:
         n = self.text.lengths[0]
         bounded = self.policy.history_frames is not None
         if index == len(self.layers):
+            heads = self._local_kv_heads()
             self.layers.append(StreamAttentionCache(
-                self.text.keys[index][:, :n], self.text.values[index][:, :n],
+                self.text.keys[index][:, :n, heads], self.text.values[index][:, :n, heads],
                 key.shape[1] // frames_in_chunk,
                 self.policy.capacity if bounded else self.initial_capacity_frames,
                 self.policy.block_frames))
@@ -239,6 +241,11 @@ class Cosmos3Stream:
             bigger.append(layer.visual_key, layer.visual_value)
             layer = self.layers[index] = bigger
         return layer
+
+    def _local_kv_heads(self) -> slice:
+        """KV heads cached on this rank: all of them, or this rank's share under tensor parallelism."""
+        plan = getattr(self.network, "_tensor_parallel", None)
+        return slice(None) if plan is None else plan.kv_slice
 
     def _layers_and_decode(self, tokens, rope, record: bool, frames: int, *, advance: bool = True):
         """All layers over one chunk + output projection.  ``advance=False`` leaves the frame
@@ -252,6 +259,16 @@ class Cosmos3Stream:
                 layer.frames += frames  # the tail written by attend() becomes history
             return [out]
 
+        plan = getattr(network, "_tensor_parallel", None)
+        if plan is not None:
+            # Heads and MLP columns are split over the ranks; every rank gets all output rows.
+            patches = plan.run(tokens, rope, attend)
+            if record:
+                return patches
+            config = network.config
+            rgb = rgb_tokens(patches, frames, self.grid)
+            return unpatchify(rgb.float(), channels=config.latent_channels, grid=self.grid,
+                              patch_size=config.patch_size)
         hidden = tokens
         for index, block in enumerate(network.layers):
             (hidden,) = block([hidden], [rope], attend, index)

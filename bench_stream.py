@@ -4,6 +4,11 @@ Anchor ``[1, 48, 1, 30, 52]``, then ``--blocks`` blocks of 4 latent frames, each
 depth/normal latents, 4 denoise steps at the sigma endpoints (1.0, 0.75, 0.5, 0.25) followed
 by a commit into a bounded cache of 6 blocks plus the anchor.  Prints one JSON line with the
 p50 / p99 milliseconds per block (device time, CUDA events around each block).
+
+On several GPUs (``python -m torch.distributed.run --nproc-per-node N ... bench_stream.py``)
+the tower is tensor parallel over the ranks: every rank feeds the same seeded inputs, the
+per-block time is the maximum over ranks.  ``--tensor-parallel`` selects the tensor-parallel
+kernels on one GPU as well.
 """
 
 from __future__ import annotations
@@ -18,9 +23,13 @@ def main() -> int:
     parser.add_argument("--blocks", type=int, default=32)
     parser.add_argument("--layers", type=int, default=36)
     parser.add_argument("--no-graphs", action="store_true")
+    parser.add_argument("--tensor-parallel", action="store_true")
     args = parser.parse_args()
 
+    import os
+
     import torch
+    import torch.distributed as dist
 
     from agentgarten_b200.bench_support import random_init_
     from agentgarten_b200.inference.serving import prepare_serving
@@ -31,8 +40,12 @@ def main() -> int:
     from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
     from agentgarten_b200.ops import native
 
-    device = torch.device("cuda", 0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    rank = dist.get_rank() if world > 1 else 0
     native.require()
     config = Cosmos3Config(num_hidden_layers=args.layers)
     net = build_network(config, init_device="meta").to(torch.bfloat16).to_empty(device=device)
@@ -40,7 +53,9 @@ def main() -> int:
     cond = Cosmos3Conditioner(config=config, codec=None, init_device="meta", geometry_noise_sigma=0.0)
     cond.to(torch.bfloat16).to_empty(device=device)
     random_init_(cond.text_encoder, seed=1)
-    prepare_serving(net, cuda_graphs=not args.no_graphs)
+    sharded = world > 1 or args.tensor_parallel
+    prepare_serving(net, cuda_graphs=not args.no_graphs, tensor_parallel=True if sharded else None,
+                    max_tokens=4096)
     policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=24, rope="top_aligned",
                           train_frames=61)
     g = torch.Generator(device=device).manual_seed(0)
@@ -75,18 +90,30 @@ def main() -> int:
         stop.record()
         torch.cuda.synchronize()
         times.append(start.elapsed_time(stop))
+    status = int(native.ext().status(device.index).item())
+    if world > 1:
+        gathered = torch.tensor(times + [float(status)], device=device)
+        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+        times, status = gathered[:-1].tolist(), int(gathered[-1].item())
+    if rank != 0:
+        dist.destroy_process_group()
+        return 0
     steady = times[8:] if len(times) > 12 else times
     steady_sorted = sorted(steady)
     print(json.dumps({
         "metric": "Cosmos3Stream ms per 4-frame block (4 denoise + 1 commit)",
         "p50_ms": statistics.median(steady),
         "p99_ms": steady_sorted[min(len(steady_sorted) - 1, int(0.99 * len(steady_sorted)))],
-        "first_blocks_ms": times[:8], "blocks": args.blocks, "n_gpus": 1, "dtype": "bf16",
+        "first_blocks_ms": times[:8], "blocks": args.blocks, "n_gpus": world, "dtype": "bf16",
+        "parallelism": f"tp{world} (heads and MLP columns; GEMM+reduce-scatter / all-gather+GEMM over peer memory)"
+        if sharded else "single GPU",
         "cuda_graphs": not args.no_graphs, "layers": args.layers,
         "cache": "anchor + 6 blocks (sink 1, history 24 frames), top-aligned RoPE",
         "tokens_per_block": 4 * 2 * 390, "gpu_launches": native.launches() - launches_before,
-        "kernel_status": int(native.ext().status(0).item()),
+        "kernel_status": status,
     }))
+    if world > 1:
+        dist.destroy_process_group()
     return 0
 
 

@@ -55,11 +55,66 @@ def check_sharded_adam(device, rank, world):
         assert torch.equal(other, gathered[0])
 
 
+def check_tensor_parallel_stream(device, rank, world):
+    """Sharded serving over peer memory against the single-GPU layer path, eager and replayed."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import synthetic_batch, tiny_conditioner, tiny_config, tiny_network
+
+    from agentgarten_b200.inference.serving import prepare_serving, release_serving
+    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+    from agentgarten_b200.ops import native
+
+    config = tiny_config(hidden_size=512, intermediate_size=1024, num_attention_heads=8,
+                         num_key_value_heads=world, head_dim=128, mrope_section=(24, 20, 20))
+    net = tiny_network(config, device="cpu", seed=0).to(device, torch.bfloat16).eval()
+    cond = tiny_conditioner(config, device="cpu", seed=1).to(device, torch.bfloat16)
+    batch = {k: v.to(device) for k, v in synthetic_batch(frames=17, height=8, width=12, text=9, seed=5).items()}
+    encoded = cond.encode(batch, training=False)
+    condition, latent = cond.condition(encoded), encoded["latent"]
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, rope="top_aligned", train_frames=13)
+
+    def block(lo, hi):
+        return Cosmos3Condition(text=condition.text, depth=condition.depth[:, :, lo:hi],
+                                normal=condition.normal[:, :, lo:hi], fps=condition.fps)
+
+    def rollout(**serving):
+        prepare_serving(net, **serving)
+        stream = Cosmos3Stream(net, policy)
+        stream.start(latent[:, :, :1], block(0, 1))
+        outs = []
+        gen = torch.Generator(device=device).manual_seed(3)
+        for b in range(4):
+            lo, hi = 1 + 4 * b, 5 + 4 * b
+            noisy = torch.randn(latent[:, :, lo:hi].shape, device=device, generator=gen)
+            for sigma in (1.0, 0.5):
+                outs.append(stream.denoise(noisy, torch.tensor([sigma], device=device), block(lo, hi)))
+            stream.commit(latent[:, :, lo:hi], block(lo, hi))
+        torch.cuda.synchronize()
+        return outs
+
+    plain = rollout(cuda_graphs=False)
+    eager = rollout(cuda_graphs=False, tensor_parallel=True, max_tokens=1024)
+    replay = rollout(cuda_graphs=True, tensor_parallel=True, max_tokens=1024)
+    assert int(native.ext().status(device.index).item()) == 0, "a bounded wait gave up"
+    for a, b, c in zip(plain, eager, replay):
+        assert torch.isfinite(b).all()
+        error = float((b.float() - a.float()).norm() / a.float().norm())
+        assert error < 2e-2, error
+        assert torch.equal(b, c)
+        same = [torch.empty_like(b) for _ in range(world)]
+        dist.all_gather(same, b.contiguous())
+        assert all(torch.equal(other, same[0]) for other in same)  # every rank holds all rows
+    release_serving(net)
+
+
 def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     device = distributed.init(device="cuda", backend="nccl")
     rank, world = dist.get_rank(), dist.get_world_size()
     check_sharded_adam(device, rank, world)
+    dist.barrier()
+    check_tensor_parallel_stream(device, rank, world)
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK")

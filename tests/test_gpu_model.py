@@ -161,3 +161,53 @@ def test_stream_graph_replay_matches_eager():
     for eager, replayed in zip(outputs[False], outputs[True]):
         assert torch.isfinite(eager).all()
         assert torch.equal(eager, replayed)
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+def _stream_outputs(net, condition, latent, policy, **serving):
+    from agentgarten_b200.inference.serving import prepare_serving
+    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream
+
+    def block(lo, hi):
+        return Cosmos3Condition(text=condition.text, depth=condition.depth[:, :, lo:hi],
+                                normal=condition.normal[:, :, lo:hi], fps=condition.fps)
+
+    prepare_serving(net, **serving)
+    stream = Cosmos3Stream(net, policy)
+    stream.start(latent[:, :, :1], block(0, 1))
+    outs = []
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    for b in range(4):
+        lo, hi = 1 + 4 * b, 5 + 4 * b
+        noisy = torch.randn(latent[:, :, lo:hi].shape, device=DEV, generator=gen)
+        for sigma in (1.0, 0.5):
+            outs.append(stream.denoise(noisy, torch.tensor([sigma], device=DEV), block(lo, hi)))
+        stream.commit(latent[:, :, lo:hi], block(lo, hi))
+    torch.cuda.synchronize()
+    return outs
+
+
+def test_tensor_parallel_kernels_on_one_rank_match_the_layer_path():
+    from agentgarten_b200.networks.cosmos3.streaming import StreamPolicy
+
+    config = _config()
+    net = tiny_network(config, device="cpu", seed=0).to(DEV, torch.bfloat16).eval()
+    cond = tiny_conditioner(config, device="cpu", seed=1).to(DEV, torch.bfloat16)
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=17, height=8, width=12, text=9, seed=5).items()}
+    encoded = cond.encode(batch, training=False)
+    condition, latent = cond.condition(encoded), encoded["latent"]
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, rope="top_aligned", train_frames=13)
+    plain = _stream_outputs(net, condition, latent, policy, cuda_graphs=False)
+    eager = _stream_outputs(net, condition, latent, policy, cuda_graphs=False, tensor_parallel=True, max_tokens=1024)
+    replay = _stream_outputs(net, condition, latent, policy, cuda_graphs=True, tensor_parallel=True, max_tokens=1024)
+    assert int(native.ext().status(0).item()) == 0
+    for a, b, c in zip(plain, eager, replay):
+        assert torch.isfinite(b).all()
+        assert rel(b, a) < 2e-2, rel(b, a)
+        assert torch.equal(b, c)
+    from agentgarten_b200.inference.serving import release_serving
+    release_serving(net)
