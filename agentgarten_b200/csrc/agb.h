@@ -160,6 +160,22 @@ struct AttnBwdArgs {
 };
 cudaError_t attention_bwd(const AttnBwdArgs& args, cudaStream_t stream);
 
+// Attention with forward-mode tangents (dense keys, optional prefix-valid text segment):
+// out/tangent fp32 [B, NQ, Hq, 128], lse fp32 [B, Hq, NQ] or null.  q/tq share strides, and so
+// do k/tk/v/tv.  Keys [0, text_len) are visible below text_valid[b] (null: all), later keys always.
+struct AttnJvpArgs {
+  const void* q; const void* k; const void* v;
+  const void* tq; const void* tk; const void* tv;
+  float* out; float* tangent; float* lse;
+  const int* text_valid;
+  int64_t nq, nk, text_len, batch;
+  int64_t q_row_stride, q_batch_stride, kv_row_stride, kv_batch_stride;
+  int hq, hkv;
+  float scale;
+  int* status;
+};
+cudaError_t attention_jvp(const AttnJvpArgs& args, cudaStream_t stream);
+
 // ------------------------------------------------------------------ streaming cache
 // dst[t] = rotate(src[t < sink ? t : t + shift]) for t < kept_tokens; rows are
 // [token][heads][128] bf16; cos/sin fp32 [kept_tokens, 128] or null (plain move).

@@ -264,6 +264,41 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   return {dq, dk, dv};
 }
 
+// (O, tangent of O, LSE) of dense attention under forward-mode differentiation.
+std::tuple<Tensor, Tensor, Tensor> attn_jvp(const Tensor& q, const Tensor& k, const Tensor& v,
+                                            const Tensor& tq, const Tensor& tk, const Tensor& tv,
+                                            double scale, int64_t text_len,
+                                            c10::optional<Tensor> text_valid) {
+  for (const Tensor* t : {&q, &k, &v, &tq, &tk, &tv}) {
+    check_bf16(*t, "attn_jvp operand");
+    TORCH_CHECK(t->dim() == 4 && t->size(3) == 128 && t->is_contiguous(),
+                "attn_jvp operands are contiguous [B, N, H, 128]");
+  }
+  TORCH_CHECK(tq.sizes() == q.sizes() && tk.sizes() == k.sizes() && tv.sizes() == v.sizes() &&
+                  k.sizes() == v.sizes() && k.size(0) == q.size(0), "attn_jvp shapes disagree");
+  c10::cuda::CUDAGuard guard(q.device());
+  auto f32 = q.options().dtype(torch::kFloat32);
+  Tensor out = torch::empty(q.sizes(), f32), tangent = torch::empty(q.sizes(), f32);
+  Tensor lse = torch::empty({q.size(0), q.size(2), q.size(1)}, f32);
+  agb::AttnJvpArgs a{};
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.tq = tq.data_ptr(); a.tk = tk.data_ptr(); a.tv = tv.data_ptr();
+  a.out = out.data_ptr<float>(); a.tangent = tangent.data_ptr<float>(); a.lse = lse.data_ptr<float>();
+  if (text_valid.has_value()) {
+    TORCH_CHECK(text_valid->scalar_type() == torch::kInt32 && text_valid->numel() == q.size(0) &&
+                    text_valid->is_cuda(), "text_valid must be int32 [B] on the device");
+    a.text_valid = text_valid->data_ptr<int>();
+  }
+  a.nq = q.size(1); a.nk = k.size(1); a.text_len = text_len; a.batch = q.size(0);
+  a.q_row_stride = q.stride(1); a.q_batch_stride = q.stride(0);
+  a.kv_row_stride = k.stride(1); a.kv_batch_stride = k.stride(0);
+  a.hq = int(q.size(2)); a.hkv = int(k.size(2));
+  a.scale = float(scale);
+  a.status = status_word(q.device().index()).data_ptr<int>();
+  check(agb::attention_jvp(a, stream_of(q)), "attention_jvp");
+  return {out, tangent, lse};
+}
+
 // ---------------------------------------------------------------- tensor-parallel serving
 // out = a @ b^T coupled to the peers (see agb::TpLink).  With a_ready the producer waits for
 // pushed rows of `a`; with slot_ptrs the output goes to the owners' partial-sum slots and
@@ -451,6 +486,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relocate", &relocate);
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);
+  m.def("attn_jvp", &attn_jvp);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_reduce_norm", &tp_reduce_norm);
   m.def("tp_signal_done", &tp_signal_done);

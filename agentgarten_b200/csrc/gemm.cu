@@ -28,6 +28,10 @@ constexpr int ATOM_BYTES = 64 * BK * 2;  // one 64-wide MN-major atom column: BK
 constexpr int GROUP_M = 16;              // tile rasterisation: 16 M-tiles per N sweep
 constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// A pushing (tensor-parallel) launch adds 4 KiB per epilogue warp: 32 rows x 64 columns of bf16
+// are transposed there so that rows leave for the peer as whole 128-byte lines.
+constexpr int PUSH_STAGE_BYTES = 32 * 128;
+constexpr int SMEM_BYTES_PUSH = SMEM_BYTES + 4 * PUSH_STAGE_BYTES;
 
 struct Params {
   __nv_bfloat16* out_bf16;
@@ -248,6 +252,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
             (int64_t(p.tp.rank) * p.tp.tiles_owned + tm / p.tp.world) * BM + warp * 32 + lane;
         out_row = static_cast<__nv_bfloat16*>(p.tp.slot[owner]) + slot_row * p.ldo;
       }
+      if (p.tp.push) {
+        // Tensor-parallel push: rows go to the owner's slot through NVLink.  A lane holds one
+        // row in TMEM order; 64 columns at a time are exchanged through shared memory (16-byte
+        // chunks, XOR-swizzled by row so neither side has bank conflicts) and leave as 128
+        // contiguous bytes per row, 4 rows per store instruction.
+        uint8_t* stage = smem + STAGES * STAGE_BYTES + 256 + warp * PUSH_STAGE_BYTES;
+        __nv_bfloat16* tile_base = static_cast<__nv_bfloat16*>(p.tp.slot[owner]) +
+            ((int64_t(p.tp.rank) * p.tp.tiles_owned + tm / p.tp.world) * BM + warp * 32) * p.ldo;
+        const int rows_left = p.m - (tm * BM + warp * 32);  // valid rows of this warp's 32
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = tn * BN + c * 32;
+          if (col0 >= p.n) break;  // uniform across the CTA
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = (c & 1) * 4 + g;
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = make_uint4(
+                pack_bf16(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1])),
+                pack_bf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3])),
+                pack_bf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5])),
+                pack_bf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7])));
+          }
+          const bool last = (c & 1) || (col0 + 32 >= p.n);
+          if (last) {
+            __syncwarp();
+            const int first_col = tn * BN + (c & ~1) * 32;  // of the 64-column group
+            const int chunk = lane & 7;
+            const int col = first_col + chunk * 8;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = 4 * i + (lane >> 3);
+              const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+              const bool filled = (c & 1) || chunk < 4;  // an odd group of 32 columns fills half
+              if (rr < rows_left && col < p.n && filled)
+                *reinterpret_cast<uint4*>(tile_base + int64_t(rr) * p.ldo + col) = v;
+            }
+            __syncwarp();
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         const int col0 = tn * BN + c * 32;
@@ -308,6 +355,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
           }
         }
       }
+      }
       tc_fence_before_sync();
       if (p.tp.push) __threadfence_system();  // this lane's stores before the warp's arrival
       __syncwarp();
@@ -352,7 +400,7 @@ cudaError_t launch(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& 
   static bool configured = false;  // per instantiation
   if (!configured) {
     cudaError_t e =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_PUSH);
     if (e != cudaSuccess) {
       set_error_detail("gemm: cudaFuncSetAttribute(max dynamic shared memory) failed");
       return e;
@@ -360,7 +408,7 @@ cudaError_t launch(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& 
     configured = true;
   }
   (void)cudaGetLastError();  // do not report an error left behind by an earlier call
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  kernel<<<grid, NUM_THREADS, p.tp.push ? SMEM_BYTES_PUSH : SMEM_BYTES, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_error_detail("gemm: kernel launch failed");
   return e;

@@ -32,12 +32,16 @@ def _has_tangent(*tensors: torch.Tensor) -> bool:
 
 
 # --------------------------------------------------------------------------- JVP
-def attention_jvp(q, k, v, dq, dk, dv, key_mask=None):
-    """Primal and tangent of softmax attention, ``[B, N, H, D]`` layout → ``(O, dO)`` FP32."""
+def attention_jvp(q, k, v, dq, dk, dv, key_mask=None, prefix=None):
+    """Primal and tangent of softmax attention, ``[B, N, H, D]`` layout → ``(O, dO)`` FP32.
+
+    ``prefix = (text_len, text_valid)`` states that ``key_mask`` is a prefix-valid text
+    segment followed by visible keys, the form the kernel masks by itself.
+    """
     if native.use(q) and q.shape[-1] == 128:
         from .attention_native import jvp_dense
 
-        return jvp_dense(q, k, v, dq, dk, dv, key_mask)
+        return jvp_dense(q, k, v, dq, dk, dv, key_mask, prefix)
     o, do = reference.attention_jvp(q, k, v, dq, dk, dv, key_mask)
     return o.float(), do.float()
 
@@ -46,16 +50,17 @@ class _AttentionWithJVP(torch.autograd.Function):
     """Dense attention that also defines its forward-mode derivative."""
 
     @staticmethod
-    def forward(q, k, v, key_mask):
+    def forward(q, k, v, key_mask, prefix):
         # a fresh contiguous tensor: forward-mode AD rejects outputs that are views
         return reference.attention(q, k, v, key_mask).contiguous()
 
     @staticmethod
     def setup_context(ctx, inputs, output):
-        q, k, v, key_mask = inputs
+        q, k, v, key_mask, prefix = inputs
         ctx.save_for_forward(q, k, v)
         ctx.save_for_backward(q, k, v)
         ctx.key_mask = key_mask
+        ctx.prefix = prefix
 
     @staticmethod
     def backward(ctx, grad):
@@ -64,28 +69,29 @@ class _AttentionWithJVP(torch.autograd.Function):
             q_, k_, v_ = (t.detach().requires_grad_(True) for t in (q, k, v))
             out = reference.attention(q_, k_, v_, ctx.key_mask)
             gq, gk, gv = torch.autograd.grad(out, (q_, k_, v_), grad)
-        return gq, gk, gv, None
+        return gq, gk, gv, None, None
 
     @staticmethod
-    def jvp(ctx, dq, dk, dv, _dmask):
+    def jvp(ctx, dq, dk, dv, _dmask, _dprefix):
         q, k, v = ctx.saved_tensors
         tangents = [torch.zeros_like(x) if dx is None else dx
                     for x, dx in ((q, dq), (k, dk), (v, dv))]
-        _, tangent = attention_jvp(q, k, v, *tangents, key_mask=ctx.key_mask)
+        _, tangent = attention_jvp(q, k, v, *tangents, key_mask=ctx.key_mask, prefix=ctx.prefix)
         return tangent.to(q.dtype).contiguous()
 
 
 # ------------------------------------------------------------------------- dense
-def attention(q, k, v, key_mask=None, causal: bool = False):
+def attention(q, k, v, key_mask=None, causal: bool = False, prefix=None):
     """Softmax attention on ``[B, N, H, D]`` tensors with grouped KV heads.
 
-    ``key_mask`` ``[B, NK]`` (True = visible) must describe a prefix-valid text segment
-    followed by visible keys for the kernel path; arbitrary masks use the PyTorch path.
+    ``key_mask`` ``[B, NK]`` (True = visible); ``prefix = (text_len, text_valid)`` may state
+    that it is a prefix-valid text segment followed by visible keys, which the tangent
+    kernel masks by itself; arbitrary masks use the PyTorch path.
     """
     if _has_tangent(q, k, v):
         if causal:
             raise NotImplementedError("forward-mode causal attention is not used by any recipe")
-        return _AttentionWithJVP.apply(q, k, v, key_mask)
+        return _AttentionWithJVP.apply(q, k, v, key_mask, prefix)
     if native.use(q) and q.shape[-1] == 128 and key_mask is None:
         from .attention_native import dense
 
@@ -193,12 +199,13 @@ def planned_attention(queries, keys, values, plan, *, text_keys=None, text_value
             ks, vs = [text_keys, *ks], [text_values, *vs]
         key = torch.cat(ks, dim=1) if len(ks) > 1 else ks[0]
         value = torch.cat(vs, dim=1) if len(vs) > 1 else vs[0]
-        mask = None
+        mask, prefix = None, None
         if text_len:
             mask = _text_mask(text_valid, text_len, key.shape[1] - text_len, key.device)
+            prefix = (text_len, text_valid)
         query = torch.cat([queries[i] for i in members], dim=1) if len(members) > 1 \
             else queries[members[0]]
-        out = attention(query, key, value, mask)
+        out = attention(query, key, value, mask, prefix=prefix)
         for i, piece in zip(members, out.split([queries[i].shape[1] for i in members], dim=1)):
             outputs[i] = piece
     return outputs

@@ -63,12 +63,23 @@ def dense(q, k, v, causal: bool = False):
     return _SegmentAttention.apply(q, k, v, None, None, None, schedule, q.shape[-1] ** -0.5)
 
 
-def jvp_dense(q, k, v, dq, dk, dv, key_mask):
-    # The tcgen05 JVP kernel is selected here once it is built into the extension.
+def jvp_dense(q, k, v, dq, dk, dv, key_mask, prefix=None):
+    """Primal and tangent on the tcgen05 JVP kernel.
+
+    ``prefix = (text_len, text_valid)`` describes a key mask of the form "the first
+    ``text_valid[b]`` of the first ``text_len`` keys, then everything"; any other mask goes
+    to the FP64 PyTorch formula.  Tangents are rounded to bf16 like the primals.
+    """
     C = native.ext()
-    if hasattr(C, "attn_jvp") and key_mask is None:
-        native.count()
-        return C.attn_jvp(q.contiguous(), k.contiguous(), v.contiguous(), dq.contiguous(),
-                          dk.contiguous(), dv.contiguous(), q.shape[-1] ** -0.5)
-    o, do = reference.attention_jvp(q, k, v, dq, dk, dv, key_mask)
-    return o.float(), do.float()
+    if key_mask is not None and prefix is None:
+        o, do = reference.attention_jvp(q, k, v, dq, dk, dv, key_mask)
+        return o.float(), do.float()
+    native.count()
+    text_len, text_valid = (0, None) if prefix is None else prefix
+    if text_valid is not None:
+        text_valid = text_valid.to(device=q.device, dtype=torch.int32).contiguous()
+    bf16 = torch.bfloat16
+    out, tangent, _ = C.attn_jvp(q.to(bf16).contiguous(), k.to(bf16).contiguous(), v.to(bf16).contiguous(),
+                                 dq.to(bf16).contiguous(), dk.to(bf16).contiguous(), dv.to(bf16).contiguous(),
+                                 q.shape[-1] ** -0.5, int(text_len), text_valid)
+    return out, tangent

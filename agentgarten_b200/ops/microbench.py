@@ -93,6 +93,18 @@ def bench_attention(tokens: int, launches: int, heads: int = 32, kv_heads: int =
              "tflops": 2.5 * flops / bwd / 1e9}]
 
 
+def bench_jvp(tokens: int, launches: int, heads: int = 32, kv_heads: int = 8) -> list[dict]:
+    from agentgarten_b200.ops.attention import attention_jvp
+
+    q, tq = (torch.randn(1, tokens, heads, 128, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    k, v, tk, tv = (torch.randn(1, tokens, kv_heads, 128, device="cuda", dtype=torch.bfloat16)
+                    for _ in range(4))
+    ms = _time(lambda: attention_jvp(q, k, v, tq, tk, tv), launches)
+    flops = 3.0 * 4.0 * tokens * tokens * heads * 128  # six products against the forward's two
+    return [{"kernel": "attn_jvp_kernel", "case": f"{tokens} tokens, {heads}/{kv_heads} heads x 128, dense",
+             "ms": ms, "tflops": flops / ms / 1e9}]
+
+
 def bench_pointwise(tokens: int, launches: int) -> list[dict]:
     out = []
     x = torch.randn(tokens, 4096, device="cuda", dtype=torch.bfloat16)
@@ -108,7 +120,7 @@ def bench_pointwise(tokens: int, launches: int) -> list[dict]:
     return out
 
 
-CASES = {"gemm": bench_gemm, "attention": bench_attention, "pointwise": bench_pointwise}
+CASES = {"gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
 
 
 def main(argv=None) -> int:

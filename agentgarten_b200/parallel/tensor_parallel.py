@@ -67,6 +67,24 @@ class TensorParallelServing:
         self.kv_slice = slice(self.rank * self.kv_heads, (self.rank + 1) * self.kv_heads)
         self._shard_weights()
         self._allocate()
+        # Set to a dict to collect (start, stop) CUDA events per phase of run() (eager mode only).
+        self.trace: dict[str, list] | None = None
+
+    def _mark(self, phase: str, start: torch.cuda.Event | None = None):
+        """Phase timing for diagnosis: returns a started event, or closes one under ``phase``."""
+        if self.trace is None or torch.cuda.is_current_stream_capturing():
+            return None
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        if start is not None:
+            self.trace.setdefault(phase, []).append((start, event))
+        return event
+
+    def trace_summary(self) -> dict[str, float]:
+        """Mean milliseconds per phase call and calls per phase, from the collected events."""
+        torch.cuda.synchronize(self.device)
+        return {phase: sum(a.elapsed_time(b) for a, b in spans) / len(spans)
+                for phase, spans in (self.trace or {}).items()}
 
     # ------------------------------------------------------------------------ set-up
     @torch.no_grad()
@@ -168,21 +186,32 @@ class TensorParallelServing:
         layers = self.layers
         self._reduce(m, owned, layers[0]["norm_in"], tokens.reshape(m, self.hidden).contiguous())
         for index, w in enumerate(layers):
+            t0 = self._mark("")
             qkv = self._gather_gemm(x, w["qkv"], close=True)
+            t1 = self._mark("gather+qkv gemm", t0)
             q = ops.head_norm_rope(qkv[:, :q_cols].contiguous().view(1, m, self.heads, self.dim),
                                    w["norm_q"], cos, sin, w["head_eps"])
             k = ops.head_norm_rope(qkv[:, q_cols:q_cols + kv_cols].contiguous().view(1, m, self.kv_heads, self.dim),
                                    w["norm_k"], cos, sin, w["head_eps"])
             v = qkv[:, q_cols + kv_cols:].contiguous().view(1, m, self.kv_heads, self.dim)
+            t2 = self._mark("head norm + rope", t1)
             (mixed,) = attend(index, [q], [k], [v])
+            t3 = self._mark("cache write + attention", t2)
             self._scatter_gemm(mixed.reshape(m, q_cols), w["out"], owned)
+            t4 = self._mark("out gemm + scatter", t3)
             self._reduce(m, owned, w["norm_mid"], None)
+            t5 = self._mark("reduce + norm + push", t4)
             gate = self._gather_gemm(x, w["gate"], close=False)
             up = self._gather_gemm(x, w["up"], close=True)
-            self._scatter_gemm(ops.silu_mul(gate, up), w["down"], owned)
+            t6 = self._mark("gather+gate/up gemm", t5)
+            act = ops.silu_mul(gate, up)
+            t7 = self._mark("silu mul", t6)
+            self._scatter_gemm(act, w["down"], owned)
+            t8 = self._mark("down gemm + scatter", t7)
             following = layers[index + 1]["norm_in"] if index + 1 < len(layers) \
                 else self.network.norm_moe_gen.weight
             self._reduce(m, owned, following, None)
+            self._mark("reduce + norm + push", t8)
         # The head reads the gathered, normalised rows (and closes this use of X); the end of
         # the step is then announced to every rank, whose next step overwrites X here.
         head = self.network.proj_out

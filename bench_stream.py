@@ -24,6 +24,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=36)
     parser.add_argument("--no-graphs", action="store_true")
     parser.add_argument("--tensor-parallel", action="store_true")
+    parser.add_argument("--trace", action="store_true",
+                        help="eager run with per-phase CUDA events of the tensor-parallel layers")
     args = parser.parse_args()
 
     import os
@@ -54,6 +56,8 @@ def main() -> int:
     cond.to(torch.bfloat16).to_empty(device=device)
     random_init_(cond.text_encoder, seed=1)
     sharded = world > 1 or args.tensor_parallel
+    if args.trace:
+        args.no_graphs = True
     prepare_serving(net, cuda_graphs=not args.no_graphs, tensor_parallel=True if sharded else None,
                     max_tokens=4096)
     policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=24, rope="top_aligned",
@@ -76,6 +80,8 @@ def main() -> int:
     times = []
     launches_before = native.launches()
     for block in range(args.blocks):
+        if args.trace and sharded and block == args.blocks - 2:
+            net._tensor_parallel.trace = {}
         cond_block = condition(4)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -95,6 +101,8 @@ def main() -> int:
         gathered = torch.tensor(times + [float(status)], device=device)
         dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
         times, status = gathered[:-1].tolist(), int(gathered[-1].item())
+    if args.trace and sharded and rank == 0:
+        print("phase ms (mean per call, rank 0):", json.dumps(net._tensor_parallel.trace_summary()))
     if rank != 0:
         dist.destroy_process_group()
         return 0

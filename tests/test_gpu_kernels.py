@@ -248,3 +248,45 @@ def test_attention_backward_planned_with_text():
         reference.attention(qs[i], kk, vv, mask).backward(grads[i].float())
     for mine, ref in zip([*queries, *keys, *values], [*qs, *ks, *vs]):
         assert _rel(mine.grad, ref.grad) < 2e-2
+
+
+@pytest.mark.parametrize("nq,nk,text_len,valid", [(256, 320, 0, None), (200, 450, 0, None),
+                                                   (130, 300, 96, (96, 17)), (64, 64, 64, (5, 64))])
+def test_attention_jvp_kernel_matches_fp64(nq, nk, text_len, valid):
+    from agentgarten_b200.ops import reference
+    from agentgarten_b200.ops.attention import attention_jvp
+
+    torch.manual_seed(nq + nk)
+    batch, hq, hkv = 2, 4, 2
+    q, tq = (torch.randn(batch, nq, hq, 128, device=DEV).bfloat16() for _ in range(2))
+    k, v, tk, tv = (torch.randn(batch, nk, hkv, 128, device=DEV).bfloat16() for _ in range(4))
+    mask, prefix = None, None
+    if valid is not None:
+        lengths = torch.tensor(valid, device=DEV)
+        mask = torch.ones(batch, nk, dtype=torch.bool, device=DEV)
+        mask[:, :text_len] = torch.arange(text_len, device=DEV)[None] < lengths[:, None]
+        prefix = (text_len, lengths)
+    out, tangent = attention_jvp(q, k, v, tq, tk, tv, key_mask=mask, prefix=prefix)
+    want, want_tangent = reference.attention_jvp(q, k, v, tq, tk, tv, mask)
+    assert out.dtype == torch.float32 and tangent.dtype == torch.float32
+    assert _rel(out, want) < 1e-2, _rel(out, want)
+    assert _rel(tangent, want_tangent) < 2e-2, _rel(tangent, want_tangent)
+    assert int(native.ext().status(0).item()) == 0
+
+
+def test_forward_mode_through_the_attention_op_uses_the_kernel():
+    import torch.autograd.forward_ad as fwAD
+
+    from agentgarten_b200 import ops
+    from agentgarten_b200.ops import reference
+
+    torch.manual_seed(0)
+    q, tq = (torch.randn(1, 192, 4, 128, device=DEV).bfloat16() for _ in range(2))
+    k, v, tk, tv = (torch.randn(1, 256, 2, 128, device=DEV).bfloat16() for _ in range(4))
+    before = native.launches()
+    with fwAD.dual_level():
+        out = ops.attention(fwAD.make_dual(q, tq), fwAD.make_dual(k, tk), fwAD.make_dual(v, tv))
+        primal, tangent = fwAD.unpack_dual(out)
+    assert native.launches() > before
+    want, want_tangent = reference.attention_jvp(q, k, v, tq, tk, tv)
+    assert _rel(primal, want) < 2e-2 and _rel(tangent, want_tangent) < 3e-2
