@@ -290,3 +290,31 @@ def test_forward_mode_through_the_attention_op_uses_the_kernel():
     assert native.launches() > before
     want, want_tangent = reference.attention_jvp(q, k, v, tq, tk, tv)
     assert _rel(primal, want) < 2e-2 and _rel(tangent, want_tangent) < 3e-2
+
+
+def test_a_peer_that_never_arrives_ends_the_wait_with_a_status():
+    """A gather-GEMM whose input rows are never announced gives up after its bounded wait,
+    records the peer-timeout code and leaves the context usable."""
+    C = native.ext()
+    torch.cuda.synchronize()
+    status = C.status(0)
+    status.zero_()
+    a = torch.randn(256, 256, device=DEV).bfloat16()
+    w = torch.randn(512, 256, device=DEV).bfloat16()
+    out = torch.empty(256, 512, device=DEV, dtype=torch.bfloat16)
+    ready = torch.zeros(2, dtype=torch.int32, device=DEV)   # nothing ever advances these
+    seen = torch.zeros(2, dtype=torch.int32, device=DEV)
+    ticket = torch.zeros(1, dtype=torch.int32, device=DEV)
+    C.tp_gemm(a, w, out, 0, 1, ready, seen, ticket, [], [], 0)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 5  # kTimeoutPeer
+    status.zero_()
+    # the same call completes once the rows are announced, and ordinary kernels still run
+    ready.fill_(128)
+    seen.zero_()
+    ticket.zero_()
+    C.tp_gemm(a, w, out, 0, 1, ready, seen, ticket, [], [], 0)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert _rel(out, a.float() @ w.float().t()) < 1e-2
+    assert seen.tolist() == [128, 128]
