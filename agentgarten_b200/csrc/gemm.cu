@@ -54,7 +54,7 @@ __device__ __forceinline__ bool wait_counter(const int* counter, int target, con
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
     if (seen - target >= 0) return true;
     if (*g.abort_flag) return false;
-    if (global_timer_ns() - start > AGB_WAIT_LIMIT_NS) {
+    if (global_timer_ns() - start > AGB_PEER_WAIT_LIMIT_NS) {
       *g.abort_flag = 1;
       if (g.status) atomicCAS(g.status, 0, kTimeoutPeer);
       return false;

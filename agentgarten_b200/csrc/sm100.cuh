@@ -29,6 +29,9 @@ enum : int {
 #ifndef AGB_WAIT_LIMIT_NS
 #define AGB_WAIT_LIMIT_NS 2000000000ull
 #endif
+// Waits on another GPU's counter give up first, so that the code reported for a missing peer
+// is kTimeoutPeer and not the timeout of a warp that was waiting behind it.
+#define AGB_PEER_WAIT_LIMIT_NS (AGB_WAIT_LIMIT_NS / 2)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -55,7 +55,7 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a
         int seen;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
         if (seen - target >= 0) break;
-        if (global_timer_ns() - start > AGB_WAIT_LIMIT_NS) {
+        if (global_timer_ns() - start > AGB_PEER_WAIT_LIMIT_NS) {
           if (a.status) atomicCAS(a.status, 0, kTimeoutPeer);
           go = 0;
           break;

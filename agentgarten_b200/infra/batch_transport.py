@@ -204,6 +204,7 @@ def prepare_batch(context, data_batch: Batch | None, *, owner_rank: int | None,
                 rng = _rng_snapshot()
         except BaseException as error:
             cause, status, rank, message = error, ERROR, dist.get_rank(), _brief(error)
+            skeleton = specs = rng = None  # whatever failed must not ride on the status message
     if context.enabled:
         box = [status, rank, message, rng, skeleton, specs]
         context.broadcast_objects(box, source_rank=int(owner_rank))

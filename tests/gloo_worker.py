@@ -1,0 +1,179 @@
+"""Worker for the CPU multi-rank tests: ``torchrun ... tests/gloo_worker.py <case> [args]``.
+
+Failures are injected on the host only: a dataset iterator that raises on one rank, an
+iterator that ends early on one rank, an unpicklable batch.  Every case ends with all ranks
+agreeing on what happened; ``CASE_OK`` is printed by rank 0.
+"""
+
+import os
+import sys
+from datetime import timedelta
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from agentgarten_b200.infra.batch_transport import fetch_batch, prepare_batch  # noqa: E402
+from agentgarten_b200.infra.model import ContextParallelContext  # noqa: E402
+
+
+def _cp_context(size):
+    from torch.distributed.device_mesh import init_device_mesh
+
+    world = dist.get_world_size()
+    if size == 1:
+        return ContextParallelContext(None)
+    mesh = init_device_mesh("cpu", (world // size, size), mesh_dim_names=("dp", "cp"))
+    return ContextParallelContext(mesh["cp"])
+
+
+def case_fetch_error_reaches_every_rank():
+    """Rank 1's dataset raises: every rank gets a RuntimeError naming rank 1."""
+    rank = dist.get_rank()
+    context = ContextParallelContext(None)
+
+    def batches():
+        yield {"x": torch.full((2,), float(rank))}
+        if rank == 1:
+            raise ValueError("corrupt sample 17")
+        yield {"x": torch.zeros(2)}
+
+    iterator = batches()
+    batch, exhausted, owner = fetch_batch(context, iterator, sequence_index=0)
+    assert not exhausted and owner is None and float(batch["x"][0]) == rank
+    try:
+        fetch_batch(context, iterator, sequence_index=1)
+    except RuntimeError as error:
+        assert "rank 1" in str(error) and "corrupt sample 17" in str(error), str(error)
+    else:
+        raise AssertionError("the failure of rank 1 did not surface on rank %d" % rank)
+
+
+def case_uneven_end_stops_everyone():
+    """Rank 0 runs out of data one batch early: all ranks report exhaustion together."""
+    rank = dist.get_rank()
+    context = ContextParallelContext(None)
+    iterator = iter([{"i": 0}] * (2 if rank == 0 else 3))
+    seen = 0
+    while True:
+        batch, exhausted, _ = fetch_batch(context, iterator, sequence_index=seen)
+        if exhausted:
+            break
+        seen += 1
+    assert seen == 2, seen
+
+
+def case_cp_transport_shares_batch_and_rng():
+    """Owner i % cp reads and prepares; the others receive tensors, structure and RNG state."""
+    rank = dist.get_rank()
+    context = _cp_context(2)
+    assert context.enabled and context.size == 2
+
+    def batches():
+        for i in range(4):
+            g = torch.Generator().manual_seed(1000 * rank + i)
+            shared = torch.randn(3, 5, generator=g)
+            yield {"latent": shared, "alias": shared, "ids": torch.arange(4) + 10 * rank + i,
+                   "meta": {"caption": f"clip {rank}-{i}", "fps": 16.0}, "empty": torch.zeros(0, 2)}
+
+    iterator = batches()
+    for index in range(4):
+        batch, exhausted, owner = fetch_batch(context, iterator, sequence_index=index)
+        assert not exhausted and owner == index % 2
+        assert (batch is not None) == (context.rank == owner)
+
+        def prepare(b):
+            torch.manual_seed(7 + index)  # the owner's generator state travels with the batch
+            return {**b, "latent": b["latent"].double() * 2}
+
+        out = prepare_batch(context, batch, owner_rank=owner, prepare=prepare)
+        assert out["latent"].dtype == torch.float64 and out["alias"] is not None
+        assert out["meta"]["caption"].startswith("clip ") and out["empty"].shape == (0, 2)
+        gathered = [None] * 2
+        dist.all_gather_object(gathered, (out["latent"].sum().item(), out["ids"].tolist(),
+                                          out["meta"]["caption"], torch.rand(1).item()),
+                               group=context.group)
+        assert gathered[0] == gathered[1], gathered  # same data and same next random number
+        owner_global = context.global_rank(owner)
+        assert out["meta"]["caption"].startswith(f"clip {owner_global}-")
+
+
+def case_cp_prepare_error_reaches_the_group():
+    context = _cp_context(2)
+
+    def prepare(b):
+        raise FloatingPointError("encoder overflow")
+
+    batch = {"x": torch.ones(2)} if context.rank == 0 else None
+    try:
+        prepare_batch(context, batch, owner_rank=0, prepare=prepare)
+    except RuntimeError as error:
+        assert "encoder overflow" in str(error)
+    else:
+        raise AssertionError("prepare failure did not surface")
+    # an unpicklable leaf is reported the same way instead of hanging the receivers
+    bad = {"x": torch.ones(2), "fn": (lambda: 0)} if context.rank == 0 else None
+    try:
+        prepare_batch(context, bad, owner_rank=0, prepare=lambda b: b)
+    except RuntimeError as error:
+        assert "prepare failed" in str(error)
+    else:
+        raise AssertionError("unpicklable batch did not surface")
+
+
+def case_context_parallel_matches_single_group():
+    """Two CP ranks reproduce the loss and gradients of the unsharded model on the same clip."""
+    from helpers import synthetic_batch, tiny_conditioner, tiny_config, tiny_network
+
+    from agentgarten_b200.models.diffusion import DiffusionModel
+    from agentgarten_b200.parallel.engine import ParallelConfig
+
+    config = tiny_config()
+    losses, grads = {}, {}
+    for cp in (1, 2):
+        net = tiny_network(config, seed=0)
+        cond = tiny_conditioner(config, seed=1)
+        parallel = ParallelConfig(parameter_dtype="float32", context_parallel_size=cp,
+                                  activation_checkpointing="none")
+        model = DiffusionModel(net=net, conditioner=cond, text_dropout=0.0, parallel=parallel,
+                               conditioner_parallel=ParallelConfig(parameter_dtype="float32",
+                                                                   activation_checkpointing="none"))
+        model.parallelize(torch.device("cpu"))
+        batch = model.prepare_data_batch(synthetic_batch(frames=5, seed=3))
+        torch.manual_seed(11)
+        model.train()
+        loss = None
+        for _name, closure, _last in model.training_step_closures(batch, iteration=0):
+            outputs, loss = closure()
+            loss.backward()
+        losses[cp] = float(loss)
+        grads[cp] = {n: p.grad.clone() for n, p in model.net.named_parameters() if p.grad is not None}
+    assert abs(losses[1] - losses[2]) < 1e-5 * max(1.0, abs(losses[1])), losses
+    world = 2
+    for name, full in grads[1].items():
+        part = grads[2][name].clone()
+        dist.all_reduce(part)  # each CP rank holds the gradient of its token shard
+        scale = float(full.abs().max()) + 1e-8
+        assert float((part - full).abs().max()) / scale < 2e-4 or \
+            float((part / world - full).abs().max()) / scale < 2e-4, name
+
+
+CASES = {name[5:]: fn for name, fn in list(globals().items()) if name.startswith("case_")}
+
+
+def main():
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("gloo", timeout=timedelta(seconds=120))
+    try:
+        CASES[sys.argv[1]]()
+        dist.barrier()
+        if dist.get_rank() == 0:
+            print("CASE_OK", sys.argv[1])
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
