@@ -2,16 +2,22 @@
 // segment-list keys (text prefix with per-sample valid length + visual segments).
 //
 // One CTA per (query tile of 128 rows, query head, sample):
-//   warps 0-3  softmax: one query row per thread; S tile TMEM -> registers, online softmax
-//              in the exp2 domain, probabilities written back to TMEM as packed bf16
-//   warp 4     TMA producer: Q once, then K and V tiles through 2-stage rings
-//   warp 5     MMA issuer:   S = Q K^T (operands in shared memory) and O += P V with P read
+//   warps 0-3  softmax group A: key tiles 0, 2, 4, ...   one query row per thread
+//   warps 4-7  softmax group B: key tiles 1, 3, 5, ...   (same rows, the other tiles)
+//   warp 8     TMA producer: Q once, then K and V tiles through 2-stage rings
+//   warp 9     MMA issuer:   S = Q K^T (operands in shared memory) and O += P V with P read
 //              from TMEM, both accumulating in TMEM
-// S is double-buffered so the tensor core computes S[j+1] while the softmax works on S[j].
-// The running output stays in TMEM and is rescaled lazily: only when a row maximum grows
-// by more than 2^8 does a warp rescale its 32 rows of O.
+// The softmax (exponentials on the special-function unit, conversion, packing) costs more
+// cycles per tile than the two products, so two groups work on alternate key tiles.  Each
+// group has its own score buffer, its own running maximum / sum and its own output
+// accumulator; the probabilities overwrite the first half of the group's score buffer, which
+// the tensor core refills only after the product that reads them has completed.  While one
+// group is in its softmax the tensor core serves the other.  The two partial results are
+// merged at the end like two key splits: O = (O_A 2^(m_A-m) + O_B 2^(m_B-m)) / l.
+// Outputs are rescaled lazily: only when a row maximum grows by more than 2^8 does a warp
+// rescale its 32 rows of its accumulator.
 //
-// TMEM columns: S0 [0,128) S1 [128,256) O [256,384) P0 [384,448) P1 [448,512).
+// TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P_x = S_x[0,64).
 #include "agb.h"
 #include "attention_common.cuh"
 #include "tensormap.h"
@@ -22,11 +28,12 @@ namespace {
 constexpr int KV_STAGES = 2;
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: a 128x128 bf16 tile (2 atoms of 16 KiB)
 constexpr int HALF_BYTES = TILE_BYTES / 2;
-constexpr int FWD_THREADS = 192;
+constexpr int FWD_THREADS = 320;
 constexpr int SMEM_TILES = 1 + 2 * KV_STAGES;  // Q + K ring + V ring
-constexpr int FWD_SMEM = SMEM_TILES * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512;
+constexpr int FWD_SMEM = SMEM_TILES * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512 +
+                         4 * 128 * int(sizeof(float)) /* row maxima and sums of both groups */;
 
-constexpr uint32_t COL_S = 0, COL_O = 256, COL_P = 384;
+constexpr uint32_t COL_S = 0, COL_O = 256;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 struct FwdParams {
@@ -57,13 +64,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* k_empty = bars + 3;       // [2]
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2] MMA -> softmax
-  uint64_t* s_free = bars + 11;       // [2] softmax -> MMA (S buffer read out)
-  uint64_t* p_ready = bars + 13;      // [2] softmax -> MMA
-  uint64_t* pv_done = bars + 15;      // [2] MMA -> softmax (P buffer free, O stable)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* s_full = bars + 9;        // [2] MMA -> softmax group: scores complete
+  uint64_t* p_ready = bars + 11;      // [2] softmax group -> MMA: probabilities in TMEM
+  uint64_t* pv_done = bars + 13;      // [2] MMA -> both: product done, P free, O stable
+  uint64_t* merge = bars + 15;        // both groups' row statistics are in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_tiles_smem = abort_flag + 1;
+  float* stats = reinterpret_cast<float*>(const_cast<int*>(n_tiles_smem) + 2);  // [group][m, l][128]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -83,10 +91,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_free[i], 4);
       mbar_init(&p_ready[i], 4);
       mbar_init(&pv_done[i], 1);
     }
+    mbar_init(merge, 8);
     mbar_fence_init();
     int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
     if (n < 0) {
@@ -95,11 +103,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     *n_tiles_smem = n;
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -110,7 +118,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
   const int n_tiles = *n_tiles_smem;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
@@ -138,7 +146,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         while (global_timer_ns() - start < 100000ull) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // -------------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_tiles > 0) {
       // S = Q K^T: both K-major, 8 k-steps of 16 over d = 128 (two 64-wide atoms).
@@ -150,7 +158,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto issue_s = [&](int j) -> bool {
         const int st = j % KV_STAGES, buf = j & 1;
         if (!mbar_wait(&k_full[st], (j / KV_STAGES) & 1, guard, kTimeoutMma)) return false;
-        if (j >= 2 && !mbar_wait(&s_free[buf], ((j - 2) >> 1) & 1, guard, kTimeoutMma)) return false;
+        // The group's previous probabilities live in this buffer until their product is done.
+        if (j >= 2 && !mbar_wait(&pv_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
 #pragma unroll
@@ -174,9 +183,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           // 16 keys per step: P advances 8 packed columns, V advances 16 rows (2048 B).
-          tc_mma_ts(tmem_base + COL_O, tmem_base + COL_P + buf * 64 + kk * 8,
+          tc_mma_ts(tmem_base + COL_O + buf * 128, tmem_base + COL_S + buf * 128 + kk * 8,
                     make_smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), idesc_o,
-                    (j | kk) != 0);
+                    ((j >> 1) | kk) != 0);
         }
         tc_commit(&v_empty[st]);
         tc_commit(&pv_done[buf]);
@@ -184,122 +193,151 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else {
     // ----------------------------------------------------------------------- softmax
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
-    const int my_row = warp * 32 + lane;        // row within the query tile
-    float m_ref = -INFINITY;                    // reference maximum (log2 domain)
+    const int group = warp >> 2;                 // 0: even key tiles, 1: odd key tiles
+    const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const int my_row = quarter * 32 + lane;      // row within the query tile
+    const uint32_t col_s = tmem_base + lane_base + COL_S + group * 128;
+    const uint32_t col_o = tmem_base + lane_base + COL_O + group * 128;
+    float m_ref = -INFINITY;                     // reference maximum (log2 domain)
     float l_sum = 0.f;
-    bool ok = n_tiles > 0;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int buf = j & 1;
+    bool ok = true;
+    for (int j = group; j < n_tiles && ok; j += 2) {
       const KeyTile t = tiles[j];
-      if (!mbar_wait(&s_full[buf], (j >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(&s_full[group], (j >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t s[4][32];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld_32x32(tmem_base + lane_base + COL_S + buf * 128 + c * 32, s[c]);
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(col_s + c * 32, s[c]);
       tmem_ld_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[buf]);
 
-      int valid = t.valid;
-      if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
-      float m_tile = -INFINITY;
+      // Row maximum of the raw scores (the scale is positive).  Only tiles with masked keys
+      // (a partial last tile, the causal diagonal) pay for the masking.
+      float m_raw = -INFINITY;
+      if (t.valid == ATT_BN && t.causal0 < 0) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(s[c][i]) * p.scale_log2;
-          v = (c * 32 + i < valid) ? v : -INFINITY;
-          s[c][i] = __float_as_uint(v);
-          m_tile = fmaxf(m_tile, v);
-        }
-      // Lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform.
+          for (int i = 0; i < 32; i += 2)
+            m_raw = fmax3(m_raw, __uint_as_float(s[c][i]), __uint_as_float(s[c][i + 1]));
+      } else {
+        int valid = t.valid;
+        if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float v = (c * 32 + i < valid) ? __uint_as_float(s[c][i]) : -INFINITY;
+            s[c][i] = __float_as_uint(v);
+            m_raw = fmaxf(m_raw, v);
+          }
+      }
+      const float m_tile = m_raw * p.scale_log2;
+      // Lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform.  The
+      // group's previous product is complete: these scores were issued after it.
       const bool grow = m_tile > m_ref + RESCALE_THRESHOLD;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, m_tile);
         const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
-        if (j > 0) {
-          // O must be stable: the previous PV product has to be complete.
-          if (!mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, guard, kTimeoutSoftmax)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after_sync();
+        if (j >= 2) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
-            tmem_ld_32x32(tmem_base + lane_base + COL_O + c * 32, o);
+            tmem_ld_32x32(col_o + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(tmem_base + lane_base + COL_O + c * 32, o);
+            tmem_st_32x32(col_o + c * 32, o);
           }
           tmem_st_wait();
         }
         l_sum *= alpha;
         m_ref = m_new;
       }
-      // A fully masked row (causal tiles above the diagonal never occur, but rows past the
-      // chunk end may see valid <= 0) keeps m_ref = -inf: exponentials are forced to zero.
+      // exp2(s * scale - m): one two-lane FMA per pair of keys, then the exponentials.  A
+      // fully masked row keeps m_ref = -inf: its scores are -inf and the shift is 0.
       const float shift = (m_ref == -INFINITY) ? 0.f : m_ref;
-      if (j >= 2 && !mbar_wait(&pv_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutSoftmax)) {
-        ok = false;
-        break;
-      }
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+      const float2 shift2 = make_float2(-shift, -shift);
+      float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           // columns (2i, 2i+1) of the 64-key half c
-          const float a = exp2f(__uint_as_float(s[2 * c + (i >> 4)][(2 * i) & 31]) - shift);
-          const float b = exp2f(__uint_as_float(s[2 * c + (i >> 4)][(2 * i + 1) & 31]) - shift);
-          l_sum += a + b;
-          packed[i] = pack_bf16(a, b);
+          const uint32_t* src = &s[2 * c + (i >> 4)][(2 * i) & 31];
+          const float2 x = ffma2(make_float2(__uint_as_float(src[0]), __uint_as_float(src[1])),
+                                 scale2, shift2);
+          const float2 e = make_float2(exp2f(x.x), exp2f(x.y));
+          sum2 = fadd2(sum2, e);
+          packed[i] = pack_bf16(e.x, e.y);
         }
-        tmem_st_32x32(tmem_base + lane_base + COL_P + buf * 64 + c * 32, packed);
+        tmem_st_32x32(col_s + c * 32, packed);  // over the scores, which are in registers
       }
+      l_sum += sum2.x + sum2.y;
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[buf]);
+      if (lane == 0) mbar_arrive(&p_ready[group]);
     }
     // ---------------------------------------------------------------------- epilogue
-    if (ok) {
-      const int last = n_tiles - 1;
-      ok = mbar_wait(&pv_done[last & 1], (last >> 1) & 1, guard, kTimeoutEpilogue);
+    // Each group waits for its last product and publishes its row statistics; then the two
+    // partial outputs are merged like two key splits, group A writing head-dim columns
+    // [0, 64) and group B [64, 128).
+    const int mine = (n_tiles - group + 1) / 2;  // key tiles this group processed
+    if (ok && mine > 0) {
+      const int last = group + 2 * (mine - 1);
+      ok = mbar_wait(&pv_done[group], (last >> 1) & 1, guard, kTimeoutEpilogue);
     }
-    if (n_tiles == 0 || ok) {
+    stats[(group * 2 + 0) * 128 + my_row] = m_ref;
+    stats[(group * 2 + 1) * 128 + my_row] = l_sum;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(merge);  // release: the stores above are ordered before it
+    if (ok) ok = mbar_wait(merge, 0, guard, kTimeoutEpilogue);
+    if (ok) {
       tc_fence_after_sync();
-      const float inv = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
+      const float m_a = stats[0 * 128 + my_row], l_a = stats[1 * 128 + my_row];
+      const float m_b = stats[2 * 128 + my_row], l_b = stats[3 * 128 + my_row];
+      const float m_all = fmaxf(m_a, m_b);
+      const float w_a = (m_a == -INFINITY) ? 0.f : exp2f(m_a - m_all);
+      const float w_b = (m_b == -INFINITY) ? 0.f : exp2f(m_b - m_all);
+      const float l_all = l_a * w_a + l_b * w_b;
+      const float inv = (l_all > 0.f) ? 1.f / l_all : 0.f;
+      const float f_a = w_a * inv, f_b = w_b * inv;
+      const bool has_a = n_tiles > 0, has_b = n_tiles > 1;  // an unused accumulator is not read
       const bool row_ok = my_row < q_rows;
       __nv_bfloat16* dst =
           p.out + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t o[32];
-        if (n_tiles > 0) {
-          tmem_ld_32x32(tmem_base + lane_base + COL_O + c * 32, o);
-          tmem_ld_wait();
-        } else {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = group * 2 + cc;  // 32-column chunk of the head dimension
+        uint32_t oa[32], ob[32];
+        if (has_a) tmem_ld_32x32(tmem_base + lane_base + COL_O + c * 32, oa);
+        if (has_b) tmem_ld_32x32(tmem_base + lane_base + COL_O + 128 + c * 32, ob);
+        tmem_ld_wait();
+        float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0;
+        for (int i = 0; i < 32; ++i) {
+          float acc = 0.f;
+          if (has_a) acc = __uint_as_float(oa[i]) * f_a;
+          if (has_b) acc += __uint_as_float(ob[i]) * f_b;
+          v[i] = acc;
         }
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
-            v.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
-            v.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
-            v.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = v;
+            uint4 w;
+            w.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
+            w.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
+            w.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
+            w.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
           }
         }
       }
-      if (row_ok && p.lse) {
-        const float lse = (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
+      if (group == 0 && row_ok && p.lse) {
+        const float lse = (l_all > 0.f) ? (m_all + log2f(l_all)) * 0.6931471805599453f : -INFINITY;
         p.lse[(int64_t(batch) * p.hq + head) * p.nq + q_row + my_row] = lse;
       }
     }
@@ -307,7 +345,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
