@@ -1,23 +1,24 @@
 // Flash-attention forward on tcgen05 for head_dim 128 with grouped KV heads and
 // segment-list keys (text prefix with per-sample valid length + visual segments).
 //
-// One CTA per (query tile of 128 rows, query head, sample):
-//   warps 0-3  softmax group A: key tiles 0, 2, 4, ...   one query row per thread
-//   warps 4-7  softmax group B: key tiles 1, 3, 5, ...   (same rows, the other tiles)
-//   warp 8     TMA producer: Q once, then K and V tiles through 2-stage rings
-//   warp 9     MMA issuer:   S = Q K^T (operands in shared memory) and O += P V with P read
-//              from TMEM, both accumulating in TMEM
-// The softmax (exponentials on the special-function unit, conversion, packing) costs more
-// cycles per tile than the two products, so two groups work on alternate key tiles.  Each
-// group has its own score buffer, its own running maximum / sum and its own output
-// accumulator; the probabilities overwrite the first half of the group's score buffer, which
-// the tensor core refills only after the product that reads them has completed.  While one
-// group is in its softmax the tensor core serves the other.  The two partial results are
-// merged at the end like two key splits: O = (O_A 2^(m_A-m) + O_B 2^(m_B-m)) / l.
-// Outputs are rescaled lazily: only when a row maximum grows by more than 2^8 does a warp
-// rescale its 32 rows of its accumulator.
+// One CTA per (query tile of 128 rows, PAIR of query heads that share a KV head, sample):
+//   warps 0-3  softmax of head A: one query row per thread
+//   warps 4-7  softmax of head B
+//   warp 8     TMA producer: both Q tiles once, then K and V tiles through 2-stage rings
+//   warp 9     MMA issuer:   S_h = Q_h K^T (operands in shared memory) and O_h += P_h V with
+//              P_h read from TMEM, for h = A, B, all accumulating in TMEM
+// Every K and V tile that reaches shared memory is used by two heads, which halves the
+// traffic from L2 per FLOP (the single-head kernel ran at the L2 bandwidth limit), and while
+// one head is in its softmax (exponentials on the special-function unit, conversion,
+// packing) the tensor core serves the other.  The probabilities overwrite the first half of
+// the head's score buffer; tcgen05.mma operations of one thread execute in issue order, so
+// the next scores of a head are issued right behind the product that reads its
+// probabilities, without a round trip through a barrier.  The running output stays in TMEM
+// and is rescaled lazily: only when a row maximum grows by more than 2^8 does a warp
+// rescale its 32 rows.  With an odd number of query heads per KV head the CTA serves one
+// head and the second group idles.
 //
-// TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P_x = S_x[0,64).
+// TMEM columns: S_A [0,128) S_B [128,256) O_A [256,384) O_B [384,512); P_h = S_h[0,64).
 #include "agb.h"
 #include "attention_common.cuh"
 #include "tensormap.h"
@@ -29,9 +30,8 @@ constexpr int KV_STAGES = 2;
 constexpr int TILE_BYTES = 128 * 128 * 2;  // 32 KiB: a 128x128 bf16 tile (2 atoms of 16 KiB)
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int FWD_THREADS = 320;
-constexpr int SMEM_TILES = 1 + 2 * KV_STAGES;  // Q + K ring + V ring
-constexpr int FWD_SMEM = SMEM_TILES * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512 +
-                         4 * 128 * int(sizeof(float)) /* row maxima and sums of both groups */;
+constexpr int SMEM_TILES = 2 + 2 * KV_STAGES;  // Q_A, Q_B + K ring + V ring
+constexpr int FWD_SMEM = SMEM_TILES * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512;
 
 constexpr uint32_t COL_S = 0, COL_O = 256;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
@@ -43,6 +43,7 @@ struct FwdParams {
   __nv_bfloat16* out;     // [B, NQ, Hq, 128]
   float* lse;             // [B, Hq, NQ] natural-log LSE
   int nq, hq, group;      // group = Hq / Hkv
+  int heads_per_cta;      // 2 when group is even, else 1
   float scale_log2;       // softmax scale * log2(e)
   int* status;
 };
@@ -54,8 +55,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sQ = smem;                          // [2] tiles
+  uint8_t* sK = smem + 2 * TILE_BYTES;
   uint8_t* sV = sK + KV_STAGES * TILE_BYTES;
   KeyTile* tiles = reinterpret_cast<KeyTile*>(sV + KV_STAGES * TILE_BYTES);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + ATT_MAX_TILES);
@@ -64,20 +65,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* k_empty = bars + 3;       // [2]
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2] MMA -> softmax group: scores complete
-  uint64_t* p_ready = bars + 11;      // [2] softmax group -> MMA: probabilities in TMEM
-  uint64_t* pv_done = bars + 13;      // [2] MMA -> both: product done, P free, O stable
-  uint64_t* merge = bars + 15;        // both groups' row statistics are in shared memory
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* s_full = bars + 9;        // [2 heads] MMA -> softmax: scores of the next tile complete
+  uint64_t* p_ready = bars + 11;      // [2 heads] softmax -> MMA: probabilities in TMEM
+  uint64_t* o_done = bars + 13;       // [2 heads] MMA -> softmax: last product complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_tiles_smem = abort_flag + 1;
-  float* stats = reinterpret_cast<float*>(const_cast<int*>(n_tiles_smem) + 2);  // [group][m, l][128]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int head = blockIdx.y;
+  const int heads = p.heads_per_cta;
+  const int head0 = blockIdx.y * heads;
   const int batch = blockIdx.z;
-  const int kv_head = head / p.group;
+  const int kv_head = head0 / p.group;
   const int* qt = p.q_tiles + 5 * blockIdx.x;
   const int q_row = qt[0], q_rows = qt[1], q_local = qt[4];
   const WaitGuard guard{abort_flag, p.status};
@@ -92,9 +92,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_ready[i], 4);
-      mbar_init(&pv_done[i], 1);
+      mbar_init(&o_done[i], 1);
     }
-    mbar_init(merge, 8);
     mbar_fence_init();
     int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
     if (n < 0) {
@@ -121,9 +120,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_3d(sQ, &tm_q, q_full, head * ATT_D, q_row, batch);
-      tma_load_3d(sQ + HALF_BYTES, &tm_q, q_full, head * ATT_D + 64, q_row, batch);
+      mbar_expect_tx(q_full, heads * TILE_BYTES);
+      for (int h = 0; h < heads; ++h) {
+        tma_load_3d(sQ + h * TILE_BYTES, &tm_q, q_full, (head0 + h) * ATT_D, q_row, batch);
+        tma_load_3d(sQ + h * TILE_BYTES + HALF_BYTES, &tm_q, q_full, (head0 + h) * ATT_D + 64, q_row, batch);
+      }
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j % KV_STAGES;
@@ -153,58 +154,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
       // O += P V: A = P from TMEM (K-major), B = V MN-major (d contiguous), 8 k-steps over keys.
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);
-      const uint32_t q_addr = smem_u32(sQ);
-      bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma);
-      auto issue_s = [&](int j) -> bool {
-        const int st = j % KV_STAGES, buf = j & 1;
-        if (!mbar_wait(&k_full[st], (j / KV_STAGES) & 1, guard, kTimeoutMma)) return false;
-        // The group's previous probabilities live in this buffer until their product is done.
-        if (j >= 2 && !mbar_wait(&pv_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutMma)) return false;
-        tc_fence_after_sync();
-        const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+      auto scores = [&](int h, int j) {
+        const uint32_t q_addr = smem_u32(sQ + h * TILE_BYTES);
+        const uint32_t k_addr = smem_u32(sK + (j % KV_STAGES) * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + COL_S + buf * 128, make_smem_desc(q_addr + off, 16, 1024),
+          tc_mma_ss(tmem_base + COL_S + h * 128, make_smem_desc(q_addr + off, 16, 1024),
                     make_smem_desc(k_addr + off, 16, 1024), idesc_s, kk != 0);
         }
-        tc_commit(&k_empty[st]);
-        tc_commit(&s_full[buf]);
-        return true;
+        tc_commit(&s_full[h]);
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles && !issue_s(j + 1)) { ok = false; break; }
-        const int st = j % KV_STAGES, buf = j & 1;
-        if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1, guard, kTimeoutMma)) { ok = false; break; }
-        if (!mbar_wait(&p_ready[buf], (j >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+      bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma) &&
+                mbar_wait(&k_full[0], 0, guard, kTimeoutMma);
+      if (ok) {
         tc_fence_after_sync();
+        for (int h = 0; h < heads; ++h) scores(h, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % KV_STAGES;
+        const bool more = j + 1 < n_tiles;
+        if (!mbar_wait(&v_full[st], (j / KV_STAGES) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        if (more && !mbar_wait(&k_full[(j + 1) % KV_STAGES], ((j + 1) / KV_STAGES) & 1, guard,
+                               kTimeoutMma)) { ok = false; break; }
         const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
+        for (int h = 0; h < heads && ok; ++h) {
+          if (!mbar_wait(&p_ready[h], j & 1, guard, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          // 16 keys per step: P advances 8 packed columns, V advances 16 rows (2048 B).
-          tc_mma_ts(tmem_base + COL_O + buf * 128, tmem_base + COL_S + buf * 128 + kk * 8,
-                    make_smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), idesc_o,
-                    ((j >> 1) | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk) {
+            // 16 keys per step: P advances 8 packed columns, V advances 16 rows (2048 B).
+            tc_mma_ts(tmem_base + COL_O + h * 128, tmem_base + COL_S + h * 128 + kk * 8,
+                      make_smem_desc(v_addr + kk * 2048, HALF_BYTES, 1024), idesc_o, (j | kk) != 0);
+          }
+          // Issued behind the product above, which reads P from the buffer these scores refill:
+          // the tensor core executes one thread's operations in issue order.
+          if (more) scores(h, j + 1);
+          else tc_commit(&o_done[h]);
         }
+        if (!ok) break;
         tc_commit(&v_empty[st]);
-        tc_commit(&pv_done[buf]);
+        if (more) tc_commit(&k_empty[(j + 1) % KV_STAGES]);
       }
     }
-  } else {
+  } else if ((warp >> 2) < heads) {
     // ----------------------------------------------------------------------- softmax
-    const int group = warp >> 2;                 // 0: even key tiles, 1: odd key tiles
+    const int h = warp >> 2;                     // which head of the pair
+    const int head = head0 + h;
     const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
     const int my_row = quarter * 32 + lane;      // row within the query tile
-    const uint32_t col_s = tmem_base + lane_base + COL_S + group * 128;
-    const uint32_t col_o = tmem_base + lane_base + COL_O + group * 128;
+    const uint32_t col_s = tmem_base + lane_base + COL_S + h * 128;
+    const uint32_t col_o = tmem_base + lane_base + COL_O + h * 128;
     float m_ref = -INFINITY;                     // reference maximum (log2 domain)
     float l_sum = 0.f;
     bool ok = true;
-    for (int j = group; j < n_tiles && ok; j += 2) {
+    for (int j = 0; j < n_tiles && ok; ++j) {
       const KeyTile t = tiles[j];
-      if (!mbar_wait(&s_full[group], (j >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(&s_full[h], j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
       uint32_t s[4][32];
 #pragma unroll
@@ -234,12 +242,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       const float m_tile = m_raw * p.scale_log2;
       // Lazy rescale, decided per warp so that the TMEM accesses stay warp-uniform.  The
-      // group's previous product is complete: these scores were issued after it.
+      // previous product of this head is complete: these scores were executed after it.
       const bool grow = m_tile > m_ref + RESCALE_THRESHOLD;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, m_tile);
         const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
-        if (j >= 2) {
+        if (j > 0) {
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
@@ -279,65 +287,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[group]);
+      if (lane == 0) mbar_arrive(&p_ready[h]);
     }
     // ---------------------------------------------------------------------- epilogue
-    // Each group waits for its last product and publishes its row statistics; then the two
-    // partial outputs are merged like two key splits, group A writing head-dim columns
-    // [0, 64) and group B [64, 128).
-    const int mine = (n_tiles - group + 1) / 2;  // key tiles this group processed
-    if (ok && mine > 0) {
-      const int last = group + 2 * (mine - 1);
-      ok = mbar_wait(&pv_done[group], (last >> 1) & 1, guard, kTimeoutEpilogue);
-    }
-    stats[(group * 2 + 0) * 128 + my_row] = m_ref;
-    stats[(group * 2 + 1) * 128 + my_row] = l_sum;
-    __syncwarp();
-    if (lane == 0) mbar_arrive(merge);  // release: the stores above are ordered before it
-    if (ok) ok = mbar_wait(merge, 0, guard, kTimeoutEpilogue);
+    if (ok && n_tiles > 0) ok = mbar_wait(&o_done[h], 0, guard, kTimeoutEpilogue);
     if (ok) {
       tc_fence_after_sync();
-      const float m_a = stats[0 * 128 + my_row], l_a = stats[1 * 128 + my_row];
-      const float m_b = stats[2 * 128 + my_row], l_b = stats[3 * 128 + my_row];
-      const float m_all = fmaxf(m_a, m_b);
-      const float w_a = (m_a == -INFINITY) ? 0.f : exp2f(m_a - m_all);
-      const float w_b = (m_b == -INFINITY) ? 0.f : exp2f(m_b - m_all);
-      const float l_all = l_a * w_a + l_b * w_b;
-      const float inv = (l_all > 0.f) ? 1.f / l_all : 0.f;
-      const float f_a = w_a * inv, f_b = w_b * inv;
-      const bool has_a = n_tiles > 0, has_b = n_tiles > 1;  // an unused accumulator is not read
+      const float inv = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
       const bool row_ok = my_row < q_rows;
       __nv_bfloat16* dst =
           p.out + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
 #pragma unroll 1
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = group * 2 + cc;  // 32-column chunk of the head dimension
-        uint32_t oa[32], ob[32];
-        if (has_a) tmem_ld_32x32(tmem_base + lane_base + COL_O + c * 32, oa);
-        if (has_b) tmem_ld_32x32(tmem_base + lane_base + COL_O + 128 + c * 32, ob);
-        tmem_ld_wait();
-        float v[32];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (n_tiles > 0) {
+          tmem_ld_32x32(col_o + c * 32, o);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float acc = 0.f;
-          if (has_a) acc = __uint_as_float(oa[i]) * f_a;
-          if (has_b) acc += __uint_as_float(ob[i]) * f_b;
-          v[i] = acc;
+          for (int i = 0; i < 32; ++i) o[i] = 0;
         }
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack_bf16(v[g * 8 + 0], v[g * 8 + 1]);
-            w.y = pack_bf16(v[g * 8 + 2], v[g * 8 + 3]);
-            w.z = pack_bf16(v[g * 8 + 4], v[g * 8 + 5]);
-            w.w = pack_bf16(v[g * 8 + 6], v[g * 8 + 7]);
-            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = w;
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+            v.y = pack_bf16(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+            v.z = pack_bf16(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+            v.w = pack_bf16(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) = v;
           }
         }
       }
-      if (group == 0 && row_ok && p.lse) {
-        const float lse = (l_all > 0.f) ? (m_all + log2f(l_all)) * 0.6931471805599453f : -INFINITY;
+      if (row_ok && p.lse) {
+        const float lse = (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
         p.lse[(int64_t(batch) * p.hq + head) * p.nq + q_row + my_row] = lse;
       }
     }
@@ -395,9 +378,10 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.nq = int(a.nq);
   p.hq = a.hq;
   p.group = a.hq / a.hkv;
+  p.heads_per_cta = (p.group % 2 == 0) ? 2 : 1;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.status = a.status;
-  dim3 grid(a.num_q_tiles, a.hq, unsigned(a.batch));
+  dim3 grid(a.num_q_tiles, a.hq / p.heads_per_cta, unsigned(a.batch));
   attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(tq, tkt, tvt, tk, tv, p);
   return cudaGetLastError();
 }
