@@ -22,6 +22,7 @@ namespace {
 constexpr int TILE_BYTES = 128 * 128 * 2;
 constexpr int HALF_BYTES = TILE_BYTES / 2;
 constexpr int BWD_THREADS = 192;
+constexpr int DQ_THREADS = 320;  // 8 elementwise warps + TMA + MMA
 constexpr float LOG2E = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------- delta
@@ -64,7 +65,7 @@ struct DqParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_vt,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -100,11 +101,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     *abort_flag = 0;
     mbar_init(q_full, 1);
     mbar_init(sp_full, 1);
-    mbar_init(sp_free, 4);
+    mbar_init(sp_free, 8);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
-      mbar_init(&ds_ready[i], 4);
+      mbar_init(&ds_ready[i], 8);
       mbar_init(&dq_done[i], 1);
     }
     mbar_fence_init();
@@ -115,7 +116,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     *n_tiles_smem = n;
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -126,7 +127,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const int n_tiles = *n_tiles_smem;
   constexpr uint32_t C_S = 0, C_DP = 128, C_DQ = 256, C_DS = 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(q_full, 2 * TILE_BYTES);
       tma_load_3d(sQ, &tm_q, q_full, head * ATT_D, q_row, batch);
@@ -151,7 +152,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         while (global_timer_ns() - start < 100000ull) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0 && n_tiles > 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both K-major
       constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);  // B MN-major
@@ -198,8 +199,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
   } else {
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
-    const int my_row = warp * 32 + lane;
+    // Eight warps: warps q and q + 4 share the 32 rows of TMEM lane quarter q and take one
+    // half of the 128 key columns each, so every scheduler has two of them to interleave.
+    const int quarter = warp & 3, half = warp >> 2;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const int my_row = quarter * 32 + lane;
     const bool row_ok = my_row < q_rows;
     const int64_t stat_index = (int64_t(batch) * p.hq + head) * p.nq + q_row + my_row;
     const bool in_range = q_row + my_row < p.nq;
@@ -218,8 +222,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       int valid = t.valid;
       if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
       if (!row_ok) valid = 0;
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t s[2][32], d[2][32];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -227,11 +230,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tmem_ld_32x32(tmem_base + lane_base + C_DP + half * 64 + c * 32, d[c]);
         }
         tmem_ld_wait();
-        if (half == 1) {
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sp_free);
-        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(sp_free);
         uint32_t packed[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -261,7 +262,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_after_sync();
       __nv_bfloat16* dst = p.dq + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t o[32];
         if (n_tiles > 0) {
           tmem_ld_32x32(tmem_base + lane_base + C_DQ + c * 32, o);
@@ -286,7 +287,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -295,7 +296,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // ---------------------------------------------------------------------------- dK / dV
 // smem: K, V (resident) + Q, dO rings (2 stages) + per-item lse/delta vectors.
 // TMEM: S^T [0,128) dP^T [128,256) dV [256,384) dK [384,512); the packed bf16 P^T / dS^T
-// overwrite the first 64 columns of S^T / dP^T once those have been read into registers.
+// overwrite the first 32 columns of each 64-column half of S^T / dP^T (each half is read into
+// registers and then overwritten by the same thread).
 constexpr int DKV_MAX_ITEMS = 2048;
 constexpr int DKV_SMEM =
     6 * TILE_BYTES + DKV_MAX_ITEMS * 8 + 2 * 2 * 128 * 4 + 1024 + 512;
@@ -312,7 +314,7 @@ struct DkvParams {
   int* status;
 };
 
-__global__ void __launch_bounds__(BWD_THREADS, 1)
+__global__ void __launch_bounds__(DQ_THREADS, 1)
 attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                 const DkvParams p) {
@@ -347,9 +349,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     *abort_flag = 0;
     mbar_init(kv_full, 1);
     mbar_init(st_full, 1);
-    mbar_init(pt_ready, 4);
+    mbar_init(pt_ready, 8);
     mbar_init(grad_done, 1);
-    mbar_init(stats_bar, 128);
+    mbar_init(stats_bar, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
@@ -373,7 +375,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     *n_items_smem = n;
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -384,7 +386,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int n_items = *n_items_smem;
   constexpr uint32_t C_ST = 0, C_DPT = 128, C_DV = 256, C_DK = 384;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0 && n_items > 0) {
       mbar_expect_tx(kv_full, 2 * TILE_BYTES);
       tma_load_3d(sK, &tm_k, kv_full, kv_head * ATT_D, k_row, batch);
@@ -408,7 +410,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         while (global_timer_ns() - start < 100000ull) {}
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0 && n_items > 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);
@@ -441,12 +443,12 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // dV += P^T dO and dK += dS^T Q: A from TMEM (K-major over q), B MN-major (d contiguous)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + kk * 8,
+          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk >> 2) * 64 + (kk & 3) * 8,
                     make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn, (i | kk) != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + kk * 8,
+          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + (kk >> 2) * 64 + (kk & 3) * 8,
                     make_smem_desc(q_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn, (i | kk) != 0);
         }
         tc_commit(&qd_empty[st]);
@@ -454,8 +456,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
   } else {
-    const uint32_t lane_base = uint32_t(warp * 32) << 16;
-    const int tid = threadIdx.x;  // 0..127: key row of this thread, and the q column it stages
+    // Eight warps: warps k and k + 4 share the 32 key rows of TMEM lane quarter k and take one
+    // half of the 128 query columns each, so every scheduler has two of them to interleave.
+    const int quarter = warp & 3, half = warp >> 2;
+    const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+    const int tid = quarter * 32 + lane;  // 0..127: key row of this thread, and the q column it stages
     bool ok = n_items > 0;
     for (int i = 0; i < n_items && ok; ++i) {
       const int2 it = items[i];
@@ -465,15 +470,14 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int q = it.x + tid;
         const bool valid = tid < rows && q < p.nq;
         const int64_t idx = (int64_t(batch) * p.hq + head) * p.nq + q;
-        my_stats[tid] = valid ? p.lse[idx] * LOG2E : INFINITY;  // +inf => probability 0
-        my_stats[128 + tid] = valid ? p.delta[idx] : 0.f;
+        if (half == 0) my_stats[tid] = valid ? p.lse[idx] * LOG2E : INFINITY;  // +inf => probability 0
+        else my_stats[128 + tid] = valid ? p.delta[idx] : 0.f;
       }
       mbar_arrive(stats_bar);
       if (!mbar_wait(stats_bar, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       if (!mbar_wait(st_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int half = 0; half < 2; ++half) {
+      {
         uint32_t s[2][32], d[2][32];
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -499,8 +503,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           dd[k2] = pack_bf16(dv[0], dv[1]);
         }
         // the packed halves land in columns this thread has already read
-        tmem_st_32x32(tmem_base + lane_base + C_ST + half * 32, pp);
-        tmem_st_32x32(tmem_base + lane_base + C_DPT + half * 32, dd);
+        tmem_st_32x32(tmem_base + lane_base + C_ST + half * 64, pp);
+        tmem_st_32x32(tmem_base + lane_base + C_DPT + half * 64, dd);
       }
       tmem_st_wait();
       tc_fence_before_sync();
@@ -512,8 +516,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after_sync();
       const bool row_ok = tid < k_rows;
       const int64_t base = ((int64_t(batch) * p.nk + k_row + tid) * p.hkv + kv_head) * ATT_D;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {  // the two halves write one gradient each
+        const int which = half;
         __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + base;
         const uint32_t col0 = which == 0 ? C_DV : C_DK;
 #pragma unroll 1
@@ -538,7 +542,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -600,7 +604,7 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
     p.nq = int(a.nq); p.hq = a.hq; p.group = a.hq / a.hkv;
     p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
     dim3 grid(a.num_q_tiles, a.hq, unsigned(a.batch));
-    attn_dq_kernel<<<grid, BWD_THREADS, DQ_SMEM, stream>>>(tq, tdo, tkt, tvt, tk, tv, p);
+    attn_dq_kernel<<<grid, DQ_THREADS, DQ_SMEM, stream>>>(tq, tdo, tkt, tvt, tk, tv, p);
   }
   if (b.num_k_tiles > 0) {
     DkvParams p;
@@ -609,7 +613,7 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
     p.nq = int(a.nq); p.nk = int(a.nk); p.hq = a.hq; p.hkv = a.hkv; p.group = a.hq / a.hkv;
     p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
     dim3 grid(b.num_k_tiles, a.hkv, unsigned(a.batch));
-    attn_dkv_kernel<<<grid, BWD_THREADS, DKV_SMEM, stream>>>(tq, tdo, tk, tv, p);
+    attn_dkv_kernel<<<grid, DQ_THREADS, DKV_SMEM, stream>>>(tq, tdo, tk, tv, p);
   }
   return cudaGetLastError();
 }
