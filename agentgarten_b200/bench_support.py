@@ -81,7 +81,10 @@ def build_training_job(device: torch.device | str, *, layers: int = 36, hidden: 
                        intermediate: int = 12288, heads: int = 32, kv_heads: int = 8,
                        vocab: int = 151936, frames: int = 21, latent_hw: tuple[int, int] = (30, 52),
                        text_tokens: int = 512, text_layers: int | None = None, lr: float = 3e-5,
-                       seed: int = 0, fully_shard: bool = True) -> TrainingJob:
+                       seed: int = 0, fully_shard: bool = True,
+                       recipe: str = "bidirectional") -> TrainingJob:
+    """``recipe``: ``bidirectional`` (rectified flow on the whole clip), ``ar_diffusion_forcing``
+    or ``ar_teacher_forcing`` (block-causal, blocks of 4 latent frames after the anchor)."""
     device = torch.device(device)
     config = Cosmos3Config(hidden_size=hidden, intermediate_size=intermediate,
                            num_hidden_layers=layers, num_attention_heads=heads,
@@ -96,9 +99,18 @@ def build_training_job(device: torch.device | str, *, layers: int = 36, hidden: 
                               activation_checkpointing="selective", compile=False)
     frozen = ParallelConfig(parameter_dtype="bfloat16", fully_shard=fully_shard,
                             activation_checkpointing="none", compile=False)
-    model = DiffusionModel(net=net, conditioner=conditioner,
-                           schedule=RectifiedFlowSchedule(shift=5.0, train_distribution="waver"),
-                           text_dropout=0.1, parallel=parallel, conditioner_parallel=frozen)
+    schedule = RectifiedFlowSchedule(shift=5.0, train_distribution="waver")
+    if recipe == "bidirectional":
+        model = DiffusionModel(net=net, conditioner=conditioner, schedule=schedule,
+                               text_dropout=0.1, parallel=parallel, conditioner_parallel=frozen)
+    elif recipe in ("ar_diffusion_forcing", "ar_teacher_forcing"):
+        from agentgarten_b200.models.autoregressive import AutoregressiveModel
+
+        model = AutoregressiveModel(net=net, conditioner=conditioner, schedule=schedule,
+                                    mode=recipe.removeprefix("ar_"), block_frames=4, text_dropout=0.1,
+                                    parallel=parallel, conditioner_parallel=frozen)
+    else:
+        raise ValueError(f"unknown recipe {recipe!r}")
     model.parallelize(device)
     random_init_(model.net, seed=seed)
     random_init_(model.conditioner.text_encoder, seed=seed + 1)

@@ -34,7 +34,11 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="agentgarten_b200", choices=["agentgarten_b200", "reference"])
     parser.add_argument("--layers", type=int, default=36, help="smaller values are for debugging only")
-    parser.add_argument("--frames", type=int, default=21)
+    parser.add_argument("--frames", type=int, default=None,
+                        help="latent frames per clip (default 21; 61 for the autoregressive recipes)")
+    parser.add_argument("--recipe", default="bidirectional",
+                        choices=["bidirectional", "ar_diffusion_forcing", "ar_teacher_forcing"],
+                        help="the headline metric is the default; the others measure the other recipes")
     parser.add_argument("--no-e2e", action="store_true")
     return parser.parse_args()
 
@@ -109,7 +113,8 @@ def main() -> int:
     rank = distributed.get_rank()
     native.require()
 
-    job = build_training_job(device, layers=args.layers, frames=args.frames)
+    frames = args.frames or (21 if args.recipe == "bidirectional" else 61)
+    job = build_training_job(device, layers=args.layers, frames=frames, recipe=args.recipe)
     host_batch = synthetic_batch(job, "cpu", seed=1000 + rank, pinned=True)
     device_batch = {k: v.to(device) for k, v in host_batch.items()}
 
@@ -161,7 +166,8 @@ def main() -> int:
         tokens = job.rgb_tokens_per_clip * world * args.steps
         value = tokens / (elapsed_ms / 1e3)
         line = {
-            "metric": "train latent-tokens/s/box (bidirectional rectified flow)",
+            "metric": "train latent-tokens/s/box (bidirectional rectified flow)"
+            if args.recipe == "bidirectional" else f"train latent-tokens/s/box ({args.recipe})",
             "value": value,
             "unit": "latent RGB tokens/s",
             "n_gpus": world,
