@@ -12,16 +12,47 @@ outputs are kept, everything else is recomputed.
 
 Parity: reference ``wm/networks/cosmos3/layers.py:269-312`` (project / finish) run under
 ``wm/infra/parallel.py:164-214`` (selective activation checkpointing).
+
+Recomputation is a memory policy, not a numerical one: when the device has room, a layer
+keeps the activations of its MLP half (``h1``, its norm, gate, up: 65 KB per token) and of
+its attention half (``n1``, q/k/v before and after the head norm: 31 KB per token) and the
+backward skips the corresponding GEMMs.  The decision is taken per layer at forward time
+from the free device memory minus a reserve, so a 7 B model on one 180 GB GPU recomputes
+almost everything while the same job with the optimizer state sharded over several GPUs
+recomputes nothing.  Results are bitwise identical either way (same kernels, same inputs).
 """
 
 from __future__ import annotations
+
+import os
 
 import torch
 
 from . import native
 from .attention import build_schedule
 
-__all__ = ["eligible", "run"]
+__all__ = ["eligible", "keep_policy", "run"]
+
+# Free device memory that is never spent on kept activations (backward workspaces, optimizer
+# temporaries, allocator fragmentation), and an optional hard switch.
+_RESERVE_BYTES = int(float(os.environ.get("AGB200_ACTIVATION_RESERVE_GB", "24")) * (1 << 30))
+_KEEP_MODE = os.environ.get("AGB200_KEEP_ACTIVATIONS", "auto")  # auto | never | always
+
+
+def keep_policy(tokens: int, hidden: int, inner: int, q_width: int, kv_width: int,
+                device: torch.device) -> tuple[bool, bool]:
+    """(keep MLP half, keep attention half) for one layer about to run its forward."""
+    if _KEEP_MODE == "never":
+        return False, False
+    if _KEEP_MODE == "always":
+        return True, True
+    free, _ = torch.cuda.mem_get_info(device)
+    free += torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+    mlp_bytes = tokens * (2 * hidden + 2 * inner) * 2
+    attn_bytes = tokens * (hidden + 2 * q_width + 3 * kv_width) * 2
+    keep_mlp = free - mlp_bytes > _RESERVE_BYTES
+    keep_attn = keep_mlp and free - mlp_bytes - attn_bytes > _RESERVE_BYTES
+    return keep_mlp, keep_attn
 
 
 def _plain_linear(module) -> bool:
@@ -79,20 +110,26 @@ class _Layer(torch.autograd.Function):
         eps, heads, kv_heads = layer.input_layernorm_moe_gen.variance_epsilon, \
             layer.num_attention_heads, layer.num_key_value_heads
         x2 = x.reshape(b * n, h)
-        n1, _ = C.rms_norm_fwd(x2, w_in, eps)
-        q, _ = C.head_norm_rope_fwd(_gemm(n1, wq).view(b, n, heads, 128), nq, cos, sin, eps)
-        k, _ = C.head_norm_rope_fwd(_gemm(n1, wk).view(b, n, kv_heads, 128), nk, cos, sin, eps)
+        keep_mlp, keep_attn = keep_policy(b * n, h, wg.shape[0], wq.shape[0], wk.shape[0], x.device)
+        n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
+        q_lin = _gemm(n1, wq).view(b, n, heads, 128)
+        k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
+        q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
+        k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
         v = _gemm(n1, wv).view(b, n, kv_heads, 128)
         attn, lse = C.attn_fwd(q, k, v, text_k, text_v, text_valid, schedule.q_tiles,
                                schedule.entries, 128 ** -0.5)
         h1 = _gemm(attn.view(b * n, heads * 128), wo, residual=x2)
-        n2, _ = C.rms_norm_fwd(h1, w_post, eps)
-        act = C.silu_mul_fwd(_gemm(n2, wg), _gemm(n2, wu))
+        n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
+        gate, up = _gemm(n2, wg), _gemm(n2, wu)
+        act = C.silu_mul_fwd(gate, up)
         y = _gemm(act, wd, residual=h1)
         native.count(7)
         ctx.layer, ctx.schedule = layer, schedule
         ctx.text = (text_k, text_v, text_valid)
         ctx.params = weights  # the parameter objects themselves (their .grad buffers are used)
+        ctx.kept_mlp = (h1, n2, rstd2, gate, up) if keep_mlp else None
+        ctx.kept_attn = (n1, rstd1, q_lin, k_lin, q, k, v, rq, rk) if keep_attn else None
         ctx.save_for_backward(x, cos, sin, attn, lse, *weights)
         return y.view(b, n, h)
 
@@ -110,10 +147,14 @@ class _Layer(torch.autograd.Function):
         x2 = x.reshape(b * n, h)
         dy2 = dy.reshape(b * n, h).contiguous()
         attn2 = attn.view(b * n, heads * 128)
-        # ---- recompute the second half
-        h1 = _gemm(attn2, wo, residual=x2)
-        n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
-        gate, up = _gemm(n2, wg), _gemm(n2, wu)
+        # ---- the second half: kept, or recomputed
+        if ctx.kept_mlp is not None:
+            h1, n2, rstd2, gate, up = ctx.kept_mlp
+            ctx.kept_mlp = None
+        else:
+            h1 = _gemm(attn2, wo, residual=x2)
+            n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
+            gate, up = _gemm(n2, wg), _gemm(n2, wu)
         act = C.silu_mul_fwd(gate, up)
         # ---- MLP backward
         dwd = _wgrad(wd, dy2, act)
@@ -131,13 +172,17 @@ class _Layer(torch.autograd.Function):
         # ---- output projection backward
         dwo = _wgrad(wo, dh1, attn2)
         dattn = _gemm(dh1, wo, trans_b=False).view(b, n, heads, 128)
-        # ---- recompute the first half
-        n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
-        q_lin = _gemm(n1, wq).view(b, n, heads, 128)
-        k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
-        q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
-        k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
-        v = _gemm(n1, wv).view(b, n, kv_heads, 128)
+        # ---- the first half: kept, or recomputed
+        if ctx.kept_attn is not None:
+            n1, rstd1, q_lin, k_lin, q, k, v, rq, rk = ctx.kept_attn
+            ctx.kept_attn = None
+        else:
+            n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
+            q_lin = _gemm(n1, wq).view(b, n, heads, 128)
+            k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
+            q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
+            k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
+            v = _gemm(n1, wv).view(b, n, kv_heads, 128)
         dq, dk, dv = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
                                 schedule.q_tiles, schedule.entries, schedule.k_tiles,
                                 schedule.q_lists, 128 ** -0.5)

@@ -199,6 +199,7 @@ def main() -> int:
             "gpu_launches": launches,
             "loss": loss_value,
             "kernel_status": status,
+            "peak_memory_gb": round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 1),
         }
         if e2e_ms is not None:
             line["e2e"] = {
