@@ -142,8 +142,15 @@ struct AttnArgs {
   int hq, hkv, num_q_tiles;
   float scale;
   int* status;
+  // Forward only: with key_splits > 1 the tile list holds key_splits copies of the query
+  // tiles (each with its own key entries); copy s writes out / lse rows s * nq + q of tensors
+  // with key_splits * nq rows per sample, to be merged by attention_combine.
+  int key_splits;
 };
 cudaError_t attention_fwd(const AttnArgs& args, cudaStream_t stream);
+// out[b, q, h, :] = sum_s w_s partial[b, s*nq + q, h, :], w_s = exp(lse_s - logsumexp_s lse_s).
+cudaError_t attention_combine(const void* partial, const float* lse, void* out, int64_t batch,
+                              int64_t nq, int hq, int splits, cudaStream_t stream);
 
 // Backward of attention_fwd.  `fwd` carries the forward tensors (out and lse filled in);
 // grad_out/dq have the layout of out, dk/dv the dense layout [B, NK, Hkv, 128]; rows of

@@ -44,6 +44,8 @@ struct FwdParams {
   float* lse;             // [B, Hq, NQ] natural-log LSE
   int nq, hq, group;      // group = Hq / Hkv
   int heads_per_cta;      // 2 when group is even, else 1
+  int base_tiles;         // query tiles of one key split: tile t belongs to split t / base_tiles
+  int out_rows;           // rows of out / lse per sample (= splits * nq); split s writes rows s*nq + q
   float scale_log2;       // softmax scale * log2(e)
   int* status;
 };
@@ -80,6 +82,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int kv_head = head0 / p.group;
   const int* qt = p.q_tiles + 5 * blockIdx.x;
   const int q_row = qt[0], q_rows = qt[1], q_local = qt[4];
+  const int out_row = q_row + (int(blockIdx.x) / p.base_tiles) * p.nq;
   const WaitGuard guard{abort_flag, p.status};
 
   if (threadIdx.x == 0) {
@@ -296,7 +299,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float inv = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
       const bool row_ok = my_row < q_rows;
       __nv_bfloat16* dst =
-          p.out + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
+          p.out + ((int64_t(batch) * p.out_rows + out_row + my_row) * p.hq + head) * ATT_D;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
@@ -321,7 +324,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (row_ok && p.lse) {
         const float lse = (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : -INFINITY;
-        p.lse[(int64_t(batch) * p.hq + head) * p.nq + q_row + my_row] = lse;
+        p.lse[(int64_t(batch) * p.hq + head) * p.out_rows + out_row + my_row] = lse;
       }
     }
   }
@@ -379,6 +382,8 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.hq = a.hq;
   p.group = a.hq / a.hkv;
   p.heads_per_cta = (p.group % 2 == 0) ? 2 : 1;
+  p.base_tiles = a.key_splits > 1 ? a.num_q_tiles / a.key_splits : a.num_q_tiles;
+  p.out_rows = int(a.nq) * (a.key_splits > 1 ? a.key_splits : 1);
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.status = a.status;
   dim3 grid(a.num_q_tiles, a.hq / p.heads_per_cta, unsigned(a.batch));

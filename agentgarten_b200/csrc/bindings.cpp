@@ -192,7 +192,7 @@ Tensor rf_combine(const Tensor& a, const Tensor& b, const Tensor& sigma, int64_t
 std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v,
                                     c10::optional<Tensor> text_k, c10::optional<Tensor> text_v,
                                     c10::optional<Tensor> text_valid, const Tensor& q_tiles,
-                                    const Tensor& entries, double scale) {
+                                    const Tensor& entries, double scale, int64_t key_splits) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_bf16(v, "v");
@@ -201,9 +201,12 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
                   v.stride(3) == 1 && v.stride(2) == 128 && k.strides() == v.strides(),
               "q/k/v must be dense over (head, dim)");
   c10::cuda::CUDAGuard guard(q.device());
-  auto out = torch::empty({q.size(0), q.size(1), q.size(2), 128}, q.options());
-  auto lse = torch::empty({q.size(0), q.size(2), q.size(1)}, q.options().dtype(torch::kFloat32));
+  const int64_t splits = key_splits > 1 ? key_splits : 1;
+  TORCH_CHECK(q_tiles.size(0) % splits == 0, "the tile list must hold key_splits copies of the query tiles");
+  auto out = torch::empty({q.size(0), splits * q.size(1), q.size(2), 128}, q.options());
+  auto lse = torch::empty({q.size(0), q.size(2), splits * q.size(1)}, q.options().dtype(torch::kFloat32));
   agb::AttnArgs a{};
+  a.key_splits = int(splits);
   a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
   a.out = out.data_ptr(); a.lse = lse.data_ptr<float>();
   a.q_tiles = q_tiles.data_ptr<int>(); a.entries = entries.data_ptr<int>();
@@ -222,7 +225,12 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   a.scale = float(scale);
   a.status = status_word(q.device().index()).data_ptr<int>();
   check(agb::attention_fwd(a, stream_of(q)), "attention_fwd");
-  return {out, lse};
+  if (splits == 1) return {out, lse};
+  auto merged = torch::empty({q.size(0), q.size(1), q.size(2), 128}, q.options());
+  check(agb::attention_combine(out.data_ptr(), lse.data_ptr<float>(), merged.data_ptr(), q.size(0),
+                               q.size(1), int(q.size(2)), int(splits), stream_of(q)),
+        "attention_combine");
+  return {merged, lse};
 }
 
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(

@@ -394,6 +394,49 @@ cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, voi
   return cudaGetLastError();
 }
 
+// One warp per (sample, query row, head): 128 bf16 values = 4 per lane.
+__global__ void __launch_bounds__(NT) attn_combine_kernel(const __nv_bfloat16* __restrict__ partial,
+                                                          const float* __restrict__ lse,
+                                                          __nv_bfloat16* __restrict__ out,
+                                                          int64_t rows_total, int64_t nq, int hq,
+                                                          int splits) {
+  const int64_t item = (int64_t(blockIdx.x) * NT + threadIdx.x) >> 5;  // (b, q, h) flattened
+  if (item >= rows_total) return;
+  const int lane = threadIdx.x & 31;
+  const int h = int(item % hq);
+  const int64_t q = (item / hq) % nq, b = item / (int64_t(hq) * nq);
+  const int64_t lse_base = (b * hq + h) * (int64_t(splits) * nq) + q;
+  float top = -INFINITY;
+  for (int s = 0; s < splits; ++s) top = fmaxf(top, lse[lse_base + s * nq]);
+  float total = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int s = 0; s < splits; ++s) {
+    const float v = lse[lse_base + s * nq];
+    const float w = (v == -INFINITY) ? 0.f : __expf(v - top);
+    if (w == 0.f) continue;  // an empty split may hold anything
+    total += w;
+    const uint2 raw = *reinterpret_cast<const uint2*>(
+        partial + ((b * (int64_t(splits) * nq) + s * nq + q) * hq + h) * 128 + lane * 4);
+    acc[0] += w * bf16_lo(raw.x);
+    acc[1] += w * bf16_hi(raw.x);
+    acc[2] += w * bf16_lo(raw.y);
+    acc[3] += w * bf16_hi(raw.y);
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  *reinterpret_cast<uint2*>(out + ((b * nq + q) * hq + h) * 128 + lane * 4) =
+      make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
+}
+
+cudaError_t attention_combine(const void* partial, const float* lse, void* out, int64_t batch,
+                              int64_t nq, int hq, int splits, cudaStream_t stream) {
+  const int64_t items = batch * nq * hq;
+  if (items == 0) return cudaSuccess;
+  const int64_t threads = items * 32;
+  attn_combine_kernel<<<unsigned((threads + NT - 1) / NT), NT, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(partial), lse, static_cast<__nv_bfloat16*>(out), items, nq,
+      hq, splits);
+  return cudaGetLastError();
+}
+
 cudaError_t rf_combine(const void* a, const void* b, const float* sigma, void* out, int64_t batch,
                        int64_t channels, int frames, int hw, int sigma_frames, int mode,
                        int is_bf16, cudaStream_t stream) {

@@ -19,7 +19,7 @@ class _SegmentAttention(torch.autograd.Function):
     def forward(ctx, q, k, v, text_k, text_v, text_valid, schedule: AttentionSchedule, scale):
         C = native.ext()
         out, lse = C.attn_fwd(q, k, v, text_k, text_v, text_valid, schedule.q_tiles,
-                              schedule.entries, float(scale))
+                              schedule.entries, float(scale), 1)
         native.count()
         ctx.save_for_backward(q, k, v, out, lse,
                               *(t for t in (text_k, text_v, text_valid) if t is not None))
@@ -57,8 +57,68 @@ def planned(queries, keys, values, plan, text_keys, text_values, text_valid):
     return list(out.split(q_sizes, dim=1))
 
 
+_split_cache: dict = {}
+_SM_COUNT: dict = {}
+
+
+def _key_splits(batch: int, nq: int, nk: int, hq: int, hkv: int, device) -> int:
+    """How many contiguous key ranges to run as separate CTAs so that the launch fills the GPU.
+
+    The forward kernel has one CTA per (query tile, pair of heads, sample).  With few query
+    tiles and many keys (a streamed block against its cache, a tensor-parallel shard) that is
+    less than a wave of long-running CTAs; splitting the keys trades them for several waves of
+    short ones.  Chooses the count that minimises waves x key tiles per CTA.
+    """
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    sms = _SM_COUNT.get(index)
+    if sms is None:
+        sms = _SM_COUNT[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    heads_per_cta = 2 if (hq // hkv) % 2 == 0 else 1
+    ctas = batch * -(-nq // 128) * (hq // heads_per_cta)
+    tiles = -(-nk // 128)
+    best, best_cost = 1, -(-ctas // sms) * tiles
+    for splits in range(2, 9):
+        per = -(-tiles // splits)
+        if per < 8:  # too little work per CTA to amortise its prologue and the merge
+            break
+        cost = -(-(ctas * splits) // sms) * per + 2  # + the merge pass
+        if cost < best_cost * 0.9:
+            best, best_cost = splits, cost
+    return best
+
+
+def _split_schedule(nq: int, nk: int, splits: int, device):
+    """Tile list with ``splits`` copies of the query tiles, copy ``s`` seeing key range ``s``."""
+    key = (nq, nk, splits, str(device))
+    hit = _split_cache.get(key)
+    if hit is None:
+        tiles = -(-nk // 128)
+        per = -(-tiles // splits) * 128
+        q_tiles, entries = [], []
+        for s in range(splits):
+            first = s * per
+            entries.append((1, first, max(0, min(per, nk - first))))
+            for offset in range(0, nq, 128):
+                q_tiles.append((offset, min(128, nq - offset), s, 1, offset))
+        hit = (torch.tensor(q_tiles, dtype=torch.int32, device=device),
+               torch.tensor(entries, dtype=torch.int32, device=device))
+        if len(_split_cache) > 256:
+            _split_cache.clear()
+        _split_cache[key] = hit
+    return hit
+
+
 def dense(q, k, v, causal: bool = False):
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if not causal and not needs_grad:
+        splits = _key_splits(q.shape[0], q.shape[1], k.shape[1], q.shape[2], k.shape[2], q.device)
+        if splits > 1:
+            q_tiles, entries = _split_schedule(q.shape[1], k.shape[1], splits, q.device)
+            native.count(2)
+            out, _ = native.ext().attn_fwd(q, k, v, None, None, None, q_tiles, entries,
+                                           q.shape[-1] ** -0.5, splits)
+            return out
     schedule = build_schedule([q.shape[1]], [k.shape[1]], [[0]], 0, q.device, causal=causal)
     return _SegmentAttention.apply(q, k, v, None, None, None, schedule, q.shape[-1] ** -0.5)
 

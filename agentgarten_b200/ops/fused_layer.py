@@ -118,7 +118,7 @@ class _Layer(torch.autograd.Function):
         k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
         v = _gemm(n1, wv).view(b, n, kv_heads, 128)
         attn, lse = C.attn_fwd(q, k, v, text_k, text_v, text_valid, schedule.q_tiles,
-                               schedule.entries, 128 ** -0.5)
+                               schedule.entries, 128 ** -0.5, 1)
         h1 = _gemm(attn.view(b * n, heads * 128), wo, residual=x2)
         n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
         gate, up = _gemm(n2, wg), _gemm(n2, wu)

@@ -318,3 +318,19 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status():
     assert int(status.item()) == 0
     assert _rel(out, a.float() @ w.float().t()) < 1e-2
     assert seen.tolist() == [128, 128]
+
+
+@pytest.mark.parametrize("nq,nk,hq,hkv", [(300, 5000, 4, 1), (128, 12000, 8, 2), (3120, 20000, 4, 1)])
+def test_split_key_attention_matches_reference(nq, nk, hq, hkv):
+    from agentgarten_b200.ops import attention_native
+
+    torch.manual_seed(nq)
+    q = torch.randn(1, nq, hq, 128, device=DEV).bfloat16()
+    k = torch.randn(1, nk, hkv, 128, device=DEV).bfloat16()
+    v = torch.randn(1, nk, hkv, 128, device=DEV).bfloat16()
+    assert attention_native._key_splits(1, nq, nk, hq, hkv, q.device) > 1
+    with torch.no_grad():
+        out = attention_native.dense(q, k, v)
+    want = reference.attention(q.float(), k.float(), v.float(), None)
+    assert _rel(out, want) < 1e-2, _rel(out, want)
+    _status_ok()
