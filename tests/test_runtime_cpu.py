@@ -1,0 +1,190 @@
+"""Unit tests of runtime pieces on CPU: RNG capture/restore, loader resume, LR lambdas,
+gradient clipping, LoRA injection, geometry preprocessing, media helpers."""
+
+import math
+import pickle
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from agentgarten_b200.data.loader import StatefulDataLoader
+from agentgarten_b200.data.video import SyntheticLatentDataset, SyntheticVideoDataset
+from agentgarten_b200.infra import rng_state
+from agentgarten_b200.infra.callbacks.grad_clip import clip_grad_norm_, clip_grad_norm_groups_
+from agentgarten_b200.infra.callbacks.media import media_artifact_filename, video_batch_to_cpu_uint8
+from agentgarten_b200.infra.optim import CosineDecay, LinearWarmup, LinearWarmupCosineDecay
+from agentgarten_b200.networks.cosmos3 import geometry
+from agentgarten_b200.networks.lora import LORA_PARAMETER_PATTERN, LoRALinear, initialize_lora_parameters, inject_lora
+
+
+# ----------------------------------------------------------------------------- RNG
+def _draw():
+    return random.random(), float(np.random.rand()), float(torch.rand(1))
+
+
+def test_rng_capture_restore_and_isolation():
+    random.seed(1); np.random.seed(2); torch.manual_seed(3)
+    state = rng_state.capture_distributed_rng_state()
+    rng_state.validate_distributed_rng_state(state)
+    first = _draw()
+    with rng_state.isolated_rng():
+        torch.manual_seed(99); random.seed(99); np.random.seed(99)
+        _draw()
+    second = _draw()  # the block above left no trace
+    rng_state.restore_distributed_rng_state(state)
+    assert _draw() == first and _draw() == second
+
+
+def test_rng_blob_refuses_foreign_pickles():
+    random.seed(5)
+    state = rng_state.capture_distributed_rng_state()
+    key = next(k for k in state["ranks"])
+    evil = pickle.dumps(print)  # a global that is not a NumPy reconstructor
+    tampered = {**state, "ranks": {key: {**state["ranks"][key],
+                                         "python_blob": torch.tensor(list(evil), dtype=torch.uint8),
+                                         "python_length": len(evil)}}}
+    with pytest.raises(Exception):
+        rng_state.validate_distributed_rng_state(tampered)
+    wrong_world = {**state, "world_size": 7}
+    with pytest.raises(RuntimeError):
+        rng_state.validate_distributed_rng_state(wrong_world)
+
+
+# -------------------------------------------------------------------------- loader
+def _ids(batches):
+    return [b["sample_id"].tolist() for b in batches]
+
+
+def test_loader_resumes_mid_epoch_and_across_epochs():
+    data = SyntheticLatentDataset(length=10, latent_frames=1, latent_height=2, latent_width=2,
+                                  channels=4, text_tokens=3, vocab_size=50)
+    make = lambda: StatefulDataLoader(data, batch_size=2, shuffle=True, seed=11, pin_memory=False)  # noqa: E731
+    straight = make()
+    epoch0 = _ids(list(straight))
+    epoch1 = _ids(list(straight))
+    assert len(epoch0) == 5 and sorted(sum(epoch0, [])) == list(range(10)) and epoch0 != epoch1
+    assert straight.state_dict() == {"epoch": 2, "batch_offset": 0}
+
+    stopped = make()
+    iterator = iter(stopped)
+    head = _ids([next(iterator), next(iterator)])
+    cursor = stopped.state_dict()
+    assert cursor == {"epoch": 0, "batch_offset": 2}
+    resumed = make()
+    resumed.load_state_dict(cursor)
+    assert head + _ids(list(resumed)) == epoch0
+    assert _ids(list(resumed)) == epoch1
+    # an older iterator may not advance the cursor once a newer one exists
+    stale = iter(stopped)
+    iter(stopped)
+    with pytest.raises(RuntimeError):
+        next(stale)
+    with pytest.raises(ValueError):
+        resumed.load_state_dict({"epoch": -1, "batch_offset": 0})
+    assert make().resume_signature() == straight.resume_signature()
+
+
+def test_synthetic_video_dataset_is_seeded():
+    data = SyntheticVideoDataset(length=3, num_frames=5, height=8, width=8)
+    a, b = data[1], data[1]
+    assert all(torch.equal(a[k], b[k]) for k in a if torch.is_tensor(a[k]))
+    assert not torch.equal(data[0]["video"], data[1]["video"])
+
+
+# ------------------------------------------------------------------------------ LR
+def test_lr_lambdas():
+    warm = LinearWarmup(4, start_factor=0.2)
+    assert warm(0) == pytest.approx(0.2) and warm(2) == pytest.approx(0.6) and warm(4) == 1.0 and warm(99) == 1.0
+    cosine = CosineDecay(10, final_factor=0.1)
+    assert cosine(0) == pytest.approx(1.0) and cosine(10) == pytest.approx(0.1) and cosine(50) == pytest.approx(0.1)
+    assert cosine(5) == pytest.approx(0.1 + 0.9 * 0.5)
+    both = LinearWarmupCosineDecay(2, 12, start_factor=0.0, final_factor=0.0)
+    values = [both(s) for s in range(13)]
+    assert values[0] == 0.0 and values[2] == pytest.approx(1.0) and values[12] == pytest.approx(0.0, abs=1e-9)
+    assert all(a >= b - 1e-12 for a, b in zip(values[2:], values[3:]))
+    pickle.loads(pickle.dumps(both))  # schedulers are checkpointed by value
+
+
+# ------------------------------------------------------------------------ clipping
+def test_group_clip_matches_torch_and_observe_only():
+    torch.manual_seed(0)
+    a, b = torch.nn.Parameter(torch.randn(5, 3)), torch.nn.Parameter(torch.randn(7))
+    a.grad, b.grad = torch.randn(5, 3), torch.randn(7)
+    want = math.sqrt(float(a.grad.square().sum() + b.grad.square().sum()))
+    before = a.grad.clone()
+    total, roles = clip_grad_norm_groups_({"student": [a], "critic": [b, a]}, float("inf"))
+    assert float(total) == pytest.approx(want, rel=1e-6) and set(roles) == {"student", "critic"}
+    assert torch.equal(a.grad, before)  # inf: observe only; `a` counted once
+    total = clip_grad_norm_([a, b], 0.5)
+    after = math.sqrt(float(a.grad.square().sum() + b.grad.square().sum()))
+    assert float(total) == pytest.approx(want, rel=1e-6) and after == pytest.approx(0.5, rel=1e-4)
+    with pytest.raises(ValueError):
+        clip_grad_norm_([a], -1.0)
+
+
+# ---------------------------------------------------------------------------- LoRA
+def test_lora_injection_targets_and_identity_at_init():
+    import re
+
+    torch.manual_seed(0)
+    net = torch.nn.ModuleDict({"layers": torch.nn.ModuleList([
+        torch.nn.ModuleDict({"q": torch.nn.Linear(8, 8, bias=False), "mlp": torch.nn.Linear(8, 16)})
+        for _ in range(2)])})
+    x = torch.randn(3, 8)
+    plain = net["layers"][0]["q"](x)
+    names = inject_lora(net, {"rank": 2, "alpha": 2.0, "dropout": 0.0,
+                              "module_patterns": [r"layers\.\d+\.q"]})
+    assert sorted(names) == ["layers.0.q", "layers.1.q"]
+    assert isinstance(net["layers"][0]["q"], LoRALinear) and not isinstance(net["layers"][0]["mlp"], LoRALinear)
+    initialize_lora_parameters(net, seed=0)
+    assert torch.allclose(net["layers"][0]["q"](x), plain)  # B starts at zero
+    adapters = [n for n, _ in net.named_parameters() if re.fullmatch(LORA_PARAMETER_PATTERN, n)]
+    assert len(adapters) == 4
+    assert inject_lora(net, {"rank": 2, "alpha": 2.0, "dropout": 0.0,
+                             "module_patterns": [r"nothing\.matches"]}) == ()
+    with pytest.raises(ValueError):
+        inject_lora(net, {"rank": 0, "module_patterns": [r".*"]})
+
+
+# ------------------------------------------------------------------------ geometry
+def test_depth_colours_and_normals():
+    depth = torch.tensor([0.0, float("nan"), 0.5, 5.0, 1e6]).view(1, 1, 1, 1, 5)
+    rgb = geometry.colorize_depth(depth, torch.tensor([1.0]))
+    assert rgb.shape == (1, 3, 1, 1, 5) and rgb.min() >= 0 and rgb.max() <= 1
+    assert torch.equal(rgb[0, :, 0, 0, 0], torch.zeros(3)) and torch.equal(rgb[0, :, 0, 0, 1], torch.zeros(3))
+    assert torch.allclose(rgb[0, :, 0, 0, 4], torch.ones(3), atol=1e-3)  # far end of the walk is white
+    near, far = rgb[0, :, 0, 0, 2], rgb[0, :, 0, 0, 3]
+    assert near.sum() < far.sum()
+    raw = torch.tensor([[255, 127, 127], [127, 127, 127]], dtype=torch.uint8).t().reshape(1, 3, 1, 1, 2)
+    unit = geometry.prepare_normal(raw)
+    assert torch.allclose(unit[0, :, 0, 0, 0].norm(), torch.tensor(1.0), atol=1e-5)
+    assert float(unit[0, :, 0, 0, 1].abs().max()) <= 1.0
+    floats = torch.randn(1, 3, 1, 2, 2)
+    assert torch.equal(geometry.prepare_normal(floats), floats)
+    with pytest.raises(TypeError):
+        geometry.prepare_normal(torch.zeros(1, 3, 1, 2, 2, dtype=torch.int32))
+    low = geometry.downsample_geometry({"depth": torch.arange(16.0).view(1, 1, 1, 4, 4)}, factor=2)["depth"]
+    assert low.shape == (1, 1, 1, 2, 2) and float(low[0, 0, 0, 0, 0]) == pytest.approx(2.5)
+
+
+def test_geometry_config_validation_and_stretch():
+    with pytest.raises(ValueError):
+        geometry.GeometryAugmentationConfig(modality_dropout_probability=1.5)
+    videos = {"depth": torch.rand(1, 3, 2, 30, 52), "normal": torch.rand(1, 3, 2, 30, 52)}
+    out = geometry.stretch_geometry(videos, training=False, divisor=32)
+    assert all(v.shape[-2] % 32 == 0 and v.shape[-1] % 32 == 0 for v in out.values())
+
+
+# --------------------------------------------------------------------------- media
+def test_media_names_and_uint8_conversion():
+    name = media_artifact_filename(artifact_name="comparison grid", iteration=12, rank=3,
+                                   sample_batch_index=1, extension="mp4", batch_index=0)
+    assert name.startswith("Iter000000012_Rank0003_") and name.endswith("_01_00.mp4") and " " not in name
+    wide = media_artifact_filename(artifact_name="x", iteration=1, rank=0, sample_batch_index=120, extension="jpg")
+    assert "@120" in wide
+    video = torch.stack([torch.full((3, 2, 4, 4), -1.0), torch.full((3, 2, 4, 4), 1.0)])
+    frames = video_batch_to_cpu_uint8(video, layout="BCTHW", float_range="minus_one_one")
+    assert len(frames) == 2 and frames[0].dtype == torch.uint8
+    assert int(frames[0].max()) == 0 and int(frames[1].min()) == 255
