@@ -138,10 +138,25 @@ class ChannelRMSNorm(nn.Module):
         self.gain = float(dim) ** 0.5
         self.gamma = nn.Parameter(torch.ones(dim, *((1, 1) if images else (1, 1, 1))))
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, silu: bool = False) -> torch.Tensor:
+        """``silu=True`` applies the activation that follows every norm in the same pass."""
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[1] <= 1024:
+            from agentgarten_b200.ops import native
+
+            if native.available():
+                # channels-last activations are [pixels, C] rows: one fused kernel, one pass
+                order = (0, *range(2, x.ndim), 1)
+                rows = x.permute(order)
+                if not rows.is_contiguous():
+                    rows = rows.contiguous()
+                native.count()
+                out = native.ext().channel_norm(rows, self.gamma.detach().float().reshape(-1).contiguous(), silu)
+                inverse = (0, x.ndim - 1, *range(1, x.ndim - 1))
+                return out.permute(inverse)
         wide = x.float()
         norm = wide.norm(dim=1, keepdim=True).clamp_min(1e-12)
-        return (wide * (self.gain / norm) * self.gamma.float()).to(x.dtype)
+        out = wide * (self.gain / norm) * self.gamma.float()
+        return (F.silu(out) if silu else out).to(x.dtype)
 
 
 class ResidualBlock(nn.Module):
@@ -158,8 +173,8 @@ class ResidualBlock(nn.Module):
 
     def forward(self, x: torch.Tensor, state: CausalState | None = None) -> torch.Tensor:
         r = self.residual
-        h = r[2](F.silu(r[0](x)), state)
-        h = r[6](r[5](F.silu(r[3](h))), state)
+        h = r[2](r[0](x, silu=True), state)
+        h = r[6](r[5](r[3](h, silu=True)), state)
         return h + self.shortcut(x)
 
 
@@ -343,7 +358,7 @@ class Encoder(nn.Module):
             x = stage(x, state)
         for layer in self.middle:
             x = layer(x, state)
-        return self.head[2](F.silu(self.head[0](x)), state)
+        return self.head[2](self.head[0](x, silu=True), state)
 
 
 class Decoder(nn.Module):
@@ -366,7 +381,7 @@ class Decoder(nn.Module):
             x = layer(x, state)
         for stage in self.upsamples:
             x = stage(x, state)
-        return self.head[2](F.silu(self.head[0](x)), state)
+        return self.head[2](self.head[0](x, silu=True), state)
 
 
 class Wan22VAE(nn.Module):

@@ -190,6 +190,12 @@ cudaError_t relocate_rows(const void* src, void* dst, const float* cosv, const f
                           int64_t kept_tokens, int sink_tokens, int shift_tokens, int heads,
                           cudaStream_t stream);
 
+// ------------------------------------------------------------------------- video VAE
+// Channel RMS norm of channels-last bf16 activations (x, out: [pixels, channels], gamma fp32
+// [channels]): out = x / max(||x||, 1e-12) * sqrt(channels) * gamma, then SiLU when silu != 0.
+cudaError_t channel_norm(const void* x, const float* gamma, void* out, int64_t pixels, int channels,
+                         int silu, cudaStream_t stream);
+
 // ----------------------------------------------------------- sharded optimizer (ZeRO)
 // Base pointers of the same flat buffer on every rank of the node (index = rank).
 struct ZeroPeers {

@@ -272,6 +272,19 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   return {dq, dk, dv};
 }
 
+// Channel RMS norm (+ SiLU) of a channels-last activation; x is [..., C] with C contiguous.
+Tensor channel_norm(const Tensor& x, const Tensor& gamma, bool silu) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && gamma.scalar_type() == torch::kFloat32 && gamma.is_contiguous() &&
+                  gamma.numel() == x.size(-1), "channel_norm: x [..., C] contiguous, gamma fp32 [C]");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty_like(x);
+  const int64_t channels = x.size(-1);
+  check(agb::channel_norm(x.data_ptr(), gamma.data_ptr<float>(), out.data_ptr(), x.numel() / channels,
+                          int(channels), silu ? 1 : 0, stream_of(x)), "channel_norm");
+  return out;
+}
+
 // (O, tangent of O, LSE) of dense attention under forward-mode differentiation.
 std::tuple<Tensor, Tensor, Tensor> attn_jvp(const Tensor& q, const Tensor& k, const Tensor& v,
                                             const Tensor& tq, const Tensor& tk, const Tensor& tv,
@@ -494,6 +507,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relocate", &relocate);
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);
+  m.def("channel_norm", &channel_norm);
   m.def("attn_jvp", &attn_jvp);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_reduce_norm", &tp_reduce_norm);

@@ -394,6 +394,71 @@ cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, voi
   return cudaGetLastError();
 }
 
+// ------------------------------------------------- channel RMS norm (+ SiLU), channels last
+// y = x / max(||x||_2, 1e-12) * sqrt(C) * gamma over the C contiguous channels of a pixel,
+// optionally followed by SiLU: the norm / activation pair in front of every convolution of
+// the video VAE, in one pass (one warp per pixel, C <= 1024, a multiple of 8).
+template <bool SILU>
+__global__ void __launch_bounds__(NT) channel_norm_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const float* __restrict__ gamma,
+                                                          __nv_bfloat16* __restrict__ out,
+                                                          int64_t pixels, int channels) {
+  const int lane = threadIdx.x & 31;
+  const int chunks = channels >> 3;
+  const float gain = sqrtf(float(channels));
+  for (int64_t pixel = (int64_t(blockIdx.x) * NT + threadIdx.x) >> 5; pixel < pixels;
+       pixel += (int64_t(gridDim.x) * NT) >> 5) {
+    const __nv_bfloat16* row = x + pixel * channels;
+    float v[4][8];
+    float sumsq = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = k * 32 + lane;
+      if (c < chunks) {
+        unpack8(*reinterpret_cast<const uint4*>(row + c * 8), v[k]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sumsq += v[k][i] * v[k][i];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+    const float scale = gain / fmaxf(sqrtf(sumsq), 1e-12f);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int c = k * 32 + lane;
+      if (c < chunks) {
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + c * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(gamma + c * 8 + 4);
+        const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float n = v[k][i] * scale * g[i];
+          y[i] = SILU ? n / (1.f + __expf(-n)) : n;
+        }
+        *reinterpret_cast<uint4*>(out + pixel * channels + c * 8) = pack8(y);
+      }
+    }
+  }
+}
+
+cudaError_t channel_norm(const void* x, const float* gamma, void* out, int64_t pixels, int channels,
+                         int silu, cudaStream_t stream) {
+  if (pixels == 0) return cudaSuccess;
+  if (channels % 8 || channels > 1024 || channels <= 0) {
+    set_error_detail("channel_norm: channels must be a multiple of 8 up to 1024");
+    return cudaErrorInvalidValue;
+  }
+  const int64_t warps_per_cta = NT / 32;
+  const int64_t ctas = (pixels + warps_per_cta - 1) / warps_per_cta;
+  const unsigned grid = unsigned(ctas < 148 * 32 ? ctas : 148 * 32);
+  auto xs = static_cast<const __nv_bfloat16*>(x);
+  auto os = static_cast<__nv_bfloat16*>(out);
+  if (silu) channel_norm_kernel<true><<<grid, NT, 0, stream>>>(xs, gamma, os, pixels, channels);
+  else channel_norm_kernel<false><<<grid, NT, 0, stream>>>(xs, gamma, os, pixels, channels);
+  return cudaGetLastError();
+}
+
 // One warp per (sample, query row, head): 128 bf16 values = 4 per lane.
 __global__ void __launch_bounds__(NT) attn_combine_kernel(const __nv_bfloat16* __restrict__ partial,
                                                           const float* __restrict__ lse,

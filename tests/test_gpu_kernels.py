@@ -334,3 +334,36 @@ def test_split_key_attention_matches_reference(nq, nk, hq, hkv):
     want = reference.attention(q.float(), k.float(), v.float(), None)
     assert _rel(out, want) < 1e-2, _rel(out, want)
     _status_ok()
+
+
+@pytest.mark.parametrize("channels,silu", [(160, True), (1024, False), (8, True), (640, True)])
+def test_channel_norm_kernel(channels, silu):
+    torch.manual_seed(channels)
+    x = torch.randn(2, 3, 5, 7, channels, device=DEV).bfloat16()
+    gamma = torch.rand(channels, device=DEV) + 0.5
+    out = native.ext().channel_norm(x, gamma, silu)
+    wide = x.float()
+    want = wide / wide.norm(dim=-1, keepdim=True).clamp_min(1e-12) * channels ** 0.5 * gamma
+    if silu:
+        want = torch.nn.functional.silu(want)
+    assert _rel(out, want) < 5e-3, _rel(out, want)
+    _status_ok()
+
+
+def test_vae_on_gpu_matches_cpu_fp32():
+    from agentgarten_b200.codecs.wan22 import random_vae
+
+    arch = dict(dim=16, dec_dim=16, z_dim=8)
+    cpu = random_vae(seed=3, **arch)
+    gpu = random_vae(seed=3, **arch).to(DEV, torch.bfloat16).to(memory_format=torch.channels_last_3d)
+    scale = (0.0, 1.0)
+    video = torch.rand(1, 3, 9, 32, 48) * 2 - 1
+    before = native.launches()
+    with torch.no_grad():
+        want = cpu.encode(video, scale, temporal_window=4)
+        got = gpu.encode(video.to(DEV, torch.bfloat16), scale, temporal_window=4)
+        assert native.launches() > before  # the fused norm kernel ran
+        assert _rel(got, want.to(DEV)) < 5e-2, _rel(got, want.to(DEV))
+        pixels = cpu.decode(want, scale, frames_per_pass=2)
+        got_pixels = gpu.decode(want.to(DEV, torch.bfloat16), scale, frames_per_pass=2)
+        assert got_pixels.shape == pixels.shape and _rel(got_pixels, pixels.to(DEV)) < 8e-2
