@@ -32,7 +32,7 @@ from agentgarten_b200.utils import log
 from agentgarten_b200.utils.misc import prefetch
 
 __all__ = ["CausalState", "Wan22VAE", "Wan22VAECodec", "Wan22Stream", "LATENT_MEAN", "LATENT_STD",
-           "pixel_fold", "pixel_unfold"]
+           "pixel_fold", "pixel_unfold", "to_channels_last"]
 
 # Per-channel statistics of the released 48-channel latent space.
 LATENT_MEAN = (
@@ -458,6 +458,17 @@ class Wan22VAE(nn.Module):
         return torch.cat(out, dim=2) if len(out) > 1 else out[0]
 
 
+@torch.no_grad()
+def to_channels_last(module: nn.Module) -> nn.Module:
+    """Convolution weights in the layout of the tensor-core kernels: 5-D -> NDHWC, 4-D -> NHWC."""
+    for parameter in module.parameters():
+        if parameter.ndim == 5:
+            parameter.data = parameter.data.contiguous(memory_format=torch.channels_last_3d)
+        elif parameter.ndim == 4 and parameter.shape[-1] * parameter.shape[-2] > 1:
+            parameter.data = parameter.data.contiguous(memory_format=torch.channels_last)
+    return module
+
+
 def _per_channel(value, channels: int):
     if isinstance(value, torch.Tensor):
         return value.view(1, channels, 1, 1, 1)
@@ -537,7 +548,7 @@ class Wan22VAECodec:
                 vae = build_vae(self.pretrained_path, device=target, **self.architecture)
             vae = vae.eval().requires_grad_(False).to(dtype=self.dtype)
             if target.type == "cuda":
-                vae = vae.to(memory_format=torch.channels_last_3d)
+                vae = to_channels_last(vae)
             self._vae = vae
         return self._vae
 

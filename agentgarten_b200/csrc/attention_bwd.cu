@@ -294,13 +294,26 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 }
 
 // ---------------------------------------------------------------------------- dK / dV
-// smem: K, V (resident) + Q, dO rings (2 stages) + per-item lse/delta vectors.
-// TMEM: S^T [0,128) dP^T [128,256) dV [256,384) dK [384,512); the packed bf16 P^T / dS^T
-// overwrite the first 32 columns of each 64-column half of S^T / dP^T (each half is read into
-// registers and then overwritten by the same thread).
-constexpr int DKV_MAX_ITEMS = 2048;
-constexpr int DKV_SMEM =
-    6 * TILE_BYTES + DKV_MAX_ITEMS * 8 + 2 * 2 * 128 * 4 + 1024 + 512;
+// One CTA per (key tile of 128 rows, KV head, sample).  It walks every (query head of the
+// group, block of 64 query rows) that can see the tile:
+//   S^T  = K Q^T, dP^T = V dO^T                 (128 keys x 64 queries each, operands in smem)
+//   P^T  = exp2(S^T scale - lse), dS^T = P^T (dP^T - delta) scale   (softmax warps)
+//   dV  += P^T dO,  dK += dS^T Q                (P^T / dS^T read from TMEM)
+// Query blocks of 64 rows leave room in TMEM for two S^T / dP^T buffers, so the scores of
+// the next block are computed while the warps work on the current one; tcgen05.mma
+// operations of one thread execute in issue order, which makes refilling a buffer behind the
+// products that read its P^T / dS^T safe without a barrier round trip.
+// smem: K, V (resident) + Q, dO rings (3 stages of 64 rows) + item list + lse/delta vectors.
+// TMEM: S^T[2] [0,128) dP^T[2] [128,256) dV [256,384) dK [384,512).  Eight warps: warps k and
+// k + 4 share the 32 key rows of lane quarter k and take 32 of the 64 query columns each; the
+// packed bf16 results overwrite the first 16 columns of the 32 they were computed from.
+constexpr int DKV_BQ = 64;                      // query rows per item
+constexpr int DKV_STAGES = 3;
+constexpr int QD_BYTES = DKV_BQ * 128 * 2;      // 16 KiB: 64 rows x 128 d, two atoms of 8 KiB
+constexpr int QD_HALF = QD_BYTES / 2;
+constexpr int DKV_MAX_ITEMS = 4096;
+constexpr int DKV_SMEM = 2 * TILE_BYTES + 2 * DKV_STAGES * QD_BYTES + DKV_MAX_ITEMS * 8 +
+                         2 * 2 * DKV_BQ * 4 + 1024 + 512;
 
 struct DkvParams {
   const int* k_tiles;  // [tiles, 5]: k_row, rows, first_reader, readers, causal (unused)
@@ -323,19 +336,19 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                              ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = smem + TILE_BYTES;
-  uint8_t* sQ = smem + 2 * TILE_BYTES;   // [2 stages]
-  uint8_t* sdO = smem + 4 * TILE_BYTES;  // [2 stages]
-  int2* items = reinterpret_cast<int2*>(smem + 6 * TILE_BYTES);  // (q_row, rows | head << 8)
-  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);  // [2][2][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * 128);
+  uint8_t* sQ = smem + 2 * TILE_BYTES;                 // [DKV_STAGES]
+  uint8_t* sdO = sQ + DKV_STAGES * QD_BYTES;           // [DKV_STAGES]
+  int2* items = reinterpret_cast<int2*>(sdO + DKV_STAGES * QD_BYTES);  // (q_row, rows | head << 8)
+  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);      // [2][lse, delta][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * DKV_BQ);
   uint64_t* kv_full = bars;
-  uint64_t* qd_full = bars + 1;    // [2]
-  uint64_t* qd_empty = bars + 3;   // [2]
-  uint64_t* st_full = bars + 5;    // S^T, dP^T ready
-  uint64_t* pt_ready = bars + 6;   // P^T, dS^T written (count 4)
-  uint64_t* grad_done = bars + 7;  // dV/dK products of an item finished
-  uint64_t* stats_bar = bars + 8;  // lse/delta of an item staged by all 128 threads
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* qd_full = bars + 1;     // [3]
+  uint64_t* qd_empty = bars + 4;    // [3]
+  uint64_t* st_full = bars + 7;     // [2] S^T, dP^T of a buffer complete
+  uint64_t* pt_ready = bars + 9;    // [2] P^T, dS^T of a buffer written (count 8)
+  uint64_t* grad_done = bars + 11;  // all gradient products finished
+  uint64_t* stats_bar = bars + 12;  // lse/delta of an item staged (count 256)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_items_smem = abort_flag + 1;
 
@@ -348,11 +361,13 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(kv_full, 1);
-    mbar_init(st_full, 1);
-    mbar_init(pt_ready, 8);
     mbar_init(grad_done, 1);
     mbar_init(stats_bar, 256);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&st_full[i], 1);
+      mbar_init(&pt_ready[i], 8);
+    }
+    for (int i = 0; i < DKV_STAGES; ++i) {
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
     }
@@ -363,9 +378,9 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int head = kv_head * p.group + g;
       for (int r = kt[2]; r < kt[2] + kt[3] && !overflow; ++r) {
         const int q0 = p.q_lists[2 * r], len = p.q_lists[2 * r + 1];
-        for (int off = 0; off < len; off += ATT_BM) {
+        for (int off = 0; off < len; off += DKV_BQ) {
           if (n >= DKV_MAX_ITEMS) { overflow = true; break; }
-          items[n++] = make_int2(q0 + off, min(ATT_BM, len - off) | (head << 8));
+          items[n++] = make_int2(q0 + off, min(DKV_BQ, len - off) | (head << 8));
         }
       }
     }
@@ -395,15 +410,15 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tma_load_3d(sV + HALF_BYTES, &tm_v, kv_full, kv_head * ATT_D + 64, k_row, batch);
       bool ok = true;
       for (int i = 0; i < n_items && ok; ++i) {
-        const int st = i & 1;
+        const int st = i % DKV_STAGES;
         const int2 it = items[i];
         const int head = it.y >> 8;
-        if (!mbar_wait(&qd_empty[st], ((i >> 1) & 1) ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
-        mbar_expect_tx(&qd_full[st], 2 * TILE_BYTES);
-        tma_load_3d(sQ + st * TILE_BYTES, &tm_q, &qd_full[st], head * ATT_D, it.x, batch);
-        tma_load_3d(sQ + st * TILE_BYTES + HALF_BYTES, &tm_q, &qd_full[st], head * ATT_D + 64, it.x, batch);
-        tma_load_3d(sdO + st * TILE_BYTES, &tm_do, &qd_full[st], head * ATT_D, it.x, batch);
-        tma_load_3d(sdO + st * TILE_BYTES + HALF_BYTES, &tm_do, &qd_full[st], head * ATT_D + 64, it.x, batch);
+        if (!mbar_wait(&qd_empty[st], ((i / DKV_STAGES) & 1) ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&qd_full[st], 2 * QD_BYTES);
+        tma_load_3d(sQ + st * QD_BYTES, &tm_q, &qd_full[st], head * ATT_D, it.x, batch);
+        tma_load_3d(sQ + st * QD_BYTES + QD_HALF, &tm_q, &qd_full[st], head * ATT_D + 64, it.x, batch);
+        tma_load_3d(sdO + st * QD_BYTES, &tm_do, &qd_full[st], head * ATT_D, it.x, batch);
+        tma_load_3d(sdO + st * QD_BYTES + QD_HALF, &tm_do, &qd_full[st], head * ATT_D + 64, it.x, batch);
       }
       if (!ok || *abort_flag) {
         const uint64_t start = global_timer_ns();
@@ -412,110 +427,113 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp == 9) {
     if (lane == 0 && n_items > 0) {
-      constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);
-      constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, DKV_BQ, 0, 0);   // 128 keys x 64 queries
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 1);      // 128 keys x 128 d
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
+      auto scores = [&](int i) -> bool {
+        const int st = i % DKV_STAGES, buf = i & 1;
+        if (!mbar_wait(&qd_full[st], (i / DKV_STAGES) & 1, guard, kTimeoutMma)) return false;
+        tc_fence_after_sync();
+        const uint32_t q_addr = smem_u32(sQ + st * QD_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + st * QD_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t ko = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          const uint32_t qo = (kk >> 2) * QD_HALF + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_ST + buf * DKV_BQ, make_smem_desc(k_addr + ko, 16, 1024),
+                    make_smem_desc(q_addr + qo, 16, 1024), idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t ko = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          const uint32_t qo = (kk >> 2) * QD_HALF + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_DPT + buf * DKV_BQ, make_smem_desc(v_addr + ko, 16, 1024),
+                    make_smem_desc(do_addr + qo, 16, 1024), idesc_s, kk != 0);
+        }
+        tc_commit(&st_full[buf]);
+        return true;
+      };
       bool ok = mbar_wait(kv_full, 0, guard, kTimeoutMma);
+      if (ok) ok = scores(0);
       for (int i = 0; i < n_items && ok; ++i) {
-        const int st = i & 1;
-        if (!mbar_wait(&qd_full[st], (i >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        const int st = i % DKV_STAGES, buf = i & 1;
+        // The other buffer last held P^T / dS^T of item i - 1, whose products were issued in
+        // the previous iteration: refilling it now is ordered behind them.
+        if (i + 1 < n_items && !scores(i + 1)) { ok = false; break; }
+        if (!mbar_wait(&pt_ready[buf], (i >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES);
-        const uint32_t do_addr = smem_u32(sdO + st * TILE_BYTES);
-        // S^T = K Q^T and dP^T = V dO^T (all operands K-major over d).  MMAs of one thread
-        // execute in issue order, so these overwrite the P^T/dS^T columns only after the
-        // gradient products of the previous item have consumed them.
+        const uint32_t q_addr = smem_u32(sQ + st * QD_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + st * QD_BYTES);
+        // 16 queries per step; the packed columns of query half h start at column 32 h.
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_ST, make_smem_desc(k_addr + off, 16, 1024),
-                    make_smem_desc(q_addr + off, 16, 1024), idesc_kk, kk != 0);
+        for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
+          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + buf * DKV_BQ + (kk >> 1) * 32 + (kk & 1) * 8,
+                    make_smem_desc(do_addr + kk * 2048, QD_HALF, 1024), idesc_g, (i | kk) != 0);
         }
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_DPT, make_smem_desc(v_addr + off, 16, 1024),
-                    make_smem_desc(do_addr + off, 16, 1024), idesc_kk, kk != 0);
-        }
-        tc_commit(st_full);
-        if (!mbar_wait(pt_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after_sync();
-        // dV += P^T dO and dK += dS^T Q: A from TMEM (K-major over q), B MN-major (d contiguous)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk >> 2) * 64 + (kk & 3) * 8,
-                    make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn, (i | kk) != 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + (kk >> 2) * 64 + (kk & 3) * 8,
-                    make_smem_desc(q_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn, (i | kk) != 0);
+        for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
+          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + buf * DKV_BQ + (kk >> 1) * 32 + (kk & 1) * 8,
+                    make_smem_desc(q_addr + kk * 2048, QD_HALF, 1024), idesc_g, (i | kk) != 0);
         }
         tc_commit(&qd_empty[st]);
-        tc_commit(grad_done);
       }
+      if (ok) tc_commit(grad_done);
     }
   } else {
-    // Eight warps: warps k and k + 4 share the 32 key rows of TMEM lane quarter k and take one
-    // half of the 128 query columns each, so every scheduler has two of them to interleave.
     const int quarter = warp & 3, half = warp >> 2;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const int tid = quarter * 32 + lane;  // 0..127: key row of this thread, and the q column it stages
+    const int tid = (warp << 5) + lane;      // 0..255
+    const int key = quarter * 32 + lane;     // key row of this thread
     bool ok = n_items > 0;
     for (int i = 0; i < n_items && ok; ++i) {
+      const int buf = i & 1;
       const int2 it = items[i];
       const int head = it.y >> 8, rows = it.y & 0xff;
-      float* my_stats = stats + (i & 1) * 256;
-      {
-        const int q = it.x + tid;
-        const bool valid = tid < rows && q < p.nq;
+      float* my_stats = stats + buf * 2 * DKV_BQ;
+      if (tid < 2 * DKV_BQ) {  // 64 threads stage lse, 64 stage delta
+        const int col = tid & (DKV_BQ - 1);
+        const int q = it.x + col;
+        const bool valid = col < rows && q < p.nq;
         const int64_t idx = (int64_t(batch) * p.hq + head) * p.nq + q;
-        if (half == 0) my_stats[tid] = valid ? p.lse[idx] * LOG2E : INFINITY;  // +inf => probability 0
-        else my_stats[128 + tid] = valid ? p.delta[idx] : 0.f;
+        if (tid < DKV_BQ) my_stats[col] = valid ? p.lse[idx] * LOG2E : INFINITY;  // +inf => probability 0
+        else my_stats[DKV_BQ + col] = valid ? p.delta[idx] : 0.f;
       }
       mbar_arrive(stats_bar);
       if (!mbar_wait(stats_bar, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
-      if (!mbar_wait(st_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(&st_full[buf], (i >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
-      {
-        uint32_t s[2][32], d[2][32];
+      uint32_t s[32], d[32];
+      tmem_ld_32x32(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, s);
+      tmem_ld_32x32(tmem_base + lane_base + C_DPT + buf * DKV_BQ + half * 32, d);
+      tmem_ld_wait();
+      uint32_t pp[16], dd[16];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld_32x32(tmem_base + lane_base + C_ST + half * 64 + c * 32, s[c]);
-          tmem_ld_32x32(tmem_base + lane_base + C_DPT + half * 64 + c * 32, d[c]);
+      for (int k2 = 0; k2 < 16; ++k2) {
+        float pv[2], dv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int col = 2 * k2 + e;
+          const int qc = half * 32 + col;
+          const float prob = exp2f(__uint_as_float(s[col]) * p.scale_log2 - my_stats[qc]);
+          pv[e] = prob;
+          dv[e] = prob * (__uint_as_float(d[col]) - my_stats[DKV_BQ + qc]) * p.scale;
         }
-        tmem_ld_wait();
-        uint32_t pp[32], dd[32];
-#pragma unroll
-        for (int k2 = 0; k2 < 32; ++k2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = 2 * k2 + e;
-            const int qc = half * 64 + col;
-            const float sv = __uint_as_float(s[col >> 5][col & 31]);
-            const float dp = __uint_as_float(d[col >> 5][col & 31]);
-            const float prob = exp2f(sv * p.scale_log2 - my_stats[qc]);
-            pv[e] = prob;
-            dv[e] = prob * (dp - my_stats[128 + qc]) * p.scale;
-          }
-          pp[k2] = pack_bf16(pv[0], pv[1]);
-          dd[k2] = pack_bf16(dv[0], dv[1]);
-        }
-        // the packed halves land in columns this thread has already read
-        tmem_st_32x32(tmem_base + lane_base + C_ST + half * 64, pp);
-        tmem_st_32x32(tmem_base + lane_base + C_DPT + half * 64, dd);
+        pp[k2] = pack_bf16(pv[0], pv[1]);
+        dd[k2] = pack_bf16(dv[0], dv[1]);
       }
+      // the packed results land in columns this thread has already read
+      tmem_st_32x16(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, pp);
+      tmem_st_32x16(tmem_base + lane_base + C_DPT + buf * DKV_BQ + half * 32, dd);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(pt_ready);
+      if (lane == 0) mbar_arrive(&pt_ready[buf]);
     }
-    if (ok) ok = mbar_wait(grad_done, (n_items - 1) & 1, guard, kTimeoutEpilogue);
+    if (ok) ok = mbar_wait(grad_done, 0, guard, kTimeoutEpilogue);
     if (ok) {
       tc_fence_after_sync();
-      const bool row_ok = tid < k_rows;
-      const int64_t base = ((int64_t(batch) * p.nk + k_row + tid) * p.hkv + kv_head) * ATT_D;
+      const bool row_ok = key < k_rows;
+      const int64_t base = ((int64_t(batch) * p.nk + k_row + key) * p.hkv + kv_head) * ATT_D;
       {  // the two halves write one gradient each
         const int which = half;
         __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + base;
@@ -551,20 +569,22 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 }  // namespace
 
 bool make_rows_map_bwd(CUtensorMap* map, const void* base, int heads, int64_t rows, int64_t batch,
-                       int64_t row_stride, int64_t batch_stride) {
+                       int64_t row_stride, int64_t batch_stride, int box_rows = 128) {
   const uint64_t dims[3] = {uint64_t(heads) * ATT_D, uint64_t(rows), uint64_t(batch)};
   const uint64_t strides[2] = {uint64_t(row_stride) * 2, uint64_t(batch_stride) * 2};
-  const uint32_t box[3] = {64, 128, 1};
+  const uint32_t box[3] = {64, uint32_t(box_rows), 1};
   return make_tensor_map_bf16(map, base, 3, dims, strides, box);
 }
 
 cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
   const AttnArgs& a = b.fwd;
   if (a.num_q_tiles == 0 || a.batch == 0) return cudaSuccess;
-  CUtensorMap tq, tdo, tkt, tvt, tk, tv;
+  CUtensorMap tq, tdo, tq64, tdo64, tkt, tvt, tk, tv;
   const int64_t dense_row = int64_t(a.hq) * ATT_D;
   if (!make_rows_map_bwd(&tq, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride) ||
       !make_rows_map_bwd(&tdo, b.grad_out, a.hq, a.nq, a.batch, dense_row, dense_row * a.nq) ||
+      !make_rows_map_bwd(&tq64, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride, DKV_BQ) ||
+      !make_rows_map_bwd(&tdo64, b.grad_out, a.hq, a.nq, a.batch, dense_row, dense_row * a.nq, DKV_BQ) ||
       !make_rows_map_bwd(&tk, a.k, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride) ||
       !make_rows_map_bwd(&tv, a.v, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride)) {
     set_error_detail("attention_bwd: tensor map refused by the driver");
@@ -613,7 +633,7 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
     p.nq = int(a.nq); p.nk = int(a.nk); p.hq = a.hq; p.hkv = a.hkv; p.group = a.hq / a.hkv;
     p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
     dim3 grid(b.num_k_tiles, a.hkv, unsigned(a.batch));
-    attn_dkv_kernel<<<grid, DQ_THREADS, DKV_SMEM, stream>>>(tq, tdo, tk, tv, p);
+    attn_dkv_kernel<<<grid, DQ_THREADS, DKV_SMEM, stream>>>(tq64, tdo64, tk, tv, p);
   }
   return cudaGetLastError();
 }

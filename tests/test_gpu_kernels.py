@@ -351,11 +351,11 @@ def test_channel_norm_kernel(channels, silu):
 
 
 def test_vae_on_gpu_matches_cpu_fp32():
-    from agentgarten_b200.codecs.wan22 import random_vae
+    from agentgarten_b200.codecs.wan22 import random_vae, to_channels_last
 
     arch = dict(dim=16, dec_dim=16, z_dim=8)
     cpu = random_vae(seed=3, **arch)
-    gpu = random_vae(seed=3, **arch).to(DEV, torch.bfloat16).to(memory_format=torch.channels_last_3d)
+    gpu = to_channels_last(random_vae(seed=3, **arch).to(DEV, torch.bfloat16))
     scale = (0.0, 1.0)
     video = torch.rand(1, 3, 9, 32, 48) * 2 - 1
     before = native.launches()
