@@ -108,6 +108,44 @@ def check_tensor_parallel_stream(device, rank, world):
     release_serving(net)
 
 
+def check_context_parallel_training(device, rank, world):
+    """Ulysses context parallelism over NCCL with the CUDA kernels: same loss and the same
+    summed gradients as the unsharded model on the same clip."""
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from helpers import synthetic_batch, tiny_conditioner, tiny_config, tiny_network
+
+    from agentgarten_b200.models.diffusion import DiffusionModel
+    from agentgarten_b200.parallel.engine import ParallelConfig
+
+    config = tiny_config(hidden_size=512, intermediate_size=1024, num_attention_heads=8,
+                         num_key_value_heads=2 * world, head_dim=128, mrope_section=(24, 20, 20))
+    losses, grads = {}, {}
+    for cp in (1, world):
+        parallel = ParallelConfig(parameter_dtype="bfloat16", context_parallel_size=cp,
+                                  fully_shard=False, activation_checkpointing="none")
+        frozen = ParallelConfig(parameter_dtype="bfloat16", fully_shard=False, activation_checkpointing="none")
+        model = DiffusionModel(net=tiny_network(config, seed=0), conditioner=tiny_conditioner(config, seed=1),
+                               text_dropout=0.0, parallel=parallel, conditioner_parallel=frozen)
+        model.parallelize(device)
+        raw = {k: v.to(device) for k, v in synthetic_batch(frames=5, height=16, width=16, text=9, seed=3).items()}
+        batch = model.prepare_data_batch(raw)
+        torch.manual_seed(11)
+        model.train()
+        _, loss = model.training_step(batch, 0)
+        loss.backward()
+        losses[cp] = float(loss)
+        grads[cp] = {n: p.grad.float().clone() for n, p in model.net.named_parameters() if p.grad is not None}
+    assert abs(losses[1] - losses[world]) < 2e-2 * max(1.0, abs(losses[1])), losses
+    worst = 0.0
+    for name, full in grads[1].items():
+        part = grads[world][name].clone()
+        dist.all_reduce(part)
+        scale = float(full.norm()) + 1e-6
+        err = min(float((part - full).norm()), float((part / world - full).norm())) / scale
+        worst = max(worst, err)
+    assert worst < 5e-2, worst
+
+
 def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     device = distributed.init(device="cuda", backend="nccl")
@@ -115,6 +153,8 @@ def main():
     check_sharded_adam(device, rank, world)
     dist.barrier()
     check_tensor_parallel_stream(device, rank, world)
+    dist.barrier()
+    check_context_parallel_training(device, rank, world)
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK")

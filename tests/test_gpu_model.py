@@ -211,3 +211,70 @@ def test_tensor_parallel_kernels_on_one_rank_match_the_layer_path():
         assert torch.equal(b, c)
     from agentgarten_b200.inference.serving import release_serving
     release_serving(net)
+
+
+def test_forward_ar_replays_cached_rollout_bitwise_on_the_kernels():
+    """Teacher-forced training and the cached rollout must give identical bits: key tiles
+    never straddle segments, so both accumulate a row over the same tile partition."""
+    from agentgarten_b200.models.flow import rf_interpolate
+
+    config = _config()
+    net = tiny_network(config, device="cpu", seed=0).to(DEV, torch.bfloat16).eval()
+    cond = tiny_conditioner(config, device="cpu", seed=1).to(DEV, torch.bfloat16)
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=9, height=16, width=16, text=9, seed=2).items()}
+    encoded = cond.encode(batch, training=False)
+    condition, latent = cond.condition(encoded), encoded["latent"]
+    anchor, target = latent[:, :, :1], latent[:, :, 1:]
+    sigma = torch.tensor([[0.7] * 4 + [0.3] * 4], device=DEV)
+    noisy = rf_interpolate(target, torch.randn_like(target), sigma)
+    before = native.launches()
+    with torch.no_grad():
+        full = net.forward_ar(anchor, noisy, sigma, condition, block_frames=4, clean=target)
+        cache = net.prefill(anchor, condition)
+        outs = []
+        for b in range(2):
+            sl = slice(4 * b, 4 * b + 4)
+            outs.append(net.denoise(cache, noisy[:, :, sl], sigma[:, sl]))
+            cache = net.commit(cache, target[:, :, sl])
+    assert native.launches() > before
+    assert torch.isfinite(full).all()
+    assert torch.equal(full, torch.cat(outs, dim=2))
+    assert int(native.ext().status(0).item()) == 0
+
+
+@pytest.mark.parametrize("regularization", ["finite_difference", "exact"])
+def test_dmd_gan_step_runs_on_the_kernels(regularization):
+    """Student / fake-score / discriminator updates on bf16 CUDA towers; the exact penalties
+    differentiate the frozen backbone in forward mode, i.e. through the tangent kernel."""
+    from agentgarten_b200.infra.config import LazyCall
+    from agentgarten_b200.infra.optim import LinearWarmup
+    from agentgarten_b200.models.dmd import DMDModel, GANConfig
+    from agentgarten_b200.networks.discriminator import DiscriminatorHead
+    from agentgarten_b200.parallel.engine import ParallelConfig
+
+    config = _config()
+    parallel = ParallelConfig(parameter_dtype="bfloat16", fully_shard=False, activation_checkpointing="none")
+    head = DiscriminatorHead(hidden_size=config.hidden_size, feature_layers=(0, 1), num_heads=4, mlp_ratio=2.0)
+    model = DMDModel(student=tiny_network(config, seed=0), real_score=tiny_network(config, seed=1),
+                     fake_score=tiny_network(config, seed=2), conditioner=tiny_conditioner(config),
+                     discriminator=head, gan=GANConfig(regularization=regularization, warmup_updates=1),
+                     fake_score_updates_per_student=1, real_score_guidance=1.0, seed=3,
+                     student_parallel=parallel, score_parallel=parallel, real_score_parallel=parallel,
+                     conditioner_parallel=parallel)
+    model.parallelize(torch.device(DEV))
+    optim = {name: LazyCall(FusedAdam)(lr=1e-4, betas=(0.0, 0.999)) for name in
+             ("student", "fake_score", "discriminator")}
+    sched = LazyCall(torch.optim.lr_scheduler.LambdaLR)(lr_lambda=LazyCall(LinearWarmup)(warmup_steps=2))
+    model.init_optimizer_scheduler(optim, sched)
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=5, height=16, width=16, text=9, seed=4).items()}
+    batch = model.prepare_data_batch(batch)
+    before = native.launches()
+    for iteration in range(3):  # discriminator warm-up, student, fake score
+        torch.manual_seed(iteration)
+        out, loss = model.training_step(batch, iteration)
+        assert torch.isfinite(loss), (iteration, float(loss))
+        loss.backward()
+        model.zero_grad(set_to_none=True)
+    assert native.launches() > before
+    torch.cuda.synchronize()
+    assert int(native.ext().status(0).item()) == 0
