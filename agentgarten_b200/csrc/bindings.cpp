@@ -130,7 +130,9 @@ std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& grad, const Tensor& x, con
 std::tuple<Tensor, Tensor> head_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& cosv,
                                               const Tensor& sinv, double eps) {
   check_bf16(x, "x");
-  TORCH_CHECK(x.dim() == 4 && x.size(3) == 128, "x must be [B, N, H, 128]");
+  TORCH_CHECK(x.dim() == 4 && x.size(3) == 128 && x.is_contiguous(), "x must be contiguous [B, N, H, 128]");
+  TORCH_CHECK(cosv.is_contiguous() && sinv.is_contiguous() && cosv.numel() == x.size(0) * x.size(1) * 128,
+              "cos/sin must be contiguous [B, N, 128]");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = x.size(0) * x.size(1);
   const int heads = int(x.size(2));
