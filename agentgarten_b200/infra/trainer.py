@@ -34,6 +34,8 @@ from .batch_transport import fetch_batch, prepare_batch
 from .callbacks.base import CallbackGroup
 from .distributed import DistributedDataParallel, ddp_sync_grad, is_rank0
 from .model import Model
+from agentgarten_b200.utils.trace import span
+
 from .nonfinite import synchronize_found_nonfinite
 from .rng_state import isolated_rng
 
@@ -336,12 +338,14 @@ class Trainer:
             count += 1
             finished = is_last
             with ddp_sync_grad(model_ddp, final_microbatch and is_last):
-                if isinstance(model_ddp, DistributedDataParallel):
-                    out, loss = model_ddp.forward_closure(closure)
-                else:
-                    out, loss = closure()
+                with span("forward"):
+                    if isinstance(model_ddp, DistributedDataParallel):
+                        out, loss = model_ddp.forward_closure(closure)
+                    else:
+                        out, loss = closure()
                 outputs.update(out)
-                scaler.scale(loss / self.grad_accum_steps).backward()
+                with span("backward"):
+                    scaler.scale(loss / self.grad_accum_steps).backward()
             total = loss.detach() if total is None else total + loss.detach()
         if count == 0 or total is None:
             raise RuntimeError("training_step_closures() yielded no closures")
@@ -365,7 +369,8 @@ class Trainer:
         found = synchronize_found_nonfinite(scaler, optimizers, fallback_device=total.device)
         if not found:
             for b in bindings:
-                scaler.step(b.optimizer)
+                with span(f"optimizer {b.name}"):
+                    scaler.step(b.optimizer)
                 b.scheduler.step()
                 self.callbacks.on_after_optimizer_step(model_ddp, b.name, b.optimizer, b.scheduler,
                                                        iteration=iteration)

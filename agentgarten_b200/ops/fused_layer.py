@@ -28,6 +28,8 @@ import os
 
 import torch
 
+from agentgarten_b200.utils.trace import span
+
 from . import native
 from .attention import build_schedule
 
@@ -136,6 +138,11 @@ class _Layer(torch.autograd.Function):
     @staticmethod
     @torch.autograd.function.once_differentiable
     def backward(ctx, dy):
+        with span("layer backward"):
+            return _Layer._backward(ctx, dy)
+
+    @staticmethod
+    def _backward(ctx, dy):
         C = native.ext()
         x, cos, sin, attn, lse, *_ = ctx.saved_tensors
         w_in, wq, wk, wv, wo, nq, nk, w_post, wg, wu, wd = ctx.params
@@ -220,6 +227,7 @@ def run(layer, chunks, ropes, attention, layer_index):
                to_out.weight, norm_q.weight, norm_k.weight,
                layer.post_attention_layernorm_moe_gen.weight, mlp.gate_proj.weight,
                mlp.up_proj.weight, mlp.down_proj.weight)
-    y = _Layer.apply(x.contiguous(), cos.contiguous(), sin.contiguous(), layer, schedule,
-                     text_k, text_v, valid, *weights)
+    with span(f"layer {layer_index} forward"):
+        y = _Layer.apply(x.contiguous(), cos.contiguous(), sin.contiguous(), layer, schedule,
+                         text_k, text_v, valid, *weights)
     return list(y.split(sizes, dim=1)) if len(sizes) > 1 else [y]

@@ -103,3 +103,65 @@ def test_restore_plan_rules():
         {"s": {"path": "p", "model_key_prefixes": ["student"], "source_model_key_prefix": ""},
          "f": {"path": "p", "model_key_prefixes": ["fake"], "source_model_key_prefix": ""}}, resume=False)
     assert len(merged) == 1 and merged[0].destinations == ("student", "fake")
+
+
+# ------------------------------------------------------------------ failures on the host
+def test_failed_write_never_publishes_latest(tmp_path, monkeypatch):
+    """The tensor write fails (a full disk, a dead mount): the error surfaces at finalize and
+    the `latest` pointer keeps naming the last good checkpoint."""
+    import pytest
+    import torch.distributed.checkpoint as dcp
+
+    model, opt, sched = _job()
+    saver = DistributedCheckpointer(tmp_path / "ckpt", async_mode=None)
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=1)
+    assert (tmp_path / "ckpt" / "latest").read_text().strip() == "iter_000000001"
+
+    def broken(*args, **kwargs):
+        raise OSError("No space left on device")
+
+    monkeypatch.setattr(dcp, "save", broken)
+    with pytest.raises(RuntimeError, match="No space left"):
+        saver.save(model, {"net": opt}, {"net": sched}, None, iteration=2)
+    assert (tmp_path / "ckpt" / "latest").read_text().strip() == "iter_000000001"
+    # error shutdown: nothing collective, nothing raised, nothing published
+    saver.finalize_after_error()
+    assert (tmp_path / "ckpt" / "latest").read_text().strip() == "iter_000000001"
+
+
+def test_failed_latest_publication_is_reported(tmp_path, monkeypatch):
+    import pytest
+
+    from agentgarten_b200.infra.checkpoint import checkpointer as module
+
+    model, opt, sched = _job()
+    saver = DistributedCheckpointer(tmp_path / "ckpt", async_mode=None)
+
+    def broken(text, path):
+        raise PermissionError("read-only file system")
+
+    monkeypatch.setattr(module, "atomic_put_text", broken)
+    with pytest.raises(RuntimeError, match="latest pointer publication"):
+        saver.save(model, {"net": opt}, {"net": sched}, None, iteration=4)
+    assert not (tmp_path / "ckpt" / "latest").exists()
+
+
+def test_truncated_shard_fails_the_load_loudly(tmp_path):
+    import pytest
+
+    model, opt, sched = _job()
+    saver = DistributedCheckpointer(tmp_path / "ckpt", async_mode=None)
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=1)
+    shard = next((tmp_path / "ckpt" / "iter_000000001" / "tensor").glob("*.distcp"))
+    data = shard.read_bytes()
+    shard.write_bytes(data[: len(data) // 3])
+    fresh, opt2, sched2 = _job(seed=7)
+    with pytest.raises(Exception):
+        DistributedCheckpointer(tmp_path / "ckpt", async_mode=None).load(fresh, {"net": opt2}, {"net": sched2}, None)
+
+
+def test_missing_checkpoint_is_a_fresh_start(tmp_path):
+    model, opt, sched = _job()
+    result = DistributedCheckpointer(tmp_path / "nothing_here", async_mode=None).load(
+        model, {"net": opt}, {"net": sched}, None)
+    assert result.iteration == 0 and result.loaded_components == ()

@@ -278,3 +278,14 @@ def test_dmd_gan_step_runs_on_the_kernels(regularization):
     assert native.launches() > before
     torch.cuda.synchronize()
     assert int(native.ext().status(0).item()) == 0
+
+
+def test_training_step_is_bitwise_reproducible():
+    """Same seed, same inputs: identical loss and gradients (no atomics anywhere in backward)."""
+    config = _config()
+    model = _model(DEV, torch.bfloat16, config)
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=5, height=16, width=16, text=9, seed=6).items()}
+    first_loss, first = _loss_and_grads(model, batch, seed=4)
+    second_loss, second = _loss_and_grads(model, batch, seed=4)
+    assert first_loss == second_loss
+    assert first.keys() == second.keys() and all(torch.equal(first[k], second[k]) for k in first)
