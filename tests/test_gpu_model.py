@@ -289,3 +289,31 @@ def test_training_step_is_bitwise_reproducible():
     second_loss, second = _loss_and_grads(model, batch, seed=4)
     assert first_loss == second_loss
     assert first.keys() == second.keys() and all(torch.equal(first[k], second[k]) for k in first)
+
+
+def test_sampling_paths_run_on_the_kernels():
+    """UniPC sampling with guidance (bidirectional) and the block-by-block cached rollout
+    (autoregressive), both decoded by the VAE in bf16 on the device."""
+    from agentgarten_b200.codecs import Wan22VAECodec
+    from agentgarten_b200.models.autoregressive import AutoregressiveModel
+
+    config = _config()
+    codec = Wan22VAECodec(None, dtype="bfloat16", architecture=dict(dim=16, dec_dim=16, z_dim=48))
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=5, height=8, width=8, text=9, seed=8).items()}
+    before = native.launches()
+    for kind in ("bidirectional", "autoregressive"):
+        net = tiny_network(config, device="cpu", seed=0)
+        cond = tiny_conditioner(config, device="cpu", seed=1)
+        cond.codec, cond.empty_prompt_ids = codec, (3, 4, 1)
+        if kind == "bidirectional":
+            model = DiffusionModel(net=net, conditioner=cond, text_dropout=0.0)
+        else:
+            model = AutoregressiveModel(net=net, conditioner=cond, mode="diffusion_forcing", block_frames=4)
+        model.to(device=DEV, dtype=torch.bfloat16).eval()
+        encoded = model.prepare_data_batch(dict(batch))
+        out = model.sample(encoded, num_steps=3, guidance=2.0, seed=1)
+        assert set(out) >= {"ground_truth", "sample"}
+        assert out["sample"].shape == (1, 3, 17, 128, 128) and torch.isfinite(out["sample"]).all()
+    assert native.launches() > before
+    torch.cuda.synchronize()
+    assert int(native.ext().status(0).item()) == 0
