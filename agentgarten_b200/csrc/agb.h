@@ -117,6 +117,8 @@ cudaError_t head_norm_rope_bwd(const void* grad, const void* x, const void* w, c
                                int64_t rows, int heads, cudaStream_t stream);
 cudaError_t silu_mul_fwd(const void* gate, const void* up, void* out, int64_t elements,
                          cudaStream_t stream);
+// out[r, c] = bf16(silu(both[r, c])) * both[r, width + c] for both = [rows, 2 * width].
+cudaError_t silu_mul_pair(const void* both, void* out, int64_t rows, int width, cudaStream_t stream);
 cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, void* dgate,
                          void* dup, int64_t elements, cudaStream_t stream);
 // mode 0: (1-s)*a + s*b; mode 1: a - s*b.  sigma fp32 [batch, sigma_frames]

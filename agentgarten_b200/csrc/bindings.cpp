@@ -169,6 +169,17 @@ Tensor silu_mul_fwd(const Tensor& gate, const Tensor& up) {
   return out;
 }
 
+Tensor silu_mul_pair(const Tensor& both) {
+  check_bf16(both, "both");
+  TORCH_CHECK(both.dim() == 2 && both.is_contiguous() && both.size(1) % 16 == 0,
+              "silu_mul_pair takes a contiguous [rows, 2 * width] matrix");
+  c10::cuda::CUDAGuard guard(both.device());
+  auto out = torch::empty({both.size(0), both.size(1) / 2}, both.options());
+  check(agb::silu_mul_pair(both.data_ptr(), out.data_ptr(), both.size(0), int(both.size(1) / 2),
+                           stream_of(both)), "silu_mul_pair");
+  return out;
+}
+
 std::tuple<Tensor, Tensor> silu_mul_bwd(const Tensor& grad, const Tensor& gate, const Tensor& up) {
   c10::cuda::CUDAGuard guard(gate.device());
   auto dgate = torch::empty_like(gate);
@@ -503,6 +514,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("head_norm_rope_bwd", &head_norm_rope_bwd);
   m.def("silu_mul_fwd", &silu_mul_fwd);
   m.def("silu_mul_bwd", &silu_mul_bwd);
+  m.def("silu_mul_pair", &silu_mul_pair);
   m.def("rf_combine", &rf_combine);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

@@ -383,6 +383,32 @@ cudaError_t silu_mul_fwd(const void* gate, const void* up, void* out, int64_t el
   return cudaGetLastError();
 }
 
+// gate and up are the two column halves of one [rows, 2 * width] matrix (one GEMM produced both).
+__global__ void __launch_bounds__(NT) silu_mul_pair_kernel(const __nv_bfloat16* __restrict__ both,
+                                                           __nv_bfloat16* __restrict__ out,
+                                                           int64_t rows, int width) {
+  const int per_row = width / 8;
+  const int64_t vecs = rows * per_row;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < vecs; i += int64_t(gridDim.x) * NT) {
+    const int64_t row = i / per_row;
+    const int col = int(i - row * per_row) * 8;
+    float g[8], u[8];
+    unpack8(*reinterpret_cast<const uint4*>(both + row * 2 * width + col), g);
+    unpack8(*reinterpret_cast<const uint4*>(both + row * 2 * width + width + col), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = round_bf16(g[k] / (1.f + __expf(-g[k]))) * u[k];
+    *reinterpret_cast<uint4*>(out + row * width + col) = pack8(g);
+  }
+}
+
+cudaError_t silu_mul_pair(const void* both, void* out, int64_t rows, int width, cudaStream_t stream) {
+  if (rows == 0 || width == 0) return cudaSuccess;
+  if (width % 8) return cudaErrorInvalidValue;
+  silu_mul_pair_kernel<<<grid_for(rows * (width / 8)), NT, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(both), static_cast<__nv_bfloat16*>(out), rows, width);
+  return cudaGetLastError();
+}
+
 cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, void* dgate,
                          void* dup, int64_t elements, cudaStream_t stream) {
   if (elements == 0) return cudaSuccess;

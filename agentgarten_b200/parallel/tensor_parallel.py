@@ -102,8 +102,7 @@ class TensorParallelServing:
             self.layers.append({
                 "qkv": torch.cat((to_q.weight[q_rows], to_k.weight[kv_rows], to_v.weight[kv_rows])).contiguous(),
                 "out": to_out.weight[:, q_rows].contiguous(),
-                "gate": mlp.gate_proj.weight[mlp_rows].contiguous(),
-                "up": mlp.up_proj.weight[mlp_rows].contiguous(),
+                "gate_up": torch.cat((mlp.gate_proj.weight[mlp_rows], mlp.up_proj.weight[mlp_rows])).contiguous(),
                 "down": mlp.down_proj.weight[:, mlp_rows].contiguous(),
                 "norm_q": norm_q.weight, "norm_k": norm_k.weight, "head_eps": norm_q.variance_epsilon,
                 "norm_in": layer.input_layernorm_moe_gen.weight,
@@ -193,7 +192,7 @@ class TensorParallelServing:
                                    w["norm_q"], cos, sin, w["head_eps"])
             k = ops.head_norm_rope(qkv[:, q_cols:q_cols + kv_cols].contiguous().view(1, m, self.kv_heads, self.dim),
                                    w["norm_k"], cos, sin, w["head_eps"])
-            v = qkv[:, q_cols + kv_cols:].contiguous().view(1, m, self.kv_heads, self.dim)
+            v = qkv[:, q_cols + kv_cols:].view(1, m, self.kv_heads, self.dim)  # copied into the cache as is
             t2 = self._mark("head norm + rope", t1)
             (mixed,) = attend(index, [q], [k], [v])
             t3 = self._mark("cache write + attention", t2)
@@ -201,10 +200,10 @@ class TensorParallelServing:
             t4 = self._mark("out gemm + scatter", t3)
             self._reduce(m, owned, w["norm_mid"], None)
             t5 = self._mark("reduce + norm + push", t4)
-            gate = self._gather_gemm(x, w["gate"], close=False)
-            up = self._gather_gemm(x, w["up"], close=True)
+            both = self._gather_gemm(x, w["gate_up"], close=True)  # [m, gate columns | up columns]
             t6 = self._mark("gather+gate/up gemm", t5)
-            act = ops.silu_mul(gate, up)
+            native.count()
+            act = native.ext().silu_mul_pair(both)
             t7 = self._mark("silu mul", t6)
             self._scatter_gemm(act, w["down"], owned)
             t8 = self._mark("down gemm + scatter", t7)

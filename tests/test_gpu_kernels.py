@@ -367,3 +367,11 @@ def test_vae_on_gpu_matches_cpu_fp32():
         pixels = cpu.decode(want, scale, frames_per_pass=2)
         got_pixels = gpu.decode(want.to(DEV, torch.bfloat16), scale, frames_per_pass=2)
         assert got_pixels.shape == pixels.shape and _rel(got_pixels, pixels.to(DEV)) < 8e-2
+
+
+def test_silu_mul_pair():
+    torch.manual_seed(0)
+    both = torch.randn(37, 2 * 48, device=DEV).bfloat16()
+    out = native.ext().silu_mul_pair(both)
+    want = ops.silu_mul(both[:, :48].contiguous(), both[:, 48:].contiguous())
+    assert torch.equal(out, want)
