@@ -58,9 +58,48 @@ def _world(group) -> tuple[int, int]:
     return 1, 0
 
 
+_NODE_GROUPS: dict[tuple[int, int], tuple[Any, Any]] = {}
+
+
+def node_groups(local_size: int) -> tuple[Any, Any]:
+    """``(shard group, replica group)`` of a job that spans several nodes.
+
+    Peer memory ends at the node, so the optimizer state is sharded over the ranks of a node
+    (consecutive global ranks) and replicated across nodes; gradients are averaged across the
+    replicas (ranks with the same local index) by NCCL before the node-local reduce.  This is
+    the hybrid sharding of the reference (mesh ``(nodes, local)``, ``wm/infra/parallel.py:125-161``).
+    Every rank must call this with the same ``local_size`` (groups are created collectively).
+    """
+    world, rank = dist.get_world_size(), dist.get_rank()
+    key = (world, local_size)
+    if key not in _NODE_GROUPS:
+        if world % local_size:
+            raise ValueError(f"{world} ranks do not split into nodes of {local_size}")
+        shard = replica = None
+        for node in range(world // local_size):
+            members = list(range(node * local_size, (node + 1) * local_size))
+            group = dist.new_group(members)
+            if rank in members:
+                shard = group
+        for local in range(local_size):
+            members = list(range(local, world, local_size))
+            group = dist.new_group(members)
+            if rank in members:
+                replica = group
+        _NODE_GROUPS[key] = (shard, replica)
+    return _NODE_GROUPS[key]
+
+
 class ZeroEngine:
     def __init__(self, optimizer: torch.optim.Optimizer, process_group: Any = None) -> None:
         self.optimizer = optimizer
+        self.replica_group = None
+        if process_group is None and dist.is_available() and dist.is_initialized():
+            from agentgarten_b200.infra.distributed import get_local_world_size
+
+            local = get_local_world_size()
+            if 0 < local < dist.get_world_size():
+                process_group, self.replica_group = node_groups(local)
         self.group = process_group
         self.world, self.rank = _world(process_group)
         if self.world > 8:
@@ -164,6 +203,9 @@ class ZeroEngine:
     def reduce_gradients(self) -> None:
         if self._reduced:
             return
+        if self.replica_group is not None:
+            # across nodes first: every node then holds the job-wide average of its local index
+            dist.all_reduce(self.flat_grad, op=dist.ReduceOp.AVG, group=self.replica_group)
         self._sync()  # every rank has finished writing its gradients
         self.C.zero_reduce(self.grad_ptrs, self.units, self.gshard, self.stats)
         native.count(2)

@@ -160,6 +160,26 @@ def case_context_parallel_matches_single_group():
             float((part / world - full).abs().max()) / scale < 2e-4, name
 
 
+def case_node_groups_for_hybrid_sharding():
+    """Four ranks as two nodes of two: shards are node-local, replicas pair equal local indices."""
+    from agentgarten_b200.parallel.zero import node_groups
+
+    rank = dist.get_rank()
+    shard, replica = node_groups(2)
+    assert dist.get_process_group_ranks(shard) == [rank - rank % 2, rank - rank % 2 + 1]
+    assert dist.get_process_group_ranks(replica) == [rank % 2, rank % 2 + 2]
+    value = torch.tensor([float(rank)])
+    dist.all_reduce(value, group=replica)
+    assert float(value) == 2 * (rank % 2) + 2
+    assert node_groups(2) == (shard, replica)  # cached: groups are created once
+    try:
+        node_groups(3)
+    except ValueError:
+        pass
+    else:
+        raise AssertionError("4 ranks cannot form nodes of 3")
+
+
 CASES = {name[5:]: fn for name, fn in list(globals().items()) if name.startswith("case_")}
 
 

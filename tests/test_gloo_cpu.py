@@ -26,6 +26,7 @@ def _run(case, ranks, port):
     ("cp_transport_shares_batch_and_rng", 4, 29643),
     ("cp_prepare_error_reaches_the_group", 2, 29644),
     ("context_parallel_matches_single_group", 2, 29645),
+    ("node_groups_for_hybrid_sharding", 4, 29646),
 ])
 def test_gloo_case(case, ranks, port):
     _run(case, ranks, port)
