@@ -107,10 +107,12 @@ int rms_norm_bwd_partials(int64_t rows);
 cudaError_t rms_norm_bwd(const void* grad, const void* x, const void* w, const float* rstd,
                          void* dx, float* dw_partial, int64_t rows, int width,
                          cudaStream_t stream);
-// x [rows, heads, 128]; cos/sin [rows, 128]; rstd fp32 [rows, heads] (may be null in fwd).
+// x [rows, heads, 128] with row_stride elements between rows (heads * 128 when dense; larger
+// when x is a column block of a wider matrix); out is dense; cos/sin [rows, 128]; rstd fp32
+// [rows, heads] (may be null in fwd).
 cudaError_t head_norm_rope_fwd(const void* x, const void* w, const void* cosv, const void* sinv,
-                               void* out, float* rstd, int64_t rows, int heads, float eps,
-                               cudaStream_t stream);
+                               void* out, float* rstd, int64_t rows, int heads, int64_t row_stride,
+                               float eps, cudaStream_t stream);
 int head_norm_rope_bwd_partials(int64_t rows, int heads);  // rows of the fp32 [.,128] partial
 cudaError_t head_norm_rope_bwd(const void* grad, const void* x, const void* w, const void* cosv,
                                const void* sinv, const float* rstd, void* dx, float* dw_partial,

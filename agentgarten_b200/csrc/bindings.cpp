@@ -130,17 +130,19 @@ std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& grad, const Tensor& x, con
 std::tuple<Tensor, Tensor> head_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& cosv,
                                               const Tensor& sinv, double eps) {
   check_bf16(x, "x");
-  TORCH_CHECK(x.dim() == 4 && x.size(3) == 128 && x.is_contiguous(), "x must be contiguous [B, N, H, 128]");
+  TORCH_CHECK(x.dim() == 4 && x.size(3) == 128 && x.stride(3) == 1 && x.stride(2) == 128 &&
+                  (x.size(0) == 1 || x.stride(0) == x.size(1) * x.stride(1)) && x.stride(1) % 8 == 0,
+              "x must be [B, N, H, 128], dense over (H, 128), rows at a constant stride");
   TORCH_CHECK(cosv.is_contiguous() && sinv.is_contiguous() && cosv.numel() == x.size(0) * x.size(1) * 128,
               "cos/sin must be contiguous [B, N, 128]");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = x.size(0) * x.size(1);
   const int heads = int(x.size(2));
-  auto out = torch::empty_like(x);
+  auto out = torch::empty(x.sizes(), x.options());
   auto rstd = torch::empty({rows, heads}, x.options().dtype(torch::kFloat32));
   check(agb::head_norm_rope_fwd(x.data_ptr(), w.data_ptr(), cosv.data_ptr(), sinv.data_ptr(),
-                                out.data_ptr(), rstd.data_ptr<float>(), rows, heads, float(eps),
-                                stream_of(x)), "head_norm_rope_fwd");
+                                out.data_ptr(), rstd.data_ptr<float>(), rows, heads, x.stride(1),
+                                float(eps), stream_of(x)), "head_norm_rope_fwd");
   return {out, rstd};
 }
 

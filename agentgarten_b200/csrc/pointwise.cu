@@ -148,12 +148,13 @@ __global__ void __launch_bounds__(NT) head_norm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
     const __nv_bfloat16* __restrict__ cosv, const __nv_bfloat16* __restrict__ sinv,
     __nv_bfloat16* __restrict__ out, float* __restrict__ rstd_out, int64_t rows, int heads,
-    float eps) {
+    int64_t row_stride, float eps) {
   const int64_t unit = int64_t(blockIdx.x) * (NT / 32) + (threadIdx.x >> 5);
   if (unit >= rows * heads) return;
   const int lane = threadIdx.x & 31;
   const int64_t token = unit / heads;
-  const __nv_bfloat16* xr = x + unit * 128;
+  // the input may be a column block of a wider matrix (e.g. the q part of a fused qkv product)
+  const __nv_bfloat16* xr = x + token * row_stride + (unit - token * heads) * 128;
   const uint32_t a = *reinterpret_cast<const uint32_t*>(xr + 2 * lane);
   const uint32_t b = *reinterpret_cast<const uint32_t*>(xr + 64 + 2 * lane);
   float v[4] = {bf16_lo(a), bf16_hi(a), bf16_lo(b), bf16_hi(b)};
@@ -342,15 +343,15 @@ cudaError_t rms_norm_bwd(const void* grad, const void* x, const void* w, const f
 }
 
 cudaError_t head_norm_rope_fwd(const void* x, const void* w, const void* cosv, const void* sinv,
-                               void* out, float* rstd, int64_t rows, int heads, float eps,
-                               cudaStream_t stream) {
+                               void* out, float* rstd, int64_t rows, int heads, int64_t row_stride,
+                               float eps, cudaStream_t stream) {
   const int64_t units = rows * heads;
   if (units == 0) return cudaSuccess;
   const unsigned grid = unsigned((units + NT / 32 - 1) / (NT / 32));
   head_norm_rope_fwd_kernel<<<grid, NT, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
       static_cast<const __nv_bfloat16*>(cosv), static_cast<const __nv_bfloat16*>(sinv),
-      static_cast<__nv_bfloat16*>(out), rstd, rows, heads, eps);
+      static_cast<__nv_bfloat16*>(out), rstd, rows, heads, row_stride, eps);
   return cudaGetLastError();
 }
 

@@ -188,10 +188,13 @@ class TensorParallelServing:
             t0 = self._mark("")
             qkv = self._gather_gemm(x, w["qkv"], close=True)
             t1 = self._mark("gather+qkv gemm", t0)
-            q = ops.head_norm_rope(qkv[:, :q_cols].contiguous().view(1, m, self.heads, self.dim),
-                                   w["norm_q"], cos, sin, w["head_eps"])
-            k = ops.head_norm_rope(qkv[:, q_cols:q_cols + kv_cols].contiguous().view(1, m, self.kv_heads, self.dim),
-                                   w["norm_k"], cos, sin, w["head_eps"])
+            # the head-norm kernel reads its column block of the fused product in place
+            C = native.ext()
+            native.count(2)
+            q, _ = C.head_norm_rope_fwd(qkv[:, :q_cols].view(1, m, self.heads, self.dim), w["norm_q"],
+                                        cos, sin, w["head_eps"])
+            k, _ = C.head_norm_rope_fwd(qkv[:, q_cols:q_cols + kv_cols].view(1, m, self.kv_heads, self.dim),
+                                        w["norm_k"], cos, sin, w["head_eps"])
             v = qkv[:, q_cols + kv_cols:].view(1, m, self.kv_heads, self.dim)  # copied into the cache as is
             t2 = self._mark("head norm + rope", t1)
             (mixed,) = attend(index, [q], [k], [v])

@@ -375,3 +375,17 @@ def test_silu_mul_pair():
     out = native.ext().silu_mul_pair(both)
     want = ops.silu_mul(both[:, :48].contiguous(), both[:, 48:].contiguous())
     assert torch.equal(out, want)
+
+
+def test_head_norm_rope_reads_a_column_block_in_place():
+    torch.manual_seed(0)
+    rows, heads = 70, 3
+    wide = torch.randn(rows, (heads + 2) * 128, device=DEV).bfloat16()
+    weight = (torch.rand(128, device=DEV) + 0.5).bfloat16()
+    cos = torch.randn(1, rows, 128, device=DEV).bfloat16()
+    sin = torch.randn(1, rows, 128, device=DEV).bfloat16()
+    block = wide[:, 128:128 + heads * 128].view(1, rows, heads, 128)
+    assert not block.is_contiguous()
+    out, _ = native.ext().head_norm_rope_fwd(block, weight, cos, sin, 1e-6)
+    want, _ = native.ext().head_norm_rope_fwd(block.contiguous(), weight, cos, sin, 1e-6)
+    assert out.is_contiguous() and torch.equal(out, want)
