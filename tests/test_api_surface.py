@@ -1,0 +1,113 @@
+"""Every public name of the ``wm`` package resolves through the alias, with the expected
+constructor arguments, so user code and resolved ``config.yaml`` targets keep working."""
+
+import importlib
+import inspect
+
+import pytest
+
+SURFACE = {
+    "wm.train": ["main"],
+    "wm.configs.compose": ["compose_config"],
+    "wm.configs.base": ["make_base_config"],
+    "wm.configs.experiments.cosmos3": ["parallel", "network", "lora", "conditioner", "gen_initialization",
+                                       "text_initialization", "optimizer", "loader", "cosmos3_base",
+                                       "GEOMETRY_AUGMENTATION", "LORA_TRAINABLE", "RELEASED_TRANSFORMER"],
+    "wm.infra.config": ["LazyCall", "LazyDict", "instantiate"],
+    "wm.infra.trainer": ["Trainer", "TrainingStepResult"],
+    "wm.infra.model": ["Model", "ContextParallelContext", "LifecycleCadence", "OptimizerBinding", "StepOutput",
+                       "TrainingClosure", "TrainingClosureSpec"],
+    "wm.infra.parallel": ["ParallelConfig", "ParallelNetwork", "ActivationCheckpointing", "ATTENTION_SAVE_OPS",
+                          "init_meshes", "parallelize_network"],
+    "wm.infra.distributed": ["init", "destroy_process_group", "get_rank", "get_world_size", "get_local_rank",
+                             "get_local_world_size", "is_rank0", "DistributedDataParallel", "wrap_ddp",
+                             "ddp_sync_grad"],
+    "wm.infra.batch_transport": ["fetch_batch", "prepare_batch"],
+    "wm.infra.nonfinite": ["synchronize_found_nonfinite"],
+    "wm.infra.rng_state": ["isolated_rng", "capture_distributed_rng_state", "restore_distributed_rng_state",
+                           "validate_distributed_rng_state"],
+    "wm.infra.checkpoint": ["DistributedCheckpointer", "LoadResult"],
+    "wm.infra.optim": ["FusedAdam", "LinearWarmup", "CosineDecay", "LinearWarmupCosineDecay"],
+    "wm.infra.callbacks": ["Callback", "CallbackGroup", "GradClip", "GradClipMonitor", "ScalarMetricCallback",
+                           "LoguruMetricSink", "MetricSink", "PeriodicSampleCallback", "ArtifactWriter",
+                           "ArtifactWriterGroup", "ImageVideoArtifactWriter", "WandbMetricSink",
+                           "WandbArtifactWriter"],
+    "wm.infra.io": ["atomic_put", "atomic_put_text", "encode_video", "encode_image", "join_path", "exists",
+                    "get", "get_text"],
+    "wm.infra.log": ["configure", "add_sink", "info", "warning", "exception", "complete"],
+    "wm.infra.utils": ["map_tensors", "to", "set_random_seed", "preserve_training_mode", "frozen_parameters",
+                       "prefetch"],
+    "wm.protocols": ["Condition", "Conditioner", "DenoisingNetwork", "BlockARNetwork", "HistoryWindow",
+                     "Discriminator"],
+    "wm.models.flow": ["FlowUniPC", "RectifiedFlowSchedule", "TrainDistribution", "UniformShift",
+                       "VelocityFunction", "invariant_randn", "rf_interpolate", "rf_x0", "sampling_seeds"],
+    "wm.models.diffusion": ["DiffusionModel"],
+    "wm.models.autoregressive": ["ARMode", "AutoregressiveModel", "corrupt_history"],
+    "wm.models.dmd": ["RCM_ENDPOINTS", "DMDModel", "GANConfig", "PhaseClock", "Regularization"],
+    "wm.models.exact_regularization": ["ExactPenalty", "exact_penalties", "check_exact_regularization"],
+    "wm.networks.cosmos3": ["Cosmos3Config", "Cosmos3Network", "Cosmos3TextEncoder", "Cosmos3Condition",
+                            "Cosmos3Conditioner", "build_network", "COSMOS3_EMPTY_PROMPT_IDS", "GEN_KEYS",
+                            "TEXT_ENCODER_KEYS", "LORA_ATTENTION_MODULES", "LORA_ATTENTION_MLP_MODULES"],
+    "wm.networks.cosmos3.streaming": ["Cosmos3Stream", "StreamPolicy", "StreamRoPE"],
+    "wm.networks.cosmos3.streaming_attention": ["StreamAttentionCache"],
+    "wm.networks.cosmos3.reference": ["denoise_with_references"],
+    "wm.networks.cosmos3.attention": ["TextContext", "sdpa", "FullAttention", "BlockCausalAttention", "KVCache",
+                                      "CachedAttention", "AnchorAttention"],
+    "wm.networks.cosmos3.context_parallel": ["ContextParallel", "ContextParallelAttention"],
+    "wm.networks.cosmos3.geometry": ["GeometryAugmentationConfig", "GeometryKind", "ModalitySelection",
+                                     "augment_geometry", "colorize_depth", "depth_scale", "downsample_geometry",
+                                     "prepare_normal", "stretch_geometry"],
+    "wm.networks.discriminator": ["DiscriminatorHead"],
+    "wm.networks.lora": ["LORA_PARAMETER_PATTERN", "LoRALinear", "inject_lora", "initialize_lora_parameters"],
+    "wm.kernels.gen_layer": ["project", "finish"],
+    "wm.kernels.stream_cache": ["relocate"],
+    "wm.kernels.attention_jvp": ["attention_jvp", "backend_for"],
+    "wm.codecs": ["Wan22VAECodec", "TAEW22SuperDecoder"],
+    "wm.codecs.taew22": ["TAEW22SuperStream"],
+    "wm.data.loader": ["StatefulDataLoader"],
+    "wm.data.video": ["ManifestVideoDataset", "SyntheticVideoDataset"],
+    "wm.inference.cosmos3": ["inspect_artifact", "load_artifact", "save_artifact", "Cosmos3Artifact",
+                             "Cosmos3ArtifactSpec", "WeightSource", "prompt_pixel_frames"],
+    "wm.inference.serving": ["prepare_serving", "release_serving"],
+}
+
+
+@pytest.mark.parametrize("module_name", sorted(SURFACE))
+def test_public_names_resolve(module_name):
+    module = importlib.import_module(module_name)
+    missing = [name for name in SURFACE[module_name] if not hasattr(module, name)]
+    assert not missing, f"{module_name} lacks {missing}"
+
+
+@pytest.mark.parametrize("name", ["bidirectional", "ar_teacher_forcing", "ar_diffusion_forcing", "dmd",
+                                  "dmd_gan", "dmd_gan_exact", "dmd_gan_lora"])
+def test_recipe_modules_build_configs(name):
+    module = importlib.import_module(f"wm.configs.experiments.cosmos3.{name}")
+    assert callable(module.build_config)
+
+
+def test_signatures_users_rely_on():
+    from wm.inference.serving import prepare_serving
+    from wm.models.autoregressive import AutoregressiveModel
+    from wm.models.diffusion import DiffusionModel
+    from wm.models.dmd import DMDModel
+    from wm.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+
+    def names(callable_):
+        return set(inspect.signature(callable_).parameters)
+
+    assert {"net", "conditioner", "schedule", "known_frames", "text_dropout", "trainable_patterns", "parallel",
+            "conditioner_parallel", "sampling", "validation_seed"} <= names(DiffusionModel.__init__)
+    assert {"net", "conditioner", "mode", "block_frames", "schedule", "text_dropout", "corrupt_clean_history",
+            "diffusion_forcing_clean_sigma"} <= names(AutoregressiveModel.__init__)
+    assert {"student", "real_score", "fake_score", "conditioner", "discriminator", "gan", "block_frames",
+            "rollout_endpoints", "score_shift", "real_score_guidance", "fake_score_updates_per_student",
+            "dmd_loss_scale", "history", "sampling", "seed"} <= names(DMDModel.__init__)
+    assert {"network", "policy", "initial_capacity_frames"} <= names(Cosmos3Stream.__init__)
+    assert {"block_frames", "sink_frames", "history_frames", "rope", "train_frames"} <= names(StreamPolicy)
+    assert {"network", "dynamic", "cuda_graphs", "inductor"} <= names(prepare_serving)
+    for method in ("reset", "start", "denoise", "commit", "validate_chunk", "update_text", "embed_chunk"):
+        assert callable(getattr(Cosmos3Stream, method))
+    assert isinstance(Cosmos3Stream.keys, property) and isinstance(Cosmos3Stream.values, property)
+    policy = StreamPolicy()
+    assert (policy.block_frames, policy.sink_frames, policy.history_frames, policy.train_frames) == (4, 5, 44, 61)
