@@ -23,13 +23,40 @@ __all__ = ["ManifestVideoDataset", "SyntheticLatentDataset", "SyntheticVideoData
 
 
 def _read_video(path: Path) -> torch.Tensor:
-    """All frames as uint8 ``[T, 3, H, W]``."""
+    """All frames as uint8 ``[T, 3, H, W]``.
+
+    ``.npy`` files hold the frames directly (``[T, H, W, 3]`` or ``[T, 3, H, W]`` uint8).
+    Encoded videos are decoded by torchcodec when it is installed, else by OpenCV.
+    """
+    if path.suffix == ".npy":
+        frames = torch.from_numpy(np.load(path))
+        if frames.dtype != torch.uint8 or frames.ndim != 4:
+            raise ValueError(f"{path}: expected uint8 frames [T, H, W, 3] or [T, 3, H, W]")
+        return frames if frames.shape[1] == 3 else frames.permute(0, 3, 1, 2).contiguous()
     try:
         from torchcodec.decoders import VideoDecoder
+    except ImportError:
+        VideoDecoder = None
+    if VideoDecoder is not None:
+        decoder = VideoDecoder(str(path))
+        return decoder.get_frames_in_range(0, len(decoder)).data
+    try:
+        import cv2
     except ImportError as error:
-        raise ImportError("reading manifest videos needs the torchcodec package") from error
-    decoder = VideoDecoder(str(path))
-    return decoder.get_frames_in_range(0, len(decoder)).data
+        raise ImportError("reading encoded videos needs torchcodec or opencv") from error
+    capture = cv2.VideoCapture(str(path))
+    frames = []
+    try:
+        while True:
+            ok, frame = capture.read()
+            if not ok:
+                break
+            frames.append(torch.from_numpy(cv2.cvtColor(frame, cv2.COLOR_BGR2RGB)))
+    finally:
+        capture.release()
+    if not frames:
+        raise ValueError(f"{path}: no frames could be decoded")
+    return torch.stack(frames).permute(0, 3, 1, 2).contiguous()
 
 
 class ManifestVideoDataset(Dataset):

@@ -188,3 +188,54 @@ def test_media_names_and_uint8_conversion():
     frames = video_batch_to_cpu_uint8(video, layout="BCTHW", float_range="minus_one_one")
     assert len(frames) == 2 and frames[0].dtype == torch.uint8
     assert int(frames[0].max()) == 0 and int(frames[1].min()) == 255
+
+
+def test_manifest_dataset_reads_validates_and_signs(tmp_path):
+    import json
+
+    from agentgarten_b200.data.video import ManifestVideoDataset
+
+    frames, height, width = 5, 8, 12
+    rng = np.random.default_rng(0)
+    rows = []
+    for index in range(2):
+        np.save(tmp_path / f"clip{index}.npy", rng.integers(0, 255, (frames, height, width, 3), dtype=np.uint8))
+        np.save(tmp_path / f"depth{index}.npy", rng.random((frames, height, width), dtype=np.float32) + 0.1)
+        np.save(tmp_path / f"normal{index}.npy", rng.standard_normal((frames, height, width, 3)).astype(np.float32))
+        rows.append({"video": f"clip{index}.npy", "depth": f"depth{index}.npy", "normal": f"normal{index}.npy",
+                     "caption": f"clip number {index}", "depth_scale": 2.0})
+    manifest = tmp_path / "train.jsonl"
+    manifest.write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    data = ManifestVideoDataset(str(manifest), num_frames=frames, height=height, width=width, fps=16.0)
+    assert len(data) == 2
+    item = data[1]
+    assert item["video"].shape == (frames, 3, height, width) and item["video"].dtype == torch.uint8
+    assert item["depth"].shape == (frames, 1, height, width) and item["normal"].shape == (frames, 3, height, width)
+    assert torch.allclose(item["normal"].norm(dim=1), torch.ones(frames, height, width), atol=1e-5)
+    assert item["caption"] == "clip number 1" and item["depth_scale"] == 2.0 and item["sample_id"] == 1
+    signature = data.resume_signature()
+    manifest.write_text(manifest.read_text() + json.dumps(rows[0]) + "\n")
+    assert ManifestVideoDataset(str(manifest), num_frames=frames, height=height, width=width).resume_signature() != signature
+    # wrong length and bad values are refused with the file name
+    with pytest.raises(ValueError, match="clip0.npy"):
+        ManifestVideoDataset(str(manifest), num_frames=frames + 4, height=height, width=width)[0]
+    bad = np.load(tmp_path / "depth0.npy"); bad[0, 0, 0] = -1.0
+    np.save(tmp_path / "depth0.npy", bad)
+    with pytest.raises(ValueError, match="non-negative"):
+        data[0]
+
+
+def test_encoded_video_is_decoded_by_the_available_backend(tmp_path):
+    cv2 = pytest.importorskip("cv2")
+    from agentgarten_b200.data.video import _read_video
+
+    path = tmp_path / "clip.avi"
+    writer = cv2.VideoWriter(str(path), cv2.VideoWriter_fourcc(*"MJPG"), 16.0, (16, 8))
+    if not writer.isOpened():
+        pytest.skip("no video encoder in this OpenCV build")
+    for value in (0, 120, 250):
+        writer.write(np.full((8, 16, 3), value, dtype=np.uint8))
+    writer.release()
+    frames = _read_video(path)
+    assert frames.shape == (3, 3, 8, 16) and frames.dtype == torch.uint8
+    assert abs(int(frames[1].float().mean()) - 120) < 6
