@@ -78,11 +78,39 @@ def encode_image(pixels: np.ndarray, *, file_format: str, **options: Any) -> Byt
     return buffer
 
 
+def _encode_with_opencv(pixels: np.ndarray, fps: int) -> bytes | None:
+    """mp4 bytes written by OpenCV into a scratch file, or ``None`` when that is not possible."""
+    try:
+        import cv2
+    except ImportError:
+        return None
+    import tempfile
+
+    height, width = int(pixels.shape[1]), int(pixels.shape[2])
+    with tempfile.TemporaryDirectory() as scratch:
+        target = os.path.join(scratch, "clip.mp4")
+        writer = cv2.VideoWriter(target, cv2.VideoWriter_fourcc(*"mp4v"), float(max(fps, 1)), (width, height))
+        if not writer.isOpened():
+            return None
+        try:
+            for frame in pixels:
+                writer.write(cv2.cvtColor(np.ascontiguousarray(frame), cv2.COLOR_RGB2BGR))
+        finally:
+            writer.release()
+        try:
+            with open(target, "rb") as handle:
+                data = handle.read()
+        except OSError:
+            return None
+    return data or None
+
+
 def encode_video(pixels: np.ndarray, *, fps: int, quality: int = 8) -> BytesIO:
     """Encode ``[T, H, W, 3]`` uint8 frames.
 
-    mp4 needs ``imageio`` with the ffmpeg plugin; when it is missing the frames are
-    stored as an animated GIF through Pillow so sampling never kills training.
+    mp4 through ``imageio`` with the ffmpeg plugin, else through OpenCV's ``mp4v`` encoder;
+    with neither, the frames are stored as an animated GIF through Pillow so that sampling
+    never kills training.
     """
     buffer = BytesIO()
     try:
@@ -92,6 +120,9 @@ def encode_video(pixels: np.ndarray, *, fps: int, quality: int = 8) -> BytesIO:
             for frame in pixels:
                 writer.append_data(frame)
     except ImportError:
+        encoded = _encode_with_opencv(pixels, fps)
+        if encoded is not None:
+            return BytesIO(encoded)
         from PIL import Image
 
         frames = [Image.fromarray(np.ascontiguousarray(f)) for f in pixels]
