@@ -389,3 +389,21 @@ def test_head_norm_rope_reads_a_column_block_in_place():
     out, _ = native.ext().head_norm_rope_fwd(block, weight, cos, sin, 1e-6)
     want, _ = native.ext().head_norm_rope_fwd(block.contiguous(), weight, cos, sin, 1e-6)
     assert out.is_contiguous() and torch.equal(out, want)
+
+
+@pytest.mark.parametrize("hq,hkv", [(3, 3), (6, 2), (2, 1)])
+def test_attention_forward_backward_with_odd_and_even_head_groups(hq, hkv):
+    """An odd number of query heads per KV head runs one head per forward CTA, an even one two."""
+    torch.manual_seed(hq * 10 + hkv)
+    q = torch.randn(2, 200, hq, 128, device=DEV).bfloat16().requires_grad_()
+    k = torch.randn(2, 330, hkv, 128, device=DEV).bfloat16().requires_grad_()
+    v = torch.randn(2, 330, hkv, 128, device=DEV).bfloat16().requires_grad_()
+    out = ops.attention(q, k, v)
+    grad = torch.randn_like(out)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), grad)
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    want = reference.attention(qf, kf, vf, None)
+    wq, wk, wv = torch.autograd.grad(want, (qf, kf, vf), grad.float())
+    assert _rel(out, want) < 1e-2
+    assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
+    _status_ok()
