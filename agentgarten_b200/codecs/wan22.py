@@ -28,6 +28,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from agentgarten_b200.ops.conv import conv_frames, conv_volume
 from agentgarten_b200.utils import log
 from agentgarten_b200.utils.misc import prefetch
 
@@ -110,10 +111,12 @@ class CausalConv3d(nn.Conv3d):
                          padding=(0, pad_h, pad_w))
         self.context = 2 * pad_t
 
-    def forward(self, x: torch.Tensor, state: CausalState | None = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, state: CausalState | None = None,
+                residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``residual`` is added to the result (inside the kernel when that runs)."""
         need = self.context
         if need == 0:
-            return super().forward(x)
+            return conv_volume(self, x, residual)
         previous = state.history.get(self) if state is not None else None
         pieces = [x] if previous is None else [previous, x]
         have = 0 if previous is None else previous.shape[2]
@@ -123,11 +126,11 @@ class CausalConv3d(nn.Conv3d):
         if state is not None:
             keep = min(_HISTORY, have + x.shape[2])
             state.history[self] = joined[:, :, -keep:].clone()
-        return super().forward(joined)
+        return conv_volume(self, joined, residual)
 
     def plain(self, x: torch.Tensor) -> torch.Tensor:
         """The bare convolution, for callers that assemble the temporal context themselves."""
-        return super().forward(x)
+        return conv_volume(self, x)
 
 
 class ChannelRMSNorm(nn.Module):
@@ -174,8 +177,7 @@ class ResidualBlock(nn.Module):
     def forward(self, x: torch.Tensor, state: CausalState | None = None) -> torch.Tensor:
         r = self.residual
         h = r[2](r[0](x, silu=True), state)
-        h = r[6](r[5](r[3](h, silu=True)), state)
-        return h + self.shortcut(x)
+        return r[6](r[5](r[3](h, silu=True)), state, residual=self.shortcut(x))
 
 
 class FrameAttention(nn.Module):
@@ -191,10 +193,10 @@ class FrameAttention(nn.Module):
     def forward(self, x: torch.Tensor, state: CausalState | None = None) -> torch.Tensor:
         b, c, t, h, w = x.shape
         frames = x.transpose(1, 2).reshape(b * t, c, h, w)
-        qkv = self.to_qkv(self.norm(frames)).reshape(b * t, 3, c, h * w).transpose(2, 3)
+        qkv = conv_frames(self.to_qkv, self.norm(frames)).reshape(b * t, 3, c, h * w).transpose(2, 3)
         mixed = F.scaled_dot_product_attention(qkv[:, 0:1], qkv[:, 1:2], qkv[:, 2:3])
         mixed = mixed.squeeze(1).transpose(1, 2).reshape(b * t, c, h, w)
-        out = self.proj(mixed).reshape(b, t, c, h, w).transpose(1, 2)
+        out = conv_frames(self.proj, mixed).reshape(b, t, c, h, w).transpose(1, 2)
         return x + out
 
 
@@ -232,7 +234,7 @@ class Resample(nn.Module):
 
     def _frames(self, x: torch.Tensor) -> torch.Tensor:
         b, c, t, h, w = x.shape
-        y = self.resample(x.transpose(1, 2).reshape(b * t, c, h, w))
+        y = conv_frames(self.resample[1], self.resample[0](x.transpose(1, 2).reshape(b * t, c, h, w)))
         return y.reshape(b, t, *y.shape[1:]).transpose(1, 2)
 
     def forward(self, x: torch.Tensor, state: CausalState | None = None) -> torch.Tensor:

@@ -200,6 +200,26 @@ cudaError_t relocate_rows(const void* src, void* dst, const float* cosv, const f
 cudaError_t channel_norm(const void* x, const float* gamma, void* out, int64_t pixels, int channels,
                          int silu, cudaStream_t stream);
 
+// ------------------------------------------------------------------ convolution (codecs)
+// Stride-1 convolution of a channels-last bf16 volume on the tensor cores, as an implicit
+// GEMM: x [B, Tin, H, W, Cin], weight [Cout, kt * kh * kw, Cin] (taps in (t, h, w) order),
+// out [B, Tout, H, W, Cout] with Tout = Tin - kt + 1.  Space is zero-padded by (pad_h, pad_w)
+// on both sides (kh = 2 * pad_h + 1, kw = 2 * pad_w + 1); time is not padded: the caller
+// prepends the frames (or zeros) a causal convolution looks back at.
+//   out = conv(x, weight) + bias + residual      (bias bf16 [Cout], residual like out; both optional)
+// Cin and Cout are multiples of 8.
+struct ConvArgs {
+  const void* x;
+  const void* weight;
+  const void* bias;
+  const void* residual;
+  void* out;
+  int batch, frames_in, height, width, cin, cout;
+  int kt, kh, kw;
+  int* status;
+};
+cudaError_t conv3d_bf16(const ConvArgs& args, int sm_count, cudaStream_t stream);
+
 // ----------------------------------------------------------- sharded optimizer (ZeRO)
 // Base pointers of the same flat buffer on every rank of the node (index = rank).
 struct ZeroPeers {

@@ -287,6 +287,42 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   return {dq, dk, dv};
 }
 
+// Stride-1 convolution of a channels-last volume: x [B, Tin, H, W, Cin], weight
+// [Cout, kt * kh * kw, Cin] -> [B, Tin - kt + 1, H, W, Cout] (+ bias [Cout], + residual like out).
+Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
+              c10::optional<Tensor> residual, int64_t kt, int64_t kh, int64_t kw) {
+  check_bf16(x, "x");
+  check_bf16(weight, "weight");
+  TORCH_CHECK(x.dim() == 5 && x.is_contiguous(), "conv3d: x is contiguous [B, T, H, W, Cin]");
+  TORCH_CHECK(weight.dim() == 3 && weight.is_contiguous() && weight.size(1) == kt * kh * kw &&
+                  weight.size(2) == x.size(4), "conv3d: weight is contiguous [Cout, taps, Cin]");
+  TORCH_CHECK(x.size(1) >= kt, "conv3d: fewer frames than the kernel is deep");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t frames_out = x.size(1) - kt + 1;
+  Tensor out = torch::empty({x.size(0), frames_out, x.size(2), x.size(3), weight.size(0)}, x.options());
+  agb::ConvArgs a{};
+  a.x = x.data_ptr();
+  a.weight = weight.data_ptr();
+  a.out = out.data_ptr();
+  if (bias.has_value()) {
+    check_bf16(*bias, "bias");
+    TORCH_CHECK(bias->numel() == weight.size(0) && bias->is_contiguous(), "conv3d: bias is [Cout]");
+    a.bias = bias->data_ptr();
+  }
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    TORCH_CHECK(residual->sizes() == out.sizes() && residual->is_contiguous(),
+                "conv3d: residual has the shape of the result, contiguous");
+    a.residual = residual->data_ptr();
+  }
+  a.batch = int(x.size(0)); a.frames_in = int(x.size(1)); a.height = int(x.size(2));
+  a.width = int(x.size(3)); a.cin = int(x.size(4)); a.cout = int(weight.size(0));
+  a.kt = int(kt); a.kh = int(kh); a.kw = int(kw);
+  a.status = status_word(x.device().index()).data_ptr<int>();
+  check(agb::conv3d_bf16(a, sm_count(x.device().index()), stream_of(x)), "conv3d");
+  return out;
+}
+
 // Channel RMS norm (+ SiLU) of a channels-last activation; x is [..., C] with C contiguous.
 Tensor channel_norm(const Tensor& x, const Tensor& gamma, bool silu) {
   check_bf16(x, "x");
@@ -524,6 +560,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);
   m.def("channel_norm", &channel_norm);
+  m.def("conv3d", &conv3d);
   m.def("attn_jvp", &attn_jvp);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_reduce_norm", &tp_reduce_norm);

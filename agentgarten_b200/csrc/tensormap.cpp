@@ -47,10 +47,11 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const ui
     cudaFree(nullptr);
     bound = true;
   }
-  cuuint64_t gdims[3];
-  cuuint64_t gstrides[2];
-  cuuint32_t gbox[3];
-  cuuint32_t estrides[3] = {1, 1, 1};
+  if (rank < 1 || rank > 5) return false;
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5];
+  cuuint32_t estrides[5] = {1, 1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) {
     gdims[i] = dims[i];
     gbox[i] = box[i];

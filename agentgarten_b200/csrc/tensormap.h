@@ -8,7 +8,7 @@
 
 namespace agb {
 
-// Encodes a bf16 tensor of up to 3 dimensions for tiled loads with 128-byte swizzle.
+// Encodes a bf16 tensor of up to 5 dimensions for tiled loads with 128-byte swizzle.
 //   dims[0] is the contiguous dimension; strides_bytes[i] is the byte stride of dims[i+1]
 //   (multiples of 16); box[0] * 2 bytes must be 128 (one swizzle span).
 // Out-of-range parts of a box read as zero.  Returns false when the driver refuses.

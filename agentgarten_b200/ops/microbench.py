@@ -1,6 +1,6 @@
 """Per-kernel timings against the measured roofline.
 
-``python -m agentgarten_b200.ops.microbench [--op gemm attention ...] [--tokens N] [--json]``
+``python -m agentgarten_b200.ops.microbench [--op conv gemm attention ...] [--tokens N] [--json]``
 
 Each case is timed with CUDA events on the launching stream after three warm-up launches;
 between timed launches a 256 MB buffer is rewritten so nothing is served from the 126 MB
@@ -120,7 +120,24 @@ def bench_pointwise(tokens: int, launches: int) -> list[dict]:
     return out
 
 
-CASES = {"gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
+def bench_conv(tokens: int, launches: int) -> list[dict]:
+    """3x3x3 convolutions at the shapes of the Wan 2.2 decoder levels, against cuDNN on the same input."""
+    out = []
+    for channels, frames, height, width in ((256, 4, 240, 416), (512, 4, 120, 208), (1024, 2, 60, 104)):
+        x = torch.randn(1, frames + 2, height, width, channels, device="cuda", dtype=torch.bfloat16)
+        weight = torch.randn(channels, channels, 3, 3, 3, device="cuda", dtype=torch.bfloat16) * 0.01
+        packed = weight.permute(0, 2, 3, 4, 1).reshape(channels, 27, channels).contiguous()
+        ms = _time(lambda: native.ext().conv3d(x, packed, None, None, 3, 3, 3), launches)
+        logical = x.permute(0, 4, 1, 2, 3)
+        cl_weight = weight.contiguous(memory_format=torch.channels_last_3d)
+        library = _time(lambda: torch.nn.functional.conv3d(logical, cl_weight, padding=(0, 1, 1)), launches)
+        flops = 2.0 * frames * height * width * 27 * channels * channels
+        out.append({"kernel": "conv3d_kernel", "case": f"{channels} ch, {frames} frames {height}x{width}, 3x3x3",
+                    "ms": ms, "tflops": flops / ms / 1e9, "cudnn_ms": library})
+    return out
+
+
+CASES = {"conv": bench_conv, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
 
 
 def main(argv=None) -> int:
@@ -146,8 +163,9 @@ def main(argv=None) -> int:
     else:
         for row in rows:
             rate = f"{row['tflops']:8.1f} TFLOP/s" if "tflops" in row else f"{row['gbs']:8.1f} GB/s   "
+            extra = f"  (cuDNN {row['cudnn_ms']:.3f} ms)" if "cudnn_ms" in row else ""
             print(f"{row['kernel']:34s} {row['case']:46s} {row['ms']:8.3f} ms {rate} "
-                  f"{row.get('fraction', 0):5.2f} {row['of']}")
+                  f"{row.get('fraction', 0):5.2f} {row['of']}{extra}")
     return 0
 
 

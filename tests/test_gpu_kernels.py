@@ -350,6 +350,57 @@ def test_channel_norm_kernel(channels, silu):
     _status_ok()
 
 
+@pytest.mark.parametrize("cin,cout,kernel,frames,height,width,extras", [
+    (64, 64, (3, 3, 3), 5, 16, 24, False),
+    (160, 320, (3, 3, 3), 4, 30, 52, True),     # ragged channel block, two column tiles, ragged patches
+    (32, 48, (1, 3, 3), 3, 8, 8, True),         # frames smaller than a patch
+    (96, 200, (1, 1, 1), 2, 9, 130, False),     # pointwise; output channels padded to the tile
+    (64, 128, (3, 1, 1), 6, 12, 20, True),      # temporal kernel only
+    (256, 256, (3, 3, 3), 3, 24, 40, True),
+])
+def test_conv_kernel_matches_fp32_convolution(cin, cout, kernel, frames, height, width, extras):
+    torch.manual_seed(cin + cout)
+    kt, kh, kw = kernel
+    x = torch.randn(2, frames, height, width, cin, device=DEV).bfloat16()
+    weight = (torch.randn(cout, cin, kt, kh, kw, device=DEV) / (cin * kt * kh * kw) ** 0.5).bfloat16()
+    bias = torch.randn(cout, device=DEV).bfloat16() if extras else None
+    packed = weight.permute(0, 2, 3, 4, 1).reshape(cout, -1, cin).contiguous()
+    residual = torch.randn(2, frames - kt + 1, height, width, cout, device=DEV).bfloat16() if extras else None
+    out = native.ext().conv3d(x, packed, bias, residual, kt, kh, kw)
+    _status_ok()
+    want = torch.nn.functional.conv3d(x.float().permute(0, 4, 1, 2, 3), weight.float(),
+                                      None if bias is None else bias.float(), padding=(0, kh // 2, kw // 2))
+    want = want.permute(0, 2, 3, 4, 1)
+    if residual is not None:
+        want = want + residual.float()
+    assert out.shape == want.shape
+    assert _rel(out, want) < 6e-3, _rel(out, want)
+    assert (out.float() - want).abs().max() < 0.06
+
+
+def test_conv_modules_use_the_kernel_and_match():
+    from agentgarten_b200.ops.conv import conv_frames, conv_volume
+
+    torch.manual_seed(5)
+    conv = torch.nn.Conv3d(64, 96, 3, padding=(0, 1, 1)).to(DEV, torch.bfloat16)
+    x = torch.randn(1, 64, 5, 20, 28, device=DEV).bfloat16().contiguous(memory_format=torch.channels_last_3d)
+    residual = torch.randn(1, 96, 3, 20, 28, device=DEV).bfloat16()
+    before = native.launches()
+    with torch.no_grad():
+        got = conv_volume(conv, x, residual)
+        want = conv(x).float() + residual.float()
+    assert native.launches() == before + 1
+    assert got.shape == want.shape and _rel(got, want) < 1e-2
+    frames = torch.nn.Conv2d(32, 32, 3, padding=1).to(DEV, torch.bfloat16)
+    y = torch.randn(3, 32, 18, 22, device=DEV).bfloat16()
+    with torch.no_grad():
+        assert _rel(conv_frames(frames, y), frames(y).float()) < 1e-2
+    # a convolution that wants gradients stays on the differentiable path
+    z = conv_volume(conv, x)
+    assert z.requires_grad
+    _status_ok()
+
+
 def test_vae_on_gpu_matches_cpu_fp32():
     from agentgarten_b200.codecs.wan22 import random_vae, to_channels_last
 
