@@ -82,9 +82,10 @@ def build_training_job(device: torch.device | str, *, layers: int = 36, hidden: 
                        vocab: int = 151936, frames: int = 21, latent_hw: tuple[int, int] = (30, 52),
                        text_tokens: int = 512, text_layers: int | None = None, lr: float = 3e-5,
                        seed: int = 0, fully_shard: bool = True,
-                       recipe: str = "bidirectional") -> TrainingJob:
+                       recipe: str = "bidirectional", context_parallel: int = 1) -> TrainingJob:
     """``recipe``: ``bidirectional`` (rectified flow on the whole clip), ``ar_diffusion_forcing``
-    or ``ar_teacher_forcing`` (block-causal, blocks of 4 latent frames after the anchor)."""
+    or ``ar_teacher_forcing`` (block-causal, blocks of 4 latent frames after the anchor).
+    ``context_parallel`` ranks share one clip (Ulysses sharding of the generation tower)."""
     device = torch.device(device)
     config = Cosmos3Config(hidden_size=hidden, intermediate_size=intermediate,
                            num_hidden_layers=layers, num_attention_heads=heads,
@@ -96,6 +97,7 @@ def build_training_job(device: torch.device | str, *, layers: int = 36, hidden: 
     conditioner = Cosmos3Conditioner(config=text_config, codec=None, init_device="meta",
                                      geometry_noise_sigma=0.0)
     parallel = ParallelConfig(parameter_dtype="bfloat16", fully_shard=fully_shard,
+                              context_parallel_size=context_parallel,
                               activation_checkpointing="selective", compile=False)
     frozen = ParallelConfig(parameter_dtype="bfloat16", fully_shard=fully_shard,
                             activation_checkpointing="none", compile=False)

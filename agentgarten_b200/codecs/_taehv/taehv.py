@@ -22,6 +22,8 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from agentgarten_b200.ops.conv import conv_frames, depthwise_frames
+
 __all__ = ["TAEHV", "StreamingTAEHV", "TemporalState", "run_stack"]
 
 # name fragment -> (pixel patch, latent channels, encoder time halvings, decoder time doublings)
@@ -33,8 +35,15 @@ _ARCHITECTURES = {
 }
 
 
+class FrameConv(nn.Conv2d):
+    """A frame convolution that runs in the tensor-core kernel when its input allows."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return conv_frames(self, x)
+
+
 def _conv3(n_in: int, n_out: int, **kwargs) -> nn.Conv2d:
-    return nn.Conv2d(n_in, n_out, 3, padding=1, **kwargs)
+    return FrameConv(n_in, n_out, 3, padding=1, **kwargs)
 
 
 class Clamp(nn.Module):
@@ -53,7 +62,12 @@ class MemBlock(nn.Module):
         self.act = nn.ReLU(inplace=True)
 
     def forward(self, x: torch.Tensor, past: torch.Tensor) -> torch.Tensor:
-        return self.act(self.conv(torch.cat([x, past], 1)) + self.skip(x))
+        # Slots 1 and 3 of ``conv`` and ``act`` are the ReLUs applied inside the convolutions here.
+        conv = self.conv
+        skip = x if isinstance(self.skip, nn.Identity) else conv_frames(self.skip, x)
+        h = conv_frames(conv[0], torch.cat([x, past], 1), relu=True)
+        h = conv_frames(conv[2], h, relu=True)
+        return conv_frames(conv[4], h, residual=skip, relu=True)
 
 
 class SuperMemBlock(nn.Module):
@@ -67,7 +81,10 @@ class SuperMemBlock(nn.Module):
             nn.Conv2d(n_f * 4, n_f, 1, bias=False))
 
     def forward(self, x: torch.Tensor, past: torch.Tensor) -> torch.Tensor:
-        return self.conv(torch.cat([x, past], 1)) + x
+        conv = self.conv
+        h = depthwise_frames(conv[0], torch.cat([x, past], 1))
+        h = conv_frames(conv[1], h, relu=True)
+        return conv_frames(conv[3], h, residual=x)
 
 
 class TPool(nn.Module):
@@ -80,7 +97,7 @@ class TPool(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         _, c, h, w = x.shape
-        return self.conv(x.reshape(-1, self.stride * c, h, w))
+        return conv_frames(self.conv, x.reshape(-1, self.stride * c, h, w))
 
 
 class TGrow(nn.Module):
@@ -93,7 +110,7 @@ class TGrow(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         _, c, h, w = x.shape
-        return self.conv(x).reshape(-1, c, h, w)
+        return conv_frames(self.conv, x).reshape(-1, c, h, w)
 
 
 class TemporalState:
@@ -188,7 +205,7 @@ class TAEHV(nn.Module):
         decoder: list[nn.Module]
         if "_super" in self.arch_name:
             widths = (512, 256, 128, 64)
-            decoder = [nn.Conv2d(self.latent_channels, widths[0], 1, bias=False)]
+            decoder = [FrameConv(self.latent_channels, widths[0], 1, bias=False)]
             for level in range(3):
                 grow = 2 if s_up[level] else 1
                 decoder += [*_stage("super", widths[level]),

@@ -206,8 +206,9 @@ cudaError_t channel_norm(const void* x, const float* gamma, void* out, int64_t p
 // out [B, Tout, H, W, Cout] with Tout = Tin - kt + 1.  Space is zero-padded by (pad_h, pad_w)
 // on both sides (kh = 2 * pad_h + 1, kw = 2 * pad_w + 1); time is not padded: the caller
 // prepends the frames (or zeros) a causal convolution looks back at.
-//   out = conv(x, weight) + bias + residual      (bias bf16 [Cout], residual like out; both optional)
-// Cin and Cout are multiples of 8.
+//   out = act(conv(x, weight) + bias + residual)   (bias [Cout], residual like out; both optional;
+//                                                   act = ReLU when relu != 0, else identity)
+// Cin and Cout are multiples of 8.  fp16 != 0: every tensor is fp16 instead of bf16.
 struct ConvArgs {
   const void* x;
   const void* weight;
@@ -216,9 +217,23 @@ struct ConvArgs {
   void* out;
   int batch, frames_in, height, width, cin, cout;
   int kt, kh, kw;
+  int relu, fp16;
   int* status;
 };
 cudaError_t conv3d_bf16(const ConvArgs& args, int sm_count, cudaStream_t stream);
+
+// Depthwise k x k convolution (k = 3, 5 or 7; stride 1, zero padding k / 2) of channels-last
+// frames: x, out [frames, H, W, C], weight [k * k, C], bias [C] or null; C a multiple of 8;
+// bf16, or fp16 when fp16 != 0.
+struct DepthwiseArgs {
+  const void* x;
+  const void* weight;
+  const void* bias;
+  void* out;
+  int frames, height, width, channels, kernel;
+  int fp16;
+};
+cudaError_t depthwise_conv(const DepthwiseArgs& args, cudaStream_t stream);
 
 // ----------------------------------------------------------- sharded optimizer (ZeRO)
 // Base pointers of the same flat buffer on every rank of the node (index = rank).

@@ -288,11 +288,17 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
 }
 
 // Stride-1 convolution of a channels-last volume: x [B, Tin, H, W, Cin], weight
-// [Cout, kt * kh * kw, Cin] -> [B, Tin - kt + 1, H, W, Cout] (+ bias [Cout], + residual like out).
+// [Cout, kt * kh * kw, Cin] -> [B, Tin - kt + 1, H, W, Cout] (+ bias [Cout], + residual like out,
+// then ReLU when asked); bf16 or fp16 throughout.
 Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
-              c10::optional<Tensor> residual, int64_t kt, int64_t kh, int64_t kw) {
-  check_bf16(x, "x");
-  check_bf16(weight, "weight");
+              c10::optional<Tensor> residual, int64_t kt, int64_t kh, int64_t kw, bool relu) {
+  const auto dtype = x.scalar_type();
+  TORCH_CHECK(x.is_cuda() && (dtype == torch::kBFloat16 || dtype == torch::kFloat16),
+              "conv3d: x is a bf16 or fp16 CUDA tensor");
+  auto same = [&](const Tensor& t, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == dtype, "conv3d: ", name, " has the dtype of x");
+  };
+  same(weight, "weight");
   TORCH_CHECK(x.dim() == 5 && x.is_contiguous(), "conv3d: x is contiguous [B, T, H, W, Cin]");
   TORCH_CHECK(weight.dim() == 3 && weight.is_contiguous() && weight.size(1) == kt * kh * kw &&
                   weight.size(2) == x.size(4), "conv3d: weight is contiguous [Cout, taps, Cin]");
@@ -305,12 +311,12 @@ Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
   a.weight = weight.data_ptr();
   a.out = out.data_ptr();
   if (bias.has_value()) {
-    check_bf16(*bias, "bias");
+    same(*bias, "bias");
     TORCH_CHECK(bias->numel() == weight.size(0) && bias->is_contiguous(), "conv3d: bias is [Cout]");
     a.bias = bias->data_ptr();
   }
   if (residual.has_value()) {
-    check_bf16(*residual, "residual");
+    same(*residual, "residual");
     TORCH_CHECK(residual->sizes() == out.sizes() && residual->is_contiguous(),
                 "conv3d: residual has the shape of the result, contiguous");
     a.residual = residual->data_ptr();
@@ -318,8 +324,36 @@ Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
   a.batch = int(x.size(0)); a.frames_in = int(x.size(1)); a.height = int(x.size(2));
   a.width = int(x.size(3)); a.cin = int(x.size(4)); a.cout = int(weight.size(0));
   a.kt = int(kt); a.kh = int(kh); a.kw = int(kw);
+  a.relu = relu ? 1 : 0;
+  a.fp16 = dtype == torch::kFloat16 ? 1 : 0;
   a.status = status_word(x.device().index()).data_ptr<int>();
   check(agb::conv3d_bf16(a, sm_count(x.device().index()), stream_of(x)), "conv3d");
+  return out;
+}
+
+// Depthwise k x k convolution of channels-last frames: x [N, H, W, C], weight [k * k, C].
+Tensor depthwise(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias, int64_t kernel) {
+  const auto dtype = x.scalar_type();
+  TORCH_CHECK(x.is_cuda() && (dtype == torch::kBFloat16 || dtype == torch::kFloat16) && x.dim() == 4 &&
+                  x.is_contiguous(), "depthwise: x is a contiguous bf16 or fp16 CUDA tensor [N, H, W, C]");
+  TORCH_CHECK(weight.is_cuda() && weight.scalar_type() == dtype && weight.is_contiguous() &&
+                  weight.dim() == 2 && weight.size(0) == kernel * kernel && weight.size(1) == x.size(3),
+              "depthwise: weight is [k * k, C] in the dtype of x");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  agb::DepthwiseArgs a{};
+  a.x = x.data_ptr();
+  a.weight = weight.data_ptr();
+  a.out = out.data_ptr();
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->is_cuda() && bias->scalar_type() == dtype && bias->is_contiguous() &&
+                    bias->numel() == x.size(3), "depthwise: bias is [C] in the dtype of x");
+    a.bias = bias->data_ptr();
+  }
+  a.frames = int(x.size(0)); a.height = int(x.size(1)); a.width = int(x.size(2));
+  a.channels = int(x.size(3)); a.kernel = int(kernel);
+  a.fp16 = dtype == torch::kFloat16 ? 1 : 0;
+  check(agb::depthwise_conv(a, stream_of(x)), "depthwise");
   return out;
 }
 
@@ -561,6 +595,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("zero_adam", &zero_adam);
   m.def("channel_norm", &channel_norm);
   m.def("conv3d", &conv3d);
+  m.def("depthwise", &depthwise);
   m.def("attn_jvp", &attn_jvp);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_reduce_norm", &tp_reduce_norm);

@@ -1,4 +1,4 @@
-// Stride-1 convolution of channels-last bf16 volumes as an implicit GEMM on tcgen05.
+// Stride-1 convolution of channels-last 16-bit float volumes as an implicit GEMM on tcgen05.
 //
 // The GEMM view: rows = output positions, columns = output channels, K = taps x input
 // channels.  A row tile is a TH x TW patch of one output frame (TH * TW = 128).  For every tap
@@ -10,12 +10,15 @@
 // feed the same pipeline as the dense GEMM of this library:
 //   warp 4 (one lane)  TMA producer -> 4-stage ring
 //   warp 5 (one lane)  tcgen05.mma into one of two TMEM accumulators
-//   warps 0-3          epilogue: TMEM -> registers -> + bias + residual -> bf16 channels-last
+//   warps 0-3          epilogue: TMEM -> registers -> + bias + residual (-> ReLU) -> channels-last
+// Operands and result are bf16 or fp16 (one type per call); accumulation is fp32.
 // Persistent, one CTA per SM.  The innermost TMA coordinate is always a multiple of 64
 // channels (128 bytes).
 #include "agb.h"
 #include "sm100.cuh"
 #include "tensormap.h"
+
+#include <cuda_fp16.h>
 
 namespace agb {
 namespace {
@@ -30,9 +33,10 @@ constexpr int NUM_THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 struct Params {
-  __nv_bfloat16* out;
-  const __nv_bfloat16* bias;
-  const __nv_bfloat16* residual;
+  uint16_t* out;             // bf16 or fp16, like the operands
+  const uint16_t* bias;
+  const uint16_t* residual;
+  int relu;
   int batch, frames_out, height, width, cin, cout;
   int kt, kh, kw, pad_h, pad_w;
   int tile_w, tile_w_shift;  // patch width (a power of two) and its log2; patch height = 128 / width
@@ -41,6 +45,21 @@ struct Params {
   uint32_t idesc;
   int* status;
 };
+
+// Two 16-bit floats of the activation type <-> two fp32 values.
+template <bool HALF>
+__device__ __forceinline__ float2 unpack2(uint32_t w) {
+  if (HALF) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return make_float2(bf16_lo(w), bf16_hi(w));
+}
+template <bool HALF>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (HALF) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  return pack_bf16(lo, hi);
+}
 
 struct TileAt {
   int b, t, h0, w0, n0;
@@ -59,6 +78,7 @@ __device__ __forceinline__ TileAt decode(int tile, const Params& p) {
   return at;
 }
 
+template <bool HALF>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
               const Params p) {
@@ -205,8 +225,8 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const int h = at.h0 + hi, w = at.w0 + wi;
       const bool row_ok = h < p.height && w < p.width;
       const int64_t position = ((int64_t(at.b) * p.frames_out + at.t) * p.height + h) * p.width + w;
-      __nv_bfloat16* out_row = p.out + position * p.cout;
-      const __nv_bfloat16* res_row = p.residual ? p.residual + position * p.cout : nullptr;
+      uint16_t* out_row = p.out + position * p.cout;
+      const uint16_t* res_row = p.residual ? p.residual + position * p.cout : nullptr;
       const uint32_t t_row = tmem_base + (uint32_t(warp * 32) << 16) + acc * MAX_BN;
 #pragma unroll 1
       for (int c = 0; c < p.bn / 32; ++c) {
@@ -228,8 +248,9 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                v[2 * i] += bf16_lo(bw[i]);
-                v[2 * i + 1] += bf16_hi(bw[i]);
+                const float2 f = unpack2<HALF>(bw[i]);
+                v[2 * i] += f.x;
+                v[2 * i + 1] += f.y;
               }
             }
             if (res_row) {
@@ -237,13 +258,18 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
-                v[2 * i] += bf16_lo(bw[i]);
-                v[2 * i + 1] += bf16_hi(bw[i]);
+                const float2 f = unpack2<HALF>(bw[i]);
+                v[2 * i] += f.x;
+                v[2 * i + 1] += f.y;
               }
             }
+            if (p.relu) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = fmaxf(v[i], 0.0f);
+            }
             *reinterpret_cast<uint4*>(out_row + col) =
-                make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
-                           pack_bf16(v[6], v[7]));
+                make_uint4(pack2<HALF>(v[0], v[1]), pack2<HALF>(v[2], v[3]), pack2<HALF>(v[4], v[5]),
+                           pack2<HALF>(v[6], v[7]));
           }
         }
       }
@@ -329,9 +355,10 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
     if (!make_tensor_map_bf16(&tw, g.weight, 3, dims, strides, box)) return cudaErrorInvalidValue;
   }
 
-  p.out = static_cast<__nv_bfloat16*>(g.out);
-  p.bias = static_cast<const __nv_bfloat16*>(g.bias);
-  p.residual = static_cast<const __nv_bfloat16*>(g.residual);
+  p.out = static_cast<uint16_t*>(g.out);
+  p.bias = static_cast<const uint16_t*>(g.bias);
+  p.residual = static_cast<const uint16_t*>(g.residual);
+  p.relu = g.relu;
   p.batch = g.batch;
   p.frames_out = frames_out;
   p.height = g.height;
@@ -343,13 +370,17 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
   p.kw = g.kw;
   p.pad_h = g.kh / 2;
   p.pad_w = g.kw / 2;
-  p.idesc = make_idesc_bf16(BM, p.bn, 0, 0);
+  // fp16 operands: the A and B format fields of the descriptor are 0 instead of 1 (bf16)
+  p.idesc = make_idesc_bf16(BM, p.bn, 0, 0) & (g.fp16 ? ~((1u << 7) | (1u << 10)) : ~0u);
   p.status = g.status;
 
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(conv3d_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(conv3d_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(conv3d_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SMEM_BYTES);
     if (e != cudaSuccess) {
       set_error_detail("conv3d: cudaFuncSetAttribute(max dynamic shared memory) failed");
       return e;
@@ -358,7 +389,10 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
   }
   (void)cudaGetLastError();
   const int grid = tiles < sm_count ? int(tiles) : sm_count;
-  conv3d_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, p);
+  if (g.fp16)
+    conv3d_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, p);
+  else
+    conv3d_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_error_detail("conv3d: kernel launch failed");
   return e;

@@ -54,6 +54,12 @@ __device__ __forceinline__ bool wait_counter(const int* counter, int target, con
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
     if (seen - target >= 0) return true;
     if (*g.abort_flag) return false;
+    // A wait that already ran out on this device (this launch or an earlier one) means the step
+    // is lost: give up at once instead of spending the limit again in every CTA and launch.
+    if (g.status && *reinterpret_cast<volatile int*>(g.status) != 0) {
+      *g.abort_flag = 1;
+      return false;
+    }
     if (global_timer_ns() - start > AGB_PEER_WAIT_LIMIT_NS) {
       *g.abort_flag = 1;
       if (g.status) atomicCAS(g.status, 0, kTimeoutPeer);

@@ -55,6 +55,12 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a
         int seen;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
         if (seen - target >= 0) break;
+        // A wait that already ran out on this device (this launch or an earlier one) means the
+        // step is lost: give up at once instead of spending the limit again in every CTA.
+        if (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) {
+          go = 0;
+          break;
+        }
         if (global_timer_ns() - start > AGB_PEER_WAIT_LIMIT_NS) {
           if (a.status) atomicCAS(a.status, 0, kTimeoutPeer);
           go = 0;

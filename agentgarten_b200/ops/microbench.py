@@ -127,7 +127,7 @@ def bench_conv(tokens: int, launches: int) -> list[dict]:
         x = torch.randn(1, frames + 2, height, width, channels, device="cuda", dtype=torch.bfloat16)
         weight = torch.randn(channels, channels, 3, 3, 3, device="cuda", dtype=torch.bfloat16) * 0.01
         packed = weight.permute(0, 2, 3, 4, 1).reshape(channels, 27, channels).contiguous()
-        ms = _time(lambda: native.ext().conv3d(x, packed, None, None, 3, 3, 3), launches)
+        ms = _time(lambda: native.ext().conv3d(x, packed, None, None, 3, 3, 3, False), launches)
         logical = x.permute(0, 4, 1, 2, 3)
         cl_weight = weight.contiguous(memory_format=torch.channels_last_3d)
         library = _time(lambda: torch.nn.functional.conv3d(logical, cl_weight, padding=(0, 1, 1)), launches)
@@ -137,7 +137,25 @@ def bench_conv(tokens: int, launches: int) -> list[dict]:
     return out
 
 
-CASES = {"conv": bench_conv, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
+def bench_depthwise(tokens: int, launches: int) -> list[dict]:
+    """7x7 depthwise convolutions of the wide TAEHV decoder (fp16), against cuDNN / ATen."""
+    out = []
+    for channels, frames, height, width in ((256, 4, 240, 416), (512, 4, 120, 208), (1024, 4, 60, 104)):
+        conv = torch.nn.Conv2d(channels, channels, 7, padding=3, groups=channels, bias=False)
+        conv = conv.to("cuda", torch.float16).to(memory_format=torch.channels_last)
+        x = torch.randn(frames, channels, height, width, device="cuda", dtype=torch.float16)
+        x = x.contiguous(memory_format=torch.channels_last)
+        from agentgarten_b200.ops.conv import depthwise_frames
+
+        with torch.no_grad():
+            ms = _time(lambda: depthwise_frames(conv, x), launches)
+            library = _time(lambda: conv(x), launches)
+        out.append({"kernel": "depthwise_kernel", "case": f"{channels} ch, {frames} x {height}x{width}, 7x7 fp16",
+                    "ms": ms, "gbs": 2 * x.numel() * 2 / ms / 1e6, "cudnn_ms": library})
+    return out
+
+
+CASES = {"conv": bench_conv, "depthwise": bench_depthwise, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
 
 
 def main(argv=None) -> int:

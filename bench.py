@@ -39,6 +39,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--recipe", default="bidirectional",
                         choices=["bidirectional", "ar_diffusion_forcing", "ar_teacher_forcing"],
                         help="the headline metric is the default; the others measure the other recipes")
+    parser.add_argument("--context-parallel", type=int, default=1,
+                        help="ranks that share one clip (divides --gpus); 1 = data parallel only")
     parser.add_argument("--no-e2e", action="store_true")
     return parser.parse_args()
 
@@ -114,8 +116,14 @@ def main() -> int:
     native.require()
 
     frames = args.frames or (21 if args.recipe == "bidirectional" else 61)
-    job = build_training_job(device, layers=args.layers, frames=frames, recipe=args.recipe)
-    host_batch = synthetic_batch(job, "cpu", seed=1000 + rank, pinned=True)
+    cp = args.context_parallel
+    if cp < 1 or world % cp:
+        raise SystemExit(f"--context-parallel {cp} does not divide {world} ranks")
+    job = build_training_job(device, layers=args.layers, frames=frames, recipe=args.recipe,
+                             context_parallel=cp)
+    # the ranks that share a clip get the same batch and draw the same noise
+    host_batch = synthetic_batch(job, "cpu", seed=1000 + rank // cp, pinned=True)
+    torch.manual_seed(77 + rank // cp)
     device_batch = {k: v.to(device) for k, v in host_batch.items()}
 
     def barrier() -> None:
@@ -163,7 +171,7 @@ def main() -> int:
     status = int(native.ext().status(device.index or 0).item())
 
     if rank == 0:
-        tokens = job.rgb_tokens_per_clip * world * args.steps
+        tokens = job.rgb_tokens_per_clip * (world // cp) * args.steps
         value = tokens / (elapsed_ms / 1e3)
         line = {
             "metric": "train latent-tokens/s/box (bidirectional rectified flow)"
@@ -185,12 +193,13 @@ def main() -> int:
                          f"{job.config.hidden_size}, {job.config.num_attention_heads}/"
                          f"{job.config.num_key_value_heads} heads x {job.config.head_dim}, MLP "
                          f"{job.config.intermediate_size}, plus frozen text tower of the same size",
-                "global_batch": world,
+                "global_batch": world // cp,
                 "seq_len": job.rgb_tokens_per_clip,
                 "tokens_in_sequence": 2 * job.rgb_tokens_per_clip,
                 "latent": [1, 48, job.frames, *job.latent_hw],
-                "parallelism": f"dp{world} (replicated bf16 parameters, sharded FP32 optimizer "
-                               "state, peer-memory reduce-scatter + Adam + all-gather)",
+                "parallelism": f"dp{world // cp}" + (f" x cp{cp} (Ulysses)" if cp > 1 else "") +
+                               " (replicated bf16 parameters, sharded FP32 optimizer state, "
+                               "peer-memory reduce-scatter + Adam + all-gather)",
                 "grad_accum_steps": job.grad_accum_steps,
                 "optimizer": "Adam lr 3e-5 betas (0.9, 0.99), FP32 master, grad clip 1.0",
                 "l2_policy": "inputs larger than L2 (14 GB of weights stream every step)",

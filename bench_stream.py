@@ -96,9 +96,16 @@ def main() -> int:
         stop.record()
         torch.cuda.synchronize()
         times.append(start.elapsed_time(stop))
+        # A bounded wait that ran out on any rank ends the run on all of them: the remaining
+        # blocks would only repeat the failure.  (Outside the timed region.)
+        failed = native.ext().status(device.index).clone()
+        if world > 1:
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+        if int(failed.item()) != 0:
+            break
     status = int(native.ext().status(device.index).item())
     if world > 1:
-        gathered = torch.tensor(times + [float(status)], device=device)
+        gathered = torch.tensor(times + [float(status)], device=device)  # same length on every rank
         dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
         times, status = gathered[:-1].tolist(), int(gathered[-1].item())
     if args.trace and sharded and rank == 0:

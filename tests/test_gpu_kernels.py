@@ -358,22 +358,25 @@ def test_channel_norm_kernel(channels, silu):
     (64, 128, (3, 1, 1), 6, 12, 20, True),      # temporal kernel only
     (256, 256, (3, 3, 3), 3, 24, 40, True),
 ])
-def test_conv_kernel_matches_fp32_convolution(cin, cout, kernel, frames, height, width, extras):
+@pytest.mark.parametrize("dtype,relu", [(torch.bfloat16, False), (torch.float16, True)])
+def test_conv_kernel_matches_fp32_convolution(cin, cout, kernel, frames, height, width, extras, dtype, relu):
     torch.manual_seed(cin + cout)
     kt, kh, kw = kernel
-    x = torch.randn(2, frames, height, width, cin, device=DEV).bfloat16()
-    weight = (torch.randn(cout, cin, kt, kh, kw, device=DEV) / (cin * kt * kh * kw) ** 0.5).bfloat16()
-    bias = torch.randn(cout, device=DEV).bfloat16() if extras else None
+    x = torch.randn(2, frames, height, width, cin, device=DEV).to(dtype)
+    weight = (torch.randn(cout, cin, kt, kh, kw, device=DEV) / (cin * kt * kh * kw) ** 0.5).to(dtype)
+    bias = torch.randn(cout, device=DEV).to(dtype) if extras else None
     packed = weight.permute(0, 2, 3, 4, 1).reshape(cout, -1, cin).contiguous()
-    residual = torch.randn(2, frames - kt + 1, height, width, cout, device=DEV).bfloat16() if extras else None
-    out = native.ext().conv3d(x, packed, bias, residual, kt, kh, kw)
+    residual = torch.randn(2, frames - kt + 1, height, width, cout, device=DEV).to(dtype) if extras else None
+    out = native.ext().conv3d(x, packed, bias, residual, kt, kh, kw, relu)
     _status_ok()
     want = torch.nn.functional.conv3d(x.float().permute(0, 4, 1, 2, 3), weight.float(),
                                       None if bias is None else bias.float(), padding=(0, kh // 2, kw // 2))
     want = want.permute(0, 2, 3, 4, 1)
     if residual is not None:
         want = want + residual.float()
-    assert out.shape == want.shape
+    if relu:
+        want = want.relu()
+    assert out.shape == want.shape and out.dtype == dtype
     assert _rel(out, want) < 6e-3, _rel(out, want)
     assert (out.float() - want).abs().max() < 0.06
 
@@ -395,9 +398,54 @@ def test_conv_modules_use_the_kernel_and_match():
     y = torch.randn(3, 32, 18, 22, device=DEV).bfloat16()
     with torch.no_grad():
         assert _rel(conv_frames(frames, y), frames(y).float()) < 1e-2
+    # output channels that are not a multiple of 8 are padded for the kernel and cut again
+    odd = torch.nn.Conv2d(64, 12, 3, padding=1).to(DEV, torch.float16)
+    y = torch.randn(2, 64, 16, 40, device=DEV).half()
+    with torch.no_grad():
+        got = conv_frames(odd, y, relu=True)
+        assert got.shape == (2, 12, 16, 40) and _rel(got, odd(y).float().relu()) < 1e-2
     # a convolution that wants gradients stays on the differentiable path
     z = conv_volume(conv, x)
     assert z.requires_grad
+    _status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("kernel,channels,height,width", [(7, 64, 13, 22), (7, 256, 9, 7), (3, 32, 6, 5), (5, 8, 8, 33)])
+def test_depthwise_kernel_matches_fp32_convolution(dtype, kernel, channels, height, width):
+    from agentgarten_b200.ops.conv import depthwise_frames
+
+    torch.manual_seed(kernel * channels)
+    conv = torch.nn.Conv2d(channels, channels, kernel, padding=kernel // 2, groups=channels,
+                           bias=kernel == 3).to(DEV, dtype)
+    x = torch.randn(3, channels, height, width, device=DEV).to(dtype)
+    before = native.launches()
+    with torch.no_grad():
+        got = depthwise_frames(conv, x)
+        want = torch.nn.functional.conv2d(x.float(), conv.weight.float(),
+                                          None if conv.bias is None else conv.bias.float(),
+                                          padding=kernel // 2, groups=channels)
+    assert native.launches() == before + 1
+    assert got.shape == want.shape and got.dtype == dtype
+    assert _rel(got, want) < (4e-3 if dtype == torch.float16 else 8e-3), _rel(got, want)
+
+
+@pytest.mark.parametrize("name", ["taew2_2", "taew2_2_super"])
+def test_taehv_decoder_on_gpu_matches_cpu_fp32(name):
+    from agentgarten_b200.codecs._taehv.taehv import TAEHV
+
+    torch.manual_seed(2)
+    cpu = TAEHV(checkpoint_path=None, arch_name=name).eval()
+    gpu = TAEHV(checkpoint_path=None, arch_name=name).eval()
+    gpu.load_state_dict(cpu.state_dict())
+    gpu = gpu.to(DEV, torch.float16).to(memory_format=torch.channels_last)
+    latent = torch.randn(1, 3, 48, 6, 10)
+    before = native.launches()
+    with torch.no_grad():
+        want = cpu.decode_video(latent, parallel=True, show_progress_bar=False)
+        got = gpu.decode_video(latent.to(DEV, torch.float16), parallel=True, show_progress_bar=False)
+    assert native.launches() > before + 10  # the convolutions ran in the kernel
+    assert got.shape == want.shape and _rel(got, want.to(DEV)) < 3e-2, _rel(got, want.to(DEV))
     _status_ok()
 
 
