@@ -195,6 +195,17 @@ cudaError_t relocate_rows(const void* src, void* dst, const float* cosv, const f
                           cudaStream_t stream);
 
 // ------------------------------------------------------------------------- video VAE
+// AdaLN modulation of bf16 rows (x, out [rows, width]; w [width]):
+//   norm_modulate:  out = rms_norm(x) * w * (1 + scale) + shift
+//   gated_residual: out = hidden + gate * y
+// scale, shift and gate are column blocks of the modulation projection: element [row, c] sits
+// at pointer + row * stride + c (stride a multiple of 8).
+cudaError_t norm_modulate(const void* x, const void* w, const void* scale, const void* shift,
+                          void* out, int64_t rows, int width, int64_t mod_stride, float eps,
+                          cudaStream_t stream);
+cudaError_t gated_residual(const void* hidden, const void* gate, const void* y, void* out,
+                           int64_t rows, int width, int64_t gate_stride, cudaStream_t stream);
+
 // Channel RMS norm of channels-last bf16 activations (x, out: [pixels, channels], gamma fp32
 // [channels]): out = x / max(||x||, 1e-12) * sqrt(channels) * gamma, then SiLU when silu != 0.
 cudaError_t channel_norm(const void* x, const float* gamma, void* out, int64_t pixels, int channels,

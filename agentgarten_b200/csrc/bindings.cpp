@@ -331,6 +331,45 @@ Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
   return out;
 }
 
+// AdaLN: rows of x [rows, H]; scale / shift / gate are [rows, H] column blocks (unit inner stride).
+namespace {
+void check_block(const Tensor& t, const Tensor& like, const char* name) {
+  check_bf16(t, name);
+  TORCH_CHECK(t.dim() == 2 && t.sizes() == like.sizes() && t.stride(1) == 1 && t.stride(0) % 8 == 0 &&
+                  (reinterpret_cast<uintptr_t>(t.data_ptr()) & 15) == 0,
+              name, " must be a [rows, H] column block with 16-byte aligned rows");
+}
+}  // namespace
+
+Tensor norm_modulate(const Tensor& x, const Tensor& w, const Tensor& scale, const Tensor& shift, double eps) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && w.numel() == x.size(1) && w.is_contiguous(),
+              "norm_modulate: x [rows, H] contiguous, w [H]");
+  check_block(scale, x, "scale");
+  check_block(shift, x, "shift");
+  TORCH_CHECK(scale.stride(0) == shift.stride(0), "scale and shift come from the same projection");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  check(agb::norm_modulate(x.data_ptr(), w.data_ptr(), scale.data_ptr(), shift.data_ptr(), out.data_ptr(),
+                           x.size(0), int(x.size(1)), scale.stride(0), float(eps), stream_of(x)),
+        "norm_modulate");
+  return out;
+}
+
+Tensor gated_residual(const Tensor& hidden, const Tensor& gate, const Tensor& y) {
+  check_bf16(hidden, "hidden");
+  check_bf16(y, "y");
+  TORCH_CHECK(hidden.dim() == 2 && hidden.is_contiguous() && y.is_contiguous() && y.sizes() == hidden.sizes(),
+              "gated_residual: hidden and y are contiguous [rows, H]");
+  check_block(gate, hidden, "gate");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  Tensor out = torch::empty_like(hidden);
+  check(agb::gated_residual(hidden.data_ptr(), gate.data_ptr(), y.data_ptr(), out.data_ptr(), hidden.size(0),
+                            int(hidden.size(1)), gate.stride(0), stream_of(hidden)), "gated_residual");
+  return out;
+}
+
 // Depthwise k x k convolution of channels-last frames: x [N, H, W, C], weight [k * k, C].
 Tensor depthwise(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias, int64_t kernel) {
   const auto dtype = x.scalar_type();
@@ -596,6 +635,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("channel_norm", &channel_norm);
   m.def("conv3d", &conv3d);
   m.def("depthwise", &depthwise);
+  m.def("norm_modulate", &norm_modulate);
+  m.def("gated_residual", &gated_residual);
   m.def("attn_jvp", &attn_jvp);
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_reduce_norm", &tp_reduce_norm);

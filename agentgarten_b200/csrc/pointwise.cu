@@ -309,6 +309,59 @@ int grid_for(int64_t work_items) {
   return int(blocks < 148 * 16 ? (blocks > 0 ? blocks : 1) : 148 * 16);
 }
 
+// --------------------------------------------------------------- AdaLN modulation
+// out = bf16(rms_norm(x) * w) * (1 + scale) + shift, one CTA per row.  scale and shift are rows
+// of a wider matrix (the six-way modulation projection), `mod_stride` elements apart.
+__global__ void __launch_bounds__(NT) norm_modulate_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    const __nv_bfloat16* __restrict__ scale, const __nv_bfloat16* __restrict__ shift,
+    __nv_bfloat16* __restrict__ out, int width, int64_t mod_stride, float eps) {
+  __shared__ float scratch[NT / 32];
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * width;
+  float sumsq = 0.f;
+  for (int c = threadIdx.x * 8; c < width; c += NT * 8) {
+    float v[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sumsq += v[i] * v[i];
+  }
+  const float rstd = rsqrtf(block_sum(sumsq, scratch) / float(width) + eps);
+  for (int c = threadIdx.x * 8; c < width; c += NT * 8) {
+    float v[8], g[8], sc[8], sh[8];
+    unpack8(*reinterpret_cast<const uint4*>(xr + c), v);
+    unpack8(*reinterpret_cast<const uint4*>(w + c), g);
+    unpack8(*reinterpret_cast<const uint4*>(scale + row * mod_stride + c), sc);
+    unpack8(*reinterpret_cast<const uint4*>(shift + row * mod_stride + c), sh);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float normed = round_bf16(g[i] * round_bf16(v[i] * rstd));
+      v[i] = round_bf16(normed * round_bf16(1.f + sc[i])) + sh[i];
+    }
+    *reinterpret_cast<uint4*>(out + row * width + c) = pack8(v);
+  }
+}
+
+// out = hidden + gate * y (gate a row of the modulation matrix, `gate_stride` elements apart).
+__global__ void __launch_bounds__(NT) gated_residual_kernel(
+    const __nv_bfloat16* __restrict__ hidden, const __nv_bfloat16* __restrict__ gate,
+    const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ out, int64_t rows, int width,
+    int64_t gate_stride) {
+  const int per_row = width / 8;
+  const int64_t total = rows * per_row;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int64_t row = i / per_row;
+    const int c = int(i % per_row) * 8;
+    float h[8], g[8], v[8];
+    unpack8(*reinterpret_cast<const uint4*>(hidden + row * width + c), h);
+    unpack8(*reinterpret_cast<const uint4*>(gate + row * gate_stride + c), g);
+    unpack8(*reinterpret_cast<const uint4*>(y + row * width + c), v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) h[k] += round_bf16(g[k] * v[k]);
+    *reinterpret_cast<uint4*>(out + row * width + c) = pack8(h);
+  }
+}
+
 }  // namespace
 
 cudaError_t rms_norm_fwd(const void* x, const void* addend, const void* w, void* total_out,
@@ -325,6 +378,30 @@ cudaError_t rms_norm_fwd(const void* x, const void* addend, const void* w, void*
     rms_norm_fwd_kernel<true><<<unsigned(rows), NT, 0, stream>>>(X, A, W, TO, O, rstd, width, eps);
   else
     rms_norm_fwd_kernel<false><<<unsigned(rows), NT, 0, stream>>>(X, A, W, TO, O, rstd, width, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t norm_modulate(const void* x, const void* w, const void* scale, const void* shift,
+                          void* out, int64_t rows, int width, int64_t mod_stride, float eps,
+                          cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  if ((width % 8) || (mod_stride % 8)) return cudaErrorInvalidValue;
+  norm_modulate_kernel<<<unsigned(rows), NT, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(scale), static_cast<const __nv_bfloat16*>(shift),
+      static_cast<__nv_bfloat16*>(out), width, mod_stride, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t gated_residual(const void* hidden, const void* gate, const void* y, void* out,
+                           int64_t rows, int width, int64_t gate_stride, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  if ((width % 8) || (gate_stride % 8)) return cudaErrorInvalidValue;
+  const int64_t blocks = (rows * (width / 8) + NT - 1) / NT;
+  gated_residual_kernel<<<unsigned(blocks < 148 * 16 ? blocks : 148 * 16), NT, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(hidden), static_cast<const __nv_bfloat16*>(gate),
+      static_cast<const __nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(out), rows, width,
+      gate_stride);
   return cudaGetLastError();
 }
 

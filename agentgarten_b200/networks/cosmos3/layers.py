@@ -269,7 +269,8 @@ class Cosmos3GenLayer(nn.Module):
     def project(self, hidden, cosine, sine, modulation=None):
         if modulation is not None:
             shift, scale = modulation[0], modulation[1]
-            norm = lambda x: self.input_layernorm_moe_gen(x) * (1 + scale) + shift  # noqa: E731
+            ln = self.input_layernorm_moe_gen
+            norm = lambda x: ops.norm_modulate(x, ln.weight, scale, shift, ln.variance_epsilon)  # noqa: E731
         else:
             norm = self.input_layernorm_moe_gen
         return _project(hidden, norm, self.self_attn, self.num_attention_heads,
@@ -281,9 +282,10 @@ class Cosmos3GenLayer(nn.Module):
             residual = hidden + out
             return residual + self.mlp_moe_gen(self.post_attention_layernorm_moe_gen(residual))
         _, _, gate_a, shift_m, scale_m, gate_m = modulation
-        residual = hidden + gate_a * out
-        normalized = self.post_attention_layernorm_moe_gen(residual) * (1 + scale_m) + shift_m
-        return residual + gate_m * self.mlp_moe_gen(normalized)
+        residual = ops.gated_residual(hidden, gate_a, out)
+        ln = self.post_attention_layernorm_moe_gen
+        normalized = ops.norm_modulate(residual, ln.weight, scale_m, shift_m, ln.variance_epsilon)
+        return ops.gated_residual(residual, gate_m, self.mlp_moe_gen(normalized))
 
     def modulation(self, embedding: torch.Tensor | None):
         """``embedding`` ``[B, N, H]`` per-token timestep embedding → six ``[B, N, H]`` terms."""

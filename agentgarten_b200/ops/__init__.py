@@ -19,7 +19,9 @@ from . import native, reference
 from .attention import attention, attention_jvp, planned_attention
 from .linear import linear
 from .pointwise import (
+    gated_residual,
     head_norm_rope,
+    norm_modulate,
     rf_interpolate,
     rf_x0,
     rms_norm,
@@ -31,9 +33,11 @@ from .pointwise import (
 __all__ = [
     "attention",
     "attention_jvp",
+    "gated_residual",
     "head_norm_rope",
     "linear",
     "native",
+    "norm_modulate",
     "planned_attention",
     "reference",
     "rf_interpolate",

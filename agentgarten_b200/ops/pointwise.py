@@ -64,6 +64,43 @@ def rms_norm_add(x, addend, weight, eps):
     return total, rms_norm(total, weight, eps)
 
 
+def _column_block(t: torch.Tensor, like: torch.Tensor) -> torch.Tensor | None:
+    """``t`` as a 2-D ``[rows, H]`` view with unit inner stride (a chunk of a wider projection), or None."""
+    if t.shape != like.shape or t.dtype != like.dtype or t.stride(-1) != 1:
+        return None
+    try:
+        flat = t.view(-1, t.shape[-1])
+    except RuntimeError:
+        return None
+    return flat if flat.stride(0) % 8 == 0 and flat.data_ptr() % 16 == 0 else None
+
+
+def norm_modulate(x: torch.Tensor, weight: torch.Tensor, scale: torch.Tensor, shift: torch.Tensor,
+                  eps: float) -> torch.Tensor:
+    """AdaLN input: ``rms_norm(x) * (1 + scale) + shift`` in one pass when no gradient is wanted
+    (``wm/networks/cosmos3/layers.py:269-276`` with the ``adaln`` option)."""
+    if native.use(x) and weight.dtype == x.dtype and x.shape[-1] % 8 == 0 and not (
+            torch.is_grad_enabled() and any(t.requires_grad for t in (x, weight, scale, shift))):
+        rows = x.reshape(-1, x.shape[-1])
+        sc, sh = _column_block(scale, x), _column_block(shift, x)
+        if rows.is_contiguous() and sc is not None and sh is not None and sc.stride(0) == sh.stride(0):
+            native.count()
+            return native.ext().norm_modulate(rows, weight.contiguous(), sc, sh, float(eps)).view(x.shape)
+    return rms_norm(x, weight, eps) * (1 + scale) + shift
+
+
+def gated_residual(hidden: torch.Tensor, gate: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """AdaLN output: ``hidden + gate * y`` in one pass when no gradient is wanted."""
+    if native.use(hidden) and y.dtype == hidden.dtype and y.shape == hidden.shape and hidden.shape[-1] % 8 == 0 \
+            and not (torch.is_grad_enabled() and any(t.requires_grad for t in (hidden, gate, y))):
+        g = _column_block(gate, hidden)
+        if g is not None and hidden.is_contiguous() and y.is_contiguous():
+            native.count()
+            width = hidden.shape[-1]
+            return native.ext().gated_residual(hidden.view(-1, width), g, y.view(-1, width)).view(hidden.shape)
+    return hidden + gate * y
+
+
 def rotary(value, cos, sin):
     return reference.rotary(value, cos, sin)
 

@@ -121,3 +121,26 @@ def test_super_decoder_surface():
         decoder.decode(torch.randn(1, 16, 1, 2, 2))
     codec = Wan22VAECodec(None, dtype="float32", decoder=decoder)
     assert torch.equal(codec.decode(latent), video)
+
+
+def test_convolution_helpers_fall_back_to_the_library_definition():
+    """Off the GPU the convolution helpers are the plain convolutions with the epilogue applied."""
+    from agentgarten_b200.ops.conv import conv_frames, conv_volume, depthwise_frames, eligible, packed_weight
+
+    torch.manual_seed(0)
+    conv = torch.nn.Conv3d(8, 16, 3, padding=(0, 1, 1))
+    x = torch.randn(1, 8, 4, 6, 7)
+    residual = torch.randn(1, 16, 2, 6, 7)
+    assert not eligible(conv, x)
+    with torch.no_grad():
+        want = torch.relu(conv(x) + residual)
+        assert torch.equal(conv_volume(conv, x, residual, relu=True), want)
+        frames = torch.nn.Conv2d(8, 12, 3, padding=1)
+        y = torch.randn(2, 8, 5, 5)
+        assert torch.equal(conv_frames(frames, y), frames(y))
+        deep = torch.nn.Conv2d(8, 8, 7, padding=3, groups=8, bias=False)
+        assert torch.equal(depthwise_frames(deep, y), deep(y))
+    # the kernel layout of a weight: [Cout rounded up to 8, taps, Cin], taps in (t, h, w) order
+    packed, bias = packed_weight(frames, torch.float32)
+    assert packed.shape == (16, 9, 8) and bias.shape == (16,)
+    assert torch.equal(packed[:12, 4], frames.weight[:, :, 1, 1]) and not packed[12:].any()

@@ -506,3 +506,28 @@ def test_attention_forward_backward_with_odd_and_even_head_groups(hq, hkv):
     assert _rel(out, want) < 1e-2
     assert _rel(dq, wq) < 2e-2 and _rel(dk, wk) < 2e-2 and _rel(dv, wv) < 2e-2
     _status_ok()
+
+
+def test_adaln_kernels_match_the_eager_sequence():
+    """norm + modulate and the gated residual read their terms in place from the six-way
+    modulation projection and reproduce the operator-by-operator bf16 result."""
+    torch.manual_seed(4)
+    rows, width = 77, 512
+    x = torch.randn(2, rows, width, device=DEV).bfloat16()
+    y = torch.randn(2, rows, width, device=DEV).bfloat16()
+    weight = (torch.rand(width, device=DEV) + 0.5).bfloat16()
+    terms = (0.3 * torch.randn(2, rows, 6 * width, device=DEV)).bfloat16().chunk(6, dim=-1)
+    shift, scale, gate = terms[0], terms[1], terms[2]
+    before = native.launches()
+    with torch.no_grad():
+        got = ops.norm_modulate(x, weight, scale, shift, 1e-6)
+        want = ops.rms_norm(x, weight, 1e-6) * (1 + scale) + shift
+        assert native.launches() >= before + 2
+        assert (got.float() - want.float()).abs().max() <= 2e-2 and _rel(got, want) < 3e-3
+        fp32 = reference.rms_norm(x.float(), weight.float(), 1e-6) * (1 + scale.float()) + shift.float()
+        assert _rel(got, fp32) < 8e-3
+        mixed = ops.gated_residual(x, gate, y)
+        assert torch.equal(mixed, x + gate * y)
+    # with gradients wanted the differentiable path runs
+    xg = x.clone().requires_grad_()
+    assert ops.norm_modulate(xg, weight, scale, shift, 1e-6).requires_grad
