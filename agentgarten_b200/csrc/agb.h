@@ -246,6 +246,15 @@ struct DepthwiseArgs {
 };
 cudaError_t depthwise_conv(const DepthwiseArgs& args, cudaStream_t stream);
 
+// Geometry preprocessing, one pass each over planar tensors (plane = T * H * W):
+//   colorize_depth: depth fp32 [B, plane] (metric; invalid <= 0 or non-finite) -> RGB fp32
+//                   [B, 3, plane] along the 7-segment colour-cube walk, scale [B] or [1];
+//   decode_normal:  uint8 [B, 3, plane] -> unit vectors fp32 [B, 3, plane] (0 when degenerate).
+cudaError_t colorize_depth(const float* depth, const float* scale, float* out, int64_t batch,
+                           int64_t plane, int scale_count, cudaStream_t stream);
+cudaError_t decode_normal(const void* normal, float* out, int64_t batch, int64_t plane,
+                          cudaStream_t stream);
+
 // ----------------------------------------------------------- sharded optimizer (ZeRO)
 // Base pointers of the same flat buffer on every rank of the node (index = rank).
 struct ZeroPeers {

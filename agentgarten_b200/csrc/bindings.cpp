@@ -370,6 +370,30 @@ Tensor gated_residual(const Tensor& hidden, const Tensor& gate, const Tensor& y)
   return out;
 }
 
+// Geometry preprocessing: depth [B, 1, T, H, W] fp32 -> RGB [B, 3, T, H, W]; uint8 normals -> unit vectors.
+Tensor colorize_depth(const Tensor& depth, const Tensor& scale) {
+  TORCH_CHECK(depth.is_cuda() && depth.scalar_type() == torch::kFloat32 && depth.dim() == 5 &&
+                  depth.size(1) == 1 && depth.is_contiguous(), "colorize_depth: depth is contiguous fp32 [B, 1, T, H, W]");
+  TORCH_CHECK(scale.is_cuda() && scale.scalar_type() == torch::kFloat32 && scale.is_contiguous() &&
+                  (scale.numel() == 1 || scale.numel() == depth.size(0)), "colorize_depth: scale is fp32 [B] or [1]");
+  c10::cuda::CUDAGuard guard(depth.device());
+  Tensor out = torch::empty({depth.size(0), 3, depth.size(2), depth.size(3), depth.size(4)}, depth.options());
+  check(agb::colorize_depth(depth.data_ptr<float>(), scale.data_ptr<float>(), out.data_ptr<float>(),
+                            depth.size(0), depth.numel() / depth.size(0), int(scale.numel()), stream_of(depth)),
+        "colorize_depth");
+  return out;
+}
+
+Tensor decode_normal(const Tensor& normal) {
+  TORCH_CHECK(normal.is_cuda() && normal.scalar_type() == torch::kUInt8 && normal.dim() == 5 &&
+                  normal.size(1) == 3 && normal.is_contiguous(), "decode_normal: normal is contiguous uint8 [B, 3, T, H, W]");
+  c10::cuda::CUDAGuard guard(normal.device());
+  Tensor out = torch::empty(normal.sizes(), normal.options().dtype(torch::kFloat32));
+  check(agb::decode_normal(normal.data_ptr(), out.data_ptr<float>(), normal.size(0),
+                           normal.numel() / normal.size(0) / 3, stream_of(normal)), "decode_normal");
+  return out;
+}
+
 // Depthwise k x k convolution of channels-last frames: x [N, H, W, C], weight [k * k, C].
 Tensor depthwise(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias, int64_t kernel) {
   const auto dtype = x.scalar_type();
@@ -635,6 +659,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("channel_norm", &channel_norm);
   m.def("conv3d", &conv3d);
   m.def("depthwise", &depthwise);
+  m.def("colorize_depth", &colorize_depth);
+  m.def("decode_normal", &decode_normal);
   m.def("norm_modulate", &norm_modulate);
   m.def("gated_residual", &gated_residual);
   m.def("attn_jvp", &attn_jvp);

@@ -100,9 +100,27 @@ class GeometryAugmentationConfig:
 
 
 # ------------------------------------------------------------------ colourisation
+def _fused_kernels(tensor: torch.Tensor):
+    """The CUDA extension when ``tensor`` lives on a GPU and no gradient is wanted (one-pass
+    kernels of ``csrc/geometry.cu``), else ``None``."""
+    if not tensor.is_cuda or (torch.is_grad_enabled() and tensor.requires_grad):
+        return None
+    from agentgarten_b200.ops import native
+
+    if not native.available():
+        return None
+    native.count()
+    return native.ext()
+
+
 def colorize_depth(depth: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """Metric depth ``[B,1,T,H,W]`` → RGB in [0,1] along a 7-segment walk on the colour
     cube.  ``t = 1 - (1 + d·s/10)^-2`` compresses far depth; invalid pixels are black."""
+    fused = _fused_kernels(depth)
+    if fused is not None and depth.dtype == torch.float32 and depth.ndim == 5 and depth.shape[1] == 1:
+        weights = scale.to(device=depth.device, dtype=torch.float32).reshape(-1).contiguous()
+        if weights.shape[0] in (1, depth.shape[0]):
+            return fused.colorize_depth(depth.contiguous(), weights)
     valid = torch.isfinite(depth) & (depth > 0)
     safe = torch.where(valid, depth.clamp_min(0.0), 0.0)
     scale = scale.to(device=depth.device, dtype=torch.float32).reshape(-1)
@@ -126,6 +144,9 @@ def prepare_normal(normal: torch.Tensor) -> torch.Tensor:
     """uint8 normals are decoded to [-1,1] and re-normalised (degenerate → 0); float normals
     are trusted as they are (a second normalisation would perturb every VAE input)."""
     if normal.dtype == torch.uint8:
+        fused = _fused_kernels(normal)
+        if fused is not None and normal.ndim == 5 and normal.shape[1] == 3:
+            return fused.decode_normal(normal.contiguous())
         n = normal.float() / 127.5 - 1.0
         finite = torch.isfinite(n).all(dim=1, keepdim=True)
         n = n.nan_to_num(nan=0.0, posinf=0.0, neginf=0.0)

@@ -22,12 +22,18 @@ from . import native
 __all__ = ["conv_frames", "conv_volume", "depthwise_frames", "eligible", "packed_weight"]
 
 
+def _weight_key(weight: torch.Tensor, dtype: torch.dtype) -> tuple:
+    """Identity of a weight's current value (inference tensors carry no version counter)."""
+    version = -1 if weight.is_inference() else weight._version
+    return (version, weight.data_ptr(), weight.device, dtype)
+
+
 def packed_weight(conv: torch.nn.Module, dtype: torch.dtype = torch.bfloat16
                   ) -> tuple[torch.Tensor, torch.Tensor | None]:
     """``[Cout', taps, Cin]`` copy of a convolution's weight and its bias in ``dtype``, cached on
     the module.  ``Cout'`` is ``Cout`` rounded up to a multiple of 8 (zero rows)."""
     weight = conv.weight
-    key = (weight._version, weight.data_ptr(), weight.device, dtype)
+    key = _weight_key(weight, dtype)
     cached = getattr(conv, "_packed_for_kernel", None)
     if cached is None or cached[0] != key:
         w = weight.detach()
@@ -126,7 +132,7 @@ def depthwise_frames(conv: torch.nn.Conv2d, x: torch.Tensor) -> torch.Tensor:
     if not fits:
         return F.conv2d(x, conv.weight, conv.bias, conv.stride, conv.padding, conv.dilation, conv.groups)
     weight = conv.weight
-    key = (weight._version, weight.data_ptr(), weight.device, x.dtype)
+    key = _weight_key(weight, x.dtype)
     cached = getattr(conv, "_packed_for_kernel", None)
     if cached is None or cached[0] != key:
         taps = weight.detach().reshape(weight.shape[0], k * k).t().contiguous()  # [k*k, C]

@@ -531,3 +531,26 @@ def test_adaln_kernels_match_the_eager_sequence():
     # with gradients wanted the differentiable path runs
     xg = x.clone().requires_grad_()
     assert ops.norm_modulate(xg, weight, scale, shift, 1e-6).requires_grad
+
+
+def test_geometry_kernels_match_the_operator_sequence(monkeypatch):
+    from agentgarten_b200.networks.cosmos3 import geometry
+
+    torch.manual_seed(9)
+    depth = torch.rand(2, 1, 3, 17, 23, device=DEV) * 30
+    depth[0, 0, 0, :3] = 0.0
+    depth[1, 0, 1, 5, :4] = float("nan")
+    depth[1, 0, 2, 7, :4] = float("inf")
+    scale = torch.tensor([0.7, 1.9], device=DEV)
+    normal = torch.randint(0, 256, (2, 3, 3, 17, 23), device=DEV, dtype=torch.uint8)
+    normal[0, :, 0, 0, :5] = 127  # (almost) zero vectors stay finite
+    before = native.launches()
+    got_rgb, got_n = geometry.colorize_depth(depth, scale), geometry.prepare_normal(normal)
+    assert native.launches() == before + 2
+    monkeypatch.setattr(geometry, "_fused_kernels", lambda tensor: None)
+    want_rgb, want_n = geometry.colorize_depth(depth, scale), geometry.prepare_normal(normal)
+    assert got_rgb.shape == want_rgb.shape and (got_rgb - want_rgb).abs().max() < 1e-5
+    assert got_n.shape == want_n.shape and (got_n - want_n).abs().max() < 1e-5
+    single = geometry.colorize_depth(depth, scale[:1])
+    monkeypatch.undo()
+    assert (single - geometry.colorize_depth(depth, scale[:1])).abs().max() < 1e-5
