@@ -14,6 +14,8 @@ Everything else — other strides, dtypes, devices, or inputs that need gradient
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -55,6 +57,8 @@ def eligible(conv: torch.nn.Module, x: torch.Tensor) -> bool:
     """Whether ``conv(x)`` can run in the kernel: bf16 or fp16 on CUDA, stride 1, 'same' in
     space, unpadded in time, input channels a multiple of 8, no gradient wanted."""
     if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and native.available()):
+        return False
+    if os.environ.get("AGB200_LIBRARY_CONV") == "1":  # measure against cuDNN
         return False
     if torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad):
         return False
@@ -123,6 +127,7 @@ def depthwise_frames(conv: torch.nn.Conv2d, x: torch.Tensor) -> torch.Tensor:
     7x7 stage of the wide TAEHV decoder blocks (``wm/codecs/_taehv/taehv.py:52-75``)."""
     k = conv.kernel_size[0]
     fits = (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and native.available()
+            and os.environ.get("AGB200_LIBRARY_CONV") != "1"
             and conv.weight.dtype == x.dtype
             and not (torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad))
             and conv.groups == conv.in_channels == conv.out_channels == x.shape[1]

@@ -155,12 +155,46 @@ def bench_depthwise(tokens: int, launches: int) -> list[dict]:
     return out
 
 
-CASES = {"conv": bench_conv, "depthwise": bench_depthwise, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
+def bench_codec(tokens: int, launches: int) -> list[dict]:
+    """Whole decoders on random weights: Wan 2.2 VAE (bf16) and the TAEHV decoders (fp16) on three
+    latent frames of 30x52 (nine 480x832 pixel frames), with this package's convolution kernels
+    and with the library convolutions (``AGB200_LIBRARY_CONV=1``)."""
+    import os
+
+    from agentgarten_b200.codecs._taehv.taehv import TAEHV
+    from agentgarten_b200.codecs.wan22 import random_vae, to_channels_last
+
+    out = []
+    latent = torch.randn(1, 48, 3, 30, 52, device="cuda")
+
+    def both(name, fn):
+        row = {"kernel": "conv3d_kernel + pointwise", "case": name}
+        for key, flag in (("ms", "0"), ("cudnn_ms", "1")):
+            os.environ["AGB200_LIBRARY_CONV"] = flag
+            with torch.no_grad():
+                row[key] = _time(fn, max(2, launches // 2))
+        os.environ.pop("AGB200_LIBRARY_CONV", None)
+        row["frames_per_s"] = 9 / row["ms"] * 1e3
+        out.append(row)
+
+    vae = to_channels_last(random_vae(seed=0).to("cuda", torch.bfloat16)).eval()
+    z = latent.bfloat16()
+    both("Wan 2.2 VAE decoder, 3 latent frames 30x52", lambda: vae.decode(z, (0.0, 1.0), frames_per_pass=2))
+    for name in ("taew2_2", "taew2_2_super"):
+        tiny = TAEHV(checkpoint_path=None, arch_name=name).eval()
+        tiny = tiny.to("cuda", torch.float16).to(memory_format=torch.channels_last)
+        frames = latent.transpose(1, 2).half()
+        both(f"TAEHV {name} decoder, 3 latent frames 30x52",
+             lambda: tiny.decode_video(frames, parallel=True, show_progress_bar=False))
+    return out
+
+
+CASES = {"codec": bench_codec, "conv": bench_conv, "depthwise": bench_depthwise, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
 
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("--op", nargs="*", default=list(CASES), choices=list(CASES))
+    parser.add_argument("--op", nargs="*", default=[c for c in CASES if c != "codec"], choices=list(CASES))
     parser.add_argument("--tokens", type=int, default=8192)
     parser.add_argument("--launches", type=int, default=10)
     parser.add_argument("--json", action="store_true")
@@ -180,7 +214,12 @@ def main(argv=None) -> int:
         print(json.dumps({"peaks": peaks, "rows": rows, "launches": native.launches()}))
     else:
         for row in rows:
-            rate = f"{row['tflops']:8.1f} TFLOP/s" if "tflops" in row else f"{row['gbs']:8.1f} GB/s   "
+            if "frames_per_s" in row:
+                rate = f"{row['frames_per_s']:8.1f} frames/s"
+            elif "tflops" in row:
+                rate = f"{row['tflops']:8.1f} TFLOP/s"
+            else:
+                rate = f"{row['gbs']:8.1f} GB/s   "
             extra = f"  (cuDNN {row['cudnn_ms']:.3f} ms)" if "cudnn_ms" in row else ""
             print(f"{row['kernel']:34s} {row['case']:46s} {row['ms']:8.3f} ms {rate} "
                   f"{row.get('fraction', 0):5.2f} {row['of']}{extra}")
