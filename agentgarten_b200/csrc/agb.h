@@ -61,7 +61,7 @@ struct TpLink {
 };
 cudaError_t gemm_bf16(const GemmArgs& args, int sm_count, cudaStream_t stream);
 
-// Owner side of the tensor-parallel residual stream, one CTA per owned row:
+// Owner side of the tensor-parallel residual stream, one CTA per four owned rows:
 //   h = bf16(residual_row + sum over source ranks (in rank order) of slot[src][row])
 //   hidden_own[row] = h;  x = weight * bf16(h * rsqrt(mean(h^2) + eps))
 //   x is stored into xbuf[peer][global_row] on every rank (peer stores), then ready[peer][tile]

@@ -14,7 +14,9 @@ namespace agb {
 namespace {
 
 constexpr int NT = 256;
-constexpr int MAX_CHUNKS = 4;  // width <= NT * 8 * MAX_CHUNKS
+constexpr int ROWS = 4;              // rows per CTA: one wait, one fence and one signal for all four
+constexpr int ROW_THREADS = NT / ROWS;  // 64 threads (two warps) walk one row
+constexpr int MAX_CHUNKS = 16;       // width <= ROW_THREADS * 8 * MAX_CHUNKS = 8192 (8 chunks up to 4096)
 
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
@@ -32,18 +34,25 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
                     pack_bf16(f[6], f[7]));
 }
 
+template <int CHUNKS>
 __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a) {
   __shared__ float scratch[NT / 32];
   __shared__ int proceed;
-  const int local_row = blockIdx.x;               // row inside this rank's owned tiles
-  const int local_tile = local_row / 128;
+  // Four consecutive rows of one owned tile (128 is a multiple of ROWS).
+  const int sub = threadIdx.x / ROW_THREADS;      // row of this thread inside the CTA's group
+  const int lane = threadIdx.x % ROW_THREADS;
+  const int first_local = blockIdx.x * ROWS;      // row inside this rank's owned tiles
+  const int local_tile = first_local / 128;
   const int tile = local_tile * a.world + a.rank;  // global row tile
-  const int64_t row = int64_t(tile) * 128 + local_row % 128;
-  const bool live = row < a.m;
+  const int64_t first_row = int64_t(tile) * 128 + first_local % 128;
+  const int live_rows = int(min(int64_t(ROWS), max(int64_t(0), a.m - first_row)));
+  const int local_row = first_local + sub;
+  const int64_t row = first_row + sub;
+  const bool live = sub < live_rows;
 
   if (threadIdx.x == 0) {
     int go = 1;
-    if (live) {
+    if (live_rows > 0) {
       // Partial sums of this tile for the current use; or, when seeding a new step, the end
       // of every rank's previous step.
       const int* counter = a.seed ? a.done : a.arrive + local_tile;
@@ -73,66 +82,70 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a
   }
   __syncthreads();
 
-  if (live && proceed) {
+  if (live_rows > 0 && proceed) {  // uniform across the CTA
     const __nv_bfloat16* slot = static_cast<const __nv_bfloat16*>(a.slot);
     __nv_bfloat16* hidden = static_cast<__nv_bfloat16*>(a.hidden_own) + int64_t(local_row) * a.width;
     const __nv_bfloat16* residual =
         a.seed ? static_cast<const __nv_bfloat16*>(a.seed) + row * a.width : hidden;
     const int64_t slot_stride = int64_t(a.tiles_owned) * 128 * a.width;  // between source ranks
-    uint4 kept[MAX_CHUNKS];
+    uint4 kept[CHUNKS];
     float sumsq = 0.f;
+    if (live) {
 #pragma unroll
-    for (int k = 0; k < MAX_CHUNKS; ++k) {
-      const int c = (k * NT + threadIdx.x) * 8;
-      if (c < a.width) {
-        float v[8];
-        unpack8(*reinterpret_cast<const uint4*>(residual + c), v);
-        if (!a.seed) {
-          float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int src = 0; src < a.world; ++src) {  // fixed order: reproducible sums
-            float part[8];
-            unpack8(*reinterpret_cast<const uint4*>(slot + src * slot_stride +
-                                                    int64_t(local_row) * a.width + c), part);
+      for (int k = 0; k < CHUNKS; ++k) {
+        const int c = (k * ROW_THREADS + lane) * 8;
+        if (c < a.width) {
+          float v[8];
+          unpack8(*reinterpret_cast<const uint4*>(residual + c), v);
+          if (!a.seed) {
+            float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int src = 0; src < a.world; ++src) {  // fixed order: reproducible sums
+              float part[8];
+              unpack8(*reinterpret_cast<const uint4*>(slot + src * slot_stride +
+                                                      int64_t(local_row) * a.width + c), part);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) total[i] += part[i];
+              for (int i = 0; i < 8; ++i) total[i] += part[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = round_bf16(v[i] + total[i]);
           }
+          kept[k] = pack8(v);
+          *reinterpret_cast<uint4*>(hidden + c) = kept[k];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] = round_bf16(v[i] + total[i]);
+          for (int i = 0; i < 8; ++i) sumsq += v[i] * v[i];
         }
-        kept[k] = pack8(v);
-        *reinterpret_cast<uint4*>(hidden + c) = kept[k];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sumsq += v[i] * v[i];
       }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = sumsq;
     __syncthreads();
-    float total = 0.f;
+    // the two warps of a row
+    const float total = scratch[2 * sub] + scratch[2 * sub + 1];
+    if (live) {
+      const float rstd = rsqrtf(total / float(a.width) + a.eps);
+      const __nv_bfloat16* weight = static_cast<const __nv_bfloat16*>(a.weight);
 #pragma unroll
-    for (int w = 0; w < NT / 32; ++w) total += scratch[w];
-    const float rstd = rsqrtf(total / float(a.width) + a.eps);
-    const __nv_bfloat16* weight = static_cast<const __nv_bfloat16*>(a.weight);
+      for (int k = 0; k < CHUNKS; ++k) {
+        const int c = (k * ROW_THREADS + lane) * 8;
+        if (c < a.width) {
+          float v[8], g[8];
+          unpack8(kept[k], v);
+          unpack8(*reinterpret_cast<const uint4*>(weight + c), g);
 #pragma unroll
-    for (int k = 0; k < MAX_CHUNKS; ++k) {
-      const int c = (k * NT + threadIdx.x) * 8;
-      if (c < a.width) {
-        float v[8], g[8];
-        unpack8(kept[k], v);
-        unpack8(*reinterpret_cast<const uint4*>(weight + c), g);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = g[i] * round_bf16(v[i] * rstd);
-        const uint4 packed = pack8(v);
-        for (int peer = 0; peer < a.world; ++peer)
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.xbuf[peer]) + row * a.width + c) = packed;
+          for (int i = 0; i < 8; ++i) v[i] = g[i] * round_bf16(v[i] * rstd);
+          const uint4 packed = pack8(v);
+          for (int peer = 0; peer < a.world; ++peer)
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.xbuf[peer]) + row * a.width + c) = packed;
+        }
       }
     }
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x < a.world) {
+      // the consumer counts rows: one addition of this CTA's rows per peer
       int* counter = a.ready[threadIdx.x] + tile;
-      asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(counter) : "memory");
+      asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(counter), "r"(live_rows) : "memory");
     }
   }
 
@@ -166,14 +179,17 @@ __global__ void tp_signal_done_kernel(const DonePeers peers, int world) {
 }  // namespace
 
 cudaError_t tp_reduce_norm(const TpReduceArgs& a, cudaStream_t stream) {
-  if (a.world < 1 || a.world > 8 || a.width % 8 || a.width > NT * 8 * MAX_CHUNKS || a.m <= 0) {
+  if (a.world < 1 || a.world > 8 || a.width % 8 || a.width > ROW_THREADS * 8 * MAX_CHUNKS || a.m <= 0) {
     set_error_detail("tp_reduce_norm: world 1..8, width a multiple of 8 up to 8192");
     return cudaErrorInvalidValue;
   }
   const int rows = a.tiles_owned * 128;
   if (rows == 0) return cudaSuccess;
   (void)cudaGetLastError();
-  tp_reduce_norm_kernel<<<rows, NT, 0, stream>>>(a);
+  if (a.width <= ROW_THREADS * 8 * (MAX_CHUNKS / 2))
+    tp_reduce_norm_kernel<MAX_CHUNKS / 2><<<rows / ROWS, NT, 0, stream>>>(a);
+  else
+    tp_reduce_norm_kernel<MAX_CHUNKS><<<rows / ROWS, NT, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

@@ -191,6 +191,37 @@ def _stream_outputs(net, condition, latent, policy, **serving):
     return outs
 
 
+@pytest.mark.parametrize("tokens", [101, 130, 387])
+def test_tensor_parallel_run_with_ragged_row_counts(tokens):
+    """Row counts that fill neither a tile of 128 nor a group of four rows: the tensor-parallel
+    kernels (one rank) against the layer-by-layer path on the same tokens."""
+    from agentgarten_b200 import ops
+    from agentgarten_b200.parallel.tensor_parallel import TensorParallelServing
+
+    torch.manual_seed(tokens)
+    config = _config()
+    net = tiny_network(config, device="cpu", seed=0).to(DEV, torch.bfloat16).eval()
+    plan = TensorParallelServing(net, None, max_tokens=512)
+    hidden = torch.randn(1, tokens, config.hidden_size, device=DEV).bfloat16()
+    positions = torch.stack((torch.arange(tokens) // 24, (torch.arange(tokens) // 6) % 4, torch.arange(tokens) % 6),
+                            dim=-1).unsqueeze(0).to(DEV)
+    rope = net.rotary_emb(positions, torch.bfloat16)
+
+    def attend(index, queries, keys, values):
+        return [ops.attention(queries[0], keys[0].contiguous(), values[0].contiguous())]
+
+    with torch.no_grad():
+        want = hidden
+        for index, layer in enumerate(net.layers):
+            (want,) = layer([want], [rope], attend, index)
+        want = net.proj_out(net.norm_moe_gen(want))
+        for _ in range(2):  # the second call reuses the counters of the first
+            got = plan.run(hidden, rope, attend)
+    torch.cuda.synchronize()
+    assert int(native.ext().status(0).item()) == 0
+    assert got.shape == want.shape and rel(got, want) < 2e-2, rel(got, want)
+
+
 def test_tensor_parallel_kernels_on_one_rank_match_the_layer_path():
     from agentgarten_b200.networks.cosmos3.streaming import StreamPolicy
 
