@@ -146,7 +146,7 @@ class ChannelRMSNorm(nn.Module):
         if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and x.shape[1] <= 1024:
             from agentgarten_b200.ops import native
 
-            if native.available():
+            if native.use(x):  # raises when the extension is missing on a GPU
                 # channels-last activations are [pixels, C] rows: one fused kernel, one pass
                 order = (0, *range(2, x.ndim), 1)
                 rows = x.permute(order)

@@ -107,7 +107,7 @@ def _fused_kernels(tensor: torch.Tensor):
         return None
     from agentgarten_b200.ops import native
 
-    if not native.available():
+    if not native.use(tensor, dtypes=(tensor.dtype,)):  # raises when the extension is missing
         return None
     native.count()
     return native.ext()

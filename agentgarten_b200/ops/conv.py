@@ -56,7 +56,7 @@ def packed_weight(conv: torch.nn.Module, dtype: torch.dtype = torch.bfloat16
 def eligible(conv: torch.nn.Module, x: torch.Tensor) -> bool:
     """Whether ``conv(x)`` can run in the kernel: bf16 or fp16 on CUDA, stride 1, 'same' in
     space, unpadded in time, input channels a multiple of 8, no gradient wanted."""
-    if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and native.available()):
+    if not native.use(x, dtypes=(torch.bfloat16, torch.float16)):  # raises when the extension is missing
         return False
     if os.environ.get("AGB200_LIBRARY_CONV") == "1":  # measure against cuDNN
         return False
@@ -126,7 +126,7 @@ def depthwise_frames(conv: torch.nn.Conv2d, x: torch.Tensor) -> torch.Tensor:
     to 7, stride 1, 'same' padding) in the register-tiled kernel of ``csrc/depthwise.cu``; the
     7x7 stage of the wide TAEHV decoder blocks (``wm/codecs/_taehv/taehv.py:52-75``)."""
     k = conv.kernel_size[0]
-    fits = (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and native.available()
+    fits = (native.use(x, dtypes=(torch.bfloat16, torch.float16))
             and os.environ.get("AGB200_LIBRARY_CONV") != "1"
             and conv.weight.dtype == x.dtype
             and not (torch.is_grad_enabled() and (x.requires_grad or conv.weight.requires_grad))
