@@ -306,6 +306,19 @@ class Cosmos3GenLayer(nn.Module):
 
         if time_embeddings is None and fused_layer.eligible(self, chunks, attention):
             return fused_layer.run(self, chunks, ropes, attention, layer_index)
+        if time_embeddings is None and len(chunks) > 1 and ops.native.use(chunks[0]) and all(
+                c.shape[0] == chunks[0].shape[0] for c in chunks):
+            # Everything but attention is row-wise: run it once over the rows of all chunks
+            # (one set of launches per layer instead of one per chunk) and hand attention
+            # per-chunk views.  Only with the CUDA kernels, whose results do not depend on how
+            # many rows are processed together (a cached rollout replays bit for bit).
+            sizes = [c.shape[1] for c in chunks]
+            rope = (torch.cat([r[0] for r in ropes], dim=1), torch.cat([r[1] for r in ropes], dim=1))
+            hidden = torch.cat(chunks, dim=1)
+            query, key, value = self.project(hidden, *rope)
+            outputs = attention(layer_index, list(query.split(sizes, dim=1)),
+                                list(key.split(sizes, dim=1)), list(value.split(sizes, dim=1)))
+            return list(self.finish(hidden, torch.cat(outputs, dim=1)).split(sizes, dim=1))
         mods = [None] * len(chunks) if time_embeddings is None else [
             self.modulation(e) for e in time_embeddings]
         projected = [self.project(h, *rope, m) for h, rope, m in zip(chunks, ropes, mods, strict=True)]
