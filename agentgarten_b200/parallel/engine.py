@@ -139,8 +139,59 @@ def _recomputes_itself(layer: nn.Module, args, kwargs) -> bool:
         return False
 
 
-def _install_recompute(layer: nn.Module) -> None:
-    """Make ``layer(...)`` run under activation recomputation whenever grad is enabled.
+class _KeepPlan:
+    """Which layers of the operator-by-operator path keep their activations this pass.
+
+    Recomputing a layer costs a third more compute and, under context parallelism, repeats
+    its exchanges.  On a CUDA device the first layer of every pass therefore measures the free
+    memory and the layers that fit (minus the reserve of ``AGB200_ACTIVATION_RESERVE_GB``) run
+    without recomputation, the rest under it; ``AGB200_KEEP_ACTIVATIONS=never|always`` fixes
+    the choice.  Ranks that share a clip take the minimum over their group, so that all of
+    them issue the same collectives.
+    """
+
+    def __init__(self, group=None) -> None:
+        self.group = group
+        self.kept_layers = 0
+
+    def keeps(self, layer: nn.Module, args) -> bool:
+        from agentgarten_b200.ops import fused_layer
+
+        mode = fused_layer._KEEP_MODE
+        chunks = args[0]
+        index = args[3] if len(args) > 3 else None
+        if mode == "never" or index is None or not chunks[0].is_cuda:
+            return False
+        if mode == "always":
+            return True
+        if index == 0:
+            self.kept_layers = self._budget(layer, chunks)
+        return index < self.kept_layers
+
+    def _budget(self, layer: nn.Module, chunks) -> int:
+        from agentgarten_b200.ops import fused_layer
+
+        device = chunks[0].device
+        rows = sum(c.shape[0] * c.shape[1] for c in chunks)
+        hidden = chunks[0].shape[-1]
+        inner = layer.mlp_moe_gen.gate_proj.weight.shape[0]
+        heads = (layer.num_attention_heads + 2 * layer.num_key_value_heads) * layer.head_dim
+        # what autograd saves for one layer, operator by operator (bf16), with headroom for
+        # the exchanged copies under context parallelism
+        per_layer = int(rows * (8 * hidden + 4 * inner + 6 * heads) * 2 * 1.25)
+        free, _ = torch.cuda.mem_get_info(device)
+        free += torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+        fit = max(0, int((free - fused_layer._RESERVE_BYTES) // max(per_layer, 1)))
+        if self.group is not None and dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            agreed = torch.tensor([fit], device=device, dtype=torch.int64)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.group)
+            fit = int(agreed.item())
+        return fit
+
+
+def _install_recompute(layer: nn.Module, plan: _KeepPlan | None = None) -> None:
+    """Make ``layer(...)`` run under activation recomputation whenever grad is enabled and the
+    plan does not keep the layer's activations.
 
     Only the bound ``forward`` of the instance is replaced, so module names and state-dict
     keys stay exactly those of the plain layer.
@@ -151,6 +202,8 @@ def _install_recompute(layer: nn.Module) -> None:
 
     def forward(*args, **kwargs):
         if not torch.is_grad_enabled() or _recomputes_itself(layer, args, kwargs):
+            return inner(*args, **kwargs)
+        if plan is not None and plan.keeps(layer, args):
             return inner(*args, **kwargs)
         return checkpoint(inner, *args, use_reentrant=False, preserve_rng_state=True, **kwargs)
 
@@ -175,8 +228,9 @@ def parallelize_network(network: ParallelNetwork, config: ParallelConfig, device
     if mode is not ActivationCheckpointing.NONE:
         # The fused CUDA layer keeps attention outputs and recomputes the rest by itself
         # (= "selective"); the op-by-op path recomputes the whole layer.
+        plan = _KeepPlan(cp_mesh.get_group() if cp_mesh is not None else None)
         for layer in network.layers:
-            _install_recompute(layer)
+            _install_recompute(layer, plan)
     network.shard_mesh = shard_mesh
     network.parallel_config = config
     if on_meta:
