@@ -239,3 +239,21 @@ def test_encoded_video_is_decoded_by_the_available_backend(tmp_path):
     frames = _read_video(path)
     assert frames.shape == (3, 3, 8, 16) and frames.dtype == torch.uint8
     assert abs(int(frames[1].float().mean()) - 120) < 6
+
+
+def test_keep_plan_recomputes_on_cpu_and_obeys_the_switch(monkeypatch):
+    """Off the GPU every layer of the operator-by-operator path is recomputed; the switch
+    fixes the choice wherever the layers run."""
+    import torch
+
+    from agentgarten_b200.ops import fused_layer
+    from agentgarten_b200.parallel.engine import _KeepPlan
+
+    plan = _KeepPlan()
+    chunks = [torch.zeros(1, 4, 8)]
+    args = (chunks, None, None, 0, None)
+    assert plan.keeps(object(), args) is False
+    monkeypatch.setattr(fused_layer, "_KEEP_MODE", "never")
+    assert plan.keeps(object(), args) is False
+    monkeypatch.setattr(fused_layer, "_KEEP_MODE", "always")
+    assert plan.keeps(object(), args) is False  # CPU tensors: nothing to measure, recompute
