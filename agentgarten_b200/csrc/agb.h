@@ -255,6 +255,24 @@ cudaError_t colorize_depth(const float* depth, const float* scale, float* out, i
 cudaError_t decode_normal(const void* normal, float* out, int64_t batch, int64_t plane,
                           cudaStream_t stream);
 
+// ------------------------------------------------- all-to-all over peer memory (one node)
+// out[s] = block `rank` of rank s's `send`, for all s.  `recv[r]` is rank r's receive buffer
+// (2 * half_bytes, the same symmetric allocation on every rank), `arrive[r]` its arrival
+// counter; `count` (exchanges completed) and `ticket` (zero between launches) are local.
+struct ExchangeArgs {
+  const void* send;       // [world, bytes_per_rank]
+  void* out;              // [world, bytes_per_rank]
+  void* recv[8];
+  int* arrive[8];
+  int* count;
+  int* ticket;
+  int64_t bytes_per_rank;  // a multiple of 16
+  int64_t half_bytes;      // >= world * bytes_per_rank
+  int rank, world;
+  int* status;
+};
+cudaError_t exchange_all_to_all(const ExchangeArgs& args, int sm_count, cudaStream_t stream);
+
 // ----------------------------------------------------------- sharded optimizer (ZeRO)
 // Base pointers of the same flat buffer on every rank of the node (index = rank).
 struct ZeroPeers {

@@ -572,6 +572,35 @@ void tp_signal_done(std::vector<int64_t> done_ptrs, const Tensor& anchor) {
   check(agb::tp_signal_done(done, int(done_ptrs.size()), stream_of(anchor)), "tp_signal_done");
 }
 
+// All-to-all over peer memory: out[s] = send_of_rank_s[rank]; send / out are [world, ...] contiguous.
+void exchange(const Tensor& send, const Tensor& out, std::vector<int64_t> recv_ptrs,
+              std::vector<int64_t> arrive_ptrs, const Tensor& state, int64_t half_bytes, int64_t rank) {
+  TORCH_CHECK(send.is_cuda() && out.is_cuda() && send.is_contiguous() && out.is_contiguous() &&
+                  send.nbytes() == out.nbytes() && send.dim() >= 1,
+              "exchange: send and out are contiguous CUDA tensors of one size");
+  const int64_t world = int64_t(recv_ptrs.size());
+  TORCH_CHECK(world >= 1 && world <= 8 && arrive_ptrs.size() == recv_ptrs.size() && send.size(0) == world,
+              "exchange: 1..8 ranks, dim 0 of send is the destination rank");
+  TORCH_CHECK(state.is_cuda() && state.scalar_type() == torch::kInt32 && state.numel() >= 2 &&
+                  state.is_contiguous(), "exchange: state is int32 [2] (count, ticket)");
+  c10::cuda::CUDAGuard guard(send.device());
+  agb::ExchangeArgs a{};
+  a.send = send.data_ptr();
+  a.out = out.data_ptr();
+  for (int64_t i = 0; i < world; ++i) {
+    a.recv[i] = reinterpret_cast<void*>(recv_ptrs[i]);
+    a.arrive[i] = reinterpret_cast<int*>(arrive_ptrs[i]);
+  }
+  a.count = state.data_ptr<int>();
+  a.ticket = state.data_ptr<int>() + 1;
+  a.bytes_per_rank = int64_t(send.nbytes()) / world;
+  a.half_bytes = half_bytes;
+  a.rank = int(rank);
+  a.world = int(world);
+  a.status = status_word(send.device().index()).data_ptr<int>();
+  check(agb::exchange_all_to_all(a, sm_count(send.device().index()), stream_of(send)), "exchange");
+}
+
 agb::ZeroPeers peers_of(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(!ptrs.empty() && ptrs.size() <= 8, "1..8 peers supported");
   agb::ZeroPeers p{};
@@ -667,5 +696,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tp_gemm", &tp_gemm);
   m.def("tp_reduce_norm", &tp_reduce_norm);
   m.def("tp_signal_done", &tp_signal_done);
+  m.def("exchange", &exchange);
   m.def("status", &status);
 }

@@ -26,23 +26,29 @@ from .attention import TextContext
 __all__ = ["ContextParallel", "ContextParallelAttention"]
 
 
+def _all_to_all(value: torch.Tensor, group) -> torch.Tensor:
+    """Within a node on CUDA: peer stores and counters (``parallel/peer_exchange.py``); else NCCL / Gloo."""
+    from agentgarten_b200.parallel import peer_exchange
+
+    value = value.contiguous()
+    out = peer_exchange.exchange(value, group)
+    if out is None:
+        out = torch.empty_like(value)
+        dist.all_to_all_single(out, value, group=group)
+    return out
+
+
 class _Exchange(torch.autograd.Function):
     """``out[s] = in_of_rank_s[my_rank]`` over dim 0; its own transpose, hence its backward."""
 
     @staticmethod
     def forward(ctx, value: torch.Tensor, group) -> torch.Tensor:
         ctx.group = group
-        value = value.contiguous()
-        out = torch.empty_like(value)
-        dist.all_to_all_single(out, value, group=group)
-        return out
+        return _all_to_all(value, group)
 
     @staticmethod
     def backward(ctx, grad: torch.Tensor):
-        grad = grad.contiguous()
-        out = torch.empty_like(grad)
-        dist.all_to_all_single(out, grad, group=ctx.group)
-        return out, None
+        return _all_to_all(grad, ctx.group), None
 
 
 class _Gather(torch.autograd.Function):

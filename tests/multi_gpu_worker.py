@@ -146,6 +146,29 @@ def check_context_parallel_training(device, rank, world):
     assert worst < 5e-2, worst
 
 
+def check_peer_exchange(device, rank, world):
+    """The peer-memory all-to-all against the library collective: several sizes (one of them
+    larger than the first buffer, so that it grows), repeated so that both halves of the
+    receive buffer and the monotonic counters are reused."""
+    from agentgarten_b200.parallel import peer_exchange
+
+    group = dist.group.WORLD
+    torch.manual_seed(100 + rank)
+    for shape in ((world, 3, 40, 128), (world, 1, 8, 64), (world, 20000, 8, 128), (world, 3, 40, 128)):
+        for repeat in range(5):
+            value = torch.randn(shape, device=device).bfloat16()
+            want = torch.empty_like(value)
+            dist.all_to_all_single(want, value, group=group)
+            got = peer_exchange.exchange(value, group)
+            assert got is not None, "the peer path must apply to an NCCL group on one node"
+            assert torch.equal(got, want), (shape, repeat)
+    torch.cuda.synchronize()
+    from agentgarten_b200.ops import native
+    assert int(native.ext().status(device.index).item()) == 0
+    dist.barrier()
+    peer_exchange.release()
+
+
 def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     device = distributed.init(device="cuda", backend="nccl")
@@ -155,6 +178,8 @@ def main():
     check_tensor_parallel_stream(device, rank, world)
     dist.barrier()
     check_context_parallel_training(device, rank, world)
+    dist.barrier()
+    check_peer_exchange(device, rank, world)
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK")
