@@ -69,7 +69,14 @@ def _link(group, device: torch.device, nbytes: int):
             # every rank reaches this point for the same exchange: finish the old buffer first
             torch.cuda.synchronize(device)
             dist.barrier(group=group)
-        link = _links[key] = _Link(group, device, half)
+        try:
+            link = _links[key] = _Link(group, device, half)
+        except (RuntimeError, ImportError) as error:  # no symmetric memory for this group
+            from agentgarten_b200.utils import log
+
+            log.warning(f"peer-memory exchange unavailable ({error}); using the library collective")
+            _links[key] = False
+            return None
     return link
 
 
