@@ -28,7 +28,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
-from agentgarten_b200.ops.conv import conv_frames, conv_volume
+from agentgarten_b200.ops.conv import conv_frames, conv_volume, conv_volume_causal, eligible
 from agentgarten_b200.utils import log
 from agentgarten_b200.utils.misc import prefetch
 
@@ -96,6 +96,20 @@ def pixel_unfold(x: torch.Tensor, patch: int = 2) -> torch.Tensor:
     return x.reshape(b, c, t, h * patch, w * patch)
 
 
+def _channels_last(x: torch.Tensor) -> bool:
+    """Whether a ``[B, C, T, H, W]`` tensor is laid out ``[B, T, H, W, C]`` in memory."""
+    return x.ndim == 5 and x.permute(0, 2, 3, 4, 1).is_contiguous()
+
+
+def _zeros_like_frames(x: torch.Tensor, frames: int) -> torch.Tensor:
+    """``frames`` zero frames shaped like those of ``x``, in its memory layout (so that joining
+    them with ``x`` along time keeps a channels-last volume channels-last)."""
+    b, c, _, h, w = x.shape
+    if _channels_last(x):
+        return x.new_zeros(b, frames, h, w, c).permute(0, 4, 1, 2, 3)
+    return x.new_zeros(b, c, frames, h, w)
+
+
 class CausalConv3d(nn.Conv3d):
     """3-D convolution that never looks at later frames.
 
@@ -118,10 +132,19 @@ class CausalConv3d(nn.Conv3d):
         if need == 0:
             return conv_volume(self, x, residual)
         previous = state.history.get(self) if state is not None else None
+        if need == self.kernel_size[0] - 1 and eligible(self, x):
+            # the kernel reads the remembered frames where they are (zeros before them)
+            out = conv_volume_causal(self, x, previous, residual)
+            if state is not None:
+                have = 0 if previous is None else previous.shape[2]
+                keep = min(_HISTORY, have + x.shape[2])
+                recent = x if x.shape[2] >= keep else torch.cat([previous, x], dim=2)
+                state.history[self] = recent[:, :, -keep:].clone()
+            return out
         pieces = [x] if previous is None else [previous, x]
         have = 0 if previous is None else previous.shape[2]
         if have < need:
-            pieces.insert(0, x.new_zeros(x.shape[0], x.shape[1], need - have, *x.shape[3:]))
+            pieces.insert(0, _zeros_like_frames(x, need - have))
         joined = torch.cat(pieces, dim=2)
         if state is not None:
             keep = min(_HISTORY, have + x.shape[2])
@@ -240,9 +263,14 @@ class Resample(nn.Module):
     def forward(self, x: torch.Tensor, state: CausalState | None = None) -> torch.Tensor:
         if self.mode == "upsample3d" and state is not None and not state.first:
             b, c, t, h, w = x.shape
-            pair = self.time_conv(x, state).reshape(b, 2, c, t, h, w)
+            pair = self.time_conv(x, state)
             # Interleave the two predicted frames of every input frame along time.
-            x = pair.permute(0, 2, 3, 1, 4, 5).reshape(b, c, 2 * t, h, w)
+            if _channels_last(pair):
+                # [B, T, H, W, (2, C)] -> [B, (T, 2), H, W, C]: one copy, result channels-last
+                rows = pair.permute(0, 2, 3, 4, 1).reshape(b, t, h, w, 2, c)
+                x = rows.permute(0, 1, 4, 2, 3, 5).reshape(b, 2 * t, h, w, c).permute(0, 4, 1, 2, 3)
+            else:
+                x = pair.reshape(b, 2, c, t, h, w).permute(0, 2, 3, 1, 4, 5).reshape(b, c, 2 * t, h, w)
         x = self._frames(x)
         if self.mode == "downsample3d" and state is not None:
             last = x[:, :, -1:].clone()
@@ -288,6 +316,19 @@ class DuplicateUp(nn.Module):
     def forward(self, x: torch.Tensor, first: bool = False) -> torch.Tensor:
         ft, fs = self.ft, self.fs
         b, _, t, h, w = x.shape
+        block = ft * fs * fs
+        if _channels_last(x) and block % self.repeats == 0:
+            # Channels-last volumes: output channel co at block offset k reads input channel
+            # (co * block + k) // repeats = co * step + k // repeats, a strided slice; one copy
+            # per block offset writes the result in place, channels-last.
+            step = block // self.repeats
+            rows = x.permute(0, 2, 3, 4, 1)
+            out = rows.new_empty(b, t, ft, h, fs, w, fs, self.out_channels)
+            for k in range(block):
+                a, i, j = k // (fs * fs), (k // fs) % fs, k % fs
+                out[:, :, a, :, i, :, j, :] = rows[..., k // self.repeats::step]
+            out = out.view(b, t * ft, h * fs, w * fs, self.out_channels).permute(0, 4, 1, 2, 3)
+            return out[:, :, ft - 1:] if first else out
         x = x.repeat_interleave(self.repeats, dim=1)
         x = x.reshape(b, self.out_channels, ft, fs, fs, t, h, w).permute(0, 1, 5, 2, 6, 3, 7, 4)
         x = x.reshape(b, self.out_channels, t * ft, h * fs, w * fs)

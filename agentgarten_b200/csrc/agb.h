@@ -229,6 +229,11 @@ struct ConvArgs {
   int batch, frames_in, height, width, cin, cout;
   int kt, kh, kw;
   int relu, fp16;
+  // causal != 0: kt - 1 implicit frames precede x, so Tout = Tin.  The last `history_frames`
+  // of them are the frames of `history` ([B, history_frames, H, W, Cin]); those before are zero.
+  int causal;
+  const void* history;
+  int history_frames;
   int* status;
 };
 cudaError_t conv3d_bf16(const ConvArgs& args, int sm_count, cudaStream_t stream);

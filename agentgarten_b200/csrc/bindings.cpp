@@ -291,7 +291,8 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
 // [Cout, kt * kh * kw, Cin] -> [B, Tin - kt + 1, H, W, Cout] (+ bias [Cout], + residual like out,
 // then ReLU when asked); bf16 or fp16 throughout.
 Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
-              c10::optional<Tensor> residual, int64_t kt, int64_t kh, int64_t kw, bool relu) {
+              c10::optional<Tensor> residual, int64_t kt, int64_t kh, int64_t kw, bool relu,
+              c10::optional<Tensor> history, bool causal) {
   const auto dtype = x.scalar_type();
   TORCH_CHECK(x.is_cuda() && (dtype == torch::kBFloat16 || dtype == torch::kFloat16),
               "conv3d: x is a bf16 or fp16 CUDA tensor");
@@ -302,9 +303,9 @@ Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
   TORCH_CHECK(x.dim() == 5 && x.is_contiguous(), "conv3d: x is contiguous [B, T, H, W, Cin]");
   TORCH_CHECK(weight.dim() == 3 && weight.is_contiguous() && weight.size(1) == kt * kh * kw &&
                   weight.size(2) == x.size(4), "conv3d: weight is contiguous [Cout, taps, Cin]");
-  TORCH_CHECK(x.size(1) >= kt, "conv3d: fewer frames than the kernel is deep");
+  TORCH_CHECK(causal || x.size(1) >= kt, "conv3d: fewer frames than the kernel is deep");
   c10::cuda::CUDAGuard guard(x.device());
-  const int64_t frames_out = x.size(1) - kt + 1;
+  const int64_t frames_out = causal ? x.size(1) : x.size(1) - kt + 1;
   Tensor out = torch::empty({x.size(0), frames_out, x.size(2), x.size(3), weight.size(0)}, x.options());
   agb::ConvArgs a{};
   a.x = x.data_ptr();
@@ -326,6 +327,16 @@ Tensor conv3d(const Tensor& x, const Tensor& weight, c10::optional<Tensor> bias,
   a.kt = int(kt); a.kh = int(kh); a.kw = int(kw);
   a.relu = relu ? 1 : 0;
   a.fp16 = dtype == torch::kFloat16 ? 1 : 0;
+  a.causal = causal ? 1 : 0;
+  if (history.has_value() && history->size(1) > 0) {
+    same(*history, "history");
+    TORCH_CHECK(causal && history->dim() == 5 && history->is_contiguous() && history->size(0) == x.size(0) &&
+                    history->size(2) == x.size(2) && history->size(3) == x.size(3) &&
+                    history->size(4) == x.size(4) && history->size(1) <= kt - 1,
+                "conv3d: history is contiguous [B, <= kt - 1, H, W, Cin] of a causal call");
+    a.history = history->data_ptr();
+    a.history_frames = int(history->size(1));
+  }
   a.status = status_word(x.device().index()).data_ptr<int>();
   check(agb::conv3d_bf16(a, sm_count(x.device().index()), stream_of(x)), "conv3d");
   return out;

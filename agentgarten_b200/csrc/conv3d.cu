@@ -39,6 +39,7 @@ struct Params {
   int relu;
   int batch, frames_out, height, width, cin, cout;
   int kt, kh, kw, pad_h, pad_w;
+  int lead, hist;            // implicit leading frames of a causal call; how many of them are history
   int tile_w, tile_w_shift;  // patch width (a power of two) and its log2; patch height = 128 / width
   int tiles_w, tiles_h, tiles_n;
   int bn;                    // output channels per tile, a multiple of 32
@@ -81,7 +82,7 @@ __device__ __forceinline__ TileAt decode(int tile, const Params& p) {
 template <bool HALF>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-              const Params p) {
+              const __grid_constant__ CUtensorMap tm_h, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -116,6 +117,7 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   if (warp == 4 && lane == 0) {
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_h);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -138,7 +140,21 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const TileAt at = decode(tile, p);
         int tap = 0;
-        for (int dt = 0; dt < p.kt && ok; ++dt)
+        for (int dt = 0; dt < p.kt && ok; ++dt) {
+          // Frame dt of the window of output frame t.  A causal call sees `lead` implicit
+          // frames before x: the last `hist` of them come from the history tensor, the ones
+          // before read as zero (a coordinate in front of the tensor).
+          const int frame = at.t + dt;
+          const CUtensorMap* source = &tm_x;
+          int frame_at = frame - p.lead;
+          if (frame < p.lead) {
+            if (frame >= p.lead - p.hist) {
+              source = &tm_h;
+              frame_at = frame - (p.lead - p.hist);
+            } else {
+              frame_at = -1;
+            }
+          }
           for (int dh = 0; dh < p.kh && ok; ++dh)
             for (int dw = 0; dw < p.kw && ok; ++dw, ++tap)
               for (int cb = 0; cb < c_blocks; ++cb) {
@@ -149,14 +165,15 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 uint8_t* sa = smem + stage * STAGE_BYTES;
                 mbar_expect_tx(&full[stage], stage_tx);
                 armed |= 1u << stage;
-                tma_load_5d(sa, &tm_x, &full[stage], cb * BK, at.w0 + dw - p.pad_w,
-                            at.h0 + dh - p.pad_h, at.t + dt, at.b);
+                tma_load_5d(sa, source, &full[stage], cb * BK, at.w0 + dw - p.pad_w,
+                            at.h0 + dh - p.pad_h, frame_at, at.b);
                 tma_load_3d(sa + A_BYTES, &tm_w, &full[stage], cb * BK, tap, at.n0);
                 if (++stage == STAGES) {
                   stage = 0;
                   phase ^= 1;
                 }
               }
+        }
       }
       if (!ok || *abort_flag) {
         // Abort path: let this thread's copies land before the CTA's shared memory dies.
@@ -291,13 +308,19 @@ conv3d_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 
 // --------------------------------------------------------------------------------- host
 cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
-  const int frames_out = g.frames_in - g.kt + 1;
+  const int lead = g.causal ? g.kt - 1 : 0;
+  const int frames_out = g.frames_in + lead - g.kt + 1;
   if (g.batch <= 0 || frames_out <= 0 || g.height <= 0 || g.width <= 0) return cudaSuccess;
   if ((g.cin % 8) || (g.cout % 8) || !(g.kh & 1) || !(g.kw & 1) || g.kt < 1 ||
       (reinterpret_cast<uintptr_t>(g.x) & 15) || (reinterpret_cast<uintptr_t>(g.weight) & 15) ||
       (reinterpret_cast<uintptr_t>(g.out) & 15) || (reinterpret_cast<uintptr_t>(g.bias) & 15) ||
       (reinterpret_cast<uintptr_t>(g.residual) & 15)) {
     set_error_detail("conv3d: channels must be multiples of 8, spatial kernel sizes odd, pointers 16-byte aligned");
+    return cudaErrorInvalidValue;
+  }
+  if (g.history_frames < 0 || g.history_frames > lead || (g.history_frames > 0 && !g.history) ||
+      (reinterpret_cast<uintptr_t>(g.history) & 15)) {
+    set_error_detail("conv3d: history holds at most kt - 1 frames of a causal call");
     return cudaErrorInvalidValue;
   }
 
@@ -337,7 +360,7 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
 
-  CUtensorMap tx, tw;
+  CUtensorMap tx, tw, th;
   {
     const uint64_t dims[5] = {uint64_t(g.cin), uint64_t(g.width), uint64_t(g.height),
                               uint64_t(g.frames_in), uint64_t(g.batch)};
@@ -346,6 +369,13 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
                                  c * g.width * g.height * g.frames_in};
     const uint32_t box[5] = {64, uint32_t(p.tile_w), uint32_t(tile_h), 1, 1};
     if (!make_tensor_map_bf16(&tx, g.x, 5, dims, strides, box)) return cudaErrorInvalidValue;
+    th = tx;
+    if (g.history_frames > 0) {
+      const uint64_t hdims[5] = {dims[0], dims[1], dims[2], uint64_t(g.history_frames), dims[4]};
+      const uint64_t hstrides[4] = {c, c * g.width, c * g.width * g.height,
+                                    c * g.width * g.height * g.history_frames};
+      if (!make_tensor_map_bf16(&th, g.history, 5, hdims, hstrides, box)) return cudaErrorInvalidValue;
+    }
   }
   {
     const int taps = g.kt * g.kh * g.kw;
@@ -370,6 +400,8 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
   p.kw = g.kw;
   p.pad_h = g.kh / 2;
   p.pad_w = g.kw / 2;
+  p.lead = lead;
+  p.hist = g.history_frames;
   // fp16 operands: the A and B format fields of the descriptor are 0 instead of 1 (bf16)
   p.idesc = make_idesc_bf16(BM, p.bn, 0, 0) & (g.fp16 ? ~((1u << 7) | (1u << 10)) : ~0u);
   p.status = g.status;
@@ -390,9 +422,9 @@ cudaError_t conv3d_bf16(const ConvArgs& g, int sm_count, cudaStream_t stream) {
   (void)cudaGetLastError();
   const int grid = tiles < sm_count ? int(tiles) : sm_count;
   if (g.fp16)
-    conv3d_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, p);
+    conv3d_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, th, p);
   else
-    conv3d_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, p);
+    conv3d_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tx, tw, th, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_error_detail("conv3d: kernel launch failed");
   return e;

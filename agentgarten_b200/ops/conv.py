@@ -21,7 +21,7 @@ import torch.nn.functional as F
 
 from . import native
 
-__all__ = ["conv_frames", "conv_volume", "depthwise_frames", "eligible", "packed_weight"]
+__all__ = ["conv_frames", "conv_volume", "conv_volume_causal", "depthwise_frames", "eligible", "packed_weight"]
 
 
 def _weight_key(weight: torch.Tensor, dtype: torch.dtype) -> tuple:
@@ -88,15 +88,16 @@ def _finish(out: torch.Tensor, residual: torch.Tensor | None, relu: bool) -> tor
     return F.relu(out) if relu else out
 
 
-def _launch(conv, rows: torch.Tensor, residual: torch.Tensor | None, kernel: tuple, relu: bool) -> torch.Tensor:
+def _launch(conv, rows: torch.Tensor, residual: torch.Tensor | None, kernel: tuple, relu: bool,
+            history: torch.Tensor | None = None, causal: bool = False) -> torch.Tensor:
     """The kernel on channels-last rows ``[B, T, H, W, Cin]`` -> ``[B, T', H, W, Cout]``."""
     weight, bias = packed_weight(conv, rows.dtype)
     padded = weight.shape[0] != conv.out_channels
     native.count()
     if padded and (residual is not None or relu):
-        out = native.ext().conv3d(rows, weight, bias, None, *kernel, False)[..., : conv.out_channels]
-        return _finish(out, residual, relu)
-    out = native.ext().conv3d(rows, weight, bias, residual, *kernel, relu)
+        out = native.ext().conv3d(rows, weight, bias, None, *kernel, False, history, causal)
+        return _finish(out[..., : conv.out_channels], residual, relu)
+    out = native.ext().conv3d(rows, weight, bias, residual, *kernel, relu, history, causal)
     return out[..., : conv.out_channels] if padded else out
 
 
@@ -107,6 +108,19 @@ def conv_volume(conv: torch.nn.Conv3d, x: torch.Tensor, residual: torch.Tensor |
         out = F.conv3d(x, conv.weight, conv.bias, conv.stride, conv.padding, conv.dilation, conv.groups)
         return _finish(out, residual, relu)
     out = _launch(conv, _rows(x), None if residual is None else _rows(residual), conv.kernel_size, relu)
+    return out.permute(0, 4, 1, 2, 3)
+
+
+def conv_volume_causal(conv: torch.nn.Conv3d, x: torch.Tensor, history: torch.Tensor | None,
+                       residual: torch.Tensor | None = None, relu: bool = False) -> torch.Tensor:
+    """Causal form for ``eligible`` calls: the ``kt - 1`` frames before ``x`` are the last frames
+    of ``history`` (``[B, C, <= kt - 1, H, W]`` or ``None``) preceded by zeros; the kernel reads
+    them where they are, nothing is joined.  Returns as many frames as ``x`` has."""
+    past = None
+    if history is not None and history.shape[2] > 0:
+        past = _rows(history[:, :, -(conv.kernel_size[0] - 1):])
+    out = _launch(conv, _rows(x), None if residual is None else _rows(residual), conv.kernel_size, relu,
+                  history=past, causal=True)
     return out.permute(0, 4, 1, 2, 3)
 
 

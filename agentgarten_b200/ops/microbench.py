@@ -127,7 +127,7 @@ def bench_conv(tokens: int, launches: int) -> list[dict]:
         x = torch.randn(1, frames + 2, height, width, channels, device="cuda", dtype=torch.bfloat16)
         weight = torch.randn(channels, channels, 3, 3, 3, device="cuda", dtype=torch.bfloat16) * 0.01
         packed = weight.permute(0, 2, 3, 4, 1).reshape(channels, 27, channels).contiguous()
-        ms = _time(lambda: native.ext().conv3d(x, packed, None, None, 3, 3, 3, False), launches)
+        ms = _time(lambda: native.ext().conv3d(x, packed, None, None, 3, 3, 3, False, None, False), launches)
         logical = x.permute(0, 4, 1, 2, 3)
         cl_weight = weight.contiguous(memory_format=torch.channels_last_3d)
         library = _time(lambda: torch.nn.functional.conv3d(logical, cl_weight, padding=(0, 1, 1)), launches)

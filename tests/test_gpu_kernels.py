@@ -367,7 +367,7 @@ def test_conv_kernel_matches_fp32_convolution(cin, cout, kernel, frames, height,
     bias = torch.randn(cout, device=DEV).to(dtype) if extras else None
     packed = weight.permute(0, 2, 3, 4, 1).reshape(cout, -1, cin).contiguous()
     residual = torch.randn(2, frames - kt + 1, height, width, cout, device=DEV).to(dtype) if extras else None
-    out = native.ext().conv3d(x, packed, bias, residual, kt, kh, kw, relu)
+    out = native.ext().conv3d(x, packed, bias, residual, kt, kh, kw, relu, None, False)
     _status_ok()
     want = torch.nn.functional.conv3d(x.float().permute(0, 4, 1, 2, 3), weight.float(),
                                       None if bias is None else bias.float(), padding=(0, kh // 2, kw // 2))
@@ -379,6 +379,26 @@ def test_conv_kernel_matches_fp32_convolution(cin, cout, kernel, frames, height,
     assert out.shape == want.shape and out.dtype == dtype
     assert _rel(out, want) < 6e-3, _rel(out, want)
     assert (out.float() - want).abs().max() < 0.06
+
+
+@pytest.mark.parametrize("history_frames", [0, 1, 2])
+def test_causal_conv_reads_history_in_place(history_frames):
+    """The causal form (zeros, then history, then the chunk, none of them joined) against the
+    convolution of the joined volume."""
+    torch.manual_seed(history_frames)
+    cin, cout, frames, height, width = 64, 96, 3, 10, 18
+    x = torch.randn(2, frames, height, width, cin, device=DEV).bfloat16()
+    history = torch.randn(2, history_frames, height, width, cin, device=DEV).bfloat16() if history_frames else None
+    weight = (torch.randn(cout, cin, 3, 3, 3, device=DEV) / (27 * cin) ** 0.5).bfloat16()
+    packed = weight.permute(0, 2, 3, 4, 1).reshape(cout, -1, cin).contiguous()
+    out = native.ext().conv3d(x, packed, None, None, 3, 3, 3, False, history, True)
+    _status_ok()
+    pieces = [torch.zeros(2, 2 - history_frames, height, width, cin, device=DEV).bfloat16()]
+    pieces += [history] if history is not None else []
+    joined = torch.cat(pieces + [x], dim=1)
+    want = native.ext().conv3d(joined, packed, None, None, 3, 3, 3, False, None, False)
+    assert out.shape == want.shape == (2, frames, height, width, cout)
+    assert torch.equal(out, want)
 
 
 def test_conv_modules_use_the_kernel_and_match():
