@@ -295,8 +295,15 @@ class AverageDown(nn.Module):
         ft, fs = self.ft, self.fs
         lead = -x.shape[2] % ft
         if lead:
-            x = torch.cat([x.new_zeros(*x.shape[:2], lead, *x.shape[3:]), x], dim=2)
+            x = torch.cat([_zeros_like_frames(x, lead), x], dim=2)
         b, c, t, h, w = x.shape
+        if _channels_last(x):
+            # [B, T, H, W, C] rows: gather each block behind its channel, average the groups;
+            # the result is channels-last again.
+            rows = x.permute(0, 2, 3, 4, 1).reshape(b, t // ft, ft, h // fs, fs, w // fs, fs, c)
+            rows = rows.permute(0, 1, 3, 5, 7, 2, 4, 6).reshape(
+                b, t // ft, h // fs, w // fs, self.out_channels, self.group)
+            return rows.mean(dim=-1).permute(0, 4, 1, 2, 3)
         x = x.reshape(b, c, t // ft, ft, h // fs, fs, w // fs, fs).permute(0, 1, 3, 5, 7, 2, 4, 6)
         x = x.reshape(b, self.out_channels, self.group, t // ft, h // fs, w // fs)
         return x.mean(dim=2)

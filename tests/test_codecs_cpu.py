@@ -144,3 +144,32 @@ def test_convolution_helpers_fall_back_to_the_library_definition():
     packed, bias = packed_weight(frames, torch.float32)
     assert packed.shape == (16, 9, 8) and bias.shape == (16,)
     assert torch.equal(packed[:12, 4], frames.weight[:, :, 1, 1]) and not packed[12:].any()
+
+
+def test_channels_last_forms_of_the_shortcuts_match_the_planar_forms():
+    """The parameter-free shortcuts and the temporal interleave have a path for channels-last
+    volumes (what the convolution kernels produce); it computes the same values and keeps the layout."""
+    from agentgarten_b200.codecs.wan22 import AverageDown, CausalState, DuplicateUp, Resample, _channels_last
+
+    torch.manual_seed(0)
+    for cin, cout, ft in ((16, 16, 2), (16, 8, 2), (32, 8, 1), (16, 16, 1)):
+        up = DuplicateUp(cin, cout, ft, 2)
+        x = torch.randn(2, cin, 3, 4, 5)
+        packed = x.contiguous(memory_format=torch.channels_last_3d)
+        for first in (False, True):
+            got = up(packed, first=first)
+            assert torch.equal(got, up(x, first=first))
+        assert _channels_last(up(packed))
+    for cin, cout, ft, frames in ((8, 16, 2, 4), (8, 8, 1, 3), (16, 16, 2, 3), (8, 32, 2, 2)):
+        down = AverageDown(cin, cout, ft, 2)
+        x = torch.randn(2, cin, frames, 4, 6)
+        got = down(x.contiguous(memory_format=torch.channels_last_3d))
+        assert _channels_last(got) and torch.allclose(got, down(x), atol=1e-6)
+    resample = Resample(8, "upsample3d")
+    x = torch.randn(1, 8, 3, 4, 5)
+    outputs = []
+    for value in (x, x.contiguous(memory_format=torch.channels_last_3d)):
+        state = CausalState()
+        state.advance()  # past the first chunk: the temporal doubling is active
+        outputs.append(resample(value, state))
+    assert outputs[0].shape == (1, 8, 6, 8, 10) and torch.allclose(outputs[0], outputs[1], atol=1e-6)
