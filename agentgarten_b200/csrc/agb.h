@@ -61,7 +61,7 @@ struct TpLink {
 };
 cudaError_t gemm_bf16(const GemmArgs& args, int sm_count, cudaStream_t stream);
 
-// Owner side of the tensor-parallel residual stream, one CTA per four owned rows:
+// Owner side of the tensor-parallel residual stream, one CTA per owned row or per four owned rows:
 //   h = bf16(residual_row + sum over source ranks (in rank order) of slot[src][row])
 //   hidden_own[row] = h;  x = weight * bf16(h * rsqrt(mean(h^2) + eps))
 //   x is stored into xbuf[peer][global_row] on every rank (peer stores), then ready[peer][tile]
@@ -89,6 +89,7 @@ struct TpReduceArgs {
   float eps;
   void* xbuf[8];           // bf16 [ceil(m/128)*128, width] on every rank
   int* ready[8];           // int32 [ceil(m/128)] on every rank
+  int rows_per_cta;        // 0: chosen from the number of owned rows; 1 or 4
   int* status;
 };
 cudaError_t tp_reduce_norm(const TpReduceArgs& args, cudaStream_t stream);

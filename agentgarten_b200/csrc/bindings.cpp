@@ -537,7 +537,8 @@ void tp_reduce_norm(int64_t rank, int64_t world, int64_t m, const Tensor& slot, 
                     const Tensor& arrive_seen, const Tensor& ticket, int64_t arrivals_per_source,
                     const Tensor& hidden_own, c10::optional<Tensor> seed, const Tensor& weight,
                     double eps, std::vector<int64_t> xbuf_ptrs, std::vector<int64_t> ready_ptrs,
-                    int64_t tiles_owned, const Tensor& done, const Tensor& done_uses) {
+                    int64_t tiles_owned, const Tensor& done, const Tensor& done_uses,
+                    int64_t rows_per_cta) {
   check_bf16(hidden_own, "hidden_own");
   check_bf16(weight, "weight");
   c10::cuda::CUDAGuard guard(hidden_own.device());
@@ -563,6 +564,7 @@ void tp_reduce_norm(int64_t rank, int64_t world, int64_t m, const Tensor& slot, 
     TORCH_CHECK(seed->is_contiguous() && seed->numel() == m * hidden_own.size(1), "seed must be [m, width]");
     a.seed = seed->data_ptr();
   }
+  a.rows_per_cta = int(rows_per_cta);
   a.done = done.data_ptr<int>();
   a.done_uses = done_uses.data_ptr<int>();
   a.weight = weight.data_ptr();

@@ -14,9 +14,11 @@ namespace agb {
 namespace {
 
 constexpr int NT = 256;
-constexpr int ROWS = 4;              // rows per CTA: one wait, one fence and one signal for all four
-constexpr int ROW_THREADS = NT / ROWS;  // 64 threads (two warps) walk one row
-constexpr int MAX_CHUNKS = 16;       // width <= ROW_THREADS * 8 * MAX_CHUNKS = 8192 (8 chunks up to 4096)
+// Rows per CTA.  Four rows (two warps each) share one wait, one fence and one signal: best when
+// a rank owns many rows.  With few rows (many ranks) one row per CTA, walked by all eight
+// warps, has the shorter critical path.
+constexpr int MANY_ROWS = 4;
+constexpr int MAX_WIDTH = 8192;
 
 __device__ __forceinline__ float round_bf16(float v) {
   return __bfloat162float(__float2bfloat16_rn(v));
@@ -34,11 +36,14 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
                     pack_bf16(f[6], f[7]));
 }
 
-template <int CHUNKS>
+// ROWS rows per CTA, NT / ROWS threads per row, CHUNKS 16-byte vectors per thread and row.
+template <int ROWS, int CHUNKS>
 __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a) {
+  constexpr int ROW_THREADS = NT / ROWS;
+  constexpr int ROW_WARPS = ROW_THREADS / 32;
   __shared__ float scratch[NT / 32];
   __shared__ int proceed;
-  // Four consecutive rows of one owned tile (128 is a multiple of ROWS).
+  // ROWS consecutive rows of one owned tile (128 is a multiple of ROWS).
   const int sub = threadIdx.x / ROW_THREADS;      // row of this thread inside the CTA's group
   const int lane = threadIdx.x % ROW_THREADS;
   const int first_local = blockIdx.x * ROWS;      // row inside this rank's owned tiles
@@ -120,8 +125,9 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a
     for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = sumsq;
     __syncthreads();
-    // the two warps of a row
-    const float total = scratch[2 * sub] + scratch[2 * sub + 1];
+    float total = 0.f;  // over the warps of this row
+#pragma unroll
+    for (int w = 0; w < ROW_WARPS; ++w) total += scratch[ROW_WARPS * sub + w];
     if (live) {
       const float rstd = rsqrtf(total / float(a.width) + a.eps);
       const __nv_bfloat16* weight = static_cast<const __nv_bfloat16*>(a.weight);
@@ -179,17 +185,28 @@ __global__ void tp_signal_done_kernel(const DonePeers peers, int world) {
 }  // namespace
 
 cudaError_t tp_reduce_norm(const TpReduceArgs& a, cudaStream_t stream) {
-  if (a.world < 1 || a.world > 8 || a.width % 8 || a.width > ROW_THREADS * 8 * MAX_CHUNKS || a.m <= 0) {
-    set_error_detail("tp_reduce_norm: world 1..8, width a multiple of 8 up to 8192");
+  if (a.world < 1 || a.world > 8 || a.width % 8 || a.width > MAX_WIDTH || a.m <= 0 ||
+      (a.rows_per_cta != 0 && a.rows_per_cta != 1 && a.rows_per_cta != MANY_ROWS)) {
+    set_error_detail("tp_reduce_norm: world 1..8, width a multiple of 8 up to 8192, rows per CTA 0 (auto), 1 or 4");
     return cudaErrorInvalidValue;
   }
   const int rows = a.tiles_owned * 128;
   if (rows == 0) return cudaSuccess;
   (void)cudaGetLastError();
-  if (a.width <= ROW_THREADS * 8 * (MAX_CHUNKS / 2))
-    tp_reduce_norm_kernel<MAX_CHUNKS / 2><<<rows / ROWS, NT, 0, stream>>>(a);
-  else
-    tp_reduce_norm_kernel<MAX_CHUNKS><<<rows / ROWS, NT, 0, stream>>>(a);
+  // auto: four rows per CTA once that still gives every SM two CTAs
+  const int per_cta = a.rows_per_cta ? a.rows_per_cta : (rows / MANY_ROWS >= 2 * 148 ? MANY_ROWS : 1);
+  const bool narrow = a.width <= MAX_WIDTH / 2;
+  if (per_cta == MANY_ROWS) {
+    if (narrow)
+      tp_reduce_norm_kernel<MANY_ROWS, 8><<<rows / MANY_ROWS, NT, 0, stream>>>(a);
+    else
+      tp_reduce_norm_kernel<MANY_ROWS, 16><<<rows / MANY_ROWS, NT, 0, stream>>>(a);
+  } else {
+    if (narrow)
+      tp_reduce_norm_kernel<1, 2><<<rows, NT, 0, stream>>>(a);
+    else
+      tp_reduce_norm_kernel<1, 4><<<rows, NT, 0, stream>>>(a);
+  }
   return cudaGetLastError();
 }
 

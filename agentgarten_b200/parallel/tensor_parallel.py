@@ -67,6 +67,8 @@ class TensorParallelServing:
         self.kv_slice = slice(self.rank * self.kv_heads, (self.rank + 1) * self.kv_heads)
         self._shard_weights()
         self._allocate()
+        # Rows per CTA of the reduce kernel: 0 lets the kernel choose from the rows a rank owns.
+        self.reduce_rows = 0
         # Set to a dict to collect (start, stop) CUDA events per phase of run() (eager mode only).
         self.trace: dict[str, list] | None = None
 
@@ -150,7 +152,7 @@ class TensorParallelServing:
         native.ext().tp_reduce_norm(
             self.rank, self.world, m, self.slots, self.arrive, self.slot_seen, self.reduce_ticket,
             4 * -(-self.hidden // _COLUMN_TILE), self.hidden_own, seed, weight, self.eps,
-            self.x_ptrs, self.ready_ptrs, owned, self.done, self.steps)
+            self.x_ptrs, self.ready_ptrs, owned, self.done, self.steps, self.reduce_rows)
 
     def _gather_gemm(self, x: torch.Tensor, weight: torch.Tensor, *, close: bool) -> torch.Tensor:
         out = torch.empty(x.shape[0], weight.shape[0], dtype=torch.bfloat16, device=x.device)

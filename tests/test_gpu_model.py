@@ -191,8 +191,9 @@ def _stream_outputs(net, condition, latent, policy, **serving):
     return outs
 
 
+@pytest.mark.parametrize("reduce_rows", [1, 4])
 @pytest.mark.parametrize("tokens", [101, 130, 387])
-def test_tensor_parallel_run_with_ragged_row_counts(tokens):
+def test_tensor_parallel_run_with_ragged_row_counts(tokens, reduce_rows):
     """Row counts that fill neither a tile of 128 nor a group of four rows: the tensor-parallel
     kernels (one rank) against the layer-by-layer path on the same tokens."""
     from agentgarten_b200 import ops
@@ -202,6 +203,7 @@ def test_tensor_parallel_run_with_ragged_row_counts(tokens):
     config = _config()
     net = tiny_network(config, device="cpu", seed=0).to(DEV, torch.bfloat16).eval()
     plan = TensorParallelServing(net, None, max_tokens=512)
+    plan.reduce_rows = reduce_rows  # both forms of the reduce kernel
     hidden = torch.randn(1, tokens, config.hidden_size, device=DEV).bfloat16()
     positions = torch.stack((torch.arange(tokens) // 24, (torch.arange(tokens) // 6) % 4, torch.arange(tokens) % 6),
                             dim=-1).unsqueeze(0).to(DEV)
