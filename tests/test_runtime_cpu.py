@@ -257,3 +257,18 @@ def test_keep_plan_recomputes_on_cpu_and_obeys_the_switch(monkeypatch):
     assert plan.keeps(object(), args) is False
     monkeypatch.setattr(fused_layer, "_KEEP_MODE", "always")
     assert plan.keeps(object(), args) is False  # CPU tensors: nothing to measure, recompute
+
+
+def test_peer_exchange_declines_what_it_cannot_serve(monkeypatch):
+    """CPU tensors, a switched-off path and an uninitialised process group fall through to the
+    library collective (the function returns None and allocates nothing)."""
+    import torch
+
+    from agentgarten_b200.parallel import peer_exchange
+
+    value = torch.zeros(2, 4, 8)
+    assert peer_exchange.exchange(value, None) is None
+    monkeypatch.setenv("AGB200_NCCL_EXCHANGE", "1")
+    assert peer_exchange.exchange(value, None) is None
+    assert not peer_exchange._links
+    peer_exchange.release()
