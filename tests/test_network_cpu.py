@@ -113,3 +113,21 @@ def test_fused_adam_matches_torch_adamw():
     zero.grad = torch.ones(3)
     no_moment.step()
     assert "exp_avg" not in no_moment.state[zero]
+
+
+def test_adaln_operators_fall_back_to_the_operator_sequence():
+    """Off the GPU (and whenever gradients are wanted) the AdaLN helpers are the plain expressions."""
+    import torch
+
+    from agentgarten_b200 import ops
+
+    torch.manual_seed(0)
+    x, y = torch.randn(2, 5, 16), torch.randn(2, 5, 16)
+    weight = torch.rand(16) + 0.5
+    shift, scale, gate = (0.3 * torch.randn(2, 5, 48)).chunk(3, dim=-1)
+    want = ops.rms_norm(x, weight, 1e-6) * (1 + scale) + shift
+    assert torch.equal(ops.norm_modulate(x, weight, scale, shift, 1e-6), want)
+    assert torch.equal(ops.gated_residual(x, gate, y), x + gate * y)
+    x.requires_grad_()
+    ops.norm_modulate(x, weight, scale, shift, 1e-6).sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad).all()
