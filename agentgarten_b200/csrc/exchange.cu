@@ -56,14 +56,14 @@ __global__ void __launch_bounds__(NT) exchange_pull_kernel(const ExchangeArgs a)
   __shared__ int proceed;
   const int count = *reinterpret_cast<volatile int*>(a.count);
   if (threadIdx.x == 0) {
-    const int target = (count + 1) * a.world;
+    const int target = static_cast<int>((static_cast<unsigned>(count) + 1u) * static_cast<unsigned>(a.world));
     const int* counter = a.arrive[a.rank];
     int go = 1;
     const uint64_t start = global_timer_ns();
     for (;;) {
       int seen;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-      if (seen - target >= 0) break;
+      if (counter_reached(seen, target)) break;
       if (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) {
         go = 0;  // an earlier wait on this device already ran out: do not spend the limit again
         break;
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(NT) exchange_pull_kernel(const ExchangeArgs a)
     if (atomicAdd(a.ticket, 1) == int(gridDim.x) - 1) {
       *a.ticket = 0;
       // The exchange is counted even when it failed, so that the ranks stay in step.
-      *reinterpret_cast<volatile int*>(a.count) = count + 1;
+      *reinterpret_cast<volatile int*>(a.count) = counter_add(count, 1);
       __threadfence();
     }
   }

@@ -52,7 +52,7 @@ __device__ __forceinline__ bool wait_counter(const int* counter, int target, con
   for (;;) {
     int seen;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-    if (seen - target >= 0) return true;
+    if (counter_reached(seen, target)) return true;
     if (*g.abort_flag) return false;
     // A wait that already ran out on this device (this launch or an earlier one) means the step
     // is lost: give up at once instead of spending the limit again in every CTA and launch.
@@ -140,7 +140,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
         if (p.tp.wait_a) {
           // Rows of this A tile are pushed into local memory by their owner; the counter
           // counts rows.  The copy below reads them through the async proxy.
-          const int target = reinterpret_cast<volatile int*>(p.tp.a_seen)[tm] + min(BM, p.m - m0);
+          const int target =
+              counter_add(reinterpret_cast<volatile int*>(p.tp.a_seen)[tm], min(BM, p.m - m0));
           if (!wait_counter(p.tp.a_ready + tm, target, guard)) {
             ok = false;
             break;
@@ -388,7 +389,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     if (atomicAdd(p.tp.ticket, 1) == int(gridDim.x) - 1) {
       *p.tp.ticket = 0;
       volatile int* seen = reinterpret_cast<volatile int*>(p.tp.a_seen);
-      for (int t = 0; t < p.tiles_m; ++t) seen[t] = seen[t] + min(BM, p.m - t * BM);
+      for (int t = 0; t < p.tiles_m; ++t) seen[t] = counter_add(seen[t], min(BM, p.m - t * BM));
       __threadfence();
     }
   }

@@ -268,6 +268,14 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// Monotonic 32-bit counters wrap after long runs; "reached" is decided on the wrapped difference.
+__device__ __forceinline__ int counter_add(int value, int amount) {
+  return static_cast<int>(static_cast<unsigned>(value) + static_cast<unsigned>(amount));
+}
+__device__ __forceinline__ bool counter_reached(int seen, int target) {
+  return static_cast<int>(static_cast<unsigned>(seen) - static_cast<unsigned>(target)) >= 0;
+}
+
 // --------------------------------------------------------------------------- small math
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

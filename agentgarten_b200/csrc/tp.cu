@@ -62,13 +62,15 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a
       // of every rank's previous step.
       const int* counter = a.seed ? a.done : a.arrive + local_tile;
       const int target = a.seed
-          ? a.world * *reinterpret_cast<volatile int*>(a.done_uses)
-          : reinterpret_cast<volatile int*>(a.arrive_seen)[local_tile] + a.world * a.arrivals_per_source;
+          ? static_cast<int>(static_cast<unsigned>(a.world) *
+                             static_cast<unsigned>(*reinterpret_cast<volatile int*>(a.done_uses)))
+          : counter_add(reinterpret_cast<volatile int*>(a.arrive_seen)[local_tile],
+                        a.world * a.arrivals_per_source);
       const uint64_t start = global_timer_ns();
       for (;;) {
         int seen;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
-        if (seen - target >= 0) break;
+        if (counter_reached(seen, target)) break;
         // A wait that already ran out on this device (this launch or an earlier one) means the
         // step is lost: give up at once instead of spending the limit again in every CTA.
         if (a.status && *reinterpret_cast<volatile int*>(a.status) != 0) {
@@ -161,11 +163,12 @@ __global__ void __launch_bounds__(NT) tp_reduce_norm_kernel(const TpReduceArgs a
       *a.ticket = 0;
       if (a.seed) {
         volatile int* steps = reinterpret_cast<volatile int*>(a.done_uses);
-        *steps = *steps + 1;
+        *steps = counter_add(*steps, 1);
       } else {
         volatile int* seen = reinterpret_cast<volatile int*>(a.arrive_seen);
         for (int t = 0; t < a.tiles_owned; ++t)
-          if ((int64_t(t) * a.world + a.rank) * 128 < a.m) seen[t] = seen[t] + a.world * a.arrivals_per_source;
+          if ((int64_t(t) * a.world + a.rank) * 128 < a.m)
+            seen[t] = counter_add(seen[t], a.world * a.arrivals_per_source);
       }
       __threadfence();
     }
