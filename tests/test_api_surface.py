@@ -111,3 +111,29 @@ def test_signatures_users_rely_on():
     assert isinstance(Cosmos3Stream.keys, property) and isinstance(Cosmos3Stream.values, property)
     policy = StreamPolicy()
     assert (policy.block_frames, policy.sink_frames, policy.history_frames, policy.train_frames) == (4, 5, 44, 61)
+
+
+def test_bench_reference_arm_reports_unavailable_and_exits_zero():
+    """The reference build cannot be installed offline: its arm prints one JSON line saying so."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    done = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--gpus", "1",
+                           "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=120)
+    assert done.returncode == 0, done.stderr
+    line = json.loads(done.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and "unavailable" in line
+
+
+def test_graft_entry_exposes_build_and_smoke():
+    import importlib.util
+    from pathlib import Path
+
+    path = Path(__file__).resolve().parents[1] / "__graft_entry__.py"
+    spec = importlib.util.spec_from_file_location("graft_entry_under_test", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    assert callable(module.build) and callable(module.smoke)
