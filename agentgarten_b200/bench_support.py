@@ -60,12 +60,14 @@ class TrainingJob:
         p = self.config.patch_size
         return self.frames * (self.latent_hw[0] // p) * (self.latent_hw[1] // p)
 
-    def step(self, batch: dict[str, Any]) -> torch.Tensor:
-        """One optimizer update; returns the (device) loss of the last microbatch."""
+    def step(self, batch: dict[str, Any], stage: Any = None) -> torch.Tensor:
+        """One optimizer update; returns the (device) loss of the last microbatch.  ``stage``
+        (optional) maps the batch to the device copy of one microbatch, so that every
+        microbatch of an end-to-end measurement makes its own host-to-device transfer."""
         model, optimizer = self.model, self.optimizer
         loss = None
         for _ in range(self.grad_accum_steps):
-            encoded = model.prepare_data_batch(batch)
+            encoded = model.prepare_data_batch(batch if stage is None else stage(batch))
             _, loss = model.training_step(encoded, 0)
             (loss / self.grad_accum_steps).backward()
         norm_sq = optimizer.grad_norm_sq()

@@ -126,14 +126,45 @@ class Cosmos3Stream:
         self._graph_pool = None
         self.reset()
 
-    def reset(self) -> None:
+    def reset(self, release: bool = False) -> None:
+        """Forget the semantic history.  A bounded stream keeps its K/V arenas and the step
+        graphs captured over them, so the next ``start`` with a prompt of the same length and
+        the same frame geometry replays them at once; ``release=True`` (and any change of
+        prompt length or geometry) frees both."""
+        keep = (not release and getattr(self, "layers", None)
+                and self.policy.history_frames is not None)
         self.text: TextContext | None = None
-        self.layers: list[StreamAttentionCache] = []
+        if keep:
+            for layer in self.layers:
+                layer.clear()
+        else:
+            self.layers: list[StreamAttentionCache] = []
+            self._graphs: dict[tuple, _StepGraph] = {}
         self.frame_ids: tuple[int, ...] = ()
         self.next_frame = 0
         self.positions: torch.Tensor | None = None
         self.grid = (0, 0)
-        self._graphs: dict[tuple, _StepGraph] = {}
+
+    @torch.inference_mode()
+    def capture_graphs(self, anchor: torch.Tensor, anchor_condition: Cosmos3Condition,
+                       block_condition: Cosmos3Condition) -> None:
+        """Runs the stream once over enough blocks to visit every cache fill level (and both
+        arenas of the full cache), so that all step graphs exist before the first real block;
+        ends with a ``reset`` that keeps them.  Needs a bounded policy and CUDA graphs."""
+        policy = self.policy
+        if not self.cuda_graphs or policy.history_frames is None:
+            return
+        self.reset()
+        self.start(anchor, anchor_condition)
+        shape = list(anchor.shape)
+        shape[2] = policy.block_frames
+        block = torch.zeros(shape, device=anchor.device, dtype=anchor.dtype)
+        sigma = torch.ones((1,), device=anchor.device)
+        fills = -(-max(policy.capacity - 1, 0) // policy.block_frames)  # blocks until the cache is full
+        for _ in range(fills + 3):
+            self.denoise(block, sigma, block_condition)
+            self.commit(block, block_condition)
+        self.reset()
 
     @property
     def keys(self) -> list[torch.Tensor]:
@@ -160,6 +191,17 @@ class Cosmos3Stream:
         self.text = condition.text
         patch = self.network.config.patch_size
         self.grid = (anchor.shape[-2] // patch, anchor.shape[-1] // patch)
+        signature = (self.grid, self.text.lengths[0], tuple(condition.depth.shape[-2:]), anchor.dtype)
+        if self.layers:  # arenas kept by reset(): reusable only for the same geometry and prompt length
+            if signature == self._arena_signature and len(self.layers) == len(self.text.keys):
+                n, heads = self.text.lengths[0], self._local_kv_heads()
+                for layer, key, value in zip(self.layers, self.text.keys, self.text.values):
+                    layer.update_text(key[:, :n, heads], value[:, :n, heads])
+            else:
+                self.reset(release=True)
+                self.text = condition.text
+                self.grid = signature[0]
+        self._arena_signature = signature
         self._run(anchor, None, condition, record=True, reference=True)
         self.next_frame = 1
         self.frame_ids = (0,)

@@ -36,6 +36,7 @@ class StreamAttentionCache:
         self.value[:, : self.text_tokens].copy_(text_v)
         self.frames = 0
         self._spare: tuple[torch.Tensor, torch.Tensor] | None = None
+        self._swapped = False  # True while the second arena is the live one
 
     # ------------------------------------------------------------------------ views
     def _visual(self, store: torch.Tensor) -> torch.Tensor:
@@ -88,7 +89,16 @@ class StreamAttentionCache:
         relocate(self.value[:, text:used], value[:, text:], sink, shift)
         self._spare = self.key, self.value
         self.key, self.value = key, value
+        self._swapped = not self._swapped
         self.frames -= evicted_frames
+
+    def clear(self) -> None:
+        """Forget the visual history but keep both arenas (and their addresses, which the
+        captured step graphs of a stream refer to); the first arena becomes the live one again."""
+        if self._swapped:
+            (self.key, self.value), self._spare = self._spare, (self.key, self.value)
+            self._swapped = False
+        self.frames = 0
 
     def update_text(self, key: torch.Tensor, value: torch.Tensor) -> None:
         self.key[:, : self.text_tokens].copy_(key)

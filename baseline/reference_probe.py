@@ -1,0 +1,165 @@
+"""Golden outputs of the UNMODIFIED reference package for the parity tests.
+
+Runs with ``PYTHONPATH=baseline/_ref:baseline/shims`` (nothing of ``agentgarten_b200`` is
+imported).  ``network`` mode builds a small generation tower and text tower on the CPU in
+FP32, runs ``forward``, ``forward_ar`` (diffusion and teacher forcing), a cached rollout
+(``prefill`` / ``denoise`` / ``commit``) and a streamed block, and writes the state dicts,
+the inputs and every output to one ``torch.save`` file.  ``train`` mode runs seeded
+optimizer updates through the reference ``Trainer`` and writes the loss sequence and the
+final parameters.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import torch
+
+
+def tiny_config():
+    from wm.networks.cosmos3 import Cosmos3Config
+
+    return Cosmos3Config(hidden_size=256, intermediate_size=1024, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=128,
+                         mrope_section=(12, 10, 10), text_bucket_tokens=16,
+                         special_tokens={"eos_token_id": 1, "start_of_generation": 2})
+
+
+def seeded_(module: torch.nn.Module, seed: int) -> None:
+    g = torch.Generator().manual_seed(seed)
+    with torch.no_grad():
+        for name, p in module.named_parameters():
+            if p.ndim >= 2 or "embed" in name:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+            elif "norm" in name:
+                p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g))
+            else:
+                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+
+
+def batch_of(frames: int, seed: int = 0):
+    g = torch.Generator().manual_seed(seed)
+    shape = (1, 48, frames, 8, 8)
+    return {"latent": torch.randn(shape, generator=g), "depth_latent": torch.randn(shape, generator=g),
+            "normal_latent": torch.randn(shape, generator=g),
+            "text_input_ids": torch.randint(3, 128, (1, 10), generator=g), "fps": torch.full((1,), 16.0)}
+
+
+def network_mode(path: str) -> None:
+    from wm.codecs import Wan22VAECodec
+    from wm.models.flow import rf_interpolate
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+    from wm.networks.cosmos3.network import Cosmos3Condition
+    from wm.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+
+    config = tiny_config()
+    net = build_network(config, init_device="cpu").float().eval()
+    seeded_(net, 0)
+    cond = Cosmos3Conditioner(config=config, codec=Wan22VAECodec(pretrained_path="unused", decoder=None),
+                              geometry_noise_sigma=0.0, init_device="cpu", empty_prompt_ids=(3, 4, 5)).float()
+    seeded_(cond.text_encoder, 1)
+    batch = cond.encode(batch_of(9), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    g = torch.Generator().manual_seed(5)
+    noise = torch.randn(latent.shape, generator=g)
+    out: dict = {"net": net.state_dict(), "text_encoder": cond.text_encoder.state_dict(),
+                 "batch": batch_of(9), "noise": noise}
+    with torch.no_grad():
+        sigma = torch.tensor([0.7])
+        noisy = rf_interpolate(latent, noise, sigma)
+        noisy[:, :, :1] = latent[:, :, :1]
+        out["forward"] = net(noisy, sigma, condition, known_frames=1)
+        block_sigma = torch.tensor([[0.9] * 4 + [0.3] * 4])
+        targets = rf_interpolate(latent[:, :, 1:], noise[:, :, 1:], block_sigma)
+        out["block_sigma"] = block_sigma
+        out["forward_ar"] = net.forward_ar(latent[:, :, :1], targets, block_sigma, condition,
+                                           block_frames=4)
+        out["forward_ar_teacher"] = net.forward_ar(latent[:, :, :1], targets, block_sigma, condition,
+                                                   block_frames=4, clean=latent[:, :, 1:])
+        cache = net.prefill(latent[:, :, :1], condition)
+        first = net.denoise(cache, targets[:, :, :4], torch.tensor([0.9]))
+        cache = net.commit(cache, latent[:, :, 1:5])
+        second = net.denoise(cache, targets[:, :, 4:], torch.tensor([0.3]))
+        out["cached"] = (first, second)
+
+        def part(lo: int, hi: int) -> Cosmos3Condition:
+            return Cosmos3Condition(text=condition.text, depth=condition.depth[:, :, lo:hi],
+                                    normal=condition.normal[:, :, lo:hi], fps=condition.fps)
+
+        stream = Cosmos3Stream(net, StreamPolicy(block_frames=4, sink_frames=1, history_frames=4,
+                                                 rope="top_aligned", train_frames=9))
+        stream.start(latent[:, :, :1], part(0, 1))
+        streamed = []
+        for block in range(2):
+            lo, hi = 1 + 4 * block, 5 + 4 * block
+            streamed.append(stream.denoise(targets[:, :, lo - 1:hi - 1], torch.tensor([0.6]), part(lo, hi)))
+            stream.commit(latent[:, :, lo:hi], part(lo, hi))
+        out["streamed"] = tuple(streamed)
+        out["stream_keys"] = [key.clone() for key in stream.keys]
+    torch.save(out, path)
+
+
+def train_mode(path: str, steps: int) -> None:
+    from wm.codecs import Wan22VAECodec
+    from wm.infra.callbacks import CallbackGroup, GradClip
+    from wm.infra.config import LazyCall
+    from wm.infra.optim import FusedAdam, LinearWarmup
+    from wm.infra.parallel import ParallelConfig
+    from wm.infra.trainer import Trainer
+    from wm.models.diffusion import DiffusionModel
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    model = DiffusionModel(
+        net=build_network(config, init_device="cpu"),
+        conditioner=Cosmos3Conditioner(config=config, geometry_noise_sigma=0.0, init_device="cpu",
+                                       empty_prompt_ids=(3, 4, 5),
+                                       codec=Wan22VAECodec(pretrained_path="unused", decoder=None)),
+        text_dropout=0.1, parallel=plain, conditioner_parallel=plain)
+    model.parallelize("cpu")
+    seeded_(model.net, 0)
+    seeded_(model.conditioner.text_encoder, 1)
+    model.train()
+    optimizer = FusedAdam(model._group_trainable_parameters(), lr=1e-3, betas=(0.9, 0.99), eps=1e-8,
+                          weight_decay=0.01, adam_w_mode=True, use_te_capturable_kernel=True,
+                          master_weights=True)
+    scheduler = torch.optim.lr_scheduler.LambdaLR(
+        optimizer, lr_lambda=LinearWarmup(warmup_steps=4, start_factor=0.1))
+    model.optimizer_dict, model.scheduler_dict = {"net": optimizer}, {"net": scheduler}
+    callbacks = CallbackGroup(
+        {"trainer": {"callbacks": {"grad_clip": LazyCall(GradClip)(max_norm=1.0)}}}, trainer=None)
+    trainer = Trainer(grad_accum_steps=2, callbacks=callbacks, device=torch.device("cpu"))
+    scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+    torch.manual_seed(1234)
+    losses = []
+    for step in range(steps):
+        for micro in range(2):
+            data = trainer._prepare_data_batch(model, batch_of(5, seed=10 * step + micro))
+            result = trainer.training_step(model, scaler, data, iteration=step, grad_accum_step=micro)
+            losses.append(float(result.loss))
+    torch.save({"losses": losses, "net": model.net.state_dict(),
+                "lr": optimizer.param_groups[0]["lr"]}, path)
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("mode", choices=["network", "train"])
+    parser.add_argument("output")
+    parser.add_argument("--steps", type=int, default=5)
+    args = parser.parse_args()
+    torch.manual_seed(0)
+    torch.set_num_threads(max(1, min(4, os.cpu_count() or 1)))
+    if args.mode == "network":
+        network_mode(args.output)
+    else:
+        train_mode(args.output, args.steps)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -22,9 +22,10 @@ import subprocess
 import sys
 import time
 
-REFERENCE_UNAVAILABLE = (
-    "reference not installable offline: build backend hatchling and runtime dependencies "
-    "hydra-core/omegaconf/transformer-engine are absent from the wheelhouse")
+ROOT = os.path.dirname(os.path.abspath(__file__))
+REFERENCE_ROOT = os.path.join(ROOT, "baseline", "_ref")
+REFERENCE_SHIMS = os.path.join(ROOT, "baseline", "shims")
+REFERENCE_RUNNER = os.path.join(ROOT, "baseline", "reference_train.py")
 
 
 def parse_args() -> argparse.Namespace:
@@ -42,6 +43,10 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--context-parallel", type=int, default=1,
                         help="ranks that share one clip (divides --gpus); 1 = data parallel only")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--grad-accum", type=int, default=1,
+                        help="microbatches per optimizer update (the headline uses 1)")
+    parser.add_argument("--reference-args", default="",
+                        help="extra arguments for baseline/reference_train.py (debugging)")
     return parser.parse_args()
 
 
@@ -91,11 +96,45 @@ class ClockSampler:
                 "samples": len(clocks), "reasons": sorted(reasons)}
 
 
+def reference_environment() -> dict[str, str]:
+    """Environment of the reference process: its import path holds the unmodified reference
+    package and the stand-ins for its two missing dependencies, nothing of this package."""
+    env = dict(os.environ)
+    env["PYTHONPATH"] = os.pathsep.join((REFERENCE_ROOT, REFERENCE_SHIMS))
+    env.pop("PYTHONSTARTUP", None)
+    return env
+
+
+def run_reference(args: argparse.Namespace) -> int:
+    """Replaces this process with ``baseline/reference_train.py`` (one per rank, so the
+    launcher's RANK / WORLD_SIZE / MASTER_* reach it unchanged)."""
+    reason = None
+    if not os.path.isfile(os.path.join(REFERENCE_ROOT, "wm", "__init__.py")):
+        reason = ("the reference package is not installed under baseline/_ref "
+                  "(copy the reference's wm/ directory there)")
+    elif args.recipe != "bidirectional" or args.context_parallel != 1:
+        reason = "the reference arm covers the bidirectional data-parallel recipe only"
+    if reason is not None:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": reason}))
+        return 0
+    command = [sys.executable, REFERENCE_RUNNER, "--gpus", str(args.gpus), "--steps", str(args.steps),
+               "--warmup", str(args.warmup), "--layers", str(args.layers),
+               "--frames", str(args.frames or 21), "--grad-accum", str(args.grad_accum)]
+    if args.no_e2e:
+        command.append("--no-e2e")
+    if args.reference_args:
+        command.extend(args.reference_args.split())
+    sys.stdout.flush()
+    os.chdir(os.path.join(ROOT, "baseline"))
+    os.execve(sys.executable, command, reference_environment())
+    return 0  # not reached
+
+
 def main() -> int:
     args = parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": REFERENCE_UNAVAILABLE}))
-        return 0
+        return run_reference(args)
 
     import torch
     import torch.distributed as dist
@@ -121,10 +160,14 @@ def main() -> int:
         raise SystemExit(f"--context-parallel {cp} does not divide {world} ranks")
     job = build_training_job(device, layers=args.layers, frames=frames, recipe=args.recipe,
                              context_parallel=cp)
+    job.grad_accum_steps = max(1, args.grad_accum)
     # the ranks that share a clip get the same batch and draw the same noise
     host_batch = synthetic_batch(job, "cpu", seed=1000 + rank // cp, pinned=True)
     torch.manual_seed(77 + rank // cp)
     device_batch = {k: v.to(device) for k, v in host_batch.items()}
+
+    def to_device(batch):
+        return {k: v.to(device, non_blocking=True) for k, v in batch.items()}
 
     def barrier() -> None:
         if world > 1:
@@ -158,8 +201,7 @@ def main() -> int:
         barrier()
         start.record()
         for _ in range(args.steps):
-            staged = {k: v.to(device, non_blocking=True) for k, v in host_batch.items()}
-            loss_value = float(job.step(staged).item())  # device -> host read of the result
+            loss_value = float(job.step(host_batch, stage=to_device).item())  # device -> host read
         stop.record()
         barrier()
         e2e_ms = start.elapsed_time(stop)
@@ -171,7 +213,7 @@ def main() -> int:
     status = int(native.ext().status(device.index or 0).item())
 
     if rank == 0:
-        tokens = job.rgb_tokens_per_clip * (world // cp) * args.steps
+        tokens = job.rgb_tokens_per_clip * (world // cp) * args.steps * job.grad_accum_steps
         value = tokens / (elapsed_ms / 1e3)
         line = {
             "metric": "train latent-tokens/s/box (bidirectional rectified flow)"
@@ -215,7 +257,7 @@ def main() -> int:
                 "value": tokens / (e2e_max / 1e3),
                 "unit": "latent RGB tokens/s",
                 "ms_per_step": e2e_max / args.steps,
-                "h2d_bytes_per_step": batch_bytes(host_batch),
+                "h2d_bytes_per_step": batch_bytes(host_batch) * job.grad_accum_steps,
                 "d2h_bytes_per_step": 4,
             }
         print(json.dumps(line))

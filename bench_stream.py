@@ -3,7 +3,12 @@
 Anchor ``[1, 48, 1, 30, 52]``, then ``--blocks`` blocks of 4 latent frames, each with fresh
 depth/normal latents, 4 denoise steps at the sigma endpoints (1.0, 0.75, 0.5, 0.25) followed
 by a commit into a bounded cache of 6 blocks plus the anchor.  Prints one JSON line with the
-p50 / p99 milliseconds per block (device time, CUDA events around each block).
+p50 / p99 milliseconds per block (device time, CUDA events around each block) over ALL
+``--blocks`` blocks: a first, untimed pass over nine blocks captures the CUDA graph of every
+cache fill level, then the stream is reset and the timed pass starts from a fresh anchor.
+
+``--impl reference`` runs the unmodified reference package on one GPU through
+``baseline/reference_stream.py`` (same workload, its own kernels and graphs).
 
 On several GPUs (``python -m torch.distributed.run --nproc-per-node N ... bench_stream.py``)
 the tower is tensor parallel over the ranks: every rank feeds the same seeded inputs, the
@@ -26,9 +31,33 @@ def main() -> int:
     parser.add_argument("--tensor-parallel", action="store_true")
     parser.add_argument("--trace", action="store_true",
                         help="eager run with per-phase CUDA events of the tensor-parallel layers")
+    parser.add_argument("--impl", default="agentgarten_b200", choices=["agentgarten_b200", "reference"])
     args = parser.parse_args()
 
     import os
+    import sys
+
+    if args.impl == "reference":
+        root = os.path.dirname(os.path.abspath(__file__))
+        if not os.path.isfile(os.path.join(root, "baseline", "_ref", "wm", "__init__.py")):
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the reference package is not installed under baseline/_ref"}))
+            return 0
+        if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable":
+                                  "the reference streams on one GPU only (it has no tensor parallelism)"}))
+            return 0
+        env = dict(os.environ)
+        env["PYTHONPATH"] = os.pathsep.join((os.path.join(root, "baseline", "_ref"),
+                                             os.path.join(root, "baseline", "shims")))
+        command = [sys.executable, os.path.join(root, "baseline", "reference_stream.py"),
+                   "--blocks", str(args.blocks), "--layers", str(args.layers)]
+        if args.no_graphs:
+            command.append("--no-graphs")
+        sys.stdout.flush()
+        os.chdir(os.path.join(root, "baseline"))
+        os.execve(sys.executable, command, env)
 
     import torch
     import torch.distributed as dist
@@ -76,7 +105,10 @@ def main() -> int:
 
     endpoints = (1.0, 0.75, 0.5, 0.25)
     stream = Cosmos3Stream(net, policy)
-    stream.start(torch.randn((1, 48, 1, 30, 52), device=device, generator=g), condition(1))
+    anchor = torch.randn((1, 48, 1, 30, 52), device=device, generator=g)
+    # every fill-level graph is captured here, before the timed blocks
+    stream.capture_graphs(anchor, condition(1), condition(4))
+    stream.start(anchor, condition(1))
     times = []
     launches_before = native.launches()
     for block in range(args.blocks):
@@ -113,7 +145,7 @@ def main() -> int:
     if rank != 0:
         dist.destroy_process_group()
         return 0
-    steady = times[8:] if len(times) > 12 else times
+    steady = times  # all blocks count: the graphs were captured before the first one
     steady_sorted = sorted(steady)
     print(json.dumps({
         "metric": "Cosmos3Stream ms per 4-frame block (4 denoise + 1 commit)",

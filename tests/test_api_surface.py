@@ -113,19 +113,45 @@ def test_signatures_users_rely_on():
     assert (policy.block_frames, policy.sink_frames, policy.history_frames, policy.train_frames) == (4, 5, 44, 61)
 
 
-def test_bench_reference_arm_reports_unavailable_and_exits_zero():
-    """The reference build cannot be installed offline: its arm prints one JSON line saying so."""
+def test_bench_reference_arm_runs_the_unmodified_reference_package():
+    """``bench.py --impl reference`` trains a tiny network on the CPU through the reference's
+    own package (imported from ``baseline/_ref``), in a process that loads nothing of this one."""
     import json
+    import os
     import subprocess
     import sys
     from pathlib import Path
 
+    import pytest
+
     root = Path(__file__).resolve().parents[1]
+    if not (root / "baseline" / "_ref" / "wm" / "__init__.py").exists():
+        pytest.skip("the reference package is not installed under baseline/_ref")
+    tiny = ("--device cpu --hidden 256 --intermediate 512 --heads 2 --kv-heads 1 --vocab 2048 "
+            "--latent-hw 8 8 --text-tokens 12")
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     done = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--gpus", "1",
-                           "--steps", "2", "--warmup", "3"], capture_output=True, text=True, timeout=120)
-    assert done.returncode == 0, done.stderr
+                           "--steps", "2", "--warmup", "3", "--layers", "2", "--frames", "3",
+                           "--reference-args", tiny], capture_output=True, text=True, timeout=600, env=env)
+    assert done.returncode == 0, done.stderr[-2000:]
     line = json.loads(done.stdout.strip().splitlines()[-1])
-    assert line["impl"] == "reference" and "unavailable" in line
+    assert line["impl"] == "reference" and "unavailable" not in line, line
+    assert line["value"] > 0 and line["e2e"]["value"] > 0 and line["e2e"]["h2d_bytes_per_step"] > 0
+    assert line["loss"] == line["loss"]  # finite, not NaN
+
+    probe = ("import sys, wm; import wm.infra.trainer; "
+             "print(wm.__file__); print(any('agentgarten_b200' in m for m in sys.modules))")
+    sys.path.insert(0, str(root))
+    try:
+        import bench
+    finally:
+        sys.path.pop(0)
+    seen = subprocess.run([sys.executable, "-c", probe], capture_output=True, text=True, timeout=300,
+                          env=bench.reference_environment(), cwd=str(root / "baseline"))
+    assert seen.returncode == 0, seen.stderr[-2000:]
+    where, leaked = seen.stdout.strip().splitlines()[-2:]
+    assert Path(where).resolve() == (root / "baseline" / "_ref" / "wm" / "__init__.py").resolve()
+    assert leaked == "False"
 
 
 def test_graft_entry_exposes_build_and_smoke():

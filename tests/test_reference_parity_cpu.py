@@ -1,0 +1,162 @@
+"""Parity with the UNMODIFIED reference package on the CPU.
+
+The reference runs in a child process whose import path holds only ``baseline/_ref`` and the
+stand-ins of ``baseline/shims`` (``baseline/reference_probe.py``); this process loads the
+state dicts it wrote into this package's modules and compares outputs, loss sequences and
+updated parameters.
+"""
+
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+REFERENCE = ROOT / "baseline" / "_ref"
+
+pytestmark = pytest.mark.skipif(not (REFERENCE / "wm" / "__init__.py").exists(),
+                                reason="the reference package is not installed under baseline/_ref")
+
+
+def reference_env():
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    env["PYTHONPATH"] = os.pathsep.join((str(REFERENCE), str(ROOT / "baseline" / "shims")))
+    return env
+
+
+def probe(mode: str, path: Path, *extra: str):
+    done = subprocess.run([sys.executable, str(ROOT / "baseline" / "reference_probe.py"), mode, str(path),
+                           *extra], capture_output=True, text=True, timeout=900, env=reference_env(),
+                          cwd=str(ROOT / "baseline"))
+    assert done.returncode == 0, done.stderr[-3000:]
+    return torch.load(path, weights_only=False)
+
+
+def tiny_config():
+    from agentgarten_b200.networks.cosmos3 import Cosmos3Config
+
+    return Cosmos3Config(hidden_size=256, intermediate_size=1024, num_hidden_layers=2,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=64, vocab_size=128,
+                         mrope_section=(12, 10, 10), text_bucket_tokens=16,
+                         special_tokens={"eos_token_id": 1, "start_of_generation": 2})
+
+
+def batch_of(frames: int, seed: int = 0):
+    g = torch.Generator().manual_seed(seed)
+    shape = (1, 48, frames, 8, 8)
+    return {"latent": torch.randn(shape, generator=g), "depth_latent": torch.randn(shape, generator=g),
+            "normal_latent": torch.randn(shape, generator=g),
+            "text_input_ids": torch.randint(3, 128, (1, 10), generator=g), "fps": torch.full((1,), 16.0)}
+
+
+def test_network_outputs_equal_the_reference(tmp_path):
+    """forward, forward_ar (both forcing modes), the cached rollout and a bounded stream with
+    eviction give the reference's outputs from the reference's state dict."""
+    from agentgarten_b200.models.flow import rf_interpolate
+    from agentgarten_b200.networks.cosmos3 import build_network
+    from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
+    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+
+    golden = probe("network", tmp_path / "network.pt")
+    config = tiny_config()
+    net = build_network(config, init_device="cpu").float().eval()
+    net.load_state_dict(golden["net"], strict=True)
+    cond = Cosmos3Conditioner(config=config, codec=None, geometry_noise_sigma=0.0, init_device="cpu",
+                              empty_prompt_ids=(3, 4, 5)).float()
+    cond.text_encoder.load_state_dict(golden["text_encoder"], strict=True)
+    batch = cond.encode(golden["batch"], training=False)
+    condition = cond.condition(batch)
+    latent, noise = batch["latent"], golden["noise"]
+    tol = dict(atol=1e-5, rtol=1e-5)
+    with torch.no_grad():
+        sigma = torch.tensor([0.7])
+        noisy = rf_interpolate(latent, noise, sigma)
+        noisy[:, :, :1] = latent[:, :, :1]
+        assert torch.allclose(net(noisy, sigma, condition, known_frames=1), golden["forward"], **tol)
+        block_sigma = golden["block_sigma"]
+        targets = rf_interpolate(latent[:, :, 1:], noise[:, :, 1:], block_sigma)
+        out = net.forward_ar(latent[:, :, :1], targets, block_sigma, condition, block_frames=4)
+        assert torch.allclose(out, golden["forward_ar"], **tol)
+        out = net.forward_ar(latent[:, :, :1], targets, block_sigma, condition, block_frames=4,
+                             clean=latent[:, :, 1:])
+        assert torch.allclose(out, golden["forward_ar_teacher"], **tol)
+        cache = net.prefill(latent[:, :, :1], condition)
+        first = net.denoise(cache, targets[:, :, :4], torch.tensor([0.9]))
+        cache = net.commit(cache, latent[:, :, 1:5])
+        second = net.denoise(cache, targets[:, :, 4:], torch.tensor([0.3]))
+        assert torch.allclose(first, golden["cached"][0], **tol)
+        assert torch.allclose(second, golden["cached"][1], **tol)
+
+        def part(lo, hi):
+            return Cosmos3Condition(text=condition.text, depth=condition.depth[:, :, lo:hi],
+                                    normal=condition.normal[:, :, lo:hi], fps=condition.fps)
+
+        stream = Cosmos3Stream(net, StreamPolicy(block_frames=4, sink_frames=1, history_frames=4,
+                                                 rope="top_aligned", train_frames=9))
+        stream.start(latent[:, :, :1], part(0, 1))
+        for block in range(2):
+            lo, hi = 1 + 4 * block, 5 + 4 * block
+            got = stream.denoise(targets[:, :, lo - 1:hi - 1], torch.tensor([0.6]), part(lo, hi))
+            assert torch.allclose(got, golden["streamed"][block], **tol)
+            stream.commit(latent[:, :, lo:hi], part(lo, hi))
+        for mine, theirs in zip(stream.keys, golden["stream_keys"], strict=True):
+            assert torch.allclose(mine, theirs, **tol)  # evicted and re-rotated history
+
+
+def test_seeded_training_repeats_the_reference_loss_sequence(tmp_path):
+    """Five optimizer updates (two microbatches each, text dropout, gradient clipping, AdamW with
+    FP32 masters, warm-up schedule) through this package's Trainer give the reference's losses
+    and parameters."""
+    from agentgarten_b200.infra.callbacks import CallbackGroup, GradClip
+    from agentgarten_b200.infra.config import LazyCall
+    from agentgarten_b200.infra.optim import FusedAdam, LinearWarmup
+    from agentgarten_b200.infra.trainer import Trainer
+    from agentgarten_b200.models.diffusion import DiffusionModel
+    from agentgarten_b200.networks.cosmos3 import build_network
+    from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
+    from agentgarten_b200.parallel.engine import ParallelConfig
+
+    golden = probe("train", tmp_path / "train.pt", "--steps", "5")
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        from reference_probe import seeded_
+    finally:
+        sys.path.pop(0)
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    model = DiffusionModel(
+        net=build_network(config, init_device="cpu"),
+        conditioner=Cosmos3Conditioner(config=config, codec=None, geometry_noise_sigma=0.0,
+                                       init_device="cpu", empty_prompt_ids=(3, 4, 5)),
+        text_dropout=0.1, parallel=plain, conditioner_parallel=plain)
+    model.parallelize("cpu")
+    seeded_(model.net, 0)
+    seeded_(model.conditioner.text_encoder, 1)
+    model.train()
+    optimizer = FusedAdam(model._group_trainable_parameters(), lr=1e-3, betas=(0.9, 0.99), eps=1e-8,
+                          weight_decay=0.01, adam_w_mode=True, use_te_capturable_kernel=True,
+                          master_weights=True)
+    scheduler = torch.optim.lr_scheduler.LambdaLR(
+        optimizer, lr_lambda=LinearWarmup(warmup_steps=4, start_factor=0.1))
+    model.optimizer_dict, model.scheduler_dict = {"net": optimizer}, {"net": scheduler}
+    callbacks = CallbackGroup(
+        {"trainer": {"callbacks": {"grad_clip": LazyCall(GradClip)(max_norm=1.0)}}}, trainer=None)
+    trainer = Trainer(grad_accum_steps=2, callbacks=callbacks, device=torch.device("cpu"))
+    scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+    torch.manual_seed(1234)
+    losses = []
+    for step in range(5):
+        for micro in range(2):
+            data = model.prepare_data_batch(batch_of(5, seed=10 * step + micro))
+            result = trainer.training_step(model, scaler, data, iteration=step, grad_accum_step=micro)
+            losses.append(float(result.loss))
+    assert losses == pytest.approx(golden["losses"], rel=2e-5, abs=2e-6)
+    assert optimizer.param_groups[0]["lr"] == pytest.approx(golden["lr"])
+    mine = model.net.state_dict()
+    for name, theirs in golden["net"].items():
+        assert torch.allclose(mine[name], theirs, atol=2e-5, rtol=1e-4), name

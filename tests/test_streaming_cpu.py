@@ -123,3 +123,47 @@ def test_reference_images_condition_a_block_without_touching_the_cache():
     assert torch.allclose(stream.denoise(noisy, sigma, block), plain, atol=1e-6)
     with pytest.raises(ValueError):
         denoise_with_references(stream, noisy, sigma, block, [torch.randn(1, 48, 2, 8, 8)])
+
+
+def test_reset_keeps_the_arenas_and_a_restarted_stream_repeats_its_outputs():
+    """A bounded stream that is reset and started again on the same prompt replays the same
+    velocities from the kept arenas; ``release=True`` and a changed geometry drop them."""
+    cfg = tiny_config()
+    net = tiny_network(cfg).eval()
+    cond = tiny_conditioner(cfg)
+    batch = cond.encode(synthetic_batch(frames=17), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, rope="top_aligned",
+                          train_frames=13)
+    stream = Cosmos3Stream(net, policy)
+    torch.manual_seed(3)
+    noise = torch.randn_like(latent)
+
+    def run():
+        stream.start(latent[:, :, :1], _block_condition(condition, 0, 1))
+        outs = []
+        for b in range(4):  # the last two commits evict (an odd number of arena swaps)
+            lo, hi = 1 + 4 * b, 5 + 4 * b
+            block = _block_condition(condition, lo, hi)
+            outs.append(stream.denoise(noise[:, :, lo:hi], torch.tensor([0.8]), block))
+            stream.commit(latent[:, :, lo:hi], block)
+        return outs
+
+    first = run()
+    arenas = [layer.key.data_ptr() for layer in stream.layers]
+    stream.reset()
+    assert stream.next_frame == 0 and stream.frame_ids == () and stream.text is None
+    assert all(layer.frames == 0 for layer in stream.layers) and len(stream.layers) == len(net.layers)
+    second = run()
+    assert [layer.key.data_ptr() for layer in stream.layers] == arenas
+    for a, b in zip(first, second):
+        assert torch.equal(a, b)
+    stream.reset(release=True)
+    assert stream.layers == []
+    run()
+    stream.reset()
+    # another frame geometry cannot reuse the arenas: they are rebuilt on start
+    small = cond.condition(cond.encode(synthetic_batch(frames=5, height=4, width=4), training=False))
+    stream.start(torch.randn(1, 48, 1, 4, 4), _block_condition(small, 0, 1))
+    assert stream.layers[0].frames == 1 and stream.grid == (2, 2)
