@@ -37,6 +37,7 @@ from typing import Any
 import torch
 import torch.distributed as dist
 
+from agentgarten_b200.ops import kernel_status
 from agentgarten_b200.infra.rng_state import (capture_distributed_rng_state,
                                               restore_distributed_rng_state,
                                               validate_distributed_rng_state)
@@ -161,6 +162,10 @@ class DistributedCheckpointer:
 
         self._wait(coordinate=True)
         root = _unwrap(model)
+        # never write parameters that a timed-out kernel left incomplete (all ranks agree)
+        some = next(iter(root.parameters()), None)
+        if some is not None:
+            kernel_status.raise_for_status(kernel_status.read(some.device), "checkpoint save")
         name = f"iter_{int(iteration):09d}"
         directory = self.save_dir / name
         rng = capture_distributed_rng_state()
@@ -209,16 +214,21 @@ class DistributedCheckpointer:
 
     # ------------------------------------------------------------------------ load
     def _resolve(self, path: str | Path | None) -> Path | None:
-        if path is not None:
-            path = Path(path)
-            pointer = path / "latest"
-            if pointer.is_file():
-                return path / pointer.read_text().strip()
-            return path
+        """``None`` loads nothing; the literal ``"latest"`` follows ``save_dir/latest`` (a missing
+        or empty pointer is an error; an absolute target is taken as it is, a relative one is
+        under ``save_dir``); anything else names the checkpoint directory itself."""
+        if path is None:
+            return None
+        if str(path) != "latest":
+            return Path(path)
         pointer = self.save_dir / "latest"
-        if pointer.is_file():
-            return self.save_dir / pointer.read_text().strip()
-        return None
+        if not pointer.is_file():
+            raise FileNotFoundError(f"No latest checkpoint pointer at {pointer}")
+        target = pointer.read_text().strip()
+        if not target:
+            raise FileNotFoundError(f"Latest checkpoint pointer is empty: {pointer}")
+        target_path = Path(target)
+        return target_path if target_path.is_absolute() else self.save_dir / target_path
 
     def load(self, model: torch.nn.Module, optimizers: Mapping[str, Any] | None = None,
              schedulers: Mapping[str, Any] | None = None, grad_scaler: Any = None, *,
@@ -231,12 +241,17 @@ class DistributedCheckpointer:
         import torch.distributed.checkpoint as dcp
         from torch.distributed.checkpoint import DefaultLoadPlanner
 
-        decision: list[Any] = [None]
+        decision: list[Any] = [None, None]
         if rank() == 0:
-            found = self._resolve(path)
-            decision = [None if found is None else str(found)]
+            try:
+                found = self._resolve(path)
+                decision = [None if found is None else str(found), None]
+            except FileNotFoundError as error:
+                decision = [None, str(error)]
         if world_size() > 1:
             dist.broadcast_object_list(decision, src=0)
+        if decision[1] is not None:  # every rank fails together
+            raise FileNotFoundError(decision[1])
         if decision[0] is None:
             return LoadResult()
         directory = Path(decision[0])

@@ -58,28 +58,47 @@ def _names(model: torch.nn.Module) -> dict[int, str]:
 
 
 def _shard_mesh(optimizer):
+    """Device mesh of the engine's shard group, for wrapping state chunks as DTensors.
+
+    One node: the 1-D mesh over the shard group's ranks.  Several nodes (state sharded inside
+    a node and replicated across nodes): the 2-D ``(replicate, shard)`` mesh over all ranks,
+    so every rank is inside the mesh and each replica's chunks are saved and restored."""
     engine = getattr(optimizer, "engine", None)
     if engine is None or engine.world == 1:
         return None
     if not hasattr(engine, "_dcp_mesh"):
-        from torch.distributed.device_mesh import init_device_mesh
+        import torch.distributed as dist
+        from torch.distributed.device_mesh import DeviceMesh, init_device_mesh
 
-        engine._dcp_mesh = init_device_mesh(engine.device.type, (engine.world,),
-                                            mesh_dim_names=("shard",))
+        if getattr(engine, "replica_group", None) is not None:
+            replicas = dist.get_world_size() // engine.world
+            engine._dcp_mesh = init_device_mesh(engine.device.type, (replicas, engine.world),
+                                                mesh_dim_names=("replicate", "shard"))
+        else:
+            ranks = dist.get_process_group_ranks(engine.group) if engine.group is not None \
+                else list(range(engine.world))
+            if ranks == list(range(dist.get_world_size())):
+                engine._dcp_mesh = init_device_mesh(engine.device.type, (engine.world,),
+                                                    mesh_dim_names=("shard",))
+            else:
+                engine._dcp_mesh = DeviceMesh(engine.device.type, ranks, mesh_dim_names=("shard",))
     return engine._dcp_mesh
 
 
 def _as_saved(optimizer, p: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
-    """Wrap this rank's chunk of a state tensor as a Shard(0) DTensor (multi-rank engine)."""
+    """Wrap this rank's chunk of a state tensor as a Shard(0) DTensor (multi-rank engine).
+    Zero-dimensional parameters cannot be sharded: their state is saved as a plain tensor
+    (it lives on the first rank of the shard group and is empty elsewhere)."""
     mesh = _shard_mesh(optimizer)
-    if mesh is None:
+    info = optimizer.engine.info[id(p)] if mesh is not None else None
+    if mesh is None or len(info.global_shape) == 0:
         return value
-    from torch.distributed.tensor import DTensor, Shard
+    from torch.distributed.tensor import DTensor, Replicate, Shard
 
-    info = optimizer.engine.info[id(p)]
     shape = torch.Size(info.global_shape)
     stride = torch.empty(shape, device="meta").stride()
-    return DTensor.from_local(value, mesh, (Shard(0),), run_check=False, shape=shape, stride=stride)
+    placements = (Shard(0),) if mesh.ndim == 1 else (Replicate(), Shard(0))
+    return DTensor.from_local(value, mesh, placements, run_check=False, shape=shape, stride=stride)
 
 
 def optimizer_state_for_save(model: torch.nn.Module, optimizer) -> dict[str, Any]:

@@ -5,7 +5,10 @@ output of its reduce-scatter kernel (already combined over the shard group); oth
 optimizers are scanned with a foreach finite check.  A GradScaler's own ``found_inf``
 records are merged in.  The flags are combined with an all-reduce(MAX) and written back
 into the GradScaler, so ``scaler.step``/``scaler.update`` take the same branch everywhere.
-One device→host read per update.
+One device→host read per update.  The kernel status word of this rank's device travels in
+the same all-reduce and the same read: a bounded wait that ran out in any kernel on any rank
+(gradient exchange, context-parallel exchange, tensor-core pipelines) raises
+``KernelStatusError`` here, before the optimizer consumes incomplete gradients.
 
 Parity: reference ``wm/infra/nonfinite.py:20-119``.
 """
@@ -16,6 +19,8 @@ from collections import defaultdict
 
 import torch
 import torch.distributed as dist
+
+from agentgarten_b200.ops.kernel_status import raise_for_status, status_flag
 
 __all__ = ["synchronize_found_nonfinite"]
 
@@ -64,13 +69,16 @@ def synchronize_found_nonfinite(grad_scaler, optimizers, *, fallback_device) -> 
     else:
         verdict = torch.zeros((), dtype=torch.float32, device=fallback_device)
     verdict.clamp_(0, 1)
+    word = torch.stack((verdict.reshape(()), status_flag(verdict.device).to(verdict.device)))
     if dist.is_available() and dist.is_initialized():
-        dist.all_reduce(verdict, op=dist.ReduceOp.MAX)
-        verdict.clamp_(0, 1)
+        dist.all_reduce(word, op=dist.ReduceOp.MAX)
+    nonfinite, status = word.tolist()  # the one host read of the update
+    raise_for_status(status, "training update")
+    verdict = word[0].clamp_(0, 1)
     for record in records:
         if record:
             for device, flag in record.items():
                 flag.copy_(verdict.to(device))
         else:
             record[verdict.device] = verdict.clone()
-    return bool(verdict.item())
+    return bool(nonfinite)

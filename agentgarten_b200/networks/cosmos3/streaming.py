@@ -124,6 +124,7 @@ class Cosmos3Stream:
         self.cuda_graphs = bool(serving.get("cuda_graphs", False)) if cuda_graphs is None \
             else bool(cuda_graphs)
         self._graph_pool = None
+        self._status_probe = None  # (pinned host copy of the kernel status word, its copy event)
         self.reset()
 
     def reset(self, release: bool = False) -> None:
@@ -222,6 +223,27 @@ class Cosmos3Stream:
         self.frame_ids += tuple(range(self.next_frame, self.next_frame + count))
         self.next_frame += count
         self._trim(condition)
+        self._check_kernel_status(clean.device)
+
+    def _check_kernel_status(self, device: torch.device) -> None:
+        """Block boundary: raise if a bounded wait ran out in any kernel of an earlier block.
+        The status word is copied to pinned host memory without stalling the stream; the copy
+        queued at the previous boundary is the one that is read, so a failure surfaces one
+        block late at the latest and a healthy stream never synchronises here."""
+        if device.type != "cuda":
+            return
+        from agentgarten_b200.ops import kernel_status
+
+        if self._status_probe is not None:
+            host, event = self._status_probe
+            if event.query():
+                kernel_status.raise_for_status(int(host.item()), "Cosmos3Stream block")
+        host = torch.empty((), dtype=torch.float32).pin_memory() if self._status_probe is None \
+            else self._status_probe[0]
+        host.copy_(kernel_status.status_flag(device), non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._status_probe = (host, event)
 
     def validate_chunk(self, value: torch.Tensor, condition: Cosmos3Condition) -> None:
         if self.text is None:

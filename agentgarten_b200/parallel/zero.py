@@ -267,7 +267,8 @@ class ZeroEngine:
     # --------------------------------------------------------------- state exchange
     def _views(self, p: torch.Tensor) -> dict[str, torch.Tensor]:
         info = self.info[id(p)]
-        shape = (info.rows, *info.global_shape[1:]) if info.global_shape else ()
+        # a zero-dimensional parameter lives whole on the first rank and is empty elsewhere
+        shape = (info.rows, *info.global_shape[1:]) if info.global_shape else (() if info.numel else (0,))
         lo, hi = info.state_offset, info.state_offset + info.numel
         g = self.optimizer.param_groups[self.group_of[id(p)]]
         out = {"master_param": self.master[lo:hi].view(shape)}
@@ -304,6 +305,9 @@ class ZeroEngine:
                     value = value.to_local()
                 if tuple(value.shape) == info.global_shape and info.global_shape:
                     value = value[info.row_offset: info.row_offset + info.rows]
+                if view.numel() == 0:
+                    state[key] = view
+                    continue
                 view.copy_(value.to(view.device, torch.float32).reshape(view.shape))
                 state[key] = view
 

@@ -51,6 +51,37 @@ def case_fetch_error_reaches_every_rank():
         raise AssertionError("the failure of rank 1 did not surface on rank %d" % rank)
 
 
+def case_kernel_status_of_one_rank_stops_every_rank():
+    """Rank 1 reports a timed-out peer wait (set on the host): the non-finite consensus of the
+    next update raises KernelStatusError on every rank, naming the code, and so does a
+    checkpoint save; after the word is cleared both proceed."""
+    from agentgarten_b200.infra.nonfinite import synchronize_found_nonfinite
+    from agentgarten_b200.ops import kernel_status
+
+    rank = dist.get_rank()
+    weight = torch.nn.Parameter(torch.ones(4))
+    weight.grad = torch.ones(4)
+    optimizer = torch.optim.SGD([weight], lr=0.1)
+    scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+    assert synchronize_found_nonfinite(scaler, (optimizer,), fallback_device="cpu") is False
+    kernel_status.inject(5 if rank == 1 else 0)
+    try:
+        synchronize_found_nonfinite(scaler, (optimizer,), fallback_device="cpu")
+    except kernel_status.KernelStatusError as error:
+        assert error.code == 5 and "kTimeoutPeer" in str(error), str(error)
+    else:
+        raise AssertionError("rank %d trained on after a peer timeout on rank 1" % rank)
+    try:
+        kernel_status.raise_for_status(kernel_status.read("cpu"), "checkpoint save")
+    except kernel_status.KernelStatusError as error:
+        assert "checkpoint save" in str(error)
+    else:
+        raise AssertionError("rank %d would have written a checkpoint" % rank)
+    kernel_status.inject(None)
+    assert kernel_status.read("cpu") == 0
+    assert synchronize_found_nonfinite(scaler, (optimizer,), fallback_device="cpu") is False
+
+
 def case_uneven_end_stops_everyone():
     """Rank 0 runs out of data one batch early: all ranks report exhaustion together."""
     rank = dist.get_rank()

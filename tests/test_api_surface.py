@@ -111,6 +111,18 @@ def test_signatures_users_rely_on():
     assert isinstance(Cosmos3Stream.keys, property) and isinstance(Cosmos3Stream.values, property)
     policy = StreamPolicy()
     assert (policy.block_frames, policy.sink_frames, policy.history_frames, policy.train_frames) == (4, 5, 44, 61)
+    # schedule factories are instantiated from resolved config files by keyword
+    from wm.infra.optim import CosineDecay, LinearWarmup, LinearWarmupCosineDecay
+
+    def keyword_only(callable_):
+        params = inspect.signature(callable_).parameters
+        return {n: p.default for n, p in params.items() if p.kind is inspect.Parameter.KEYWORD_ONLY}
+
+    assert keyword_only(LinearWarmup) == {"warmup_steps": 100, "start_factor": 1.0e-6}
+    assert keyword_only(CosineDecay) == {"decay_steps": inspect.Parameter.empty, "min_factor": 0.0}
+    assert keyword_only(LinearWarmupCosineDecay) == {
+        "warmup_steps": inspect.Parameter.empty, "decay_steps": inspect.Parameter.empty,
+        "start_factor": 0.0, "min_factor": 0.0}
 
 
 def test_bench_reference_arm_runs_the_unmodified_reference_package():

@@ -17,7 +17,7 @@ def _job(seed=0):
     model.parallelize("cpu")
     opt = FusedAdam(model._group_trainable_parameters(), lr=1e-3, use_te_capturable_kernel=True,
                     master_weights=True)
-    sched = torch.optim.lr_scheduler.LambdaLR(opt, LinearWarmup(10, 0.1))
+    sched = torch.optim.lr_scheduler.LambdaLR(opt, LinearWarmup(warmup_steps=10, start_factor=0.1))
     model.optimizer_dict, model.scheduler_dict = {"net": opt}, {"net": sched}
     return model, opt, sched
 
@@ -55,7 +55,7 @@ def test_save_resume_continues_exactly(tmp_path):
     fresh, opt2, sched2 = _job(seed=5)
     loader2 = StatefulDataLoader(loader.dataset, batch_size=2, shuffle=True, seed=3)
     loader_ckpt = DistributedCheckpointer(tmp_path / "ckpt", async_mode=None)
-    result = loader_ckpt.load(fresh, {"net": opt2}, {"net": sched2}, None, dataloader=loader2)
+    result = loader_ckpt.load(fresh, {"net": opt2}, {"net": sched2}, None, path="latest", dataloader=loader2)
     assert result.iteration == 3 and "model" in result.loaded_components
     assert not result.missing_model_keys and not result.unexpected_model_keys
     assert loader2.state_dict() == {"epoch": 0, "batch_offset": 1}
@@ -157,11 +157,36 @@ def test_truncated_shard_fails_the_load_loudly(tmp_path):
     shard.write_bytes(data[: len(data) // 3])
     fresh, opt2, sched2 = _job(seed=7)
     with pytest.raises(Exception):
-        DistributedCheckpointer(tmp_path / "ckpt", async_mode=None).load(fresh, {"net": opt2}, {"net": sched2}, None)
+        DistributedCheckpointer(tmp_path / "ckpt", async_mode=None).load(fresh, {"net": opt2}, {"net": sched2}, None,
+                                                                        path="latest")
 
 
-def test_missing_checkpoint_is_a_fresh_start(tmp_path):
+def test_load_path_semantics(tmp_path):
+    """``None`` loads nothing (even when ``latest`` exists), the literal ``"latest"`` follows the
+    pointer and fails without one, an absolute pointer target is honoured, and a directory
+    path names the checkpoint itself."""
+    import pytest
+
     model, opt, sched = _job()
-    result = DistributedCheckpointer(tmp_path / "nothing_here", async_mode=None).load(
-        model, {"net": opt}, {"net": sched}, None)
+    saver = DistributedCheckpointer(tmp_path / "ckpt", async_mode=None)
+    with pytest.raises(FileNotFoundError, match="No latest checkpoint pointer"):
+        saver.load(model, {"net": opt}, {"net": sched}, None, path="latest")
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=2)
+    saver.finalize()
+    fresh, opt2, sched2 = _job(seed=7)
+    result = saver.load(fresh, {"net": opt2}, {"net": sched2}, None)          # path=None
     assert result.iteration == 0 and result.loaded_components == ()
+    result = saver.load(fresh, {"net": opt2}, {"net": sched2}, None, path="latest")
+    assert result.iteration == 2 and "model" in result.loaded_components
+    fresh, opt2, sched2 = _job(seed=8)
+    result = saver.load(fresh, {"net": opt2}, {"net": sched2}, None, path=tmp_path / "ckpt" / "iter_000000002")
+    assert result.iteration == 2
+    # an absolute pointer target, from a checkpointer whose save_dir is elsewhere
+    other = DistributedCheckpointer(tmp_path / "elsewhere", async_mode=None)
+    (tmp_path / "elsewhere").mkdir()
+    (tmp_path / "elsewhere" / "latest").write_text(str(tmp_path / "ckpt" / "iter_000000002") + "\n")
+    fresh, opt2, sched2 = _job(seed=9)
+    assert other.load(fresh, {"net": opt2}, {"net": sched2}, None, path="latest").iteration == 2
+    (tmp_path / "elsewhere" / "latest").write_text("\n")
+    with pytest.raises(FileNotFoundError, match="empty"):
+        other.load(fresh, {"net": opt2}, {"net": sched2}, None, path="latest")

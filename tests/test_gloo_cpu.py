@@ -27,6 +27,7 @@ def _run(case, ranks, port):
     ("cp_prepare_error_reaches_the_group", 2, 29644),
     ("context_parallel_matches_single_group", 2, 29645),
     ("node_groups_for_hybrid_sharding", 4, 29646),
+    ("kernel_status_of_one_rank_stops_every_rank", 2, 29647),
 ])
 def test_gloo_case(case, ranks, port):
     _run(case, ranks, port)

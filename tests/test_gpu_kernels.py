@@ -308,6 +308,15 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status():
     C.tp_gemm(a, w, out, 0, 1, ready, seen, ticket, [], [], 0)
     torch.cuda.synchronize()
     assert int(status.item()) == 5  # kTimeoutPeer
+    # the production readers see it: the update consensus and the checkpoint guard raise
+    from agentgarten_b200.infra.nonfinite import synchronize_found_nonfinite
+    from agentgarten_b200.ops import kernel_status
+
+    weight = torch.nn.Parameter(torch.ones(4, device=DEV))
+    weight.grad = torch.ones(4, device=DEV)
+    with pytest.raises(kernel_status.KernelStatusError, match="kTimeoutPeer"):
+        synchronize_found_nonfinite(None, (torch.optim.SGD([weight], lr=0.1),), fallback_device=DEV)
+    assert kernel_status.read(DEV) == 5
     status.zero_()
     # the same call completes once the rows are announced, and ordinary kernels still run
     ready.fill_(128)

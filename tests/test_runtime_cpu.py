@@ -95,16 +95,28 @@ def test_synthetic_video_dataset_is_seeded():
 
 # ------------------------------------------------------------------------------ LR
 def test_lr_lambdas():
-    warm = LinearWarmup(4, start_factor=0.2)
+    warm = LinearWarmup(warmup_steps=4, start_factor=0.2)
     assert warm(0) == pytest.approx(0.2) and warm(2) == pytest.approx(0.6) and warm(4) == 1.0 and warm(99) == 1.0
-    cosine = CosineDecay(10, final_factor=0.1)
+    cosine = CosineDecay(decay_steps=10, min_factor=0.1)
     assert cosine(0) == pytest.approx(1.0) and cosine(10) == pytest.approx(0.1) and cosine(50) == pytest.approx(0.1)
     assert cosine(5) == pytest.approx(0.1 + 0.9 * 0.5)
-    both = LinearWarmupCosineDecay(2, 12, start_factor=0.0, final_factor=0.0)
+    both = LinearWarmupCosineDecay(warmup_steps=2, decay_steps=12, start_factor=0.0, min_factor=0.0)
     values = [both(s) for s in range(13)]
     assert values[0] == 0.0 and values[2] == pytest.approx(1.0) and values[12] == pytest.approx(0.0, abs=1e-9)
     assert all(a >= b - 1e-12 for a, b in zip(values[2:], values[3:]))
     pickle.loads(pickle.dumps(both))  # schedulers are checkpointed by value
+    # keyword names, defaults and validation of a resolved reference config
+    default = LinearWarmup()
+    assert (default.warmup_steps, default.start_factor) == (100, 1.0e-6) and default(0) > 0.0
+    with pytest.raises(TypeError):
+        LinearWarmup(4)
+    for bad in (dict(decay_steps=0), dict(decay_steps=5, min_factor=1.5), dict(decay_steps=5, min_factor=float("nan"))):
+        with pytest.raises(ValueError):
+            CosineDecay(**bad)
+    for bad in (dict(warmup_steps=-1, decay_steps=5), dict(warmup_steps=5, decay_steps=5),
+                dict(warmup_steps=1, decay_steps=5, start_factor=2.0)):
+        with pytest.raises(ValueError):
+            LinearWarmupCosineDecay(**bad)
 
 
 # ------------------------------------------------------------------------ clipping

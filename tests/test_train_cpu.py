@@ -81,8 +81,7 @@ def test_train_checkpoint_resume_continues_the_same_run(tmp_path):
     assert (tmp_path / "a" / "config.yaml").is_file()
     # stop after three updates, then resume to six: same losses as the uninterrupted run
     _train(["train.max_iterations=3"], tmp_path / "b")
-    resumed = _losses(_train(["train.max_iterations=6", f"train.checkpoint_path={tmp_path / 'b' / 'checkpoints'}"],
-                             tmp_path / "b"))
+    resumed = _losses(_train(["train.max_iterations=6", "train.checkpoint_path=latest"], tmp_path / "b"))
     assert sorted(resumed) == [4, 5, 6]
     for step in (4, 5, 6):
         assert resumed[step] == pytest.approx(straight[step], rel=1e-5), (step, resumed, straight)
