@@ -209,6 +209,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const bool in_range = q_row + my_row < p.nq;
     const float lse2 = in_range ? p.lse[stat_index] * LOG2E : 0.f;
     const float delta = in_range ? p.delta[stat_index] : 0.f;
+    // dS = exp2(S scale_log2 - lse2) * (dP scale - delta scale): two-lane arithmetic, 32 key
+    // columns at a time so that the compiler has registers left to overlap the exponentials.
+    const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+    const float2 nl2 = make_float2(-lse2, -lse2);
+    const float2 ps2 = make_float2(p.scale, p.scale);
+    const float2 nd2 = make_float2(-delta * p.scale, -delta * p.scale);
     bool ok = n_tiles > 0;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int buf = j & 1;
@@ -219,35 +225,40 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = false;
         break;
       }
+      // Only tiles with masked keys or rows (a partial last tile, the causal diagonal, the
+      // ragged last query tile) pay for the masking; the test is uniform over the CTA.
+      const bool plain = t.valid == ATT_BN && t.causal0 < 0 && q_rows == ATT_BM;
       int valid = t.valid;
       if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
       if (!row_ok) valid = 0;
-      {
-        uint32_t s[2][32], d[2][32];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld_32x32(tmem_base + lane_base + C_S + half * 64 + c * 32, s[c]);
-          tmem_ld_32x32(tmem_base + lane_base + C_DP + half * 64 + c * 32, d[c]);
-        }
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tmem_base + lane_base + C_S + half * 64 + c * 32, sv);
+        tmem_ld_32x32(tmem_base + lane_base + C_DP + half * 64 + c * 32, dv);
         tmem_ld_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(sp_free);
-        uint32_t packed[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float ds2[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int col = 2 * i + e;  // within this half
-            const float sv = __uint_as_float(s[col >> 5][col & 31]);
-            const float dp = __uint_as_float(d[col >> 5][col & 31]);
-            const float prob = (half * 64 + col < valid) ? exp2f(sv * p.scale_log2 - lse2) : 0.f;
-            ds2[e] = prob * (dp - delta) * p.scale;
-          }
-          packed[i] = pack_bf16(ds2[0], ds2[1]);
+        if (c == 1) {  // S and dP of this tile are in registers: the next scores may overwrite them
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sp_free);
         }
-        tmem_st_32x32(tmem_base + lane_base + C_DS + buf * 64 + half * 32, packed);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 x = ffma2(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])),
+                                 sc2, nl2);
+          float2 e = make_float2(exp2f(x.x), exp2f(x.y));
+          if (!plain) {
+            const int col = half * 64 + c * 32 + 2 * i;
+            if (col >= valid) e.x = 0.f;
+            if (col + 1 >= valid) e.y = 0.f;
+          }
+          const float2 g = ffma2(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])),
+                                 ps2, nd2);
+          const float2 ds = fmul2(e, g);
+          packed[i] = pack_bf16(ds.x, ds.y);
+        }
+        tmem_st_32x16(tmem_base + lane_base + C_DS + buf * 64 + half * 32 + c * 16, packed);
       }
       tmem_st_wait();
       tc_fence_before_sync();
@@ -485,41 +496,60 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int tid = (warp << 5) + lane;      // 0..255
     const int key = quarter * 32 + lane;     // key row of this thread
     bool ok = n_items > 0;
-    for (int i = 0; i < n_items && ok; ++i) {
-      const int buf = i & 1;
+    // Per query column the warps need -lse*log2(e) and -delta*scale.  They are staged in shared
+    // memory one item ahead: the global loads of item i + 1 are issued before the work on item
+    // i and stored behind it, so their latency never sits between two items.
+    const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
+    const float2 ps2 = make_float2(p.scale, p.scale);
+    auto fetch_stat = [&](int i) -> float {
+      // threads 0..63: -lse*log2(e) (or -inf: probability 0), threads 64..127: -delta*scale
       const int2 it = items[i];
       const int head = it.y >> 8, rows = it.y & 0xff;
-      float* my_stats = stats + buf * 2 * DKV_BQ;
-      if (tid < 2 * DKV_BQ) {  // 64 threads stage lse, 64 stage delta
-        const int col = tid & (DKV_BQ - 1);
-        const int q = it.x + col;
-        const bool valid = col < rows && q < p.nq;
-        const int64_t idx = (int64_t(batch) * p.hq + head) * p.nq + q;
-        if (tid < DKV_BQ) my_stats[col] = valid ? p.lse[idx] * LOG2E : INFINITY;  // +inf => probability 0
-        else my_stats[DKV_BQ + col] = valid ? p.delta[idx] : 0.f;
-      }
+      const int col = tid & (DKV_BQ - 1);
+      const int q = it.x + col;
+      const bool valid = col < rows && q < p.nq;
+      const int64_t idx = (int64_t(batch) * p.hq + head) * p.nq + q;
+      if (tid < DKV_BQ) return valid ? -p.lse[idx] * LOG2E : -INFINITY;
+      return valid ? -p.delta[idx] * p.scale : 0.f;
+    };
+    if (ok) {
+      if (tid < 2 * DKV_BQ) stats[tid] = fetch_stat(0);  // buffer 0: [nl[64], nd[64]]
       mbar_arrive(stats_bar);
+    }
+    for (int i = 0; i < n_items && ok; ++i) {
+      const int buf = i & 1;
+      const bool more = i + 1 < n_items;
+      float next_stat = 0.f;
+      if (more && tid < 2 * DKV_BQ) next_stat = fetch_stat(i + 1);
+      const float* my_stats = stats + buf * 2 * DKV_BQ;
       if (!mbar_wait(stats_bar, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       if (!mbar_wait(&st_full[buf], (i >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t s[32], d[32];
-      tmem_ld_32x32(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, s);
-      tmem_ld_32x32(tmem_base + lane_base + C_DPT + buf * DKV_BQ + half * 32, d);
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, sv);
+      tmem_ld_32x32(tmem_base + lane_base + C_DPT + buf * DKV_BQ + half * 32, dv);
       tmem_ld_wait();
       uint32_t pp[16], dd[16];
+      const float4* nl4 = reinterpret_cast<const float4*>(my_stats + half * 32);
+      const float4* nd4 = reinterpret_cast<const float4*>(my_stats + DKV_BQ + half * 32);
 #pragma unroll
-      for (int k2 = 0; k2 < 16; ++k2) {
-        float pv[2], dv[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int col = 2 * k2 + e;
-          const int qc = half * 32 + col;
-          const float prob = exp2f(__uint_as_float(s[col]) * p.scale_log2 - my_stats[qc]);
-          pv[e] = prob;
-          dv[e] = prob * (__uint_as_float(d[col]) - my_stats[DKV_BQ + qc]) * p.scale;
-        }
-        pp[k2] = pack_bf16(pv[0], pv[1]);
-        dd[k2] = pack_bf16(dv[0], dv[1]);
+      for (int k4 = 0; k4 < 8; ++k4) {  // four query columns per step
+        const float4 nl = nl4[k4], nd = nd4[k4];
+        const float2 x0 = ffma2(make_float2(__uint_as_float(sv[4 * k4]), __uint_as_float(sv[4 * k4 + 1])),
+                                sc2, make_float2(nl.x, nl.y));
+        const float2 x1 = ffma2(make_float2(__uint_as_float(sv[4 * k4 + 2]), __uint_as_float(sv[4 * k4 + 3])),
+                                sc2, make_float2(nl.z, nl.w));
+        const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
+        const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
+        const float2 g0 = ffma2(make_float2(__uint_as_float(dv[4 * k4]), __uint_as_float(dv[4 * k4 + 1])),
+                                ps2, make_float2(nd.x, nd.y));
+        const float2 g1 = ffma2(make_float2(__uint_as_float(dv[4 * k4 + 2]), __uint_as_float(dv[4 * k4 + 3])),
+                                ps2, make_float2(nd.z, nd.w));
+        const float2 d0 = fmul2(e0, g0), d1 = fmul2(e1, g1);
+        pp[2 * k4] = pack_bf16(e0.x, e0.y);
+        pp[2 * k4 + 1] = pack_bf16(e1.x, e1.y);
+        dd[2 * k4] = pack_bf16(d0.x, d0.y);
+        dd[2 * k4 + 1] = pack_bf16(d1.x, d1.y);
       }
       // the packed results land in columns this thread has already read
       tmem_st_32x16(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, pp);
@@ -528,6 +558,12 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pt_ready[buf]);
+      // The other stats buffer was last read for item i - 1; every thread has passed the wait
+      // of phase i above, which all threads entered only after finishing item i - 1.
+      if (more) {
+        if (tid < 2 * DKV_BQ) stats[(buf ^ 1) * 2 * DKV_BQ + tid] = next_stat;
+        mbar_arrive(stats_bar);
+      }
     }
     if (ok) ok = mbar_wait(grad_done, 0, guard, kTimeoutEpilogue);
     if (ok) {

@@ -106,10 +106,10 @@ def _nest(flat: Mapping[str, Any], prefix: str) -> dict[str, Any]:
 class DistributedCheckpointer:
     def __init__(self, save_dir: str | Path, *, async_mode: str | None = "thread",
                  async_timeout_seconds: float = 3600.0) -> None:
-        if async_mode not in (None, "none", "thread"):
-            raise ValueError(f"async_mode must be None or 'thread', got {async_mode!r}")
+        if async_mode not in (None, "none", "disabled", "thread"):
+            raise ValueError(f"async_mode must be 'disabled' or 'thread', got {async_mode!r}")
         self.save_dir = Path(save_dir)
-        self.async_mode = None if async_mode in (None, "none") else async_mode
+        self.async_mode = None if async_mode in (None, "none", "disabled") else async_mode
         self.async_timeout_seconds = float(async_timeout_seconds)
         self._pending: _Pending | None = None
         self._pending_rng: Mapping[str, Any] | None = None
@@ -232,7 +232,7 @@ class DistributedCheckpointer:
 
     def load(self, model: torch.nn.Module, optimizers: Mapping[str, Any] | None = None,
              schedulers: Mapping[str, Any] | None = None, grad_scaler: Any = None, *,
-             path: str | Path | None = None, components: Iterable[str] | None = None,
+             path: str | Path | None = "latest", components: Iterable[str] | None = None,
              dataloader: Any = None, runtime_metadata: Mapping[str, Any] | None = None,
              model_key_prefix: str | None = None,
              model_key_prefixes: Iterable[str | None] | None = None,

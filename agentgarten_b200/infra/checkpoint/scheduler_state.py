@@ -34,11 +34,10 @@ def scheduler_adapter_name(scheduler) -> str:
 
 
 def scheduler_state_for_save(scheduler) -> dict[str, Any]:
-    state = scheduler.state_dict()
-    if isinstance(scheduler, torch.optim.lr_scheduler.LambdaLR):
-        # callables are part of the recipe, not of the progress
-        state = {k: v for k, v in state.items() if k != "lr_lambdas"}
-    return {"adapter": scheduler_adapter_name(scheduler), "state": state}
+    # The whole state dict is written (a LambdaLR's callable objects appear as their attribute
+    # dicts under ``lr_lambdas``), which keeps the directory layout identical to the reference's;
+    # restoring reads the progress fields only, the callables stay those of the current recipe.
+    return {"adapter": scheduler_adapter_name(scheduler), "state": dict(scheduler.state_dict())}
 
 
 def _apply_lrs(scheduler, lrs: list[float]) -> None:

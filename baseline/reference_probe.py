@@ -28,15 +28,22 @@ def tiny_config():
 
 
 def seeded_(module: torch.nn.Module, seed: int) -> None:
+    """Seeded full tensors, the same on every rank; a sharded parameter keeps its own chunk."""
+    from torch.distributed.tensor import DTensor, distribute_tensor
+
     g = torch.Generator().manual_seed(seed)
     with torch.no_grad():
         for name, p in module.named_parameters():
             if p.ndim >= 2 or "embed" in name:
-                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+                full = torch.randn(p.shape, generator=g) * 0.02
             elif "norm" in name:
-                p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g))
+                full = 1.0 + 0.1 * torch.randn(p.shape, generator=g)
             else:
-                p.copy_(torch.randn(p.shape, generator=g) * 0.02)
+                full = torch.randn(p.shape, generator=g) * 0.02
+            if isinstance(p, DTensor):
+                p.to_local().copy_(distribute_tensor(full, p.device_mesh, p.placements).to_local())
+            else:
+                p.copy_(full)
 
 
 def batch_of(frames: int, seed: int = 0):
@@ -146,18 +153,90 @@ def train_mode(path: str, steps: int) -> None:
                 "lr": optimizer.param_groups[0]["lr"]}, path)
 
 
+def checkpoint_mode(path: str, directory: str, resume: bool) -> None:
+    """Two or more Gloo ranks, FSDP2.  Without ``resume``: two updates, a checkpoint
+    ``iter_000000002`` under ``directory``, a third update; with it: load ``directory/latest``
+    (written by either implementation) into a fresh job and run the third update.  The loss
+    of the third update (mean over ranks) is written to ``path`` by rank 0."""
+    import torch.distributed as dist
+
+    from wm.codecs import Wan22VAECodec
+    from wm.infra import distributed
+    from wm.infra.checkpoint import DistributedCheckpointer
+    from wm.infra.callbacks import CallbackGroup, GradClip
+    from wm.infra.config import LazyCall
+    from wm.infra.optim import FusedAdam, LinearWarmup
+    from wm.infra.parallel import ParallelConfig
+    from wm.infra.trainer import Trainer
+    from wm.models.diffusion import DiffusionModel
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+
+    device = distributed.init(device="cpu", backend="gloo")
+    rank = distributed.get_rank()
+    config = tiny_config()
+    sharded = ParallelConfig(parameter_dtype="float32", fully_shard=True, activation_checkpointing="none",
+                             compile=False)
+    model = DiffusionModel(
+        net=build_network(config, init_device="meta"),
+        conditioner=Cosmos3Conditioner(config=config, geometry_noise_sigma=0.0, init_device="meta",
+                                       empty_prompt_ids=(3, 4, 5),
+                                       codec=Wan22VAECodec(pretrained_path="unused", decoder=None)),
+        text_dropout=0.0, parallel=sharded, conditioner_parallel=sharded)
+    model.parallelize(device)
+    seeded_(model.net, 0 if not resume else 50)  # a resumed job starts from other weights
+    seeded_(model.conditioner.text_encoder, 1)
+    model.train()
+    optimizer = FusedAdam(model._group_trainable_parameters(), lr=1e-3, betas=(0.9, 0.99), eps=1e-8,
+                          weight_decay=0.01, adam_w_mode=True, use_te_capturable_kernel=True,
+                          master_weights=True)
+    scheduler = torch.optim.lr_scheduler.LambdaLR(
+        optimizer, lr_lambda=LinearWarmup(warmup_steps=4, start_factor=0.1))
+    model.optimizer_dict, model.scheduler_dict = {"net": optimizer}, {"net": scheduler}
+    callbacks = CallbackGroup(
+        {"trainer": {"callbacks": {"grad_clip": LazyCall(GradClip)(max_norm=1.0)}}}, trainer=None)
+    trainer = Trainer(grad_accum_steps=1, callbacks=callbacks, device=device)
+    scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+    checkpointer = DistributedCheckpointer(directory, async_mode="disabled")
+
+    def update(step: int) -> float:
+        torch.manual_seed(1000 * step + rank)  # noise and sigma of this update
+        data = model.prepare_data_batch(batch_of(5, seed=100 * step + rank))
+        result = trainer.training_step(model, scaler, data, iteration=step)
+        loss = result.loss.detach().clone()
+        dist.all_reduce(loss)
+        return float(loss) / dist.get_world_size()
+
+    if resume:
+        loaded = checkpointer.load(model, model.optimizer_dict, model.scheduler_dict, scaler, path="latest")
+        assert loaded.iteration == 2, loaded
+    else:
+        for step in range(2):
+            update(step)
+        checkpointer.save(model, model.optimizer_dict, model.scheduler_dict, scaler, iteration=2)
+        checkpointer.finalize()
+    loss = update(2)
+    if rank == 0:
+        torch.save({"loss": loss, "lr": optimizer.param_groups[0]["lr"]}, path)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("mode", choices=["network", "train"])
+    parser.add_argument("mode", choices=["network", "train", "checkpoint"])
     parser.add_argument("output")
     parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--directory", default=None)
+    parser.add_argument("--resume", action="store_true")
     args = parser.parse_args()
     torch.manual_seed(0)
     torch.set_num_threads(max(1, min(4, os.cpu_count() or 1)))
     if args.mode == "network":
         network_mode(args.output)
-    else:
+    elif args.mode == "train":
         train_mode(args.output, args.steps)
+    else:
+        checkpoint_mode(args.output, args.directory, args.resume)
     return 0
 
 

@@ -174,7 +174,7 @@ def test_load_path_semantics(tmp_path):
     saver.save(model, {"net": opt}, {"net": sched}, None, iteration=2)
     saver.finalize()
     fresh, opt2, sched2 = _job(seed=7)
-    result = saver.load(fresh, {"net": opt2}, {"net": sched2}, None)          # path=None
+    result = saver.load(fresh, {"net": opt2}, {"net": sched2}, None, path=None)
     assert result.iteration == 0 and result.loaded_components == ()
     result = saver.load(fresh, {"net": opt2}, {"net": sched2}, None, path="latest")
     assert result.iteration == 2 and "model" in result.loaded_components

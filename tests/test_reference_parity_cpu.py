@@ -160,3 +160,45 @@ def test_seeded_training_repeats_the_reference_loss_sequence(tmp_path):
     mine = model.net.state_dict()
     for name, theirs in golden["net"].items():
         assert torch.allclose(mine[name], theirs, atol=2e-5, rtol=1e-4), name
+
+
+def _ranks(script, *arguments, env, port, cwd):
+    done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), *arguments],
+                          capture_output=True, text=True, timeout=900, env=env, cwd=str(cwd))
+    assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-4000:]
+
+
+def test_checkpoints_interchange_with_the_reference(tmp_path):
+    """Two Gloo ranks.  The reference (FSDP2, sharded optimizer state) trains two updates and
+    saves ``iter_000000002``; this package resumes it and its third update gives the reference's
+    third loss.  Then the reverse: this package saves, the reference resumes.  The two
+    directories hold the same tensor keys."""
+    from torch.distributed.checkpoint import FileSystemReader
+
+    own_env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    own_env.update(AGB200_DISABLE_NATIVE="1", OMP_NUM_THREADS="2", PYTHONPATH=str(ROOT))
+    probe_script = ROOT / "baseline" / "reference_probe.py"
+    worker = ROOT / "tests" / "interchange_worker.py"
+    theirs, mine = tmp_path / "reference_ckpt", tmp_path / "own_ckpt"
+
+    _ranks(probe_script, "checkpoint", str(tmp_path / "a.pt"), "--directory", str(theirs),
+           env=reference_env(), port=29671, cwd=ROOT / "baseline")
+    _ranks(worker, str(tmp_path / "b.pt"), "--directory", str(theirs), "--resume",
+           env=own_env, port=29672, cwd=ROOT)
+    a, b = torch.load(tmp_path / "a.pt"), torch.load(tmp_path / "b.pt")
+    assert b["loss"] == pytest.approx(a["loss"], rel=1e-6) and b["lr"] == pytest.approx(a["lr"])
+
+    _ranks(worker, str(tmp_path / "c.pt"), "--directory", str(mine), env=own_env, port=29673, cwd=ROOT)
+    _ranks(probe_script, "checkpoint", str(tmp_path / "d.pt"), "--directory", str(mine), "--resume",
+           env=reference_env(), port=29674, cwd=ROOT / "baseline")
+    c, d = torch.load(tmp_path / "c.pt"), torch.load(tmp_path / "d.pt")
+    assert d["loss"] == pytest.approx(c["loss"], rel=1e-6) and d["lr"] == pytest.approx(c["lr"])
+    assert c["loss"] == pytest.approx(a["loss"], rel=1e-6)  # the two runs are the same run
+
+    keys = [set(FileSystemReader(str(d / "iter_000000002" / "tensor")).read_metadata().state_dict_metadata)
+            for d in (theirs, mine)]
+    assert keys[0] == keys[1], (sorted(keys[0] - keys[1])[:5], sorted(keys[1] - keys[0])[:5])
+    assert (theirs / "latest").read_text() == (mine / "latest").read_text()
+    assert sorted(p.name for p in (theirs / "iter_000000002").iterdir()) == \
+        sorted(p.name for p in (mine / "iter_000000002").iterdir())
