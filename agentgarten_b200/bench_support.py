@@ -20,6 +20,7 @@ from agentgarten_b200.models.diffusion import DiffusionModel
 from agentgarten_b200.models.flow import RectifiedFlowSchedule
 from agentgarten_b200.networks.cosmos3 import Cosmos3Config, build_network
 from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
+from agentgarten_b200.parallel import zero
 from agentgarten_b200.parallel.engine import ParallelConfig
 
 __all__ = ["TrainingJob", "build_training_job", "random_init_", "synthetic_batch"]
@@ -66,7 +67,8 @@ class TrainingJob:
         microbatch of an end-to-end measurement makes its own host-to-device transfer."""
         model, optimizer = self.model, self.optimizer
         loss = None
-        for _ in range(self.grad_accum_steps):
+        for micro in range(self.grad_accum_steps):
+            zero.arm_overlap(micro == self.grad_accum_steps - 1)
             encoded = model.prepare_data_batch(batch if stage is None else stage(batch))
             _, loss = model.training_step(encoded, 0)
             (loss / self.grad_accum_steps).backward()

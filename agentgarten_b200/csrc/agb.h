@@ -290,6 +290,24 @@ int zero_reduce_parts(int num_units, int sm_count);  // length of the partial bu
 cudaError_t zero_reduce(const ZeroPeers& grads, const int64_t* units, int num_units,
                         float* gshard, float* partial_sumsq, int* partial_bad, float* sumsq_out,
                         float* bad_out, int sm_count, cudaStream_t stream);
+// The same reduce over units [unit_begin, unit_end) with `parts` CTAs (partial buffers of that
+// length); with `ready` the kernel first waits, at most limit_ns, until *ready has reached
+// ready_target (every rank has announced the gradients of this bucket).  write_back_rank >= 0:
+// the bf16 average also replaces rank write_back_rank's own gradient of the range.
+cudaError_t zero_reduce_range(const ZeroPeers& grads, const int64_t* units, int unit_begin,
+                              int unit_end, float* gshard, float* partial_sumsq, int* partial_bad,
+                              int parts, const int* ready, int ready_target, int* status,
+                              uint64_t limit_ns, int write_back_rank, cudaStream_t stream);
+// Adds one to int32 slot `slot` of the counter table of every rank (system-scope release).
+cudaError_t zero_signal(const ZeroPeers& counters, int slot, cudaStream_t stream);
+// Waits (bounded) until *counter has reached target.
+cudaError_t zero_wait(const int* counter, int target, int* status, uint64_t limit_ns,
+                      cudaStream_t stream);
+// Folds the partials in index order and, with more than one rank, exchanges the two numbers
+// through the ranks' tables (int32 [8][4]) and sums them in rank order.
+cudaError_t zero_stats(const float* partial_sumsq, const int* partial_bad, int parts,
+                       const ZeroPeers& tables, int rank, int epoch, float* sumsq_out,
+                       float* bad_out, int* status, uint64_t limit_ns, cudaStream_t stream);
 // hyper: fp32 [rows, 8] = lr, beta1, beta2, eps, weight_decay, 1-beta1^t, sqrt(1-beta2^t),
 // adam_w flag.  grad_scale / skip_flag: device scalars (may be null).
 // gshard may be null in both calls: zero_reduce then only produces the statistics and

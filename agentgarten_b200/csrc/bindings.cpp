@@ -639,6 +639,48 @@ void zero_reduce(std::vector<int64_t> grad_ptrs, const Tensor& units,
         "zero_reduce");
 }
 
+constexpr uint64_t kGradientWaitNs = 30ull * 1000000000ull;  // ranks may be seconds apart in a step
+
+// One bucket of the reduce: units [begin, end), partials written at [part_offset, part_offset + parts).
+void zero_reduce_range(std::vector<int64_t> grad_ptrs, const Tensor& units, int64_t begin, int64_t end,
+                       c10::optional<Tensor> gshard_opt, const Tensor& psum, const Tensor& pbad,
+                       int64_t part_offset, int64_t parts, c10::optional<Tensor> ready,
+                       int64_t ready_slot, int64_t ready_target, int64_t write_back_rank) {
+  c10::cuda::CUDAGuard guard(psum.device());
+  TORCH_CHECK(part_offset + parts <= psum.numel() && psum.numel() == pbad.numel(), "partial buffers too small");
+  const int dev = psum.device().index();
+  check(agb::zero_reduce_range(
+            peers_of(grad_ptrs), units.data_ptr<int64_t>(), int(begin), int(end),
+            gshard_opt.has_value() ? gshard_opt->data_ptr<float>() : nullptr,
+            psum.data_ptr<float>() + part_offset, pbad.data_ptr<int>() + part_offset, int(parts),
+            ready.has_value() ? ready->data_ptr<int>() + ready_slot : nullptr, int(ready_target),
+            status_word(dev).data_ptr<int>(), kGradientWaitNs, int(write_back_rank), stream_of(psum)),
+        "zero_reduce_range");
+}
+
+void zero_signal(std::vector<int64_t> counter_ptrs, int64_t slot, const Tensor& anchor) {
+  c10::cuda::CUDAGuard guard(anchor.device());
+  check(agb::zero_signal(peers_of(counter_ptrs), int(slot), stream_of(anchor)), "zero_signal");
+}
+
+void zero_wait(const Tensor& counters, int64_t slot, int64_t target) {
+  c10::cuda::CUDAGuard guard(counters.device());
+  check(agb::zero_wait(counters.data_ptr<int>() + slot, int(target),
+                       status_word(counters.device().index()).data_ptr<int>(), kGradientWaitNs,
+                       stream_of(counters)), "zero_wait");
+}
+
+void zero_stats(const Tensor& psum, const Tensor& pbad, int64_t parts, std::vector<int64_t> table_ptrs,
+                int64_t rank, int64_t epoch, const Tensor& stats) {
+  c10::cuda::CUDAGuard guard(stats.device());
+  agb::ZeroPeers tables = table_ptrs.empty() ? agb::ZeroPeers{} : peers_of(table_ptrs);
+  if (table_ptrs.empty()) tables.world = 1;
+  check(agb::zero_stats(psum.data_ptr<float>(), pbad.data_ptr<int>(), int(parts), tables, int(rank),
+                        int(epoch), stats.data_ptr<float>(), stats.data_ptr<float>() + 1,
+                        status_word(stats.device().index()).data_ptr<int>(), kGradientWaitNs,
+                        stream_of(stats)), "zero_stats");
+}
+
 void zero_adam(std::vector<int64_t> param_ptrs, std::vector<int64_t> grad_ptrs,
                const Tensor& units, c10::optional<Tensor> gshard, const Tensor& master, const Tensor& exp_avg, const Tensor& exp_avg_sq,
                const Tensor& hyper, c10::optional<Tensor> grad_scale,
@@ -698,6 +740,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("relocate", &relocate);
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);
+  m.def("zero_reduce_range", &zero_reduce_range);
+  m.def("zero_signal", &zero_signal);
+  m.def("zero_wait", &zero_wait);
+  m.def("zero_stats", &zero_stats);
   m.def("channel_norm", &channel_norm);
   m.def("conv3d", &conv3d);
   m.def("depthwise", &depthwise);

@@ -12,16 +12,27 @@
 //                 1/world, store the FP32 result locally, and emit per-CTA partial sums of
 //                 squares and a non-finite flag.  zero_reduce_finish folds the partials in
 //                 a fixed order (deterministic norm).
+//                 With several ranks the bf16 average is written back over this rank's own
+//                 gradient of the range (no peer reads that range), so the peers' gradients
+//                 cross NVLink once and no FP32 gradient shard is allocated -- the reduced
+//                 gradient is bf16, as it is after FSDP2's reduce-scatter.
 //   zero_adam:    Adam/AdamW on the owned units with FP32 master weights and moments (the
-//                 averaged gradient is either read from the FP32 shard written by
-//                 zero_reduce or, without that buffer, summed again from the peers); the
+//                 averaged gradient is read from an FP32 shard, from this rank's own buffer
+//                 after the write-back, or summed again from the peers); the
 //                 gradient is multiplied by a device-resident factor (the clip coefficient)
 //                 on the fly; the new bf16 values are stored into every rank's parameter
 //                 buffer (st.global on peer pointers): the all-gather costs no extra pass.
 //
-// Cross-rank ordering (all gradients written before the reduce, all parameters written
-// before the next forward) is provided by the caller on the stream; the kernels never wait
-// on another GPU.
+// Cross-rank ordering uses monotonic system-scope counters in symmetric memory instead of
+// library collectives: a rank announces "my gradients of bucket b are complete" by adding 1 to
+// slot b on every peer (zero_signal); the bucket's reduce kernel waits (bounded) until its own
+// slot has reached world * epoch before it loads the peers' gradients, so a bucket can be
+// reduced on a side stream while the backward pass of earlier layers is still running.
+// zero_stats folds the per-CTA partial sums in a fixed order, stores this rank's two numbers
+// into every peer's slot table and sums all ranks' entries in rank order: the global gradient
+// norm without an all-reduce, and at the same time the point after which every rank has
+// finished reading its peers' gradients.  After Adam a "done" counter tells the peers that
+// the stores into their parameter buffers are complete (zero_signal / zero_wait).
 #include "agb.h"
 #include "sm100.cuh"
 
@@ -39,28 +50,68 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
+// Bounded wait (system scope) until a monotonic counter reaches `target`; false on timeout.
+__device__ bool wait_reached(const int* counter, int target, int* status, uint64_t limit_ns) {
+  const uint64_t start = global_timer_ns();
+  for (;;) {
+    int seen;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (counter_reached(seen, target)) return true;
+    if (status && *reinterpret_cast<volatile int*>(status) != 0) return false;  // step already lost
+    if (global_timer_ns() - start > limit_ns) {
+      if (status) atomicCAS(status, 0, kTimeoutPeer);
+      return false;
+    }
+    __nanosleep(256);
+  }
+}
+
 __global__ void __launch_bounds__(ZT) zero_reduce_kernel(ZeroPeers grads, const int64_t* units,
-                                                         int num_units, float* gshard,
+                                                         int unit_begin, int num_units, float* gshard,
                                                          float* partial_sumsq, int* partial_bad,
-                                                         float inv_world) {
+                                                         float inv_world, const int* ready,
+                                                         int ready_target, int* status,
+                                                         uint64_t limit_ns, int write_back_rank) {
   __shared__ float red[ZT / 32];
   __shared__ int bad_any;
-  if (threadIdx.x == 0) bad_any = 0;
+  __shared__ int go;
+  if (threadIdx.x == 0) {
+    bad_any = 0;
+    // every rank has finished writing the gradients of this bucket
+    go = ready ? (wait_reached(ready, ready_target, status, limit_ns) ? 1 : 0) : 1;
+  }
   __syncthreads();
   float sumsq = 0.f;
   int bad = 0;
-  for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+  if (!go) {  // a peer never arrived: report through the status word, poison the norm
+    if (threadIdx.x == 0) {
+      partial_sumsq[blockIdx.x] = 0.f;
+      partial_bad[blockIdx.x] = 1;
+    }
+    return;
+  }
+  for (int u = unit_begin + blockIdx.x; u < num_units; u += gridDim.x) {
     const int64_t flat = units[4 * u], state = units[4 * u + 1];
     const int count = int(units[4 * u + 2]);
     if (((flat | state) & 7) == 0 && (count & 7) == 0) {
       for (int i = threadIdx.x * 8; i < count; i += ZT * 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r = 0; r < grads.world; ++r) {
-          float v[8];
-          unpack8(*reinterpret_cast<const uint4*>(
-                      static_cast<const __nv_bfloat16*>(grads.ptr[r]) + flat + i), v);
+        // All peers' loads of this chunk are issued before the first sum (an NVLink load takes
+        // microseconds; one at a time would leave the links idle), the sums stay in rank order.
+        uint4 raw[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) acc[k] += v[k];
+        for (int r = 0; r < 8; ++r)
+          if (r < grads.world)
+            raw[r] = *reinterpret_cast<const uint4*>(
+                static_cast<const __nv_bfloat16*>(grads.ptr[r]) + flat + i);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r < grads.world) {
+            float v[8];
+            unpack8(raw[r], v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] += v[k];
+          }
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
@@ -73,6 +124,12 @@ __global__ void __launch_bounds__(ZT) zero_reduce_kernel(ZeroPeers grads, const 
           dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
           dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
+        if (write_back_rank >= 0) {
+          // the average replaces this rank's own gradient of the range it owns (no peer reads it)
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(grads.ptr[write_back_rank]) + flat + i) =
+              make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]),
+                         pack_bf16(acc[4], acc[5]), pack_bf16(acc[6], acc[7]));
+        }
       }
     } else {
       for (int i = threadIdx.x; i < count; i += ZT) {
@@ -83,6 +140,8 @@ __global__ void __launch_bounds__(ZT) zero_reduce_kernel(ZeroPeers grads, const 
         sumsq += acc * acc;
         bad |= !isfinite(acc);
         if (gshard) gshard[state + i] = acc;
+        if (write_back_rank >= 0)
+          static_cast<__nv_bfloat16*>(grads.ptr[write_back_rank])[flat + i] = __float2bfloat16_rn(acc);
       }
     }
   }
@@ -117,6 +176,65 @@ __global__ void zero_reduce_finish_kernel(const float* partial_sumsq, const int*
     *sumsq_out = s;
     *bad_out = bad ? 1.f : 0.f;
   }
+}
+
+// counters.ptr[r] + slot on every rank r is advanced by one (release, system scope).
+__global__ void zero_signal_kernel(ZeroPeers counters, int slot) {
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < counters.world; ++r) {
+      int* c = static_cast<int*>(counters.ptr[r]) + slot;
+      asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(c) : "memory");
+    }
+  }
+}
+
+__global__ void zero_wait_kernel(const int* counter, int target, int* status, uint64_t limit_ns) {
+  if (threadIdx.x == 0) wait_reached(counter, target, status, limit_ns);
+}
+
+// One warp.  Folds `parts` partials in index order, then (world > 1) publishes this rank's
+// (sum of squares, non-finite flag) in slot `rank` of every peer's table -- three 32-bit words
+// per rank: sum, flag, epoch tag written last with release -- waits for all ranks' entries of
+// this epoch and adds them in rank order.
+__global__ void zero_stats_kernel(const float* partial_sumsq, const int* partial_bad, int parts,
+                                  ZeroPeers tables, int rank, int epoch, float* sumsq_out,
+                                  float* bad_out, int* status, uint64_t limit_ns) {
+  float s = 0.f;
+  int bad = 0;
+  for (int i = threadIdx.x; i < parts; i += 32) {
+    s += partial_sumsq[i];
+    bad |= partial_bad[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+  }
+  if (threadIdx.x != 0) return;
+  if (tables.world > 1) {
+    for (int r = 0; r < tables.world; ++r) {
+      int* entry = static_cast<int*>(tables.ptr[r]) + 4 * rank;
+      reinterpret_cast<volatile float*>(entry)[0] = s;
+      reinterpret_cast<volatile int*>(entry)[1] = bad;
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(entry + 2), "r"(epoch) : "memory");
+    }
+    const int* mine = static_cast<const int*>(tables.ptr[rank]);
+    float total = 0.f;
+    int any = 0;
+    for (int r = 0; r < tables.world; ++r) {
+      if (!wait_reached(mine + 4 * r + 2, epoch, status, limit_ns)) {
+        any = 1;
+        break;
+      }
+      total += reinterpret_cast<const volatile float*>(mine + 4 * r)[0];
+      any |= reinterpret_cast<const volatile int*>(mine + 4 * r)[1];
+    }
+    s = total;
+    bad = any;
+  }
+  *sumsq_out = s;
+  *bad_out = bad ? 1.f : 0.f;
 }
 
 struct Hyper {  // one row of the hyper-parameter table (8 floats)
@@ -252,10 +370,42 @@ cudaError_t zero_reduce(const ZeroPeers& grads, const int64_t* units, int num_un
                         float* gshard, float* partial_sumsq, int* partial_bad, float* sumsq_out,
                         float* bad_out, int sm_count, cudaStream_t stream) {
   const int parts = zero_reduce_parts(num_units, sm_count);
-  zero_reduce_kernel<<<parts, ZT, 0, stream>>>(grads, units, num_units, gshard, partial_sumsq,
-                                               partial_bad, 1.f / float(grads.world));
+  zero_reduce_kernel<<<parts, ZT, 0, stream>>>(grads, units, 0, num_units, gshard, partial_sumsq,
+                                               partial_bad, 1.f / float(grads.world), nullptr, 0,
+                                               nullptr, 0, -1);
   zero_reduce_finish_kernel<<<1, 32, 0, stream>>>(partial_sumsq, partial_bad, parts, sumsq_out,
                                                   bad_out);
+  return cudaGetLastError();
+}
+
+cudaError_t zero_reduce_range(const ZeroPeers& grads, const int64_t* units, int unit_begin,
+                              int unit_end, float* gshard, float* partial_sumsq, int* partial_bad,
+                              int parts, const int* ready, int ready_target, int* status,
+                              uint64_t limit_ns, int write_back_rank, cudaStream_t stream) {
+  if (parts <= 0) return cudaSuccess;
+  zero_reduce_kernel<<<parts, ZT, 0, stream>>>(grads, units, unit_begin, unit_end, gshard,
+                                               partial_sumsq, partial_bad, 1.f / float(grads.world),
+                                               ready, ready_target, status, limit_ns,
+                                               write_back_rank);
+  return cudaGetLastError();
+}
+
+cudaError_t zero_signal(const ZeroPeers& counters, int slot, cudaStream_t stream) {
+  zero_signal_kernel<<<1, 32, 0, stream>>>(counters, slot);
+  return cudaGetLastError();
+}
+
+cudaError_t zero_wait(const int* counter, int target, int* status, uint64_t limit_ns,
+                      cudaStream_t stream) {
+  zero_wait_kernel<<<1, 32, 0, stream>>>(counter, target, status, limit_ns);
+  return cudaGetLastError();
+}
+
+cudaError_t zero_stats(const float* partial_sumsq, const int* partial_bad, int parts,
+                       const ZeroPeers& tables, int rank, int epoch, float* sumsq_out,
+                       float* bad_out, int* status, uint64_t limit_ns, cudaStream_t stream) {
+  zero_stats_kernel<<<1, 32, 0, stream>>>(partial_sumsq, partial_bad, parts, tables, rank, epoch,
+                                          sumsq_out, bad_out, status, limit_ns);
   return cudaGetLastError();
 }
 

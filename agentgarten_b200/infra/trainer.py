@@ -36,6 +36,8 @@ from .distributed import DistributedDataParallel, ddp_sync_grad, is_rank0
 from .model import Model
 from agentgarten_b200.utils.trace import span
 
+from agentgarten_b200.parallel import zero
+
 from .nonfinite import synchronize_found_nonfinite
 from .rng_state import isolated_rng
 
@@ -337,6 +339,9 @@ class Trainer:
                                 f"{type(is_last).__name__}")
             count += 1
             finished = is_last
+            # The last backward pass of an update lets the sharded optimizer engines reduce each
+            # layer's gradients over the peers as soon as that layer's backward has finished.
+            zero.arm_overlap(final_microbatch and is_last)
             with ddp_sync_grad(model_ddp, final_microbatch and is_last):
                 with span("forward"):
                     if isinstance(model_ddp, DistributedDataParallel):

@@ -133,6 +133,10 @@ class _Layer(torch.autograd.Function):
         ctx.kept_mlp = (h1, n2, rstd2, gate, up) if keep_mlp else None
         ctx.kept_attn = (n1, rstd1, q_lin, k_lin, q, k, v, rq, rk) if keep_attn else None
         ctx.save_for_backward(x, cos, sin, attn, lse, *weights)
+        if any(w.requires_grad for w in weights):
+            from agentgarten_b200.parallel import zero
+
+            zero.note_forward(weights)  # its backward reports the layer's gradients to the optimizer engine
         return y.view(b, n, h)
 
     @staticmethod
@@ -205,10 +209,29 @@ class _Layer(torch.autograd.Function):
         dx, dw_in = C.rms_norm_bwd(dn1, x2, w_in, rstd1)
         dx.add_(dh1)
         native.count(20)
-        cast = lambda g, w: None if g is None else g.to(w.dtype)  # noqa: E731
+        # Vector gradients go into the parameters' gradient buffers here as well (autograd would
+        # only add returned values after this function), so that the layer can be reported to
+        # the optimizer engine as complete: its bucket is then reduced over the peers while the
+        # backward pass of the earlier layers runs.
+        dw_in, dnq, dnk, dw_post = (_accumulate(w, g) for w, g in
+                                    ((w_in, dw_in), (nq, dnq), (nk, dnk), (w_post, dw_post)))
+        if any(w.requires_grad for w in ctx.params):
+            from agentgarten_b200.parallel import zero
+
+            zero.grads_ready(ctx.params)
         return (dx.view(b, n, h), None, None, None, None, None, None, None,
-                cast(dw_in, w_in), dwq, dwk, dwv, dwo, cast(dnq, nq), cast(dnk, nk),
-                cast(dw_post, w_post), dwg, dwu, dwd)
+                dw_in, dwq, dwk, dwv, dwo, dnq, dnk, dw_post, dwg, dwu, dwd)
+
+
+def _accumulate(weight: torch.Tensor, grad):
+    """Add ``grad`` to an existing gradient buffer of ``weight`` (returns None), or hand it to
+    autograd in the parameter's dtype when there is none yet."""
+    if grad is None or not weight.requires_grad:
+        return None
+    if weight.grad is not None:
+        weight.grad.add_(grad.to(weight.grad.dtype))
+        return None
+    return grad.to(weight.dtype)
 
 
 def run(layer, chunks, ropes, attention, layer_index):

@@ -10,14 +10,23 @@ world, dim=0)`` of every parameter — so the FP32 state a rank holds (master we
 both moments of its chunks) has exactly the layout a ``Shard(0)`` DTensor of that parameter
 would have, and sharded checkpoints are interchangeable with FSDP2 ones.
 
-One update is two kernels (see ``csrc/zero.cu``):
+One update (see ``csrc/zero.cu``):
 
-1. ``zero_reduce`` — reads the owned ranges from *every* rank's gradient buffer (peer
-   loads), averages in FP32, stores the FP32 shard and produces the squared norm and a
-   non-finite flag.  The tiny all-reduce of those two numbers doubles as the point after
-   which every rank may clear its gradient buffer.
-2. ``zero_adam`` — Adam on the owned ranges with the clip coefficient applied on the fly,
-   writing the new bf16 values straight into every rank's parameter buffer (peer stores).
+1. ``zero_reduce_range`` per *bucket* — reads the owned ranges of a bucket from every rank's
+   gradient buffer (peer loads), averages in FP32, stores the FP32 shard and per-CTA partial
+   sums of squares.  The fused generation layers report "the gradients of my parameters are
+   complete" from their backward pass (:func:`grads_ready`); the engine then announces the
+   bucket to the peers (a system-scope counter, ``zero_signal``) and launches its reduce on a
+   side stream, where it waits for the peers' announcements and runs under the backward pass
+   of the earlier layers.  Gradients cross NVLink once.
+2. ``zero_stats`` — folds the partial sums in a fixed order and exchanges the two numbers
+   (squared norm, non-finite flag) through the ranks' slot tables: the global norm without a
+   library collective, and the point after which every rank may clear its gradient buffer.
+3. ``zero_adam`` — Adam on the owned ranges from the averaged gradient (written back in bf16
+   over this rank's own gradient of those ranges by the reduce) with the clip
+   coefficient applied on the fly, writing the new bf16 values straight into every rank's
+   parameter buffer (peer stores); a "done" counter then tells the peers that their buffers
+   are complete.
 
 Parity: replaces FSDP2's reduce-scatter + all-gather and Transformer-Engine's multi-tensor
 Adam of the reference (``wm/infra/parallel.py:232-249``, ``wm/infra/optim/fused_adam.py:269-337``).
@@ -26,6 +35,8 @@ Adam of the reference (``wm/infra/parallel.py:232-249``, ``wm/infra/optim/fused_
 from __future__ import annotations
 
 import math
+import os
+import weakref
 from dataclasses import dataclass
 from typing import Any
 
@@ -34,7 +45,47 @@ import torch.distributed as dist
 
 from agentgarten_b200.ops import native
 
-__all__ = ["ShardInfo", "ZeroEngine"]
+__all__ = ["ShardInfo", "ZeroEngine", "arm_overlap", "grads_ready", "note_forward"]
+
+# Live engines, for the module-level hooks below.  An engine keeps its parameters alive, so
+# the ids in its ``param_units`` cannot be reused by other tensors while it is in this set.
+_ENGINES: "weakref.WeakSet[ZeroEngine]" = weakref.WeakSet()
+
+
+def arm_overlap(armed: bool = True) -> None:
+    """Tell every engine that the backward pass about to run is the last of its update."""
+    for engine in list(_ENGINES):
+        engine.arm_overlap(armed)
+
+
+def _owner(params):
+    for engine in list(_ENGINES):
+        if params and id(params[0]) in engine.param_units:
+            return engine
+    return None
+
+
+def note_forward(params) -> None:
+    """A layer whose backward pass will report through :func:`grads_ready` ran its forward
+    pass on ``params``: one more backward pass must finish before its bucket is complete."""
+    if _ENGINES:
+        params = tuple(params)
+        engine = _owner(params)
+        if engine is not None:
+            engine._pending[id(params[0])] = engine._pending.get(id(params[0]), 0) + 1
+
+
+def grads_ready(params) -> None:
+    """A backward pass of one layer has written its gradients of ``params``.  When it was the
+    last outstanding one of that layer in this update, the layer's bucket is reduced."""
+    if _ENGINES:
+        params = tuple(params)
+        engine = _owner(params)
+        if engine is not None:
+            left = engine._pending.get(id(params[0]), 1) - 1
+            engine._pending[id(params[0])] = left
+            if left <= 0:
+                engine.grads_ready(params)
 
 UNIT = 16384      # elements per work unit
 ALIGN = 64        # every parameter starts at a multiple of this many elements
@@ -123,6 +174,7 @@ class ZeroEngine:
         self.flat_grad, self.grad_ptrs = self._allocate(total)
         self.flat_grad.zero_()
         self.info: dict[int, ShardInfo] = {}
+        self.param_units: dict[int, tuple[int, int]] = {}  # parameter -> [first, last) unit
         units: list[tuple[int, int, int, int]] = []
         state_total = 0
         with torch.no_grad():
@@ -142,6 +194,7 @@ class ZeroEngine:
                 self.info[id(p)] = ShardInfo(shape, first, rows, off + first * row_elems,
                                              state_offset, count)
                 gi = self.group_of[id(p)]
+                self.param_units[id(p)] = (len(units), len(units) + -(-count // UNIT))
                 for start in range(0, count, UNIT):
                     units.append((off + first * row_elems + start, state_offset + start,
                                   min(UNIT, count - start), gi))
@@ -152,8 +205,9 @@ class ZeroEngine:
         self.num_units = len(units)
         if not units:
             self.units = self.units[:0]
-        # The averaged FP32 gradient shard is not materialised: the Adam kernel sums the
-        # peers' gradients again (in the same order), which saves 4 bytes per owned element.
+        # No FP32 gradient shard: with peers the reduce writes the bf16 average back over this
+        # rank's own gradient of the ranges it owns (which no peer reads), Adam then reads only
+        # local memory and the peers' gradients cross NVLink once.
         self.gshard = None
         self.master = torch.zeros(self.state_total, dtype=torch.float32, device=dev)
         need_m = any(float(g["betas"][0]) > 0 for g in groups)
@@ -173,6 +227,42 @@ class ZeroEngine:
         self.steps = [0] * len(groups)
         self.skip_nonfinite = True
         self._reduced = False
+        # ---- bucketed reduce: partial sums, counters, side stream ---------------------------
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        self._full_parts = max(1, min(self.num_units, sms * 8))
+        # CTAs of a bucket reduced under the backward pass: one per SM, so that the burst is
+        # short (bound by NVLink, a fraction of a millisecond per layer) and slows every SM's
+        # resident GEMM or attention CTA alike instead of stretching the kernels' slowest SM.
+        self._bucket_parts = sms
+        self._max_buckets = 64
+        self.partial_sumsq = torch.zeros(self._max_buckets * self._bucket_parts + self._full_parts,
+                                         dtype=torch.float32, device=dev)
+        self.partial_bad = torch.zeros_like(self.partial_sumsq, dtype=torch.int32)
+        self._buckets: dict[tuple[int, int], int] = {}   # unit range -> slot (same on all ranks)
+        self._launched: list[tuple[int, int]] = []       # ranges reduced so far in this update
+        self._used_parts = 0
+        self._armed = False
+        self._pending: dict[int, int] = {}   # first parameter of a layer -> backward passes outstanding
+        self._epoch = 0
+        self._side = torch.cuda.Stream(device=dev)
+        self.counter_ptrs: list[int] = []
+        self.table_ptrs: list[int] = []
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else dist.group.WORLD
+            self.counters = symm.empty(128, dtype=torch.int32, device=dev)   # 0..95 buckets, 96.. tails, 127 done
+            self.table = symm.empty(32, dtype=torch.int32, device=dev)       # [8 ranks][sum, flag, epoch, -]
+            self.counters.zero_()
+            self.table.zero_()
+            for buf in (self.counters, self.table):
+                handle = symm.rendezvous(buf, group=group)
+                self._handles.append(handle)
+                (self.counter_ptrs if buf is self.counters else self.table_ptrs).extend(
+                    int(x) for x in handle.buffer_ptrs)
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=group)  # zeroed counters everywhere before the first signal
+        _ENGINES.add(self)
 
     # ------------------------------------------------------------------ allocation
     def _allocate(self, numel: int) -> tuple[torch.Tensor, list[int]]:
@@ -188,30 +278,81 @@ class ZeroEngine:
         self._handles = getattr(self, "_handles", []) + [handle]
         return buf, ptrs
 
-    def _sync(self) -> None:
-        """Stream-ordered rendezvous of all ranks (a one-element all-reduce)."""
-        if self.world > 1:
-            dist.all_reduce(self._token, group=self.group)
-
-    @property
-    def _token(self) -> torch.Tensor:
-        if not hasattr(self, "_token_buf"):
-            self._token_buf = torch.zeros(1, dtype=torch.float32, device=self.device)
-        return self._token_buf
-
     # ------------------------------------------------------------------- gradients
+    def arm_overlap(self, armed: bool = True) -> None:
+        """The next backward pass is the last one of this update: buckets reported through
+        :func:`grads_ready` are reduced at once, under the rest of the backward pass."""
+        self._armed = (bool(armed) and self.world > 1 and self.replica_group is None
+                       and os.environ.get("AGB200_GRAD_OVERLAP", "1") != "0")
+
+    def _launch_range(self, lo: int, hi: int, stream: torch.cuda.Stream, parts: int) -> None:
+        """Announce units [lo, hi) to the peers and reduce them on ``stream``."""
+        ready = slot = None
+        target = 0
+        if self.world > 1:
+            key = (lo, hi)
+            if key not in self._buckets:
+                if len(self._buckets) >= 127:
+                    raise RuntimeError("too many gradient buckets")
+                self._buckets[key] = len(self._buckets)
+            slot = self._buckets[key]
+            ready, target = self.counters, self.world * self._epoch
+        with torch.cuda.stream(stream):
+            if slot is not None:
+                self.C.zero_signal(self.counter_ptrs, slot, self.counters)
+            self.C.zero_reduce_range(self.grad_ptrs, self.units, lo, hi, self.gshard, self.partial_sumsq,
+                                     self.partial_bad, self._used_parts, parts, ready,
+                                     slot if slot is not None else 0, target,
+                                     self.rank if self.world > 1 else -1)
+        native.count(2 if slot is not None else 1)
+        self._used_parts += parts
+        self._launched.append((lo, hi))
+
+    def grads_ready(self, params) -> bool:
+        """Called from a layer's backward pass when the gradients of ``params`` are complete on
+        this rank.  Returns True when their reduce was launched (side stream)."""
+        if not self._armed or self._reduced:
+            return False
+        ranges = [self.param_units[id(p)] for p in params if id(p) in self.param_units]
+        if not ranges:
+            return False
+        lo, hi = min(r[0] for r in ranges), max(r[1] for r in ranges)
+        if hi <= lo or sum(r[1] - r[0] for r in ranges) != hi - lo:
+            return False  # not one contiguous run of units: left to the final reduce
+        if any(lo < b and a < hi for a, b in self._launched) or len(self._launched) >= self._max_buckets:
+            return False
+        if not self._launched:
+            self._epoch += 1
+        self._side.wait_stream(torch.cuda.current_stream(self.device))
+        self._launch_range(lo, hi, self._side, self._bucket_parts)
+        return True
+
     def reduce_gradients(self) -> None:
         if self._reduced:
             return
         if self.replica_group is not None:
             # across nodes first: every node then holds the job-wide average of its local index
             dist.all_reduce(self.flat_grad, op=dist.ReduceOp.AVG, group=self.replica_group)
-        self._sync()  # every rank has finished writing its gradients
-        self.C.zero_reduce(self.grad_ptrs, self.units, self.gshard, self.stats)
-        native.count(2)
-        if self.world > 1:
-            # norm/flag over shards; after it every rank has finished reading peers' gradients
-            dist.all_reduce(self.stats, group=self.group)
+        main = torch.cuda.current_stream(self.device)
+        if not self._launched:
+            self._epoch += 1
+        else:
+            main.wait_stream(self._side)
+        # what the backward pass did not report: the complement of the launched ranges
+        cursor = 0
+        for lo, hi in sorted(self._launched) + [(self.num_units, self.num_units)]:
+            if lo > cursor:
+                share = max(1, min(self._full_parts - 0, (lo - cursor)))
+                share = min(share, self.partial_sumsq.numel() - self._used_parts)
+                self._launch_range(cursor, lo, main, share)
+            cursor = max(cursor, hi)
+        self.C.zero_stats(self.partial_sumsq, self.partial_bad, self._used_parts,
+                          self.table_ptrs, self.rank, self._epoch, self.stats)
+        native.count()
+        self._launched.clear()
+        self._pending.clear()
+        self._used_parts = 0
+        self._armed = False
         self._reduced = True
 
     def grad_norm_sq(self) -> torch.Tensor:
@@ -258,10 +399,16 @@ class ZeroEngine:
         else:
             self.scale.fill_(float(grad_scale))
         skip = self.stats[1:2] if self.skip_nonfinite else None
-        self.C.zero_adam(self.param_ptrs, self.grad_ptrs, self.units, self.gshard, self.master, self.exp_avg,
+        # after the reduce this rank's own buffer holds the averaged gradient of its ranges
+        self.C.zero_adam(self.param_ptrs, [self.grad_ptrs[self.rank]], self.units, self.gshard, self.master, self.exp_avg,
                          self.exp_avg_sq, self.hyper, self.scale, skip)
         native.count()
-        self._sync()  # every rank's parameter buffer is complete before the next forward
+        if self.world > 1:
+            # every rank's stores into this rank's parameter buffer are complete before the
+            # next forward: each rank adds one to slot 127 of all tables after its Adam kernel
+            self.C.zero_signal(self.counter_ptrs, 127, self.counters)
+            self.C.zero_wait(self.counters, 127, self.world * self._epoch)
+            native.count(2)
         self._reduced = False
 
     # --------------------------------------------------------------- state exchange

@@ -55,6 +55,36 @@ def check_sharded_adam(device, rank, world):
         assert torch.equal(other, gathered[0])
 
 
+def check_overlapped_gradient_path(device, rank, world):
+    """Two updates of a small job with per-rank data: reducing each layer's gradients from its
+    backward pass (side stream, counters between the ranks) gives bit for bit the parameters of
+    the run that reduces everything after the backward pass, on every rank."""
+    from agentgarten_b200.bench_support import build_training_job, synthetic_batch
+    from agentgarten_b200.ops import native
+
+    results = {}
+    for mode in ("1", "0"):
+        os.environ["AGB200_GRAD_OVERLAP"] = mode
+        job = build_training_job(device, layers=3, hidden=512, intermediate=1024, heads=4, kv_heads=2,
+                                 frames=3, latent_hw=(16, 16), text_tokens=20)
+        batch = synthetic_batch(job, device, seed=500 + rank)
+        torch.manual_seed(9 + rank)
+        for _ in range(2):
+            job.step(batch)
+        torch.cuda.synchronize()
+        engine = job.optimizer.engine
+        results[mode] = (engine.flat_param.clone(), len(engine._buckets))
+        assert int(native.ext().status(device.index).item()) == 0, "a bounded wait gave up"
+        del job, engine
+    os.environ.pop("AGB200_GRAD_OVERLAP")
+    assert results["1"][1] >= 3, results["1"][1]      # one bucket per layer plus the rest
+    assert results["0"][1] == 1
+    assert torch.equal(results["1"][0], results["0"][0])
+    gathered = [torch.empty_like(results["1"][0]) for _ in range(world)]
+    dist.all_gather(gathered, results["1"][0])
+    assert all(torch.equal(other, gathered[0]) for other in gathered)  # replicas agree
+
+
 def check_tensor_parallel_stream(device, rank, world):
     """Sharded serving over peer memory against the single-GPU layer path, eager and replayed."""
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
@@ -174,6 +204,8 @@ def main():
     device = distributed.init(device="cuda", backend="nccl")
     rank, world = dist.get_rank(), dist.get_world_size()
     check_sharded_adam(device, rank, world)
+    dist.barrier()
+    check_overlapped_gradient_path(device, rank, world)
     dist.barrier()
     check_tensor_parallel_stream(device, rank, world)
     dist.barrier()
