@@ -153,6 +153,45 @@ def train_mode(path: str, steps: int) -> None:
                 "lr": optimizer.param_groups[0]["lr"]}, path)
 
 
+def autoregressive_mode(path: str) -> None:
+    """Training and validation losses of the block-causal objective in both forcing modes
+    (teacher forcing with degraded history), and their gradients' norm."""
+    from wm.codecs import Wan22VAECodec
+    from wm.models.autoregressive import AutoregressiveModel, corrupt_history
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+    from wm.infra.parallel import ParallelConfig
+
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    out: dict = {}
+    for mode in ("teacher_forcing", "diffusion_forcing"):
+        model = AutoregressiveModel(
+            net=build_network(config, init_device="cpu"),
+            conditioner=Cosmos3Conditioner(config=config, geometry_noise_sigma=0.0, init_device="cpu",
+                                           empty_prompt_ids=(3, 4, 5),
+                                           codec=Wan22VAECodec(pretrained_path="unused", decoder=None)),
+            mode=mode, block_frames=4, text_dropout=0.5, parallel=plain, conditioner_parallel=plain)
+        model.parallelize("cpu")
+        seeded_(model.net, 0)
+        seeded_(model.conditioner.text_encoder, 1)
+        model.train()
+        data = model.prepare_data_batch(batch_of(9, seed=3))
+        torch.manual_seed(77)
+        report, loss = model.training_step(data, 0)
+        loss.backward()
+        norm = torch.sqrt(sum(p.grad.square().sum() for p in model.net.parameters() if p.grad is not None))
+        model.eval()
+        _, validation = model.validation_step(model.prepare_data_batch(batch_of(9, seed=4)), 0)
+        out[mode] = {"loss": float(loss), "sigma": report["sigma"], "grad_norm": float(norm),
+                     "validation": float(validation)}
+    g = torch.Generator().manual_seed(5)
+    frames = torch.randn(2, 6, 7, 12, 10, generator=g)
+    out["corrupted"] = corrupt_history(frames, torch.Generator().manual_seed(6))
+    out["frames"] = frames
+    torch.save(out, path)
+
+
 def checkpoint_mode(path: str, directory: str, resume: bool) -> None:
     """Two or more Gloo ranks, FSDP2.  Without ``resume``: two updates, a checkpoint
     ``iter_000000002`` under ``directory``, a third update; with it: load ``directory/latest``
@@ -223,7 +262,7 @@ def checkpoint_mode(path: str, directory: str, resume: bool) -> None:
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("mode", choices=["network", "train", "checkpoint"])
+    parser.add_argument("mode", choices=["network", "train", "checkpoint", "autoregressive"])
     parser.add_argument("output")
     parser.add_argument("--steps", type=int, default=5)
     parser.add_argument("--directory", default=None)
@@ -235,6 +274,8 @@ def main() -> int:
         network_mode(args.output)
     elif args.mode == "train":
         train_mode(args.output, args.steps)
+    elif args.mode == "autoregressive":
+        autoregressive_mode(args.output)
     else:
         checkpoint_mode(args.output, args.directory, args.resume)
     return 0

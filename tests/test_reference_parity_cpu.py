@@ -162,6 +162,49 @@ def test_seeded_training_repeats_the_reference_loss_sequence(tmp_path):
         assert torch.allclose(mine[name], theirs, atol=2e-5, rtol=1e-4), name
 
 
+def test_autoregressive_objective_equals_the_reference(tmp_path):
+    """Seeded training loss (text dropout, per-block sigmas, degraded clean history), gradient
+    norm and validation loss of both forcing modes, and the history degradation itself."""
+    from agentgarten_b200.models.autoregressive import AutoregressiveModel, corrupt_history
+    from agentgarten_b200.networks.cosmos3 import build_network
+    from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
+    from agentgarten_b200.parallel.engine import ParallelConfig
+
+    golden = probe("autoregressive", tmp_path / "ar.pt")
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        from reference_probe import seeded_
+    finally:
+        sys.path.pop(0)
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    for mode in ("teacher_forcing", "diffusion_forcing"):
+        model = AutoregressiveModel(
+            net=build_network(config, init_device="cpu"),
+            conditioner=Cosmos3Conditioner(config=config, codec=None, geometry_noise_sigma=0.0,
+                                           init_device="cpu", empty_prompt_ids=(3, 4, 5)),
+            mode=mode, block_frames=4, text_dropout=0.5, parallel=plain, conditioner_parallel=plain)
+        model.parallelize("cpu")
+        seeded_(model.net, 0)
+        seeded_(model.conditioner.text_encoder, 1)
+        model.train()
+        data = model.prepare_data_batch(batch_of(9, seed=3))
+        torch.manual_seed(77)
+        report, loss = model.training_step(data, 0)
+        loss.backward()
+        norm = torch.sqrt(sum(p.grad.square().sum() for p in model.net.parameters() if p.grad is not None))
+        model.eval()
+        _, validation = model.validation_step(model.prepare_data_batch(batch_of(9, seed=4)), 0)
+        want = golden[mode]
+        assert float(loss) == pytest.approx(want["loss"], rel=2e-5), mode
+        assert torch.allclose(report["sigma"], want["sigma"])
+        assert float(norm) == pytest.approx(want["grad_norm"], rel=1e-4), mode
+        assert float(validation) == pytest.approx(want["validation"], rel=2e-5), mode
+    mine = corrupt_history(golden["frames"], torch.Generator().manual_seed(6))
+    assert torch.allclose(mine, golden["corrupted"], atol=1e-6)
+
+
 def _ranks(script, *arguments, env, port, cwd):
     done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), *arguments],
