@@ -1,34 +1,36 @@
 """Adversarial Forcing: few-step distillation of a block-causal student (DMD + GAN).
 
-Roles: a trainable few-step ``student``, a frozen teacher ``real_score``, a trainable
-``fake_score`` that tracks the student's distribution, and optionally a ``discriminator``
-head on the teacher's hidden features.  :class:`PhaseClock` decides the role of each
-iteration: discriminator-only warm-up, then one student update every
-``fake_score_updates_per_student + 1`` iterations, the rest train the fake score (and the
-discriminator).
+Four roles: the trainable few-step ``student``; the frozen teacher ``real_score``; the
+trainable ``fake_score`` that follows the student's output distribution; optionally a
+``discriminator`` head on the teacher's hidden features (:mod:`.dmd_adversarial`).  A
+:class:`PhaseClock` gives each iteration its role: discriminator-only warm-up, then one
+student update per cycle, the other iterations train the fake score and the discriminator.
 
-A student iteration is *Self Gradient Forcing*: pass 1 rolls the student out block by block
-with its KV cache under ``no_grad`` up to a random exit step shared by all ranks; pass 2
-replays the recorded queries through ``forward_ar`` with gradients (bitwise equal to pass 1,
-see ``metrics/student/sgf_recovery_max_abs``) and receives the distribution-matching
-gradient ``(x0_fake - x0_real) / mean|x0 - x0_real|`` computed in FP64, plus the generator
-gradient of the GAN term.  The discriminator is regularised by finite-difference R1/R2 or
-by the exact penalties of :mod:`agentgarten_b200.models.exact_regularization`.
+Every iteration first rolls the student out without gradients (:mod:`.dmd_rollout`) up to an
+exit step drawn identically on every rank.  On a student iteration the recorded queries are
+replayed through ``forward_ar`` with gradients — bit for bit the same evaluation, which the
+``metrics/student/sgf_recovery_max_abs`` output monitors — and the clean estimate receives
 
-Parity: reference ``wm/models/dmd.py:55-698``.
+* the distribution-matching gradient ``(x0_fake - x0_real) / mean|x0 - x0_real|`` of the two
+  score networks at a random noise level (FP64, injected as a squared distance to a detached
+  target), and
+* the generator gradient of the GAN term, injected as a linear term.
+
+On the other iterations the fake score regresses the rectified-flow velocity of the generated
+clip and the discriminator separates noised real clips from noised generated ones.
+
+Parity: reference ``wm/models/dmd.py:55-698`` (roles, constructor keywords, optimizer role
+names, metric names, checkpoint exclusions).
 """
 
 from __future__ import annotations
 
 import itertools
 from collections.abc import Iterator, Mapping, Sequence
-from dataclasses import dataclass, replace
-from enum import StrEnum
-from functools import partial
+from dataclasses import replace
 from typing import Any
 
 import torch
-import torch.nn.functional as F
 from torch import Tensor, nn
 
 from agentgarten_b200.infra.config import instantiate
@@ -36,93 +38,23 @@ from agentgarten_b200.infra.model import StepOutput, TrainingClosureSpec
 from agentgarten_b200.infra.rng_state import isolated_rng
 from agentgarten_b200.parallel.engine import ParallelConfig, parallelize_network
 from agentgarten_b200.protocols import HistoryWindow
-from agentgarten_b200.utils import log
-from agentgarten_b200.utils.misc import frozen_parameters
 
 from .base import ConditionedModel
-from .exact_regularization import check_exact_regularization, exact_penalties
+from .dmd_adversarial import Adversary
+from .dmd_rollout import Rollout, StudentRollout
+from .dmd_schedule import RCM_ENDPOINTS, GANConfig, PhaseClock, Regularization
+from .exact_regularization import check_exact_regularization
 from .flow import UniformShift, invariant_randn, rf_interpolate, rf_x0, sampling_seeds
 
 __all__ = ["RCM_ENDPOINTS", "DMDModel", "GANConfig", "PhaseClock", "Regularization"]
 
-# Sigma endpoints of the 4-step rollout; an n-step rollout uses the first n.
-RCM_ENDPOINTS = (1600.0 / 1601.0, 15.0 / 16.0, 5.0 / 6.0, 5.0 / 8.0)
 
-
-class Regularization(StrEnum):
-    FINITE_DIFFERENCE = "finite_difference"
-    EXACT = "exact"
-
-
-@dataclass(frozen=True)
-class GANConfig:
-    generator_weight: float = 0.01
-    discriminator_weight: float = 0.01
-    relativistic: bool = True
-    regularization: Regularization = Regularization.FINITE_DIFFERENCE
-    # finite difference: weight * E[(D(x + sigma*eps) - D(x))^2]
-    regularization_weight: float = 30.0
-    regularization_sigma: float = 0.05
-    # exact: weight * E[||grad_x D||^2]; 0.075 = 30 * 0.05^2 matches the local scale above
-    exact_regularization_weight: float = 0.075
-    warmup_updates: int = 0
-
-    def __post_init__(self) -> None:
-        object.__setattr__(self, "regularization", Regularization(self.regularization))
-        if self.warmup_updates < 0:
-            raise ValueError("warmup_updates must be non-negative")
-
-
-@dataclass(frozen=True)
-class PhaseClock:
-    fake_score_updates_per_student: int = 5
-    warmup_updates: int = 0
-
-    def __post_init__(self) -> None:
-        if self.fake_score_updates_per_student < 1 or self.warmup_updates < 0:
-            raise ValueError(f"invalid phase clock {self}")
-
-    @property
-    def cycle(self) -> int:
-        return self.fake_score_updates_per_student + 1
-
-    def is_warmup(self, iteration: int) -> bool:
-        return iteration < self.warmup_updates
-
-    def is_student(self, iteration: int) -> bool:
-        return not self.is_warmup(iteration) and (iteration - self.warmup_updates) % self.cycle == 0
-
-    def role_updates(self, iteration: int) -> dict[str, int]:
-        """Updates each role has received after ``iteration`` iterations."""
-        after_warmup = max(0, iteration - self.warmup_updates)
-        student = -(-after_warmup // self.cycle)
-        return {"student": student, "fake_score": after_warmup - student}
-
-    def is_cadence_due(self, iteration: int, interval: int | None) -> bool:
-        """Cadences count student updates and fire only at the end of a full cycle."""
-        if interval is None or interval <= 0 or iteration <= 0:
-            return False
-        n = self.role_updates(iteration)
-        return (n["student"] > 0 and n["student"] % interval == 0 and n["fake_score"] > 0
-                and n["fake_score"] % (interval * self.fake_score_updates_per_student) == 0)
-
-
-@dataclass
-class _Rollout:
-    noisy: Tensor   # [B, C, T, H, W] query of every block at its exit step
-    sigma: Tensor   # [B, T]
-    clean: Tensor   # [B, C, T, H, W] committed x0 (the generated clip)
-
-
-def _pair_loss(real: Tensor, fake: Tensor, *, relativistic: bool) -> Tensor:
-    if relativistic:
-        return F.softplus(-(real - fake)).mean()
-    return (F.softplus(-real) + F.softplus(fake)).mean()
-
-
-def _pair_metrics(pair: Tensor, real: Tensor, fake: Tensor) -> dict[str, Tensor]:
-    return {"metrics/discriminator/pair_loss": pair.detach(),
-            "metrics/discriminator/accuracy": (real > fake).float().mean().detach()}
+def _checked_endpoints(values: Sequence[float]) -> tuple[float, ...]:
+    levels = tuple(float(v) for v in values)
+    descending = all(a > b for a, b in itertools.pairwise(levels))
+    if not levels or not descending or not all(0 < v <= 1 for v in levels):
+        raise ValueError(f"rollout endpoints must be strictly descending in (0, 1]: {levels}")
+    return levels
 
 
 class DMDModel(ConditionedModel):
@@ -142,33 +74,31 @@ class DMDModel(ConditionedModel):
                  discriminator_parallel: ParallelConfig | None = None,
                  conditioner_parallel: ParallelConfig | None = None,
                  sampling: Mapping[str, Any] | None = None, seed: int = 0) -> None:
-        if (discriminator is None) != (gan is None):
+        if (discriminator is None) is not (gan is None):
             raise ValueError("pass both discriminator and gan, or neither")
-        endpoints = tuple(float(v) for v in rollout_endpoints)
-        if (not endpoints or any(not 0 < v <= 1 for v in endpoints)
-                or any(a <= b for a, b in itertools.pairwise(endpoints))):
-            raise ValueError(f"rollout endpoints must be strictly descending in (0, 1]: {endpoints}")
+        levels = _checked_endpoints(rollout_endpoints)
         if block_frames < 1 or int(block_frames) != block_frames:
             raise ValueError(f"block_frames must be a positive integer, got {block_frames}")
-        super().__init__(conditioner=conditioner,
-                         sampling_defaults={"num_steps": len(endpoints), "seed": 0},
-                         sampling=sampling)
+        super().__init__(conditioner=conditioner, sampling=sampling,
+                         sampling_defaults={"num_steps": len(levels), "seed": 0})
         self.student, self.real_score, self.fake_score = student, real_score, fake_score
         self.discriminator, self.gan = discriminator, gan
         self.block_frames = int(block_frames)
-        self.rollout_endpoints = endpoints
+        self.rollout_endpoints = levels
         self.score_time = UniformShift(score_shift)
         self.real_score_guidance = float(real_score_guidance)
-        self.clock = PhaseClock(fake_score_updates_per_student, gan.warmup_updates if gan else 0)
+        self.clock = PhaseClock(fake_score_updates_per_student, 0 if gan is None else gan.warmup_updates)
         self.dmd_loss_scale = float(dmd_loss_scale)
-        self.history = history or HistoryWindow()
-        plain = ParallelConfig(fully_shard=False, compile=False)
-        self.student_parallel = student_parallel or plain
-        self.score_parallel = score_parallel or plain
-        self.real_score_parallel = real_score_parallel or self.score_parallel
-        self.discriminator_parallel = discriminator_parallel or plain
-        self.conditioner_parallel = conditioner_parallel or self.score_parallel
+        self.history = history if history is not None else HistoryWindow()
         self.seed = int(seed)
+
+        unsharded = ParallelConfig(fully_shard=False, compile=False)
+        self.student_parallel = student_parallel or unsharded
+        self.score_parallel = score_parallel or unsharded
+        self.real_score_parallel = real_score_parallel or self.score_parallel
+        self.discriminator_parallel = discriminator_parallel or unsharded
+        self.conditioner_parallel = conditioner_parallel or self.score_parallel
+
         self.real_score.requires_grad_(False)
         self.configure_trainable_parameters(student_trainable_patterns, module=self.student)
         self.configure_trainable_parameters(fake_score_trainable_patterns, module=self.fake_score)
@@ -179,21 +109,33 @@ class DMDModel(ConditionedModel):
                                  "context_parallel_size=1 or finite_difference regularization")
             check_exact_regularization(self.real_score, discriminator)
 
+    # plain (non-module) helpers built on demand: they hold references to registered modules
+    @property
+    def _rollouts(self) -> StudentRollout:
+        return StudentRollout(self.student, self.rollout_endpoints, self.block_frames, self.history)
+
+    @property
+    def _adversary(self) -> Adversary:
+        if self.gan is None or self.discriminator is None:
+            raise RuntimeError("this objective was built without a discriminator")
+        return Adversary(self.gan, self.discriminator, self._teacher_features)
+
     # ------------------------------------------------------------------- lifecycle
     def parallelize(self, device) -> None:
-        mesh = parallelize_network(self.student, replace(self.student_parallel,
-                                                         reshard_after_forward=False), device)
-        others = [parallelize_network(self.real_score, self.real_score_parallel, device),
+        # the student replays right after a long rollout: keep its parameters gathered
+        resident = replace(self.student_parallel, reshard_after_forward=False)
+        meshes = [parallelize_network(self.student, resident, device),
+                  parallelize_network(self.real_score, self.real_score_parallel, device),
                   parallelize_network(self.fake_score, self.score_parallel, device)]
         self.parallelize_conditioner(self.conditioner_parallel, device)
         if self.discriminator is not None:
             self.discriminator.parallelize(self.discriminator_parallel, device)
         self.real_score.eval()
-        self.register_context_parallel_mesh(mesh, *others)
+        self.register_context_parallel_mesh(*meshes)
 
     def train(self, mode: bool = True) -> "DMDModel":
         super().train(mode)
-        self.real_score.eval()
+        self.real_score.eval()  # the teacher never leaves evaluation mode
         return self
 
     def is_cadence_due(self, iteration: int, interval: int | None) -> bool:
@@ -204,256 +146,154 @@ class DMDModel(ConditionedModel):
             return ("discriminator",)
         if self.clock.is_student(iteration):
             return ("student",)
-        return ("fake_score", "discriminator") if self.gan else ("fake_score",)
+        return ("fake_score",) if self.gan is None else ("fake_score", "discriminator")
 
     def init_optimizer_scheduler(self, optimizer_config, scheduler_config):
-        roles = {"student": self.student, "fake_score": self.fake_score}
+        trained = {"student": self.student, "fake_score": self.fake_score}
         if self.discriminator is not None:
-            roles["discriminator"] = self.discriminator
-        missing = set(roles) - set(optimizer_config)
-        if missing:
-            raise KeyError(f"optimizer config lacks roles {sorted(missing)}")
-        self.optimizer_dict, self.scheduler_dict = {}, {}
-        for name, module in roles.items():
-            optimizer = instantiate(optimizer_config[name],
-                                    params=self._group_module_trainable_parameters(module))
-            self.optimizer_dict[name] = optimizer
-            self.scheduler_dict[name] = instantiate(scheduler_config, optimizer=optimizer)
+            trained["discriminator"] = self.discriminator
+        absent = sorted(set(trained) - set(optimizer_config))
+        if absent:
+            raise KeyError(f"optimizer config lacks roles {absent}")
+        self.optimizer_dict = {
+            role: instantiate(optimizer_config[role], params=self._group_module_trainable_parameters(module))
+            for role, module in trained.items()}
+        self.scheduler_dict = {role: instantiate(scheduler_config, optimizer=optimizer)
+                               for role, optimizer in self.optimizer_dict.items()}
         return self.optimizer_dict, self.scheduler_dict
 
     # --------------------------------------------------------------------- rollout
     def _exit_step(self, iteration: int) -> int:
-        """Same draw on every rank: a CPU generator seeded from (seed, iteration)."""
-        g = torch.Generator().manual_seed(self.seed * 1_000_003 + iteration)
-        return int(torch.randint(len(self.rollout_endpoints), (1,), generator=g))
+        """The same draw on every rank: a CPU generator seeded from (seed, iteration)."""
+        draw = torch.Generator().manual_seed(self.seed * 1_000_003 + iteration)
+        return int(torch.randint(len(self.rollout_endpoints), (1,), generator=draw))
 
     def _validate_rollout(self, frames: int, steps: int) -> None:
-        if frames < 1 or frames % self.block_frames:
-            raise ValueError("target latent frames must be a positive multiple of "
-                             f"block_frames={self.block_frames}, got {frames}")
-        if int(steps) != steps or not 1 <= steps <= len(self.rollout_endpoints):
-            raise ValueError(f"num_steps must be an integer in [1, {len(self.rollout_endpoints)}], "
-                             f"got {steps}")
+        self._rollouts.check(frames, steps)
 
-    @torch.no_grad()
     def _rollout(self, anchor: Tensor, condition, frames: int, steps: int, *,
-                 noise: Tensor | None = None) -> _Rollout:
-        """``noise``: optional ``[steps, B, C, frames, H, W]`` draws; default global RNG."""
-        self._validate_rollout(frames, steps)
-        endpoints = self.rollout_endpoints[:steps]
-        batch, device = anchor.shape[0], anchor.device
-        shape = (batch, anchor.shape[1], self.block_frames, *anchor.shape[3:])
-        cache = self.student.prefill(anchor, condition, history=self.history)
-        queries, cleans = [], []
-        clean = anchor
-        blocks = frames // self.block_frames
-
-        def draw(step: int, start: int) -> Tensor:
-            if noise is None:
-                return torch.randn(shape, device=device)
-            return noise[step, :, :, start:start + self.block_frames]
-
-        for index in range(blocks):
-            start = index * self.block_frames
-            current = draw(0, start)
-            for step, sigma in enumerate(endpoints):
-                level = torch.full((batch,), sigma, device=device)
-                if step:
-                    current = rf_interpolate(clean, draw(step, start), level)
-                velocity = self.student.denoise(cache, current, level).float()
-                clean = rf_x0(current, level, velocity)
-            queries.append(current)
-            cleans.append(clean)
-            if index < blocks - 1:
-                cache = self.student.commit(cache, clean)
-        exit_sigma = torch.full((batch, frames), endpoints[-1], device=device)
-        return _Rollout(torch.cat(queries, 2), exit_sigma, torch.cat(cleans, 2))
+                 noise: Tensor | None = None) -> Rollout:
+        return self._rollouts.run(anchor, condition, frames, steps, noise=noise)
 
     # ---------------------------------------------------------------------- scores
-    def _score(self, network, anchor, noisy, sigma, condition) -> Tensor:
-        velocity = network(torch.cat((anchor, noisy), dim=2), sigma, condition, known_frames=1)
-        return velocity[:, :, 1:].float()
+    @staticmethod
+    def _velocity(network: nn.Module, anchor: Tensor, noisy: Tensor, sigma: Tensor, condition) -> Tensor:
+        """A bidirectional score network on [anchor | noisy]: velocity of the noisy frames."""
+        clip = torch.cat((anchor, noisy), dim=2)
+        return network(clip, sigma, condition, known_frames=1)[:, :, 1:].float()
 
-    def _gan_roles(self):
-        if self.gan is None or self.discriminator is None:
-            raise RuntimeError("this objective was built without a discriminator")
-        return self.gan, self.discriminator
-
-    def _real_features(self, anchor, noisy, sigma, condition):
+    def _teacher_features(self, anchor: Tensor, noisy: Tensor, sigma: Tensor, condition):
         """Hidden states of the frozen teacher at the discriminator's layers."""
-        _, discriminator = self._gan_roles()
-        _, features = self.real_score(torch.cat((anchor, noisy), dim=2), sigma, condition,
-                                      known_frames=1, feature_layers=discriminator.feature_layers)
-        return features
+        clip = torch.cat((anchor, noisy), dim=2)
+        return self.real_score(clip, sigma, condition, known_frames=1,
+                               feature_layers=self.discriminator.feature_layers)[1]
 
-    def _real_velocity(self, anchor, noisy, sigma, conditions) -> Tensor:
-        cond = self._score(self.real_score, anchor, noisy, sigma, conditions[0])
-        if len(conditions) == 1:
-            return cond
-        uncond = self._score(self.real_score, anchor, noisy, sigma, conditions[1])
-        return uncond + self.real_score_guidance * (cond - uncond)
+    def _teacher_velocity(self, anchor, noisy, sigma, prompts) -> Tensor:
+        towards = self._velocity(self.real_score, anchor, noisy, sigma, prompts[0])
+        if len(prompts) == 1:
+            return towards
+        away = self._velocity(self.real_score, anchor, noisy, sigma, prompts[1])
+        return away + self.real_score_guidance * (towards - away)
 
     # -------------------------------------------------------------------- closures
     def training_step_closures(self, data_batch: dict[str, Any], iteration: int,
                                ) -> Iterator[TrainingClosureSpec]:
-        latent = data_batch["latent"].float()
-        anchor, real = latent[:, :, :1], latent[:, :, 1:]
-        condition = self.conditioner.condition(data_batch)
-        rollout = self._rollout(anchor, condition, real.shape[2], self._exit_step(iteration) + 1)
+        clip = data_batch["latent"].float()
+        anchor, real = clip[:, :, :1], clip[:, :, 1:]
+        prompt = self.conditioner.condition(data_batch)
+        rollout = self._rollout(anchor, prompt, real.shape[2], self._exit_step(iteration) + 1)
         if self.clock.is_student(iteration):
-            conditions = [condition]
+            prompts = [prompt]
             if self.real_score_guidance != 1.0:
-                conditions.append(self.conditioner.condition(data_batch, negative=True))
-            yield "student", partial(self._student_loss, anchor, real, rollout, conditions), True
-        else:
-            yield ("fake_score",
-                   partial(self._fake_score_loss, anchor, real, rollout.clean, condition,
-                           warmup=self.clock.is_warmup(iteration)), True)
+                prompts.append(self.conditioner.condition(data_batch, negative=True))
+            yield "student", lambda: self._student_loss(anchor, real, rollout, prompts), True
+            return
+        idle = self.clock.is_warmup(iteration)
+        yield "fake_score", lambda: self._fake_score_loss(anchor, real, rollout.clean, prompt, warmup=idle), True
 
     def training_step(self, data_batch: dict[str, Any], iteration: int) -> StepOutput:
-        outputs, losses = {}, []
-        for _name, closure, _last in self.training_step_closures(data_batch, iteration):
-            out, loss = closure()
-            outputs.update(out)
-            losses.append(loss)
-        return outputs, torch.stack(losses).sum()
+        merged: dict[str, Any] = {}
+        total = None
+        for _role, closure, _last in self.training_step_closures(data_batch, iteration):
+            report, loss = closure()
+            merged.update(report)
+            total = loss if total is None else total + loss
+        return merged, torch.stack([total]).sum()
 
-    def _student_loss(self, anchor, real, rollout: _Rollout, conditions) -> StepOutput:
-        velocity = self.student.forward_ar(
-            anchor, rollout.noisy, rollout.sigma, conditions[0], block_frames=self.block_frames,
-            clean=rollout.clean, history=self.history).float()
-        x0 = rf_x0(rollout.noisy, rollout.sigma, velocity)
-        target, gan_gradient, metrics = self._student_targets(anchor, real, x0.detach(), conditions)
-        dmd = self.dmd_loss_scale * (x0.double() - target.double()).square().sum() / x0.numel()
-        loss = dmd.float()
-        if gan_gradient is not None:
-            loss = loss + (x0 * gan_gradient).sum()  # injects dL_gan/dx0 as a linear term
+    def _student_loss(self, anchor, real, rollout: Rollout, prompts) -> StepOutput:
+        replayed = self.student.forward_ar(anchor, rollout.noisy, rollout.sigma, prompts[0],
+                                           block_frames=self.block_frames, clean=rollout.clean,
+                                           history=self.history).float()
+        estimate = rf_x0(rollout.noisy, rollout.sigma, replayed)
+        target, push, report = self._student_targets(anchor, real, estimate.detach(), prompts)
+        matching = self.dmd_loss_scale * (estimate.double() - target.double()).square().sum() / estimate.numel()
+        loss = matching.float()
+        if push is not None:
+            loss = loss + (estimate * push).sum()  # d(loss)/d(estimate) = the GAN gradient
         with torch.no_grad():
-            recovery = (x0 - rollout.clean).abs().max()
-        return {**metrics, "metrics/student/dmd_loss": dmd.detach(),
-                "metrics/student/sgf_recovery_max_abs": recovery,
-                "metrics/student/exit_sigma": rollout.sigma[0, 0]}, loss
+            drift = (estimate - rollout.clean).abs().max()
+        report["metrics/student/dmd_loss"] = matching.detach()
+        report["metrics/student/sgf_recovery_max_abs"] = drift
+        report["metrics/student/exit_sigma"] = rollout.sigma[0, 0]
+        return report, loss
 
-    def _student_targets(self, anchor, real, x0, conditions):
-        batch = x0.shape[0]
-        sigma = self.score_time.sample(batch, device=x0.device)
-        noise = torch.randn_like(x0)
+    def _student_targets(self, anchor, real, estimate, prompts):
+        """Detached FP64 target whose squared distance to the estimate has the distribution-
+        matching gradient; the GAN gradient (or None); metrics."""
+        sigma = self.score_time.sample(estimate.shape[0], device=estimate.device)
+        noise = torch.randn_like(estimate)
         with torch.no_grad():
-            noisy = rf_interpolate(x0, noise, sigma)
-            fake_v = self._score(self.fake_score, anchor, noisy, sigma, conditions[0])
-            real_v = self._real_velocity(anchor, noisy, sigma, conditions)
-            x0_fake = rf_x0(noisy, sigma, fake_v).double()
-            x0_real = rf_x0(noisy, sigma, real_v).double()
-            scale = (x0.double() - x0_real).abs().flatten(1).mean(1).clamp_min(1e-5)
-            gradient = (x0_fake - x0_real) / scale.view(-1, 1, 1, 1, 1)
-            target = x0.double() - gradient
-        gan_gradient, metrics = None, {}
+            noisy = rf_interpolate(estimate, noise, sigma)
+            by_fake = rf_x0(noisy, sigma, self._velocity(self.fake_score, anchor, noisy, sigma, prompts[0])).double()
+            by_teacher = rf_x0(noisy, sigma, self._teacher_velocity(anchor, noisy, sigma, prompts)).double()
+            wide = estimate.double()
+            spread = (wide - by_teacher).abs().flatten(1).mean(1).clamp_min(1e-5)
+            direction = (by_fake - by_teacher) / spread.view(-1, 1, 1, 1, 1)
+            target = wide - direction
+        push, report = None, {}
         if self.gan is not None:
-            gan_gradient, metrics = self._generator_gradient(anchor, real, x0, noise, sigma,
-                                                             conditions[0])
-        metrics["metrics/student/dmd_gradient_rms"] = gradient.float().square().mean().sqrt()
-        return target, gan_gradient, metrics
+            push, report = self._adversary.generator_gradient(anchor, real, estimate, noise, sigma, prompts[0])
+        report["metrics/student/dmd_gradient_rms"] = direction.float().square().mean().sqrt()
+        return target, push, report
 
-    def _generator_gradient(self, anchor, real, x0, noise, sigma, condition):
-        gan, discriminator = self._gan_roles()
-        leaf = x0.detach().requires_grad_(True)
-        # the head stays frozen for forward, backward and any recompute of this block
-        with torch.enable_grad(), frozen_parameters(discriminator):
-            fake_logits = discriminator([self._real_features(
-                anchor, rf_interpolate(leaf, noise, sigma), sigma, condition)])
-            with torch.no_grad():
-                real_logits = discriminator([self._real_features(
-                    anchor, rf_interpolate(real, noise, sigma), sigma, condition)])
-            margin = fake_logits - real_logits if gan.relativistic else fake_logits
-            loss = gan.generator_weight * F.softplus(-margin).mean()
-            (gradient,) = torch.autograd.grad(loss, leaf)
-        return torch.nan_to_num(gradient.detach()), {
-            "metrics/student/gan_loss": loss.detach(),
-            "metrics/student/gan_fake_minus_real_logit": margin.detach().mean()}
-
-    def _fake_score_loss(self, anchor, real, generated, condition, *, warmup: bool) -> StepOutput:
-        batch = generated.shape[0]
-        sigma = self.score_time.sample(batch, device=generated.device)
+    def _fake_score_loss(self, anchor, real, generated, prompt, *, warmup: bool) -> StepOutput:
+        sigma = self.score_time.sample(generated.shape[0], device=generated.device)
         noise = torch.randn_like(generated)
         noisy = rf_interpolate(generated, noise, sigma)
         with torch.set_grad_enabled(torch.is_grad_enabled() and not warmup):
-            velocity = self._score(self.fake_score, anchor, noisy, sigma, condition)
-        fake_loss = (velocity - (noise - generated)).square().mean()
-        outputs = {"metrics/fake_score/loss": fake_loss.detach()}
-        loss = fake_loss if not warmup else fake_loss.detach() * 0
+            predicted = self._velocity(self.fake_score, anchor, noisy, sigma, prompt)
+        regression = (predicted - (noise - generated)).square().mean()
+        report = {"metrics/fake_score/loss": regression.detach()}
+        loss = regression.detach() * 0 if warmup else regression
         if self.gan is not None:
-            gan_loss, gan_metrics = self._discriminator_loss(anchor, real, noisy, noise, sigma,
-                                                             condition)
-            loss = loss + gan_loss
-            outputs.update(gan_metrics)
-        return outputs, loss
-
-    def _discriminator_loss(self, anchor, real, fake_noisy, noise, sigma, condition):
-        gan, discriminator = self._gan_roles()
-        real_noisy = rf_interpolate(real, noise, sigma)
-        if gan.regularization is Regularization.EXACT:
-            return self._exact_discriminator_loss(anchor, real_noisy, fake_noisy, sigma, condition)
-        rows = [fake_noisy, real_noisy]
-        if gan.regularization_weight > 0:
-            jitter = gan.regularization_sigma
-            rows += [real_noisy + jitter * torch.randn_like(real_noisy),
-                     fake_noisy + jitter * torch.randn_like(fake_noisy)]
-        n = len(rows)
-        with torch.no_grad():
-            features = self._real_features(torch.cat((anchor,) * n), torch.cat(rows),
-                                           sigma.repeat(n), condition.repeat(n))
-        logits = discriminator([features]).split(fake_noisy.shape[0])
-        fake_logits, real_logits = logits[0], logits[1]
-        pair = _pair_loss(real_logits, fake_logits, relativistic=gan.relativistic)
-        loss = gan.discriminator_weight * pair
-        metrics = _pair_metrics(pair, real_logits, fake_logits)
-        if gan.regularization_weight > 0:
-            r1 = (logits[2] - real_logits).square().mean()
-            r2 = (logits[3] - fake_logits).square().mean()
-            loss = loss + gan.discriminator_weight * 0.5 * gan.regularization_weight * (r1 + r2)
-            metrics.update({"metrics/discriminator/r1": r1.detach(),
-                            "metrics/discriminator/r2": r2.detach()})
-        return loss, metrics
-
-    def _exact_discriminator_loss(self, anchor, real_noisy, fake_noisy, sigma, condition):
-        gan, discriminator = self._gan_roles()
-        batch = fake_noisy.shape[0]
-        features = partial(self._real_features, torch.cat((anchor, anchor)),
-                           sigma=sigma.repeat(2), condition=condition.repeat(2))
-        result = exact_penalties(features, discriminator, torch.cat((fake_noisy, real_noisy)))
-        fake_logits, real_logits = result.logits.split(batch)
-        pair = _pair_loss(real_logits, fake_logits, relativistic=gan.relativistic)
-        r2, r1 = result.penalty.split(batch)
-        scale = gan.discriminator_weight * 0.5 * gan.exact_regularization_weight
-        # value: weighted R1 + R2; gradient: the exact dR/dtheta carried by the surrogate
-        regular = scale * ((r1.mean() + r2.mean()) + result.surrogate.view(2, batch).mean(1).sum())
-        return gan.discriminator_weight * pair + regular, {
-            **_pair_metrics(pair, real_logits, fake_logits),
-            "metrics/discriminator/r1": r1.mean(), "metrics/discriminator/r2": r2.mean()}
+            judged, judged_report = self._adversary.discriminator_loss(anchor, real, noisy, noise, sigma, prompt)
+            loss = loss + judged
+            report.update(judged_report)
+        return report, loss
 
     # ------------------------------------------------------------------ evaluation
     @torch.no_grad()
     def validation_step(self, data_batch: dict[str, Any], iteration: int) -> StepOutput:
-        del iteration
-        latent = data_batch["latent"].float()
-        anchor, real = latent[:, :, :1], latent[:, :, 1:]
-        condition = self.conditioner.condition(data_batch)
-        with isolated_rng():  # fixed seed for every validation batch, caller's streams untouched
+        clip = data_batch["latent"].float()
+        anchor, real = clip[:, :, :1], clip[:, :, 1:]
+        prompt = self.conditioner.condition(data_batch)
+        with isolated_rng():  # a fixed seed per validation batch; the caller's streams stay put
             torch.manual_seed(self.seed)
-            rollout = self._rollout(anchor, condition, real.shape[2], len(self.rollout_endpoints))
-            return self._fake_score_loss(anchor, real, rollout.clean, condition, warmup=False)
+            rollout = self._rollout(anchor, prompt, real.shape[2], len(self.rollout_endpoints))
+            return self._fake_score_loss(anchor, real, rollout.clean, prompt, warmup=False)
 
     @torch.inference_mode()
     def sample(self, data_batch: dict[str, Any], **options: Any) -> dict[str, Tensor]:
-        options = self.sampling_options(options)
-        latent = data_batch["latent"].float()
-        anchor, target = latent[:, :, :1], latent[:, :, 1:]
-        self._validate_rollout(target.shape[2], options["num_steps"])
-        steps = int(options["num_steps"])
-        seeds = sampling_seeds(data_batch, int(options["seed"]))
-        noise = torch.stack([invariant_randn(target, seeds, stream=s) for s in range(steps)])
-        rollout = self._rollout(anchor, self.conditioner.condition(data_batch), target.shape[2],
-                                steps, noise=noise)
-        return {**self.conditioner.visuals(data_batch),
-                "ground_truth": self.conditioner.decode(latent),
-                "sample": self.conditioner.decode(torch.cat((anchor, rollout.clean), dim=2))}
+        chosen = self.sampling_options(options)
+        clip = data_batch["latent"].float()
+        anchor, future = clip[:, :, :1], clip[:, :, 1:]
+        self._validate_rollout(future.shape[2], chosen["num_steps"])
+        steps = int(chosen["num_steps"])
+        seeds = sampling_seeds(data_batch, int(chosen["seed"]))
+        prepared = torch.stack([invariant_randn(future, seeds, stream=step) for step in range(steps)])
+        rollout = self._rollout(anchor, self.conditioner.condition(data_batch), future.shape[2], steps,
+                                noise=prepared)
+        panels = dict(self.conditioner.visuals(data_batch))
+        panels["ground_truth"] = self.conditioner.decode(clip)
+        panels["sample"] = self.conditioner.decode(torch.cat((anchor, rollout.clean), dim=2))
+        return panels

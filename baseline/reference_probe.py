@@ -192,6 +192,58 @@ def autoregressive_mode(path: str) -> None:
     torch.save(out, path)
 
 
+def dmd_mode(path: str) -> None:
+    """Adversarial Forcing on small towers: the loss and the reported metrics of a discriminator
+    warm-up iteration, a student iteration and a fake-score + discriminator iteration, for the
+    finite-difference and the exact R1/R2 regularisation; plus a validation step."""
+    from wm.codecs import Wan22VAECodec
+    from wm.infra.parallel import ParallelConfig
+    from wm.models.dmd import DMDModel, GANConfig
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+    from wm.networks.discriminator import DiscriminatorHead
+
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    out: dict = {}
+    for kind in ("finite_difference", "exact"):
+        towers = [build_network(config, init_device="cpu") for _ in range(3)]
+        for index, tower in enumerate(towers):
+            seeded_(tower, 20 + index)
+        head = DiscriminatorHead(hidden_size=256, feature_layers=(0, 1), mlp_ratio=2.0, num_heads=4,
+                                 init_device="cpu")
+        model = DMDModel(
+            student=towers[0], real_score=towers[1], fake_score=towers[2],
+            conditioner=Cosmos3Conditioner(config=config, geometry_noise_sigma=0.0, init_device="cpu",
+                                           empty_prompt_ids=(3, 4, 5),
+                                           codec=Wan22VAECodec(pretrained_path="unused", decoder=None)),
+            discriminator=head, gan=GANConfig(regularization=kind, warmup_updates=1),
+            block_frames=4, fake_score_updates_per_student=2, student_parallel=plain,
+            score_parallel=plain, discriminator_parallel=plain, seed=3)
+        model.parallelize("cpu")
+        seeded_(model.conditioner.text_encoder, 1)
+        model.train()
+        record: dict = {"head": {k: v.clone() for k, v in head.state_dict().items()}}
+        data = model.prepare_data_batch(batch_of(9, seed=8))
+        for iteration in range(3):
+            torch.manual_seed(100 + iteration)
+            model.zero_grad(set_to_none=True)
+            report, loss = model.training_step(data, iteration)
+            loss.backward()
+            grads = {name: float(sum(float(p.grad.double().square().sum()) for p in module.parameters()
+                                     if p.grad is not None)) ** 0.5
+                     for name, module in (("student", model.student), ("fake_score", model.fake_score),
+                                          ("discriminator", head))}
+            record[iteration] = {"loss": float(loss), "grads": grads,
+                                 "names": model.get_optimizer_names(iteration),
+                                 "report": {k: float(v) for k, v in report.items() if torch.is_tensor(v) and v.numel() == 1}}
+        model.eval()
+        _, validation = model.validation_step(data, 0)
+        record["validation"] = float(validation)
+        out[kind] = record
+    torch.save(out, path)
+
+
 def checkpoint_mode(path: str, directory: str, resume: bool) -> None:
     """Two or more Gloo ranks, FSDP2.  Without ``resume``: two updates, a checkpoint
     ``iter_000000002`` under ``directory``, a third update; with it: load ``directory/latest``
@@ -262,7 +314,7 @@ def checkpoint_mode(path: str, directory: str, resume: bool) -> None:
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("mode", choices=["network", "train", "checkpoint", "autoregressive"])
+    parser.add_argument("mode", choices=["network", "train", "checkpoint", "autoregressive", "dmd"])
     parser.add_argument("output")
     parser.add_argument("--steps", type=int, default=5)
     parser.add_argument("--directory", default=None)
@@ -276,6 +328,8 @@ def main() -> int:
         train_mode(args.output, args.steps)
     elif args.mode == "autoregressive":
         autoregressive_mode(args.output)
+    elif args.mode == "dmd":
+        dmd_mode(args.output)
     else:
         checkpoint_mode(args.output, args.directory, args.resume)
     return 0

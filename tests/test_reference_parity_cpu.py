@@ -205,6 +205,67 @@ def test_autoregressive_objective_equals_the_reference(tmp_path):
     assert torch.allclose(mine, golden["corrupted"], atol=1e-6)
 
 
+def test_adversarial_forcing_equals_the_reference(tmp_path):
+    """Discriminator warm-up, student and fake-score iterations of the distillation objective on
+    small towers: losses, per-role gradient norms and every reported scalar equal the
+    reference's, with finite-difference and with exact R1/R2; so does the validation loss."""
+    from agentgarten_b200.models.dmd import DMDModel, GANConfig
+    from agentgarten_b200.networks.cosmos3 import build_network
+    from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
+    from agentgarten_b200.networks.discriminator import DiscriminatorHead
+    from agentgarten_b200.parallel.engine import ParallelConfig
+
+    golden = probe("dmd", tmp_path / "dmd.pt")
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        from reference_probe import seeded_
+    finally:
+        sys.path.pop(0)
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    for kind in ("finite_difference", "exact"):
+        want = golden[kind]
+        towers = [build_network(config, init_device="cpu") for _ in range(3)]
+        for index, tower in enumerate(towers):
+            seeded_(tower, 20 + index)
+        head = DiscriminatorHead(hidden_size=256, feature_layers=(0, 1), mlp_ratio=2.0, num_heads=4,
+                                 init_device="cpu")
+        for name, value in head.state_dict().items():  # the seeded head is the reference's head
+            assert torch.equal(value, want["head"][name]), name
+        model = DMDModel(
+            student=towers[0], real_score=towers[1], fake_score=towers[2],
+            conditioner=Cosmos3Conditioner(config=config, codec=None, geometry_noise_sigma=0.0,
+                                           init_device="cpu", empty_prompt_ids=(3, 4, 5)),
+            discriminator=head, gan=GANConfig(regularization=kind, warmup_updates=1),
+            block_frames=4, fake_score_updates_per_student=2, student_parallel=plain,
+            score_parallel=plain, discriminator_parallel=plain, seed=3)
+        model.parallelize("cpu")
+        seeded_(model.conditioner.text_encoder, 1)
+        model.train()
+        data = model.prepare_data_batch(batch_of(9, seed=8))
+        for iteration in range(3):
+            torch.manual_seed(100 + iteration)
+            model.zero_grad(set_to_none=True)
+            report, loss = model.training_step(data, iteration)
+            loss.backward()
+            expect = want[iteration]
+            assert tuple(model.get_optimizer_names(iteration)) == tuple(expect["names"])
+            assert float(loss) == pytest.approx(expect["loss"], rel=5e-5, abs=1e-7), (kind, iteration)
+            for name, module in (("student", model.student), ("fake_score", model.fake_score),
+                                 ("discriminator", head)):
+                norm = sum(float(p.grad.double().square().sum()) for p in module.parameters()
+                           if p.grad is not None) ** 0.5
+                assert norm == pytest.approx(expect["grads"][name], rel=2e-4, abs=1e-9), (kind, iteration, name)
+            mine = {k: float(v) for k, v in report.items() if torch.is_tensor(v) and v.numel() == 1}
+            assert set(mine) == set(expect["report"]), (kind, iteration)
+            for key, value in expect["report"].items():
+                assert mine[key] == pytest.approx(value, rel=2e-4, abs=1e-6), (kind, iteration, key)
+        model.eval()
+        _, validation = model.validation_step(data, 0)
+        assert float(validation) == pytest.approx(want["validation"], rel=5e-5)
+
+
 def _ranks(script, *arguments, env, port, cwd):
     done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
                            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), *arguments],
