@@ -24,7 +24,7 @@ def _job(seed=0):
 
 def _step(model, opt, sched, batch, seed):
     g = torch.Generator().manual_seed(seed)
-    _, loss = model._loss(batch, generator=g, drop_text=False)
+    _, loss = model._objective(batch, g, None)
     loss.backward()
     opt.step()
     sched.step()

@@ -50,7 +50,7 @@ def test_fused_layer_matches_op_path_and_fp32(monkeypatch):
     def run(m, b, device):
         g = torch.Generator(device=device).manual_seed(7)
         m.zero_grad(set_to_none=True)
-        out, loss = m._loss(m.prepare_data_batch(b), generator=g, drop_text=False)
+        out, loss = m._objective(m.prepare_data_batch(b), g, None)
         loss.backward()
         return float(loss), {n: p.grad.detach().float().cpu() for n, p in m.net.named_parameters()
                              if p.grad is not None}

@@ -65,7 +65,7 @@ def test_bidirectional_training_step_decreases_loss():
     losses = []
     for it in range(8):
         g = torch.Generator().manual_seed(0)
-        _, loss = model._loss(batch, generator=g, drop_text=False)
+        _, loss = model._objective(batch, g, None)
         loss.backward()
         opt.step()
         opt.zero_grad()
