@@ -18,7 +18,15 @@ projection plus a modality embedding), each with its own 3-axis RoPE positions. 
 prompt never becomes a token of this tower: the text tower's per-layer keys and values are
 prepended to the keys of every layer.
 
-Parity: reference ``wm/networks/cosmos3/network.py:59-568``.
+Every entry point describes its input as a short *chunk table* (:class:`_ChunkTable`): rows of
+(latent frames, per-frame sigma or none, index of the first frame, is-it-the-reference-frame),
+which the table turns into token chunks, RoPE positions and — for AdaLN networks — per-token
+timestep embeddings, one row at a time, so that a frame is embedded with the same row count
+whether it arrives through ``forward_ar`` or through the cached rollout (their outputs must be
+bit-identical).
+
+Parity: reference ``wm/networks/cosmos3/network.py:59-568`` (module and parameter names, entry
+point signatures, token order, position formula).
 """
 
 from __future__ import annotations
@@ -27,6 +35,7 @@ from collections.abc import Callable, Sequence
 from dataclasses import dataclass, replace
 
 import torch
+from einops import rearrange
 from torch import nn
 
 from agentgarten_b200.parallel.network import ParallelNetwork
@@ -67,14 +76,16 @@ Attention = Callable[[int, list, list, list], list]
 
 def pack_text_rows(input_ids: torch.Tensor, attention_mask: torch.Tensor | None,
                    special_tokens: dict[str, int]) -> list[torch.Tensor]:
-    """Strip padding and wrap each prompt as ``[bos?] ids eos start_of_generation``."""
-    if attention_mask is None:
-        rows = list(input_ids.unbind(0))
-    else:
-        rows = [row[mask.bool()] for row, mask in zip(input_ids, attention_mask, strict=True)]
-    head = [special_tokens["bos_token_id"]] if "bos_token_id" in special_tokens else []
-    tail = [special_tokens["eos_token_id"], special_tokens["start_of_generation"]]
-    return [torch.cat((row.new_tensor(head), row.long(), row.new_tensor(tail))) for row in rows]
+    """Unpadded prompts wrapped as ``[bos?] ids eos start_of_generation`` (one 1-D tensor each)."""
+    opening = [special_tokens[key] for key in ("bos_token_id",) if key in special_tokens]
+    closing = [special_tokens["eos_token_id"], special_tokens["start_of_generation"]]
+    packed = []
+    for index in range(input_ids.shape[0]):
+        ids = input_ids[index]
+        if attention_mask is not None:
+            ids = ids[attention_mask[index].bool()]
+        packed.append(torch.cat((ids.new_tensor(opening), ids.long(), ids.new_tensor(closing))))
+    return packed
 
 
 class Cosmos3TextEncoder(ParallelNetwork):
@@ -94,23 +105,22 @@ class Cosmos3TextEncoder(ParallelNetwork):
     @torch.no_grad()
     def forward(self, input_ids: torch.Tensor,
                 attention_mask: torch.Tensor | None = None) -> TextContext:
-        rows = pack_text_rows(input_ids, attention_mask, self.config.special_tokens)
-        lengths = tuple(int(row.numel()) for row in rows)
-        bucket = max(*lengths, int(self.config.text_bucket_tokens or 0))
         device = self.embed_tokens.weight.device
-        tokens = torch.zeros(len(rows), bucket, dtype=torch.long, device=device)
-        for index, row in enumerate(rows):
-            tokens[index, : row.numel()] = row.to(device)
-        hidden = self.embed_tokens(tokens)
-        steps = torch.arange(bucket, device=device, dtype=torch.float32)
-        positions = steps[None, :, None].expand(len(rows), -1, 3)
-        rope = self.rotary_emb(positions, hidden.dtype)
-        keys, values = [], []
+        prompts = pack_text_rows(input_ids, attention_mask, self.config.special_tokens)
+        lengths = tuple(int(prompt.numel()) for prompt in prompts)
+        # one stable width on every rank (longer prompts widen it locally), zero padded
+        width = max(max(lengths), int(self.config.text_bucket_tokens or 0))
+        table = torch.zeros(len(prompts), width, dtype=torch.long, device=device)
+        for row, prompt in zip(table, prompts):
+            row[: prompt.numel()] = prompt.to(device)
+        hidden = self.embed_tokens(table)
+        index = torch.arange(width, device=device, dtype=torch.float32)
+        rope = self.rotary_emb(index.view(1, width, 1).expand(len(prompts), width, 3), hidden.dtype)
+        per_layer = []
         for layer in self.layers:
             hidden, key, value = layer(hidden, rope)
-            keys.append(key)
-            values.append(value)
-        return TextContext(keys=tuple(keys), values=tuple(values),
+            per_layer.append((key, value))
+        return TextContext(keys=tuple(k for k, _ in per_layer), values=tuple(v for _, v in per_layer),
                            valid_lengths=torch.tensor(lengths, device=device), lengths=lengths)
 
 
@@ -122,13 +132,11 @@ class Cosmos3Condition:
     fps: torch.Tensor
 
     def repeat(self, times: int) -> "Cosmos3Condition":
+        """The same condition for ``times`` stacked copies of the batch."""
         if times == 1:
             return self
-        return Cosmos3Condition(
-            text=self.text.repeat(times),
-            depth=torch.cat((self.depth,) * times),
-            normal=torch.cat((self.normal,) * times),
-            fps=torch.cat((self.fps,) * times))
+        tiled = {name: torch.cat([getattr(self, name)] * times) for name in ("depth", "normal", "fps")}
+        return Cosmos3Condition(text=self.text.repeat(times), **tiled)
 
     def with_text(self, text: TextContext) -> "Cosmos3Condition":
         return replace(self, text=text)
@@ -136,21 +144,16 @@ class Cosmos3Condition:
 
 def patchify(latent: torch.Tensor, patch_size: int) -> torch.Tensor:
     """``[B, C, T, H, W]`` → ``[B, T, (H/p)(W/p), p*p*C]`` (patch pixels row-major, C fastest)."""
-    b, c, t, h, w = latent.shape
-    if h % patch_size or w % patch_size:
-        raise ValueError(f"latent {h}x{w} is not divisible by patch {patch_size}")
-    p = patch_size
-    view = latent.reshape(b, c, t, h // p, p, w // p, p)
-    return view.permute(0, 2, 3, 5, 4, 6, 1).reshape(b, t, (h // p) * (w // p), p * p * c)
+    height, width = latent.shape[-2:]
+    if height % patch_size or width % patch_size:
+        raise ValueError(f"latent {height}x{width} is not divisible by patch {patch_size}")
+    return rearrange(latent, "b c t (h p) (w q) -> b t (h w) (p q c)", p=patch_size, q=patch_size)
 
 
 def unpatchify(patches: torch.Tensor, *, channels: int, grid: tuple[int, int],
                patch_size: int) -> torch.Tensor:
-    b, t = patches.shape[:2]
-    gh, gw = grid
-    p = patch_size
-    view = patches.reshape(b, t, gh, gw, p, p, channels)
-    return view.permute(0, 6, 1, 2, 4, 3, 5).reshape(b, channels, t, gh * p, gw * p)
+    return rearrange(patches, "b t (h w) (p q c) -> b c t (h p) (w q)", h=grid[0], w=grid[1],
+                     p=patch_size, q=patch_size, c=channels)
 
 
 @dataclass(frozen=True)
@@ -162,19 +165,64 @@ class GeometryFrames:
     rgb_positions: torch.Tensor
 
     def chunk(self, rgb: torch.Tensor, start: int, stop: int):
-        """Interleave RGB tokens ``[B, T, N, D]`` with frames ``start:stop`` → (tokens, positions)."""
+        """RGB tokens ``[B, T, N, D]`` of frames ``start:stop`` of this span, each frame followed
+        by its geometry tokens → (tokens ``[B, L, D]``, positions ``[B, L, 3]``)."""
+        span = slice(start, stop)
         if self.geometry is None:
-            return rgb.flatten(1, 2), self.rgb_positions[:, start:stop].flatten(1, 2)
-        tokens = torch.cat((rgb, self.geometry[:, start:stop]), dim=2).flatten(1, 2)
-        positions = torch.cat(
-            (self.rgb_positions[:, start:stop], self.geometry_positions[:, start:stop]),
-            dim=2).flatten(1, 2)
-        return tokens, positions
+            per_frame, where = rgb, self.rgb_positions[:, span]
+        else:
+            per_frame = torch.cat((rgb, self.geometry[:, span]), dim=2)
+            where = torch.cat((self.rgb_positions[:, span], self.geometry_positions[:, span]), dim=2)
+        return per_frame.flatten(1, 2), where.flatten(1, 2)
 
 
 def rgb_tokens(hidden: torch.Tensor, frames: int, grid: tuple[int, int]) -> torch.Tensor:
-    """Pick the RGB tokens of every frame out of frame-major hidden states."""
+    """The RGB tokens of every frame out of frame-major hidden states: ``[B, T, N, D]``."""
     return hidden.unflatten(1, (frames, -1))[:, :, : grid[0] * grid[1]]
+
+
+class _ChunkTable:
+    """Rows of an entry point's input, embedded one by one (see the module text)."""
+
+    def __init__(self, network: "Cosmos3Network", condition: "Cosmos3Condition",
+                 grid: tuple[int, int]) -> None:
+        self.network, self.condition, self.grid = network, condition, grid
+        self.tokens: list[torch.Tensor] = []
+        self.positions: list[torch.Tensor] = []
+        self.time_tokens: list[torch.Tensor | None] = []
+        self.per_frame = network._tokens_per_frame(condition, grid)
+
+    def add(self, latent: torch.Tensor, sigma: torch.Tensor | None, first: int, *,
+            reference: bool = False) -> None:
+        """``latent`` [B, C, T, H, W] are condition frames ``first : first + T``; ``sigma`` [B, T]
+        or ``None`` for clean frames; ``reference`` marks the external first frame."""
+        network, count = self.network, latent.shape[2]
+        rgb = network.embed_rgb(latent, sigma, reference=reference, condition=self.condition, start=first)
+        self._push(rgb, sigma, first, count, latent.shape[0])
+
+    def add_mixed(self, latent: torch.Tensor, sigma: torch.Tensor, known: int) -> None:
+        """One chunk whose first ``known`` frames are clean (the very first one being the
+        reference frame) and whose other frames carry ``sigma`` [B, T]: the bidirectional input."""
+        network = self.network
+        clean = network.embed_rgb(latent[:, :, :known], None, condition=self.condition)
+        if known and network.config.first_frame_reference_embedding:
+            mark = network.first_frame_reference_embed.to(clean.dtype)
+            clean = torch.cat((clean[:, :1] + mark, clean[:, 1:]), dim=1)
+        noisy = network.embed_rgb(latent[:, :, known:], sigma[:, known:], condition=self.condition, start=known)
+        levels = torch.cat((torch.zeros_like(sigma[:, :known]), sigma[:, known:]), dim=1)
+        self._push(torch.cat((clean, noisy), dim=1), levels, 0, latent.shape[2], latent.shape[0])
+
+    def _push(self, rgb, sigma, first, count, batch) -> None:
+        frame = self.network.geometry_frames(self.condition, start=first, stop=first + count, rgb_grid=self.grid)
+        tokens, positions = frame.chunk(rgb, 0, count)
+        self.tokens.append(tokens)
+        self.positions.append(positions)
+        self.time_tokens.append(self.network._time_tokens(sigma, batch, count, self.per_frame))
+
+    def run(self, policy, *, feature_layers: Sequence[int] = ()):
+        adaln = self.network.config.timestep_conditioning == "adaln"
+        return self.network.run_layers(self.tokens, self.positions, policy, feature_layers=feature_layers,
+                                       time_embeddings=self.time_tokens if adaln else None)
 
 
 class Cosmos3Network(ParallelNetwork):
@@ -202,31 +250,40 @@ class Cosmos3Network(ParallelNetwork):
             mesh, self.config.num_attention_heads, self.config.num_key_value_heads)
 
     def initialize_after_materialization(self) -> None:
+        """Parameters that no released checkpoint provides start at their neutral values."""
         from agentgarten_b200.networks.lora import initialize_lora_parameters
 
         initialize_lora_parameters(self)
+        width = self.config.hidden_size
         with torch.no_grad():
             self.geometry_modality_embed.zero_()
             self.first_frame_reference_embed.zero_()
             for layer in self.layers:
-                if layer.adaln is not None:
-                    layer.adaln.weight.zero_()
-                    layer.adaln.bias.zero_()
-                    layer.adaln.bias[2 * self.config.hidden_size: 3 * self.config.hidden_size] = 1
-                    layer.adaln.bias[5 * self.config.hidden_size:] = 1
+                if layer.adaln is None:
+                    continue
+                layer.adaln.weight.zero_()
+                layer.adaln.bias.zero_()
+                layer.adaln.bias[2 * width: 3 * width] = 1   # gates of the two halves open
+                layer.adaln.bias[5 * width:] = 1
 
     # ------------------------------------------------------------------- embedding
     @property
     def dtype(self) -> torch.dtype:
         return self.proj_in.weight.dtype
 
+    def _grid(self, latent: torch.Tensor) -> tuple[int, int]:
+        patch = self.config.patch_size
+        return latent.shape[-2] // patch, latent.shape[-1] // patch
+
     def _patches(self, latent, condition, start, stop):
-        patches = patchify(latent.to(self.dtype), self.config.patch_size)
+        """Patch vectors of latent frames; with channel-wise geometry the depth and normal
+        patches of the same frames are appended to every vector."""
+        patch = self.config.patch_size
+        parts = [patchify(latent.to(self.dtype), patch)]
         if self.config.geometry_mode == "channels":
-            depth = patchify(condition.depth[:, :, start:stop].to(self.dtype), self.config.patch_size)
-            normal = patchify(condition.normal[:, :, start:stop].to(self.dtype), self.config.patch_size)
-            patches = torch.cat((patches, depth, normal), dim=-1)
-        return patches
+            parts += [patchify(control[:, :, start:stop].to(self.dtype), patch)
+                      for control in (condition.depth, condition.normal)]
+        return parts[0] if len(parts) == 1 else torch.cat(parts, dim=-1)
 
     def embed_rgb(self, latent: torch.Tensor, sigma: torch.Tensor | None, *,
                   reference: bool = False, condition: "Cosmos3Condition | None" = None,
@@ -236,19 +293,17 @@ class Cosmos3Network(ParallelNetwork):
         ``sigma`` ``[B, T]`` adds the timestep embedding; ``None`` marks clean frames.
         ``reference`` marks a chunk that is exactly the external first frame C0.
         """
-        frames = latent.shape[2]
-        tokens = self.proj_in(self._patches(latent, condition, start, start + frames))
+        tokens = self.proj_in(self._patches(latent, condition, start, start + latent.shape[2]))
         if reference and self.config.first_frame_reference_embedding:
             tokens = tokens + self.first_frame_reference_embed.to(tokens.dtype)
-        if sigma is not None:
-            tokens = tokens + self.time_embedding(sigma)[:, :, None].to(tokens.dtype)
-        return tokens
+        if sigma is None:
+            return tokens
+        return tokens + self.time_embedding(sigma)[:, :, None].to(tokens.dtype)
 
     def time_embedding(self, sigma: torch.Tensor) -> torch.Tensor:
         """Per-frame FP32 timestep embedding ``[B, T, D]``."""
-        batch, frames = sigma.shape
-        timestep = sigma.reshape(-1).float() * 1000.0 * self.config.timestep_scale
-        return self.time_embedder(timestep).reshape(batch, frames, -1)
+        scaled = sigma.float().flatten() * (1000.0 * self.config.timestep_scale)
+        return self.time_embedder(scaled).unflatten(0, tuple(sigma.shape))
 
     def geometry_frames(self, condition: "Cosmos3Condition", *, start: int, stop: int,
                         rgb_grid: tuple[int, int],
@@ -259,43 +314,37 @@ class Cosmos3Network(ParallelNetwork):
         geometry rows/columns are rescaled onto the RGB grid.  ``frame_indices`` overrides
         the temporal indices (streaming relocates retained history).
         """
-        config = self.config
-        device = condition.depth.device
-        if frame_indices is None:
-            temporal = torch.arange(start, stop, device=device, dtype=torch.float32)[None]
-        else:
-            temporal = frame_indices.to(device=device, dtype=torch.float32)[None]
+        config, device = self.config, condition.depth.device
+        indices = torch.arange(start, stop, device=device) if frame_indices is None else frame_indices
+        when = indices.to(device=device, dtype=torch.float32)[None]
         if config.enable_fps_modulation:
-            temporal = temporal * (config.base_fps / condition.fps.float().to(device))[:, None]
-        origin = condition.text.valid_lengths.to(device=device, dtype=torch.float32)
-        temporal = temporal + origin[:, None] + config.temporal_modality_margin
-        rgb_positions = _grid_positions(temporal, rgb_grid, rgb_grid)
+            when = when * (config.base_fps / condition.fps.float().to(device))[:, None]
+        prompt_length = condition.text.valid_lengths.to(device=device, dtype=torch.float32)
+        when = when + prompt_length[:, None] + config.temporal_modality_margin
+        rgb_positions = _grid_positions(when, rgb_grid, rgb_grid)
         if config.geometry_mode == "channels":
             return GeometryFrames(None, None, rgb_positions)
-        depth = patchify(condition.depth[:, :, start:stop].to(self.dtype), config.patch_size)
-        normal = patchify(condition.normal[:, :, start:stop].to(self.dtype), config.patch_size)
-        # proj_in is affine: projecting the mean equals the mean of the projections.
-        geometry = self.proj_in(torch.lerp(depth, normal, 0.5)) + self.geometry_modality_embed
-        geometry_grid = (condition.depth.shape[-2] // config.patch_size,
-                         condition.depth.shape[-1] // config.patch_size)
-        return GeometryFrames(
-            geometry=geometry,
-            geometry_positions=_grid_positions(temporal, geometry_grid, rgb_grid),
-            rgb_positions=rgb_positions)
+        controls = [patchify(control[:, :, start:stop].to(self.dtype), config.patch_size)
+                    for control in (condition.depth, condition.normal)]
+        # proj_in is affine: the projection of the mean is the mean of the projections
+        geometry = self.proj_in(torch.lerp(controls[0], controls[1], 0.5)) + self.geometry_modality_embed
+        return GeometryFrames(geometry=geometry,
+                              geometry_positions=_grid_positions(when, self._grid(condition.depth), rgb_grid),
+                              rgb_positions=rgb_positions)
 
     def decode_velocity(self, hidden: torch.Tensor, grid: tuple[int, int]) -> torch.Tensor:
         """RGB hidden states ``[B, T, N, D]`` → latent velocity ``[B, C, T, H, W]`` (≥FP32)."""
         patches = self.proj_out(self.norm_moe_gen(hidden))
-        return unpatchify(
-            patches.to(torch.promote_types(patches.dtype, torch.float32)),
-            channels=self.config.latent_channels, grid=grid, patch_size=self.config.patch_size)
+        wide = torch.promote_types(patches.dtype, torch.float32)
+        return unpatchify(patches.to(wide), channels=self.config.latent_channels, grid=grid,
+                          patch_size=self.config.patch_size)
 
     def _tokens_per_frame(self, condition, grid) -> int:
-        rgb = grid[0] * grid[1]
-        if self.config.geometry_mode == "channels":
-            return rgb
-        p = self.config.patch_size
-        return rgb + (condition.depth.shape[-2] // p) * (condition.depth.shape[-1] // p)
+        per_frame = grid[0] * grid[1]
+        if self.config.geometry_mode != "channels":
+            rows, columns = self._grid(condition.depth)
+            per_frame += rows * columns
+        return per_frame
 
     def _time_tokens(self, sigma, batch, frames, per_frame):
         """AdaLN only: per-token timestep embedding of a chunk (clean frames use sigma 0)."""
@@ -303,36 +352,36 @@ class Cosmos3Network(ParallelNetwork):
             return None
         if sigma is None:
             sigma = torch.zeros(batch, frames, device=self.proj_in.weight.device)
-        embedding = self.time_embedding(sigma).to(self.dtype)
-        return embedding[:, :, None].expand(-1, -1, per_frame, -1).flatten(1, 2)
+        per_frame_embedding = self.time_embedding(sigma).to(self.dtype)
+        return per_frame_embedding.repeat_interleave(per_frame, dim=1)
 
     # --------------------------------------------------------------------- decoder
     def run_layers(self, chunks: list[torch.Tensor], positions: list[torch.Tensor],
                    attention: Attention, *, feature_layers: Sequence[int] = (),
                    time_embeddings: list | None = None):
         """Run the layer stack; returns final chunks and the chunk lists of tapped layers."""
-        cp = self.context_parallel
-        sizes = [chunk.shape[1] for chunk in chunks]
-        if cp is not None:
+        sharding = self.context_parallel
+        lengths = [chunk.shape[1] for chunk in chunks]
+        if sharding is not None:
             from .context_parallel import ContextParallelAttention
 
-            chunks = [cp.shard(chunk) for chunk in chunks]
-            positions = [cp.shard(position) for position in positions]
+            chunks = [sharding.shard(chunk) for chunk in chunks]
+            positions = [sharding.shard(position) for position in positions]
             if time_embeddings is not None:
-                time_embeddings = [None if e is None else cp.shard(e) for e in time_embeddings]
-            attention = ContextParallelAttention(attention, cp, sizes)
-        ropes = [self.rotary_emb(position, chunk.dtype)
-                 for chunk, position in zip(chunks, positions, strict=True)]
-        wanted = frozenset(int(index) for index in feature_layers)
-        features: list[list[torch.Tensor]] = []
+                time_embeddings = [e if e is None else sharding.shard(e) for e in time_embeddings]
+            attention = ContextParallelAttention(attention, sharding, lengths)
+        ropes = [self.rotary_emb(position, chunk.dtype) for chunk, position in zip(chunks, positions, strict=True)]
+        tapped = {int(index): None for index in feature_layers}
         for index, layer in enumerate(self.layers):
             chunks = layer(chunks, ropes, attention, index, time_embeddings)
-            if index in wanted:
-                features.append(chunks)
-        if cp is not None:
-            chunks = [cp.gather(c, n) for c, n in zip(chunks, sizes, strict=True)]
-            features = [[cp.gather(c, n) for c, n in zip(group, sizes, strict=True)]
-                        for group in features]
+            if index in tapped:
+                tapped[index] = chunks
+        features = [tapped[index] for index in sorted(tapped) if tapped[index] is not None]
+        if sharding is not None:
+            def whole(group):
+                return [sharding.gather(chunk, length) for chunk, length in zip(group, lengths, strict=True)]
+
+            chunks, features = whole(chunks), [whole(group) for group in features]
         return chunks, features
 
     def _text(self, text: TextContext) -> TextContext:
@@ -342,148 +391,96 @@ class Cosmos3Network(ParallelNetwork):
     def forward(self, noisy: torch.Tensor, sigma: torch.Tensor, condition: Cosmos3Condition, *,
                 known_frames: int = 1, feature_layers: Sequence[int] = ()):
         batch, _, frames, height, width = noisy.shape
-        patch = self.config.patch_size
-        grid = (height // patch, width // patch)
-        sigma = frame_sigma(sigma, batch, frames).to(noisy.device)
-        known = self.embed_rgb(noisy[:, :, :known_frames], None, condition=condition)
-        if known_frames and self.config.first_frame_reference_embedding:
-            # Only the true first frame is the external reference C0.
-            known = torch.cat(
-                (known[:, :1] + self.first_frame_reference_embed.to(known.dtype), known[:, 1:]),
-                dim=1)
-        rest = self.embed_rgb(noisy[:, :, known_frames:], sigma[:, known_frames:],
-                              condition=condition, start=known_frames)
-        rgb = torch.cat((known, rest), dim=1)
-        frame = self.geometry_frames(condition, start=0, stop=frames, rgb_grid=grid)
-        tokens, positions = frame.chunk(rgb, 0, frames)
-        per_frame = self._tokens_per_frame(condition, grid)
-        time_tokens = None
-        if self.config.timestep_conditioning == "adaln":
-            mixed = torch.cat((torch.zeros_like(sigma[:, :known_frames]), sigma[:, known_frames:]), 1)
-            time_tokens = [self._time_tokens(mixed, batch, frames, per_frame)]
-        (hidden,), features = self.run_layers(
-            [tokens], [positions], FullAttention(self._text(condition.text)),
-            feature_layers=feature_layers, time_embeddings=time_tokens)
-        rgb_hidden = rgb_tokens(hidden, frames, grid)
-        velocity = self.decode_velocity(rgb_hidden[:, known_frames:], grid)
-        velocity = torch.cat(
-            (velocity.new_zeros(batch, velocity.shape[1], known_frames, height, width), velocity),
-            dim=2)
+        grid = self._grid(noisy)
+        table = _ChunkTable(self, condition, grid)
+        table.add_mixed(noisy, frame_sigma(sigma, batch, frames).to(noisy.device), known_frames)
+        (hidden,), features = table.run(FullAttention(self._text(condition.text)), feature_layers=feature_layers)
+        predicted = self.decode_velocity(rgb_tokens(hidden, frames, grid)[:, known_frames:], grid)
+        still = predicted.new_zeros(batch, predicted.shape[1], known_frames, height, width)
+        velocity = torch.cat((still, predicted), dim=2)
         if feature_layers:
-            return velocity, tuple(feature[0] for feature in features)
+            return velocity, tuple(group[0] for group in features)
         return velocity
 
     # --------------------------------------------------------- block autoregression
     def forward_ar(self, anchor: torch.Tensor, noisy: torch.Tensor, sigma: torch.Tensor,
                    condition: Cosmos3Condition, *, block_frames: int,
                    clean: torch.Tensor | None = None, history: HistoryWindow | None = None):
-        batch, _, frames, height, width = noisy.shape
+        batch, _, frames = noisy.shape[:3]
         if frames % block_frames:
             raise ValueError(f"{frames} target frames are not a multiple of {block_frames}")
-        patch = self.config.patch_size
-        grid = (height // patch, width // patch)
-        sigma = frame_sigma(sigma, batch, frames).to(noisy.device)
-        per_frame = self._tokens_per_frame(condition, grid)
-        chunks, positions, time_tokens = [], [], []
-
-        def add(latent, frame_sigma_, first, reference=False):
-            # Geometry is embedded per chunk, with the row count of the cached rollout.
-            count = latent.shape[2]
-            rgb = self.embed_rgb(latent, frame_sigma_, reference=reference,
-                                 condition=condition, start=first)
-            frame = self.geometry_frames(condition, start=first, stop=first + count, rgb_grid=grid)
-            token, position = frame.chunk(rgb, 0, count)
-            chunks.append(token)
-            positions.append(position)
-            time_tokens.append(self._time_tokens(frame_sigma_, batch, count, per_frame))
-
-        add(anchor, None, 0, reference=True)
-        for start in range(0, frames, block_frames):
-            stop = start + block_frames
-            add(noisy[:, :, start:stop], sigma[:, start:stop], start + 1)
+        grid = self._grid(noisy)
+        levels = frame_sigma(sigma, batch, frames).to(noisy.device)
+        # rows: C0, then per block the noisy frames and (teacher forcing) their clean version
+        table = _ChunkTable(self, condition, grid)
+        table.add(anchor, None, 0, reference=True)
+        for first in range(0, frames, block_frames):
+            block = slice(first, first + block_frames)
+            table.add(noisy[:, :, block], levels[:, block], first + 1)
             if clean is not None:
-                add(clean[:, :, start:stop], None, start + 1)
-        policy = BlockCausalAttention(self._text(condition.text),
-                                      teacher_forcing=clean is not None,
-                                      history=history or HistoryWindow())
-        adaln = self.config.timestep_conditioning == "adaln"
-        hidden, _ = self.run_layers(chunks, positions, policy,
-                                    time_embeddings=time_tokens if adaln else None)
-        stride = 1 if clean is None else 2
-        outputs = [self.decode_velocity(rgb_tokens(chunk, block_frames, grid), grid)
-                   for chunk in hidden[1::stride]]
-        return torch.cat(outputs, dim=2)
+                table.add(clean[:, :, block], None, first + 1)
+        policy = BlockCausalAttention(self._text(condition.text), teacher_forcing=clean is not None,
+                                      history=history if history is not None else HistoryWindow())
+        hidden, _ = table.run(policy)
+        queried = hidden[1::2] if clean is not None else hidden[1:]
+        return torch.cat([self.decode_velocity(rgb_tokens(chunk, block_frames, grid), grid)
+                          for chunk in queried], dim=2)
 
     # -------------------------------------------------------------------- KV cache
     def prefill(self, anchor: torch.Tensor, condition: Cosmos3Condition, *,
                 history: HistoryWindow | None = None) -> KVCache:
-        patch = self.config.patch_size
-        grid = (anchor.shape[-2] // patch, anchor.shape[-1] // patch)
-        frame = self.geometry_frames(condition, start=0, stop=1, rgb_grid=grid)
-        token, position = frame.chunk(
-            self.embed_rgb(anchor, None, reference=True, condition=condition), 0, 1)
+        grid = self._grid(anchor)
         text = self._text(condition.text)
+        table = _ChunkTable(self, condition, grid)
+        table.add(anchor, None, 0, reference=True)
         policy = AnchorAttention(text)
-        per_frame = self._tokens_per_frame(condition, grid)
-        time_tokens = self._time_tokens(None, anchor.shape[0], 1, per_frame)
-        self.run_layers([token], [position], policy,
-                        time_embeddings=None if time_tokens is None else [time_tokens])
-        return KVCache(text=text, anchor=tuple(policy.recorded),
-                       history=history or HistoryWindow(), condition=condition, grid=grid)
+        table.run(policy)
+        return KVCache(text=text, anchor=tuple(policy.recorded), condition=condition, grid=grid,
+                       history=history if history is not None else HistoryWindow())
 
     def denoise(self, cache: KVCache, noisy: torch.Tensor, sigma: torch.Tensor) -> torch.Tensor:
-        hidden = self._cached_chunk(cache, noisy, sigma, record=None)
+        hidden, _ = self._cached_chunk(cache, noisy, sigma, record=False)
         return self.decode_velocity(rgb_tokens(hidden, noisy.shape[2], cache.grid), cache.grid)
 
     def commit(self, cache: KVCache, clean: torch.Tensor,
                sigma: torch.Tensor | None = None) -> KVCache:
-        recorded: list[tuple[torch.Tensor, torch.Tensor]] = []
-        self._cached_chunk(cache, clean, sigma, record=recorded)
+        _, recorded = self._cached_chunk(cache, clean, sigma, record=True)
         return cache.committed(tuple(recorded), clean.shape[2])
 
-    def _cached_chunk(self, cache: KVCache, latent: torch.Tensor, sigma, *, record):
+    def _cached_chunk(self, cache: KVCache, latent: torch.Tensor, sigma, *, record: bool):
+        """The next block against the cache → (hidden states, recorded K/V per layer)."""
         batch, _, frames = latent.shape[:3]
-        start = 1 + cache.frames_committed
-        condition = cache.condition
-        frame = self.geometry_frames(condition, start=start, stop=start + frames,
-                                     rgb_grid=cache.grid)
-        per_frame_sigma = None if sigma is None else \
-            frame_sigma(sigma, batch, frames).to(latent.device)
-        rgb = self.embed_rgb(latent, per_frame_sigma, condition=condition, start=start)
-        token, position = frame.chunk(rgb, 0, frames)
-        policy = CachedAttention(cache, record=record is not None)
-        time_tokens = self._time_tokens(per_frame_sigma, batch, frames,
-                                        self._tokens_per_frame(condition, cache.grid))
-        (hidden,), _ = self.run_layers(
-            [token], [position], policy,
-            time_embeddings=None if time_tokens is None else [time_tokens])
-        if record is not None:
-            record.extend(policy.recorded)
-        return hidden
+        levels = None if sigma is None else frame_sigma(sigma, batch, frames).to(latent.device)
+        table = _ChunkTable(self, cache.condition, cache.grid)
+        table.add(latent, levels, 1 + cache.frames_committed)
+        policy = CachedAttention(cache, record=record)
+        (hidden,), _ = table.run(policy)
+        return hidden, (policy.recorded if record else ())
 
 
 def frame_sigma(sigma, batch: int, frames: int) -> torch.Tensor:
     """Broadcast a scalar, ``[B]`` or ``[B, T]`` sigma to per-frame ``[B, T]`` FP32."""
-    sigma = torch.as_tensor(sigma).float()
-    if sigma.ndim == 0:
-        sigma = sigma.expand(batch)
-    if sigma.ndim == 1:
-        sigma = sigma[:, None].expand(batch, frames)
-    if tuple(sigma.shape) != (batch, frames):
-        raise ValueError(f"sigma must be [B] or [B, {frames}], got {tuple(sigma.shape)}")
-    return sigma
+    levels = torch.as_tensor(sigma).float()
+    if levels.ndim <= 1:
+        levels = levels.reshape(-1, 1).expand(batch, frames)
+    if tuple(levels.shape) != (batch, frames):
+        raise ValueError(f"sigma must be [B] or [B, {frames}], got {tuple(levels.shape)}")
+    return levels
 
 
 def _grid_positions(temporal: torch.Tensor, grid: tuple[int, int],
                     rgb_grid: tuple[int, int]) -> torch.Tensor:
-    """``[B, F, h*w, 3]`` positions; rows/cols are pixel centres rescaled to the RGB grid."""
+    """``[B, F, h*w, 3]`` positions (time, row, column); rows and columns are the pixel centres
+    of ``grid`` expressed on ``rgb_grid``, so a coarser geometry grid overlays the RGB one."""
     batch, frames = temporal.shape
-    h, w = grid
-    device = temporal.device
-    rows = (torch.arange(h, device=device, dtype=torch.float32) + 0.5) * (rgb_grid[0] / h) - 0.5
-    cols = (torch.arange(w, device=device, dtype=torch.float32) + 0.5) * (rgb_grid[1] / w) - 0.5
-    out = torch.empty(batch, frames, h, w, 3, device=device, dtype=torch.float32)
-    out[..., 0] = temporal[:, :, None, None]
-    out[..., 1] = rows[None, None, :, None]
-    out[..., 2] = cols[None, None, None, :]
-    return out.reshape(batch, frames, h * w, 3)
+    rows, columns = grid
+
+    def centres(count: int, onto: int) -> torch.Tensor:
+        steps = torch.arange(count, device=temporal.device, dtype=torch.float32)
+        return (steps + 0.5) * (onto / count) - 0.5
+
+    shape = (batch, frames, rows, columns)
+    axes = (temporal.view(batch, frames, 1, 1).expand(shape),
+            centres(rows, rgb_grid[0]).view(1, 1, rows, 1).expand(shape),
+            centres(columns, rgb_grid[1]).view(1, 1, 1, columns).expand(shape))
+    return torch.stack(axes, dim=-1).reshape(batch, frames, rows * columns, 3)
