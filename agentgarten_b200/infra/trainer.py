@@ -317,84 +317,93 @@ class Trainer:
     # ------------------------------------------------------------------------ step
     def training_step(self, model_ddp: torch.nn.Module, grad_scaler: Any, data_batch: Batch, *,
                       iteration: int = 0, grad_accum_step: int = 0) -> TrainingStepResult:
-        if not 0 <= grad_accum_step < self.grad_accum_steps:
+        """One microbatch: run the objective's loss closures (forward + backward each); on the
+        last microbatch of an update also reduce, clip (callbacks), agree on finiteness, step
+        and clear.  The hooks fire in the order the callback interface documents."""
+        if grad_accum_step not in range(self.grad_accum_steps):
             raise ValueError(f"grad_accum_step must be in [0, {self.grad_accum_steps}), "
                              f"got {grad_accum_step}")
-        scaler = grad_scaler if grad_scaler is not None else _NoScaler()
+        scaler = _NoScaler() if grad_scaler is None else grad_scaler
         model = _root(model_ddp)
         bindings = model.get_optimizer_bindings(iteration)
-        optimizers = tuple(b.optimizer for b in bindings)
+        closes_update = grad_accum_step + 1 == self.grad_accum_steps
         self.callbacks.on_training_step_start(model, data_batch, iteration=iteration)
+        outputs, loss = self._backward_passes(model_ddp, model, scaler, data_batch, iteration, closes_update)
+        if not closes_update:
+            self.callbacks.on_training_step_batch_end(model, data_batch, outputs, loss, iteration=iteration)
+            return TrainingStepResult(outputs, loss, grad_accum_step + 1, did_update=False)
+        nonfinite = self._update(model_ddp, bindings, scaler, loss.device, iteration)
+        self.callbacks.on_training_step_batch_end(model, data_batch, outputs, loss, iteration=iteration)
+        if not nonfinite:
+            self.callbacks.on_training_step_end(model, data_batch, outputs, loss, iteration=iteration + 1)
+        return TrainingStepResult(outputs, loss, 0, did_update=not nonfinite, found_nonfinite=nonfinite)
 
-        final_microbatch = grad_accum_step == self.grad_accum_steps - 1
+    def _backward_passes(self, model_ddp, model: Model, scaler, data_batch: Batch, iteration: int,
+                         closes_update: bool) -> tuple[Batch, torch.Tensor]:
+        """Every closure of the objective, forward and backward; returns the merged step
+        outputs and the summed (detached) loss.  The objective must flag its last closure, and
+        only that one: gradient synchronisation is switched on for exactly that backward."""
         outputs: Batch = {}
-        total: torch.Tensor | None = None
-        finished, count = False, 0
-        for _name, closure, is_last in model.training_step_closures(data_batch, iteration):
-            if finished:
-                raise RuntimeError("training_step_closures() yielded a closure after "
-                                   "is_last=True; the final marker must be on the last closure")
-            if not isinstance(is_last, bool):
-                raise TypeError("training_step_closures() is_last must be a bool, got "
+        losses: list[torch.Tensor] = []
+        saw_last = False
+        for _role, closure, is_last in model.training_step_closures(data_batch, iteration):
+            if saw_last:
+                raise RuntimeError("training_step_closures() produced another closure behind the one "
+                                   "it flagged with is_last=True")
+            if type(is_last) is not bool:
+                raise TypeError("training_step_closures() must yield a bool as is_last, not "
                                 f"{type(is_last).__name__}")
-            count += 1
-            finished = is_last
-            # The last backward pass of an update lets the sharded optimizer engines reduce each
-            # layer's gradients over the peers as soon as that layer's backward has finished.
-            zero.arm_overlap(final_microbatch and is_last)
-            with ddp_sync_grad(model_ddp, final_microbatch and is_last):
+            saw_last = is_last
+            final_backward = closes_update and is_last
+            # from its last backward pass on, the sharded optimizer engines may reduce a layer's
+            # gradients over the peers as soon as that layer's backward has finished
+            zero.arm_overlap(final_backward)
+            with ddp_sync_grad(model_ddp, final_backward):
                 with span("forward"):
-                    if isinstance(model_ddp, DistributedDataParallel):
-                        out, loss = model_ddp.forward_closure(closure)
-                    else:
-                        out, loss = closure()
-                outputs.update(out)
+                    through_reducer = isinstance(model_ddp, DistributedDataParallel)
+                    report, loss = model_ddp.forward_closure(closure) if through_reducer else closure()
+                outputs.update(report)
                 with span("backward"):
                     scaler.scale(loss / self.grad_accum_steps).backward()
-            total = loss.detach() if total is None else total + loss.detach()
-        if count == 0 or total is None:
-            raise RuntimeError("training_step_closures() yielded no closures")
-        if not finished:
-            raise RuntimeError("training_step_closures() must mark exactly its final closure "
-                               "with is_last=True")
+            losses.append(loss.detach())
+        if not losses:
+            raise RuntimeError("training_step_closures() produced no closure at all")
+        if not saw_last:
+            raise RuntimeError("training_step_closures() never flagged a closure with is_last=True")
+        total = losses[0]
+        for more in losses[1:]:
+            total = total + more
+        return outputs, total
 
-        if grad_accum_step + 1 < self.grad_accum_steps:
-            self.callbacks.on_training_step_batch_end(model, data_batch, outputs, total,
-                                                      iteration=iteration)
-            return TrainingStepResult(outputs, total, grad_accum_step + 1, False)
-
+    def _update(self, model_ddp, bindings, scaler, device, iteration: int) -> bool:
+        """Reduce, let callbacks clip, agree across ranks on finiteness, then step every active
+        role or skip all of them; clear gradients either way.  Returns True when skipped."""
+        hooks = self.callbacks
+        optimizers = tuple(binding.optimizer for binding in bindings)
         for optimizer in optimizers:
             scaler.unscale_(optimizer)
-            reduce = getattr(optimizer, "reduce_gradients", None)
-            if callable(reduce):
-                reduce()  # data-parallel mean; a no-op when already done or single rank
-        for b in bindings:
-            self.callbacks.on_before_optimizer_step(model_ddp, b.optimizer, b.scheduler, scaler,
-                                                    iteration=iteration)
-        found = synchronize_found_nonfinite(scaler, optimizers, fallback_device=total.device)
-        if not found:
-            for b in bindings:
-                with span(f"optimizer {b.name}"):
-                    scaler.step(b.optimizer)
-                b.scheduler.step()
-                self.callbacks.on_after_optimizer_step(model_ddp, b.name, b.optimizer, b.scheduler,
-                                                       iteration=iteration)
-        else:
-            self.callbacks.on_optimizer_step_skipped(model_ddp, tuple(b.name for b in bindings),
-                                                     iteration=iteration)
-        for b in bindings:
-            self.callbacks.on_before_zero_grad(model_ddp, b.optimizer, b.scheduler,
-                                               iteration=iteration)
-            b.optimizer.zero_grad(set_to_none=True)
-            if hasattr(b.optimizer, "grad_scale"):
-                b.optimizer.grad_scale = 1.0
-        scaler.update()  # shared by all active optimizers: exactly once
-        self.callbacks.on_training_step_batch_end(model, data_batch, outputs, total,
-                                                  iteration=iteration)
-        if not found:
-            self.callbacks.on_training_step_end(model, data_batch, outputs, total,
-                                                iteration=iteration + 1)
-        return TrainingStepResult(outputs, total, 0, not found, found)
+            if callable(getattr(optimizer, "reduce_gradients", None)):
+                optimizer.reduce_gradients()  # data-parallel mean (idempotent per update)
+        for binding in bindings:
+            hooks.on_before_optimizer_step(model_ddp, binding.optimizer, binding.scheduler, scaler,
+                                           iteration=iteration)
+        nonfinite = synchronize_found_nonfinite(scaler, optimizers, fallback_device=device)
+        if nonfinite:
+            hooks.on_optimizer_step_skipped(model_ddp, tuple(binding.name for binding in bindings),
+                                            iteration=iteration)
+        for binding in bindings if not nonfinite else ():
+            with span(f"optimizer {binding.name}"):
+                scaler.step(binding.optimizer)
+            binding.scheduler.step()
+            hooks.on_after_optimizer_step(model_ddp, binding.name, binding.optimizer, binding.scheduler,
+                                          iteration=iteration)
+        for binding in bindings:
+            hooks.on_before_zero_grad(model_ddp, binding.optimizer, binding.scheduler, iteration=iteration)
+            binding.optimizer.zero_grad(set_to_none=True)
+            if hasattr(binding.optimizer, "grad_scale"):
+                binding.optimizer.grad_scale = 1.0   # the clip coefficient applies to one update
+        scaler.update()  # one scaler serves all roles: exactly once per update
+        return nonfinite
 
     # -------------------------------------------------------------------- validate
     @torch.no_grad()
