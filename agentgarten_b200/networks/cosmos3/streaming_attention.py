@@ -39,37 +39,41 @@ class StreamAttentionCache:
         self._swapped = False  # True while the second arena is the live one
 
     # ------------------------------------------------------------------------ views
-    def _visual(self, store: torch.Tensor) -> torch.Tensor:
-        lo = self.text_tokens
-        return store[:, lo: lo + self.frames * self.frame_tokens]
+    def _row_of_frame(self, frame: int) -> int:
+        """Arena row at which visual frame ``frame`` starts (the text rows come first)."""
+        return self.text_tokens + frame * self.frame_tokens
 
     @property
     def visual_key(self) -> torch.Tensor:
-        return self._visual(self.key)
+        return self.key[:, self.text_tokens: self._row_of_frame(self.frames)]
 
     @property
     def visual_value(self) -> torch.Tensor:
-        return self._visual(self.value)
+        return self.value[:, self.text_tokens: self._row_of_frame(self.frames)]
+
+    def _write(self, first_row: int, key: torch.Tensor, value: torch.Tensor) -> int:
+        """Copy a chunk's K/V into both arenas from ``first_row`` on; returns the row behind it."""
+        behind = first_row + key.shape[1]
+        self.key[:, first_row:behind].copy_(key)
+        self.value[:, first_row:behind].copy_(value)
+        return behind
 
     # ------------------------------------------------------------------------- use
     def attend(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -> torch.Tensor:
-        """Attention of an uncommitted chunk over text, committed history and itself."""
-        start = self.text_tokens + self.frames * self.frame_tokens
-        stop = start + key.shape[1]
-        self.key[:, start:stop].copy_(key)
-        self.value[:, start:stop].copy_(value)
-        return ops.attention(query, self.key[:, :stop], self.value[:, :stop], None)
+        """Attention of an uncommitted chunk over text, committed history and itself.  The chunk
+        is parked behind the history; ``frames`` is untouched, so nothing is committed."""
+        behind = self._write(self._row_of_frame(self.frames), key, value)
+        return ops.attention(query, self.key[:, :behind], self.value[:, :behind], None)
 
     def append(self, key: torch.Tensor, value: torch.Tensor) -> None:
-        start = self.text_tokens + self.frames * self.frame_tokens
-        self.key[:, start: start + key.shape[1]].copy_(key)
-        self.value[:, start: start + value.shape[1]].copy_(value)
+        """Commit a chunk: its K/V become history."""
+        self._write(self._row_of_frame(self.frames), key, value)
         self.frames += key.shape[1] // self.frame_tokens
 
     def replace_visual(self, key: torch.Tensor, value: torch.Tensor) -> None:
-        self.frames = key.shape[1] // self.frame_tokens
-        self.visual_key.copy_(key)
-        self.visual_value.copy_(value)
+        """The whole history is replaced (eviction without re-rotation, or a rebuilt cache)."""
+        self.frames = 0
+        self.append(key, value)
 
     def relocate(self, sink_frames: int, evicted_frames: int,
                  rotation: tuple[torch.Tensor, torch.Tensor]) -> None:
