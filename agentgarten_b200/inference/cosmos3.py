@@ -96,149 +96,172 @@ class Cosmos3Artifact:
 
 def prompt_pixel_frames(config: Mapping[str, Any]) -> int:
     """The caption horizon (pixel frames) the run was trained with: ``1 + 4N``."""
-    count = config["dataloader_val"]["dataset"]["num_frames"]
-    if type(count) is not int or count <= 1 or (count - 1) % 4:
-        raise ValueError(f"caption horizon must be 1 + 4N pixel frames, got {count!r}")
-    return count
+    horizon = config["dataloader_val"]["dataset"]["num_frames"]
+    valid = type(horizon) is int and horizon > 1 and horizon % 4 == 1
+    if not valid:
+        raise ValueError(f"caption horizon must be 1 + 4N pixel frames, got {horizon!r}")
+    return horizon
 
 
-def _absolute(path: str, root: Path) -> Path:
-    location = Path(path).expanduser()
-    return (location if location.is_absolute() else root / location).resolve()
+class _Run:
+    """What a run's resolved ``config.yaml`` (a plain YAML tree, nothing is instantiated) says
+    about the served towers.  Relative paths in it are relative to ``base``."""
+
+    def __init__(self, tree: Mapping[str, Any], base: Path) -> None:
+        self.tree, self.base = tree, base
+        model = tree["model"]
+        self.role = "student" if "student" in model else "net"   # distilled runs serve the student
+        self.node = model[self.role]
+        shape = self.node["config"]
+        if not isinstance(shape, Mapping):
+            raise ValueError(f"unresolved network config: {shape!r}")
+        accepted = {field.name for field in fields(Cosmos3Config)}
+        self.config = Cosmos3Config(**{key: shape[key] for key in shape if key in accepted})
+
+    def path(self, text: str) -> Path:
+        location = Path(text).expanduser()
+        return (location if location.is_absolute() else self.base / location).resolve()
+
+    @property
+    def tokenizer(self) -> Path:
+        return self.path(self.tree["model"]["conditioner"]["tokenizer_path"])
+
+    def initial_weights(self) -> tuple[list[WeightSource], list[WeightSource]]:
+        """The run's ``train.model_initializations`` sorted into (served tower, text tower)."""
+        served: list[WeightSource] = []
+        text: list[WeightSource] = []
+        for overlay in (self.tree["train"].get("model_initializations") or {}).values():
+            if overlay.get("path") is None:
+                continue
+            source = WeightSource(
+                self.path(overlay["path"]),
+                (overlay.get("source_model_key_prefix") or "").removeprefix("model."),
+                tuple(overlay.get("source_model_key_patterns") or ()))
+            targets = overlay.get("model_key_prefixes") or (overlay.get("model_key_prefix"),)
+            if self.role in targets:
+                served.append(source)
+            if _TEXT_PREFIX in targets:
+                text.append(source)
+        return served, text
+
+    def spec(self, checkpoint: Path, served, text, iteration: int) -> Cosmos3ArtifactSpec:
+        return Cosmos3ArtifactSpec(checkpoint=checkpoint, config=self.config, student=tuple(served),
+                                   text=tuple(text), tokenizer_path=self.tokenizer,
+                                   prompt_pixel_frames=prompt_pixel_frames(self.tree),
+                                   iteration=iteration, lora=self.node.get("lora"))
 
 
-def _tower(config: Mapping[str, Any]) -> tuple[str, Mapping[str, Any], Cosmos3Config]:
-    """Which model entry owns the served weights (``student`` when distilled, else ``net``)."""
-    model = config["model"]
-    role = "student" if "student" in model else "net"
-    node = model[role]
-    raw = node["config"]
-    if not isinstance(raw, Mapping):
-        raise ValueError(f"unresolved network config: {raw!r}")
-    known = {f.name for f in fields(Cosmos3Config)}
-    return role, node, Cosmos3Config(**{k: v for k, v in raw.items() if k in known})
+def _config_beside(checkpoint: Path) -> Path:
+    """``config.yaml`` of the run: in the checkpoint, in the job directory two levels up
+    (``job/checkpoints/iter_N``), or next to the checkpoint."""
+    for folder in (checkpoint, checkpoint.parent.parent, checkpoint.parent):
+        if (folder / "config.yaml").is_file():
+            return folder / "config.yaml"
+    raise FileNotFoundError(f"no resolved config.yaml beside {checkpoint}")
 
 
 def inspect_artifact(checkpoint: str | Path) -> Cosmos3ArtifactSpec:
     checkpoint = Path(checkpoint).expanduser().resolve()
-    holder = checkpoint.parent if checkpoint.is_file() else checkpoint
-    if (holder / "manifest.json").is_file():
-        return _inspect_export(holder)
+    folder = checkpoint.parent if checkpoint.is_file() else checkpoint
+    if (folder / "manifest.json").is_file():
+        return _inspect_export(folder)
     if not (checkpoint / "tensor" / ".metadata").is_file():
         raise FileNotFoundError(f"expected a DCP checkpoint with tensor/.metadata: {checkpoint}")
-    places = (checkpoint / "config.yaml", checkpoint.parent.parent / "config.yaml",
-              checkpoint.parent / "config.yaml")
-    config_path = next((p for p in places if p.is_file()), None)
-    if config_path is None:
-        raise FileNotFoundError(f"no resolved config.yaml beside {checkpoint}")
-    config = yaml.safe_load(config_path.read_text())
-    role, node, topology = _tower(config)
-
-    student: list[WeightSource] = []
-    text: list[WeightSource] = []
-    for entry in (config["train"].get("model_initializations") or {}).values():
-        if entry.get("path") is None:
-            continue
-        destinations = entry.get("model_key_prefixes") or (entry.get("model_key_prefix"),)
-        source = WeightSource(_absolute(entry["path"], config_path.parent),
-                              (entry.get("source_model_key_prefix") or "").removeprefix("model."),
-                              tuple(entry.get("source_model_key_patterns") or ()))
-        if role in destinations:
-            student.append(source)
-        if _TEXT_PREFIX in destinations:
-            text.append(source)
+    config_path = _config_beside(checkpoint)
+    run = _Run(yaml.safe_load(config_path.read_text()), config_path.parent)
+    served, text = run.initial_weights()
     from torch.distributed.checkpoint import FileSystemReader
 
-    saved = FileSystemReader(str(checkpoint / "tensor")).read_metadata().state_dict_metadata
-    if f"model.{_TEXT_PREFIX}.embed_tokens.weight" in saved:
+    stored = FileSystemReader(str(checkpoint / "tensor")).read_metadata().state_dict_metadata
+    if f"model.{_TEXT_PREFIX}.embed_tokens.weight" in stored:   # the run saved its text tower too
         text.append(WeightSource(checkpoint, _TEXT_PREFIX))
     if not text:
         raise ValueError("checkpoint does not identify its frozen UND weight source")
-    student.append(WeightSource(checkpoint, role))  # the checkpoint overlays what it owns
-    numbered = re.fullmatch(r"iter_(\d+)", checkpoint.name)
-    return Cosmos3ArtifactSpec(
-        checkpoint=checkpoint, config=topology, student=tuple(student), text=tuple(text),
-        tokenizer_path=_absolute(config["model"]["conditioner"]["tokenizer_path"], config_path.parent),
-        prompt_pixel_frames=prompt_pixel_frames(config),
-        iteration=int(numbered[1]) if numbered else 0, lora=node.get("lora"))
+    served.append(WeightSource(checkpoint, run.role))  # last: the checkpoint overlays what it owns
+    number = re.fullmatch(r"iter_(\d+)", checkpoint.name)
+    return run.spec(checkpoint, served, text, int(number.group(1)) if number else 0)
 
 
 def _inspect_export(root: Path) -> Cosmos3ArtifactSpec:
     manifest = json.loads((root / "manifest.json").read_text())
-    if manifest.get("schema") != MANIFEST_SCHEMA or manifest.get("version") != MANIFEST_VERSION:
+    if (manifest.get("schema"), manifest.get("version")) != (MANIFEST_SCHEMA, MANIFEST_VERSION):
         raise ValueError("unsupported serving manifest schema/version")
 
-    def inside(name: str) -> Path:
-        path = (root / name).resolve()
-        if not path.is_relative_to(root) or not path.is_file():
-            raise ValueError(f"serving manifest must name an existing local file: {name!r}")
-        return path
+    def local_file(name: str) -> Path:
+        candidate = (root / name).resolve()
+        if candidate.is_file() and candidate.is_relative_to(root):
+            return candidate
+        raise ValueError(f"serving manifest must name an existing local file: {name!r}")
 
-    config = yaml.safe_load(inside(manifest.get("config", "config.yaml")).read_text())
-    _, node, topology = _tower(config)
+    run = _Run(yaml.safe_load(local_file(manifest.get("config", "config.yaml")).read_text()), root)
     iteration = manifest["iteration"]
     if type(iteration) is not int or iteration < 0:
         raise ValueError("manifest iteration must be a nonnegative integer")
-    # exported tensors carry module-local names: no prefix
-    student, text = (WeightSource(inside(manifest[role]["file"]), "") for role in ("student", "und"))
-    return Cosmos3ArtifactSpec(
-        checkpoint=root, config=topology, student=(student,), text=(text,),
-        tokenizer_path=_absolute(config["model"]["conditioner"]["tokenizer_path"], root),
-        prompt_pixel_frames=prompt_pixel_frames(config), iteration=iteration, lora=node.get("lora"))
+    # exported tensors carry module-local names, hence the empty prefixes
+    towers = {role: (WeightSource(local_file(manifest[role]["file"]), ""),) for role in ("student", "und")}
+    return run.spec(root, towers["student"], towers["und"], iteration)
 
 
-def _reject_undeclared_lora(keys: Iterable[str]) -> None:
-    stray = sorted(k for k in keys if ".lora_" in k)
+def _refuse_stray_lora(names: Iterable[str]) -> None:
+    """Adapter tensors that no ``lora`` declaration accounts for would be dropped silently."""
+    stray = sorted(name for name in names if ".lora_" in name)
     if stray:
         raise ValueError(f"checkpoint has undeclared LoRA weights: {stray[:4]}")
 
 
-def _load_tensor_file(module: nn.Module, source: WeightSource) -> set[str]:
-    prefix = source.prefix.rstrip(".") + "." if source.prefix else ""
-    parameters = dict(module.named_parameters())
-    _, entries, _ = tensor_file.read_header(source.path)
-    chosen = {name: prefix + name for name in parameters if prefix + name in entries}
-    _reject_undeclared_lora(k for k in entries.keys() - set(chosen.values()) if k.startswith(prefix))
-    with torch.no_grad():
-        return tensor_file.copy_into(source.path, {n: parameters[n] for n in chosen}, chosen)
+class _TowerLoader:
+    """Fills one materialised tower from its overlays, in order, and checks full coverage."""
 
+    def __init__(self, tower: nn.Module, sources: tuple[WeightSource, ...]) -> None:
+        self.tower, self.sources = tower, sources
+        self.filled: set[str] = set()
 
-def _load_tower(module: nn.Module, sources: tuple[WeightSource, ...]) -> None:
-    from agentgarten_b200.infra.checkpoint import DistributedCheckpointer
+    def _from_tensor_file(self, source: WeightSource) -> None:
+        lead = source.prefix.rstrip(".") + "." if source.prefix else ""
+        live = dict(self.tower.named_parameters())
+        _, stored, _ = tensor_file.read_header(source.path)
+        wanted = {name: lead + name for name in live if lead + name in stored}
+        unused = stored.keys() - set(wanted.values())
+        _refuse_stray_lora(name for name in unused if name.startswith(lead))
+        with torch.no_grad():
+            self.filled |= tensor_file.copy_into(source.path, {name: live[name] for name in wanted}, wanted)
 
-    restorer = DistributedCheckpointer(sources[-1].path.parent)
-    covered: set[str] = set()
-    for source in sources:
-        if source.path.suffix == ".safetensors":
-            covered |= _load_tensor_file(module, source)
-            continue
-        result = restorer.load(module, path=source.path, components=("model",),
-                               source_model_key_prefix=source.prefix, model_key_prefix="",
-                               source_model_key_patterns=source.patterns)
-        _reject_undeclared_lora(result.unexpected_model_keys)
-        covered |= set(result.loaded_model_keys)
-    absent = set(module.state_dict()) - covered
-    if absent:
-        raise ValueError(f"inference weights are incomplete: {sorted(absent)[:12]}")
+    def _from_checkpoint(self, source: WeightSource) -> None:
+        from agentgarten_b200.infra.checkpoint import DistributedCheckpointer
+
+        outcome = DistributedCheckpointer(source.path.parent).load(
+            self.tower, path=source.path, components=("model",), model_key_prefix="",
+            source_model_key_prefix=source.prefix, source_model_key_patterns=source.patterns)
+        _refuse_stray_lora(outcome.unexpected_model_keys)
+        self.filled |= set(outcome.loaded_model_keys)
+
+    def run(self) -> None:
+        for source in self.sources:
+            if source.path.suffix == ".safetensors":
+                self._from_tensor_file(source)
+            else:
+                self._from_checkpoint(source)
+        missing = sorted(set(self.tower.state_dict()) - self.filled)
+        if missing:
+            raise ValueError(f"inference weights are incomplete: {missing[:12]}")
 
 
 def load_artifact(spec: Cosmos3ArtifactSpec, *, device: str | torch.device = "cuda",
                   dtype: torch.dtype = torch.bfloat16,
                   progress: Callable[[str, int, int], None] | None = None) -> Cosmos3Artifact:
     """Materialise the student and the text tower (with declared LoRA) and nothing else."""
-    student = build_network(spec.config, init_device="meta", lora=dict(spec.lora) if spec.lora else None)
+    report = progress if progress is not None else (lambda *_: None)
+    served = build_network(spec.config, init_device="meta", lora=dict(spec.lora) if spec.lora else None)
     with torch.device("meta"):
         text = Cosmos3TextEncoder(spec.config)
-    for label, tower, sources in (("und", text, spec.text), ("student", student, spec.student)):
-        if progress is not None:
-            progress(label, 0, 0)
+    for label, tower, sources in (("und", text, spec.text), ("student", served, spec.student)):
+        report(label, 0, 0)
         tower.to(dtype=dtype).to_empty(device=device)
-        _load_tower(tower, sources)
+        _TowerLoader(tower, sources).run()
         tower.eval().requires_grad_(False)
-        if progress is not None:
-            count = len(tower.state_dict())
-            progress(label, count, count)
-    return Cosmos3Artifact(student, text, spec)
+        total = len(tower.state_dict())
+        report(label, total, total)
+    return Cosmos3Artifact(served, text, spec)
 
 
 def _plain(value: Any) -> Any:

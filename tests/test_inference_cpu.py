@@ -117,9 +117,9 @@ def test_artifact_from_a_training_run_and_from_its_export(tmp_path):
 
 
 def test_undeclared_lora_tensors_are_refused(tmp_path):
-    from agentgarten_b200.inference.cosmos3 import WeightSource, _load_tensor_file
+    from agentgarten_b200.inference.cosmos3 import WeightSource, _TowerLoader
     module = torch.nn.Linear(4, 4, bias=False)
     tensor_file.write_tensors({"weight": torch.zeros(4, 4), "weight.lora_A": torch.zeros(2, 4)},
                               tmp_path / "w.safetensors")
     with pytest.raises(ValueError, match="undeclared LoRA"):
-        _load_tensor_file(module, WeightSource(pathlib.Path(tmp_path / "w.safetensors"), ""))
+        _TowerLoader(module, (WeightSource(pathlib.Path(tmp_path / "w.safetensors"), ""),)).run()
