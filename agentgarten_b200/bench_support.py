@@ -23,7 +23,7 @@ from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
 from agentgarten_b200.parallel import zero
 from agentgarten_b200.parallel.engine import ParallelConfig
 
-__all__ = ["TrainingJob", "build_training_job", "random_init_", "synthetic_batch"]
+__all__ = ["TrainingJob", "build_training_job", "random_init_", "stream_benchmark", "synthetic_batch"]
 
 
 @torch.no_grad()
@@ -152,3 +152,101 @@ def synthetic_batch(job: TrainingJob, device: torch.device | str = "cpu", seed: 
 
 def batch_bytes(batch: dict[str, Any]) -> int:
     return sum(v.numel() * v.element_size() for v in batch.values() if isinstance(v, torch.Tensor))
+
+
+def stream_benchmark(device: torch.device, *, blocks: int = 32, layers: int = 36, graphs: bool = True,
+                     tensor_parallel: bool = False, trace: bool = False) -> dict[str, Any]:
+    """Cosmos3Stream on synthetic inputs: batch 1, anchor ``[1, 48, 1, 30, 52]``, ``blocks`` blocks
+    of 4 latent frames, each 4 denoise steps at sigma (1.0, 0.75, 0.5, 0.25) and a commit into a
+    cache of 6 blocks plus the anchor.  With an initialised process group of more than one rank
+    (or ``tensor_parallel``) the tower is sharded over the ranks, which must all call this with
+    the same arguments.  Every cache fill level's CUDA graph is captured before the first timed
+    block; ALL blocks count.  Returns per-block device times (max over ranks) and their
+    p50 / p99."""
+    import statistics
+
+    import torch.distributed as dist
+
+    from agentgarten_b200.inference.serving import prepare_serving, release_serving
+    from agentgarten_b200.models.flow import rf_interpolate, rf_x0
+    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
+    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+    from agentgarten_b200.ops import native
+
+    world = dist.get_world_size() if dist.is_available() and dist.is_initialized() else 1
+    config = Cosmos3Config(num_hidden_layers=layers)
+    net = build_network(config, init_device="meta").to(torch.bfloat16).to_empty(device=device)
+    random_init_(net, seed=0)
+    cond = Cosmos3Conditioner(config=config, codec=None, init_device="meta", geometry_noise_sigma=0.0)
+    cond.to(torch.bfloat16).to_empty(device=device)
+    random_init_(cond.text_encoder, seed=1)
+    sharded = world > 1 or tensor_parallel
+    graphs = graphs and not trace
+    prepare_serving(net, cuda_graphs=graphs, tensor_parallel=True if sharded else None, max_tokens=4096)
+    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=24, rope="top_aligned",
+                          train_frames=61)
+    g = torch.Generator(device=device).manual_seed(0)
+    shape = (1, 48, 4, 30, 52)
+    ids = torch.randint(1000, 150000, (1, 512), device=device, generator=g)
+    with torch.inference_mode():
+        text = cond.text_encoder(ids, None)
+    del cond
+
+    def condition(frames):
+        s = (1, 48, frames, 30, 52)
+        return Cosmos3Condition(text=text, depth=torch.randn(s, device=device, generator=g),
+                                normal=torch.randn(s, device=device, generator=g),
+                                fps=torch.full((1,), 16.0, device=device))
+
+    endpoints = (1.0, 0.75, 0.5, 0.25)
+    stream = Cosmos3Stream(net, policy)
+    anchor = torch.randn((1, 48, 1, 30, 52), device=device, generator=g)
+    stream.capture_graphs(anchor, condition(1), condition(4))   # before the timed blocks
+    stream.start(anchor, condition(1))
+    times: list[float] = []
+    launches_before = native.launches()
+    for block in range(blocks):
+        if trace and sharded and block == blocks - 2:
+            net._tensor_parallel.trace = {}
+        cond_block = condition(4)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        clean = None
+        for sigma in endpoints:
+            level = torch.full((1,), sigma, device=device)
+            noise = torch.randn(shape, device=device, generator=g)
+            current = noise if clean is None else rf_interpolate(clean, noise, level)
+            clean = rf_x0(current, level, stream.denoise(current, level, cond_block))
+        stream.commit(clean, cond_block)
+        stop.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(stop))
+        # a bounded wait that ran out on any rank ends the run on all of them (outside the timing)
+        failed = native.ext().status(device.index).clone()
+        if world > 1:
+            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
+        if int(failed.item()) != 0:
+            break
+    status = int(native.ext().status(device.index).item())
+    if world > 1:
+        gathered = torch.tensor(times + [float(status)], device=device)  # same length on every rank
+        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+        times, status = gathered[:-1].tolist(), int(gathered[-1].item())
+    phases = net._tensor_parallel.trace_summary() if trace and sharded else None
+    launches = native.launches() - launches_before
+    release_serving(net)
+    ordered = sorted(times)
+    return {
+        "metric": "Cosmos3Stream ms per 4-frame block (4 denoise + 1 commit)",
+        "p50_ms": statistics.median(times),
+        "p99_ms": ordered[min(len(ordered) - 1, int(0.99 * len(ordered)))],
+        "mean_ms": statistics.fmean(times),
+        "first_blocks_ms": times[:8], "blocks": blocks, "n_gpus": world, "dtype": "bf16",
+        "parallelism": f"tp{world} (heads and MLP columns; GEMM+reduce-scatter / all-gather+GEMM over peer memory)"
+        if sharded else "single GPU",
+        "cuda_graphs": graphs, "layers": layers,
+        "cache": "anchor + 6 blocks (sink 1, history 24 frames), top-aligned RoPE",
+        "tokens_per_block": 4 * 2 * 390, "gpu_launches": launches, "kernel_status": status,
+        "timed": "all blocks; every fill-level graph captured beforehand",
+        **({"phase_ms": phases} if phases is not None else {}),
+    }

@@ -30,13 +30,17 @@ class _RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(int(dim)))
 
     def forward(self, value: Tensor) -> Tensor:
-        wide = value.to(torch.promote_types(value.dtype, torch.float32))
-        wide = wide * torch.rsqrt(wide.square().mean(-1, keepdim=True) + self.eps)
-        return wide.to(value) * self.weight
+        # statistics in at least FP32 (and never a downcast of FP64 inputs)
+        working = value.to(torch.promote_types(value.dtype, torch.float32))
+        scale = torch.rsqrt(working.pow(2).mean(dim=-1, keepdim=True) + self.eps)
+        return (working * scale).to(value) * self.weight
 
 
 class _QueryPool(nn.Module):
-    """One learned query attends over the feature tokens of a layer."""
+    """A learned query attends over the tokens of one tapped layer and returns one vector per
+    sample.  The attention is spelled out with matrix products and a softmax: one query per
+    sample is cheap, and unlike fused attention kernels this supports the double backward that
+    exact R1/R2 takes through the head."""
 
     def __init__(self, hidden: int, heads: int) -> None:
         super().__init__()
@@ -52,30 +56,34 @@ class _QueryPool(nn.Module):
         self.post_norm_k = _RMSNorm(hidden)
         self.to_out = nn.Linear(hidden, hidden)
 
+    def _per_head(self, rows: Tensor) -> Tensor:
+        """[B, N, hidden] → [B, heads, N, head_dim]"""
+        return rows.unflatten(-1, (self.num_heads, self.head_dim)).transpose(1, 2)
+
     def forward(self, features: Tensor) -> Tensor:
-        # work in the head's dtype: the paired and penalty terms live on small differences
-        features = features.to(self.to_k.weight.dtype)
-        b, n = features.shape[:2]
-        start = self.query_token[:, 0].expand(b, -1, -1)
-        q = self.post_norm_q(self.to_q(start)).view(b, 1, self.num_heads, -1)
-        normed = self.pre_norm_kv(features)
-        k = self.post_norm_k(self.to_k(normed)).view(b, n, self.num_heads, -1)
-        v = self.to_v(normed).view(b, n, self.num_heads, -1)
-        weights = (torch.einsum("bqhd,bkhd->bhqk", q, k) * self.head_dim ** -0.5).softmax(-1)
-        pooled = torch.einsum("bhqk,bkhd->bhqd", weights, v).transpose(1, 2).reshape(b, 1, -1)
-        return (self.to_out(pooled) + start)[:, 0]
+        # in the head's own precision: the paired and penalty terms live on small differences
+        tokens = self.pre_norm_kv(features.to(self.to_k.weight.dtype))
+        seed = self.query_token[:, 0].expand(tokens.shape[0], -1, -1)            # [B, 1, hidden]
+        query = self._per_head(self.post_norm_q(self.to_q(seed)))
+        key = self._per_head(self.post_norm_k(self.to_k(tokens)))
+        value = self._per_head(self.to_v(tokens))
+        weights = torch.softmax(query @ key.transpose(-1, -2) * self.head_dim ** -0.5, dim=-1)
+        pooled = (weights @ value).transpose(1, 2).flatten(-2)                   # [B, 1, hidden]
+        return (self.to_out(pooled) + seed).squeeze(1)
 
 
 class _MLP(nn.Module):
     def __init__(self, hidden: int, ratio: float) -> None:
         super().__init__()
+        inner = int(hidden * ratio)
         self.norm = _RMSNorm(hidden)
-        self.fc1 = nn.Linear(hidden, int(hidden * ratio))
+        self.fc1 = nn.Linear(hidden, inner)
         self.activation = nn.GELU()
-        self.fc2 = nn.Linear(int(hidden * ratio), hidden)
+        self.fc2 = nn.Linear(inner, hidden)
 
     def forward(self, value: Tensor) -> Tensor:
-        return value + self.fc2(self.activation(self.fc1(self.norm(value))))
+        update = self.fc2(self.activation(self.fc1(self.norm(value))))
+        return value + update
 
 
 class _Branch(nn.Module):
@@ -93,41 +101,49 @@ class DiscriminatorHead(nn.Module):
                  mlp_ratio: float = 4.0, num_heads: int = 32, initial_logit_sign: float = 1.0,
                  seed: int = 0xD2D20000, init_device: str = "cpu") -> None:
         super().__init__()
-        self.feature_layers = tuple(sorted(int(i) for i in feature_layers))
-        if not self.feature_layers or len(set(self.feature_layers)) != len(self.feature_layers):
+        taps = sorted(int(index) for index in feature_layers)
+        if not taps or len(taps) != len(set(taps)):
             raise ValueError(f"feature_layers must be unique and non-empty: {feature_layers}")
         if initial_logit_sign not in (-1.0, 1.0):
             raise ValueError("initial_logit_sign must be -1 or 1")
+        self.feature_layers = tuple(taps)
         self.initial_logit_sign = float(initial_logit_sign)
         self.seed = int(seed)
+        joined = hidden_size * len(taps)
         with torch.device(init_device):
-            self.branches = nn.ModuleList(_Branch(hidden_size, mlp_ratio, num_heads)
-                                          for _ in self.feature_layers)
-            width = hidden_size * len(self.feature_layers)
-            self.final_norm = nn.LayerNorm(width, eps=1e-6)
-            self.final_linear = nn.Linear(width, 1)
-        if not any(p.is_meta for p in self.parameters()):
+            self.branches = nn.ModuleList(_Branch(hidden_size, mlp_ratio, num_heads) for _ in taps)
+            self.final_norm = nn.LayerNorm(joined, eps=1e-6)
+            self.final_linear = nn.Linear(joined, 1)
+        if all(not parameter.is_meta for parameter in self.parameters()):
             self.reset_parameters()
 
     @torch.no_grad()
     def reset_parameters(self, shard_index: int = 0) -> None:
-        """Xavier-uniform linears, unit norms, N(0, 0.02) query tokens — from one seeded
-        generator walked in module order."""
-        generator = torch.Generator(device=self.final_linear.weight.device)
-        generator.manual_seed(self.seed + int(shard_index))
+        """Seeded and independent of the memory layout, so that every rank builds the same head:
+        modules are visited in registration order and draw from one generator — Xavier-uniform
+        matrices (zero biases), N(0, 0.02) query tokens; norms start at one."""
+        draws = torch.Generator(device=self.final_linear.weight.device)
+        draws.manual_seed(self.seed + int(shard_index))
+
+        def xavier_(linear: nn.Linear) -> None:
+            rows, columns = linear.weight.shape
+            limit = (6.0 / float(rows + columns)) ** 0.5
+            linear.weight.uniform_(-limit, limit, generator=draws)
+            if linear.bias is not None:
+                linear.bias.zero_()
+
+        def unit_(norm: nn.Module) -> None:
+            norm.weight.fill_(1.0)
+            if getattr(norm, "bias", None) is not None:
+                norm.bias.zero_()
+
         for module in self.modules():
             if isinstance(module, nn.Linear):
-                fan_out, fan_in = module.weight.shape
-                bound = (6.0 / float(fan_in + fan_out)) ** 0.5
-                module.weight.uniform_(-bound, bound, generator=generator)
-                if module.bias is not None:
-                    module.bias.zero_()
+                xavier_(module)
             elif isinstance(module, (_RMSNorm, nn.LayerNorm)):
-                module.weight.fill_(1.0)
-                if getattr(module, "bias", None) is not None:
-                    module.bias.zero_()
+                unit_(module)
             elif isinstance(module, _QueryPool):
-                module.query_token.normal_(0.0, 0.02, generator=generator)
+                module.query_token.normal_(0.0, 0.02, generator=draws)
         self.final_linear.weight.mul_(self.initial_logit_sign)
 
     def parallelize(self, config: ParallelConfig, device) -> None:

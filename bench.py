@@ -45,6 +45,9 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--grad-accum", type=int, default=1,
                         help="microbatches per optimizer update (the headline uses 1)")
+    parser.add_argument("--no-stream", action="store_true",
+                        help="skip the streaming measurement that follows the training regions")
+    parser.add_argument("--stream-blocks", type=int, default=32)
     parser.add_argument("--reference-args", default="",
                         help="extra arguments for baseline/reference_train.py (debugging)")
     return parser.parse_args()
@@ -212,8 +215,39 @@ def main() -> int:
     elapsed_ms, e2e_max = float(times[0]), float(times[1])
     status = int(native.ext().status(device.index or 0).item())
 
+    # Every rank must hold the same parameters after the timed updates (the all-gather half of
+    # the optimizer kernel writes them through peer memory): checksum, min and max over ranks.
+    flat = job.optimizer.engine.flat_param
+    checksum = torch.stack((flat.double().sum(), flat.double().abs().sum(),
+                            flat.view(torch.int16).long().sum().double()))
+    low, high = checksum.clone(), checksum.clone()
+    if world > 1:
+        dist.all_reduce(low, op=dist.ReduceOp.MIN)
+        dist.all_reduce(high, op=dist.ReduceOp.MAX)
+    replicas_in_sync = bool(torch.equal(low, high)) if cp == 1 else None
+    peak_gb = round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 1)
+    rgb_tokens, accum, model_config = job.rgb_tokens_per_clip, job.grad_accum_steps, job.config
+    latent_hw, job_frames = job.latent_hw, job.frames
+
+    # Streaming (the second half of the headline metric): the training job is released first.
+    stream = None
+    if not args.no_stream and args.recipe == "bidirectional" and args.layers == 36:
+        import gc
+
+        from agentgarten_b200.bench_support import stream_benchmark
+
+        del job, device_batch, flat, loss
+        gc.collect()
+        torch.cuda.empty_cache()
+        try:
+            result = stream_benchmark(device, blocks=args.stream_blocks)
+            stream = {k: result[k] for k in ("p50_ms", "p99_ms", "mean_ms", "blocks", "n_gpus",
+                                             "parallelism", "cuda_graphs", "kernel_status", "timed")}
+        except Exception as error:  # the training numbers stand on their own
+            stream = {"unavailable": f"{type(error).__name__}: {' '.join(str(error).split())[:200]}"}
+
     if rank == 0:
-        tokens = job.rgb_tokens_per_clip * (world // cp) * args.steps * job.grad_accum_steps
+        tokens = rgb_tokens * (world // cp) * args.steps * accum
         value = tokens / (elapsed_ms / 1e3)
         line = {
             "metric": "train latent-tokens/s/box (bidirectional rectified flow)"
@@ -231,18 +265,18 @@ def main() -> int:
             "data": "synthetic cached latents N(0,1), random-init weights",
             "impl": "agentgarten_b200",
             "config": {
-                "model": f"Cosmos3-Nano-shaped DiT: {job.config.num_hidden_layers} layers, hidden "
-                         f"{job.config.hidden_size}, {job.config.num_attention_heads}/"
-                         f"{job.config.num_key_value_heads} heads x {job.config.head_dim}, MLP "
-                         f"{job.config.intermediate_size}, plus frozen text tower of the same size",
+                "model": f"Cosmos3-Nano-shaped DiT: {model_config.num_hidden_layers} layers, hidden "
+                         f"{model_config.hidden_size}, {model_config.num_attention_heads}/"
+                         f"{model_config.num_key_value_heads} heads x {model_config.head_dim}, MLP "
+                         f"{model_config.intermediate_size}, plus frozen text tower of the same size",
                 "global_batch": world // cp,
-                "seq_len": job.rgb_tokens_per_clip,
-                "tokens_in_sequence": 2 * job.rgb_tokens_per_clip,
-                "latent": [1, 48, job.frames, *job.latent_hw],
+                "seq_len": rgb_tokens,
+                "tokens_in_sequence": 2 * rgb_tokens,
+                "latent": [1, 48, job_frames, *latent_hw],
                 "parallelism": f"dp{world // cp}" + (f" x cp{cp} (Ulysses)" if cp > 1 else "") +
                                " (replicated bf16 parameters, sharded FP32 optimizer state, "
-                               "peer-memory reduce-scatter + Adam + all-gather)",
-                "grad_accum_steps": job.grad_accum_steps,
+                               "peer-memory reduce-scatter under the backward pass + Adam + all-gather)",
+                "grad_accum_steps": accum,
                 "optimizer": "Adam lr 3e-5 betas (0.9, 0.99), FP32 master, grad clip 1.0",
                 "l2_policy": "inputs larger than L2 (14 GB of weights stream every step)",
             },
@@ -250,14 +284,17 @@ def main() -> int:
             "gpu_launches": launches,
             "loss": loss_value,
             "kernel_status": status,
-            "peak_memory_gb": round(torch.cuda.max_memory_allocated(device) / 2 ** 30, 1),
+            "peak_memory_gb": peak_gb,
+            "replicas_in_sync": replicas_in_sync,
         }
+        if stream is not None:
+            line["stream"] = stream
         if e2e_ms is not None:
             line["e2e"] = {
                 "value": tokens / (e2e_max / 1e3),
                 "unit": "latent RGB tokens/s",
                 "ms_per_step": e2e_max / args.steps,
-                "h2d_bytes_per_step": batch_bytes(host_batch) * job.grad_accum_steps,
+                "h2d_bytes_per_step": batch_bytes(host_batch) * accum,
                 "d2h_bytes_per_step": 4,
             }
         print(json.dumps(line))

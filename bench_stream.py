@@ -20,7 +20,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import statistics
 
 
 def main() -> int:
@@ -62,13 +61,7 @@ def main() -> int:
     import torch
     import torch.distributed as dist
 
-    from agentgarten_b200.bench_support import random_init_
-    from agentgarten_b200.inference.serving import prepare_serving
-    from agentgarten_b200.models.flow import rf_interpolate, rf_x0
-    from agentgarten_b200.networks.cosmos3 import Cosmos3Config, build_network
-    from agentgarten_b200.networks.cosmos3.conditioner import Cosmos3Conditioner
-    from agentgarten_b200.networks.cosmos3.network import Cosmos3Condition
-    from agentgarten_b200.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+    from agentgarten_b200.bench_support import stream_benchmark
     from agentgarten_b200.ops import native
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -78,87 +71,13 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=device)
     rank = dist.get_rank() if world > 1 else 0
     native.require()
-    config = Cosmos3Config(num_hidden_layers=args.layers)
-    net = build_network(config, init_device="meta").to(torch.bfloat16).to_empty(device=device)
-    random_init_(net, seed=0)
-    cond = Cosmos3Conditioner(config=config, codec=None, init_device="meta", geometry_noise_sigma=0.0)
-    cond.to(torch.bfloat16).to_empty(device=device)
-    random_init_(cond.text_encoder, seed=1)
-    sharded = world > 1 or args.tensor_parallel
-    if args.trace:
-        args.no_graphs = True
-    prepare_serving(net, cuda_graphs=not args.no_graphs, tensor_parallel=True if sharded else None,
-                    max_tokens=4096)
-    policy = StreamPolicy(block_frames=4, sink_frames=1, history_frames=24, rope="top_aligned",
-                          train_frames=61)
-    g = torch.Generator(device=device).manual_seed(0)
-    shape = (1, 48, 4, 30, 52)
-    ids = torch.randint(1000, 150000, (1, 512), device=device, generator=g)
-    with torch.inference_mode():
-        text = cond.text_encoder(ids, None)
-
-    def condition(frames):
-        s = (1, 48, frames, 30, 52)
-        return Cosmos3Condition(text=text, depth=torch.randn(s, device=device, generator=g),
-                                normal=torch.randn(s, device=device, generator=g),
-                                fps=torch.full((1,), 16.0, device=device))
-
-    endpoints = (1.0, 0.75, 0.5, 0.25)
-    stream = Cosmos3Stream(net, policy)
-    anchor = torch.randn((1, 48, 1, 30, 52), device=device, generator=g)
-    # every fill-level graph is captured here, before the timed blocks
-    stream.capture_graphs(anchor, condition(1), condition(4))
-    stream.start(anchor, condition(1))
-    times = []
-    launches_before = native.launches()
-    for block in range(args.blocks):
-        if args.trace and sharded and block == args.blocks - 2:
-            net._tensor_parallel.trace = {}
-        cond_block = condition(4)
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        clean = None
-        for step, sigma in enumerate(endpoints):
-            s = torch.full((1,), sigma, device=device)
-            noise = torch.randn(shape, device=device, generator=g)
-            current = noise if clean is None else rf_interpolate(clean, noise, s)
-            velocity = stream.denoise(current, s, cond_block)
-            clean = rf_x0(current, s, velocity)
-        stream.commit(clean, cond_block)
-        stop.record()
-        torch.cuda.synchronize()
-        times.append(start.elapsed_time(stop))
-        # A bounded wait that ran out on any rank ends the run on all of them: the remaining
-        # blocks would only repeat the failure.  (Outside the timed region.)
-        failed = native.ext().status(device.index).clone()
-        if world > 1:
-            dist.all_reduce(failed, op=dist.ReduceOp.MAX)
-        if int(failed.item()) != 0:
-            break
-    status = int(native.ext().status(device.index).item())
-    if world > 1:
-        gathered = torch.tensor(times + [float(status)], device=device)  # same length on every rank
-        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
-        times, status = gathered[:-1].tolist(), int(gathered[-1].item())
-    if args.trace and sharded and rank == 0:
-        print("phase ms (mean per call, rank 0):", json.dumps(net._tensor_parallel.trace_summary()))
-    if rank != 0:
-        dist.destroy_process_group()
-        return 0
-    steady = times  # all blocks count: the graphs were captured before the first one
-    steady_sorted = sorted(steady)
-    print(json.dumps({
-        "metric": "Cosmos3Stream ms per 4-frame block (4 denoise + 1 commit)",
-        "p50_ms": statistics.median(steady),
-        "p99_ms": steady_sorted[min(len(steady_sorted) - 1, int(0.99 * len(steady_sorted)))],
-        "first_blocks_ms": times[:8], "blocks": args.blocks, "n_gpus": world, "dtype": "bf16",
-        "parallelism": f"tp{world} (heads and MLP columns; GEMM+reduce-scatter / all-gather+GEMM over peer memory)"
-        if sharded else "single GPU",
-        "cuda_graphs": not args.no_graphs, "layers": args.layers,
-        "cache": "anchor + 6 blocks (sink 1, history 24 frames), top-aligned RoPE",
-        "tokens_per_block": 4 * 2 * 390, "gpu_launches": native.launches() - launches_before,
-        "kernel_status": status,
-    }))
+    result = stream_benchmark(device, blocks=args.blocks, layers=args.layers, graphs=not args.no_graphs,
+                              tensor_parallel=args.tensor_parallel, trace=args.trace)
+    if rank == 0:
+        phases = result.pop("phase_ms", None)
+        if phases is not None:
+            print("phase ms (mean per call, rank 0):", json.dumps(phases))
+        print(json.dumps(result))
     if world > 1:
         dist.destroy_process_group()
     return 0
