@@ -49,10 +49,29 @@ class _Linear(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         ctx.save_for_backward(x2, weight)
+        ctx.save_for_forward(x2, weight)
         ctx.has_bias = bias is not None
         ctx.shape = x.shape
         out = gemm(x2, weight, bias=bias)
         return out.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def jvp(ctx, x_tangent, weight_tangent, bias_tangent):
+        """Forward mode: ``d(x W^T + b) = dx W^T + x dW^T + db`` on the same tensor-core kernel
+        (the exact R1/R2 penalties push a direction through the frozen backbone this way)."""
+        x2, weight = ctx.saved_tensors
+        tangent = None
+        if x_tangent is not None:
+            rows = x_tangent.reshape(-1, x_tangent.shape[-1]).to(x2.dtype)
+            tangent = gemm(rows if rows.is_contiguous() else rows.contiguous(), weight)
+        if weight_tangent is not None:
+            moved = weight_tangent.to(weight.dtype).contiguous()
+            tangent = gemm(x2, moved) if tangent is None else gemm(x2, moved, out=tangent, accumulate=True)
+        if tangent is None:
+            tangent = x2.new_zeros(x2.shape[0], weight.shape[0])
+        if bias_tangent is not None:
+            tangent = tangent + bias_tangent.to(tangent.dtype)
+        return tangent.view(*ctx.shape[:-1], weight.shape[0])
 
     @staticmethod
     @torch.autograd.function.once_differentiable
@@ -72,9 +91,6 @@ class _Linear(torch.autograd.Function):
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    import torch.autograd.forward_ad as fwAD
-
-    if (native.use(x) and _gemm_ok(x, weight) and x.shape[-1] % 8 == 0
-            and fwAD.unpack_dual(x).tangent is None and fwAD.unpack_dual(weight).tangent is None):
-        return _Linear.apply(x, weight, bias)
+    if native.use(x) and _gemm_ok(x, weight) and x.shape[-1] % 8 == 0:
+        return _Linear.apply(x, weight, bias)  # reverse mode and forward mode (dual inputs) alike
     return F.linear(x, weight, bias)

@@ -34,6 +34,7 @@ from agentgarten_b200.infra.distributed import get_local_world_size
 from .network import ParallelNetwork
 
 __all__ = [
+    "replicated_parameter_bytes",
     "ATTENTION_SAVE_OPS",
     "ActivationCheckpointing",
     "ParallelConfig",
@@ -84,6 +85,45 @@ class ParallelConfig:
             object.__setattr__(self, "fsdp_mesh_shape", tuple(int(v) for v in self.fsdp_mesh_shape))
         object.__setattr__(self, "selective_save_ops", tuple(self.selective_save_ops))
         object.__setattr__(self, "compile_options", dict(self.compile_options))
+        # Knobs of the reference's FSDP2 wrapping that this engine cannot honour are refused
+        # rather than ignored.  (``reshard_after_forward`` is accepted in both settings: bf16
+        # parameters stay whole on every GPU here, there is nothing to reshard; see
+        # ``replicated_parameter_bytes`` for the memory this costs.)
+        if self.reduce_dtype != "float32":
+            raise ValueError("gradients are reduced in float32 by the peer-memory kernels; "
+                             f"reduce_dtype={self.reduce_dtype!r} is not supported")
+        shape = self.fsdp_mesh_shape
+        if shape is not None and (len(shape) not in (1, 2) or any(v < 1 for v in shape)):
+            raise ValueError(f"fsdp_mesh_shape must be (ranks,) or (nodes, ranks per node), got {shape}")
+        if shape is not None and len(shape) == 2 and shape[1] > 8:
+            raise ValueError("the optimizer state is sharded over the GPUs of one node (at most 8); "
+                             f"fsdp_mesh_shape={shape} asks for a shard group of {shape[1]}")
+
+
+def replicated_parameter_bytes(network: nn.Module, dtype: torch.dtype = torch.bfloat16) -> int:
+    """Device memory that the whole parameters and gradients of ``network`` take on EVERY GPU:
+    this engine shards the FP32 optimizer state (ZeRO-1/2), not the bf16 parameters, so a
+    trainable tower costs 2 x its parameter bytes per GPU and a frozen one 1 x."""
+    size = torch.empty((), dtype=dtype).element_size()
+    total = 0
+    for parameter in network.parameters():
+        total += parameter.numel() * size * (2 if parameter.requires_grad else 1)
+    return total
+
+
+def _check_fits_replicated(network: nn.Module, dtype: torch.dtype, device: torch.device) -> None:
+    """Fail before materialising a tower whose replicated parameters cannot fit the device
+    (the sharded-parameter mode of FSDP2 would train it; this engine cannot)."""
+    if device.type != "cuda":
+        return
+    need = replicated_parameter_bytes(network, dtype)
+    free, _ = torch.cuda.mem_get_info(device)
+    if need > free:
+        raise MemoryError(
+            f"{type(network).__name__}: whole parameters and gradients need {need / 2**30:.1f} GiB on every "
+            f"GPU, {free / 2**30:.1f} GiB are free.  Parameters are replicated here (only the FP32 "
+            "optimizer state is sharded); a model of this size needs parameter sharding, which this "
+            "engine does not implement.")
 
 
 _MESHES: dict[tuple, tuple[Any, Any]] = {}
@@ -234,6 +274,7 @@ def parallelize_network(network: ParallelNetwork, config: ParallelConfig, device
     network.shard_mesh = shard_mesh
     network.parallel_config = config
     if on_meta:
+        _check_fits_replicated(network, dtype, device)
         network.to_empty(device=device)
         if config.random_init_seed is not None:
             _random_init(network, int(config.random_init_seed))

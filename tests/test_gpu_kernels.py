@@ -292,6 +292,29 @@ def test_forward_mode_through_the_attention_op_uses_the_kernel():
     assert _rel(primal, want) < 2e-2 and _rel(tangent, want_tangent) < 3e-2
 
 
+def test_linear_forward_mode_runs_on_the_gemm_kernel():
+    """A dual input (and a dual weight) go through the tcgen05 GEMM: tangent = dx W^T + x dW^T."""
+    import torch.autograd.forward_ad as fwAD
+
+    from agentgarten_b200.ops.linear import linear
+
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x, dx = (torch.randn(3, 50, 256, device=DEV, generator=g).bfloat16() for _ in range(2))
+    w, dw = (torch.randn(384, 256, device=DEV, generator=g).bfloat16() * 0.1 for _ in range(2))
+    b = torch.randn(384, device=DEV, generator=g).bfloat16()
+    before = native.launches()
+    with torch.no_grad(), fwAD.dual_level():
+        out = linear(fwAD.make_dual(x, dx), fwAD.make_dual(w, dw), b)
+        primal, tangent = fwAD.unpack_dual(out)
+    assert native.launches() - before >= 3
+    want = x.float() @ w.float().t() + b.float()
+    want_tangent = dx.float() @ w.float().t() + x.float() @ dw.float().t()
+    assert _rel(primal, want) < 1e-2 and _rel(tangent, want_tangent) < 2e-2
+    with torch.no_grad(), fwAD.dual_level():
+        only_x = fwAD.unpack_dual(linear(fwAD.make_dual(x, dx), w, None)).tangent
+    assert _rel(only_x, dx.float() @ w.float().t()) < 1e-2
+
+
 def test_a_peer_that_never_arrives_ends_the_wait_with_a_status():
     """A gather-GEMM whose input rows are never announced gives up after its bounded wait,
     records the peer-timeout code and leaves the context usable."""

@@ -284,3 +284,21 @@ def test_peer_exchange_declines_what_it_cannot_serve(monkeypatch):
     assert peer_exchange.exchange(value, None) is None
     assert not peer_exchange._links
     peer_exchange.release()
+
+
+def test_parallel_config_refuses_what_the_engine_cannot_honour():
+    """Knobs of the reference's FSDP2 wrapping that would change behaviour are refused, not
+    ignored; the ones that cannot matter here are accepted."""
+    from agentgarten_b200.parallel.engine import ParallelConfig, replicated_parameter_bytes
+
+    ParallelConfig(reshard_after_forward=True)
+    ParallelConfig(reshard_after_forward=False, fsdp_mesh_shape=(2, 8))
+    with pytest.raises(ValueError, match="float32"):
+        ParallelConfig(reduce_dtype="bfloat16")
+    with pytest.raises(ValueError, match="fsdp_mesh_shape"):
+        ParallelConfig(fsdp_mesh_shape=(2, 2, 2))
+    with pytest.raises(ValueError, match="one node"):
+        ParallelConfig(fsdp_mesh_shape=(1, 16))
+    tower = torch.nn.Sequential(torch.nn.Linear(8, 8, bias=False), torch.nn.Linear(8, 4, bias=False))
+    tower[1].requires_grad_(False)
+    assert replicated_parameter_bytes(tower) == 2 * (64 * 2) + 32 * 2
