@@ -60,6 +60,8 @@ struct TpLink {
   int* arrive[8];      // int32 [tiles_owned] on every rank
 };
 cudaError_t gemm_bf16(const GemmArgs& args, int sm_count, cudaStream_t stream);
+// The same product on CTA pairs (tcgen05.mma.cta_group::2, 256x256 tiles); g.tp must be null.
+cudaError_t gemm_bf16_pairs(const GemmArgs& g, int sm_count, cudaStream_t stream);
 
 // Owner side of the tensor-parallel residual stream, one CTA per owned row or per four owned rows:
 //   h = bf16(residual_row + sum over source ranks (in rank order) of slot[src][row])
@@ -117,11 +119,15 @@ cudaError_t head_norm_rope_fwd(const void* x, const void* w, const void* cosv, c
 int head_norm_rope_bwd_partials(int64_t rows, int heads);  // rows of the fp32 [.,128] partial
 cudaError_t head_norm_rope_bwd(const void* grad, const void* x, const void* w, const void* cosv,
                                const void* sinv, const float* rstd, void* dx, float* dw_partial,
-                               int64_t rows, int heads, cudaStream_t stream);
+                               int64_t rows, int heads, int64_t x_row_stride, int64_t dx_row_stride,
+                               cudaStream_t stream);  // strides in elements per token row
 cudaError_t silu_mul_fwd(const void* gate, const void* up, void* out, int64_t elements,
                          cudaStream_t stream);
 // out[r, c] = bf16(silu(both[r, c])) * both[r, width + c] for both = [rows, 2 * width].
 cudaError_t silu_mul_pair(const void* both, void* out, int64_t rows, int width, cudaStream_t stream);
+// dboth = [dgate | dup] for grad [rows, width] and both = [gate | up] ([rows, 2 * width]).
+cudaError_t silu_mul_pair_bwd(const void* grad, const void* both, void* dboth, int64_t rows,
+                              int width, cudaStream_t stream);
 cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, void* dgate,
                          void* dup, int64_t elements, cudaStream_t stream);
 // mode 0: (1-s)*a + s*b; mode 1: a - s*b.  sigma fp32 [batch, sigma_frames]
@@ -143,6 +149,7 @@ struct AttnArgs {
   const int* q_tiles; const int* entries; const int* text_valid;
   int64_t nq, nk, text_len, batch;
   int64_t q_row_stride, q_batch_stride, kv_row_stride, kv_batch_stride;
+  int64_t v_row_stride, v_batch_stride;  // 0: v has the strides of k (v may be a column slice)
   int64_t text_row_stride, text_batch_stride;
   int hq, hkv, num_q_tiles;
   float scale;
@@ -166,6 +173,9 @@ struct AttnBwdArgs {
   AttnArgs fwd;
   const void* grad_out;
   void* dq; void* dk; void* dv;
+  // Row / batch strides of dv in elements (0: dense [B, NK, Hkv, 128]), so that dv can be
+  // written into the v columns of a fused [rows, q | k | v] gradient matrix.
+  int64_t dv_row_stride, dv_batch_stride;
   float* delta;
   const int* k_tiles; const int* q_lists;
   int num_k_tiles;

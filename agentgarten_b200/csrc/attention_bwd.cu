@@ -332,7 +332,8 @@ struct DkvParams {
   const float* lse;
   const float* delta;
   __nv_bfloat16* dk;  // [B, NK, Hkv, 128]
-  __nv_bfloat16* dv;
+  __nv_bfloat16* dv;  // rows at dv_row_stride (dense by default)
+  int64_t dv_row_stride, dv_batch_stride;
   int nq, nk, hq, hkv, group;
   float scale, scale_log2;
   int* status;
@@ -570,9 +571,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after_sync();
       const bool row_ok = key < k_rows;
       const int64_t base = ((int64_t(batch) * p.nk + k_row + key) * p.hkv + kv_head) * ATT_D;
+      const int64_t base_v = int64_t(batch) * p.dv_batch_stride + int64_t(k_row + key) * p.dv_row_stride +
+                             int64_t(kv_head) * ATT_D;
       {  // the two halves write one gradient each
         const int which = half;
-        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + base;
+        __nv_bfloat16* dst = which == 0 ? p.dv + base_v : p.dk + base;
         const uint32_t col0 = which == 0 ? C_DV : C_DK;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
@@ -622,7 +625,8 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
       !make_rows_map_bwd(&tq64, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride, DKV_BQ) ||
       !make_rows_map_bwd(&tdo64, b.grad_out, a.hq, a.nq, a.batch, dense_row, dense_row * a.nq, DKV_BQ) ||
       !make_rows_map_bwd(&tk, a.k, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride) ||
-      !make_rows_map_bwd(&tv, a.v, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride)) {
+      !make_rows_map_bwd(&tv, a.v, a.hkv, a.nk, a.batch, a.v_row_stride ? a.v_row_stride : a.kv_row_stride,
+                     a.v_row_stride ? a.v_batch_stride : a.kv_batch_stride)) {
     set_error_detail("attention_bwd: tensor map refused by the driver");
     return cudaErrorInvalidValue;
   }
@@ -666,6 +670,8 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
     DkvParams p;
     p.k_tiles = b.k_tiles; p.q_lists = b.q_lists; p.lse = a.lse; p.delta = b.delta;
     p.dk = static_cast<__nv_bfloat16*>(b.dk); p.dv = static_cast<__nv_bfloat16*>(b.dv);
+    p.dv_row_stride = b.dv_row_stride ? b.dv_row_stride : int64_t(a.hkv) * ATT_D;
+    p.dv_batch_stride = b.dv_row_stride ? b.dv_batch_stride : int64_t(a.nk) * a.hkv * ATT_D;
     p.nq = int(a.nq); p.nk = int(a.nk); p.hq = a.hq; p.hkv = a.hkv; p.group = a.hq / a.hkv;
     p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
     dim3 grid(b.num_k_tiles, a.hkv, unsigned(a.batch));

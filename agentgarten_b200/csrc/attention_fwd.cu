@@ -353,7 +353,8 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   CUtensorMap tq, tkt, tvt, tk, tv;
   if (!make_rows_map(&tq, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride) ||
       !make_rows_map(&tk, a.k, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride) ||
-      !make_rows_map(&tv, a.v, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride))
+      !make_rows_map(&tv, a.v, a.hkv, a.nk, a.batch, a.v_row_stride ? a.v_row_stride : a.kv_row_stride,
+                     a.v_row_stride ? a.v_batch_stride : a.kv_batch_stride))
     return cudaErrorInvalidValue;
   if (a.text_k) {
     if (!make_rows_map(&tkt, a.text_k, a.hkv, a.text_len, a.batch, a.text_row_stride,

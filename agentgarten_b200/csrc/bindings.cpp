@@ -146,18 +146,27 @@ std::tuple<Tensor, Tensor> head_norm_rope_fwd(const Tensor& x, const Tensor& w, 
   return {out, rstd};
 }
 
+// x may be a column slice of a wider matrix (rows at a constant stride); `out`, when given,
+// receives dx and may be such a slice too.
 std::tuple<Tensor, Tensor> head_norm_rope_bwd(const Tensor& grad, const Tensor& x, const Tensor& w,
                                               const Tensor& cosv, const Tensor& sinv,
-                                              const Tensor& rstd) {
+                                              const Tensor& rstd, c10::optional<Tensor> out) {
+  auto sliced = [](const Tensor& t) {
+    return t.dim() == 4 && t.size(3) == 128 && t.stride(3) == 1 && t.stride(2) == 128 &&
+           (t.size(0) == 1 || t.stride(0) == t.size(1) * t.stride(1)) && t.stride(1) % 8 == 0;
+  };
+  TORCH_CHECK(grad.is_contiguous() && sliced(x), "grad is contiguous, x is [B, N, H, 128] with rows at a constant stride");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = x.size(0) * x.size(1);
   const int heads = int(x.size(2));
-  auto dx = torch::empty_like(x);
+  Tensor dx = out.has_value() ? *out : torch::empty({x.size(0), x.size(1), x.size(2), 128}, x.options());
+  TORCH_CHECK(sliced(dx) && dx.sizes() == x.sizes(), "out must have the shape of x and rows at a constant stride");
   const int parts = agb::head_norm_rope_bwd_partials(rows, heads);
   auto partial = torch::zeros({parts, 128}, x.options().dtype(torch::kFloat32));
   check(agb::head_norm_rope_bwd(grad.data_ptr(), x.data_ptr(), w.data_ptr(), cosv.data_ptr(),
                                 sinv.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
-                                partial.data_ptr<float>(), rows, heads, stream_of(x)),
+                                partial.data_ptr<float>(), rows, heads, x.stride(1), dx.stride(1),
+                                stream_of(x)),
         "head_norm_rope_bwd");
   return {dx, partial.sum(0)};
 }
@@ -180,6 +189,18 @@ Tensor silu_mul_pair(const Tensor& both) {
   check(agb::silu_mul_pair(both.data_ptr(), out.data_ptr(), both.size(0), int(both.size(1) / 2),
                            stream_of(both)), "silu_mul_pair");
   return out;
+}
+
+Tensor silu_mul_pair_bwd(const Tensor& grad, const Tensor& both) {
+  check_bf16(both, "both");
+  TORCH_CHECK(both.dim() == 2 && both.is_contiguous() && grad.is_contiguous() &&
+                  grad.size(0) == both.size(0) && 2 * grad.size(1) == both.size(1) && grad.size(1) % 8 == 0,
+              "silu_mul_pair_bwd takes grad [rows, width] and both [rows, 2 * width]");
+  c10::cuda::CUDAGuard guard(both.device());
+  auto dboth = torch::empty_like(both);
+  check(agb::silu_mul_pair_bwd(grad.data_ptr(), both.data_ptr(), dboth.data_ptr(), both.size(0),
+                               int(grad.size(1)), stream_of(both)), "silu_mul_pair_bwd");
+  return dboth;
 }
 
 std::tuple<Tensor, Tensor> silu_mul_bwd(const Tensor& grad, const Tensor& gate, const Tensor& up) {
@@ -213,7 +234,8 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   check_bf16(v, "v");
   TORCH_CHECK(q.dim() == 4 && q.size(3) == 128 && k.dim() == 4 && k.size(3) == 128, "head_dim must be 128");
   TORCH_CHECK(q.stride(3) == 1 && q.stride(2) == 128 && k.stride(3) == 1 && k.stride(2) == 128 &&
-                  v.stride(3) == 1 && v.stride(2) == 128 && k.strides() == v.strides(),
+                  v.stride(3) == 1 && v.stride(2) == 128 && k.sizes() == v.sizes() &&
+                  v.stride(1) % 8 == 0 && v.stride(0) % 8 == 0,
               "q/k/v must be dense over (head, dim)");
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t splits = key_splits > 1 ? key_splits : 1;
@@ -228,6 +250,7 @@ std::tuple<Tensor, Tensor> attn_fwd(const Tensor& q, const Tensor& k, const Tens
   a.nq = q.size(1); a.nk = k.size(1); a.batch = q.size(0);
   a.q_row_stride = q.stride(1); a.q_batch_stride = q.stride(0);
   a.kv_row_stride = k.stride(1); a.kv_batch_stride = k.stride(0);
+  a.v_row_stride = v.stride(1); a.v_batch_stride = v.stride(0);
   if (text_k.has_value()) {
     check_bf16(*text_k, "text_k");
     TORCH_CHECK(text_k->strides() == text_v->strides() && text_k->stride(2) == 128, "text k/v layout");
@@ -252,14 +275,18 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
     const Tensor& grad, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
     const Tensor& lse, c10::optional<Tensor> text_k, c10::optional<Tensor> text_v,
     c10::optional<Tensor> text_valid, const Tensor& q_tiles, const Tensor& entries,
-    const Tensor& k_tiles, const Tensor& q_lists, double scale) {
+    const Tensor& k_tiles, const Tensor& q_lists, double scale, c10::optional<Tensor> dv_out) {
   check_bf16(grad, "grad");
   TORCH_CHECK(grad.is_contiguous() && out.is_contiguous(), "grad/out must be contiguous");
-  TORCH_CHECK(q.stride(2) == 128 && k.stride(2) == 128 && k.strides() == v.strides(), "q/k/v layout");
+  TORCH_CHECK(q.stride(2) == 128 && k.stride(2) == 128 && v.stride(2) == 128 && v.stride(3) == 1 &&
+                  k.sizes() == v.sizes() && v.stride(1) % 8 == 0 && v.stride(0) % 8 == 0, "q/k/v layout");
   c10::cuda::CUDAGuard guard(q.device());
   auto dq = torch::empty({q.size(0), q.size(1), q.size(2), 128}, q.options());
   auto dk = torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
-  auto dv = torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
+  // dv_out: a caller-zeroed [B, NK, Hkv, 128] view (for example the v columns of a fused
+  // gradient matrix); rows of keys that nothing attends to are left untouched.
+  Tensor dv = dv_out.has_value() ? *dv_out : torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
+  TORCH_CHECK(dv.sizes() == k.sizes() && dv.stride(3) == 1 && dv.stride(2) == 128, "dv_out layout");
   auto delta = torch::empty({q.size(0), q.size(2), q.size(1)}, q.options().dtype(torch::kFloat32));
   agb::AttnBwdArgs b{};
   agb::AttnArgs& a = b.fwd;
@@ -269,6 +296,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   a.nq = q.size(1); a.nk = k.size(1); a.batch = q.size(0);
   a.q_row_stride = q.stride(1); a.q_batch_stride = q.stride(0);
   a.kv_row_stride = k.stride(1); a.kv_batch_stride = k.stride(0);
+  a.v_row_stride = v.stride(1); a.v_batch_stride = v.stride(0);
   if (text_k.has_value()) {
     a.text_k = text_k->data_ptr(); a.text_v = text_v->data_ptr();
     a.text_len = text_k->size(1);
@@ -280,6 +308,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   a.status = status_word(q.device().index()).data_ptr<int>();
   b.grad_out = grad.data_ptr();
   b.dq = dq.data_ptr(); b.dk = dk.data_ptr(); b.dv = dv.data_ptr();
+  b.dv_row_stride = dv.stride(1); b.dv_batch_stride = dv.stride(0);
   b.delta = delta.data_ptr<float>();
   b.k_tiles = k_tiles.data_ptr<int>(); b.q_lists = q_lists.data_ptr<int>();
   b.num_k_tiles = int(k_tiles.size(0));
@@ -734,6 +763,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_mul_fwd", &silu_mul_fwd);
   m.def("silu_mul_bwd", &silu_mul_bwd);
   m.def("silu_mul_pair", &silu_mul_pair);
+  m.def("silu_mul_pair_bwd", &silu_mul_pair_bwd);
   m.def("rf_combine", &rf_combine);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

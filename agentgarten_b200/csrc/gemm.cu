@@ -10,6 +10,8 @@
 //
 // The value of an output row depends only on that row of A (fixed tile shape, fixed K
 // order, no split-K), so results are invariant to how many rows are multiplied together.
+#include <cstdlib>
+
 #include "agb.h"
 #include "sm100.cuh"
 #include "tensormap.h"
@@ -423,6 +425,15 @@ cudaError_t launch(const GemmArgs& g, const CUtensorMap& ta, const CUtensorMap& 
 
 }  // namespace
 
+// Products with enough 256 x 256 tiles run on CTA pairs (csrc/gemm2.cu); both kernels add the
+// K slices in the same order, so a result does not depend on which of the two a call got
+// (tests/test_gpu_kernels.py compares them bit for bit).  AGB200_GEMM_PAIRS=0 keeps every
+// product on single-CTA tiles; the variable is read at each call so that a test can switch it.
+static bool use_cta_pairs() {
+  const char* choice = getenv("AGB200_GEMM_PAIRS");
+  return choice == nullptr || choice[0] != '0';
+}
+
 cudaError_t gemm_bf16(const GemmArgs& g, int sm_count, cudaStream_t stream) {
   if (g.m <= 0 || g.n <= 0 || g.k <= 0) return cudaSuccess;
   if ((g.n % 8) || (g.lda % 8) || (g.ldb % 8) || (g.ldo % 4) ||
@@ -430,6 +441,13 @@ cudaError_t gemm_bf16(const GemmArgs& g, int sm_count, cudaStream_t stream) {
       (reinterpret_cast<uintptr_t>(g.out) & 15)) {
     set_error_detail("gemm: sizes/strides must be multiples of 8 elements and pointers 16-byte aligned");
     return cudaErrorInvalidValue;
+  }
+
+  // Two SMs per 256 x 256 tile once there are enough tiles to give every pair of SMs one;
+  // smaller products keep 128-row tiles, which spread over more SMs.
+  if (!g.tp && use_cta_pairs() &&
+      ((g.m + 255) / 256) * ((g.n + 255) / 256) >= int64_t(sm_count) / 2) {
+    return gemm_bf16_pairs(g, sm_count, stream);
   }
 
   CUtensorMap ta, tb;

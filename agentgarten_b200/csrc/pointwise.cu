@@ -191,7 +191,8 @@ __global__ void __launch_bounds__(NT) head_norm_rope_bwd_kernel(
     const __nv_bfloat16* __restrict__ grad, const __nv_bfloat16* __restrict__ x,
     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ cosv,
     const __nv_bfloat16* __restrict__ sinv, const float* __restrict__ rstd,
-    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int64_t rows, int heads) {
+    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int64_t rows, int heads,
+    int64_t x_row_stride, int64_t dx_row_stride) {
   const int lane = threadIdx.x & 31;
   const int64_t warp_global = int64_t(blockIdx.x) * (NT / 32) + (threadIdx.x >> 5);
   const int64_t u0 = warp_global * HEAD_UNITS_PER_WARP;
@@ -202,6 +203,9 @@ __global__ void __launch_bounds__(NT) head_norm_rope_bwd_kernel(
   float dw[4] = {0.f, 0.f, 0.f, 0.f};
   for (int64_t unit = u0; unit < u1; ++unit) {
     const int64_t token = unit / heads;
+    // x and dx may be column slices of wider matrices (the q or k part of a fused q|k|v product)
+    const int64_t x_at = token * x_row_stride + (unit - token * heads) * 128;
+    const int64_t dx_at = token * dx_row_stride + (unit - token * heads) * 128;
     const uint32_t ga = *reinterpret_cast<const uint32_t*>(grad + unit * 128 + 2 * lane);
     const uint32_t gb = *reinterpret_cast<const uint32_t*>(grad + unit * 128 + 64 + 2 * lane);
     const float g[4] = {bf16_lo(ga), bf16_hi(ga), bf16_lo(gb), bf16_hi(gb)};
@@ -214,8 +218,8 @@ __global__ void __launch_bounds__(NT) head_norm_rope_bwd_kernel(
     // out_i = y_i c_i - y_{i+64} s_i ; out_{i+64} = y_{i+64} c_{i+64} + y_i s_{i+64}
     const float dy[4] = {g[0] * c[0] + g[2] * s[2], g[1] * c[1] + g[3] * s[3],
                          g[2] * c[2] - g[0] * s[0], g[3] * c[3] - g[1] * s[1]};
-    const uint32_t xa = *reinterpret_cast<const uint32_t*>(x + unit * 128 + 2 * lane);
-    const uint32_t xb = *reinterpret_cast<const uint32_t*>(x + unit * 128 + 64 + 2 * lane);
+    const uint32_t xa = *reinterpret_cast<const uint32_t*>(x + x_at + 2 * lane);
+    const uint32_t xb = *reinterpret_cast<const uint32_t*>(x + x_at + 64 + 2 * lane);
     const float xv[4] = {bf16_lo(xa), bf16_hi(xa), bf16_lo(xb), bf16_hi(xb)};
     const float r = rstd[unit];
     float dot = 0.f;
@@ -230,8 +234,8 @@ __global__ void __launch_bounds__(NT) head_norm_rope_bwd_kernel(
     float o4[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) o4[i] = dy[i] * wv[i] * r - xv[i] * coef;
-    *reinterpret_cast<uint32_t*>(dx + unit * 128 + 2 * lane) = pack_bf16(o4[0], o4[1]);
-    *reinterpret_cast<uint32_t*>(dx + unit * 128 + 64 + 2 * lane) = pack_bf16(o4[2], o4[3]);
+    *reinterpret_cast<uint32_t*>(dx + dx_at + 2 * lane) = pack_bf16(o4[0], o4[1]);
+    *reinterpret_cast<uint32_t*>(dx + dx_at + 64 + 2 * lane) = pack_bf16(o4[2], o4[3]);
   }
   float* dst = dw_partial + warp_global * 128;
   dst[2 * lane] = dw[0];
@@ -440,14 +444,15 @@ int head_norm_rope_bwd_partials(int64_t rows, int heads) {
 
 cudaError_t head_norm_rope_bwd(const void* grad, const void* x, const void* w, const void* cosv,
                                const void* sinv, const float* rstd, void* dx, float* dw_partial,
-                               int64_t rows, int heads, cudaStream_t stream) {
+                               int64_t rows, int heads, int64_t x_row_stride, int64_t dx_row_stride,
+                               cudaStream_t stream) {
   if (rows * heads == 0) return cudaSuccess;
   const int partial_rows = head_norm_rope_bwd_partials(rows, heads);
   head_norm_rope_bwd_kernel<<<partial_rows / (NT / 32), NT, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(grad), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(cosv),
       static_cast<const __nv_bfloat16*>(sinv), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial,
-      rows, heads);
+      rows, heads, x_row_stride, dx_row_stride);
   return cudaGetLastError();
 }
 
@@ -484,6 +489,42 @@ cudaError_t silu_mul_pair(const void* both, void* out, int64_t rows, int width, 
   if (width % 8) return cudaErrorInvalidValue;
   silu_mul_pair_kernel<<<grid_for(rows * (width / 8)), NT, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(both), static_cast<__nv_bfloat16*>(out), rows, width);
+  return cudaGetLastError();
+}
+
+// Backward of silu_mul_pair: grad [rows, width], both = [gate | up], dboth = [dgate | dup].
+__global__ void __launch_bounds__(NT) silu_mul_pair_bwd_kernel(const __nv_bfloat16* __restrict__ grad,
+                                                               const __nv_bfloat16* __restrict__ both,
+                                                               __nv_bfloat16* __restrict__ dboth,
+                                                               int64_t rows, int width) {
+  const int per_row = width / 8;
+  const int64_t vecs = rows * per_row;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < vecs; i += int64_t(gridDim.x) * NT) {
+    const int64_t row = i / per_row;
+    const int col = int(i - row * per_row) * 8;
+    float d[8], g[8], u[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const uint4*>(grad + row * width + col), d);
+    unpack8(*reinterpret_cast<const uint4*>(both + row * 2 * width + col), g);
+    unpack8(*reinterpret_cast<const uint4*>(both + row * 2 * width + width + col), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sig = 1.f / (1.f + __expf(-g[k]));
+      const float silu = g[k] * sig;
+      du[k] = d[k] * round_bf16(silu);
+      dg[k] = d[k] * u[k] * sig * (1.f + g[k] * (1.f - sig));
+    }
+    *reinterpret_cast<uint4*>(dboth + row * 2 * width + col) = pack8(dg);
+    *reinterpret_cast<uint4*>(dboth + row * 2 * width + width + col) = pack8(du);
+  }
+}
+
+cudaError_t silu_mul_pair_bwd(const void* grad, const void* both, void* dboth, int64_t rows,
+                              int width, cudaStream_t stream) {
+  if (rows == 0 || width == 0) return cudaSuccess;
+  if (width % 8) return cudaErrorInvalidValue;
+  silu_mul_pair_bwd_kernel<<<grid_for(rows * (width / 8)), NT, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(grad), static_cast<const __nv_bfloat16*>(both),
+      static_cast<__nv_bfloat16*>(dboth), rows, width);
   return cudaGetLastError();
 }
 

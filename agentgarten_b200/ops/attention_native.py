@@ -35,7 +35,7 @@ class _SegmentAttention(torch.autograd.Function):
         C = native.ext()
         dq, dk, dv = C.attn_bwd(grad.contiguous(), q, k, v, out, lse, text_k, text_v, text_valid,
                                 ctx.schedule.q_tiles, ctx.schedule.entries,
-                                ctx.schedule.k_tiles, ctx.schedule.q_lists, ctx.scale)
+                                ctx.schedule.k_tiles, ctx.schedule.q_lists, ctx.scale, None)
         native.count(3)
         return dq, dk, dv, None, None, None, None, None
 

@@ -13,6 +13,15 @@ outputs are kept, everything else is recomputed.
 Parity: reference ``wm/networks/cosmos3/layers.py:269-312`` (project / finish) run under
 ``wm/infra/parallel.py:164-214`` (selective activation checkpointing).
 
+The q, k and v projections run as one GEMM (N = q + 2 kv widths) and gate and up as another
+whenever their weight matrices lie back to back in one storage, which is how the optimizer
+engine's flat parameter buffer lays them out (``parallel/zero.py``); their gradient buffers
+are adjacent in the same way, so each group also takes one input-gradient and one
+weight-gradient GEMM in the backward pass.  The head norm reads q and k as column slices of
+the joint product, attention reads v as one, and the attention backward writes dv straight
+into the v columns of the joint gradient.  Weights that are not adjacent (a model without the
+flat buffer) take one GEMM each; an output column is the same K-ordered sum either way.
+
 Recomputation is a memory policy, not a numerical one: when the device has room, a layer
 keeps the activations of its MLP half (``h1``, its norm, gate, up: 65 KB per token) and of
 its attention half (``n1``, q/k/v before and after the head norm: 31 KB per token) and the
@@ -103,6 +112,70 @@ def _wgrad(weight: torch.Tensor, grad_rows: torch.Tensor, input_rows: torch.Tens
     return _gemm(grad_rows, input_rows, trans_a=True, trans_b=False)
 
 
+def _joined(parts):
+    """One ``[sum of rows, K]`` view over matrices that lie back to back in one storage, in
+    this order; None when they do not."""
+    first = parts[0]
+    if any(p is None for p in parts):
+        return None
+    at, storage = first.data_ptr(), first.untyped_storage().data_ptr()
+    for p in parts:
+        if (p.dim() != 2 or not p.is_contiguous() or p.shape[1] != first.shape[1] or p.dtype != first.dtype
+                or p.data_ptr() != at or p.untyped_storage().data_ptr() != storage):
+            return None
+        at += p.numel() * p.element_size()
+    rows = sum(p.shape[0] for p in parts)
+    return first.detach().as_strided((rows, first.shape[1]), (first.shape[1], 1))
+
+
+def _wgrad_group(weights, grad_rows: torch.Tensor, input_rows: torch.Tensor):
+    """Weight gradients of matrices whose products were computed as one GEMM: ``grad_rows`` holds
+    their output gradients side by side.  One GEMM into the joint gradient buffer when the
+    buffers are adjacent, else one per matrix from the column slices."""
+    joint = _joined([w.grad if w.requires_grad else None for w in weights])
+    if joint is not None:
+        _gemm(grad_rows, input_rows, trans_a=True, trans_b=False, out=joint, accumulate=True)
+        return [None] * len(weights)
+    results, at = [], 0
+    for w in weights:
+        results.append(_wgrad(w, grad_rows[:, at:at + w.shape[0]], input_rows))
+        at += w.shape[0]
+    return results
+
+
+def _project_qkv(C, n1, weights, shape, cos, sin, eps):
+    """(q_lin, k_lin, q, k, v, rstd_q, rstd_k, joint): the three projections of the normalised
+    rows and the head norm + RoPE of q and k.  ``joint`` is the [rows, q | k | v] product when one
+    GEMM made it (q_lin, k_lin and v are then column slices of it), else None."""
+    b, n, heads, kv_heads = shape
+    wq, wk, wv, nq, nk = weights
+    wqkv = _joined((wq, wk, wv))
+    if wqkv is not None:
+        joint = _gemm(n1, wqkv).view(b, n, -1)
+        q_lin = joint[..., :heads * 128].unflatten(-1, (heads, 128))
+        k_lin = joint[..., heads * 128:(heads + kv_heads) * 128].unflatten(-1, (kv_heads, 128))
+        v = joint[..., (heads + kv_heads) * 128:].unflatten(-1, (kv_heads, 128))
+    else:
+        joint = None
+        q_lin = _gemm(n1, wq).view(b, n, heads, 128)
+        k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
+        v = _gemm(n1, wv).view(b, n, kv_heads, 128)
+    q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
+    k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
+    return q_lin, k_lin, q, k, v, rq, rk, joint
+
+
+def _gate_up(C, n2, wg, wu):
+    """(activation, kept): silu(gate) * up of the normalised rows; ``kept`` is what the backward
+    needs of the projections: the joint [rows, gate | up] product, or the pair."""
+    wgu = _joined((wg, wu))
+    if wgu is not None:
+        both = _gemm(n2, wgu)
+        return C.silu_mul_pair(both), (both,)
+    gate, up = _gemm(n2, wg), _gemm(n2, wu)
+    return C.silu_mul_fwd(gate, up), (gate, up)
+
+
 class _Layer(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cos, sin, layer, schedule, text_k, text_v, text_valid, *weights):
@@ -114,23 +187,19 @@ class _Layer(torch.autograd.Function):
         x2 = x.reshape(b * n, h)
         keep_mlp, keep_attn = keep_policy(b * n, h, wg.shape[0], wq.shape[0], wk.shape[0], x.device)
         n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
-        q_lin = _gemm(n1, wq).view(b, n, heads, 128)
-        k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
-        q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
-        k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
-        v = _gemm(n1, wv).view(b, n, kv_heads, 128)
+        q_lin, k_lin, q, k, v, rq, rk, _ = _project_qkv(C, n1, (wq, wk, wv, nq, nk),
+                                                        (b, n, heads, kv_heads), cos, sin, eps)
         attn, lse = C.attn_fwd(q, k, v, text_k, text_v, text_valid, schedule.q_tiles,
                                schedule.entries, 128 ** -0.5, 1)
         h1 = _gemm(attn.view(b * n, heads * 128), wo, residual=x2)
         n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
-        gate, up = _gemm(n2, wg), _gemm(n2, wu)
-        act = C.silu_mul_fwd(gate, up)
+        act, projected = _gate_up(C, n2, wg, wu)
         y = _gemm(act, wd, residual=h1)
         native.count(7)
         ctx.layer, ctx.schedule = layer, schedule
         ctx.text = (text_k, text_v, text_valid)
         ctx.params = weights  # the parameter objects themselves (their .grad buffers are used)
-        ctx.kept_mlp = (h1, n2, rstd2, gate, up) if keep_mlp else None
+        ctx.kept_mlp = (h1, n2, rstd2, projected) if keep_mlp else None
         ctx.kept_attn = (n1, rstd1, q_lin, k_lin, q, k, v, rq, rk) if keep_attn else None
         ctx.save_for_backward(x, cos, sin, attn, lse, *weights)
         if any(w.requires_grad for w in weights):
@@ -160,23 +229,30 @@ class _Layer(torch.autograd.Function):
         attn2 = attn.view(b * n, heads * 128)
         # ---- the second half: kept, or recomputed
         if ctx.kept_mlp is not None:
-            h1, n2, rstd2, gate, up = ctx.kept_mlp
+            h1, n2, rstd2, projected = ctx.kept_mlp
             ctx.kept_mlp = None
+            act = C.silu_mul_pair(projected[0]) if len(projected) == 1 else C.silu_mul_fwd(*projected)
         else:
             h1 = _gemm(attn2, wo, residual=x2)
             n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
-            gate, up = _gemm(n2, wg), _gemm(n2, wu)
-        act = C.silu_mul_fwd(gate, up)
+            act, projected = _gate_up(C, n2, wg, wu)
         # ---- MLP backward
         dwd = _wgrad(wd, dy2, act)
         dact = _gemm(dy2, wd, trans_b=False)
         del act
-        dgate, dup = C.silu_mul_bwd(dact, gate, up)
-        del dact, gate, up
-        dwg, dwu = _wgrad(wg, dgate, n2), _wgrad(wu, dup, n2)
-        dn2 = _gemm(dgate, wg, trans_b=False)
-        _gemm(dup, wu, trans_b=False, out=dn2, accumulate=True)
-        del dgate, dup, n2
+        if len(projected) == 1:   # gate | up came from one GEMM: one GEMM each way back as well
+            dboth = C.silu_mul_pair_bwd(dact, projected[0])
+            del dact, projected
+            dwg, dwu = _wgrad_group((wg, wu), dboth, n2)
+            dn2 = _gemm(dboth, _joined((wg, wu)), trans_b=False)
+            del dboth, n2
+        else:
+            dgate, dup = C.silu_mul_bwd(dact, *projected)
+            del dact, projected
+            dwg, dwu = _wgrad(wg, dgate, n2), _wgrad(wu, dup, n2)
+            dn2 = _gemm(dgate, wg, trans_b=False)
+            _gemm(dup, wu, trans_b=False, out=dn2, accumulate=True)
+            del dgate, dup, n2
         dh1, dw_post = C.rms_norm_bwd(dn2, h1, w_post, rstd2)
         del dn2, h1
         dh1.add_(dy2)
@@ -189,23 +265,42 @@ class _Layer(torch.autograd.Function):
             ctx.kept_attn = None
         else:
             n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
-            q_lin = _gemm(n1, wq).view(b, n, heads, 128)
-            k_lin = _gemm(n1, wk).view(b, n, kv_heads, 128)
-            q, rq = C.head_norm_rope_fwd(q_lin, nq, cos, sin, eps)
-            k, rk = C.head_norm_rope_fwd(k_lin, nk, cos, sin, eps)
-            v = _gemm(n1, wv).view(b, n, kv_heads, 128)
-        dq, dk, dv = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
-                                schedule.q_tiles, schedule.entries, schedule.k_tiles,
-                                schedule.q_lists, 128 ** -0.5)
-        del dattn, q, k, v
-        dq_lin, dnq = C.head_norm_rope_bwd(dq, q_lin, nq, cos, sin, rq)
-        dk_lin, dnk = C.head_norm_rope_bwd(dk, k_lin, nk, cos, sin, rk)
-        del dq, dk, q_lin, k_lin
-        dq2, dk2, dv2 = dq_lin.view(b * n, -1), dk_lin.view(b * n, -1), dv.view(b * n, -1)
-        dwq, dwk, dwv = _wgrad(wq, dq2, n1), _wgrad(wk, dk2, n1), _wgrad(wv, dv2, n1)
-        dn1 = _gemm(dq2, wq, trans_b=False)
-        _gemm(dk2, wk, trans_b=False, out=dn1, accumulate=True)
-        _gemm(dv2, wv, trans_b=False, out=dn1, accumulate=True)
+            q_lin, k_lin, q, k, v, rq, rk, _ = _project_qkv(C, n1, (wq, wk, wv, nq, nk),
+                                                            (b, n, heads, kv_heads), cos, sin, eps)
+        wqkv = _joined((wq, wk, wv))
+        if wqkv is not None:
+            # One [rows, q | k | v] gradient: attention writes dv into its columns, the head-norm
+            # backward writes dq and dk into theirs; then one GEMM each for dW and dx.
+            split = (heads * 128, (heads + kv_heads) * 128)
+            dqkv = torch.empty(b, n, wqkv.shape[0], device=x.device, dtype=x.dtype)
+            dv = dqkv[..., split[1]:].unflatten(-1, (kv_heads, 128))
+            dv.zero_()
+            dq, dk, _ = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
+                                   schedule.q_tiles, schedule.entries, schedule.k_tiles,
+                                   schedule.q_lists, 128 ** -0.5, dv)
+            del dattn, q, k, v
+            _, dnq = C.head_norm_rope_bwd(dq, q_lin, nq, cos, sin, rq,
+                                          dqkv[..., :split[0]].unflatten(-1, (heads, 128)))
+            _, dnk = C.head_norm_rope_bwd(dk, k_lin, nk, cos, sin, rk,
+                                          dqkv[..., split[0]:split[1]].unflatten(-1, (kv_heads, 128)))
+            del dq, dk, q_lin, k_lin
+            dqkv = dqkv.view(b * n, -1)
+            dwq, dwk, dwv = _wgrad_group((wq, wk, wv), dqkv, n1)
+            dn1 = _gemm(dqkv, wqkv, trans_b=False)
+            del dqkv
+        else:
+            dq, dk, dv = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
+                                    schedule.q_tiles, schedule.entries, schedule.k_tiles,
+                                    schedule.q_lists, 128 ** -0.5, None)
+            del dattn, q, k, v
+            dq_lin, dnq = C.head_norm_rope_bwd(dq, q_lin, nq, cos, sin, rq, None)
+            dk_lin, dnk = C.head_norm_rope_bwd(dk, k_lin, nk, cos, sin, rk, None)
+            del dq, dk, q_lin, k_lin
+            dq2, dk2, dv2 = dq_lin.view(b * n, -1), dk_lin.view(b * n, -1), dv.view(b * n, -1)
+            dwq, dwk, dwv = _wgrad(wq, dq2, n1), _wgrad(wk, dk2, n1), _wgrad(wv, dv2, n1)
+            dn1 = _gemm(dq2, wq, trans_b=False)
+            _gemm(dk2, wk, trans_b=False, out=dn1, accumulate=True)
+            _gemm(dv2, wv, trans_b=False, out=dn1, accumulate=True)
         dx, dw_in = C.rms_norm_bwd(dn1, x2, w_in, rstd1)
         dx.add_(dh1)
         native.count(20)

@@ -122,7 +122,7 @@ class _HeadNormRope(torch.autograd.Function):
         C = native.ext()
         value, weight, cos, sin, rstd = ctx.saved_tensors
         dx, dw = C.head_norm_rope_bwd(grad.contiguous(), value, weight.contiguous(),
-                                      cos.contiguous(), sin.contiguous(), rstd)
+                                      cos.contiguous(), sin.contiguous(), rstd, None)
         native.count(2)
         return dx, dw.to(weight.dtype), None, None, None
 

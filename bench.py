@@ -217,10 +217,13 @@ def main() -> int:
 
     # Every rank must hold the same parameters after the timed updates (the all-gather half of
     # the optimizer kernel writes them through peer memory): checksum, min and max over ranks.
-    flat = job.optimizer.engine.flat_param
-    checksum = torch.stack((flat.double().sum(), flat.double().abs().sum(),
-                            flat.view(torch.int16).long().sum().double()))
-    low, high = checksum.clone(), checksum.clone()
+    flat = job.optimizer.engine.flat_param.view(torch.int16)
+    sums = torch.zeros(2, dtype=torch.int64, device=device)
+    for chunk in flat.split(1 << 26):          # bit patterns, in pieces: no 50 GB temporaries
+        wide = chunk.to(torch.int64)
+        sums[0] += wide.sum()
+        sums[1] += (wide * wide).sum()
+    low, high = sums.clone(), sums.clone()
     if world > 1:
         dist.all_reduce(low, op=dist.ReduceOp.MIN)
         dist.all_reduce(high, op=dist.ReduceOp.MAX)

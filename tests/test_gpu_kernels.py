@@ -65,6 +65,43 @@ def test_gemm_row_invariance():
     assert torch.equal(whole[130:391], part)
 
 
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False)])
+def test_gemm_on_cta_pairs_matches_single_cta_tiles(trans_a, trans_b, monkeypatch):
+    """Enough 256 x 256 tiles for one per pair of SMs sends a product to the two-SM kernel
+    (tcgen05 cta_group::2): ragged edges, both operand layouts and every epilogue give bit for
+    bit what the single-CTA kernel gives, and both agree with an fp32 product."""
+    torch.manual_seed(21)
+    m, n, k = 2312, 2328, 320          # 10 x 10 tiles with ragged last rows and columns
+    a = torch.randn((k, m) if trans_a else (m, k), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((n, k) if trans_b else (k, n), device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(n, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+    start32 = torch.randn(m, n, device=DEV, dtype=torch.float32)
+    start16 = torch.randn(m, n, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        plain = gemm(a, b, trans_a=trans_a, trans_b=trans_b)
+        fused = gemm(a, b, trans_a=trans_a, trans_b=trans_b, bias=bias, residual=res)
+        acc32, acc16 = start32.clone(), start16.clone()
+        gemm(a, b, trans_a=trans_a, trans_b=trans_b, out=acc32, accumulate=True)
+        gemm(a, b, trans_a=trans_a, trans_b=trans_b, out=acc16, accumulate=True)
+        torch.cuda.synchronize()
+        return plain, fused, acc32, acc16
+
+    monkeypatch.setenv("AGB200_GEMM_PAIRS", "1")
+    pairs = run()
+    monkeypatch.setenv("AGB200_GEMM_PAIRS", "0")
+    single = run()
+    _status_ok()
+    ref = (a.float().t() if trans_a else a.float()) @ (b.float().t() if trans_b else b.float())
+    assert _rel(pairs[0], ref) < 4e-3
+    assert _rel(pairs[1], ref + bias.float() + res.float()) < 4e-3
+    assert _rel(pairs[2], start32 + ref) < 1e-3
+    assert _rel(pairs[3], start16.float() + ref) < 4e-3
+    for got, want in zip(pairs, single):
+        assert torch.equal(got, want)
+
+
 def test_linear_autograd():
     torch.manual_seed(3)
     x = torch.randn(2, 100, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)

@@ -78,6 +78,39 @@ def test_fused_layer_matches_op_path_and_fp32(monkeypatch):
     del reference
 
 
+def test_joint_projection_gemms_match_one_gemm_per_weight():
+    """With the optimizer engine's flat buffer q|k|v and gate|up are adjacent in memory, so each
+    group runs as one GEMM forward and two backward (strided head norm, dv written into the joint
+    gradient).  Forward values are bit for bit those of one GEMM per weight; gradients agree to
+    bf16 rounding (the joint input gradient is summed in fp32 over all of q|k|v)."""
+    from agentgarten_b200.ops import fused_layer
+
+    config = _config()
+    batch = {k: v.to(DEV) for k, v in synthetic_batch(frames=3, height=16, width=16, text=9, seed=8).items()}
+    model = _model(DEV, torch.bfloat16, config)
+    loss_separate, separate = _loss_and_grads(model, batch, seed=5)
+    FusedAdam([p for p in model.net.parameters() if p.requires_grad], lr=1e-4,
+              use_te_capturable_kernel=True, master_weights=True)
+    blocks = [m for m in model.net.modules() if hasattr(m, "mlp_moe_gen")]
+    q, k, v = (m.weight for m in blocks[0].self_attn.parts()[:3])
+    assert fused_layer._joined((q, k, v)) is not None and fused_layer._joined((q.grad, k.grad, v.grad)) is not None
+    mlp = blocks[0].mlp_moe_gen
+    assert fused_layer._joined((mlp.gate_proj.weight, mlp.up_proj.weight)) is not None
+    torch.manual_seed(5)
+    for p in model.net.parameters():
+        if p.grad is not None:
+            p.grad.zero_()
+    _, loss = model.training_step(model.prepare_data_batch(batch), 0)
+    loss.backward()
+    torch.cuda.synchronize()
+    assert int(native.ext().status(0).item()) == 0
+    assert float(loss) == loss_separate
+    for name, p in model.net.named_parameters():
+        if name in separate and separate[name].norm() > 1e-8:
+            rel = float((p.grad.float().cpu() - separate[name]).norm() / separate[name].norm())
+            assert rel < 2e-2, (name, rel)
+
+
 def test_flat_adam_matches_foreach():
     torch.manual_seed(0)
     shapes = [(64, 32), (7, 24), (130,), (3, 5, 8)]
