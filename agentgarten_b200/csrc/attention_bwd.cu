@@ -315,16 +315,17 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 // operations of one thread execute in issue order, which makes refilling a buffer behind the
 // products that read its P^T / dS^T safe without a barrier round trip.
 // smem: K, V (resident) + Q, dO rings (3 stages of 64 rows) + item list + lse/delta vectors.
-// TMEM: S^T[2] [0,128) dP^T[2] [128,256) dV [256,384) dK [384,512).  Eight warps: warps k and
-// k + 4 share the 32 key rows of lane quarter k and take 32 of the 64 query columns each; the
-// packed bf16 results overwrite the first 16 columns of the 32 they were computed from.
+// TMEM: S^T[2] [0,128) dP^T[2] [128,256) dV [256,384) dK [384,512).  Eight warps in two groups
+// of four: group g works on the items of score buffer g (every other item), warp k of a group on
+// the 32 key rows of lane quarter k; the packed bf16 results overwrite the first 16 columns of
+// the 32 they were computed from.
 constexpr int DKV_BQ = 64;                      // query rows per item
 constexpr int DKV_STAGES = 3;
 constexpr int QD_BYTES = DKV_BQ * 128 * 2;      // 16 KiB: 64 rows x 128 d, two atoms of 8 KiB
 constexpr int QD_HALF = QD_BYTES / 2;
 constexpr int DKV_MAX_ITEMS = 4096;
 constexpr int DKV_SMEM = 2 * TILE_BYTES + 2 * DKV_STAGES * QD_BYTES + DKV_MAX_ITEMS * 8 +
-                         2 * 2 * DKV_BQ * 4 + 1024 + 512;
+                         2 * 2 * 2 * DKV_BQ * 4 + 1024 + 512;
 
 struct DkvParams {
   const int* k_tiles;  // [tiles, 5]: k_row, rows, first_reader, readers, causal (unused)
@@ -351,16 +352,16 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQ = smem + 2 * TILE_BYTES;                 // [DKV_STAGES]
   uint8_t* sdO = sQ + DKV_STAGES * QD_BYTES;           // [DKV_STAGES]
   int2* items = reinterpret_cast<int2*>(sdO + DKV_STAGES * QD_BYTES);  // (q_row, rows | head << 8)
-  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);      // [2][lse, delta][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * DKV_BQ);
+  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);      // [2 groups][2][lse, delta][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * 2 * DKV_BQ);
   uint64_t* kv_full = bars;
   uint64_t* qd_full = bars + 1;     // [3]
   uint64_t* qd_empty = bars + 4;    // [3]
   uint64_t* st_full = bars + 7;     // [2] S^T, dP^T of a buffer complete
-  uint64_t* pt_ready = bars + 9;    // [2] P^T, dS^T of a buffer written (count 8)
+  uint64_t* pt_ready = bars + 9;    // [2] P^T, dS^T of a buffer written (count 4)
   uint64_t* grad_done = bars + 11;  // all gradient products finished
-  uint64_t* stats_bar = bars + 12;  // lse/delta of an item staged (count 256)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* stats_bar = bars + 12;  // [2] lse/delta of a group's next item staged (count 128)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_items_smem = abort_flag + 1;
 
@@ -374,10 +375,10 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     *abort_flag = 0;
     mbar_init(kv_full, 1);
     mbar_init(grad_done, 1);
-    mbar_init(stats_bar, 256);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&st_full[i], 1);
-      mbar_init(&pt_ready[i], 8);
+      mbar_init(&pt_ready[i], 4);
+      mbar_init(&stats_bar[i], 128);
     }
     for (int i = 0; i < DKV_STAGES; ++i) {
       mbar_init(&qd_full[i], 1);
@@ -492,16 +493,23 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (ok) tc_commit(grad_done);
     }
   } else {
-    const int quarter = warp & 3, half = warp >> 2;
+    // Two groups of four warps take alternate items (group g: items g, g + 2, ... in score buffer
+    // g), so that one group's waits (for its scores, for its TMEM loads) are covered by the
+    // other group's arithmetic.  A thread owns one key row and all 64 query columns of its item,
+    // 32 at a time.
+    const int quarter = warp & 3, group = warp >> 2;
+    const int half = group;                  // the epilogue splits dV / dK the same way
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const int tid = (warp << 5) + lane;      // 0..255
-    const int key = quarter * 32 + lane;     // key row of this thread
+    const int tid = (quarter << 5) + lane;   // 0..127 within the group
+    const int key = tid;                     // key row of this thread
     bool ok = n_items > 0;
-    // Per query column the warps need -lse*log2(e) and -delta*scale.  They are staged in shared
-    // memory one item ahead: the global loads of item i + 1 are issued before the work on item
-    // i and stored behind it, so their latency never sits between two items.
+    // Per query column the warps need -lse*log2(e) and -delta*scale.  Each group stages them in
+    // shared memory one of its items ahead: the global loads are issued before the work on the
+    // current item and stored behind it, so their latency never sits between two items.
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     const float2 ps2 = make_float2(p.scale, p.scale);
+    float* group_stats = stats + group * (2 * 2 * DKV_BQ);   // [2 buffers][nl[64], nd[64]]
+    uint64_t* group_bar = &stats_bar[group];
     auto fetch_stat = [&](int i) -> float {
       // threads 0..63: -lse*log2(e) (or -inf: probability 0), threads 64..127: -delta*scale
       const int2 it = items[i];
@@ -513,57 +521,61 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (tid < DKV_BQ) return valid ? -p.lse[idx] * LOG2E : -INFINITY;
       return valid ? -p.delta[idx] * p.scale : 0.f;
     };
-    if (ok) {
-      if (tid < 2 * DKV_BQ) stats[tid] = fetch_stat(0);  // buffer 0: [nl[64], nd[64]]
-      mbar_arrive(stats_bar);
+    if (group < n_items) {
+      group_stats[tid] = fetch_stat(group);
+      mbar_arrive(group_bar);
     }
-    for (int i = 0; i < n_items && ok; ++i) {
-      const int buf = i & 1;
-      const bool more = i + 1 < n_items;
+    const int buf = group;
+    for (int i = group, n = 0; i < n_items && ok; i += 2, ++n) {
+      const bool more = i + 2 < n_items;
       float next_stat = 0.f;
-      if (more && tid < 2 * DKV_BQ) next_stat = fetch_stat(i + 1);
-      const float* my_stats = stats + buf * 2 * DKV_BQ;
-      if (!mbar_wait(stats_bar, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
-      if (!mbar_wait(&st_full[buf], (i >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (more) next_stat = fetch_stat(i + 2);
+      const float* my_stats = group_stats + (n & 1) * 2 * DKV_BQ;
+      if (!mbar_wait(group_bar, n & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(&st_full[buf], n & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, sv);
-      tmem_ld_32x32(tmem_base + lane_base + C_DPT + buf * DKV_BQ + half * 32, dv);
-      tmem_ld_wait();
-      uint32_t pp[16], dd[16];
-      const float4* nl4 = reinterpret_cast<const float4*>(my_stats + half * 32);
-      const float4* nd4 = reinterpret_cast<const float4*>(my_stats + DKV_BQ + half * 32);
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tmem_base + lane_base + C_ST + buf * DKV_BQ + c * 32, sv);
+        tmem_ld_32x32(tmem_base + lane_base + C_DPT + buf * DKV_BQ + c * 32, dv);
+        tmem_ld_wait();
+        uint32_t pp[16], dd[16];
+        const float4* nl4 = reinterpret_cast<const float4*>(my_stats + c * 32);
+        const float4* nd4 = reinterpret_cast<const float4*>(my_stats + DKV_BQ + c * 32);
 #pragma unroll
-      for (int k4 = 0; k4 < 8; ++k4) {  // four query columns per step
-        const float4 nl = nl4[k4], nd = nd4[k4];
-        const float2 x0 = ffma2(make_float2(__uint_as_float(sv[4 * k4]), __uint_as_float(sv[4 * k4 + 1])),
-                                sc2, make_float2(nl.x, nl.y));
-        const float2 x1 = ffma2(make_float2(__uint_as_float(sv[4 * k4 + 2]), __uint_as_float(sv[4 * k4 + 3])),
-                                sc2, make_float2(nl.z, nl.w));
-        const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
-        const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
-        const float2 g0 = ffma2(make_float2(__uint_as_float(dv[4 * k4]), __uint_as_float(dv[4 * k4 + 1])),
-                                ps2, make_float2(nd.x, nd.y));
-        const float2 g1 = ffma2(make_float2(__uint_as_float(dv[4 * k4 + 2]), __uint_as_float(dv[4 * k4 + 3])),
-                                ps2, make_float2(nd.z, nd.w));
-        const float2 d0 = fmul2(e0, g0), d1 = fmul2(e1, g1);
-        pp[2 * k4] = pack_bf16(e0.x, e0.y);
-        pp[2 * k4 + 1] = pack_bf16(e1.x, e1.y);
-        dd[2 * k4] = pack_bf16(d0.x, d0.y);
-        dd[2 * k4 + 1] = pack_bf16(d1.x, d1.y);
+        for (int k4 = 0; k4 < 8; ++k4) {  // four query columns per step
+          const float4 nl = nl4[k4], nd = nd4[k4];
+          const float2 x0 = ffma2(make_float2(__uint_as_float(sv[4 * k4]), __uint_as_float(sv[4 * k4 + 1])),
+                                  sc2, make_float2(nl.x, nl.y));
+          const float2 x1 = ffma2(make_float2(__uint_as_float(sv[4 * k4 + 2]), __uint_as_float(sv[4 * k4 + 3])),
+                                  sc2, make_float2(nl.z, nl.w));
+          const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
+          const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
+          const float2 g0 = ffma2(make_float2(__uint_as_float(dv[4 * k4]), __uint_as_float(dv[4 * k4 + 1])),
+                                  ps2, make_float2(nd.x, nd.y));
+          const float2 g1 = ffma2(make_float2(__uint_as_float(dv[4 * k4 + 2]), __uint_as_float(dv[4 * k4 + 3])),
+                                  ps2, make_float2(nd.z, nd.w));
+          const float2 d0 = fmul2(e0, g0), d1 = fmul2(e1, g1);
+          pp[2 * k4] = pack_bf16(e0.x, e0.y);
+          pp[2 * k4 + 1] = pack_bf16(e1.x, e1.y);
+          dd[2 * k4] = pack_bf16(d0.x, d0.y);
+          dd[2 * k4 + 1] = pack_bf16(d1.x, d1.y);
+        }
+        // the packed results land in columns this thread has already read
+        tmem_st_32x16(tmem_base + lane_base + C_ST + buf * DKV_BQ + c * 32, pp);
+        tmem_st_32x16(tmem_base + lane_base + C_DPT + buf * DKV_BQ + c * 32, dd);
       }
-      // the packed results land in columns this thread has already read
-      tmem_st_32x16(tmem_base + lane_base + C_ST + buf * DKV_BQ + half * 32, pp);
-      tmem_st_32x16(tmem_base + lane_base + C_DPT + buf * DKV_BQ + half * 32, dd);
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&pt_ready[buf]);
-      // The other stats buffer was last read for item i - 1; every thread has passed the wait
-      // of phase i above, which all threads entered only after finishing item i - 1.
+      // The other stats buffer of the group was last read for its previous item; every thread
+      // of the group has passed the wait of this phase, which all of them entered only after
+      // finishing that item.
       if (more) {
-        if (tid < 2 * DKV_BQ) stats[(buf ^ 1) * 2 * DKV_BQ + tid] = next_stat;
-        mbar_arrive(stats_bar);
+        group_stats[((n + 1) & 1) * 2 * DKV_BQ + tid] = next_stat;
+        mbar_arrive(group_bar);
       }
     }
     if (ok) ok = mbar_wait(grad_done, 0, guard, kTimeoutEpilogue);

@@ -3,7 +3,9 @@
 #include "agb.h"
 
 #include <cstdio>
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 namespace agb {
 namespace {
@@ -32,6 +34,23 @@ EncodeFn encode_fn() {
 
 namespace {
 thread_local const char* g_detail = "";
+
+// A tensor map is a pure function of (base, rank, dims, strides, box) for the fixed type,
+// swizzle and fill used here, and the allocator hands the same addresses back step after
+// step, so encoded maps are kept per host thread and looked up instead of re-encoded
+// (two or more encodes per launch otherwise, a few thousand launches per training step).
+struct MapKey {
+  uint64_t words[16];
+  bool operator==(const MapKey& other) const { return memcmp(words, other.words, sizeof(words)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& key) const {
+    uint64_t h = 0x9e3779b97f4a7c15ull;
+    for (uint64_t w : key.words) h = (h ^ w) * 0x100000001b3ull + (h >> 29);
+    return size_t(h);
+  }
+};
+constexpr size_t kMaxCachedMaps = 1 << 14;
 }
 void set_error_detail(const char* text) { g_detail = text; }
 const char* error_detail() { return g_detail; }
@@ -48,6 +67,20 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const ui
     bound = true;
   }
   if (rank < 1 || rank > 5) return false;
+  MapKey key{};
+  key.words[0] = reinterpret_cast<uint64_t>(base);
+  key.words[1] = uint64_t(rank);
+  for (int i = 0; i < rank; ++i) {
+    key.words[2 + i] = dims[i];
+    key.words[11 + i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) key.words[7 + i] = strides_bytes[i];
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *map = found->second;
+    return true;
+  }
   cuuint64_t gdims[5];
   cuuint64_t gstrides[4];
   cuuint32_t gbox[5];
@@ -69,8 +102,11 @@ bool make_tensor_map_bf16(CUtensorMap* map, const void* base, int rank, const ui
              (unsigned long long)(rank > 1 ? dims[1] : 0), (unsigned long long)(rank > 2 ? dims[2] : 0),
              (unsigned long long)(rank > 1 ? strides_bytes[0] : 0), box[0], rank > 1 ? box[1] : 0);
     set_error_detail(text);
+    return false;
   }
-  return r == CUDA_SUCCESS;
+  if (cache.size() >= kMaxCachedMaps) cache.clear();
+  cache.emplace(key, *map);
+  return true;
 }
 
 }  // namespace agb

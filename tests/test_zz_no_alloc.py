@@ -45,11 +45,17 @@ def test_no_alloc_rms_norm_bwd_matches_regular_entry_point():
         dw = torch.empty(width, device=device, dtype=torch.float32)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        # The driver's own count of free device memory sees what torch's allocator cannot
+        # (a cudaMalloc inside the library); compared from the second call on, after the
+        # first has loaded the module's code and its static scratch.
+        free_before = torch.cuda.mem_get_info(device)[0]
         code = fn(grad.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
                   dw.data_ptr(), rows, width, stream)
         torch.cuda.synchronize()
         assert code == 0, lib.agb_noalloc_last_error().decode()
         assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            assert torch.cuda.mem_get_info(device)[0] >= free_before
         assert torch.equal(dx, dx_ref), call
         assert torch.allclose(dw, dw_ref, rtol=1e-5, atol=1e-5), call
 
@@ -62,3 +68,6 @@ def test_no_alloc_rejects_oversized_request():
     assert code < 0
     assert b"scratch" in lib.agb_noalloc_last_error()
     assert fn(p, p, p, p, p, p, 16, 12, None) < 0
+    assert b"width" in lib.agb_noalloc_last_error()
+    assert fn(p, p, p, p, p, p, -1, 64, None) < 0
+    assert b"rows" in lib.agb_noalloc_last_error()
