@@ -306,26 +306,28 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 // ---------------------------------------------------------------------------- dK / dV
 // One CTA per (key tile of 128 rows, KV head, sample).  It walks every (query head of the
-// group, block of 64 query rows) that can see the tile:
-//   S^T  = K Q^T, dP^T = V dO^T                 (128 keys x 64 queries each, operands in smem)
+// group, block of 128 query rows) that can see the tile:
+//   S^T  = K Q^T, dP^T = V dO^T                 (128 keys x 128 queries each, operands in smem)
 //   P^T  = exp2(S^T scale - lse), dS^T = P^T (dP^T - delta) scale   (softmax warps)
 //   dV  += P^T dO,  dK += dS^T Q                (P^T / dS^T read from TMEM)
-// Query blocks of 64 rows leave room in TMEM for two S^T / dP^T buffers, so the scores of
-// the next block are computed while the warps work on the current one; tcgen05.mma
-// operations of one thread execute in issue order, which makes refilling a buffer behind the
-// products that read its P^T / dS^T safe without a barrier round trip.
-// smem: K, V (resident) + Q, dO rings (3 stages of 64 rows) + item list + lse/delta vectors.
-// TMEM: S^T[2] [0,128) dP^T[2] [128,256) dV [256,384) dK [384,512).  Eight warps in two groups
-// of four: group g works on the items of score buffer g (every other item), warp k of a group on
-// the 32 key rows of lane quarter k; the packed bf16 results overwrite the first 16 columns of
-// the 32 they were computed from.
-constexpr int DKV_BQ = 64;                      // query rows per item
-constexpr int DKV_STAGES = 3;
-constexpr int QD_BYTES = DKV_BQ * 128 * 2;      // 16 KiB: 64 rows x 128 d, two atoms of 8 KiB
-constexpr int QD_HALF = QD_BYTES / 2;
-constexpr int DKV_MAX_ITEMS = 4096;
-constexpr int DKV_SMEM = 2 * TILE_BYTES + 2 * DKV_STAGES * QD_BYTES + DKV_MAX_ITEMS * 8 +
-                         2 * 2 * 2 * DKV_BQ * 4 + 1024 + 512;
+// A tcgen05.mma of 128 rows costs about 90 cycles to issue whatever its width up to 128
+// columns (measured: 92 cycles for N = 64 and N = 128 alike, 128 for N = 256), so the kernel
+// issues as few and as wide products as TMEM allows: blocks of 128 queries, which fill TMEM
+// with one S^T, one dP^T and the two accumulators.  With single score buffers the overlap
+// comes from the order of issue, one block staggered against the next:
+//   dV(i) | S^T(i+1) | dK(i) | dP^T(i+1)
+// The exponentials of block i+1 run under dK(i) and dP^T(i+1), its dS^T under dV(i+1) and
+// S^T(i+2); tcgen05.mma operations of one thread execute in issue order, which makes
+// refilling a buffer behind the product that reads its P^T / dS^T safe without a barrier.
+// smem: K, V (resident) + Q, dO rings (2 stages of 128 rows) + item list + lse/delta vectors.
+// TMEM: S^T [0,128) dP^T [128,256) dV [256,384) dK [384,512).  Eight warps: warps k and k + 4
+// share the 32 key rows of lane quarter k and take 64 of the 128 query columns each, 32 at a
+// time; the packed bf16 results overwrite the first 16 columns of the 32 they came from.
+constexpr int DKV_BQ = 128;                     // query rows per item
+constexpr int DKV_STAGES = 2;
+constexpr int DKV_MAX_ITEMS = 2048;
+constexpr int DKV_SMEM = 2 * TILE_BYTES + 2 * DKV_STAGES * TILE_BYTES + DKV_MAX_ITEMS * 8 +
+                         2 * 2 * DKV_BQ * 4 + 1024 + 512;
 
 struct DkvParams {
   const int* k_tiles;  // [tiles, 5]: k_row, rows, first_reader, readers, causal (unused)
@@ -350,18 +352,20 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sK = smem;
   uint8_t* sV = smem + TILE_BYTES;
   uint8_t* sQ = smem + 2 * TILE_BYTES;                 // [DKV_STAGES]
-  uint8_t* sdO = sQ + DKV_STAGES * QD_BYTES;           // [DKV_STAGES]
-  int2* items = reinterpret_cast<int2*>(sdO + DKV_STAGES * QD_BYTES);  // (q_row, rows | head << 8)
-  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);      // [2 groups][2][lse, delta][64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * 2 * DKV_BQ);
+  uint8_t* sdO = sQ + DKV_STAGES * TILE_BYTES;         // [DKV_STAGES]
+  int2* items = reinterpret_cast<int2*>(sdO + DKV_STAGES * TILE_BYTES);  // (q_row, rows | head << 8)
+  float* stats = reinterpret_cast<float*>(items + DKV_MAX_ITEMS);        // [2][nl[128], nd[128]]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stats + 2 * 2 * DKV_BQ);
   uint64_t* kv_full = bars;
-  uint64_t* qd_full = bars + 1;     // [3]
-  uint64_t* qd_empty = bars + 4;    // [3]
-  uint64_t* st_full = bars + 7;     // [2] S^T, dP^T of a buffer complete
-  uint64_t* pt_ready = bars + 9;    // [2] P^T, dS^T of a buffer written (count 4)
-  uint64_t* grad_done = bars + 11;  // all gradient products finished
-  uint64_t* stats_bar = bars + 12;  // [2] lse/delta of a group's next item staged (count 128)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* qd_full = bars + 1;     // [2]
+  uint64_t* qd_empty = bars + 3;    // [2]
+  uint64_t* st_full = bars + 5;     // S^T of an item complete
+  uint64_t* dp_full = bars + 6;     // dP^T of an item complete
+  uint64_t* pt_ready = bars + 7;    // P^T written (count 8)
+  uint64_t* ds_ready = bars + 8;    // dS^T written (count 8)
+  uint64_t* grad_done = bars + 9;   // all gradient products finished
+  uint64_t* stats_bar = bars + 10;  // lse/delta of an item staged (count 256)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_items_smem = abort_flag + 1;
 
@@ -375,11 +379,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     *abort_flag = 0;
     mbar_init(kv_full, 1);
     mbar_init(grad_done, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&st_full[i], 1);
-      mbar_init(&pt_ready[i], 4);
-      mbar_init(&stats_bar[i], 128);
-    }
+    mbar_init(stats_bar, 256);
+    mbar_init(st_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(pt_ready, 8);
+    mbar_init(ds_ready, 8);
     for (int i = 0; i < DKV_STAGES; ++i) {
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
@@ -427,11 +431,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int2 it = items[i];
         const int head = it.y >> 8;
         if (!mbar_wait(&qd_empty[st], ((i / DKV_STAGES) & 1) ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
-        mbar_expect_tx(&qd_full[st], 2 * QD_BYTES);
-        tma_load_3d(sQ + st * QD_BYTES, &tm_q, &qd_full[st], head * ATT_D, it.x, batch);
-        tma_load_3d(sQ + st * QD_BYTES + QD_HALF, &tm_q, &qd_full[st], head * ATT_D + 64, it.x, batch);
-        tma_load_3d(sdO + st * QD_BYTES, &tm_do, &qd_full[st], head * ATT_D, it.x, batch);
-        tma_load_3d(sdO + st * QD_BYTES + QD_HALF, &tm_do, &qd_full[st], head * ATT_D + 64, it.x, batch);
+        mbar_expect_tx(&qd_full[st], 2 * TILE_BYTES);
+        tma_load_3d(sQ + st * TILE_BYTES, &tm_q, &qd_full[st], head * ATT_D, it.x, batch);
+        tma_load_3d(sQ + st * TILE_BYTES + HALF_BYTES, &tm_q, &qd_full[st], head * ATT_D + 64, it.x, batch);
+        tma_load_3d(sdO + st * TILE_BYTES, &tm_do, &qd_full[st], head * ATT_D, it.x, batch);
+        tma_load_3d(sdO + st * TILE_BYTES + HALF_BYTES, &tm_do, &qd_full[st], head * ATT_D + 64, it.x, batch);
       }
       if (!ok || *abort_flag) {
         const uint64_t start = global_timer_ns();
@@ -440,78 +444,78 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp == 9) {
     if (lane == 0 && n_items > 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, DKV_BQ, 0, 0);   // 128 keys x 64 queries
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, DKV_BQ, 0, 0);   // 128 keys x 128 queries
       constexpr uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 1);      // 128 keys x 128 d
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
-      auto scores = [&](int i) -> bool {
-        const int st = i % DKV_STAGES, buf = i & 1;
+      // S^T of item i (needs its Q in shared memory; the buffer's last reader, dV(i-1), was
+      // issued before).
+      auto score_s = [&](int i) -> bool {
+        const int st = i % DKV_STAGES;
         if (!mbar_wait(&qd_full[st], (i / DKV_STAGES) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
-        const uint32_t q_addr = smem_u32(sQ + st * QD_BYTES);
-        const uint32_t do_addr = smem_u32(sdO + st * QD_BYTES);
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t ko = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          const uint32_t qo = (kk >> 2) * QD_HALF + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_ST + buf * DKV_BQ, make_smem_desc(k_addr + ko, 16, 1024),
-                    make_smem_desc(q_addr + qo, 16, 1024), idesc_s, kk != 0);
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_ST, make_smem_desc(k_addr + off, 16, 1024),
+                    make_smem_desc(q_addr + off, 16, 1024), idesc_s, kk != 0);
         }
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t ko = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          const uint32_t qo = (kk >> 2) * QD_HALF + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_DPT + buf * DKV_BQ, make_smem_desc(v_addr + ko, 16, 1024),
-                    make_smem_desc(do_addr + qo, 16, 1024), idesc_s, kk != 0);
-        }
-        tc_commit(&st_full[buf]);
+        tc_commit(st_full);
         return true;
       };
-      bool ok = mbar_wait(kv_full, 0, guard, kTimeoutMma);
-      if (ok) ok = scores(0);
-      for (int i = 0; i < n_items && ok; ++i) {
-        const int st = i % DKV_STAGES, buf = i & 1;
-        // The other buffer last held P^T / dS^T of item i - 1, whose products were issued in
-        // the previous iteration: refilling it now is ordered behind them.
-        if (i + 1 < n_items && !scores(i + 1)) { ok = false; break; }
-        if (!mbar_wait(&pt_ready[buf], (i >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t q_addr = smem_u32(sQ + st * QD_BYTES);
-        const uint32_t do_addr = smem_u32(sdO + st * QD_BYTES);
-        // 16 queries per step; the packed columns of query half h start at column 32 h.
+      // dP^T of item i (its dO arrived with Q; the buffer's last reader, dK(i-1), was issued before).
+      auto score_p = [&](int i) {
+        const int st = i % DKV_STAGES;
+        const uint32_t do_addr = smem_u32(sdO + st * TILE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
-          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + buf * DKV_BQ + (kk >> 1) * 32 + (kk & 1) * 8,
-                    make_smem_desc(do_addr + kk * 2048, QD_HALF, 1024), idesc_g, (i | kk) != 0);
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
+          tc_mma_ss(tmem_base + C_DPT, make_smem_desc(v_addr + off, 16, 1024),
+                    make_smem_desc(do_addr + off, 16, 1024), idesc_s, kk != 0);
         }
+        tc_commit(dp_full);
+      };
+      bool ok = mbar_wait(kv_full, 0, guard, kTimeoutMma);
+      if (ok) ok = score_s(0);
+      if (ok) score_p(0);
+      for (int i = 0; i < n_items && ok; ++i) {
+        const int st = i % DKV_STAGES;
+        const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES);
+        const uint32_t do_addr = smem_u32(sdO + st * TILE_BYTES);
+        if (!mbar_wait(pt_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after_sync();
+        // 16 queries per step; the packed columns of query chunk c (32 queries) start at column 32 c.
 #pragma unroll
         for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
-          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + buf * DKV_BQ + (kk >> 1) * 32 + (kk & 1) * 8,
-                    make_smem_desc(q_addr + kk * 2048, QD_HALF, 1024), idesc_g, (i | kk) != 0);
+          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk >> 1) * 32 + (kk & 1) * 8,
+                    make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_g, (i | kk) != 0);
+        }
+        if (i + 1 < n_items && !score_s(i + 1)) { ok = false; break; }
+        if (!mbar_wait(ds_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
+          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + (kk >> 1) * 32 + (kk & 1) * 8,
+                    make_smem_desc(q_addr + kk * 2048, HALF_BYTES, 1024), idesc_g, (i | kk) != 0);
         }
         tc_commit(&qd_empty[st]);
+        if (i + 1 < n_items) score_p(i + 1);
       }
       if (ok) tc_commit(grad_done);
     }
   } else {
-    // Two groups of four warps take alternate items (group g: items g, g + 2, ... in score buffer
-    // g), so that one group's waits (for its scores, for its TMEM loads) are covered by the
-    // other group's arithmetic.  A thread owns one key row and all 64 query columns of its item,
-    // 32 at a time.
-    const int quarter = warp & 3, group = warp >> 2;
-    const int half = group;                  // the epilogue splits dV / dK the same way
+    const int quarter = warp & 3, half = warp >> 2;
     const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-    const int tid = (quarter << 5) + lane;   // 0..127 within the group
-    const int key = tid;                     // key row of this thread
+    const int tid = (warp << 5) + lane;      // 0..255
+    const int key = quarter * 32 + lane;     // key row of this thread
     bool ok = n_items > 0;
-    // Per query column the warps need -lse*log2(e) and -delta*scale.  Each group stages them in
-    // shared memory one of its items ahead: the global loads are issued before the work on the
-    // current item and stored behind it, so their latency never sits between two items.
+    // Per query column the warps need -lse*log2(e) and -delta*scale.  They are staged in shared
+    // memory one item ahead: the global loads of item i + 1 are issued before the work on item
+    // i and stored behind it, so their latency never sits between two items.
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     const float2 ps2 = make_float2(p.scale, p.scale);
-    float* group_stats = stats + group * (2 * 2 * DKV_BQ);   // [2 buffers][nl[64], nd[64]]
-    uint64_t* group_bar = &stats_bar[group];
     auto fetch_stat = [&](int i) -> float {
-      // threads 0..63: -lse*log2(e) (or -inf: probability 0), threads 64..127: -delta*scale
+      // threads 0..127: -lse*log2(e) (or -inf: probability 0), threads 128..255: -delta*scale
       const int2 it = items[i];
       const int head = it.y >> 8, rows = it.y & 0xff;
       const int col = tid & (DKV_BQ - 1);
@@ -521,61 +525,76 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (tid < DKV_BQ) return valid ? -p.lse[idx] * LOG2E : -INFINITY;
       return valid ? -p.delta[idx] * p.scale : 0.f;
     };
-    if (group < n_items) {
-      group_stats[tid] = fetch_stat(group);
-      mbar_arrive(group_bar);
+    if (ok) {
+      stats[tid] = fetch_stat(0);  // buffer 0: [nl[128], nd[128]]
+      mbar_arrive(stats_bar);
     }
-    const int buf = group;
-    for (int i = group, n = 0; i < n_items && ok; i += 2, ++n) {
-      const bool more = i + 2 < n_items;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const bool more = i + 1 < n_items;
       float next_stat = 0.f;
-      if (more) next_stat = fetch_stat(i + 2);
-      const float* my_stats = group_stats + (n & 1) * 2 * DKV_BQ;
-      if (!mbar_wait(group_bar, n & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
-      if (!mbar_wait(&st_full[buf], n & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (more) next_stat = fetch_stat(i + 1);
+      const float* my_stats = stats + (i & 1) * 2 * DKV_BQ + half * 64;
+      if (!mbar_wait(stats_bar, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(st_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
-#pragma unroll 1
+      float2 prob[32];  // the probabilities of this thread's 64 query columns, kept for dS^T
+#pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tmem_base + lane_base + C_ST + buf * DKV_BQ + c * 32, sv);
-        tmem_ld_32x32(tmem_base + lane_base + C_DPT + buf * DKV_BQ + c * 32, dv);
+        uint32_t sv[32], pp[16];
+        tmem_ld_32x32(tmem_base + lane_base + C_ST + half * 64 + c * 32, sv);
         tmem_ld_wait();
-        uint32_t pp[16], dd[16];
         const float4* nl4 = reinterpret_cast<const float4*>(my_stats + c * 32);
-        const float4* nd4 = reinterpret_cast<const float4*>(my_stats + DKV_BQ + c * 32);
 #pragma unroll
         for (int k4 = 0; k4 < 8; ++k4) {  // four query columns per step
-          const float4 nl = nl4[k4], nd = nd4[k4];
+          const float4 nl = nl4[k4];
           const float2 x0 = ffma2(make_float2(__uint_as_float(sv[4 * k4]), __uint_as_float(sv[4 * k4 + 1])),
                                   sc2, make_float2(nl.x, nl.y));
           const float2 x1 = ffma2(make_float2(__uint_as_float(sv[4 * k4 + 2]), __uint_as_float(sv[4 * k4 + 3])),
                                   sc2, make_float2(nl.z, nl.w));
           const float2 e0 = make_float2(exp2f(x0.x), exp2f(x0.y));
           const float2 e1 = make_float2(exp2f(x1.x), exp2f(x1.y));
-          const float2 g0 = ffma2(make_float2(__uint_as_float(dv[4 * k4]), __uint_as_float(dv[4 * k4 + 1])),
-                                  ps2, make_float2(nd.x, nd.y));
-          const float2 g1 = ffma2(make_float2(__uint_as_float(dv[4 * k4 + 2]), __uint_as_float(dv[4 * k4 + 3])),
-                                  ps2, make_float2(nd.z, nd.w));
-          const float2 d0 = fmul2(e0, g0), d1 = fmul2(e1, g1);
+          prob[c * 16 + 2 * k4] = e0;
+          prob[c * 16 + 2 * k4 + 1] = e1;
           pp[2 * k4] = pack_bf16(e0.x, e0.y);
           pp[2 * k4 + 1] = pack_bf16(e1.x, e1.y);
-          dd[2 * k4] = pack_bf16(d0.x, d0.y);
-          dd[2 * k4 + 1] = pack_bf16(d1.x, d1.y);
         }
         // the packed results land in columns this thread has already read
-        tmem_st_32x16(tmem_base + lane_base + C_ST + buf * DKV_BQ + c * 32, pp);
-        tmem_st_32x16(tmem_base + lane_base + C_DPT + buf * DKV_BQ + c * 32, dd);
+        tmem_st_32x16(tmem_base + lane_base + C_ST + half * 64 + c * 32, pp);
       }
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&pt_ready[buf]);
-      // The other stats buffer of the group was last read for its previous item; every thread
-      // of the group has passed the wait of this phase, which all of them entered only after
-      // finishing that item.
+      if (lane == 0) mbar_arrive(pt_ready);
+      if (!mbar_wait(dp_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dv[32], dd[16];
+        tmem_ld_32x32(tmem_base + lane_base + C_DPT + half * 64 + c * 32, dv);
+        tmem_ld_wait();
+        const float4* nd4 = reinterpret_cast<const float4*>(my_stats + DKV_BQ + c * 32);
+#pragma unroll
+        for (int k4 = 0; k4 < 8; ++k4) {
+          const float4 nd = nd4[k4];
+          const float2 g0 = ffma2(make_float2(__uint_as_float(dv[4 * k4]), __uint_as_float(dv[4 * k4 + 1])),
+                                  ps2, make_float2(nd.x, nd.y));
+          const float2 g1 = ffma2(make_float2(__uint_as_float(dv[4 * k4 + 2]), __uint_as_float(dv[4 * k4 + 3])),
+                                  ps2, make_float2(nd.z, nd.w));
+          const float2 d0 = fmul2(prob[c * 16 + 2 * k4], g0), d1 = fmul2(prob[c * 16 + 2 * k4 + 1], g1);
+          dd[2 * k4] = pack_bf16(d0.x, d0.y);
+          dd[2 * k4 + 1] = pack_bf16(d1.x, d1.y);
+        }
+        tmem_st_32x16(tmem_base + lane_base + C_DPT + half * 64 + c * 32, dd);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+      // The other stats buffer was last read for item i - 1; every thread has passed the wait
+      // of phase i above, which all threads entered only after finishing item i - 1.
       if (more) {
-        group_stats[((n + 1) & 1) * 2 * DKV_BQ + tid] = next_stat;
-        mbar_arrive(group_bar);
+        stats[((i + 1) & 1) * 2 * DKV_BQ + tid] = next_stat;
+        mbar_arrive(stats_bar);
       }
     }
     if (ok) ok = mbar_wait(grad_done, 0, guard, kTimeoutEpilogue);
@@ -630,12 +649,10 @@ bool make_rows_map_bwd(CUtensorMap* map, const void* base, int heads, int64_t ro
 cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
   const AttnArgs& a = b.fwd;
   if (a.num_q_tiles == 0 || a.batch == 0) return cudaSuccess;
-  CUtensorMap tq, tdo, tq64, tdo64, tkt, tvt, tk, tv;
+  CUtensorMap tq, tdo, tkt, tvt, tk, tv;
   const int64_t dense_row = int64_t(a.hq) * ATT_D;
   if (!make_rows_map_bwd(&tq, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride) ||
       !make_rows_map_bwd(&tdo, b.grad_out, a.hq, a.nq, a.batch, dense_row, dense_row * a.nq) ||
-      !make_rows_map_bwd(&tq64, a.q, a.hq, a.nq, a.batch, a.q_row_stride, a.q_batch_stride, DKV_BQ) ||
-      !make_rows_map_bwd(&tdo64, b.grad_out, a.hq, a.nq, a.batch, dense_row, dense_row * a.nq, DKV_BQ) ||
       !make_rows_map_bwd(&tk, a.k, a.hkv, a.nk, a.batch, a.kv_row_stride, a.kv_batch_stride) ||
       !make_rows_map_bwd(&tv, a.v, a.hkv, a.nk, a.batch, a.v_row_stride ? a.v_row_stride : a.kv_row_stride,
                      a.v_row_stride ? a.v_batch_stride : a.kv_batch_stride)) {
@@ -687,7 +704,7 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
     p.nq = int(a.nq); p.nk = int(a.nk); p.hq = a.hq; p.hkv = a.hkv; p.group = a.hq / a.hkv;
     p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
     dim3 grid(b.num_k_tiles, a.hkv, unsigned(a.batch));
-    attn_dkv_kernel<<<grid, DQ_THREADS, DKV_SMEM, stream>>>(tq64, tdo64, tk, tv, p);
+    attn_dkv_kernel<<<grid, DQ_THREADS, DKV_SMEM, stream>>>(tq, tdo, tk, tv, p);
   }
   return cudaGetLastError();
 }
