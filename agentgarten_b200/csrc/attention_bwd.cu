@@ -49,8 +49,16 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
 }
 
 // ------------------------------------------------------------------------------- dQ
-// smem: Q, dO (resident) + K, V rings (2 stages).  TMEM: S [0,128) dP [128,256)
-// dQ [256,384) dS0 [384,448) dS1 [448,512).
+// One CTA per (query tile of 128 rows, query head, sample) walks the key tiles of the tile's
+// segments.  Three products per key tile, issued one tile staggered so that the tensor pipe
+// never waits for the elementwise warps (a tcgen05.mma of 128 rows costs about 90 cycles to
+// issue whatever its width up to 128 columns, so the products are as wide as they can be):
+//   S(j+1) = Q K^T | dQ += dS(j) K | dP(j+1) = dO V^T
+// The exponentials of tile j+1 run under dQ(j) and dP(j+1), its dS under S(j+2).  The
+// probabilities stay in registers; dS is packed over the first half of the dP columns it came
+// from and read from there by the dQ product.
+// smem: Q, dO (resident) + K, V rings (2 stages each, released separately: V after dP, K
+// after dQ).  TMEM: S[2] [0,256) dP [256,384) dQ [384,512).
 constexpr int DQ_SMEM = 6 * TILE_BYTES + ATT_MAX_TILES * int(sizeof(KeyTile)) + 1024 + 512;
 
 struct DqParams {
@@ -80,13 +88,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   KeyTile* tiles = reinterpret_cast<KeyTile*>(smem + 6 * TILE_BYTES);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + ATT_MAX_TILES);
   uint64_t* q_full = bars;        // Q and dO
-  uint64_t* kv_full = bars + 1;   // [2]
-  uint64_t* kv_empty = bars + 3;  // [2]
-  uint64_t* sp_full = bars + 5;   // S and dP of the current tile are in TMEM
-  uint64_t* sp_free = bars + 6;   // softmax has read them out (count 4)
-  uint64_t* ds_ready = bars + 7;  // [2] (count 4)
-  uint64_t* dq_done = bars + 9;   // [2] dQ product of a tile finished (dS buffer free)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* k_empty = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2] S of a tile is in TMEM
+  uint64_t* dp_full = bars + 11;  // dP of a tile is in TMEM
+  uint64_t* ds_ready = bars + 12; // dS of a tile written over dP (count 8)
+  uint64_t* dq_done = bars + 13;  // every dQ product finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_tiles_smem = abort_flag + 1;
 
@@ -100,13 +110,15 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(q_full, 1);
-    mbar_init(sp_full, 1);
-    mbar_init(sp_free, 8);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_ready, 8);
+    mbar_init(dq_done, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
-      mbar_init(&ds_ready[i], 8);
-      mbar_init(&dq_done[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
     }
     mbar_fence_init();
     int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
@@ -125,7 +137,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   const int n_tiles = *n_tiles_smem;
-  constexpr uint32_t C_S = 0, C_DP = 128, C_DQ = 256, C_DS = 384;
+  constexpr uint32_t C_S = 0, C_DP = 256, C_DQ = 384;
 
   if (warp == 8) {
     if (lane == 0 && n_tiles > 0) {
@@ -137,15 +149,19 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
+        const uint32_t parity = ((j >> 1) & 1) ^ 1;
         const KeyTile t = tiles[j];
         const CUtensorMap* mk = t.source == 0 ? &tm_kt : &tm_k;
         const CUtensorMap* mv = t.source == 0 ? &tm_vt : &tm_v;
-        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1, guard, kTimeoutProducer)) { ok = false; break; }
-        mbar_expect_tx(&kv_full[st], 2 * TILE_BYTES);
-        tma_load_3d(sK + st * TILE_BYTES, mk, &kv_full[st], kv_head * ATT_D, t.row, batch);
-        tma_load_3d(sK + st * TILE_BYTES + HALF_BYTES, mk, &kv_full[st], kv_head * ATT_D + 64, t.row, batch);
-        tma_load_3d(sV + st * TILE_BYTES, mv, &kv_full[st], kv_head * ATT_D, t.row, batch);
-        tma_load_3d(sV + st * TILE_BYTES + HALF_BYTES, mv, &kv_full[st], kv_head * ATT_D + 64, t.row, batch);
+        // the V stage comes free one product earlier than the K stage
+        if (!mbar_wait(&v_empty[st], parity, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], TILE_BYTES);
+        tma_load_3d(sV + st * TILE_BYTES, mv, &v_full[st], kv_head * ATT_D, t.row, batch);
+        tma_load_3d(sV + st * TILE_BYTES + HALF_BYTES, mv, &v_full[st], kv_head * ATT_D + 64, t.row, batch);
+        if (!mbar_wait(&k_empty[st], parity, guard, kTimeoutProducer)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], TILE_BYTES);
+        tma_load_3d(sK + st * TILE_BYTES, mk, &k_full[st], kv_head * ATT_D, t.row, batch);
+        tma_load_3d(sK + st * TILE_BYTES + HALF_BYTES, mk, &k_full[st], kv_head * ATT_D + 64, t.row, batch);
       }
       if (!ok || *abort_flag) {
         const uint64_t start = global_timer_ns();
@@ -158,45 +174,57 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);  // B MN-major
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
       bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma);
-      auto issue_scores = [&](int j) -> bool {
+      // S of tile j into buffer j & 1 (its last reader, the exponentials of tile j - 2, finished
+      // before dS(j-2) was announced, which the dQ product of that tile waited for).
+      auto score_s = [&](int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(&kv_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
-        if (j >= 1 && !mbar_wait(sp_free, (j - 1) & 1, guard, kTimeoutMma)) return false;
+        if (!mbar_wait(&k_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
-        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_S, make_smem_desc(q_addr + off, 16, 1024),
+          tc_mma_ss(tmem_base + C_S + st * 128, make_smem_desc(q_addr + off, 16, 1024),
                     make_smem_desc(k_addr + off, 16, 1024), idesc_kk, kk != 0);
         }
+        tc_commit(&s_full[st]);
+        return true;
+      };
+      // dP of tile j over dS(j-1), behind the dQ product that read it.
+      auto score_p = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
           tc_mma_ss(tmem_base + C_DP, make_smem_desc(do_addr + off, 16, 1024),
                     make_smem_desc(v_addr + off, 16, 1024), idesc_kk, kk != 0);
         }
-        tc_commit(sp_full);
+        tc_commit(dp_full);
+        tc_commit(&v_empty[st]);
         return true;
       };
-      if (ok) ok = issue_scores(0);
+      if (ok) ok = score_s(0);
+      if (ok) ok = score_p(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int st = j & 1, buf = j & 1;
-        // scores of the next tile run while the softmax warps still work on this one
-        if (j + 1 < n_tiles && !issue_scores(j + 1)) { ok = false; break; }
-        if (!mbar_wait(&ds_ready[buf], (j >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        const int st = j & 1;
+        if (j + 1 < n_tiles && !score_s(j + 1)) { ok = false; break; }
+        if (!mbar_wait(ds_ready, j & 1, guard, kTimeoutMma)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
+        // 16 keys per step; the packed columns of key chunk c (32 keys) start at column 32 c.
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_ts(tmem_base + C_DQ, tmem_base + C_DS + buf * 64 + kk * 8,
+          tc_mma_ts(tmem_base + C_DQ, tmem_base + C_DP + (kk >> 1) * 32 + (kk & 1) * 8,
                     make_smem_desc(k_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn,
                     (j | kk) != 0);
         }
-        tc_commit(&kv_empty[st]);
-        tc_commit(&dq_done[buf]);
+        tc_commit(&k_empty[st]);
+        if (j + 1 < n_tiles && !score_p(j + 1)) { ok = false; break; }
       }
+      if (ok) tc_commit(dq_done);
     }
   } else {
     // Eight warps: warps q and q + 4 share the 32 rows of TMEM lane quarter q and take one
@@ -210,7 +238,7 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const float lse2 = in_range ? p.lse[stat_index] * LOG2E : 0.f;
     const float delta = in_range ? p.delta[stat_index] : 0.f;
     // dS = exp2(S scale_log2 - lse2) * (dP scale - delta scale): two-lane arithmetic, 32 key
-    // columns at a time so that the compiler has registers left to overlap the exponentials.
+    // columns at a time.
     const float2 sc2 = make_float2(p.scale_log2, p.scale_log2);
     const float2 nl2 = make_float2(-lse2, -lse2);
     const float2 ps2 = make_float2(p.scale, p.scale);
@@ -219,30 +247,20 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int buf = j & 1;
       const KeyTile t = tiles[j];
-      if (!mbar_wait(sp_full, j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      if (!mbar_wait(&s_full[buf], (j >> 1) & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
-      if (j >= 2 && !mbar_wait(&dq_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutSoftmax)) {
-        ok = false;
-        break;
-      }
       // Only tiles with masked keys or rows (a partial last tile, the causal diagonal, the
       // ragged last query tile) pay for the masking; the test is uniform over the CTA.
       const bool plain = t.valid == ATT_BN && t.causal0 < 0 && q_rows == ATT_BM;
       int valid = t.valid;
       if (t.causal0 >= 0) valid = min(valid, q_local + my_row + 1 - t.causal0);
       if (!row_ok) valid = 0;
+      float2 prob[32];  // probabilities of this thread's 64 key columns, kept for dS
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tmem_base + lane_base + C_S + half * 64 + c * 32, sv);
-        tmem_ld_32x32(tmem_base + lane_base + C_DP + half * 64 + c * 32, dv);
+        uint32_t sv[32];
+        tmem_ld_32x32(tmem_base + lane_base + C_S + buf * 128 + half * 64 + c * 32, sv);
         tmem_ld_wait();
-        if (c == 1) {  // S and dP of this tile are in registers: the next scores may overwrite them
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(sp_free);
-        }
-        uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 x = ffma2(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])),
@@ -253,22 +271,32 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (col >= valid) e.x = 0.f;
             if (col + 1 >= valid) e.y = 0.f;
           }
+          prob[c * 16 + i] = e;
+        }
+      }
+      if (!mbar_wait(dp_full, j & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
+      tc_fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t dv[32], packed[16];
+        tmem_ld_32x32(tmem_base + lane_base + C_DP + half * 64 + c * 32, dv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
           const float2 g = ffma2(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])),
                                  ps2, nd2);
-          const float2 ds = fmul2(e, g);
+          const float2 ds = fmul2(prob[c * 16 + i], g);
           packed[i] = pack_bf16(ds.x, ds.y);
         }
-        tmem_st_32x16(tmem_base + lane_base + C_DS + buf * 64 + half * 32 + c * 16, packed);
+        // the packed results land in columns this thread has already read
+        tmem_st_32x16(tmem_base + lane_base + C_DP + half * 64 + c * 32, packed);
       }
       tmem_st_wait();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ds_ready[buf]);
+      if (lane == 0) mbar_arrive(ds_ready);
     }
-    if (ok) {
-      const int last = n_tiles - 1;
-      ok = mbar_wait(&dq_done[last & 1], (last >> 1) & 1, guard, kTimeoutEpilogue);
-    }
+    if (ok) ok = mbar_wait(dq_done, 0, guard, kTimeoutEpilogue);
     if (n_tiles == 0 || ok) {
       tc_fence_after_sync();
       __nv_bfloat16* dst = p.dq + ((int64_t(batch) * p.nq + q_row + my_row) * p.hq + head) * ATT_D;
