@@ -94,9 +94,9 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2] S of a tile is in TMEM
   uint64_t* dp_full = bars + 11;  // dP of a tile is in TMEM
-  uint64_t* ds_ready = bars + 12; // dS of a tile written over dP (count 8)
-  uint64_t* dq_done = bars + 13;  // every dQ product finished
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* ds_ready = bars + 12; // [2] dS of key chunk c of both halves written over dP (count 8)
+  uint64_t* dq_done = bars + 14;  // every dQ product finished
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_tiles_smem = abort_flag + 1;
 
@@ -111,7 +111,8 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     *abort_flag = 0;
     mbar_init(q_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(ds_ready, 8);
+    mbar_init(&ds_ready[0], 8);
+    mbar_init(&ds_ready[1], 8);
     mbar_init(dq_done, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
@@ -211,16 +212,23 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         if (j + 1 < n_tiles && !score_s(j + 1)) { ok = false; break; }
-        if (!mbar_wait(ds_ready, j & 1, guard, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
-        // 16 keys per step; the packed columns of key chunk c (32 keys) start at column 32 c.
+        // 16 keys per step; the packed columns of the 32 keys [32 g, 32 g + 32) start at column
+        // 32 g.  The warps announce dS in two parts (their first and their second 32 columns:
+        // g = c and g = 2 + c), so half of the product is issued while they finish the rest.
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          tc_mma_ts(tmem_base + C_DQ, tmem_base + C_DP + (kk >> 1) * 32 + (kk & 1) * 8,
-                    make_smem_desc(k_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn,
-                    (j | kk) != 0);
+        for (int c = 0; c < 2 && ok; ++c) {
+          if (!mbar_wait(&ds_ready[c], j & 1, guard, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const int kk = (s4 >> 1) * 4 + c * 2 + (s4 & 1);
+            tc_mma_ts(tmem_base + C_DQ, tmem_base + C_DP + (kk >> 1) * 32 + (kk & 1) * 8,
+                      make_smem_desc(k_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn,
+                      (j | c | s4) != 0);
+          }
         }
+        if (!ok) break;
         tc_commit(&k_empty[st]);
         if (j + 1 < n_tiles && !score_p(j + 1)) { ok = false; break; }
       }
@@ -290,11 +298,11 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         // the packed results land in columns this thread has already read
         tmem_st_32x16(tmem_base + lane_base + C_DP + half * 64 + c * 32, packed);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ds_ready[c]);
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
     }
     if (ok) ok = mbar_wait(dq_done, 0, guard, kTimeoutEpilogue);
     if (n_tiles == 0 || ok) {
@@ -389,11 +397,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* qd_empty = bars + 3;    // [2]
   uint64_t* st_full = bars + 5;     // S^T of an item complete
   uint64_t* dp_full = bars + 6;     // dP^T of an item complete
-  uint64_t* pt_ready = bars + 7;    // P^T written (count 8)
-  uint64_t* ds_ready = bars + 8;    // dS^T written (count 8)
-  uint64_t* grad_done = bars + 9;   // all gradient products finished
-  uint64_t* stats_bar = bars + 10;  // lse/delta of an item staged (count 256)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* pt_ready = bars + 7;    // [2] P^T of query chunk c of both halves written (count 8)
+  uint64_t* ds_ready = bars + 9;    // dS^T written (count 8)
+  uint64_t* grad_done = bars + 10;  // all gradient products finished
+  uint64_t* stats_bar = bars + 11;  // lse/delta of an item staged (count 256)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* n_items_smem = abort_flag + 1;
 
@@ -410,7 +418,8 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(stats_bar, 256);
     mbar_init(st_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(pt_ready, 8);
+    mbar_init(&pt_ready[0], 8);
+    mbar_init(&pt_ready[1], 8);
     mbar_init(ds_ready, 8);
     for (int i = 0; i < DKV_STAGES; ++i) {
       mbar_init(&qd_full[i], 1);
@@ -510,14 +519,22 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int st = i % DKV_STAGES;
         const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES);
         const uint32_t do_addr = smem_u32(sdO + st * TILE_BYTES);
-        if (!mbar_wait(pt_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
-        tc_fence_after_sync();
-        // 16 queries per step; the packed columns of query chunk c (32 queries) start at column 32 c.
+        // 16 queries per step; the packed columns of the 32 queries [32 g, 32 g + 32) start at
+        // column 32 g.  The warps announce P^T in two parts (their first and their second 32
+        // columns: g = c and g = 2 + c), so the first half of dV is issued while the second half
+        // of the exponentials is still being computed.
 #pragma unroll
-        for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
-          tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk >> 1) * 32 + (kk & 1) * 8,
-                    make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_g, (i | kk) != 0);
+        for (int c = 0; c < 2 && ok; ++c) {
+          if (!mbar_wait(&pt_ready[c], i & 1, guard, kTimeoutMma)) { ok = false; break; }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int s4 = 0; s4 < 4; ++s4) {
+            const int kk = (s4 >> 1) * 4 + c * 2 + (s4 & 1);
+            tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk >> 1) * 32 + (kk & 1) * 8,
+                      make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_g, (i | c | s4) != 0);
+          }
         }
+        if (!ok) break;
         if (i + 1 < n_items && !score_s(i + 1)) { ok = false; break; }
         if (!mbar_wait(ds_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
         tc_fence_after_sync();
@@ -588,11 +605,11 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         // the packed results land in columns this thread has already read
         tmem_st_32x16(tmem_base + lane_base + C_ST + half * 64 + c * 32, pp);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&pt_ready[c]);
       }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pt_ready);
       if (!mbar_wait(dp_full, i & 1, guard, kTimeoutSoftmax)) { ok = false; break; }
       tc_fence_after_sync();
 #pragma unroll
