@@ -327,4 +327,9 @@ cudaError_t zero_adam(const ZeroPeers& params, const ZeroPeers& grads, const int
                       const float* hyper, const float* grad_scale, const float* skip_flag,
                       int sm_count, cudaStream_t stream);
 
+// Diagnostic: every SM issues `iterations` x 8 tcgen05.mma (M 128, K 16, `columns` wide) back to
+// back; cycles[0] receives the cycles block 0 needed, or -1 when its bounded wait gave up.
+cudaError_t mma_issue_rate(int columns, bool a_from_tmem, int iterations, int sm_count, long long* cycles,
+                           int* status, cudaStream_t stream);
+
 }  // namespace agb

@@ -753,7 +753,22 @@ Tensor status(int64_t device) { return status_word(int(device)); }
 
 }  // namespace
 
+// Cycles per tcgen05.mma (M 128, K 16) issued back to back; see csrc/mma_rate.cu.
+double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
+  const int device = c10::cuda::current_device();
+  c10::cuda::CUDAGuard guard(device);
+  auto cycles = torch::zeros({1}, torch::dtype(torch::kInt64).device(torch::kCUDA, device));
+  auto stream = c10::cuda::getCurrentCUDAStream(device).stream();
+  check(agb::mma_issue_rate(int(columns), a_from_tmem, int(iterations), sm_count(device),
+                            reinterpret_cast<long long*>(cycles.data_ptr<int64_t>()),
+                            status_word(device).data_ptr<int>(), stream), "mma_issue_rate");
+  const int64_t total = cycles.item<int64_t>();
+  TORCH_CHECK(total >= 0, "mma_issue_rate: the bounded wait gave up");
+  return double(total) / double(iterations * 8);
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("mma_issue_rate", &mma_issue_rate);
   m.def("gemm", &gemm);
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_add_fwd", &rms_norm_add_fwd);

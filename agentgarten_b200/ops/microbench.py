@@ -189,12 +189,30 @@ def bench_codec(tokens: int, launches: int) -> list[dict]:
     return out
 
 
-CASES = {"codec": bench_codec, "conv": bench_conv, "depthwise": bench_depthwise, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
+def bench_mma_rate(tokens: int, launches: int) -> list[dict]:
+    """Cycles per tcgen05.mma instruction (M 128, K 16) issued back to back: the figure the
+    attention kernels' tile shapes are chosen from.  ``tflops`` is what that rate gives on all SMs
+    at the maximum SM clock."""
+    out = []
+    C = native.ext()
+    mhz = 1965.0   # the part's maximum SM clock; under the power cap a long kernel sees 1.5-1.7 GHz
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    for columns, from_tmem in ((64, False), (128, False), (256, False), (64, True), (128, True)):
+        C.mma_issue_rate(columns, from_tmem, 16)
+        cycles = C.mma_issue_rate(columns, from_tmem, 256)
+        flops_per_cycle = 2.0 * 128 * columns * 16 / cycles
+        out.append({"kernel": "tcgen05.mma issue rate", "ms": cycles,
+                    "case": f"M128 N{columns} K16, A from {'TMEM' if from_tmem else 'smem'}: cycles per instruction in the ms column",
+                    "tflops": flops_per_cycle * sms * mhz * 1e6 / 1e12})
+    return out
+
+
+CASES = {"mma_rate": bench_mma_rate, "codec": bench_codec, "conv": bench_conv, "depthwise": bench_depthwise, "gemm": bench_gemm, "attention": bench_attention, "jvp": bench_jvp, "pointwise": bench_pointwise}
 
 
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    parser.add_argument("--op", nargs="*", default=[c for c in CASES if c != "codec"], choices=list(CASES))
+    parser.add_argument("--op", nargs="*", default=[c for c in CASES if c not in ("codec", "mma_rate")], choices=list(CASES))
     parser.add_argument("--tokens", type=int, default=8192)
     parser.add_argument("--launches", type=int, default=10)
     parser.add_argument("--json", action="store_true")
