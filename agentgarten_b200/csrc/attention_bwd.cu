@@ -170,41 +170,41 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && n_tiles > 0) {
+    if (n_tiles > 0) {  // the whole warp runs the loop; one elected lane issues
       constexpr uint32_t idesc_kk = make_idesc_bf16(128, 128, 0, 0);  // both K-major
       constexpr uint32_t idesc_mn = make_idesc_bf16(128, 128, 0, 1);  // B MN-major
       const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sdO);
-      bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma);
+      bool ok = mbar_wait_w(q_full, 0, guard, kTimeoutMma);
       // S of tile j into buffer j & 1 (its last reader, the exponentials of tile j - 2, finished
       // before dS(j-2) was announced, which the dQ product of that tile waited for).
       auto score_s = [&](int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(&k_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
+        if (!mbar_wait_w(&k_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sK + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_S + st * 128, make_smem_desc(q_addr + off, 16, 1024),
+          tc_mma_ss_w(tmem_base + C_S + st * 128, make_smem_desc(q_addr + off, 16, 1024),
                     make_smem_desc(k_addr + off, 16, 1024), idesc_kk, kk != 0);
         }
-        tc_commit(&s_full[st]);
+        tc_commit_w(&s_full[st]);
         return true;
       };
       // dP of tile j over dS(j-1), behind the dQ product that read it.
       auto score_p = [&](int j) -> bool {
         const int st = j & 1;
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
+        if (!mbar_wait_w(&v_full[st], (j >> 1) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(sV + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_DP, make_smem_desc(do_addr + off, 16, 1024),
+          tc_mma_ss_w(tmem_base + C_DP, make_smem_desc(do_addr + off, 16, 1024),
                     make_smem_desc(v_addr + off, 16, 1024), idesc_kk, kk != 0);
         }
-        tc_commit(dp_full);
-        tc_commit(&v_empty[st]);
+        tc_commit_w(dp_full);
+        tc_commit_w(&v_empty[st]);
         return true;
       };
       if (ok) ok = score_s(0);
@@ -218,21 +218,21 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // g = c and g = 2 + c), so half of the product is issued while they finish the rest.
 #pragma unroll
         for (int c = 0; c < 2 && ok; ++c) {
-          if (!mbar_wait(&ds_ready[c], j & 1, guard, kTimeoutMma)) { ok = false; break; }
+          if (!mbar_wait_w(&ds_ready[c], j & 1, guard, kTimeoutMma)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
           for (int s4 = 0; s4 < 4; ++s4) {
             const int kk = (s4 >> 1) * 4 + c * 2 + (s4 & 1);
-            tc_mma_ts(tmem_base + C_DQ, tmem_base + C_DP + (kk >> 1) * 32 + (kk & 1) * 8,
+            tc_mma_ts_w(tmem_base + C_DQ, tmem_base + C_DP + (kk >> 1) * 32 + (kk & 1) * 8,
                       make_smem_desc(k_addr + kk * 2048, HALF_BYTES, 1024), idesc_mn,
                       (j | c | s4) != 0);
           }
         }
         if (!ok) break;
-        tc_commit(&k_empty[st]);
+        tc_commit_w(&k_empty[st]);
         if (j + 1 < n_tiles && !score_p(j + 1)) { ok = false; break; }
       }
-      if (ok) tc_commit(dq_done);
+      if (ok) tc_commit_w(dq_done);
     }
   } else {
     // Eight warps: warps q and q + 4 share the 32 rows of TMEM lane quarter q and take one
@@ -480,7 +480,7 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
   } else if (warp == 9) {
-    if (lane == 0 && n_items > 0) {
+    if (n_items > 0) {  // the whole warp runs the loop; one elected lane issues
       constexpr uint32_t idesc_s = make_idesc_bf16(128, DKV_BQ, 0, 0);   // 128 keys x 128 queries
       constexpr uint32_t idesc_g = make_idesc_bf16(128, 128, 0, 1);      // 128 keys x 128 d
       const uint32_t k_addr = smem_u32(sK), v_addr = smem_u32(sV);
@@ -488,16 +488,16 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // issued before).
       auto score_s = [&](int i) -> bool {
         const int st = i % DKV_STAGES;
-        if (!mbar_wait(&qd_full[st], (i / DKV_STAGES) & 1, guard, kTimeoutMma)) return false;
+        if (!mbar_wait_w(&qd_full[st], (i / DKV_STAGES) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
         const uint32_t q_addr = smem_u32(sQ + st * TILE_BYTES);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_ST, make_smem_desc(k_addr + off, 16, 1024),
+          tc_mma_ss_w(tmem_base + C_ST, make_smem_desc(k_addr + off, 16, 1024),
                     make_smem_desc(q_addr + off, 16, 1024), idesc_s, kk != 0);
         }
-        tc_commit(st_full);
+        tc_commit_w(st_full);
         return true;
       };
       // dP^T of item i (its dO arrived with Q; the buffer's last reader, dK(i-1), was issued before).
@@ -507,12 +507,12 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * HALF_BYTES + (kk & 3) * 32;
-          tc_mma_ss(tmem_base + C_DPT, make_smem_desc(v_addr + off, 16, 1024),
+          tc_mma_ss_w(tmem_base + C_DPT, make_smem_desc(v_addr + off, 16, 1024),
                     make_smem_desc(do_addr + off, 16, 1024), idesc_s, kk != 0);
         }
-        tc_commit(dp_full);
+        tc_commit_w(dp_full);
       };
-      bool ok = mbar_wait(kv_full, 0, guard, kTimeoutMma);
+      bool ok = mbar_wait_w(kv_full, 0, guard, kTimeoutMma);
       if (ok) ok = score_s(0);
       if (ok) score_p(0);
       for (int i = 0; i < n_items && ok; ++i) {
@@ -525,28 +525,28 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // of the exponentials is still being computed.
 #pragma unroll
         for (int c = 0; c < 2 && ok; ++c) {
-          if (!mbar_wait(&pt_ready[c], i & 1, guard, kTimeoutMma)) { ok = false; break; }
+          if (!mbar_wait_w(&pt_ready[c], i & 1, guard, kTimeoutMma)) { ok = false; break; }
           tc_fence_after_sync();
 #pragma unroll
           for (int s4 = 0; s4 < 4; ++s4) {
             const int kk = (s4 >> 1) * 4 + c * 2 + (s4 & 1);
-            tc_mma_ts(tmem_base + C_DV, tmem_base + C_ST + (kk >> 1) * 32 + (kk & 1) * 8,
+            tc_mma_ts_w(tmem_base + C_DV, tmem_base + C_ST + (kk >> 1) * 32 + (kk & 1) * 8,
                       make_smem_desc(do_addr + kk * 2048, HALF_BYTES, 1024), idesc_g, (i | c | s4) != 0);
           }
         }
         if (!ok) break;
         if (i + 1 < n_items && !score_s(i + 1)) { ok = false; break; }
-        if (!mbar_wait(ds_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait_w(ds_ready, i & 1, guard, kTimeoutMma)) { ok = false; break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int kk = 0; kk < DKV_BQ / 16; ++kk) {
-          tc_mma_ts(tmem_base + C_DK, tmem_base + C_DPT + (kk >> 1) * 32 + (kk & 1) * 8,
+          tc_mma_ts_w(tmem_base + C_DK, tmem_base + C_DPT + (kk >> 1) * 32 + (kk & 1) * 8,
                     make_smem_desc(q_addr + kk * 2048, HALF_BYTES, 1024), idesc_g, (i | kk) != 0);
         }
-        tc_commit(&qd_empty[st]);
+        tc_commit_w(&qd_empty[st]);
         if (i + 1 < n_items) score_p(i + 1);
       }
-      if (ok) tc_commit(grad_done);
+      if (ok) tc_commit_w(grad_done);
     }
   } else {
     const int quarter = warp & 3, half = warp >> 2;

@@ -195,7 +195,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
     }
   } else if (warp == 5) {
     // -------------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    {  // the whole warp runs the loop (addresses stay warp-uniform); one elected lane issues
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
@@ -204,14 +204,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, guard, kTimeoutMma)) {
+        if (!mbar_wait_w(&acc_empty[acc], acc_phase ^ 1, guard, kTimeoutMma)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(&full[stage], phase, guard, kTimeoutMma)) {
+          if (!mbar_wait_w(&full[stage], phase, guard, kTimeoutMma)) {
             ok = false;
             break;
           }
@@ -224,15 +224,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CU
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, ATOM_BYTES, 1024)
                                      : make_smem_desc(sb + kk * 32, 16, 1024);
-            tc_mma_ss(d_tmem, da, db, idesc, (kb | kk) != 0);
+            tc_mma_ss_w(d_tmem, da, db, idesc, (kb | kk) != 0);
           }
-          tc_commit(&empty[stage]);  // frees the stage once these MMAs have read it
+          tc_commit_w(&empty[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(&acc_full[acc]);
+        if (ok) tc_commit_w(&acc_full[acc]);
       }
     }
   } else {
