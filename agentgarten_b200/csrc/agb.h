@@ -181,6 +181,14 @@ struct AttnBwdArgs {
   int num_k_tiles;
 };
 cudaError_t attention_bwd(const AttnBwdArgs& args, cudaStream_t stream);
+// The same gradients in one pass over the scores (csrc/attention_bwd_fused.cu).  k_tiles int32
+// [num_k_tiles, 5] (k_row, rows, first_block, blocks, source: 0 text, 1 visual) in the order in
+// which the tiles take their turns, text tiles included; blocks int32 [*, 4] (q_block_row, lo, hi,
+// turn) with q_block_row a multiple of 128; dq_acc fp32 [B, nq_pad, Hq, 128] and turns int32
+// [1 + B * Hq * nq_pad / 128], both zeroed by the caller.  args.k_tiles / q_lists are unused,
+// args.num_k_tiles counts the rows of k_tiles.
+cudaError_t attention_bwd_fused(const AttnBwdArgs& args, const int* k_tiles, const int* blocks,
+                                float* dq_acc, int* turns, int64_t nq_pad, cudaStream_t stream);
 
 // Attention with forward-mode tangents (dense keys, optional prefix-valid text segment):
 // out/tangent fp32 [B, NQ, Hq, 128], lse fp32 [B, Hq, NQ] or null.  q/tq share strides, and so

@@ -316,6 +316,56 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(
   return {dq, dk, dv};
 }
 
+// The same gradients from the one-pass kernel.  k_tiles_f / blocks_f come from the schedule
+// (ops/attention.py::AttentionSchedule.fused); nq_pad is the query count rounded up to 128.
+std::tuple<Tensor, Tensor, Tensor> attn_bwd_fused(
+    const Tensor& grad, const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& out,
+    const Tensor& lse, c10::optional<Tensor> text_k, c10::optional<Tensor> text_v,
+    c10::optional<Tensor> text_valid, const Tensor& k_tiles_f, const Tensor& blocks_f, double scale,
+    c10::optional<Tensor> dv_out) {
+  check_bf16(grad, "grad");
+  TORCH_CHECK(grad.is_contiguous() && out.is_contiguous(), "grad/out must be contiguous");
+  TORCH_CHECK(q.stride(2) == 128 && k.stride(2) == 128 && v.stride(2) == 128 && v.stride(3) == 1 &&
+                  k.sizes() == v.sizes() && v.stride(1) % 8 == 0 && v.stride(0) % 8 == 0, "q/k/v layout");
+  TORCH_CHECK(k_tiles_f.dim() == 2 && k_tiles_f.size(1) == 5 && blocks_f.dim() == 2 && blocks_f.size(1) == 4 &&
+                  k_tiles_f.is_contiguous() && blocks_f.is_contiguous(), "fused schedule layout");
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t nq_pad = (q.size(1) + 127) / 128 * 128;
+  auto dq = torch::empty({q.size(0), q.size(1), q.size(2), 128}, q.options());
+  auto dk = torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
+  Tensor dv = dv_out.has_value() ? *dv_out : torch::zeros({k.size(0), k.size(1), k.size(2), 128}, k.options());
+  TORCH_CHECK(dv.sizes() == k.sizes() && dv.stride(3) == 1 && dv.stride(2) == 128, "dv_out layout");
+  auto delta = torch::empty({q.size(0), q.size(2), q.size(1)}, q.options().dtype(torch::kFloat32));
+  auto dq_acc = torch::zeros({q.size(0), nq_pad, q.size(2), 128}, q.options().dtype(torch::kFloat32));
+  auto turns = torch::zeros({1 + q.size(0) * q.size(2) * (nq_pad / 128)}, q.options().dtype(torch::kInt32));
+  agb::AttnBwdArgs b{};
+  agb::AttnArgs& a = b.fwd;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.out = out.data_ptr(); a.lse = lse.data_ptr<float>();
+  a.nq = q.size(1); a.nk = k.size(1); a.batch = q.size(0);
+  a.q_row_stride = q.stride(1); a.q_batch_stride = q.stride(0);
+  a.kv_row_stride = k.stride(1); a.kv_batch_stride = k.stride(0);
+  a.v_row_stride = v.stride(1); a.v_batch_stride = v.stride(0);
+  if (text_k.has_value()) {
+    a.text_k = text_k->data_ptr(); a.text_v = text_v->data_ptr();
+    a.text_len = text_k->size(1);
+    a.text_row_stride = text_k->stride(1); a.text_batch_stride = text_k->stride(0);
+  }
+  if (text_valid.has_value()) a.text_valid = text_valid->data_ptr<int>();
+  a.hq = int(q.size(2)); a.hkv = int(k.size(2));
+  a.scale = float(scale);
+  a.status = status_word(q.device().index()).data_ptr<int>();
+  b.grad_out = grad.data_ptr();
+  b.dq = dq.data_ptr(); b.dk = dk.data_ptr(); b.dv = dv.data_ptr();
+  b.dv_row_stride = dv.stride(1); b.dv_batch_stride = dv.stride(0);
+  b.delta = delta.data_ptr<float>();
+  b.num_k_tiles = int(k_tiles_f.size(0));
+  check(agb::attention_bwd_fused(b, k_tiles_f.data_ptr<int>(), blocks_f.data_ptr<int>(),
+                                 dq_acc.data_ptr<float>(), turns.data_ptr<int>(), nq_pad, stream_of(q)),
+        "attention_bwd_fused");
+  return {dq, dk, dv};
+}
+
 // Stride-1 convolution of a channels-last volume: x [B, Tin, H, W, Cin], weight
 // [Cout, kt * kh * kw, Cin] -> [B, Tin - kt + 1, H, W, Cout] (+ bias [Cout], + residual like out,
 // then ReLU when asked); bf16 or fp16 throughout.
@@ -782,6 +832,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rf_combine", &rf_combine);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
+  m.def("attn_bwd_fused", &attn_bwd_fused);
   m.def("relocate", &relocate);
   m.def("zero_reduce", &zero_reduce);
   m.def("zero_adam", &zero_adam);

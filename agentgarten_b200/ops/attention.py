@@ -109,6 +109,12 @@ class AttentionSchedule:
     with source 0 = text (valid length per sample), 1 = visual, 2 = visual under a causal
     mask against the chunk.  ``k_tiles[t] = (k_row, rows, first_reader, readers, causal)``
     and ``q_lists[r] = (q_row, q_len)`` are the transposed lists used by the dK/dV pass.
+
+    ``fused_tiles[t] = (k_row, rows, first_block, blocks, source)`` and ``fused_blocks[i] =
+    (q_block_row, lo, hi, turn)`` describe the one-pass backward: key tiles (text tiles first,
+    source 0) in the order in which they add to dQ, and for each tile the blocks of 128 query rows
+    (aligned to multiples of 128) that see it, with the columns ``[lo, hi)`` of the block that
+    do and the tile's turn among all tiles that add to that block.  None for causal schedules.
     """
 
     q_tiles: torch.Tensor
@@ -118,6 +124,8 @@ class AttentionSchedule:
     total_q: int
     total_k: int
     text_len: int
+    fused_tiles: torch.Tensor | None = None
+    fused_blocks: torch.Tensor | None = None
 
 
 _schedule_cache: dict = {}
@@ -161,13 +169,54 @@ def build_schedule(q_sizes: list[int], k_sizes: list[int], plan: list[list[int]]
         data = torch.tensor(rows or [[0] * width], dtype=torch.int32).reshape(-1, width)
         return data.to(device)
 
+    fused_tiles, fused_blocks = (None, None) if causal else _fused_lists(readers, k_sizes, k_start, text_len, q_row)
     schedule = AttentionSchedule(
         q_tiles=tensor(q_tiles, 5), entries=tensor(entries, 3), k_tiles=tensor(k_tiles, 5),
-        q_lists=tensor(q_lists, 2), total_q=q_row, total_k=k_start[-1], text_len=text_len)
+        q_lists=tensor(q_lists, 2), total_q=q_row, total_k=k_start[-1], text_len=text_len,
+        fused_tiles=None if fused_tiles is None else tensor(fused_tiles, 5),
+        fused_blocks=None if fused_blocks is None else tensor(fused_blocks, 4))
     if len(_schedule_cache) > 256:
         _schedule_cache.clear()
     _schedule_cache[key] = schedule
     return schedule
+
+
+def _fused_lists(readers, k_sizes, k_start, text_len: int, total_q: int):
+    """Work lists of the one-pass backward (see ``AttentionSchedule``)."""
+    taken = [0] * (-(-total_q // TILE))          # turns handed out so far, per query block
+    tiles, blocks = [], []
+
+    def add_tile(k_row, rows, ranges, source):
+        first = len(blocks)
+        for q0, length in ranges:
+            for block in range(q0 // TILE, (q0 + length - 1) // TILE + 1):
+                lo = max(q0, block * TILE) - block * TILE
+                hi = min(q0 + length, (block + 1) * TILE) - block * TILE
+                blocks.append((block * TILE, lo, hi, taken[block]))
+                taken[block] += 1
+        if len(blocks) > first:
+            tiles.append((k_row, rows, first, len(blocks) - first, source))
+
+    def merged(ranges):
+        out = []
+        for q0, length in sorted(ranges):
+            if out and out[-1][0] + out[-1][1] == q0:
+                out[-1] = (out[-1][0], out[-1][1] + length)
+            else:
+                out.append((q0, length))
+        return out
+
+    if total_q == 0:
+        return [], []
+    for offset in range(0, text_len, TILE):
+        add_tile(offset, min(TILE, text_len - offset), [(0, total_q)], 0)
+    for j, size in enumerate(k_sizes):
+        ranges = merged(readers[j])
+        if not ranges:
+            continue
+        for offset in range(0, size, TILE):
+            add_tile(k_start[j] + offset, min(TILE, size - offset), ranges, 1)
+    return tiles, blocks
 
 
 def _text_mask(text_valid, text_len: int, visual: int, device) -> torch.Tensor:

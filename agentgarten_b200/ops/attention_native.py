@@ -2,6 +2,8 @@
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import native, reference
@@ -12,6 +14,18 @@ __all__ = ["dense", "jvp_dense", "planned"]
 
 def _cat(chunks: list[torch.Tensor]) -> torch.Tensor:
     return chunks[0].contiguous() if len(chunks) == 1 else torch.cat(chunks, dim=1)
+
+
+def segment_backward(C, grad, q, k, v, out, lse, text_k, text_v, text_valid, schedule, scale, dv_out):
+    """(dq, dk, dv) of segment attention from the dQ and dK/dV kernels; ``AGB200_ATTN_BWD=fused``
+    selects the one-pass kernel (``csrc/attention_bwd_fused.cu``) where the schedule has its work
+    lists.  The one-pass form gives the same gradients bit-reproducibly but is the slower of the
+    two today (6.2 against 3.5 ms at 8192 tokens), so it is not the default."""
+    if schedule.fused_tiles is not None and os.environ.get("AGB200_ATTN_BWD", "split") == "fused":
+        return C.attn_bwd_fused(grad, q, k, v, out, lse, text_k, text_v, text_valid,
+                                schedule.fused_tiles, schedule.fused_blocks, scale, dv_out)
+    return C.attn_bwd(grad, q, k, v, out, lse, text_k, text_v, text_valid, schedule.q_tiles,
+                      schedule.entries, schedule.k_tiles, schedule.q_lists, scale, dv_out)
 
 
 class _SegmentAttention(torch.autograd.Function):
@@ -33,9 +47,8 @@ class _SegmentAttention(torch.autograd.Function):
         q, k, v, out, lse, *text = ctx.saved_tensors
         text_k, text_v, text_valid = text if ctx.has_text else (None, None, None)
         C = native.ext()
-        dq, dk, dv = C.attn_bwd(grad.contiguous(), q, k, v, out, lse, text_k, text_v, text_valid,
-                                ctx.schedule.q_tiles, ctx.schedule.entries,
-                                ctx.schedule.k_tiles, ctx.schedule.q_lists, ctx.scale, None)
+        dq, dk, dv = segment_backward(C, grad.contiguous(), q, k, v, out, lse, text_k, text_v, text_valid,
+                              ctx.schedule, ctx.scale, None)
         native.count(3)
         return dq, dk, dv, None, None, None, None, None
 
@@ -119,6 +132,10 @@ def dense(q, k, v, causal: bool = False):
             out, _ = native.ext().attn_fwd(q, k, v, None, None, None, q_tiles, entries,
                                            q.shape[-1] ** -0.5, splits)
             return out
+    if causal and needs_grad:
+        # The dK/dV kernel has no per-element causal mask (the frozen text tower is the only
+        # causal caller): a text tower that is being trained differentiates the PyTorch formula.
+        return reference.attention(q, k, v, causal=True)
     schedule = build_schedule([q.shape[1]], [k.shape[1]], [[0]], 0, q.device, causal=causal)
     return _SegmentAttention.apply(q, k, v, None, None, None, schedule, q.shape[-1] ** -0.5)
 

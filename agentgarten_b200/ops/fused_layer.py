@@ -41,6 +41,7 @@ from agentgarten_b200.utils.trace import span
 
 from . import native
 from .attention import build_schedule
+from .attention_native import segment_backward as attention_backward
 
 __all__ = ["eligible", "keep_policy", "run"]
 
@@ -275,9 +276,8 @@ class _Layer(torch.autograd.Function):
             dqkv = torch.empty(b, n, wqkv.shape[0], device=x.device, dtype=x.dtype)
             dv = dqkv[..., split[1]:].unflatten(-1, (kv_heads, 128))
             dv.zero_()
-            dq, dk, _ = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
-                                   schedule.q_tiles, schedule.entries, schedule.k_tiles,
-                                   schedule.q_lists, 128 ** -0.5, dv)
+            dq, dk, _ = attention_backward(C, dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
+                                           schedule, 128 ** -0.5, dv)
             del dattn, q, k, v
             _, dnq = C.head_norm_rope_bwd(dq, q_lin, nq, cos, sin, rq,
                                           dqkv[..., :split[0]].unflatten(-1, (heads, 128)))
@@ -289,9 +289,8 @@ class _Layer(torch.autograd.Function):
             dn1 = _gemm(dqkv, wqkv, trans_b=False)
             del dqkv
         else:
-            dq, dk, dv = C.attn_bwd(dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
-                                    schedule.q_tiles, schedule.entries, schedule.k_tiles,
-                                    schedule.q_lists, 128 ** -0.5, None)
+            dq, dk, dv = attention_backward(C, dattn, q, k, v, attn, lse, text_k, text_v, text_valid,
+                                            schedule, 128 ** -0.5, None)
             del dattn, q, k, v
             dq_lin, dnq = C.head_norm_rope_bwd(dq, q_lin, nq, cos, sin, rq, None)
             dk_lin, dnk = C.head_norm_rope_bwd(dk, k_lin, nk, cos, sin, rk, None)

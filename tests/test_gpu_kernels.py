@@ -244,7 +244,34 @@ def test_attention_chunk_invariance():
     assert torch.equal(both[1], alone[0])
 
 
-def test_attention_backward_dense():
+@pytest.fixture(params=["fused", "split"])
+def backward_form(request, monkeypatch):
+    """Both forms of the attention backward: one pass over the scores, or the dQ and dK/dV kernels."""
+    monkeypatch.setenv("AGB200_ATTN_BWD", request.param)
+    return request.param
+
+
+def test_one_pass_backward_is_bit_reproducible_and_matches_the_two_kernel_form(monkeypatch):
+    """Many key tiles add to every query block (the order is fixed by the turn counters): two runs
+    agree bit for bit, and the result agrees with the two-kernel form to bf16 rounding."""
+    q, k, v = _attention_inputs(2, 1000, 1210, 8, 2, 31)
+    q, k, v = (t.requires_grad_(True) for t in (q, k, v))
+    grad = torch.randn(2, 1000, 8, 128, device=DEV, dtype=torch.bfloat16)
+
+    def run(form):
+        monkeypatch.setenv("AGB200_ATTN_BWD", form)
+        out = ops.attention(q, k, v)
+        return torch.autograd.grad(out, (q, k, v), grad)
+
+    first, second, split = run("fused"), run("fused"), run("split")
+    _status_ok()
+    for a, b in zip(first, second):
+        assert torch.equal(a, b)
+    for a, b in zip(first, split):
+        assert _rel(a, b) < 1e-2
+
+
+def test_attention_backward_dense(backward_form):
     q, k, v = _attention_inputs(2, 300, 420, 4, 2, 20)
     q, k, v = (t.requires_grad_(True) for t in (q, k, v))
     out = ops.attention(q, k, v)
@@ -258,7 +285,7 @@ def test_attention_backward_dense():
     assert _rel(v.grad, vr.grad) < 2e-2
 
 
-def test_attention_backward_planned_with_text():
+def test_attention_backward_planned_with_text(backward_form):
     b, hq, hkv = 2, 4, 2
     sizes = [130, 260, 96]
     g = torch.Generator(device=DEV).manual_seed(21)
@@ -580,7 +607,7 @@ def test_head_norm_rope_reads_a_column_block_in_place():
 
 
 @pytest.mark.parametrize("hq,hkv", [(3, 3), (6, 2), (2, 1)])
-def test_attention_forward_backward_with_odd_and_even_head_groups(hq, hkv):
+def test_attention_forward_backward_with_odd_and_even_head_groups(hq, hkv, backward_form):
     """An odd number of query heads per KV head runs one head per forward CTA, an even one two."""
     torch.manual_seed(hq * 10 + hkv)
     q = torch.randn(2, 200, hq, 128, device=DEV).bfloat16().requires_grad_()

@@ -131,3 +131,37 @@ def test_adaln_operators_fall_back_to_the_operator_sequence():
     x.requires_grad_()
     ops.norm_modulate(x, weight, scale, shift, 1e-6).sum().backward()
     assert x.grad is not None and torch.isfinite(x.grad).all()
+
+
+def test_one_pass_backward_work_lists_cover_every_reader_once_and_number_the_turns():
+    """Every (key tile, visible query row) appears in exactly one block entry, blocks are aligned
+    to 128 rows, and the turns of a block count up from zero in tile order."""
+    import collections
+
+    from agentgarten_b200.ops.attention import build_schedule
+
+    sizes = [300, 200, 390]
+    plan = [[0], [0, 1], [0, 2]]
+    schedule = build_schedule(sizes, sizes, plan, 130, torch.device("cpu"))
+    tiles, blocks = schedule.fused_tiles.tolist(), schedule.fused_blocks.tolist()
+    starts = [0, 300, 500, 890]
+    turns = collections.defaultdict(list)
+    for k_row, rows, first, count, source in tiles:
+        seen = set()
+        for q_block, lo, hi, turn in blocks[first:first + count]:
+            assert q_block % 128 == 0 and 0 <= lo < hi <= 128
+            turns[q_block].append(turn)
+            rows_seen = set(range(q_block + lo, q_block + hi))
+            assert not (rows_seen & seen)
+            seen |= rows_seen
+        if source == 0:
+            want = set(range(890))
+        else:
+            chunk = max(j for j in range(3) if starts[j] <= k_row)
+            want = {r for c, visible in enumerate(plan) if chunk in visible
+                    for r in range(starts[c], starts[c + 1])}
+        assert seen == want, (k_row, source)
+    assert [t[4] for t in tiles[:2]] == [0, 0] and all(t[4] == 1 for t in tiles[2:])
+    for q_block, taken in turns.items():
+        assert taken == list(range(len(taken))), q_block
+    assert build_schedule([200], [200], [[0]], 0, torch.device("cpu"), causal=True).fused_tiles is None
