@@ -69,6 +69,7 @@ struct DqParams {
   const float* delta;  // [B, Hq, NQ]
   __nv_bfloat16* dq;   // [B, NQ, Hq, 128]
   int nq, hq, group;
+  int nk, text_len;    // extents the work lists are checked against
   float scale, scale_log2;
   int* status;
 };
@@ -122,9 +123,12 @@ attn_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(&s_full[i], 1);
     }
     mbar_fence_init();
-    int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
+    int n = rows_inside(q_row, q_rows, p.nq, ATT_BM) && qt[2] >= 0 && qt[3] >= 0
+                ? build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles, p.nk,
+                                  p.text_len)
+                : -2;
     if (n < 0) {
-      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+      if (p.status) atomicCAS(p.status, 0, n == -2 ? kBadIndex : kBadArgument);
       n = 0;
     }
     *n_tiles_smem = n;
@@ -428,18 +432,23 @@ attn_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_fence_init();
     int n = 0;
     bool overflow = false;
-    for (int g = 0; g < p.group && !overflow; ++g) {
+    bool inside = rows_inside(k_row, k_rows, p.nk, 128) && kt[2] >= 0 && kt[3] >= 0;
+    for (int g = 0; g < p.group && !overflow && inside; ++g) {
       const int head = kv_head * p.group + g;
       for (int r = kt[2]; r < kt[2] + kt[3] && !overflow; ++r) {
         const int q0 = p.q_lists[2 * r], len = p.q_lists[2 * r + 1];
+        if (q0 < 0 || len < 0 || int64_t(q0) + len > p.nq) {
+          inside = false;
+          break;
+        }
         for (int off = 0; off < len; off += DKV_BQ) {
           if (n >= DKV_MAX_ITEMS) { overflow = true; break; }
           items[n++] = make_int2(q0 + off, min(DKV_BQ, len - off) | (head << 8));
         }
       }
     }
-    if (overflow) {
-      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+    if (overflow || !inside) {
+      if (p.status) atomicCAS(p.status, 0, inside ? kBadArgument : kBadIndex);
       n = 0;
     }
     *n_items_smem = n;
@@ -736,6 +745,7 @@ cudaError_t attention_bwd(const AttnBwdArgs& b, cudaStream_t stream) {
     p.q_tiles = a.q_tiles; p.entries = a.entries; p.text_valid = a.text_valid;
     p.lse = a.lse; p.delta = b.delta; p.dq = static_cast<__nv_bfloat16*>(b.dq);
     p.nq = int(a.nq); p.hq = a.hq; p.group = a.hq / a.hkv;
+    p.nk = int(a.nk); p.text_len = int(a.text_len);
     p.scale = a.scale; p.scale_log2 = scale_log2; p.status = a.status;
     dim3 grid(a.num_q_tiles, a.hq, unsigned(a.batch));
     attn_dq_kernel<<<grid, DQ_THREADS, DQ_SMEM, stream>>>(tq, tdo, tkt, tvt, tk, tv, p);

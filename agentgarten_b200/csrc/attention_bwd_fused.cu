@@ -56,7 +56,7 @@ struct FusedParams {
   int* turns;          // [B, Hq, nq_pad / 128] counters, zeroed by the caller; turns[-1] is the ticket
   int* ticket;
   int64_t dv_row_stride, dv_batch_stride;
-  int nq, nq_pad, nk, hq, hkv, group, batch_count;
+  int nq, nq_pad, nk, text_len, hq, hkv, group, batch_count;
   float scale, scale_log2;
   int* status;
 };
@@ -155,15 +155,25 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const bool text = kt[4] == 0;
   int k_valid = k_rows;
   if (text && p.text_valid) k_valid = max(0, min(k_rows, p.text_valid[batch] - k_row));
+  for (int i = threadIdx.x; i < min(max(kt[3], 0), FUSED_MAX_BLOCKS); i += FUSED_THREADS) {
+    blocks[i] = p.blocks[max(kt[2], 0) + i];
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     int n = kt[3];
-    if (n > FUSED_MAX_BLOCKS) {
-      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+    // the entries this CTA is about to follow, against the extents of its tensors
+    bool inside = rows_inside(k_row, k_rows, text ? p.text_len : p.nk, 128) && kt[2] >= 0 && n >= 0;
+    for (int i = 0; i < min(n, FUSED_MAX_BLOCKS) && inside; ++i) {
+      const int4 blk = blocks[i];
+      inside = blk.x >= 0 && blk.x % FUSED_BQ == 0 && blk.x < p.nq_pad && blk.y >= 0 && blk.y < blk.z &&
+               blk.z <= FUSED_BQ && blk.w >= 0;
+    }
+    if (n > FUSED_MAX_BLOCKS || !inside) {
+      if (p.status) atomicCAS(p.status, 0, inside ? kBadArgument : kBadIndex);
       n = 0;
     }
     *n_blocks_smem = n;
   }
-  for (int i = threadIdx.x; i < min(kt[3], FUSED_MAX_BLOCKS); i += FUSED_THREADS) blocks[i] = p.blocks[kt[2] + i];
   __syncthreads();
   const uint32_t tmem_base = *tmem_slot;
   const int n_blocks = *n_blocks_smem;
@@ -599,6 +609,7 @@ cudaError_t attention_bwd_fused(const AttnBwdArgs& b, const int* k_tiles, const 
     p.nq = int(a.nq);
     p.nq_pad = int(nq_pad);
     p.nk = int(a.nk);
+    p.text_len = int(a.text_len);
     p.hq = a.hq;
     p.hkv = a.hkv;
     p.group = a.hq / a.hkv;

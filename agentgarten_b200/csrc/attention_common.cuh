@@ -29,16 +29,28 @@ struct KeyTile {
   int causal0;  // -1: no causal mask; else key index (segment-local) of the tile's first key
 };
 
+// The work lists come from the host.  Every kernel checks the entries it is about to follow
+// against the extents of its tensors before the first access (one thread, a few comparisons
+// per CTA) and, instead of following a bad one, records kBadIndex and does nothing.
+__device__ __forceinline__ bool rows_inside(int row, int rows, int64_t extent, int most) {
+  return row >= 0 && rows >= 1 && rows <= most && int64_t(row) + rows <= extent;
+}
+
 // Expands the segment entries of one query tile into a list of key tiles in shared memory.
-// Called by one thread.  Returns the tile count, or -1 when the list would overflow.
+// Called by one thread.  Returns the tile count, -1 when the list would overflow, -2 when an
+// entry does not lie inside its key tensor (nk visual keys, text_len text keys).
 __device__ inline int build_key_tiles(const int* __restrict__ entries, int first, int count,
                                       const int* __restrict__ text_valid, int batch, int q_local,
-                                      int q_rows, KeyTile* out) {
+                                      int q_rows, KeyTile* out, int64_t nk, int64_t text_len) {
   int n = 0;
   for (int e = first; e < first + count; ++e) {
     const int source = entries[3 * e + 0];
     const int k_row = entries[3 * e + 1];
     int len = entries[3 * e + 2];
+    if (source < 0 || source > 2 || k_row < 0 || len < 0 ||
+        int64_t(k_row) + len > (source == 0 ? text_len : nk)) {
+      return -2;
+    }
     if (source == 0 && text_valid) len = min(len, text_valid[batch]);
     const bool causal = source == 2;
     if (causal) len = min(len, q_local + q_rows);  // keys past the last query row are masked

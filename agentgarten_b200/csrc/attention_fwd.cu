@@ -43,6 +43,7 @@ struct FwdParams {
   __nv_bfloat16* out;     // [B, NQ, Hq, 128]
   float* lse;             // [B, Hq, NQ] natural-log LSE
   int nq, hq, group;      // group = Hq / Hkv
+  int nk, text_len;       // extents the work lists are checked against
   int heads_per_cta;      // 2 when group is even, else 1
   int base_tiles;         // query tiles of one key split: tile t belongs to split t / base_tiles
   int out_rows;           // rows of out / lse per sample (= splits * nq); split s writes rows s*nq + q
@@ -98,9 +99,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&o_done[i], 1);
     }
     mbar_fence_init();
-    int n = build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles);
+    int n = rows_inside(q_row, q_rows, p.nq, ATT_BM) && qt[2] >= 0 && qt[3] >= 0
+                ? build_key_tiles(p.entries, qt[2], qt[3], p.text_valid, batch, q_local, q_rows, tiles, p.nk,
+                                  p.text_len)
+                : -2;
     if (n < 0) {
-      if (p.status) atomicCAS(p.status, 0, kBadArgument);
+      if (p.status) atomicCAS(p.status, 0, n == -2 ? kBadIndex : kBadArgument);
       n = 0;
     }
     *n_tiles_smem = n;
@@ -380,6 +384,8 @@ cudaError_t attention_fwd(const AttnArgs& a, cudaStream_t stream) {
   p.out = static_cast<__nv_bfloat16*>(a.out);
   p.lse = a.lse;
   p.nq = int(a.nq);
+  p.nk = int(a.nk);
+  p.text_len = int(a.text_len);
   p.hq = a.hq;
   p.group = a.hq / a.hkv;
   p.heads_per_cta = (p.group % 2 == 0) ? 2 : 1;

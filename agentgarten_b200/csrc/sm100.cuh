@@ -23,6 +23,7 @@ enum : int {
   kTimeoutSoftmax = 4,
   kTimeoutPeer = 5,       // a flag owned by another GPU never arrived
   kBadArgument = 6,
+  kBadIndex = 7,          // a work-list entry pointed outside its tensor: the CTA skipped its work
 };
 
 // Upper bound of one wait, in nanoseconds of %globaltimer.

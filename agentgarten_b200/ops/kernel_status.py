@@ -26,6 +26,8 @@ CODES = {
     3: "kTimeoutEpilogue (an epilogue waited too long for an accumulator)",
     4: "kTimeoutSoftmax (a softmax warp waited too long)",
     5: "kTimeoutPeer (a flag owned by another GPU never arrived)",
+    6: "kBadArgument (a work list does not fit the kernel's tables)",
+    7: "kBadIndex (a work-list entry pointed outside its tensor; the CTA skipped its work)",
 }
 
 _injected: int | None = None

@@ -37,6 +37,9 @@ class _Link:
         self.group, self.device, self.half_bytes = group, device, half_bytes
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.buffer = symm.empty(2 * half_bytes, dtype=torch.uint8, device=device)
+        from .debug import poison
+
+        poison(self.buffer)   # under AGB200_POISON=1: a block nobody stored reads as NaN
         self.counter = symm.empty(4, dtype=torch.int32, device=device)
         self.counter.zero_()
         self._handles = [symm.rendezvous(self.buffer, group=group), symm.rendezvous(self.counter, group=group)]

@@ -111,14 +111,23 @@ class TensorParallelServing:
                 "norm_mid": layer.post_attention_layernorm_moe_gen.weight,
             })
 
-    def _symmetric(self, numel: int, dtype: torch.dtype) -> tuple[torch.Tensor, list[int]]:
+    def _symmetric(self, numel: int, dtype: torch.dtype, data: bool = False) -> tuple[torch.Tensor, list[int]]:
+        """A buffer every rank can address.  Counters start at zero; ``data`` buffers (rows that
+        peers push) start at zero too, or as NaN under ``AGB200_POISON=1`` so that a consumer that
+        reads a row nobody pushed produces non-finite values instead of plausible ones."""
+        from .debug import poison
+
         if self.world == 1:
             buf = torch.zeros(numel, dtype=dtype, device=self.device)
+            if data:
+                poison(buf)
             return buf, [buf.data_ptr()]
         import torch.distributed._symmetric_memory as symm
 
         buf = symm.empty(numel, dtype=dtype, device=self.device)
         buf.zero_()
+        if data:
+            poison(buf)
         handle = symm.rendezvous(buf, group=self.group if self.group is not None else dist.group.WORLD)
         self._handles.append(handle)
         return buf, [int(p) for p in handle.buffer_ptrs]
@@ -126,8 +135,9 @@ class TensorParallelServing:
     def _allocate(self) -> None:
         self._handles: list = []
         h = self.hidden
-        self.x, self.x_ptrs = self._symmetric(self.max_tiles * _TILE * h, torch.bfloat16)
-        self.slots, self.slot_ptrs = self._symmetric(self.world * self.max_owned * _TILE * h, torch.bfloat16)
+        self.x, self.x_ptrs = self._symmetric(self.max_tiles * _TILE * h, torch.bfloat16, data=True)
+        self.slots, self.slot_ptrs = self._symmetric(self.world * self.max_owned * _TILE * h, torch.bfloat16,
+                                                     data=True)
         counters, pointers = self._symmetric(self.max_tiles + self.max_owned + 1, torch.int32)
         self.ready = counters[: self.max_tiles]
         self.arrive = counters[self.max_tiles: self.max_tiles + self.max_owned]

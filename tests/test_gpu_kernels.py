@@ -416,6 +416,31 @@ def test_a_peer_that_never_arrives_ends_the_wait_with_a_status():
     assert seen.tolist() == [128, 128]
 
 
+def test_a_work_list_entry_outside_its_tensor_is_refused_by_the_kernel():
+    """The attention kernels check the entries of their host-built work lists against the
+    extents of their tensors before the first access: a key segment that reaches past the keys
+    makes the CTAs record kBadIndex and skip their work (no access through the bad entry); the
+    context stays usable and the same call with a sound list runs."""
+    from agentgarten_b200.ops.attention import build_schedule
+
+    C = native.ext()
+    torch.cuda.synchronize()
+    status = C.status(0)
+    status.zero_()
+    q, k, v = _attention_inputs(1, 256, 256, 2, 1, 40)
+    schedule = build_schedule([256], [256], [[0]], 0, q.device)
+    entries = schedule.entries.clone()
+    entries[0, 2] = 384              # 384 keys claimed, 256 exist (a tiled load past them would read zeros)
+    C.attn_fwd(q, k, v, None, None, None, schedule.q_tiles, entries, 128 ** -0.5, 1)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 7   # kBadIndex
+    status.zero_()
+    out, _ = C.attn_fwd(q, k, v, None, None, None, schedule.q_tiles, schedule.entries, 128 ** -0.5, 1)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert _rel(out, reference.attention(q.float(), k.float(), v.float())) < 1e-2
+
+
 @pytest.mark.parametrize("nq,nk,hq,hkv", [(300, 5000, 4, 1), (128, 12000, 8, 2), (3120, 20000, 4, 1)])
 def test_split_key_attention_matches_reference(nq, nk, hq, hkv):
     from agentgarten_b200.ops import attention_native

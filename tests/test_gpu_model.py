@@ -257,8 +257,13 @@ def test_tensor_parallel_run_with_ragged_row_counts(tokens, reduce_rows):
     assert got.shape == want.shape and rel(got, want) < 2e-2, rel(got, want)
 
 
-def test_tensor_parallel_kernels_on_one_rank_match_the_layer_path():
+def test_tensor_parallel_kernels_on_one_rank_match_the_layer_path(monkeypatch):
+    """Runs with the peer-written buffers poisoned (NaN until a producer stores into them): the
+    outputs stay finite and equal to the layer path, so no consumer reads a row before it was
+    pushed."""
     from agentgarten_b200.networks.cosmos3.streaming import StreamPolicy
+
+    monkeypatch.setenv("AGB200_POISON", "1")
 
     config = _config()
     net = tiny_network(config, device="cpu", seed=0).to(DEV, torch.bfloat16).eval()

@@ -302,3 +302,15 @@ def test_parallel_config_refuses_what_the_engine_cannot_honour():
     tower = torch.nn.Sequential(torch.nn.Linear(8, 8, bias=False), torch.nn.Linear(8, 4, bias=False))
     tower[1].requires_grad_(False)
     assert replicated_parameter_bytes(tower) == 2 * (64 * 2) + 32 * 2
+
+
+def test_poison_fills_data_buffers_only_when_asked(monkeypatch):
+    from agentgarten_b200.parallel import debug
+
+    monkeypatch.delenv("AGB200_POISON", raising=False)
+    rows = torch.zeros(4, 8, dtype=torch.bfloat16)
+    assert debug.poison(rows) is rows and rows.abs().sum() == 0
+    monkeypatch.setenv("AGB200_POISON", "1")
+    assert torch.isnan(debug.poison(rows)).all()
+    assert torch.isnan(debug.poison(torch.zeros(3, dtype=torch.float32))).all()
+    assert debug.poison(torch.zeros(0)).numel() == 0
