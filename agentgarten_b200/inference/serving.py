@@ -37,6 +37,8 @@ def prepare_serving(network: torch.nn.Module, *, dynamic: bool = False, cuda_gra
     on_cuda = next(network.parameters()).is_cuda
     network._serving_options = {"cuda_graphs": bool(cuda_graphs) and on_cuda}
     network._tensor_parallel = None
+    if on_cuda:
+        _adjoin_projections(network)
     if tensor_parallel is not None and tensor_parallel is not False:
         if not on_cuda:
             raise ValueError("tensor-parallel serving needs CUDA devices")
@@ -45,6 +47,24 @@ def prepare_serving(network: torch.nn.Module, *, dynamic: bool = False, cuda_gra
         group = None if tensor_parallel is True else tensor_parallel
         network._tensor_parallel = TensorParallelServing(network, group, max_tokens=max_tokens)
     return network
+
+
+def _adjoin_projections(network: torch.nn.Module) -> None:
+    """Lay the q | k | v and the gate | up weights of every layer out back to back (a one-time
+    copy, one layer at a time), so that a served step runs each group as one GEMM: at the 3120
+    rows of a streamed block the k and v projections alone fill less than a wave of SMs."""
+    from agentgarten_b200 import ops
+
+    for module in network.modules():
+        groups = []
+        if callable(getattr(module, "parts", None)):
+            groups.append(module.parts()[:3])
+        if all(hasattr(module, name) for name in ("gate_proj", "up_proj", "down_proj")):
+            groups.append((module.gate_proj, module.up_proj))
+        for group in groups:
+            if all(isinstance(m, torch.nn.Linear) and m.bias is None and m.weight.dim() == 2 for m in group) \
+                    and len({m.weight.shape[1] for m in group}) == 1:
+                ops.adjoin([m.weight for m in group])
 
 
 def release_serving(network: torch.nn.Module) -> torch.nn.Module:

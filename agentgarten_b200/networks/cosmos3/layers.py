@@ -113,6 +113,9 @@ class Cosmos3MLP(nn.Module):
         self.down_proj = Linear(config.intermediate_size, config.hidden_size, bias=False)
 
     def forward(self, value: torch.Tensor) -> torch.Tensor:
+        both = ops.joint_linear(value, (self.gate_proj, self.up_proj))  # one GEMM where it applies
+        if both is not None:
+            return self.down_proj(ops.silu_mul_pair(both))
         return self.down_proj(ops.silu_mul(self.gate_proj(value), self.up_proj(value)))
 
 
@@ -216,6 +219,14 @@ def _project(hidden, norm, attn: _Projections, heads: int, kv_heads: int, dim: i
     to_q, to_k, to_v, _out, norm_q, norm_k = attn.parts()
     normalized = norm(hidden)
     eps = norm_q.variance_epsilon
+    # one GEMM over q | k | v where the three weights are adjacent in memory and no gradient is
+    # wanted (serving after prepare_serving, frozen towers under the optimizer engine's layout)
+    joint = ops.joint_linear(normalized, (to_q, to_k, to_v))
+    if joint is not None:
+        q_lin, k_lin, value = joint.split((heads * dim, kv_heads * dim, kv_heads * dim), dim=-1)
+        query = ops.head_norm_rope(q_lin.unflatten(-1, (heads, dim)), norm_q.weight, cos, sin, eps)
+        key = ops.head_norm_rope(k_lin.unflatten(-1, (kv_heads, dim)), norm_k.weight, cos, sin, eps)
+        return query, key, value.unflatten(-1, (kv_heads, dim))
     query = ops.head_norm_rope(
         to_q(normalized).view(batch, tokens, heads, dim), norm_q.weight, cos, sin, eps)
     key = ops.head_norm_rope(

@@ -17,7 +17,7 @@ import torch.autograd.forward_ad as fwAD
 
 from . import native, reference
 from .attention import attention, attention_jvp, planned_attention
-from .linear import linear
+from .linear import adjoin, joined, joint_linear, linear
 from .pointwise import (
     gated_residual,
     head_norm_rope,
@@ -28,13 +28,17 @@ from .pointwise import (
     rms_norm_add,
     rotary,
     silu_mul,
+    silu_mul_pair,
 )
 
 __all__ = [
+    "adjoin",
     "attention",
     "attention_jvp",
     "gated_residual",
     "head_norm_rope",
+    "joined",
+    "joint_linear",
     "linear",
     "native",
     "norm_modulate",
@@ -46,4 +50,5 @@ __all__ = [
     "rms_norm_add",
     "rotary",
     "silu_mul",
+    "silu_mul_pair",
 ]

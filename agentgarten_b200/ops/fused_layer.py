@@ -41,6 +41,7 @@ from agentgarten_b200.utils.trace import span
 
 from . import native
 from .attention import build_schedule
+from .linear import joined as _joined
 from .attention_native import segment_backward as attention_backward
 
 __all__ = ["eligible", "keep_policy", "run"]
@@ -111,22 +112,6 @@ def _wgrad(weight: torch.Tensor, grad_rows: torch.Tensor, input_rows: torch.Tens
         _gemm(grad_rows, input_rows, trans_a=True, trans_b=False, out=weight.grad, accumulate=True)
         return None
     return _gemm(grad_rows, input_rows, trans_a=True, trans_b=False)
-
-
-def _joined(parts):
-    """One ``[sum of rows, K]`` view over matrices that lie back to back in one storage, in
-    this order; None when they do not."""
-    first = parts[0]
-    if any(p is None for p in parts):
-        return None
-    at, storage = first.data_ptr(), first.untyped_storage().data_ptr()
-    for p in parts:
-        if (p.dim() != 2 or not p.is_contiguous() or p.shape[1] != first.shape[1] or p.dtype != first.dtype
-                or p.data_ptr() != at or p.untyped_storage().data_ptr() != storage):
-            return None
-        at += p.numel() * p.element_size()
-    rows = sum(p.shape[0] for p in parts)
-    return first.detach().as_strided((rows, first.shape[1]), (first.shape[1], 1))
 
 
 def _wgrad_group(weights, grad_rows: torch.Tensor, input_rows: torch.Tensor):

@@ -18,7 +18,7 @@ import torch.nn.functional as F
 
 from . import native
 
-__all__ = ["gemm", "linear"]
+__all__ = ["adjoin", "gemm", "joined", "joint_linear", "linear"]
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
@@ -88,6 +88,64 @@ class _Linear(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = g2.float().sum(0).to(grad.dtype)
         return dx, dw, db
+
+
+def joined(parts):
+    """One ``[sum of rows, K]`` view over matrices that lie back to back in one storage, in
+    this order (the optimizer engine's flat parameter buffer and ``prepare_serving`` lay q|k|v and
+    gate|up out that way); None when they do not."""
+    first = parts[0]
+    if any(p is None for p in parts):
+        return None
+    at, storage = first.data_ptr(), first.untyped_storage().data_ptr()
+    for p in parts:
+        if (p.dim() != 2 or not p.is_contiguous() or p.shape[1] != first.shape[1] or p.dtype != first.dtype
+                or p.data_ptr() != at or p.untyped_storage().data_ptr() != storage):
+            return None
+        at += p.numel() * p.element_size()
+    rows = sum(p.shape[0] for p in parts)
+    return first.detach().as_strided((rows, first.shape[1]), (first.shape[1], 1))
+
+
+def adjoin(parameters) -> None:
+    """Move the data of 2-D parameters of equal width into one buffer, back to back, so that
+    :func:`joined` finds them (a one-time copy; the old storages are released)."""
+    parameters = list(parameters)
+    if joined([p.data for p in parameters]) is not None:
+        return
+    width = parameters[0].shape[1]
+    assert all(p.dim() == 2 and p.shape[1] == width and p.dtype == parameters[0].dtype for p in parameters)
+    buffer = torch.empty(sum(p.shape[0] for p in parameters), width, dtype=parameters[0].dtype,
+                         device=parameters[0].device)
+    at = 0
+    for p in parameters:
+        view = buffer[at:at + p.shape[0]]
+        view.copy_(p.data)
+        p.data = view
+        at += p.shape[0]
+
+
+def joint_linear(x: torch.Tensor, modules) -> torch.Tensor | None:
+    """``x`` through several bias-free linears as ONE GEMM over their adjacent weights:
+    ``[..., sum of out features]``, or None when that does not apply (weights not adjacent, a
+    bias, gradients or tangents wanted, not the CUDA bf16 path).  An output column is the same
+    K-ordered sum as from one GEMM per weight."""
+    weights = [m.weight for m in modules]
+    if any(m.bias is not None for m in modules) or not native.use(x) or x.shape[-1] % 8:
+        return None
+    if torch.is_grad_enabled() and (x.requires_grad or any(w.requires_grad for w in weights)):
+        return None
+    # plain linears only: a subclass with its own forward (LoRA) must not be bypassed
+    if any(type(m).__name__ != "Linear" for m in modules) or not _gemm_ok(x, weights[0]):
+        return None
+    import torch.autograd.forward_ad as fwAD
+
+    if fwAD.unpack_dual(x).tangent is not None:
+        return None
+    weight = joined(weights)
+    if weight is None:
+        return None
+    return _Linear.apply(x, weight, None)
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:

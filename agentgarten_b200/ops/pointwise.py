@@ -127,10 +127,21 @@ class _HeadNormRope(torch.autograd.Function):
         return dx, dw.to(weight.dtype), None, None, None
 
 
+def _row_strided(value) -> bool:
+    """``[B, N, H, 128]`` dense over (H, 128) with rows at a constant stride: a column slice of a
+    wider matrix, which the kernel reads in place."""
+    return (value.dim() == 4 and value.stride(3) == 1 and value.stride(2) == 128 and value.stride(1) % 8 == 0
+            and (value.shape[0] == 1 or value.stride(0) == value.shape[1] * value.stride(1)))
+
+
 def head_norm_rope(value, weight, cos, sin, eps):
     """Per-head RMSNorm over ``D`` then rotate-half RoPE; ``value`` is ``[B, N, H, D]``."""
     if (native.use(value) and value.shape[-1] == 128 and weight.dtype == value.dtype
             and cos.dtype == value.dtype and _plain(value, weight)):
+        if not (torch.is_grad_enabled() and (value.requires_grad or weight.requires_grad)) and _row_strided(value):
+            native.count()
+            return native.ext().head_norm_rope_fwd(value, weight.contiguous(), cos.contiguous(),
+                                                   sin.contiguous(), float(eps))[0]
         return _HeadNormRope.apply(value, weight, cos, sin, eps)
     return reference.head_norm_rope(value, weight, cos, sin, eps)
 
@@ -158,6 +169,16 @@ def silu_mul(gate, up):
     if native.use(gate) and _plain(gate, up) and gate.numel() % 8 == 0:
         return _SiluMul.apply(gate, up)
     return reference.silu_mul(gate, up)
+
+
+def silu_mul_pair(both):
+    """``silu(gate) * up`` for ``both = [gate | up]`` along the last dimension (the product of a
+    joint gate|up GEMM); no gradient."""
+    width = both.shape[-1] // 2
+    if native.use(both) and both.is_contiguous() and width % 8 == 0 and not both.requires_grad:
+        native.count()
+        return native.ext().silu_mul_pair(both.view(-1, 2 * width)).view(*both.shape[:-1], width)
+    return reference.silu_mul(both[..., :width], both[..., width:])
 
 
 def rf_interpolate(x0, noise, sigma):
