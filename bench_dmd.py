@@ -23,6 +23,13 @@ import json
 import os
 import sys
 
+# The exact R1/R2 pass of a fake-score update runs while that tower's kept activations are
+# alive and needs tens of GB for its forward-mode tangents: the layers keep fewer activations
+# (they recompute instead) so that the pass has room, and the allocator may grow its segments
+# instead of failing on fragmentation.  Both are defaults that the environment can override.
+os.environ.setdefault("AGB200_ACTIVATION_RESERVE_GB", "72")
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
 
 def parse_args() -> argparse.Namespace:
     parser = argparse.ArgumentParser(description=__doc__.split("\n")[0])
