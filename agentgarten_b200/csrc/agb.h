@@ -335,6 +335,15 @@ cudaError_t zero_adam(const ZeroPeers& params, const ZeroPeers& grads, const int
                       const float* hyper, const float* grad_scale, const float* skip_flag,
                       int sm_count, cudaStream_t stream);
 
+// M-RoPE tables: positions fp32 [tokens, 3], inverse fp32 [64], axis int32 [64] -> cos / sin
+// [tokens, 128] (bf16 or fp32), slot j and j + 64 alike.
+cudaError_t rope_tables(const float* positions, const float* inverse, const int* axis, void* cosine, void* sine,
+                        int64_t tokens, bool bf16_out, cudaStream_t stream);
+// [B, C, T, H, W] <-> [B, T, (H/p)(W/p), p*p*C] with the cast between fp32 and bf16 in the same pass.
+cudaError_t patch_layout(const void* src, void* dst, int64_t batch, int64_t channels, int64_t frames,
+                         int64_t height, int64_t width, int patch, bool to_patches, bool src_bf16,
+                         bool dst_bf16, cudaStream_t stream);
+
 // Diagnostic: every SM issues `iterations` x 8 tcgen05.mma (M 128, K 16, `columns` wide) back to
 // back; cycles[0] receives the cycles block 0 needed, or -1 when its bounded wait gave up.
 cudaError_t mma_issue_rate(int columns, bool a_from_tmem, int iterations, int sm_count, long long* cycles,

@@ -165,3 +165,25 @@ def test_one_pass_backward_work_lists_cover_every_reader_once_and_number_the_tur
     for q_block, taken in turns.items():
         assert taken == list(range(len(taken))), q_block
     assert build_schedule([200], [200], [[0]], 0, torch.device("cpu"), causal=True).fused_tiles is None
+
+
+def test_adjoined_weights_form_one_view_and_keep_their_values():
+    """``adjoin`` lays 2-D parameters out back to back without changing them, ``joined`` then finds
+    one matrix over them; parameters in separate storages (or in another order) are not joined, and
+    the joint GEMM never applies on the CPU."""
+    from agentgarten_b200 import ops
+
+    torch.manual_seed(0)
+    q, k, v = (torch.nn.Linear(16, n, bias=False) for n in (32, 8, 8))
+    before = [m.weight.detach().clone() for m in (q, k, v)]
+    assert ops.joined([m.weight for m in (q, k, v)]) is None
+    ops.adjoin([m.weight for m in (q, k, v)])
+    whole = ops.joined([m.weight for m in (q, k, v)])
+    assert whole is not None and whole.shape == (48, 16)
+    assert torch.equal(whole, torch.cat(before))
+    for module, old in zip((q, k, v), before):
+        assert torch.equal(module.weight, old)
+    assert ops.joined([k.weight, q.weight, v.weight]) is None
+    ops.adjoin([m.weight for m in (q, k, v)])            # already adjacent: nothing moves
+    assert ops.joined([m.weight for m in (q, k, v)]).data_ptr() == whole.data_ptr()
+    assert ops.joint_linear(torch.randn(3, 16), (q, k, v)) is None
