@@ -803,6 +803,52 @@ Tensor status(int64_t device) { return status_word(int(device)); }
 
 }  // namespace
 
+// cos / sin tables of the 3-axis RoPE: positions [..., 3] fp32, inverse [64] fp32, axis [64] int32.
+std::tuple<Tensor, Tensor> rope_tables(const Tensor& positions, const Tensor& inverse, const Tensor& axis,
+                                       bool bf16_out) {
+  TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == torch::kFloat32 && positions.is_contiguous() &&
+                  positions.size(-1) == 3, "positions: contiguous fp32 [..., 3]");
+  TORCH_CHECK(inverse.scalar_type() == torch::kFloat32 && inverse.numel() == 64 && inverse.is_contiguous() &&
+                  axis.scalar_type() == torch::kInt32 && axis.numel() == 64 && axis.is_contiguous(),
+              "inverse fp32 [64], axis int32 [64]");
+  c10::cuda::CUDAGuard guard(positions.device());
+  auto shape = positions.sizes().vec();
+  shape.back() = 128;
+  auto options = positions.options().dtype(bf16_out ? torch::kBFloat16 : torch::kFloat32);
+  auto cosine = torch::empty(shape, options), sine = torch::empty(shape, options);
+  check(agb::rope_tables(positions.data_ptr<float>(), inverse.data_ptr<float>(), axis.data_ptr<int>(),
+                         cosine.data_ptr(), sine.data_ptr(), positions.numel() / 3, bf16_out,
+                         stream_of(positions)), "rope_tables");
+  return {cosine, sine};
+}
+
+// [B, C, T, H, W] -> [B, T, (H/p)(W/p), p*p*C] (to_patches) or back, fp32 / bf16 on either side.
+Tensor patch_layout(const Tensor& src, int64_t channels, int64_t height, int64_t width, int64_t patch,
+                    bool to_patches, bool bf16_out) {
+  const auto in = src.scalar_type();
+  TORCH_CHECK(src.is_cuda() && src.is_contiguous() && (in == torch::kFloat32 || in == torch::kBFloat16),
+              "patch_layout: contiguous fp32 or bf16 CUDA tensor");
+  TORCH_CHECK(patch >= 1 && height % patch == 0 && width % patch == 0, "patch does not divide the frame");
+  c10::cuda::CUDAGuard guard(src.device());
+  int64_t batch, frames;
+  Tensor dst;
+  auto options = src.options().dtype(bf16_out ? torch::kBFloat16 : torch::kFloat32);
+  if (to_patches) {
+    TORCH_CHECK(src.dim() == 5 && src.size(1) == channels && src.size(3) == height && src.size(4) == width,
+                "patch_layout: latent is [B, C, T, H, W]");
+    batch = src.size(0); frames = src.size(2);
+    dst = torch::empty({batch, frames, (height / patch) * (width / patch), patch * patch * channels}, options);
+  } else {
+    TORCH_CHECK(src.dim() == 4 && src.size(2) == (height / patch) * (width / patch) &&
+                    src.size(3) == patch * patch * channels, "patch_layout: patches are [B, T, N, p*p*C]");
+    batch = src.size(0); frames = src.size(1);
+    dst = torch::empty({batch, channels, frames, height, width}, options);
+  }
+  check(agb::patch_layout(src.data_ptr(), dst.data_ptr(), batch, channels, frames, height, width, int(patch),
+                          to_patches, in == torch::kBFloat16, bf16_out, stream_of(src)), "patch_layout");
+  return dst;
+}
+
 // Cycles per tcgen05.mma (M 128, K 16) issued back to back; see csrc/mma_rate.cu.
 double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
   const int device = c10::cuda::current_device();
@@ -819,6 +865,8 @@ double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mma_issue_rate", &mma_issue_rate);
+  m.def("rope_tables", &rope_tables);
+  m.def("patch_layout", &patch_layout);
   m.def("gemm", &gemm);
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_add_fwd", &rms_norm_add_fwd);

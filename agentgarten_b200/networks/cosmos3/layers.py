@@ -181,6 +181,15 @@ class Cosmos3RotaryEmbedding(nn.Module):
 
     @torch.no_grad()
     def forward(self, positions: torch.Tensor, dtype: torch.dtype):
+        if positions.is_cuda and dtype in (torch.bfloat16, torch.float32) and self.head_dim == 128 \
+                and ops.native.available():
+            # one kernel: gather the axis, scale, cosine and sine (evaluated in double), cast, duplicate
+            device = positions.device
+            exponent = torch.arange(0, self.head_dim, 2, dtype=torch.float32, device=device)
+            inverse = 1.0 / (self.rope_theta ** (exponent / self.head_dim))
+            ops.native.count()
+            return ops.native.ext().rope_tables(positions.float().contiguous(), inverse,
+                                                self.axis_of_slot(device).int(), dtype == torch.bfloat16)
         angle = self.angles(positions)
         full = torch.cat((angle, angle), dim=-1)
         return full.cos().to(dtype), full.sin().to(dtype)

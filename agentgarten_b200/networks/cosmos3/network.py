@@ -142,17 +142,60 @@ class Cosmos3Condition:
         return replace(self, text=text)
 
 
-def patchify(latent: torch.Tensor, patch_size: int) -> torch.Tensor:
-    """``[B, C, T, H, W]`` → ``[B, T, (H/p)(W/p), p*p*C]`` (patch pixels row-major, C fastest)."""
+class _PatchLayout(torch.autograd.Function):
+    """The two layouts as one gather kernel each, with the cast to ``dtype`` in the same pass; the
+    gradient of one is the other."""
+
+    @staticmethod
+    def forward(ctx, value, channels, height, width, patch, to_patches, dtype):
+        from agentgarten_b200.ops import native
+
+        ctx.args = (channels, height, width, patch, to_patches, value.dtype)
+        native.count()
+        return native.ext().patch_layout(value.contiguous(), channels, height, width, patch, to_patches,
+                                         dtype == torch.bfloat16)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        from agentgarten_b200.ops import native
+
+        channels, height, width, patch, to_patches, dtype = ctx.args
+        native.count()
+        back = native.ext().patch_layout(grad.contiguous(), channels, height, width, patch, not to_patches,
+                                         dtype == torch.bfloat16)
+        return back, None, None, None, None, None, None
+
+
+def _on_kernel(value: torch.Tensor, dtype: torch.dtype) -> bool:
+    import torch.autograd.forward_ad as fwAD
+
+    from agentgarten_b200.ops import native
+
+    both = (torch.float32, torch.bfloat16)
+    return (value.is_cuda and value.dtype in both and dtype in both and native.available()
+            and fwAD.unpack_dual(value).tangent is None)
+
+
+def patchify(latent: torch.Tensor, patch_size: int, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``[B, C, T, H, W]`` → ``[B, T, (H/p)(W/p), p*p*C]`` (patch pixels row-major, C fastest), cast
+    to ``dtype`` (default: unchanged)."""
     height, width = latent.shape[-2:]
     if height % patch_size or width % patch_size:
         raise ValueError(f"latent {height}x{width} is not divisible by patch {patch_size}")
-    return rearrange(latent, "b c t (h p) (w q) -> b t (h w) (p q c)", p=patch_size, q=patch_size)
+    dtype = latent.dtype if dtype is None else dtype
+    if latent.dim() == 5 and _on_kernel(latent, dtype):
+        return _PatchLayout.apply(latent, latent.shape[1], height, width, patch_size, True, dtype)
+    return rearrange(latent.to(dtype), "b c t (h p) (w q) -> b t (h w) (p q c)", p=patch_size, q=patch_size)
 
 
 def unpatchify(patches: torch.Tensor, *, channels: int, grid: tuple[int, int],
-               patch_size: int) -> torch.Tensor:
-    return rearrange(patches, "b t (h w) (p q c) -> b c t (h p) (w q)", h=grid[0], w=grid[1],
+               patch_size: int, dtype: torch.dtype | None = None) -> torch.Tensor:
+    dtype = patches.dtype if dtype is None else dtype
+    if patches.dim() == 4 and _on_kernel(patches, dtype):
+        return _PatchLayout.apply(patches, channels, grid[0] * patch_size, grid[1] * patch_size,
+                                  patch_size, False, dtype)
+    return rearrange(patches.to(dtype), "b t (h w) (p q c) -> b c t (h p) (w q)", h=grid[0], w=grid[1],
                      p=patch_size, q=patch_size, c=channels)
 
 
@@ -279,9 +322,9 @@ class Cosmos3Network(ParallelNetwork):
         """Patch vectors of latent frames; with channel-wise geometry the depth and normal
         patches of the same frames are appended to every vector."""
         patch = self.config.patch_size
-        parts = [patchify(latent.to(self.dtype), patch)]
+        parts = [patchify(latent, patch, self.dtype)]
         if self.config.geometry_mode == "channels":
-            parts += [patchify(control[:, :, start:stop].to(self.dtype), patch)
+            parts += [patchify(control[:, :, start:stop], patch, self.dtype)
                       for control in (condition.depth, condition.normal)]
         return parts[0] if len(parts) == 1 else torch.cat(parts, dim=-1)
 
@@ -324,7 +367,7 @@ class Cosmos3Network(ParallelNetwork):
         rgb_positions = _grid_positions(when, rgb_grid, rgb_grid)
         if config.geometry_mode == "channels":
             return GeometryFrames(None, None, rgb_positions)
-        controls = [patchify(control[:, :, start:stop].to(self.dtype), config.patch_size)
+        controls = [patchify(control[:, :, start:stop], config.patch_size, self.dtype)
                     for control in (condition.depth, condition.normal)]
         # proj_in is affine: the projection of the mean is the mean of the projections
         geometry = self.proj_in(torch.lerp(controls[0], controls[1], 0.5)) + self.geometry_modality_embed
@@ -336,8 +379,8 @@ class Cosmos3Network(ParallelNetwork):
         """RGB hidden states ``[B, T, N, D]`` → latent velocity ``[B, C, T, H, W]`` (≥FP32)."""
         patches = self.proj_out(self.norm_moe_gen(hidden))
         wide = torch.promote_types(patches.dtype, torch.float32)
-        return unpatchify(patches.to(wide), channels=self.config.latent_channels, grid=grid,
-                          patch_size=self.config.patch_size)
+        return unpatchify(patches, channels=self.config.latent_channels, grid=grid,
+                          patch_size=self.config.patch_size, dtype=wide)
 
     def _tokens_per_frame(self, condition, grid) -> int:
         per_frame = grid[0] * grid[1]

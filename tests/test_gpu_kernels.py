@@ -695,3 +695,47 @@ def test_geometry_kernels_match_the_operator_sequence(monkeypatch):
     single = geometry.colorize_depth(depth, scale[:1])
     monkeypatch.undo()
     assert (single - geometry.colorize_depth(depth, scale[:1])).abs().max() < 1e-5
+
+
+def test_rope_table_kernel_matches_the_definition():
+    """cos / sin tables from one kernel against the PyTorch definition (FP32 angle, then cosine
+    and sine): equal after rounding to bf16 except where the FP32 results differ in the last
+    place and straddle a bf16 boundary; FP32 tables within 2e-7."""
+    from agentgarten_b200.networks.cosmos3 import Cosmos3Config
+    from agentgarten_b200.networks.cosmos3.layers import Cosmos3RotaryEmbedding
+
+    rope = Cosmos3RotaryEmbedding(Cosmos3Config(num_hidden_layers=1))
+    g = torch.Generator(device=DEV).manual_seed(2)
+    positions = torch.rand(2, 777, 3, device=DEV, generator=g) * 600
+    before = native.launches()
+    cos32, sin32 = rope(positions, torch.float32)
+    cos16, sin16 = rope(positions, torch.bfloat16)
+    assert native.launches() == before + 2
+    angle = rope.angles(positions)
+    full = torch.cat((angle, angle), dim=-1)
+    assert (cos32 - full.cos()).abs().max() < 2e-7 and (sin32 - full.sin()).abs().max() < 2e-7
+    for got, want in ((cos16, full.cos().bfloat16()), (sin16, full.sin().bfloat16())):
+        assert got.shape == want.shape and (got != want).float().mean() < 1e-3
+        assert (got.float() - want.float()).abs().max() < 1e-2
+
+
+@pytest.mark.parametrize("src,dst", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                     (torch.float32, torch.float32)])
+def test_patch_layout_kernels_match_the_rearrangement(src, dst):
+    from einops import rearrange
+
+    from agentgarten_b200.networks.cosmos3.network import patchify, unpatchify
+
+    g = torch.Generator(device=DEV).manual_seed(3)
+    latent = torch.randn(2, 12, 3, 6, 10, device=DEV, generator=g).to(src).requires_grad_()
+    before = native.launches()
+    patches = patchify(latent, 2, dst)
+    assert native.launches() == before + 1
+    want = rearrange(latent.detach().to(dst), "b c t (h p) (w q) -> b t (h w) (p q c)", p=2, q=2)
+    assert patches.dtype == dst and torch.equal(patches, want)
+    grad = torch.randn(patches.shape, device=DEV, generator=g).to(dst)
+    patches.backward(grad)
+    back = rearrange(grad.to(src), "b t (h w) (p q c) -> b c t (h p) (w q)", h=3, w=5, p=2, q=2, c=12)
+    assert torch.equal(latent.grad, back)
+    again = unpatchify(patches.detach(), channels=12, grid=(3, 5), patch_size=2, dtype=src)
+    assert torch.equal(again, latent.detach().to(dst).to(src))
