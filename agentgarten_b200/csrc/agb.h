@@ -278,6 +278,17 @@ cudaError_t colorize_depth(const float* depth, const float* scale, float* out, i
                            int64_t plane, int scale_count, cudaStream_t stream);
 cudaError_t decode_normal(const void* normal, float* out, int64_t batch, int64_t plane,
                           cudaStream_t stream);
+// Frame stacks [images, H, W] fp32.  pool_frames: mean over factor x factor windows, non-finite
+// inputs as zero.  blur_frames: separable blur with 2 * radius + 1 taps and replicated borders
+// (scratch has the size of src).  warp_frames: [B, C, T, H, W], bilinear sampling of the
+// scale / shift / shear / perspective map given by params [B * T, 8] = (sx, sy, tx, ty, hx, hy,
+// px, py), border clamped; frames with copy[b * T + t] != 0 are copied.
+cudaError_t pool_frames(const float* src, float* dst, int64_t images, int h, int w, int factor,
+                        cudaStream_t stream);
+cudaError_t blur_frames(const float* src, float* scratch, float* dst, const float* taps, int radius,
+                        int64_t images, int h, int w, cudaStream_t stream);
+cudaError_t warp_frames(const float* src, float* dst, const float* params, const uint8_t* copy, int64_t batch,
+                        int channels, int frames, int h, int w, cudaStream_t stream);
 
 // ------------------------------------------------- all-to-all over peer memory (one node)
 // out[s] = block `rank` of rank s's `send`, for all s.  `recv[r]` is rank r's receive buffer

@@ -474,6 +474,58 @@ Tensor colorize_depth(const Tensor& depth, const Tensor& scale) {
   return out;
 }
 
+static void check_frames(const Tensor& t, int64_t dims, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous() && t.dim() == dims, what,
+              ": contiguous fp32 CUDA tensor of ", dims, " dimensions");
+}
+
+// [..., H, W] -> [..., H / factor, W / factor]: window means, non-finite inputs as zero.
+Tensor pool_frames(const Tensor& video, int64_t factor) {
+  TORCH_CHECK(video.dim() >= 2, "pool_frames: at least [H, W]");
+  check_frames(video, video.dim(), "pool_frames");
+  const int64_t h = video.size(-2), w = video.size(-1);
+  TORCH_CHECK(factor >= 1 && h >= factor && w >= factor, "pool_frames: the window does not fit the frame");
+  c10::cuda::CUDAGuard guard(video.device());
+  auto shape = video.sizes().vec();
+  shape[shape.size() - 2] = h / factor;
+  shape[shape.size() - 1] = w / factor;
+  auto out = torch::empty(shape, video.options());
+  check(agb::pool_frames(video.data_ptr<float>(), out.data_ptr<float>(), video.numel() / (h * w), int(h), int(w),
+                         int(factor), stream_of(video)), "pool_frames");
+  return out;
+}
+
+// Separable blur of [..., H, W] with the odd-length `taps` and replicated borders.
+Tensor blur_frames(const Tensor& images, const Tensor& taps) {
+  TORCH_CHECK(images.dim() >= 2, "blur_frames: at least [H, W]");
+  check_frames(images, images.dim(), "blur_frames");
+  TORCH_CHECK(taps.is_cuda() && taps.scalar_type() == torch::kFloat32 && taps.is_contiguous() &&
+                  taps.numel() % 2 == 1, "blur_frames: taps is a contiguous fp32 vector of odd length");
+  c10::cuda::CUDAGuard guard(images.device());
+  const int64_t h = images.size(-2), w = images.size(-1);
+  auto scratch = torch::empty_like(images), out = torch::empty_like(images);
+  check(agb::blur_frames(images.data_ptr<float>(), scratch.data_ptr<float>(), out.data_ptr<float>(),
+                         taps.data_ptr<float>(), int(taps.numel() / 2), images.numel() / std::max<int64_t>(h * w, 1),
+                         int(h), int(w), stream_of(images)), "blur_frames");
+  return out;
+}
+
+// [B, C, T, H, W] warped frame by frame: params [B, T, 8] fp32, copy [B, T] uint8.
+Tensor warp_frames(const Tensor& video, const Tensor& params, const Tensor& copy) {
+  check_frames(video, 5, "warp_frames");
+  const int64_t b = video.size(0), t = video.size(2);
+  TORCH_CHECK(params.is_cuda() && params.scalar_type() == torch::kFloat32 && params.is_contiguous() &&
+                  params.numel() == b * t * 8, "warp_frames: params is contiguous fp32 [B, T, 8]");
+  TORCH_CHECK(copy.is_cuda() && copy.scalar_type() == torch::kUInt8 && copy.is_contiguous() &&
+                  copy.numel() == b * t, "warp_frames: copy is contiguous uint8 [B, T]");
+  c10::cuda::CUDAGuard guard(video.device());
+  auto out = torch::empty_like(video);
+  check(agb::warp_frames(video.data_ptr<float>(), out.data_ptr<float>(), params.data_ptr<float>(),
+                         copy.data_ptr<uint8_t>(), b, int(video.size(1)), int(t), int(video.size(3)),
+                         int(video.size(4)), stream_of(video)), "warp_frames");
+  return out;
+}
+
 Tensor decode_normal(const Tensor& normal) {
   TORCH_CHECK(normal.is_cuda() && normal.scalar_type() == torch::kUInt8 && normal.dim() == 5 &&
                   normal.size(1) == 3 && normal.is_contiguous(), "decode_normal: normal is contiguous uint8 [B, 3, T, H, W]");
@@ -893,6 +945,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("depthwise", &depthwise);
   m.def("colorize_depth", &colorize_depth);
   m.def("decode_normal", &decode_normal);
+  m.def("pool_frames", &pool_frames);
+  m.def("blur_frames", &blur_frames);
+  m.def("warp_frames", &warp_frames);
   m.def("norm_modulate", &norm_modulate);
   m.def("gated_residual", &gated_residual);
   m.def("attn_jvp", &attn_jvp);

@@ -63,6 +63,85 @@ unsigned grid_for(int64_t total) {
   return unsigned(blocks < 148 * 32 ? blocks : 148 * 32);
 }
 
+
+// ------------------------------------------------------------------ pooling, blur, warp
+// All three work on frame stacks [images, H, W] (fp32), one thread per output pixel.
+
+// Mean over factor x factor windows (floor division of the extent, as avg_pool2d does), with
+// non-finite inputs read as zero.
+__global__ void __launch_bounds__(NT) pool_frames_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                         int64_t images, int h, int w, int factor) {
+  const int oh = h / factor, ow = w / factor;
+  const int64_t total = images * oh * ow;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int x = int(i % ow), y = int((i / ow) % oh);
+    const int64_t image = i / (int64_t(ow) * oh);
+    const float* base = src + (image * h + int64_t(y) * factor) * w + int64_t(x) * factor;
+    float sum = 0.f;
+    for (int dy = 0; dy < factor; ++dy) {
+      for (int dx = 0; dx < factor; ++dx) {
+        const float v = base[int64_t(dy) * w + dx];
+        sum += isfinite(v) ? v : 0.f;
+      }
+    }
+    dst[i] = sum / float(factor * factor);
+  }
+}
+
+// One pass of a separable blur with replicated borders: along x (horizontal = 1) or along y.
+__global__ void __launch_bounds__(NT) blur_pass_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                       const float* __restrict__ taps, int radius,
+                                                       int64_t images, int h, int w, int horizontal) {
+  const int64_t total = images * h * w;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int x = int(i % w), y = int((i / w) % h);
+    const float* plane = src + (i / (int64_t(w) * h)) * int64_t(h) * w;
+    float sum = 0.f;
+    for (int k = -radius; k <= radius; ++k) {
+      const int xx = horizontal ? min(max(x + k, 0), w - 1) : x;
+      const int yy = horizontal ? y : min(max(y + k, 0), h - 1);
+      sum += taps[k + radius] * plane[int64_t(yy) * w + xx];
+    }
+    dst[i] = sum;
+  }
+}
+
+// Scale / shift / shear / perspective warp of frame t of sample b with bilinear sampling and
+// border clamping (grid_sample, align_corners = false).  params[b * frames + t] holds
+// (sx, sy, tx, ty, hx, hy, px, py); a frame whose `copy` flag is set is copied unchanged.
+// Layout [B, C, T, H, W]; the sampling grid is never materialised.
+__global__ void __launch_bounds__(NT) warp_frames_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                         const float* __restrict__ params,
+                                                         const uint8_t* __restrict__ copy, int64_t batch,
+                                                         int channels, int frames, int h, int w) {
+  const int64_t total = batch * channels * frames * int64_t(h) * w;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int x = int(i % w), y = int((i / w) % h);
+    const int64_t plane_index = i / (int64_t(w) * h);       // (b * C + c) * T + t
+    const int t = int(plane_index % frames);
+    const int64_t b = plane_index / (int64_t(frames) * channels);
+    const float* plane = src + plane_index * int64_t(h) * w;
+    if (copy[b * frames + t]) {
+      dst[i] = plane[int64_t(y) * w + x];
+      continue;
+    }
+    const float* q = params + (b * frames + t) * 8;
+    const float gx = (x + 0.5f) * (2.0f / w) - 1.0f, gy = (y + 0.5f) * (2.0f / h) - 1.0f;
+    const float denom = fmaxf(1.0f + q[6] * gx + q[7] * gy, 0.5f);
+    const float u = (q[0] * gx + q[4] * gy + q[2]) / denom;
+    const float v = (q[5] * gx + q[1] * gy + q[3]) / denom;
+    // normalised -> pixel coordinates (align_corners = false), clamped to the border
+    const float fx = fminf(fmaxf(((u + 1.0f) * w - 1.0f) * 0.5f, 0.f), float(w - 1));
+    const float fy = fminf(fmaxf(((v + 1.0f) * h - 1.0f) * 0.5f, 0.f), float(h - 1));
+    const int x0 = int(floorf(fx)), y0 = int(floorf(fy));
+    const int x1 = min(x0 + 1, w - 1), y1 = min(y0 + 1, h - 1);
+    const float ax = fx - x0, ay = fy - y0;
+    const float top = plane[int64_t(y0) * w + x0] * (1.f - ax) + plane[int64_t(y0) * w + x1] * ax;
+    const float bottom = plane[int64_t(y1) * w + x0] * (1.f - ax) + plane[int64_t(y1) * w + x1] * ax;
+    dst[i] = top * (1.f - ay) + bottom * ay;
+  }
+}
+
 }  // namespace
 
 cudaError_t colorize_depth(const float* depth, const float* scale, float* out, int64_t batch,
@@ -79,6 +158,39 @@ cudaError_t decode_normal(const void* normal, float* out, int64_t batch, int64_t
   if (total == 0) return cudaSuccess;
   decode_normal_kernel<<<grid_for(total), NT, 0, stream>>>(static_cast<const uint8_t*>(normal), out,
                                                            plane, total);
+  return cudaGetLastError();
+}
+
+
+static unsigned geometry_grid(int64_t total) {
+  return unsigned(std::min<int64_t>((total + NT - 1) / NT, 148 * 32));
+}
+
+cudaError_t pool_frames(const float* src, float* dst, int64_t images, int h, int w, int factor,
+                        cudaStream_t stream) {
+  if (factor < 1 || h / factor < 1 || w / factor < 1) return cudaErrorInvalidValue;
+  const int64_t total = images * (h / factor) * (w / factor);
+  if (total == 0) return cudaSuccess;
+  pool_frames_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, dst, images, h, w, factor);
+  return cudaGetLastError();
+}
+
+cudaError_t blur_frames(const float* src, float* scratch, float* dst, const float* taps, int radius,
+                        int64_t images, int h, int w, cudaStream_t stream) {
+  const int64_t total = images * int64_t(h) * w;
+  if (total == 0) return cudaSuccess;
+  if (radius < 0) return cudaErrorInvalidValue;
+  blur_pass_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, scratch, taps, radius, images, h, w, 1);
+  blur_pass_kernel<<<geometry_grid(total), NT, 0, stream>>>(scratch, dst, taps, radius, images, h, w, 0);
+  return cudaGetLastError();
+}
+
+cudaError_t warp_frames(const float* src, float* dst, const float* params, const uint8_t* copy, int64_t batch,
+                        int channels, int frames, int h, int w, cudaStream_t stream) {
+  const int64_t total = batch * channels * frames * int64_t(h) * w;
+  if (total == 0) return cudaSuccess;
+  warp_frames_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, dst, params, copy, batch, channels, frames,
+                                                             h, w);
   return cudaGetLastError();
 }
 

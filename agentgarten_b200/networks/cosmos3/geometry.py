@@ -173,6 +173,10 @@ def _images_as_frames(images: torch.Tensor, batch: int) -> torch.Tensor:
 def downsample_geometry(videos: Mapping[str, torch.Tensor], *, factor: int) -> dict[str, torch.Tensor]:
     out = {}
     for name, video in videos.items():
+        fused = _fused_kernels(video) if video.dtype == torch.float32 else None
+        if fused is not None:
+            out[name] = fused.pool_frames(video.contiguous(), factor)  # cleans and pools in one pass
+            continue
         clean = torch.nan_to_num(video, nan=0.0, posinf=0.0, neginf=0.0)
         low = F.avg_pool2d(_frames_as_images(clean), kernel_size=factor, stride=factor)
         out[name] = _images_as_frames(low, video.shape[0]).contiguous()
@@ -200,6 +204,9 @@ def _gaussian(images: torch.Tensor, sigma: float) -> torch.Tensor:
     x = torch.arange(-radius, radius + 1, device=images.device, dtype=images.dtype)
     kernel = torch.exp(-0.5 * x.square() / (sigma * sigma))
     kernel = kernel / kernel.sum()
+    fused = _fused_kernels(images) if images.dtype == torch.float32 else None
+    if fused is not None:
+        return fused.blur_frames(images.contiguous(), kernel.contiguous())  # no padded copies
     c = images.shape[1]
     rows = kernel.view(1, 1, 1, -1).repeat(c, 1, 1, 1)
     cols = kernel.view(1, 1, -1, 1).repeat(c, 1, 1, 1)
@@ -273,6 +280,19 @@ def _warp_from_first_frame(videos, *, config) -> dict[str, torch.Tensor]:
     tx, ty = strength * col(shift, 0) * 2.0, strength * col(shift, 1) * 2.0
     hx, hy = strength * col(shear, 0), strength * col(shear, 1)
     px, py = strength * col(persp, 0), strength * col(persp, 1)
+    stacked_input = torch.cat([videos[n] for n in videos], dim=1)
+    fused = _fused_kernels(stacked_input) if stacked_input.dtype == torch.float32 else None
+    if fused is not None:
+        # one kernel: the map of every frame from its eight numbers, bilinear sampling with border
+        # clamping, the unchanged last frame and the samples that are not warped
+        terms = [term.expand(b, t, 1, 1).reshape(b, t) for term in (sx, sy, tx, ty, hx, hy, px, py)]
+        keep = (~applied).to(device)[:, None].expand(b, t).clone()
+        if t > 1:
+            keep[:, -1] = True
+        warped = fused.warp_frames(stacked_input.contiguous(), torch.stack(terms, dim=-1).contiguous(),
+                                   keep.to(torch.uint8).contiguous())
+        names = tuple(videos)
+        return dict(zip(names, warped.split([int(videos[n].shape[1]) for n in names], dim=1), strict=True))
     denom = (1.0 + px * gx + py * gy).clamp_min(0.5)
     src_x = (sx * gx + hx * gy + tx) / denom
     src_y = (hy * gx + sy * gy + ty) / denom

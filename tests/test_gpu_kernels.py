@@ -739,3 +739,38 @@ def test_patch_layout_kernels_match_the_rearrangement(src, dst):
     assert torch.equal(latent.grad, back)
     again = unpatchify(patches.detach(), channels=12, grid=(3, 5), patch_size=2, dtype=src)
     assert torch.equal(again, latent.detach().to(dst).to(src))
+
+
+def test_geometry_pool_blur_and_warp_kernels_match_the_library_formulation(monkeypatch):
+    """The three frame kernels against avg_pool2d / padded depthwise conv2d / grid_sample: the
+    same functions of ``networks/cosmos3/geometry.py`` run once on the kernels and once with them
+    switched off, with the same random draws."""
+    from agentgarten_b200.networks.cosmos3 import geometry
+
+    g = torch.Generator(device=DEV).manual_seed(11)
+    depth = torch.randn(2, 3, 5, 36, 52, device=DEV, generator=g)
+    depth[0, 0, 0, 0, 0] = float("nan")
+    depth[1, 2, 3, 5, 7] = float("inf")
+    normal = torch.randn(2, 3, 5, 36, 52, device=DEV, generator=g)
+    config = geometry.GeometryAugmentationConfig(spatial_probability=1.0, spatial_max_scale=1.3,
+                                                 spatial_max_shift_fraction=0.1, spatial_max_shear=0.1,
+                                                 spatial_max_perspective=0.1)
+
+    def run():
+        torch.manual_seed(5)
+        pooled = geometry.downsample_geometry({"depth": depth, "normal": normal}, factor=4)
+        blurred = geometry._gaussian(normal[0].permute(1, 0, 2, 3).contiguous(), 1.7)
+        warped = geometry._warp_from_first_frame({"depth": normal, "normal": normal * 2}, config=config)
+        return pooled, blurred, warped
+
+    before = native.launches()
+    mine = run()
+    assert native.launches() >= before + 4
+    monkeypatch.setattr(geometry, "_fused_kernels", lambda tensor: None)
+    want = run()
+    for name in ("depth", "normal"):
+        assert mine[0][name].shape == want[0][name].shape
+        assert torch.allclose(mine[0][name], want[0][name], atol=1e-5)
+        assert torch.allclose(mine[2][name], want[2][name], atol=2e-4), float((mine[2][name] - want[2][name]).abs().max())
+        assert torch.equal(mine[2][name][:, :, -1], want[2][name][:, :, -1])   # the last frame is untouched
+    assert torch.allclose(mine[1], want[1], atol=1e-5)
