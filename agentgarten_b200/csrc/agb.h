@@ -355,6 +355,12 @@ cudaError_t patch_layout(const void* src, void* dst, int64_t batch, int64_t chan
                          int64_t height, int64_t width, int patch, bool to_patches, bool src_bf16,
                          bool dst_bf16, cudaStream_t stream);
 
+// Maximum of n <= 32 unsigned values over the GPUs that share the multicast mapping `multicast` of
+// the symmetric buffer `local` (>= 65 words, zeroed before the first call); state is one int of
+// this GPU's own memory (calls made).  One launch: csrc/multimem.cu.
+cudaError_t multimem_max(void* local, void* multicast, int* state, const uint32_t* in, uint32_t* out, int n,
+                         int world, int rank, int* status, uint64_t limit_ns, cudaStream_t stream);
+
 // Diagnostic: every SM issues `iterations` x 8 tcgen05.mma (M 128, K 16, `columns` wide) back to
 // back; cycles[0] receives the cycles block 0 needed, or -1 when its bounded wait gave up.
 cudaError_t mma_issue_rate(int columns, bool a_from_tmem, int iterations, int sm_count, long long* cycles,

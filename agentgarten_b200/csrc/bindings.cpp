@@ -901,6 +901,23 @@ Tensor patch_layout(const Tensor& src, int64_t channels, int64_t height, int64_t
   return dst;
 }
 
+// Element-wise maximum of a few int32 values over the GPUs of a node through the switch.
+void multimem_max(const Tensor& buffer, int64_t multicast_ptr, const Tensor& state, const Tensor& values,
+                  const Tensor& out, int64_t world, int64_t rank, int64_t limit_ns) {
+  TORCH_CHECK(buffer.is_cuda() && buffer.scalar_type() == torch::kInt32 && buffer.numel() >= 65 &&
+                  state.scalar_type() == torch::kInt32 && values.scalar_type() == torch::kInt32 &&
+                  out.scalar_type() == torch::kInt32 && values.is_contiguous() && out.is_contiguous() &&
+                  values.numel() == out.numel() && values.numel() >= 1 && values.numel() <= 32,
+              "multimem_max: int32 buffers, 1..32 values");
+  TORCH_CHECK(multicast_ptr != 0, "multimem_max: no multicast mapping");
+  c10::cuda::CUDAGuard guard(buffer.device());
+  check(agb::multimem_max(buffer.data_ptr(), reinterpret_cast<void*>(multicast_ptr), state.data_ptr<int>(),
+                          reinterpret_cast<const uint32_t*>(values.data_ptr<int>()),
+                          reinterpret_cast<uint32_t*>(out.data_ptr<int>()), int(values.numel()), int(world),
+                          int(rank), status_word(buffer.device().index()).data_ptr<int>(), uint64_t(limit_ns),
+                          stream_of(buffer)), "multimem_max");
+}
+
 // Cycles per tcgen05.mma (M 128, K 16) issued back to back; see csrc/mma_rate.cu.
 double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
   const int device = c10::cuda::current_device();
@@ -917,6 +934,7 @@ double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mma_issue_rate", &mma_issue_rate);
+  m.def("multimem_max", &multimem_max);
   m.def("rope_tables", &rope_tables);
   m.def("patch_layout", &patch_layout);
   m.def("gemm", &gemm);

@@ -199,6 +199,30 @@ def check_peer_exchange(device, rank, world):
     peer_exchange.release()
 
 
+def check_switch_consensus(device, rank, world):
+    """The maximum of a few small values over the ranks through the NVSwitch multicast mapping
+    against the library all-reduce, repeated so that both halves of the buffer and the call
+    counter are reused; where the GPUs have no multicast mapping the same call takes the library
+    path and must agree all the same."""
+    from agentgarten_b200.ops import native
+    from agentgarten_b200.parallel import consensus
+
+    for call in range(7):
+        word = torch.tensor([float((rank + call) % 3 == 0), float((call * (rank + 1)) % 8), float(rank)],
+                            device=device)
+        want = word.clone()
+        dist.all_reduce(want, op=dist.ReduceOp.MAX)
+        got = consensus.maximum(word.clone())
+        assert torch.equal(got, want), (call, got.tolist(), want.tolist())
+    torch.cuda.synchronize()
+    assert int(native.ext().status(device.index).item()) == 0
+    used = consensus._link(dist.group.WORLD, device) is not None
+    if rank == 0:
+        print("SWITCH_CONSENSUS", "multimem" if used else "library path (no multicast mapping)")
+    dist.barrier()
+    consensus.release()
+
+
 def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     device = distributed.init(device="cuda", backend="nccl")
@@ -212,6 +236,8 @@ def main():
     check_context_parallel_training(device, rank, world)
     dist.barrier()
     check_peer_exchange(device, rank, world)
+    dist.barrier()
+    check_switch_consensus(device, rank, world)
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK")
