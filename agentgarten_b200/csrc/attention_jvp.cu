@@ -154,16 +154,16 @@ attn_jvp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
   } else if (warp == 5) {
     // -------------------------------------------------------------------- MMA issuer
-    if (lane == 0 && n_tiles > 0) {
+    if (n_tiles > 0) {  // the whole warp runs the loop; one elected lane issues
       constexpr uint32_t idesc_s = make_idesc_bf16(128, JBN, 0, 0);   // both K-major over d
       constexpr uint32_t idesc_o = make_idesc_bf16(128, 128, 0, 1);   // P from TMEM, V MN-major
       const uint32_t q_addr = smem_u32(sQ), tq_addr = smem_u32(sTQ);
-      bool ok = mbar_wait(q_full, 0, guard, kTimeoutMma);
+      bool ok = mbar_wait_w(q_full, 0, guard, kTimeoutMma);
       auto scores = [&](int j) -> bool {
         const int st = j % JSTAGES, buf = j & 1;
-        if (!mbar_wait(&k_full[st], (j / JSTAGES) & 1, guard, kTimeoutMma)) return false;
+        if (!mbar_wait_w(&k_full[st], (j / JSTAGES) & 1, guard, kTimeoutMma)) return false;
         // P and W of tile j-2 live in this buffer until their products have completed.
-        if (j >= 2 && !mbar_wait(&pv_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutMma)) return false;
+        if (j >= 2 && !mbar_wait_w(&pv_done[buf], ((j - 2) >> 1) & 1, guard, kTimeoutMma)) return false;
         tc_fence_after_sync();
         const uint32_t k_addr = smem_u32(sK + st * 2 * K_BYTES);
         const uint32_t tk_addr = k_addr + K_BYTES;
@@ -172,51 +172,51 @@ attn_jvp_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qo = (kk >> 2) * Q_HALF + (kk & 3) * 32;
           const uint32_t ko = (kk >> 2) * K_HALF + (kk & 3) * 32;
-          tc_mma_ss(s_col, make_smem_desc(q_addr + qo, 16, 1024), make_smem_desc(k_addr + ko, 16, 1024),
+          tc_mma_ss_w(s_col, make_smem_desc(q_addr + qo, 16, 1024), make_smem_desc(k_addr + ko, 16, 1024),
                     idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qo = (kk >> 2) * Q_HALF + (kk & 3) * 32;
           const uint32_t ko = (kk >> 2) * K_HALF + (kk & 3) * 32;
-          tc_mma_ss(t_col, make_smem_desc(tq_addr + qo, 16, 1024), make_smem_desc(k_addr + ko, 16, 1024),
+          tc_mma_ss_w(t_col, make_smem_desc(tq_addr + qo, 16, 1024), make_smem_desc(k_addr + ko, 16, 1024),
                     idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t qo = (kk >> 2) * Q_HALF + (kk & 3) * 32;
           const uint32_t ko = (kk >> 2) * K_HALF + (kk & 3) * 32;
-          tc_mma_ss(t_col, make_smem_desc(q_addr + qo, 16, 1024), make_smem_desc(tk_addr + ko, 16, 1024),
+          tc_mma_ss_w(t_col, make_smem_desc(q_addr + qo, 16, 1024), make_smem_desc(tk_addr + ko, 16, 1024),
                     idesc_s, true);
         }
-        tc_commit(&k_empty[st]);
-        tc_commit(&s_full[buf]);
+        tc_commit_w(&k_empty[st]);
+        tc_commit_w(&s_full[buf]);
         return true;
       };
       if (ok) ok = scores(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles && !scores(j + 1)) { ok = false; break; }
         const int st = j % JSTAGES, buf = j & 1;
-        if (!mbar_wait(&v_full[st], (j / JSTAGES) & 1, guard, kTimeoutMma)) { ok = false; break; }
-        if (!mbar_wait(&p_ready[buf], (j >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait_w(&v_full[st], (j / JSTAGES) & 1, guard, kTimeoutMma)) { ok = false; break; }
+        if (!mbar_wait_w(&p_ready[buf], (j >> 1) & 1, guard, kTimeoutMma)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t v_addr = smem_u32(sV + st * 2 * K_BYTES);
         const uint32_t tv_addr = v_addr + K_BYTES;
         const uint32_t p_col = tmem_base + CS + buf * JBN, w_col = tmem_base + CT + buf * JBN;
 #pragma unroll
         for (int kk = 0; kk < JBN / 16; ++kk)  // 16 keys per step: 8 packed columns, 16 V rows
-          tc_mma_ts(tmem_base + CO, p_col + kk * 8, make_smem_desc(v_addr + kk * 2048, K_HALF, 1024),
+          tc_mma_ts_w(tmem_base + CO, p_col + kk * 8, make_smem_desc(v_addr + kk * 2048, K_HALF, 1024),
                     idesc_o, (j | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < JBN / 16; ++kk)
-          tc_mma_ts(tmem_base + CA, w_col + kk * 8, make_smem_desc(v_addr + kk * 2048, K_HALF, 1024),
+          tc_mma_ts_w(tmem_base + CA, w_col + kk * 8, make_smem_desc(v_addr + kk * 2048, K_HALF, 1024),
                     idesc_o, (j | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < JBN / 16; ++kk)
-          tc_mma_ts(tmem_base + CA, p_col + kk * 8, make_smem_desc(tv_addr + kk * 2048, K_HALF, 1024),
+          tc_mma_ts_w(tmem_base + CA, p_col + kk * 8, make_smem_desc(tv_addr + kk * 2048, K_HALF, 1024),
                     idesc_o, true);
-        tc_commit(&v_empty[st]);
-        tc_commit(&pv_done[buf]);
+        tc_commit_w(&v_empty[st]);
+        tc_commit_w(&pv_done[buf]);
       }
     }
   } else {
