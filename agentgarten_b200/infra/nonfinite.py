@@ -71,7 +71,10 @@ def synchronize_found_nonfinite(grad_scaler, optimizers, *, fallback_device) -> 
     verdict.clamp_(0, 1)
     word = torch.stack((verdict.reshape(()), status_flag(verdict.device).to(verdict.device)))
     if dist.is_available() and dist.is_initialized():
-        dist.all_reduce(word, op=dist.ReduceOp.MAX)
+        # inside a node through the NVSwitch multicast mapping (one launch), else the library all-reduce
+        from agentgarten_b200.parallel.consensus import maximum
+
+        maximum(word)
     nonfinite, status = word.tolist()  # the one host read of the update
     raise_for_status(status, "training update")
     verdict = word[0].clamp_(0, 1)

@@ -216,6 +216,16 @@ def check_switch_consensus(device, rank, world):
         assert torch.equal(got, want), (call, got.tolist(), want.tolist())
     torch.cuda.synchronize()
     assert int(native.ext().status(device.index).item()) == 0
+    # the trainer's consensus takes the same path: one rank with a non-finite gradient stops all
+    from agentgarten_b200.infra.nonfinite import synchronize_found_nonfinite
+
+    for bad_rank in (None, world - 1):
+        weight = torch.nn.Parameter(torch.ones(8, device=device))
+        weight.grad = torch.ones(8, device=device)
+        if rank == bad_rank:
+            weight.grad[3] = float("inf")
+        verdict = synchronize_found_nonfinite(None, (torch.optim.SGD([weight], lr=0.1),), fallback_device=device)
+        assert verdict == (bad_rank is not None), (bad_rank, verdict)
     used = consensus._link(dist.group.WORLD, device) is not None
     if rank == 0:
         print("SWITCH_CONSENSUS", "multimem" if used else "library path (no multicast mapping)")
