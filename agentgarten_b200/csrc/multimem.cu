@@ -8,9 +8,9 @@
 //   2. once its own counter shows that all have arrived, GPU r reduces the elements
 //      i = r, r + world, ... with multimem.ld_reduce.max (the switch combines the copies) and
 //      writes each result to every copy with multimem.st;
-//   3. a second arrival round, then every GPU reads the results from its own copy.
+//   3. a second arrival, then every GPU reads the results from its own copy.
 // Each element is reduced exactly once, so all GPUs read identical bits.  The buffer has two
-// halves used by alternating calls, and a call enters its first round only after finishing the
+// halves used by alternating calls, and a call makes its first arrival only after finishing the
 // reads of the previous one, so a half is never rewritten while a peer still reads it.  The
 // call count lives in device memory: the kernel can be replayed from a CUDA graph.  Both waits
 // are bounded (status word kTimeoutPeer).
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(MM_MAX) multimem_max_kernel(uint32_t* local, u
   __threadfence_system();
   __syncthreads();
   if (i == 0) {
-    mm_arrive(counter_mc);  // round 1 of this call: every copy holds its owner's values
+    mm_arrive(counter_mc);  // first arrival of this call: every copy holds its owner's values
     ok_shared = mm_wait(counter, counter_add(0, (2 * call + 1) * world), status, limit_ns) ? 1 : 0;
   }
   __syncthreads();
@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(MM_MAX) multimem_max_kernel(uint32_t* local, u
   __threadfence_system();
   __syncthreads();
   if (i == 0) {
-    if (ok) mm_arrive(counter_mc);  // round 2: every copy holds the results
+    if (ok) mm_arrive(counter_mc);  // second arrival: every copy holds the results
     ok_shared = ok && mm_wait(counter, counter_add(0, (2 * call + 2) * world), status, limit_ns) ? 1 : 0;
     state[0] = call + 1;
   }
