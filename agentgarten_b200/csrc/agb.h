@@ -361,6 +361,13 @@ cudaError_t patch_layout(const void* src, void* dst, int64_t batch, int64_t chan
 cudaError_t multimem_max(void* local, void* multicast, int* state, const uint32_t* in, uint32_t* out, int n,
                          int world, int rank, int* status, uint64_t limit_ns, cudaStream_t stream);
 
+// y [m, n] = x [m, k] W[n, k]^T + b for a few FP32 rows (m <= 64 is the intended range), W and b in
+// bf16 or fp32; and its gradients dx [m, k], dw [n, k], db [n] in FP32 (any of the three may be null).
+cudaError_t rows_linear_fwd(const float* x, const void* w, const void* bias, float* y, int m, int n, int k,
+                            bool bf16_weights, cudaStream_t stream);
+cudaError_t rows_linear_bwd(const float* dy, const float* x, const void* w, float* dx, float* dw, float* db, int m,
+                            int n, int k, bool bf16_weights, cudaStream_t stream);
+
 // Diagnostic: every SM issues `iterations` x 8 tcgen05.mma (M 128, K 16, `columns` wide) back to
 // back; cycles[0] receives the cycles block 0 needed, or -1 when its bounded wait gave up.
 cudaError_t mma_issue_rate(int columns, bool a_from_tmem, int iterations, int sm_count, long long* cycles,

@@ -918,6 +918,42 @@ void multimem_max(const Tensor& buffer, int64_t multicast_ptr, const Tensor& sta
                           stream_of(buffer)), "multimem_max");
 }
 
+// A few FP32 rows through a wide linear layer in FP32, weights read as they are (bf16 or fp32).
+Tensor rows_linear_fwd(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias) {
+  const auto wt = w.scalar_type();
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.dim() == 2 && x.is_contiguous() &&
+                  w.dim() == 2 && w.is_contiguous() && w.size(1) == x.size(1) &&
+                  (wt == torch::kBFloat16 || wt == torch::kFloat32), "rows_linear: x fp32 [m, k], w [n, k]");
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == wt && bias->is_contiguous() && bias->numel() == w.size(0), "rows_linear: bias");
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty({x.size(0), w.size(0)}, x.options());
+  check(agb::rows_linear_fwd(x.data_ptr<float>(), w.data_ptr(), bias.has_value() ? bias->data_ptr() : nullptr,
+                             y.data_ptr<float>(), int(x.size(0)), int(w.size(0)), int(x.size(1)),
+                             wt == torch::kBFloat16, stream_of(x)), "rows_linear_fwd");
+  return y;
+}
+
+std::tuple<Tensor, Tensor, Tensor> rows_linear_bwd(const Tensor& dy, const Tensor& x, const Tensor& w,
+                                                   bool need_dx, bool need_dw) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == torch::kFloat32 && dy.is_contiguous() && dy.dim() == 2 &&
+                  x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.size(0) == dy.size(0) &&
+                  w.is_contiguous() && w.size(0) == dy.size(1) && w.size(1) == x.size(1), "rows_linear_bwd shapes");
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor dx, dw, db;
+  if (need_dx) dx = torch::empty_like(x);
+  if (need_dw) {
+    dw = torch::empty({w.size(0), w.size(1)}, dy.options());
+    db = torch::empty({w.size(0)}, dy.options());
+  }
+  check(agb::rows_linear_bwd(dy.data_ptr<float>(), x.data_ptr<float>(), w.data_ptr(),
+                             need_dx ? dx.data_ptr<float>() : nullptr, need_dw ? dw.data_ptr<float>() : nullptr,
+                             need_dw ? db.data_ptr<float>() : nullptr, int(dy.size(0)), int(dy.size(1)),
+                             int(x.size(1)), w.scalar_type() == torch::kBFloat16, stream_of(dy)), "rows_linear_bwd");
+  return {dx, dw, db};
+}
+
 // Cycles per tcgen05.mma (M 128, K 16) issued back to back; see csrc/mma_rate.cu.
 double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
   const int device = c10::cuda::current_device();
@@ -934,6 +970,8 @@ double mma_issue_rate(int64_t columns, bool a_from_tmem, int64_t iterations) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mma_issue_rate", &mma_issue_rate);
+  m.def("rows_linear_fwd", &rows_linear_fwd);
+  m.def("rows_linear_bwd", &rows_linear_bwd);
   m.def("multimem_max", &multimem_max);
   m.def("rope_tables", &rope_tables);
   m.def("patch_layout", &patch_layout);

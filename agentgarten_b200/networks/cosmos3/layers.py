@@ -142,10 +142,8 @@ class TimestepEmbedder(nn.Module):
         features = torch.cat((angle.cos(), angle.sin()), dim=-1)
         features = features.to(self.linear_1.weight.dtype).float()
         with torch.autocast(timestep.device.type, enabled=False):
-            hidden = self.act(torch.nn.functional.linear(
-                features, self.linear_1.weight.float(), self.linear_1.bias.float()))
-            return torch.nn.functional.linear(
-                hidden, self.linear_2.weight.float(), self.linear_2.bias.float())
+            hidden = self.act(ops.rows_linear(features, self.linear_1.weight, self.linear_1.bias))
+            return ops.rows_linear(hidden, self.linear_2.weight, self.linear_2.bias)
 
 
 class Cosmos3RotaryEmbedding(nn.Module):

@@ -17,7 +17,7 @@ import torch.autograd.forward_ad as fwAD
 
 from . import native, reference
 from .attention import attention, attention_jvp, planned_attention
-from .linear import adjoin, joined, joint_linear, linear
+from .linear import adjoin, joined, joint_linear, linear, rows_linear
 from .pointwise import (
     gated_residual,
     head_norm_rope,
@@ -47,6 +47,7 @@ __all__ = [
     "rf_interpolate",
     "rf_x0",
     "rms_norm",
+    "rows_linear",
     "rms_norm_add",
     "rotary",
     "silu_mul",

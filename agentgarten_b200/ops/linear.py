@@ -18,7 +18,7 @@ import torch.nn.functional as F
 
 from . import native
 
-__all__ = ["adjoin", "gemm", "joined", "joint_linear", "linear"]
+__all__ = ["adjoin", "gemm", "joined", "joint_linear", "linear", "rows_linear"]
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
@@ -88,6 +88,44 @@ class _Linear(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = g2.float().sum(0).to(grad.dtype)
         return dx, dw, db
+
+
+class _RowsLinear(torch.autograd.Function):
+    """A few FP32 rows through a wide linear layer, evaluated in FP32 with the weights read in their
+    own type (``csrc/rows_linear.cu``); gradients in FP32, cast to the parameters' type."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        native.count()
+        ctx.save_for_backward(x, weight)
+        ctx.bias_dtype = None if bias is None else bias.dtype
+        return native.ext().rows_linear_fwd(x, weight, bias)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, grad):
+        x, weight = ctx.saved_tensors
+        need_dx, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1] or ctx.needs_input_grad[2]
+        native.count(2)
+        dx, dw, db = native.ext().rows_linear_bwd(grad.contiguous(), x, weight, need_dx, need_dw)
+        return (dx, dw.to(weight.dtype) if ctx.needs_input_grad[1] else None,
+                db.to(ctx.bias_dtype) if ctx.needs_input_grad[2] and ctx.bias_dtype is not None else None)
+
+
+def rows_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T + bias`` in FP32 for a few FP32 rows ``x`` (the timestep embedder): on CUDA a
+    kernel that reads bf16 or fp32 weights in place, elsewhere PyTorch with upcast weights.
+
+    Parity: the FP32 MLP of ``wm/networks/cosmos3/layers.py:100-128`` (cuBLAS ``sgemm`` there)."""
+    import torch.autograd.forward_ad as fwAD
+
+    ok = (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= 256
+          and weight.dtype in (torch.bfloat16, torch.float32) and weight.dim() == 2
+          and (bias is None or bias.dtype == weight.dtype) and native.available()
+          and fwAD.unpack_dual(x).tangent is None and fwAD.unpack_dual(weight).tangent is None)
+    if ok:
+        return _RowsLinear.apply(x.contiguous(), weight.contiguous(), None if bias is None else bias.contiguous())
+    return F.linear(x, weight.float(), None if bias is None else bias.float())
 
 
 def joined(parts):

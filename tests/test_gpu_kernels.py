@@ -774,3 +774,26 @@ def test_geometry_pool_blur_and_warp_kernels_match_the_library_formulation(monke
         assert torch.allclose(mine[2][name], want[2][name], atol=2e-4), float((mine[2][name] - want[2][name]).abs().max())
         assert torch.equal(mine[2][name][:, :, -1], want[2][name][:, :, -1])   # the last frame is untouched
     assert torch.allclose(mine[1], want[1], atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rows_linear_matches_fp32_linear_and_its_gradients(dtype):
+    """The timestep embedder's FP32 linears on their own kernels: values and all three gradients
+    against ``F.linear`` on the upcast weights."""
+    g = torch.Generator(device=DEV).manual_seed(6)
+    x = torch.randn(13, 256, device=DEV, generator=g, requires_grad=True)
+    w = (torch.randn(384, 256, device=DEV, generator=g) * 0.1).to(dtype).requires_grad_()
+    b = torch.randn(384, device=DEV, generator=g).to(dtype).requires_grad_()
+    before = native.launches()
+    y = ops.rows_linear(x, w, b)
+    grad = torch.randn(y.shape, device=DEV, generator=g)
+    y.backward(grad)
+    assert native.launches() == before + 3 and y.dtype == torch.float32
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    want = torch.nn.functional.linear(xr, wr, br)
+    want.backward(grad)
+    assert torch.allclose(y, want, atol=1e-4, rtol=1e-5)
+    assert torch.allclose(x.grad, xr.grad, atol=1e-4, rtol=1e-5)
+    tolerance = 1e-4 if dtype == torch.float32 else 4e-2
+    assert torch.allclose(w.grad.float(), wr.grad, atol=tolerance, rtol=1e-2)
+    assert torch.allclose(b.grad.float(), br.grad, atol=tolerance, rtol=1e-2)
