@@ -48,19 +48,24 @@ __all__ = ["eligible", "keep_policy", "run"]
 
 # Free device memory that is never spent on kept activations (backward workspaces, optimizer
 # temporaries, allocator fragmentation), and an optional hard switch.
-_RESERVE_BYTES = int(float(os.environ.get("AGB200_ACTIVATION_RESERVE_GB", "24")) * (1 << 30))
+_RESERVE_BYTES = int(float(os.environ.get("AGB200_ACTIVATION_RESERVE_GB", "20")) * (1 << 30))
 _KEEP_MODE = os.environ.get("AGB200_KEEP_ACTIVATIONS", "auto")  # auto | never | always
 
 
 def keep_policy(tokens: int, hidden: int, inner: int, q_width: int, kv_width: int,
-                device: torch.device) -> tuple[bool, bool]:
-    """(keep MLP half, keep attention half) for one layer about to run its forward."""
+                device: torch.device, layers_ahead: int = 0) -> tuple[bool, bool]:
+    """(keep MLP half, keep attention half) for one layer about to run its forward.
+
+    ``layers_ahead`` layers still have to run after this one in the same pass; each of them saves
+    at least its input and its attention output, and that memory is set aside before anything
+    optional is kept (a long clip on one GPU would otherwise spend it here and run out there)."""
     if _KEEP_MODE == "never":
         return False, False
     if _KEEP_MODE == "always":
         return True, True
     free, _ = torch.cuda.mem_get_info(device)
     free += torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+    free -= layers_ahead * tokens * (hidden + q_width) * 2
     mlp_bytes = tokens * (2 * hidden + 2 * inner) * 2
     attn_bytes = tokens * (hidden + 2 * q_width + 3 * kv_width) * 2
     keep_mlp = free - mlp_bytes > _RESERVE_BYTES
@@ -164,14 +169,15 @@ def _gate_up(C, n2, wg, wu):
 
 class _Layer(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, cos, sin, layer, schedule, text_k, text_v, text_valid, *weights):
+    def forward(ctx, x, cos, sin, layer, schedule, text_k, text_v, text_valid, layers_ahead, *weights):
         C = native.ext()
         w_in, wq, wk, wv, wo, nq, nk, w_post, wg, wu, wd = weights
         b, n, h = x.shape
         eps, heads, kv_heads = layer.input_layernorm_moe_gen.variance_epsilon, \
             layer.num_attention_heads, layer.num_key_value_heads
         x2 = x.reshape(b * n, h)
-        keep_mlp, keep_attn = keep_policy(b * n, h, wg.shape[0], wq.shape[0], wk.shape[0], x.device)
+        keep_mlp, keep_attn = keep_policy(b * n, h, wg.shape[0], wq.shape[0], wk.shape[0], x.device,
+                                          layers_ahead)
         n1, rstd1 = C.rms_norm_fwd(x2, w_in, eps)
         q_lin, k_lin, q, k, v, rq, rk, _ = _project_qkv(C, n1, (wq, wk, wv, nq, nk),
                                                         (b, n, heads, kv_heads), cos, sin, eps)
@@ -298,7 +304,7 @@ class _Layer(torch.autograd.Function):
             from agentgarten_b200.parallel import zero
 
             zero.grads_ready(ctx.params)
-        return (dx.view(b, n, h), None, None, None, None, None, None, None,
+        return (dx.view(b, n, h), None, None, None, None, None, None, None, None,
                 dw_in, dwq, dwk, dwv, dwo, dnq, dnk, dw_post, dwg, dwu, dwd)
 
 
@@ -331,5 +337,5 @@ def run(layer, chunks, ropes, attention, layer_index):
                mlp.up_proj.weight, mlp.down_proj.weight)
     with span(f"layer {layer_index} forward"):
         y = _Layer.apply(x.contiguous(), cos.contiguous(), sin.contiguous(), layer, schedule,
-                         text_k, text_v, valid, *weights)
+                         text_k, text_v, valid, max(0, len(text.keys) - layer_index - 1), *weights)
     return list(y.split(sizes, dim=1)) if len(sizes) > 1 else [y]

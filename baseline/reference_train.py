@@ -50,6 +50,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--latent-hw", type=int, nargs=2, default=(30, 52))
     parser.add_argument("--text-tokens", type=int, default=512)
     parser.add_argument("--grad-accum", type=int, default=1)
+    parser.add_argument("--recipe", default="bidirectional",
+                        choices=["bidirectional", "ar_teacher_forcing", "ar_diffusion_forcing"])
     parser.add_argument("--device", default="cuda")
     parser.add_argument("--no-compile", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
@@ -151,16 +153,29 @@ def build(args: argparse.Namespace, device, compile_layers: bool):
                               compile=compile_layers)
     frozen = ParallelConfig(parameter_dtype=dtype, fully_shard=True, context_parallel_size=1,
                             fsdp_mesh_shape=None, activation_checkpointing="none", compile=False)
-    model = DiffusionModel(
-        net=build_network(config, init_device="meta"),
-        # the codec object is lazy: with cached latents its weights are never read
-        conditioner=Cosmos3Conditioner(
-            config=config, codec=Wan22VAECodec(pretrained_path="unused-with-cached-latents",
-                                               dtype="bfloat16", decoder=None),
-            geometry_noise_sigma=0.0, init_device="meta"),
-        schedule=RectifiedFlowSchedule(shift=5.0, train_distribution="waver"),
-        text_dropout=0.1, parallel=parallel, conditioner_parallel=frozen,
-        sampling={"num_steps": 35, "guidance": 6.0, "seed": 2026})
+    # the codec object is lazy: with cached latents its weights are never read
+    conditioner = Cosmos3Conditioner(
+        config=config, codec=Wan22VAECodec(pretrained_path="unused-with-cached-latents",
+                                           dtype="bfloat16", decoder=None),
+        geometry_noise_sigma=0.0, init_device="meta")
+    schedule = RectifiedFlowSchedule(shift=5.0, train_distribution="waver")
+    if args.recipe == "bidirectional":
+        model = DiffusionModel(
+            net=build_network(config, init_device="meta"), conditioner=conditioner, schedule=schedule,
+            text_dropout=0.1, parallel=parallel, conditioner_parallel=frozen,
+            sampling={"num_steps": 35, "guidance": 6.0, "seed": 2026})
+    else:
+        # the autoregressive recipes of wm/configs/experiments/cosmos3/ar_*_forcing.py
+        from wm.models.autoregressive import AutoregressiveModel
+
+        forcing = args.recipe.removeprefix("ar_")
+        model = AutoregressiveModel(
+            net=build_network(config, init_device="meta"), conditioner=conditioner, mode=forcing,
+            block_frames=4, schedule=schedule, text_dropout=0.1,
+            corrupt_clean_history=forcing == "teacher_forcing", parallel=parallel,
+            conditioner_parallel=frozen,
+            sampling={"num_steps": 16, "guidance": 6.0, "seed": 2026, "sink_blocks": 0,
+                      "recent_blocks": None})
     model.parallelize(device)
     random_init_(model.net, seed=0)
     random_init_(model.conditioner.text_encoder, seed=1)
@@ -327,7 +342,8 @@ def run(args: argparse.Namespace) -> dict:
     tokens_per_clip = args.frames * (args.latent_hw[0] // patch) * (args.latent_hw[1] // patch)
     tokens = tokens_per_clip * world * args.steps * args.grad_accum
     line = {
-        "metric": "train latent-tokens/s/box (bidirectional rectified flow)",
+        "metric": "train latent-tokens/s/box (bidirectional rectified flow)" if args.recipe == "bidirectional"
+                  else f"train latent-tokens/s/box ({args.recipe})",
         "value": tokens / (elapsed_ms / 1e3),
         "unit": "latent RGB tokens/s",
         "n_gpus": world,

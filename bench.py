@@ -115,15 +115,16 @@ def run_reference(args: argparse.Namespace) -> int:
     if not os.path.isfile(os.path.join(REFERENCE_ROOT, "wm", "__init__.py")):
         reason = ("the reference package is not installed under baseline/_ref "
                   "(copy the reference's wm/ directory there)")
-    elif args.recipe != "bidirectional" or args.context_parallel != 1:
-        reason = "the reference arm covers the bidirectional data-parallel recipe only"
+    elif args.context_parallel != 1:
+        reason = "the reference arm runs the recipes data-parallel only (no context parallelism)"
     if reason is not None:
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"impl": "reference", "unavailable": reason}))
         return 0
     command = [sys.executable, REFERENCE_RUNNER, "--gpus", str(args.gpus), "--steps", str(args.steps),
                "--warmup", str(args.warmup), "--layers", str(args.layers),
-               "--frames", str(args.frames or 21), "--grad-accum", str(args.grad_accum)]
+               "--frames", str(args.frames or (21 if args.recipe == "bidirectional" else 61)),
+               "--grad-accum", str(args.grad_accum), "--recipe", args.recipe]
     if args.no_e2e:
         command.append("--no-e2e")
     if args.reference_args:
