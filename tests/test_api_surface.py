@@ -125,7 +125,8 @@ def test_signatures_users_rely_on():
         "start_factor": 0.0, "min_factor": 0.0}
 
 
-def test_bench_reference_arm_runs_the_unmodified_reference_package():
+@pytest.mark.parametrize("recipe,frames", [("bidirectional", "3"), ("ar_diffusion_forcing", "9")])
+def test_bench_reference_arm_runs_the_unmodified_reference_package(recipe, frames):
     """``bench.py --impl reference`` trains a tiny network on the CPU through the reference's
     own package (imported from ``baseline/_ref``), in a process that loads nothing of this one."""
     import json
@@ -143,8 +144,9 @@ def test_bench_reference_arm_runs_the_unmodified_reference_package():
             "--latent-hw 8 8 --text-tokens 12")
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     done = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--gpus", "1",
-                           "--steps", "2", "--warmup", "3", "--layers", "2", "--frames", "3",
-                           "--reference-args", tiny], capture_output=True, text=True, timeout=600, env=env)
+                           "--steps", "2", "--warmup", "3", "--layers", "2", "--frames", frames,
+                           "--recipe", recipe, "--reference-args", tiny],
+                          capture_output=True, text=True, timeout=600, env=env)
     assert done.returncode == 0, done.stderr[-2000:]
     line = json.loads(done.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" not in line, line
