@@ -365,8 +365,11 @@ cudaError_t multimem_max(void* local, void* multicast, int* state, const uint32_
 // bf16 or fp32; and its gradients dx [m, k], dw [n, k], db [n] in FP32 (any of the three may be null).
 cudaError_t rows_linear_fwd(const float* x, const void* w, const void* bias, float* y, int m, int n, int k,
                             bool bf16_weights, cudaStream_t stream);
-cudaError_t rows_linear_bwd(const float* dy, const float* x, const void* w, float* dx, float* dw, float* db, int m,
-                            int n, int k, bool bf16_weights, cudaStream_t stream);
+// k a multiple of 8.  dx is summed from per-slice partial sums: dx_partial holds
+// rows_linear_slices(n) * m * k floats.
+int rows_linear_slices(int n);
+cudaError_t rows_linear_bwd(const float* dy, const float* x, const void* w, float* dx, float* dx_partial,
+                            float* dw, float* db, int m, int n, int k, bool bf16_weights, cudaStream_t stream);
 
 // Diagnostic: every SM issues `iterations` x 8 tcgen05.mma (M 128, K 16, `columns` wide) back to
 // back; cycles[0] receives the cycles block 0 needed, or -1 when its bounded wait gave up.

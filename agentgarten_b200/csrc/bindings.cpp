@@ -941,14 +941,19 @@ std::tuple<Tensor, Tensor, Tensor> rows_linear_bwd(const Tensor& dy, const Tenso
                   x.scalar_type() == torch::kFloat32 && x.is_contiguous() && x.size(0) == dy.size(0) &&
                   w.is_contiguous() && w.size(0) == dy.size(1) && w.size(1) == x.size(1), "rows_linear_bwd shapes");
   c10::cuda::CUDAGuard guard(dy.device());
-  Tensor dx, dw, db;
-  if (need_dx) dx = torch::empty_like(x);
+  Tensor dx, dw, db, partial;
+  TORCH_CHECK(x.size(1) % 8 == 0, "rows_linear: the input width must be a multiple of 8");
+  if (need_dx) {
+    dx = torch::empty_like(x);
+    partial = torch::empty({agb::rows_linear_slices(int(dy.size(1))), x.size(0), x.size(1)}, x.options());
+  }
   if (need_dw) {
     dw = torch::empty({w.size(0), w.size(1)}, dy.options());
     db = torch::empty({w.size(0)}, dy.options());
   }
   check(agb::rows_linear_bwd(dy.data_ptr<float>(), x.data_ptr<float>(), w.data_ptr(),
-                             need_dx ? dx.data_ptr<float>() : nullptr, need_dw ? dw.data_ptr<float>() : nullptr,
+                             need_dx ? dx.data_ptr<float>() : nullptr,
+                             need_dx ? partial.data_ptr<float>() : nullptr, need_dw ? dw.data_ptr<float>() : nullptr,
                              need_dw ? db.data_ptr<float>() : nullptr, int(dy.size(0)), int(dy.size(1)),
                              int(x.size(1)), w.scalar_type() == torch::kBFloat16, stream_of(dy)), "rows_linear_bwd");
   return {dx, dw, db};

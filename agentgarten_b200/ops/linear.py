@@ -119,7 +119,7 @@ def rows_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     Parity: the FP32 MLP of ``wm/networks/cosmos3/layers.py:100-128`` (cuBLAS ``sgemm`` there)."""
     import torch.autograd.forward_ad as fwAD
 
-    ok = (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= 256
+    ok = (x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.shape[0] <= 256 and x.shape[1] % 8 == 0
           and weight.dtype in (torch.bfloat16, torch.float32) and weight.dim() == 2
           and (bias is None or bias.dtype == weight.dtype) and native.available()
           and fwAD.unpack_dual(x).tangent is None and fwAD.unpack_dual(weight).tangent is None)
