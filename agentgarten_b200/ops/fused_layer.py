@@ -48,7 +48,7 @@ __all__ = ["eligible", "keep_policy", "run"]
 
 # Free device memory that is never spent on kept activations (backward workspaces, optimizer
 # temporaries, allocator fragmentation), and an optional hard switch.
-_RESERVE_BYTES = int(float(os.environ.get("AGB200_ACTIVATION_RESERVE_GB", "20")) * (1 << 30))
+_RESERVE_BYTES = int(float(os.environ.get("AGB200_ACTIVATION_RESERVE_GB", "12")) * (1 << 30))
 _KEEP_MODE = os.environ.get("AGB200_KEEP_ACTIVATIONS", "auto")  # auto | never | always
 
 
@@ -66,6 +66,7 @@ def keep_policy(tokens: int, hidden: int, inner: int, q_width: int, kv_width: in
     free, _ = torch.cuda.mem_get_info(device)
     free += torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
     free -= layers_ahead * tokens * (hidden + q_width) * 2
+    free -= tokens * 65536   # the backward pass of a layer needs workspace in proportion to its rows
     mlp_bytes = tokens * (2 * hidden + 2 * inner) * 2
     attn_bytes = tokens * (hidden + 2 * q_width + 3 * kv_width) * 2
     keep_mlp = free - mlp_bytes > _RESERVE_BYTES
