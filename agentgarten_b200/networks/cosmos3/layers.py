@@ -112,11 +112,15 @@ class Cosmos3MLP(nn.Module):
         self.up_proj = Linear(config.hidden_size, config.intermediate_size, bias=False)
         self.down_proj = Linear(config.intermediate_size, config.hidden_size, bias=False)
 
-    def forward(self, value: torch.Tensor) -> torch.Tensor:
+    def forward(self, value: torch.Tensor, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """``down(silu(gate(value)) * up(value))``, plus ``residual`` when one is given (added in the
+        down projection's epilogue where no gradient is wanted)."""
         both = ops.joint_linear(value, (self.gate_proj, self.up_proj))  # one GEMM where it applies
-        if both is not None:
-            return self.down_proj(ops.silu_mul_pair(both))
-        return self.down_proj(ops.silu_mul(self.gate_proj(value), self.up_proj(value)))
+        act = ops.silu_mul_pair(both) if both is not None \
+            else ops.silu_mul(self.gate_proj(value), self.up_proj(value))
+        if residual is None:
+            return self.down_proj(act)
+        return ops.linear_residual(act, self.down_proj, residual)
 
 
 class TimestepEmbedder(nn.Module):
@@ -295,10 +299,10 @@ class Cosmos3GenLayer(nn.Module):
                         self.num_key_value_heads, self.head_dim, cosine, sine)
 
     def finish(self, hidden, attention, modulation=None):
-        out = self.self_attn.to_add_out(attention.flatten(-2))
         if modulation is None:
-            residual = hidden + out
-            return residual + self.mlp_moe_gen(self.post_attention_layernorm_moe_gen(residual))
+            residual = ops.linear_residual(attention.flatten(-2), self.self_attn.to_add_out, hidden)
+            return self.mlp_moe_gen(self.post_attention_layernorm_moe_gen(residual), residual=residual)
+        out = self.self_attn.to_add_out(attention.flatten(-2))
         _, _, gate_a, shift_m, scale_m, gate_m = modulation
         residual = ops.gated_residual(hidden, gate_a, out)
         ln = self.post_attention_layernorm_moe_gen

@@ -17,7 +17,7 @@ import torch.autograd.forward_ad as fwAD
 
 from . import native, reference
 from .attention import attention, attention_jvp, planned_attention
-from .linear import adjoin, joined, joint_linear, linear, rows_linear
+from .linear import adjoin, joined, joint_linear, linear, linear_residual, rows_linear
 from .pointwise import (
     gated_residual,
     head_norm_rope,
@@ -40,6 +40,7 @@ __all__ = [
     "joined",
     "joint_linear",
     "linear",
+    "linear_residual",
     "native",
     "norm_modulate",
     "planned_attention",

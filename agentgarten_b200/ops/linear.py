@@ -18,7 +18,7 @@ import torch.nn.functional as F
 
 from . import native
 
-__all__ = ["adjoin", "gemm", "joined", "joint_linear", "linear", "rows_linear"]
+__all__ = ["adjoin", "gemm", "joined", "joint_linear", "linear", "linear_residual", "rows_linear"]
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
@@ -126,6 +126,27 @@ def rows_linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     if ok:
         return _RowsLinear.apply(x.contiguous(), weight.contiguous(), None if bias is None else bias.contiguous())
     return F.linear(x, weight.float(), None if bias is None else bias.float())
+
+
+def linear_residual(x: torch.Tensor, module, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + module(x)`` for a bias-free linear ``module``.  Where no gradient or tangent is
+    wanted on the CUDA bf16 path the sum happens in the GEMM's epilogue (FP32 accumulator plus
+    residual, rounded once, as the whole-layer training path does); otherwise it is the plain sum."""
+    import torch.autograd.forward_ad as fwAD
+
+    weight = module.weight
+    fused = (type(module).__name__ == "Linear" and module.bias is None and native.use(x) and _gemm_ok(x, weight)
+             and x.shape[-1] % 8 == 0 and residual.dtype == x.dtype and residual.shape[:-1] == x.shape[:-1]
+             and not (torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or residual.requires_grad))
+             and fwAD.unpack_dual(x).tangent is None and fwAD.unpack_dual(residual).tangent is None)
+    if not fused:
+        return residual + module(x)
+    native.count()
+    rows = x.reshape(-1, x.shape[-1])
+    res = residual.reshape(-1, residual.shape[-1])
+    out = native.ext().gemm(rows if rows.is_contiguous() else rows.contiguous(), weight, False, True, None, False,
+                            None, res if res.is_contiguous() else res.contiguous(), torch.bfloat16)
+    return out.view(*x.shape[:-1], weight.shape[0])
 
 
 def joined(parts):
