@@ -107,9 +107,10 @@ cudaError_t rms_norm_fwd(const void* x, const void* addend, const void* w, void*
                          cudaStream_t stream);
 // dw_partial is fp32 [rms_norm_bwd_partials(rows), width]; the caller sums it over dim 0.
 int rms_norm_bwd_partials(int64_t rows);
+// extra (bf16 [rows, width], may be null) is added to dx in FP32 before its one rounding.
 cudaError_t rms_norm_bwd(const void* grad, const void* x, const void* w, const float* rstd,
                          void* dx, float* dw_partial, int64_t rows, int width,
-                         cudaStream_t stream);
+                         cudaStream_t stream, const void* extra = nullptr);
 // x [rows, heads, 128] with row_stride elements between rows (heads * 128 when dense; larger
 // when x is a column block of a wider matrix); out is dense; cos/sin [rows, 128]; rstd fp32
 // [rows, heads] (may be null in fwd).

@@ -127,6 +127,22 @@ std::tuple<Tensor, Tensor> rms_norm_bwd(const Tensor& grad, const Tensor& x, con
   return {dx, partial.sum(0)};
 }
 
+// The same with `extra` (a gradient reaching x on another path) added before dx is rounded.
+std::tuple<Tensor, Tensor> rms_norm_bwd_add(const Tensor& grad, const Tensor& x, const Tensor& w,
+                                            const Tensor& rstd, const Tensor& extra) {
+  check_bf16(extra, "extra");
+  TORCH_CHECK(extra.is_contiguous() && extra.sizes() == x.sizes() && grad.is_contiguous() && x.is_contiguous(),
+              "rms_norm_bwd_add: contiguous tensors of one shape");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = torch::empty_like(x);
+  const int parts = agb::rms_norm_bwd_partials(x.size(0));
+  auto partial = torch::empty({parts, x.size(1)}, x.options().dtype(torch::kFloat32));
+  check(agb::rms_norm_bwd(grad.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(),
+                          dx.data_ptr(), partial.data_ptr<float>(), x.size(0), int(x.size(1)),
+                          stream_of(x), extra.data_ptr()), "rms_norm_bwd_add");
+  return {dx, partial.sum(0)};
+}
+
 std::tuple<Tensor, Tensor> head_norm_rope_fwd(const Tensor& x, const Tensor& w, const Tensor& cosv,
                                               const Tensor& sinv, double eps) {
   check_bf16(x, "x");
@@ -984,6 +1000,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_add_fwd", &rms_norm_add_fwd);
   m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("rms_norm_bwd_add", &rms_norm_bwd_add);
   m.def("head_norm_rope_fwd", &head_norm_rope_fwd);
   m.def("head_norm_rope_bwd", &head_norm_rope_bwd);
   m.def("silu_mul_fwd", &silu_mul_fwd);

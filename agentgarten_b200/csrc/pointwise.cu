@@ -87,7 +87,10 @@ constexpr int MAX_CHUNKS = 4;  // width <= NT * 8 * MAX_CHUNKS = 8192
 __global__ void __launch_bounds__(NT) rms_norm_bwd_kernel(
     const __nv_bfloat16* __restrict__ grad, const __nv_bfloat16* __restrict__ x,
     const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
-    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int width) {
+    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int width,
+    const __nv_bfloat16* __restrict__ extra) {
+  // extra (may be null): a gradient that reaches the same tensor on another path (the residual
+  // branch); it is added in FP32 before the one rounding of dx.
   __shared__ float scratch[NT / 32];
   float dw[MAX_CHUNKS][8];
 #pragma unroll
@@ -126,6 +129,12 @@ __global__ void __launch_bounds__(NT) rms_norm_bwd_kernel(
         unpack8(*reinterpret_cast<const uint4*>(w + c), wv);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = g[i] * wv[i] * r - xv[i] * coef;
+        if (extra) {
+          float e[8];
+          unpack8(*reinterpret_cast<const uint4*>(extra + row * width + c), e);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += e[i];
+        }
         *reinterpret_cast<uint4*>(dx + row * width + c) = pack8(o);
       }
     }
@@ -413,13 +422,13 @@ int rms_norm_bwd_partials(int64_t rows) { return int((rows + ROWS_PER_CTA - 1) /
 
 cudaError_t rms_norm_bwd(const void* grad, const void* x, const void* w, const float* rstd,
                          void* dx, float* dw_partial, int64_t rows, int width,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const void* extra) {
   if (rows == 0) return cudaSuccess;
   if (width % 8 || width > NT * 8 * MAX_CHUNKS) return cudaErrorInvalidValue;
   rms_norm_bwd_kernel<<<rms_norm_bwd_partials(rows), NT, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(grad), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial,
-      int(rows), width);
+      int(rows), width, static_cast<const __nv_bfloat16*>(extra));
   return cudaGetLastError();
 }
 

@@ -246,9 +246,8 @@ class _Layer(torch.autograd.Function):
             dn2 = _gemm(dgate, wg, trans_b=False)
             _gemm(dup, wu, trans_b=False, out=dn2, accumulate=True)
             del dgate, dup, n2
-        dh1, dw_post = C.rms_norm_bwd(dn2, h1, w_post, rstd2)
+        dh1, dw_post = C.rms_norm_bwd_add(dn2, h1, w_post, rstd2, dy2)   # + the residual branch
         del dn2, h1
-        dh1.add_(dy2)
         # ---- output projection backward
         dwo = _wgrad(wo, dh1, attn2)
         dattn = _gemm(dh1, wo, trans_b=False).view(b, n, heads, 128)
@@ -292,8 +291,7 @@ class _Layer(torch.autograd.Function):
             dn1 = _gemm(dq2, wq, trans_b=False)
             _gemm(dk2, wk, trans_b=False, out=dn1, accumulate=True)
             _gemm(dv2, wv, trans_b=False, out=dn1, accumulate=True)
-        dx, dw_in = C.rms_norm_bwd(dn1, x2, w_in, rstd1)
-        dx.add_(dh1)
+        dx, dw_in = C.rms_norm_bwd_add(dn1, x2, w_in, rstd1, dh1)        # + the residual branch
         native.count(20)
         # Vector gradients go into the parameters' gradient buffers here as well (autograd would
         # only add returned values after this function), so that the layer can be reported to
