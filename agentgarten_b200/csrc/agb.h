@@ -127,8 +127,9 @@ cudaError_t silu_mul_fwd(const void* gate, const void* up, void* out, int64_t el
 // out[r, c] = bf16(silu(both[r, c])) * both[r, width + c] for both = [rows, 2 * width].
 cudaError_t silu_mul_pair(const void* both, void* out, int64_t rows, int width, cudaStream_t stream);
 // dboth = [dgate | dup] for grad [rows, width] and both = [gate | up] ([rows, 2 * width]).
+// act (bf16 [rows, width], may be null) also receives the forward value silu(gate) * up.
 cudaError_t silu_mul_pair_bwd(const void* grad, const void* both, void* dboth, int64_t rows,
-                              int width, cudaStream_t stream);
+                              int width, cudaStream_t stream, void* act = nullptr);
 cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, void* dgate,
                          void* dup, int64_t elements, cudaStream_t stream);
 // mode 0: (1-s)*a + s*b; mode 1: a - s*b.  sigma fp32 [batch, sigma_frames]

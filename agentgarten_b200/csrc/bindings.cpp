@@ -219,6 +219,20 @@ Tensor silu_mul_pair_bwd(const Tensor& grad, const Tensor& both) {
   return dboth;
 }
 
+// (dboth, act): the gradient of both = [gate | up] and the forward activation, in one pass.
+std::tuple<Tensor, Tensor> silu_mul_pair_bwd_act(const Tensor& grad, const Tensor& both) {
+  check_bf16(both, "both");
+  TORCH_CHECK(both.dim() == 2 && both.is_contiguous() && grad.is_contiguous() &&
+                  grad.size(0) == both.size(0) && 2 * grad.size(1) == both.size(1) && grad.size(1) % 8 == 0,
+              "silu_mul_pair_bwd_act takes grad [rows, width] and both [rows, 2 * width]");
+  c10::cuda::CUDAGuard guard(both.device());
+  auto dboth = torch::empty_like(both);
+  auto act = torch::empty_like(grad);
+  check(agb::silu_mul_pair_bwd(grad.data_ptr(), both.data_ptr(), dboth.data_ptr(), both.size(0),
+                               int(grad.size(1)), stream_of(both), act.data_ptr()), "silu_mul_pair_bwd_act");
+  return {dboth, act};
+}
+
 std::tuple<Tensor, Tensor> silu_mul_bwd(const Tensor& grad, const Tensor& gate, const Tensor& up) {
   c10::cuda::CUDAGuard guard(gate.device());
   auto dgate = torch::empty_like(gate);
@@ -1007,6 +1021,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("silu_mul_bwd", &silu_mul_bwd);
   m.def("silu_mul_pair", &silu_mul_pair);
   m.def("silu_mul_pair_bwd", &silu_mul_pair_bwd);
+  m.def("silu_mul_pair_bwd_act", &silu_mul_pair_bwd_act);
   m.def("rf_combine", &rf_combine);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

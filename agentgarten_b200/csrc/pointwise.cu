@@ -502,9 +502,13 @@ cudaError_t silu_mul_pair(const void* both, void* out, int64_t rows, int width, 
 }
 
 // Backward of silu_mul_pair: grad [rows, width], both = [gate | up], dboth = [dgate | dup].
+// With `act` given it also writes the forward value silu(gate) * up (bit for bit what
+// silu_mul_pair gives), which the caller needs for the next weight gradient: one pass over
+// `both` instead of two.
 __global__ void __launch_bounds__(NT) silu_mul_pair_bwd_kernel(const __nv_bfloat16* __restrict__ grad,
                                                                const __nv_bfloat16* __restrict__ both,
                                                                __nv_bfloat16* __restrict__ dboth,
+                                                               __nv_bfloat16* __restrict__ act,
                                                                int64_t rows, int width) {
   const int per_row = width / 8;
   const int64_t vecs = rows * per_row;
@@ -524,16 +528,21 @@ __global__ void __launch_bounds__(NT) silu_mul_pair_bwd_kernel(const __nv_bfloat
     }
     *reinterpret_cast<uint4*>(dboth + row * 2 * width + col) = pack8(dg);
     *reinterpret_cast<uint4*>(dboth + row * 2 * width + width + col) = pack8(du);
+    if (act) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) d[k] = round_bf16(g[k] / (1.f + __expf(-g[k]))) * u[k];
+      *reinterpret_cast<uint4*>(act + row * width + col) = pack8(d);
+    }
   }
 }
 
 cudaError_t silu_mul_pair_bwd(const void* grad, const void* both, void* dboth, int64_t rows,
-                              int width, cudaStream_t stream) {
+                              int width, cudaStream_t stream, void* act) {
   if (rows == 0 || width == 0) return cudaSuccess;
   if (width % 8) return cudaErrorInvalidValue;
   silu_mul_pair_bwd_kernel<<<grid_for(rows * (width / 8)), NT, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(grad), static_cast<const __nv_bfloat16*>(both),
-      static_cast<__nv_bfloat16*>(dboth), rows, width);
+      static_cast<__nv_bfloat16*>(dboth), static_cast<__nv_bfloat16*>(act), rows, width);
   return cudaGetLastError();
 }
 

@@ -157,13 +157,15 @@ def _project_qkv(C, n1, weights, shape, cos, sin, eps):
     return q_lin, k_lin, q, k, v, rq, rk, joint
 
 
-def _gate_up(C, n2, wg, wu):
+def _gate_up(C, n2, wg, wu, activation: bool = True):
     """(activation, kept): silu(gate) * up of the normalised rows; ``kept`` is what the backward
-    needs of the projections: the joint [rows, gate | up] product, or the pair."""
+    needs of the projections: the joint [rows, gate | up] product, or the pair.  With
+    ``activation=False`` the joint form leaves the activation to the caller (the backward pass
+    gets it from the kernel that also produces the gradient of the product)."""
     wgu = _joined((wg, wu))
     if wgu is not None:
         both = _gemm(n2, wgu)
-        return C.silu_mul_pair(both), (both,)
+        return (C.silu_mul_pair(both) if activation else None), (both,)
     gate, up = _gemm(n2, wg), _gemm(n2, wu)
     return C.silu_mul_fwd(gate, up), (gate, up)
 
@@ -224,22 +226,26 @@ class _Layer(torch.autograd.Function):
         if ctx.kept_mlp is not None:
             h1, n2, rstd2, projected = ctx.kept_mlp
             ctx.kept_mlp = None
-            act = C.silu_mul_pair(projected[0]) if len(projected) == 1 else C.silu_mul_fwd(*projected)
+            act = None if len(projected) == 1 else C.silu_mul_fwd(*projected)
         else:
             h1 = _gemm(attn2, wo, residual=x2)
             n2, rstd2 = C.rms_norm_fwd(h1, w_post, eps)
-            act, projected = _gate_up(C, n2, wg, wu)
+            act, projected = _gate_up(C, n2, wg, wu, activation=False)
         # ---- MLP backward
-        dwd = _wgrad(wd, dy2, act)
         dact = _gemm(dy2, wd, trans_b=False)
-        del act
         if len(projected) == 1:   # gate | up came from one GEMM: one GEMM each way back as well
-            dboth = C.silu_mul_pair_bwd(dact, projected[0])
+            # one pass over the product gives its gradient and the activation the down projection's
+            # weight gradient needs
+            dboth, act = C.silu_mul_pair_bwd_act(dact, projected[0])
             del dact, projected
+            dwd = _wgrad(wd, dy2, act)
+            del act
             dwg, dwu = _wgrad_group((wg, wu), dboth, n2)
             dn2 = _gemm(dboth, _joined((wg, wu)), trans_b=False)
             del dboth, n2
         else:
+            dwd = _wgrad(wd, dy2, act)
+            del act
             dgate, dup = C.silu_mul_bwd(dact, *projected)
             del dact, projected
             dwg, dwu = _wgrad(wg, dgate, n2), _wgrad(wu, dup, n2)
