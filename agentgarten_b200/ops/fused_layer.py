@@ -324,11 +324,45 @@ def _accumulate(weight: torch.Tensor, grad):
     return grad.to(weight.dtype)
 
 
+_rope_cache: tuple | None = None   # (ids of the per-chunk tables, the tables, their concatenations)
+
+
+def _joined_ropes(ropes):
+    """The per-chunk cos / sin tables as one table each; the same list comes back for every layer
+    of a pass, so the concatenation is made once per pass."""
+    global _rope_cache
+    if len(ropes) == 1:
+        return ropes[0]
+    key = tuple(id(t) for pair in ropes for t in pair)
+    if _rope_cache is None or _rope_cache[0] != key:
+        cos = torch.cat([r[0] for r in ropes], dim=1)
+        sin = torch.cat([r[1] for r in ropes], dim=1)
+        _rope_cache = (key, list(ropes), (cos, sin))   # the sources are kept so that their ids stay theirs
+    return _rope_cache[2]
+
+
+def _whole_of(chunks, sizes):
+    """The tensor these chunks were split from by the previous layer's :func:`run`, when they are
+    exactly its pieces in order; else None.  Using it skips a concatenation per layer (and, in
+    the backward pass, the concatenation of the pieces' gradients)."""
+    whole = getattr(chunks[0], "_agb_whole", None)
+    if whole is None or getattr(whole, "_agb_sizes", None) != tuple(sizes):
+        return None
+    for index, chunk in enumerate(chunks):
+        if getattr(chunk, "_agb_whole", None) is not whole or getattr(chunk, "_agb_index", -1) != index:
+            return None
+    return whole
+
+
 def run(layer, chunks, ropes, attention, layer_index):
     sizes = [c.shape[1] for c in chunks]
-    x = chunks[0] if len(chunks) == 1 else torch.cat(chunks, dim=1)
-    cos = ropes[0][0] if len(ropes) == 1 else torch.cat([r[0] for r in ropes], dim=1)
-    sin = ropes[0][1] if len(ropes) == 1 else torch.cat([r[1] for r in ropes], dim=1)
+    if len(chunks) == 1:
+        x = chunks[0]
+    else:
+        x = _whole_of(chunks, sizes)
+        if x is None:
+            x = torch.cat(chunks, dim=1)
+    cos, sin = _joined_ropes(ropes)
     plan = attention.plan(len(chunks))
     text = attention.text
     text_k, text_v = text.keys[layer_index].contiguous(), text.values[layer_index].contiguous()
@@ -343,4 +377,10 @@ def run(layer, chunks, ropes, attention, layer_index):
     with span(f"layer {layer_index} forward"):
         y = _Layer.apply(x.contiguous(), cos.contiguous(), sin.contiguous(), layer, schedule,
                          text_k, text_v, valid, max(0, len(text.keys) - layer_index - 1), *weights)
-    return list(y.split(sizes, dim=1)) if len(sizes) > 1 else [y]
+    if len(sizes) == 1:
+        return [y]
+    pieces = list(y.split(sizes, dim=1))
+    y._agb_sizes = tuple(sizes)
+    for index, piece in enumerate(pieces):   # the next layer recognises them and takes y itself
+        piece._agb_whole, piece._agb_index = y, index
+    return pieces
