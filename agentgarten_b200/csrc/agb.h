@@ -98,7 +98,6 @@ cudaError_t tp_reduce_norm(const TpReduceArgs& args, cudaStream_t stream);
 // End of a step: adds 1 (release, system scope) to the `done` counter of every rank.
 cudaError_t tp_signal_done(int* const done[8], int world, cudaStream_t stream);
 
-
 // -------------------------------------------------------------------------- pointwise
 // All tensors bf16 unless stated.  `addend` may be null (plain RMSNorm); with it,
 // total_out = bf16(x + addend) is written and normalised.  rstd (fp32 [rows]) may be null.
@@ -137,6 +136,13 @@ cudaError_t silu_mul_bwd(const void* grad, const void* gate, const void* up, voi
 cudaError_t rf_combine(const void* a, const void* b, const float* sigma, void* out, int64_t batch,
                        int64_t channels, int frames, int hw, int sigma_frames, int mode,
                        int is_bf16, cudaStream_t stream);
+// Distribution-matching target in FP64: per sample (row of `per` fp32 elements) spread =
+// max(mean |estimate - teacher|, 1e-5), target = estimate - (fake - teacher) / spread.
+// `partial` and `squares` hold dmd_target_blocks() doubles per sample; `squares` receives the
+// per-block sums of float(step)^2.
+int dmd_target_blocks();
+cudaError_t dmd_target(const float* estimate, const float* fake, const float* teacher, double* partial,
+                       double* target, double* squares, int64_t batch, int64_t per, cudaStream_t stream);
 
 // -------------------------------------------------------------------------- attention
 // Segment-list flash attention, head_dim 128, bf16.  q [B, NQ, Hq, 128], k/v [B, NK, Hkv, 128]
@@ -291,6 +297,15 @@ cudaError_t blur_frames(const float* src, float* scratch, float* dst, const floa
                         int64_t images, int h, int w, cudaStream_t stream);
 cudaError_t warp_frames(const float* src, float* dst, const float* params, const uint8_t* copy, int64_t batch,
                         int channels, int frames, int h, int w, cudaStream_t stream);
+// resize_frames: [images, H, W] -> [images, OH, OW]; area = 1 takes the mean over each output
+// pixel's source bin (adaptive average pooling), area = 0 samples bilinearly with aligned pixel
+// centres.  stretch_frames: [B, planes, H, W] -> [B, planes, TH, TW], the four quadrants around
+// the centre resized bilinearly; top[b] / left[b] (0 <= top <= TH - H, 0 <= left <= TW - W) are
+// the rows / columns the upper / left half gains.
+cudaError_t resize_frames(const float* src, float* dst, int64_t images, int h, int w, int oh, int ow,
+                          int area, cudaStream_t stream);
+cudaError_t stretch_frames(const float* src, float* dst, const int* top, const int* left, int64_t batch,
+                           int64_t planes, int h, int w, int th, int tw, cudaStream_t stream);
 
 // ------------------------------------------------- all-to-all over peer memory (one node)
 // out[s] = block `rank` of rank s's `send`, for all s.  `recv[r]` is rank r's receive buffer

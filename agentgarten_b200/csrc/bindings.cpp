@@ -556,6 +556,61 @@ Tensor warp_frames(const Tensor& video, const Tensor& params, const Tensor& copy
   return out;
 }
 
+// [..., H, W] -> [..., OH, OW]: mean over source bins (area = true) or bilinear sampling.
+Tensor resize_frames(const Tensor& images, int64_t oh, int64_t ow, bool area) {
+  TORCH_CHECK(images.dim() >= 2, "resize_frames: at least [H, W]");
+  check_frames(images, images.dim(), "resize_frames");
+  const int64_t h = images.size(-2), w = images.size(-1);
+  TORCH_CHECK(h >= 1 && w >= 1 && oh >= 1 && ow >= 1, "resize_frames: empty extent");
+  c10::cuda::CUDAGuard guard(images.device());
+  auto shape = images.sizes().vec();
+  shape[shape.size() - 2] = oh;
+  shape[shape.size() - 1] = ow;
+  auto out = torch::empty(shape, images.options());
+  check(agb::resize_frames(images.data_ptr<float>(), out.data_ptr<float>(), images.numel() / (h * w), int(h),
+                           int(w), int(oh), int(ow), area ? 1 : 0, stream_of(images)), "resize_frames");
+  return out;
+}
+
+// [B, ..., H, W] -> [B, ..., TH, TW]: quadrant stretch; top / left are int32 [B] on the device.
+Tensor stretch_frames(const Tensor& video, const Tensor& top, const Tensor& left, int64_t th, int64_t tw) {
+  TORCH_CHECK(video.dim() >= 3, "stretch_frames: at least [B, H, W]");
+  check_frames(video, video.dim(), "stretch_frames");
+  const int64_t b = video.size(0), h = video.size(-2), w = video.size(-1);
+  TORCH_CHECK(h >= 2 && w >= 2 && th >= h && tw >= w, "stretch_frames: the target is smaller than the frame");
+  for (const Tensor* t : {&top, &left})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kInt32 && t->is_contiguous() && t->numel() == b,
+                "stretch_frames: top and left are contiguous int32 [B] on the device");
+  c10::cuda::CUDAGuard guard(video.device());
+  auto shape = video.sizes().vec();
+  shape[shape.size() - 2] = th;
+  shape[shape.size() - 1] = tw;
+  auto out = torch::empty(shape, video.options());
+  check(agb::stretch_frames(video.data_ptr<float>(), out.data_ptr<float>(), top.data_ptr<int>(),
+                            left.data_ptr<int>(), b, b ? video.numel() / (b * h * w) : 0, int(h), int(w), int(th),
+                            int(tw), stream_of(video)), "stretch_frames");
+  return out;
+}
+
+// Distribution-matching target: fp32 [B, ...] inputs -> (fp64 target, fp64 [B, blocks] sums of
+// float(step)^2 whose total over the element count is the mean square of the step).
+std::tuple<Tensor, Tensor> dmd_target(const Tensor& estimate, const Tensor& fake, const Tensor& teacher) {
+  for (const Tensor* t : {&estimate, &fake, &teacher})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == torch::kFloat32 && t->is_contiguous() &&
+                    t->sizes() == estimate.sizes() && t->dim() >= 2,
+                "dmd_target: three contiguous fp32 CUDA tensors of one shape [B, ...]");
+  c10::cuda::CUDAGuard guard(estimate.device());
+  const int64_t b = estimate.size(0), per = b ? estimate.numel() / b : 0;
+  const auto wide = estimate.options().dtype(torch::kFloat64);
+  auto target = torch::empty(estimate.sizes(), wide);
+  auto partial = torch::empty({b, agb::dmd_target_blocks()}, wide);
+  auto squares = torch::zeros({b, agb::dmd_target_blocks()}, wide);
+  check(agb::dmd_target(estimate.data_ptr<float>(), fake.data_ptr<float>(), teacher.data_ptr<float>(),
+                        partial.data_ptr<double>(), target.data_ptr<double>(), squares.data_ptr<double>(), b, per,
+                        stream_of(estimate)), "dmd_target");
+  return {target, squares};
+}
+
 Tensor decode_normal(const Tensor& normal) {
   TORCH_CHECK(normal.is_cuda() && normal.scalar_type() == torch::kUInt8 && normal.dim() == 5 &&
                   normal.size(1) == 3 && normal.is_contiguous(), "decode_normal: normal is contiguous uint8 [B, 3, T, H, W]");
@@ -1041,6 +1096,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("pool_frames", &pool_frames);
   m.def("blur_frames", &blur_frames);
   m.def("warp_frames", &warp_frames);
+  m.def("resize_frames", &resize_frames);
+  m.def("stretch_frames", &stretch_frames);
+  m.def("dmd_target", &dmd_target);
   m.def("norm_modulate", &norm_modulate);
   m.def("gated_residual", &gated_residual);
   m.def("attn_jvp", &attn_jvp);

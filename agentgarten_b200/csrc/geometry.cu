@@ -162,6 +162,98 @@ cudaError_t decode_normal(const void* normal, float* out, int64_t batch, int64_t
 }
 
 
+// ------------------------------------------------------------------ resampling
+// Bilinear source position of output index `o` when `in` samples are resized to `out` with
+// pixel centres aligned (the half-pixel rule of interpolate(..., align_corners=False)):
+// the lower sample, whether an upper one exists, and the weight of the upper one.
+struct Lerp {
+  int lo, step;
+  float w;
+};
+__device__ __forceinline__ Lerp lerp_of(int o, int in, int out) {
+  const float scale = float(in) / float(out);
+  float src = scale * (float(o) + 0.5f) - 0.5f;
+  src = src < 0.f ? 0.f : src;
+  Lerp r;
+  r.lo = min(int(src), in - 1);
+  r.step = r.lo < in - 1 ? 1 : 0;
+  r.w = src - float(r.lo);
+  return r;
+}
+
+// Mean over the source bin of each output pixel, bins as in adaptive average pooling:
+// [floor(o * in / out), ceil((o + 1) * in / out)).
+__global__ void __launch_bounds__(NT) area_frames_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                         int64_t images, int h, int w, int oh, int ow) {
+  const int64_t total = images * oh * ow;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int x = int(i % ow), y = int((i / ow) % oh);
+    const float* plane = src + (i / (int64_t(ow) * oh)) * int64_t(h) * w;
+    const int y0 = int(int64_t(y) * h / oh), y1 = int((int64_t(y + 1) * h + oh - 1) / oh);
+    const int x0 = int(int64_t(x) * w / ow), x1 = int((int64_t(x + 1) * w + ow - 1) / ow);
+    float sum = 0.f;
+    for (int yy = y0; yy < y1; ++yy)
+      for (int xx = x0; xx < x1; ++xx) sum += plane[int64_t(yy) * w + xx];
+    dst[i] = sum / float((y1 - y0) * (x1 - x0));
+  }
+}
+
+__global__ void __launch_bounds__(NT) bilinear_frames_kernel(const float* __restrict__ src,
+                                                             float* __restrict__ dst, int64_t images, int h,
+                                                             int w, int oh, int ow) {
+  const int64_t total = images * oh * ow;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int x = int(i % ow), y = int((i / ow) % oh);
+    const float* plane = src + (i / (int64_t(ow) * oh)) * int64_t(h) * w;
+    const Lerp ly = lerp_of(y, h, oh), lx = lerp_of(x, w, ow);
+    const float* r0 = plane + int64_t(ly.lo) * w + lx.lo;
+    const float* r1 = r0 + int64_t(ly.step) * w;
+    const float top = (1.f - lx.w) * r0[0] + lx.w * r0[lx.step];
+    const float bottom = (1.f - lx.w) * r1[0] + lx.w * r1[lx.step];
+    dst[i] = (1.f - ly.w) * top + ly.w * bottom;
+  }
+}
+
+// Quadrant stretch of [B, planes, H, W] to [B, planes, TH, TW]: the upper H/2 rows are resized
+// bilinearly to H/2 + top[b] rows and the lower ones take the rest of TH; then the left W/2
+// columns to W/2 + left[b] and the right ones the rest of TW.  Rows first, columns second, as
+// two separate resizes would round.
+__global__ void __launch_bounds__(NT) stretch_frames_kernel(const float* __restrict__ src,
+                                                            float* __restrict__ dst,
+                                                            const int* __restrict__ top,
+                                                            const int* __restrict__ left, int64_t batch,
+                                                            int64_t planes, int h, int w, int th, int tw) {
+  const int64_t total = batch * planes * th * tw;
+  const int up = h / 2, left_w = w / 2;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < total; i += int64_t(gridDim.x) * NT) {
+    const int x = int(i % tw), y = int((i / tw) % th);
+    const int64_t plane_index = i / (int64_t(tw) * th);
+    const int64_t sample = plane_index / planes;
+    const float* plane = src + plane_index * int64_t(h) * w;
+    const int rows_above = up + top[sample], cols_left = left_w + left[sample];
+    Lerp ly, lx;
+    int y_base = 0, x_base = 0;
+    if (y < rows_above) {
+      ly = lerp_of(y, up, rows_above);
+    } else {
+      ly = lerp_of(y - rows_above, h - up, th - rows_above);
+      y_base = up;
+    }
+    if (x < cols_left) {
+      lx = lerp_of(x, left_w, cols_left);
+    } else {
+      lx = lerp_of(x - cols_left, w - left_w, tw - cols_left);
+      x_base = left_w;
+    }
+    const float* c0 = plane + int64_t(y_base + ly.lo) * w + x_base + lx.lo;
+    const float* c1 = c0 + lx.step;
+    const int64_t down = int64_t(ly.step) * w;
+    const float near = (1.f - ly.w) * c0[0] + ly.w * c0[down];
+    const float far = (1.f - ly.w) * c1[0] + ly.w * c1[down];
+    dst[i] = (1.f - lx.w) * near + lx.w * far;
+  }
+}
+
 static unsigned geometry_grid(int64_t total) {
   return unsigned(std::min<int64_t>((total + NT - 1) / NT, 148 * 32));
 }
@@ -191,6 +283,28 @@ cudaError_t warp_frames(const float* src, float* dst, const float* params, const
   if (total == 0) return cudaSuccess;
   warp_frames_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, dst, params, copy, batch, channels, frames,
                                                              h, w);
+  return cudaGetLastError();
+}
+
+cudaError_t resize_frames(const float* src, float* dst, int64_t images, int h, int w, int oh, int ow,
+                          int area, cudaStream_t stream) {
+  if (h < 1 || w < 1 || oh < 1 || ow < 1) return cudaErrorInvalidValue;
+  const int64_t total = images * int64_t(oh) * ow;
+  if (total == 0) return cudaSuccess;
+  if (area)
+    area_frames_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, dst, images, h, w, oh, ow);
+  else
+    bilinear_frames_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, dst, images, h, w, oh, ow);
+  return cudaGetLastError();
+}
+
+cudaError_t stretch_frames(const float* src, float* dst, const int* top, const int* left, int64_t batch,
+                           int64_t planes, int h, int w, int th, int tw, cudaStream_t stream) {
+  if (h < 2 || w < 2 || th < h || tw < w) return cudaErrorInvalidValue;
+  const int64_t total = batch * planes * int64_t(th) * tw;
+  if (total == 0) return cudaSuccess;
+  stretch_frames_kernel<<<geometry_grid(total), NT, 0, stream>>>(src, dst, top, left, batch, planes, h, w,
+                                                                th, tw);
   return cudaGetLastError();
 }
 

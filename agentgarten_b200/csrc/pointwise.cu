@@ -317,6 +317,59 @@ __global__ void __launch_bounds__(NT) rf_combine_kernel(const T* __restrict__ a,
   }
 }
 
+// ------------------------------------------------------ distribution-matching target
+// For each sample (row of `per` elements), all arithmetic in FP64 as the eager expression:
+//   spread = max(mean |estimate - teacher|, 1e-5)
+//   step   = (fake - teacher) / spread,   target = estimate - step
+// Pass one leaves per-block partial sums of |estimate - teacher| (no atomics: the sum has a
+// fixed order); pass two adds a sample's partials, writes the target and leaves per-block
+// partial sums of float(step)^2 for the reported root mean square.
+constexpr int DMD_BLOCKS = 32;  // blocks per sample in both passes
+
+__device__ __forceinline__ double block_sum(double v, double* shared) {
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if ((threadIdx.x & 31) == 0) shared[threadIdx.x >> 5] = v;
+  __syncthreads();
+  double total = 0.0;
+  for (int i = 0; i < NT / 32; ++i) total += shared[i];
+  __syncthreads();
+  return total;
+}
+
+__global__ void __launch_bounds__(NT) dmd_spread_kernel(const float* __restrict__ estimate,
+                                                        const float* __restrict__ teacher,
+                                                        double* __restrict__ partial, int64_t per) {
+  __shared__ double shared[NT / 32];
+  const int64_t base = int64_t(blockIdx.y) * per;
+  double sum = 0.0;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < per; i += int64_t(DMD_BLOCKS) * NT)
+    sum += fabs(double(estimate[base + i]) - double(teacher[base + i]));
+  sum = block_sum(sum, shared);
+  if (threadIdx.x == 0) partial[blockIdx.y * DMD_BLOCKS + blockIdx.x] = sum;
+}
+
+__global__ void __launch_bounds__(NT) dmd_target_kernel(const float* __restrict__ estimate,
+                                                        const float* __restrict__ fake,
+                                                        const float* __restrict__ teacher,
+                                                        const double* __restrict__ partial,
+                                                        double* __restrict__ target,
+                                                        double* __restrict__ squares, int64_t per) {
+  __shared__ double shared[NT / 32];
+  double total = 0.0;
+  for (int i = 0; i < DMD_BLOCKS; ++i) total += partial[blockIdx.y * DMD_BLOCKS + i];
+  const double spread = fmax(total / double(per), 1e-5);
+  const int64_t base = int64_t(blockIdx.y) * per;
+  double sum = 0.0;
+  for (int64_t i = int64_t(blockIdx.x) * NT + threadIdx.x; i < per; i += int64_t(DMD_BLOCKS) * NT) {
+    const double step = (double(fake[base + i]) - double(teacher[base + i])) / spread;
+    target[base + i] = double(estimate[base + i]) - step;
+    const float narrow = float(step);
+    sum += double(narrow * narrow);
+  }
+  sum = block_sum(sum, shared);
+  if (threadIdx.x == 0) squares[blockIdx.y * DMD_BLOCKS + blockIdx.x] = sum;
+}
+
 int grid_for(int64_t work_items) {
   const int64_t blocks = (work_items + NT - 1) / NT;
   return int(blocks < 148 * 16 ? (blocks > 0 ? blocks : 1) : 148 * 16);
@@ -679,6 +732,18 @@ cudaError_t rf_combine(const void* a, const void* b, const float* sigma, void* o
     rf_combine_kernel<float><<<grid_for(total), NT, 0, stream>>>(
         static_cast<const float*>(a), static_cast<const float*>(b), sigma,
         static_cast<float*>(out), total, per_sample, frames, hw, sigma_frames, mode);
+  return cudaGetLastError();
+}
+
+int dmd_target_blocks() { return DMD_BLOCKS; }
+
+cudaError_t dmd_target(const float* estimate, const float* fake, const float* teacher, double* partial,
+                       double* target, double* squares, int64_t batch, int64_t per, cudaStream_t stream) {
+  if (batch == 0 || per == 0) return cudaSuccess;
+  if (batch > 65535) return cudaErrorInvalidValue;
+  const dim3 grid(DMD_BLOCKS, unsigned(batch));
+  dmd_spread_kernel<<<grid, NT, 0, stream>>>(estimate, teacher, partial, per);
+  dmd_target_kernel<<<grid, NT, 0, stream>>>(estimate, fake, teacher, partial, target, squares, per);
   return cudaGetLastError();
 }
 

@@ -33,6 +33,7 @@ from typing import Any
 import torch
 from torch import Tensor, nn
 
+from agentgarten_b200 import ops
 from agentgarten_b200.infra.config import instantiate
 from agentgarten_b200.infra.model import StepOutput, TrainingClosureSpec
 from agentgarten_b200.infra.rng_state import isolated_rng
@@ -244,16 +245,13 @@ class DMDModel(ConditionedModel):
         noise = torch.randn_like(estimate)
         with torch.no_grad():
             noisy = rf_interpolate(estimate, noise, sigma)
-            by_fake = rf_x0(noisy, sigma, self._velocity(self.fake_score, anchor, noisy, sigma, prompts[0])).double()
-            by_teacher = rf_x0(noisy, sigma, self._teacher_velocity(anchor, noisy, sigma, prompts)).double()
-            wide = estimate.double()
-            spread = (wide - by_teacher).abs().flatten(1).mean(1).clamp_min(1e-5)
-            direction = (by_fake - by_teacher) / spread.view(-1, 1, 1, 1, 1)
-            target = wide - direction
+            by_fake = rf_x0(noisy, sigma, self._velocity(self.fake_score, anchor, noisy, sigma, prompts[0]))
+            by_teacher = rf_x0(noisy, sigma, self._teacher_velocity(anchor, noisy, sigma, prompts))
+            target, step_rms = ops.dmd_target(estimate, by_fake, by_teacher)
         push, report = None, {}
         if self.gan is not None:
             push, report = self._adversary.generator_gradient(anchor, real, estimate, noise, sigma, prompts[0])
-        report["metrics/student/dmd_gradient_rms"] = direction.float().square().mean().sqrt()
+        report["metrics/student/dmd_gradient_rms"] = step_rms
         return target, push, report
 
     def _fake_score_loss(self, anchor, real, generated, prompt, *, warmup: bool) -> StepOutput:

@@ -236,8 +236,14 @@ def _suppress_texture(videos, *, data_batch, config) -> dict[str, torch.Tensor]:
         f = float(factors[i])
         images = torch.cat([videos[n][i].permute(1, 0, 2, 3) for n in names], dim=1)
         images = _gaussian(images, f * config.texture_gaussian_sigma_scale)
-        low = F.interpolate(images, size=(max(1, round(h / f)), max(1, round(w / f))), mode="area")
-        smooth = F.interpolate(low, size=(h, w), mode="bilinear", align_corners=False)
+        low_size = (max(1, round(h / f)), max(1, round(w / f)))
+        fused = _fused_kernels(images) if images.dtype == torch.float32 else None
+        if fused is not None:
+            low = fused.resize_frames(images.contiguous(), *low_size, True)
+            smooth = fused.resize_frames(low, h, w, False)
+        else:
+            low = F.interpolate(images, size=low_size, mode="area")
+            smooth = F.interpolate(low, size=(h, w), mode="bilinear", align_corners=False)
         for n, part in zip(names, smooth.split(widths, dim=1), strict=True):
             out[n][i].copy_(part.permute(1, 0, 2, 3))
     return out
@@ -401,6 +407,13 @@ def stretch_geometry(videos, *, training: bool, divisor: int) -> dict[str, torch
         lefts = torch.full((b,), extra_w // 2, dtype=torch.long)
     names = tuple(videos)
     widths = [int(videos[n].shape[1]) for n in names]
+    fused = _fused_kernels(first) if first.dtype == torch.float32 and min(h, w) >= 2 else None
+    if fused is not None and all(videos[n].dtype == torch.float32 for n in names):
+        # one kernel for all samples and modalities: both resizes of every quadrant, no pieces
+        stacked = torch.cat([videos[n] for n in names], dim=1).contiguous()
+        grown = fused.stretch_frames(stacked, tops.to(first.device, torch.int32),
+                                     lefts.to(first.device, torch.int32), th, tw)
+        return dict(zip(names, grown.split(widths, dim=1), strict=True))
     rows: dict[str, list[torch.Tensor]] = {n: [] for n in names}
     up, left_w = h // 2, w // 2
     down, right_w = h - up, w - left_w

@@ -24,6 +24,7 @@ from .pointwise import (
     norm_modulate,
     rf_interpolate,
     rf_x0,
+    dmd_target,
     rms_norm,
     rms_norm_add,
     rotary,
@@ -47,6 +48,7 @@ __all__ = [
     "reference",
     "rf_interpolate",
     "rf_x0",
+    "dmd_target",
     "rms_norm",
     "rows_linear",
     "rms_norm_add",

@@ -201,3 +201,24 @@ def rf_x0(noisy, sigma, velocity):
         return C.rf_combine(noisy.contiguous(), velocity.contiguous(),
                             sigma.float().contiguous(), 1)
     return reference.rf_x0(noisy, sigma, velocity)
+
+
+def dmd_target(estimate, by_fake, by_teacher):
+    """Distribution-matching target in FP64 and the root mean square of its step.
+
+    Per sample ``spread = max(mean |estimate - by_teacher|, 1e-5)``; the step is
+    ``(by_fake - by_teacher) / spread`` and the target ``estimate - step`` (reference
+    ``wm/models/dmd.py:496-507``).  On a GPU two launches replace the chain of FP64 tensor
+    expressions; the sums run in a fixed order.
+    """
+    if (native.use(estimate, dtypes=(torch.float32,)) and not torch.is_grad_enabled()
+            and by_fake.dtype == by_teacher.dtype == torch.float32 and estimate.ndim >= 2
+            and estimate.shape == by_fake.shape == by_teacher.shape and estimate.shape[0] <= 65535):
+        C = native.ext()
+        native.count(2)
+        target, squares = C.dmd_target(estimate.contiguous(), by_fake.contiguous(), by_teacher.contiguous())
+        return target, (squares.sum() / max(1, estimate.numel())).sqrt().float()
+    wide, teacher = estimate.double(), by_teacher.double()
+    spread = (wide - teacher).abs().flatten(1).mean(1).clamp_min(1e-5)
+    step = (by_fake.double() - teacher) / spread.view(-1, *([1] * (estimate.ndim - 1)))
+    return wide - step, step.float().square().mean().sqrt()

@@ -776,6 +776,59 @@ def test_geometry_pool_blur_and_warp_kernels_match_the_library_formulation(monke
     assert torch.allclose(mine[1], want[1], atol=1e-5)
 
 
+def test_geometry_resize_and_stretch_kernels_match_the_library_formulation(monkeypatch):
+    """Texture suppression (area down, bilinear up) and the quadrant stretch against
+    ``F.interpolate``: the same functions of ``networks/cosmos3/geometry.py`` with the kernels on
+    and off, with the same random draws; extents that divide neither way."""
+    from agentgarten_b200.networks.cosmos3 import geometry
+
+    g = torch.Generator(device=DEV).manual_seed(13)
+    depth = torch.randn(3, 3, 4, 37, 53, device=DEV, generator=g)
+    normal = torch.randn(3, 3, 4, 37, 53, device=DEV, generator=g)
+    config = geometry.GeometryAugmentationConfig(texture_suppression_probability=1.0,
+                                                 texture_downsample_min=1.5, texture_downsample_max=3.7)
+
+    def run(training):
+        torch.manual_seed(9)
+        smooth = geometry._suppress_texture({"depth": depth, "normal": normal}, data_batch={}, config=config)
+        grown = geometry.stretch_geometry({"depth": depth, "normal": normal}, training=training, divisor=16)
+        return smooth, grown
+
+    for training in (True, False):
+        with monkeypatch.context() as patch:
+            before = native.launches()
+            mine = run(training)
+            assert native.launches() >= before + 3 * 2 + 1   # per sample the blur and the resizes; one stretch
+            patch.setattr(geometry, "_fused_kernels", lambda tensor: None)
+            want = run(training)
+        for name in ("depth", "normal"):
+            assert mine[1][name].shape == want[1][name].shape == (3, 3, 4, 48, 64)
+            for part in (0, 1):
+                error = float((mine[part][name] - want[part][name]).abs().max())
+                assert error < 2e-5, (training, part, name, error)
+
+
+def test_dmd_target_kernel_matches_the_fp64_expression():
+    """Target and step size of the distribution-matching loss: two launches against the chain of
+    FP64 tensor expressions, one sample with a spread below the floor."""
+    g = torch.Generator(device=DEV).manual_seed(17)
+    estimate = torch.randn(3, 16, 5, 12, 20, device=DEV, generator=g)
+    fake = estimate + 0.3 * torch.randn(estimate.shape, device=DEV, generator=g)
+    teacher = estimate + 0.2 * torch.randn(estimate.shape, device=DEV, generator=g)
+    teacher[2] = estimate[2] + 1e-7          # spread clamps to 1e-5
+    before = native.launches()
+    with torch.no_grad():
+        target, rms = ops.dmd_target(estimate, fake, teacher)
+    assert native.launches() == before + 2 and target.dtype == torch.float64
+    wide, far = estimate.double(), teacher.double()
+    spread = (wide - far).abs().flatten(1).mean(1).clamp_min(1e-5)
+    step = (fake.double() - far) / spread.view(-1, 1, 1, 1, 1)
+    assert torch.allclose(target, wide - step, rtol=1e-12, atol=1e-12)
+    assert float(rms) == pytest.approx(float(step.float().square().mean().sqrt()), rel=1e-5)
+    again, _ = ops.dmd_target(estimate, fake, teacher)   # gradients on: the tensor expressions
+    assert torch.allclose(again, target, rtol=1e-12, atol=1e-12)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 def test_rows_linear_matches_fp32_linear_and_its_gradients(dtype):
     """The timestep embedder's FP32 linears on their own kernels: values and all three gradients
