@@ -377,6 +377,16 @@ cudaError_t patch_layout(const void* src, void* dst, int64_t batch, int64_t chan
 // this GPU's own memory (calls made).  One launch: csrc/multimem.cu.
 cudaError_t multimem_max(void* local, void* multicast, int* state, const uint32_t* in, uint32_t* out, int n,
                          int world, int rank, int* status, uint64_t limit_ns, cudaStream_t stream);
+// All-gather / broadcast of a payload through multicast stores (csrc/multimem.cu): this GPU's
+// `bytes_mine` bytes (may be 0) go to `offset` of the shared payload of `bytes_total` bytes, and
+// the whole payload is copied to `out` once every GPU's part has landed.  Sizes, offset and both
+// pointers are multiples of 16; the symmetric buffer of `buffer_bytes` bytes holds a counter and
+// two halves of multimem_share_capacity(buffer_bytes) bytes; state is int32[2] in local memory,
+// zero before the first call.  Every GPU must make the same sequence of calls (same totals).
+int64_t multimem_share_capacity(int64_t buffer_bytes);
+cudaError_t multimem_share(void* local, void* multicast, int64_t buffer_bytes, int* state, const void* src,
+                           int64_t bytes_mine, int64_t offset, void* out, int64_t bytes_total, int world,
+                           int sm_count, int* status, uint64_t limit_ns, cudaStream_t stream);
 
 // y [m, n] = x [m, k] W[n, k]^T + b for a few FP32 rows (m <= 64 is the intended range), W and b in
 // bf16 or fp32; and its gradients dx [m, k], dw [n, k], db [n] in FP32 (any of the three may be null).

@@ -1003,6 +1003,26 @@ void multimem_max(const Tensor& buffer, int64_t multicast_ptr, const Tensor& sta
                           stream_of(buffer)), "multimem_max");
 }
 
+// All-gather / broadcast through multicast stores: `part` (uint8, may be empty) lands at `offset`
+// of a payload of out.numel() bytes on every GPU; `out` receives the whole payload.
+void multimem_share(const Tensor& buffer, int64_t multicast_ptr, const Tensor& state, const Tensor& part,
+                    int64_t offset, const Tensor& out, int64_t world, int64_t limit_ns) {
+  TORCH_CHECK(buffer.is_cuda() && buffer.is_contiguous() && state.is_cuda() &&
+                  state.scalar_type() == torch::kInt32 && state.numel() >= 2 &&
+                  part.scalar_type() == torch::kUInt8 && out.scalar_type() == torch::kUInt8 &&
+                  part.is_contiguous() && out.is_contiguous() && out.is_cuda(),
+              "multimem_share: contiguous byte tensors on the device");
+  TORCH_CHECK(multicast_ptr != 0, "multimem_share: no multicast mapping");
+  c10::cuda::CUDAGuard guard(buffer.device());
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  check(agb::multimem_share(buffer.data_ptr(), reinterpret_cast<void*>(multicast_ptr),
+                            int64_t(buffer.numel()) * int64_t(buffer.element_size()), state.data_ptr<int>(),
+                            part.numel() ? part.data_ptr() : nullptr, part.numel(), offset, out.data_ptr(),
+                            out.numel(), int(world), sms, status_word(buffer.device().index()).data_ptr<int>(),
+                            uint64_t(limit_ns), stream_of(buffer)), "multimem_share");
+}
+int64_t multimem_share_capacity(int64_t buffer_bytes) { return agb::multimem_share_capacity(buffer_bytes); }
+
 // A few FP32 rows through a wide linear layer in FP32, weights read as they are (bf16 or fp32).
 Tensor rows_linear_fwd(const Tensor& x, const Tensor& w, c10::optional<Tensor> bias) {
   const auto wt = w.scalar_type();
@@ -1063,6 +1083,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rows_linear_fwd", &rows_linear_fwd);
   m.def("rows_linear_bwd", &rows_linear_bwd);
   m.def("multimem_max", &multimem_max);
+  m.def("multimem_share", &multimem_share);
+  m.def("multimem_share_capacity", &multimem_share_capacity);
   m.def("rope_tables", &rope_tables);
   m.def("patch_layout", &patch_layout);
   m.def("gemm", &gemm);

@@ -89,6 +89,56 @@ __global__ void __launch_bounds__(MM_MAX) multimem_max_kernel(uint32_t* local, u
   if (i < n) out[i] = ok ? *reinterpret_cast<volatile uint32_t*>(mine + i) : in[i];
 }
 
+// ------------------------------------------------------------------ shared payloads
+// All-gather and broadcast through multicast stores.  The symmetric buffer holds an arrival
+// counter (first SHARE_HEADER bytes) and two payload halves used by alternating calls.  Each GPU
+// stores its part (possibly nothing) at its offset of the current half with multimem.st, so the
+// bytes land in every GPU's copy; each CTA then announces its stores with one multimem.red and
+// waits (bounded) until the CTAs of all GPUs have done so, and copies the whole payload from its
+// own copy into `out`.  Every GPU launches the same grid (it depends on the total size only),
+// at most one CTA per SM, so that all CTAs that wait on one another are resident.  A half is
+// rewritten two calls later, after the call in between has seen every GPU arrive, i.e. after
+// every GPU has finished copying out of it.  `state` (this GPU's memory): [0] calls made,
+// [1] arrivals expected before this call; the second kernel advances both.
+constexpr int SHARE_HEADER = 256;
+constexpr int SHARE_THREADS = 256;
+
+__device__ __forceinline__ void mm_store16(uint4* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc),
+               "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)),
+               "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+__global__ void __launch_bounds__(SHARE_THREADS) multimem_share_kernel(
+    char* local, char* mc, int64_t half_vecs, const int* state, const uint4* __restrict__ src, int64_t vec_mine,
+    int64_t vec_offset, uint4* __restrict__ out, int64_t vec_total, int world, int* status, uint64_t limit_ns) {
+  __shared__ int ok_shared;
+  const int call = state[0];
+  const int target = counter_add(state[1], world * int(gridDim.x));
+  const int64_t half = int64_t(call & 1) * half_vecs;
+  uint4* everywhere = reinterpret_cast<uint4*>(mc + SHARE_HEADER) + half + vec_offset;
+  const int64_t stride = int64_t(gridDim.x) * SHARE_THREADS;
+  for (int64_t i = int64_t(blockIdx.x) * SHARE_THREADS + threadIdx.x; i < vec_mine; i += stride)
+    mm_store16(everywhere + i, src[i]);
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mm_arrive(reinterpret_cast<int*>(mc));
+    ok_shared = mm_wait(reinterpret_cast<const int*>(local), target, status, limit_ns) ? 1 : 0;
+  }
+  __syncthreads();
+  if (!ok_shared) return;
+  const uint4* mine = reinterpret_cast<const uint4*>(local + SHARE_HEADER) + half;
+  for (int64_t i = int64_t(blockIdx.x) * SHARE_THREADS + threadIdx.x; i < vec_total; i += stride)
+    out[i] = __ldcg(mine + i);
+}
+
+__global__ void multimem_share_done_kernel(int* state, int arrivals) {
+  state[0] += 1;
+  state[1] = counter_add(state[1], arrivals);
+}
+
 }  // namespace
 
 cudaError_t multimem_max(void* local, void* multicast, int* state, const uint32_t* in, uint32_t* out, int n,
@@ -98,6 +148,32 @@ cudaError_t multimem_max(void* local, void* multicast, int* state, const uint32_
   }
   multimem_max_kernel<<<1, MM_MAX, 0, stream>>>(static_cast<uint32_t*>(local), static_cast<uint32_t*>(multicast),
                                                 state, in, out, n, world, rank, status, limit_ns);
+  return cudaGetLastError();
+}
+
+int64_t multimem_share_capacity(int64_t buffer_bytes) {
+  const int64_t half = (buffer_bytes - SHARE_HEADER) / 2;
+  return half < 16 ? 0 : half / 16 * 16;
+}
+
+cudaError_t multimem_share(void* local, void* multicast, int64_t buffer_bytes, int* state, const void* src,
+                           int64_t bytes_mine, int64_t offset, void* out, int64_t bytes_total, int world,
+                           int sm_count, int* status, uint64_t limit_ns, cudaStream_t stream) {
+  const int64_t capacity = multimem_share_capacity(buffer_bytes);
+  if (!local || !multicast || world < 1 || bytes_total < 16 || bytes_total > capacity || bytes_mine < 0 ||
+      offset < 0 || offset + bytes_mine > bytes_total || (bytes_mine | offset | bytes_total) % 16 != 0 ||
+      (bytes_mine > 0 && (!src || reinterpret_cast<uintptr_t>(src) % 16 != 0)) ||
+      reinterpret_cast<uintptr_t>(out) % 16 != 0 || sm_count < 1) {
+    return cudaErrorInvalidValue;
+  }
+  const int64_t vec_total = bytes_total / 16;
+  const int64_t wanted = (vec_total + SHARE_THREADS * 8 - 1) / (SHARE_THREADS * 8);
+  const int grid = int(wanted < sm_count ? wanted : sm_count);
+  multimem_share_kernel<<<grid, SHARE_THREADS, 0, stream>>>(
+      static_cast<char*>(local), static_cast<char*>(multicast), capacity / 16, state,
+      static_cast<const uint4*>(src), bytes_mine / 16, offset / 16, static_cast<uint4*>(out), vec_total, world,
+      status, limit_ns);
+  multimem_share_done_kernel<<<1, 1, 0, stream>>>(state, world * grid);
   return cudaGetLastError();
 }
 

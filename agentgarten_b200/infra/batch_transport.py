@@ -216,6 +216,9 @@ def prepare_batch(context, data_batch: Batch | None, *, owner_rank: int | None,
     if not mine:
         _, total = _layout(specs)
         buffer = torch.empty(max(total, 16), dtype=torch.uint8, device=device)
-    dist.broadcast(buffer, src=context.global_rank(int(owner_rank)), group=context.group)
+    from agentgarten_b200.parallel import switch_share
+
+    if not switch_share.broadcast(buffer, int(owner_rank), context.group):  # multicast stores in a node
+        dist.broadcast(buffer, src=context.global_rank(int(owner_rank)), group=context.group)
     _rng_adopt(rng)
     return _fill(skeleton, _unpack(specs, buffer))

@@ -55,6 +55,11 @@ class _Gather(torch.autograd.Function):
     @staticmethod
     def forward(ctx, value: torch.Tensor, group, rank: int, size: int) -> torch.Tensor:
         ctx.rank, ctx.size, ctx.local = rank, size, value.shape[1]
+        from agentgarten_b200.parallel import switch_share
+
+        stacked = switch_share.all_gather(value, group)   # one launch through the switch, or None
+        if stacked is not None:
+            return stacked.movedim(0, 1).reshape(value.shape[0], size * value.shape[1], *value.shape[2:])
         parts = [torch.empty_like(value) for _ in range(size)]
         dist.all_gather(parts, value.contiguous(), group=group)
         return torch.cat(parts, dim=1)

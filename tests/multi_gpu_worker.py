@@ -233,22 +233,62 @@ def check_switch_consensus(device, rank, world):
     consensus.release()
 
 
+def check_switch_share(device, rank, world):
+    """All-gather and broadcast through multicast stores against the library collectives: sizes
+    that are no multiple of 16 bytes, one that makes the buffer grow, repeated calls that reuse
+    both halves; then the context-parallel gather (values and gradient) on that path."""
+    from agentgarten_b200.ops import native
+    from agentgarten_b200.parallel import switch_share
+
+    g = torch.Generator(device=device).manual_seed(100 + rank)
+    used = None
+    for call, shape in enumerate([(1, 37, 5), (2, 300, 64), (1, 2048, 4096), (3, 7), (1, 2048, 4096),
+                                  (3 << 20, 5)]):
+        dtype = (torch.bfloat16, torch.float32)[call % 2]
+        value = torch.randn(shape, device=device, generator=g).to(dtype)
+        parts = [torch.empty_like(value) for _ in range(world)]
+        dist.all_gather(parts, value)
+        got = switch_share.all_gather(value)
+        used = got is not None
+        if used:
+            assert torch.equal(got, torch.stack(parts)), (call, shape)
+        payload = (value.float() * 3).to(dtype).view(torch.uint8).reshape(-1)[: value.numel() * 2 - 3]
+        payload = payload.clone()
+        want = payload.clone()
+        source = call % world
+        dist.broadcast(want, src=source)
+        if switch_share.broadcast(payload, source):
+            assert torch.equal(payload, want), (call, shape)
+    torch.cuda.synchronize()
+    assert int(native.ext().status(device.index).item()) == 0
+    from agentgarten_b200.networks.cosmos3.context_parallel import _Gather
+
+    local = torch.randn(2, 11, 24, device=device, generator=g, requires_grad=True)
+    whole = _Gather.apply(local, dist.group.WORLD, rank, world)
+    parts = [torch.empty_like(local) for _ in range(world)]
+    dist.all_gather(parts, local.detach())
+    assert torch.equal(whole, torch.cat(parts, dim=1))
+    weight = torch.randn(whole.shape, device=device, generator=torch.Generator(device=device).manual_seed(7))
+    (whole * weight).sum().backward()
+    assert torch.equal(local.grad, weight[:, rank * 11:(rank + 1) * 11] * world)
+    if rank == 0:
+        print("SWITCH_SHARE", "multimem" if used else "library path (no multicast mapping)")
+    dist.barrier()
+    switch_share.release()
+
+
 def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     device = distributed.init(device="cuda", backend="nccl")
     rank, world = dist.get_rank(), dist.get_world_size()
-    check_sharded_adam(device, rank, world)
-    dist.barrier()
-    check_overlapped_gradient_path(device, rank, world)
-    dist.barrier()
-    check_tensor_parallel_stream(device, rank, world)
-    dist.barrier()
-    check_context_parallel_training(device, rank, world)
-    dist.barrier()
-    check_peer_exchange(device, rank, world)
-    dist.barrier()
-    check_switch_consensus(device, rank, world)
-    dist.barrier()
+    checks = [check_sharded_adam, check_overlapped_gradient_path, check_tensor_parallel_stream,
+              check_context_parallel_training, check_peer_exchange, check_switch_consensus, check_switch_share]
+    wanted = sys.argv[1:]   # names of checks to run; all of them without arguments
+    for check in checks:
+        if wanted and check.__name__ not in wanted:
+            continue
+        check(device, rank, world)
+        dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK")
     dist.destroy_process_group()
