@@ -119,8 +119,15 @@ __global__ void __launch_bounds__(SHARE_THREADS) multimem_share_kernel(
   const int64_t half = int64_t(call & 1) * half_vecs;
   uint4* everywhere = reinterpret_cast<uint4*>(mc + SHARE_HEADER) + half + vec_offset;
   const int64_t stride = int64_t(gridDim.x) * SHARE_THREADS;
-  for (int64_t i = int64_t(blockIdx.x) * SHARE_THREADS + threadIdx.x; i < vec_mine; i += stride)
-    mm_store16(everywhere + i, src[i]);
+  int64_t i = int64_t(blockIdx.x) * SHARE_THREADS + threadIdx.x;
+  for (; i + 3 * stride < vec_mine; i += 4 * stride) {  // four loads in flight per thread
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = src[i + u * stride];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) mm_store16(everywhere + i + u * stride, v[u]);
+  }
+  for (; i < vec_mine; i += stride) mm_store16(everywhere + i, src[i]);
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -130,8 +137,15 @@ __global__ void __launch_bounds__(SHARE_THREADS) multimem_share_kernel(
   __syncthreads();
   if (!ok_shared) return;
   const uint4* mine = reinterpret_cast<const uint4*>(local + SHARE_HEADER) + half;
-  for (int64_t i = int64_t(blockIdx.x) * SHARE_THREADS + threadIdx.x; i < vec_total; i += stride)
-    out[i] = __ldcg(mine + i);
+  i = int64_t(blockIdx.x) * SHARE_THREADS + threadIdx.x;
+  for (; i + 3 * stride < vec_total; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = __ldcg(mine + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) out[i + u * stride] = v[u];
+  }
+  for (; i < vec_total; i += stride) out[i] = __ldcg(mine + i);
 }
 
 __global__ void multimem_share_done_kernel(int* state, int arrivals) {
