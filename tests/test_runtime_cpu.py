@@ -314,3 +314,19 @@ def test_poison_fills_data_buffers_only_when_asked(monkeypatch):
     assert torch.isnan(debug.poison(rows)).all()
     assert torch.isnan(debug.poison(torch.zeros(3, dtype=torch.float32))).all()
     assert debug.poison(torch.zeros(0)).numel() == 0
+
+
+def test_switch_share_declines_off_the_gpu_and_pads_to_whole_vectors():
+    """Without a process group, on CPU tensors or with the switch path switched off, the callers
+    keep their library collective; payloads are handed to the kernel in whole 16-byte vectors."""
+    from agentgarten_b200.parallel import switch_share
+
+    rows = torch.arange(21, dtype=torch.float32).reshape(3, 7)
+    assert switch_share.all_gather(rows) is None
+    assert switch_share.broadcast(rows, 0) is False
+    padded = switch_share._bytes_of(rows.to(torch.bfloat16))
+    assert padded.dtype == torch.uint8 and padded.numel() == 48 and padded.data_ptr() % 16 == 0
+    assert torch.equal(padded[:42].view(torch.bfloat16), rows.to(torch.bfloat16).reshape(-1))
+    whole = switch_share._bytes_of(torch.zeros(8, dtype=torch.float32))
+    assert whole.numel() == 32
+    assert switch_share._round_up(17, 16) == 32 and switch_share._round_up(32, 16) == 32
