@@ -72,7 +72,17 @@ def init(*, device=None, backend: str | None = None,
 
 
 def destroy_process_group() -> None:
+    """Ends the process group.  The peer-memory links of this package are keyed by their group and
+    hold symmetric buffers that were exchanged through it, so they are dropped first: a later
+    ``init`` in the same process starts from fresh links."""
     if dist.is_available() and dist.is_initialized():
+        import importlib
+
+        for name in ("peer_exchange", "consensus", "switch_share"):
+            try:
+                importlib.import_module(f"agentgarten_b200.parallel.{name}").release()
+            except Exception:  # a link that cannot be dropped must not keep the group alive
+                pass
         dist.destroy_process_group()
 
 
