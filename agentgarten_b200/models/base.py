@@ -21,44 +21,44 @@ from agentgarten_b200.parallel.engine import ParallelConfig, parallelize_network
 __all__ = ["ConditionedModel"]
 
 
+class _ClosedOptions(dict):
+    """Options whose key set is fixed when the model is built: a call may change values, not
+    add keys (a misspelt option must not be ignored silently for a whole sampling run)."""
+
+    def overridden(self, changes: Mapping[str, Any]) -> dict[str, Any]:
+        merged = dict(self)
+        for key, value in changes.items():
+            if key not in merged:
+                stray = sorted(name for name in changes if name not in self)
+                raise TypeError(f"unknown sampling options {stray}")
+            merged[key] = value
+        return merged
+
+
 class ConditionedModel(Model):
     # State-dict keys below these prefixes belong to frozen roles and are never saved;
-    # subclasses with more frozen networks (a teacher, say) append theirs.
+    # subclasses with more frozen networks (a teacher, say) list theirs as well.
     checkpoint_excluded_prefixes: ClassVar[tuple[str, ...]] = ("conditioner.",)
 
     def __init__(self, *, conditioner: nn.Module, sampling_defaults: Mapping[str, Any],
                  sampling: Mapping[str, Any] | None = None) -> None:
         super().__init__()
-        for parameter in conditioner.parameters():
-            parameter.requires_grad_(False)
-        self.conditioner = conditioner
-        self.sampling: dict[str, Any] = dict(sampling_defaults)
+        self.conditioner = conditioner.requires_grad_(False)
+        self.sampling = _ClosedOptions(sampling_defaults)
         self.sampling.update(sampling or {})
 
-    # -- placement ------------------------------------------------------------------------
     def parallelize_conditioner(self, config: ParallelConfig, device) -> None:
         """Only the text tower has weights worth placing; the codec loads itself lazily."""
         parallelize_network(self.conditioner.text_encoder, config, device)
 
-    # -- data -----------------------------------------------------------------------------
     def prepare_data_batch(self, data_batch: dict[str, Any]) -> dict[str, Any]:
+        """Raw batch -> latents and token ids, on the training device (cached keys pass through)."""
         return self.conditioner.encode(data_batch, training=self.training)
 
-    # -- checkpoints ----------------------------------------------------------------------
     def checkpoint_model_state_dict(self, state_dict: dict[str, Any]) -> dict[str, Any]:
         frozen = self.checkpoint_excluded_prefixes
-        kept = {}
-        for key, value in state_dict.items():
-            if not key.startswith(frozen):
-                kept[key] = value
-        return kept
+        return dict(item for item in state_dict.items() if not item[0].startswith(frozen))
 
-    # -- sampling -------------------------------------------------------------------------
     def sampling_options(self, overrides: Mapping[str, Any]) -> dict[str, Any]:
-        """Configured options with per-call ``overrides``; unknown keys are an error."""
-        stray = sorted(key for key in overrides if key not in self.sampling)
-        if stray:
-            raise TypeError(f"unknown sampling options {stray}")
-        merged = dict(self.sampling)
-        merged.update(overrides)
-        return merged
+        """Configured options with per-call ``overrides``; unknown keys are a ``TypeError``."""
+        return self.sampling.overridden(overrides)

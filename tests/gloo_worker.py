@@ -82,6 +82,38 @@ def case_kernel_status_of_one_rank_stops_every_rank():
     assert synchronize_found_nonfinite(scaler, (optimizer,), fallback_device="cpu") is False
 
 
+def case_a_rank_that_leaves_ends_the_next_collective_of_the_others():
+    """The last rank stops taking part between two steps (it simply never makes the next call):
+    with the short process-group timeout of the run the others get an error from their next
+    batch agreement instead of waiting for ever."""
+    import time
+
+    rank, world = dist.get_rank(), dist.get_world_size()   # the group was made with GROUP_TIMEOUT
+    context = ContextParallelContext(None)
+    iterator = iter([{"i": 0}] * 4)
+    batch, exhausted, _ = fetch_batch(context, iterator, sequence_index=0)   # a step everyone takes
+    assert not exhausted and batch == {"i": 0}
+    began = time.monotonic()
+    if rank == world - 1:
+        time.sleep(8.0)                  # between steps: no collective of this rank is in flight
+    else:
+        try:
+            fetch_batch(context, iterator, sequence_index=1)
+        except RuntimeError as error:
+            waited = time.monotonic() - began
+            assert waited < 30.0, waited
+            assert str(error), "the error carries the backend's message"
+        else:
+            raise AssertionError("rank %d went on without rank %d" % (rank, world - 1))
+    # The group is broken now and cannot serve the worker's closing barrier: every rank waits
+    # until all are past the timeout and ends here.
+    time.sleep(max(0.0, 12.0 - (time.monotonic() - began)))
+    if rank == 0:
+        print("CASE_OK", sys.argv[1], flush=True)
+    sys.stdout.flush()
+    os._exit(0)
+
+
 def case_uneven_end_stops_everyone():
     """Rank 0 runs out of data one batch early: all ranks report exhaustion together."""
     rank = dist.get_rank()
@@ -212,11 +244,14 @@ def case_node_groups_for_hybrid_sharding():
 
 
 CASES = {name[5:]: fn for name, fn in list(globals().items()) if name.startswith("case_")}
+# seconds after which a collective of the job's group gives up (the run's
+# ``runtime.process_group_timeout_seconds``); cases that let one run out choose a short one
+GROUP_TIMEOUT = {"a_rank_that_leaves_ends_the_next_collective_of_the_others": 4}
 
 
 def main():
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    dist.init_process_group("gloo", timeout=timedelta(seconds=120))
+    dist.init_process_group("gloo", timeout=timedelta(seconds=GROUP_TIMEOUT.get(sys.argv[1], 120)))
     try:
         CASES[sys.argv[1]]()
         dist.barrier()

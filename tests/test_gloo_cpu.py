@@ -28,6 +28,7 @@ def _run(case, ranks, port):
     ("context_parallel_matches_single_group", 2, 29645),
     ("node_groups_for_hybrid_sharding", 4, 29646),
     ("kernel_status_of_one_rank_stops_every_rank", 2, 29647),
+    ("a_rank_that_leaves_ends_the_next_collective_of_the_others", 3, 29648),
 ])
 def test_gloo_case(case, ranks, port):
     _run(case, ranks, port)
