@@ -129,6 +129,40 @@ def test_failed_write_never_publishes_latest(tmp_path, monkeypatch):
     assert (tmp_path / "ckpt" / "latest").read_text().strip() == "iter_000000001"
 
 
+def test_async_save_that_stalls_or_fails_is_reported_at_the_next_finalize(tmp_path, monkeypatch):
+    """The background write never finishes (a hung mount) or fails in its thread: the save call
+    itself returns, the error surfaces at ``finalize`` (a time-out after ``async_timeout_seconds``
+    in the first case) and `latest` still names the last complete checkpoint."""
+    from concurrent.futures import Future
+
+    import pytest
+    import torch.distributed.checkpoint as dcp
+
+    model, opt, sched = _job()
+    saver = DistributedCheckpointer(tmp_path / "ckpt", async_mode="thread")
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=1)
+    saver.finalize()
+    saver.async_timeout_seconds = 0.2                  # from here on a write gets 0.2 s
+    pointer = tmp_path / "ckpt" / "latest"
+    assert pointer.read_text().strip() == "iter_000000001"
+
+    never = Future()                                   # a write that does not come back
+    monkeypatch.setattr(dcp, "async_save", lambda *args, **kwargs: never)
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=2)       # returns at once
+    with pytest.raises(RuntimeError, match="iter_000000002"):
+        saver.finalize()
+    assert pointer.read_text().strip() == "iter_000000001"
+
+    failed = Future()
+    failed.set_exception(OSError("Input/output error"))
+    monkeypatch.setattr(dcp, "async_save", lambda *args, **kwargs: failed)
+    saver.save(model, {"net": opt}, {"net": sched}, None, iteration=3)
+    with pytest.raises(RuntimeError, match="Input/output error"):
+        saver.save(model, {"net": opt}, {"net": sched}, None, iteration=4)   # waits for 3 first
+    assert pointer.read_text().strip() == "iter_000000001"
+    saver.finalize_after_error()                       # nothing pending any more, nothing raised
+
+
 def test_failed_latest_publication_is_reported(tmp_path, monkeypatch):
     import pytest
 
