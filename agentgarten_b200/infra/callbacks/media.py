@@ -65,9 +65,17 @@ def _to_uint8(video: Tensor, float_range: str, chunk: int) -> Tensor:
     return out
 
 
-def video_batch_to_cpu_uint8(video: Tensor, *, layout: str = "BCTHW",
-                             float_range: str = "minus_one_one", frame_chunk_size: int = 8) -> list[Tensor]:
-    return [_to_uint8(v, float_range, frame_chunk_size) for v in _canonical(video, layout)]
+def _clips_uint8(value: Tensor, layout: str, float_range: str, frame_chunk_size: int) -> list[Tensor]:
+    """One CPU uint8 ``[T, H, W, 3]`` clip per sample (the layout the encoders take)."""
+    return [_to_uint8(v, float_range, frame_chunk_size) for v in _canonical(value, layout)]
+
+
+def video_batch_to_cpu_uint8(value: Tensor, *, layout: str = "BCTHW",
+                             float_range: str = "minus_one_one", frame_chunk_size: int = 8) -> Tensor:
+    """A media batch as one CPU uint8 tensor ``[B, C, T, H, W]``, converted a few frames at a
+    time (reference ``wm/infra/callbacks/media.py:84-100``)."""
+    clips = _clips_uint8(value, layout, float_range, frame_chunk_size)
+    return torch.stack([clip.permute(3, 0, 1, 2) for clip in clips])
 
 
 def _resize(pixels: Tensor, size: tuple[int, int], chunk: int) -> Tensor:
@@ -155,8 +163,7 @@ class ImageVideoArtifactWriter:
             for name, tensor in named.items():
                 if not torch.is_tensor(tensor):
                     continue
-                clips = video_batch_to_cpu_uint8(tensor, layout=self.layout, float_range=self.float_range,
-                                                 frame_chunk_size=self.frame_chunk_size)
+                clips = _clips_uint8(tensor, self.layout, self.float_range, self.frame_chunk_size)
                 for b, pixels in enumerate(clips):
                     yield str(name), b, len(clips), pixels
 

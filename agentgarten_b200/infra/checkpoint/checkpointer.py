@@ -104,11 +104,12 @@ def _nest(flat: Mapping[str, Any], prefix: str) -> dict[str, Any]:
 
 
 class DistributedCheckpointer:
-    def __init__(self, save_dir: str | Path, *, async_mode: str | None = "thread",
+    def __init__(self, save_dir: str | Path, *, async_mode: str | None = "disabled",
                  async_timeout_seconds: float = 3600.0) -> None:
         if async_mode not in (None, "none", "disabled", "thread"):
             raise ValueError(f"async_mode must be 'disabled' or 'thread', got {async_mode!r}")
         self.save_dir = Path(save_dir)
+        self.latest_path = self.save_dir / "latest"
         self.async_mode = None if async_mode in (None, "none", "disabled") else async_mode
         self.async_timeout_seconds = float(async_timeout_seconds)
         self._pending: _Pending | None = None
@@ -124,7 +125,7 @@ class DistributedCheckpointer:
         error = None
         if rank() == 0:
             try:
-                atomic_put_text(name + "\n", self.save_dir / "latest")
+                atomic_put_text(name + "\n", self.latest_path)
             except BaseException as e:
                 error = e
         raise_together("latest pointer publication", error)
@@ -206,10 +207,10 @@ class DistributedCheckpointer:
         return str(directory)
 
     # --------------------------------------------------------------- initial weights
-    def initialize_model(self, model: torch.nn.Module, model_initializations: Mapping[str, Any] | None,
+    def initialize_model(self, model: torch.nn.Module, initializations: Mapping[str, Any] | None,
                          *, resume: bool = False) -> None:
         """Apply the ``train.model_initializations`` overlays in order."""
-        for item in plan_model_initializations(dict(model_initializations or {}), resume=resume):
+        for item in plan_model_initializations(dict(initializations or {}), resume=resume):
             self.load(model, {}, {}, None, components=("model",), **item.load_kwargs())
 
     # ------------------------------------------------------------------------ load
@@ -221,7 +222,7 @@ class DistributedCheckpointer:
             return None
         if str(path) != "latest":
             return Path(path)
-        pointer = self.save_dir / "latest"
+        pointer = self.latest_path
         if not pointer.is_file():
             raise FileNotFoundError(f"No latest checkpoint pointer at {pointer}")
         target = pointer.read_text().strip()
@@ -237,10 +238,11 @@ class DistributedCheckpointer:
              model_key_prefix: str | None = None,
              model_key_prefixes: Iterable[str | None] | None = None,
              source_model_key_prefix: str | None = None,
-             source_model_key_patterns: Iterable[str] = ()) -> LoadResult:
+             source_model_key_patterns: Iterable[str] | None = None) -> LoadResult:
         import torch.distributed.checkpoint as dcp
         from torch.distributed.checkpoint import DefaultLoadPlanner
 
+        source_model_key_patterns = tuple(source_model_key_patterns or ())
         decision: list[Any] = [None, None]
         if rank() == 0:
             try:

@@ -46,18 +46,18 @@ def _apply_lrs(scheduler, lrs: list[float]) -> None:
     scheduler._last_lr = lrs
 
 
-def restore_lambda_lr_progress(scheduler, loaded: Mapping[str, Any], saved_fields: set[str]) -> bool:
+def restore_lambda_lr_progress(scheduler, loaded_state: Mapping[str, Any], saved_fields: set[str]) -> bool:
     if "last_epoch" not in saved_fields:
         return False
-    scheduler.last_epoch = int(loaded["last_epoch"])
+    scheduler.last_epoch = int(loaded_state["last_epoch"])
     if "_step_count" in saved_fields:
-        scheduler._step_count = int(loaded["_step_count"])
+        scheduler._step_count = int(loaded_state["_step_count"])
     _apply_lrs(scheduler, [base * fn(scheduler.last_epoch)
                            for base, fn in zip(scheduler.base_lrs, scheduler.lr_lambdas, strict=True)])
     return True
 
 
-def restore_closed_form_scheduler_progress(name: str, scheduler, loaded: Mapping[str, Any],
+def restore_closed_form_scheduler_progress(name: str, scheduler, loaded_state: Mapping[str, Any],
                                            saved_fields: set[str]) -> bool:
     if "last_epoch" not in saved_fields:
         return False
@@ -68,29 +68,29 @@ def restore_closed_form_scheduler_progress(name: str, scheduler, loaded: Mapping
         return False
     current = scheduler.state_dict()
     progress = {"last_epoch", "_step_count", "_last_lr", "_get_lr_called_within_step"}
-    if any(not option_equal(loaded[f], current[f]) for f in (set(loaded) & set(current)) - progress):
+    if any(not option_equal(loaded_state[f], current[f]) for f in (set(loaded_state) & set(current)) - progress):
         warn_rank0(f"Scheduler '{name}' resumed progress while keeping current recipe options.")
-    scheduler.last_epoch = int(loaded["last_epoch"])
+    scheduler.last_epoch = int(loaded_state["last_epoch"])
     if "_step_count" in saved_fields:
-        scheduler._step_count = int(loaded["_step_count"])
+        scheduler._step_count = int(loaded_state["_step_count"])
     _apply_lrs(scheduler, list(closed_form()))
     return True
 
 
-def restore_grad_scaler_progress(grad_scaler, current: Mapping[str, Any], loaded: Mapping[str, Any],
+def restore_grad_scaler_progress(grad_scaler, current_state: Mapping[str, Any], loaded_state: Mapping[str, Any],
                                  saved_fields: set[str]) -> bool:
     have = [f for f in ("scale", "_growth_tracker") if f in saved_fields]
-    if have and not current:
+    if have and not current_state:
         warn_rank0("Checkpoint has enabled GradScaler progress while the current GradScaler is "
                    "disabled; keeping it disabled.")
         return False
-    if not have or not current:
+    if not have or not current_state:
         return False
-    merged = dict(current)
+    merged = dict(current_state)
     for f in have:
-        merged[f] = loaded[f]
+        merged[f] = loaded_state[f]
     grad_scaler.load_state_dict(merged)
     recipe = ("growth_factor", "backoff_factor", "growth_interval")
-    if any(f in saved_fields and not option_equal(loaded[f], current[f]) for f in recipe):
+    if any(f in saved_fields and not option_equal(loaded_state[f], current_state[f]) for f in recipe):
         warn_rank0("GradScaler resumed scale progress while keeping current growth/backoff settings.")
     return True

@@ -58,55 +58,58 @@ def _stateful(loader: Any) -> bool:
         and callable(getattr(loader, "load_state_dict", None))
 
 
-def capture_dataloader_snapshot(loader: Any, runtime_metadata: Mapping[str, Any] | None,
+def capture_dataloader_snapshot(dataloader: Any, runtime_metadata: Mapping[str, Any] | None = None,
                                 ) -> DataloaderSnapshot | None:
-    support = gather_objects(_stateful(loader))
+    support = gather_objects(_stateful(dataloader))
     if not all(support):
         if any(support):
             warn_rank0("Only some ranks have a stateful dataloader; its cursor is not saved.")
         return None
     error, state = None, None
     try:
-        state = dict(loader.state_dict())
+        state = dict(dataloader.state_dict())
     except BaseException as e:  # reported collectively below
         error = e
     raise_together("dataloader snapshot", error)
     return DataloaderSnapshot(state, {"version": VERSION, "world_size": world_size(),
                                       "mesh": _plain((runtime_metadata or {}).get("mesh")),
-                                      "workers": _signature(loader)})
+                                      "workers": _signature(dataloader)})
 
 
-def save_dataloader_snapshot(directory: Path, snapshot: DataloaderSnapshot | None) -> None:
+def save_dataloader_snapshot(checkpoint_path: str | Path, snapshot: DataloaderSnapshot | None) -> None:
     if snapshot is None:
         return
+    checkpoint_path = Path(checkpoint_path)
     error = None
     try:
         buffer = io.BytesIO()
         torch.save(snapshot.state, buffer)
-        atomic_put(buffer.getvalue(), directory / "dataloader" / f"rank_{rank():05d}.pt")
+        atomic_put(buffer.getvalue(), checkpoint_path / "dataloader" / f"rank_{rank():05d}.pt")
         if rank() == 0:
             atomic_put_text(json.dumps(snapshot.metadata, sort_keys=True) + "\n",
-                            directory / "dataloader" / "metadata.json")
+                            checkpoint_path / "dataloader" / "metadata.json")
     except BaseException as e:
         error = e
     raise_together("dataloader sidecar write", error)
 
 
-def save_checkpoint_metadata(directory: Path, *, iteration: int,
-                             runtime_metadata: Mapping[str, Any] | None) -> None:
+def save_checkpoint_metadata(checkpoint_path: str | Path, *, iteration: int,
+                             runtime_metadata: Mapping[str, Any] | None = None) -> None:
+    checkpoint_path = Path(checkpoint_path)
     error = None
     if rank() == 0:
         try:
             payload = {"version": VERSION, "iteration": int(iteration), "world_size": world_size(),
                        "runtime": _plain(dict(runtime_metadata or {}))}
-            atomic_put_text(json.dumps(payload, sort_keys=True) + "\n", directory / "metadata.json")
+            atomic_put_text(json.dumps(payload, sort_keys=True) + "\n", checkpoint_path / "metadata.json")
         except BaseException as e:
             error = e
     raise_together("metadata write", error)
 
 
-def warn_runtime_metadata_changes(directory: Path, runtime_metadata: Mapping[str, Any] | None) -> None:
-    path = directory / "metadata.json"
+def warn_runtime_metadata_changes(checkpoint_path: str | Path,
+                                  runtime_metadata: Mapping[str, Any] | None = None) -> None:
+    path = Path(checkpoint_path) / "metadata.json"
     if rank() != 0 or not path.is_file():
         return
     try:
@@ -121,21 +124,22 @@ def warn_runtime_metadata_changes(directory: Path, runtime_metadata: Mapping[str
         warn_rank0("Runtime metadata (mesh / topology) differs from the checkpoint's.")
 
 
-def restore_dataloader_snapshot(directory: Path, loader: Any,
-                                runtime_metadata: Mapping[str, Any] | None) -> bool:
+def restore_dataloader_snapshot(checkpoint_path: str | Path, dataloader: Any,
+                                runtime_metadata: Mapping[str, Any] | None = None) -> bool:
     """Restore the cursor when the checkpoint's loader stream is the current one."""
-    support = gather_objects(_stateful(loader))
+    checkpoint_path = Path(checkpoint_path)
+    support = gather_objects(_stateful(dataloader))
     if not all(support):
         return False
     decision: list[Any] = [False, None]
     if rank() == 0:
-        meta_path = directory / "dataloader" / "metadata.json"
+        meta_path = checkpoint_path / "dataloader" / "metadata.json"
         try:
             if meta_path.is_file():
                 saved = json.loads(meta_path.read_text())
                 same = (int(saved.get("world_size", -1)) == world_size()
                         and saved.get("mesh") == _plain((runtime_metadata or {}).get("mesh"))
-                        and saved.get("workers") == _signature(loader))
+                        and saved.get("workers") == _signature(dataloader))
                 decision = [bool(same), None if same else "dataloader stream changed"]
             else:
                 decision = [False, "no dataloader sidecar"]
@@ -149,8 +153,8 @@ def restore_dataloader_snapshot(directory: Path, loader: Any,
         return False
     error = None
     try:
-        state = torch.load(directory / "dataloader" / f"rank_{rank():05d}.pt", weights_only=True)
-        loader.load_state_dict(state)
+        state = torch.load(checkpoint_path / "dataloader" / f"rank_{rank():05d}.pt", weights_only=True)
+        dataloader.load_state_dict(state)
     except BaseException as e:
         error = e
     raise_together("dataloader restore", error)

@@ -62,9 +62,9 @@ class LoRALinear(nn.Linear):
         nn.init.kaiming_uniform_(self.lora_A.weight, a=math.sqrt(5))
         nn.init.zeros_(self.lora_B.weight)
 
-    def forward(self, value: torch.Tensor) -> torch.Tensor:
-        base = ops.linear(value, self.weight, self.bias)
-        low = ops.linear(self.lora_dropout(value), self.lora_A.weight)
+    def forward(self, input: torch.Tensor) -> torch.Tensor:  # noqa: A002 (nn.Linear's name)
+        base = ops.linear(input, self.weight, self.bias)
+        low = ops.linear(self.lora_dropout(input), self.lora_A.weight)
         return base + ops.linear(low, self.lora_B.weight) * self.scaling
 
 

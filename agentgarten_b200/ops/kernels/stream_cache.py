@@ -13,12 +13,13 @@ from agentgarten_b200.ops import native, reference
 __all__ = ["relocate"]
 
 
-def relocate(source: torch.Tensor, destination: torch.Tensor, kept_prefix: int, shift: int,
+def relocate(source: torch.Tensor, out: torch.Tensor, kept_tokens: int, shift_tokens: int,
              rotation: tuple[torch.Tensor, torch.Tensor] | None = None) -> None:
-    """``destination[:, r] = source[:, r]`` for ``r < kept_prefix`` and
-    ``rotate(source[:, r + shift])`` behind it, for the ``source.shape[1] - shift`` rows
-    that survive.  ``source``/``destination`` are ``[1, N, H, D]``; ``rotation`` is a pair of
-    FP32 ``[1, N - shift, D]`` tables (``None``: plain move)."""
+    """``out[:, r] = source[:, r]`` for ``r < kept_tokens`` and
+    ``rotate(source[:, r + shift_tokens])`` behind it, for the ``source.shape[1] - shift_tokens``
+    rows that survive.  ``source`` / ``out`` are ``[1, N, H, D]``; ``rotation`` is a pair of
+    FP32 ``[1, N - shift_tokens, D]`` tables (``None``: plain move)."""
+    destination, kept_prefix, shift = out, kept_tokens, shift_tokens
     kept = source.shape[1] - shift
     if (native.use(source) and source.shape[-1] == 128 and source.shape[0] == 1
             and source[0].is_contiguous() and destination[0].is_contiguous()):

@@ -52,15 +52,20 @@ def map_tensors(value: Any, transform: Callable[[torch.Tensor], torch.Tensor]) -
     return visit(value)
 
 
-def to(value: Any, device: torch.device | str | None = None, dtype: torch.dtype | None = None,
-       non_blocking: bool = True) -> Any:
-    """Move tensors of a tree; ``dtype`` only applies to floating tensors."""
+def to(data: Any, device: torch.device | str | None = None, dtype: torch.dtype | None = None,
+       memory_format: torch.memory_format = torch.preserve_format) -> Any:
+    """Move / cast every tensor of a tree.  Copies to an accelerator are asynchronous (the source
+    may be pinned), copies to the host are not; a channels-last format is applied only to
+    tensors of the matching rank (4 for ``channels_last``, 5 for ``channels_last_3d``)."""
+    to_host = device is not None and torch.device(device).type == "cpu"
+    rank_of = {torch.channels_last: 4, torch.channels_last_3d: 5}
 
     def move(tensor: torch.Tensor) -> torch.Tensor:
-        target = dtype if (dtype is not None and tensor.is_floating_point()) else None
-        return tensor.to(device=device, dtype=target, non_blocking=non_blocking)
+        layout = memory_format if rank_of.get(memory_format, tensor.dim()) == tensor.dim() \
+            else torch.preserve_format
+        return tensor.to(device=device, dtype=dtype, memory_format=layout, non_blocking=not to_host)
 
-    return map_tensors(value, move)
+    return map_tensors(data, move)
 
 
 def set_random_seed(seed: int, by_rank: bool = False) -> None:

@@ -198,7 +198,7 @@ def test_media_names_and_uint8_conversion():
     assert "@120" in wide
     video = torch.stack([torch.full((3, 2, 4, 4), -1.0), torch.full((3, 2, 4, 4), 1.0)])
     frames = video_batch_to_cpu_uint8(video, layout="BCTHW", float_range="minus_one_one")
-    assert len(frames) == 2 and frames[0].dtype == torch.uint8
+    assert frames.shape == (2, 3, 2, 4, 4) and frames.dtype == torch.uint8 and frames.device.type == "cpu"
     assert int(frames[0].max()) == 0 and int(frames[1].min()) == 255
 
 
@@ -330,3 +330,74 @@ def test_switch_share_declines_off_the_gpu_and_pads_to_whole_vectors():
     whole = switch_share._bytes_of(torch.zeros(8, dtype=torch.float32))
     assert whole.numel() == 32
     assert switch_share._round_up(17, 16) == 32 and switch_share._round_up(32, 16) == 32
+
+
+def test_wandb_sinks_share_one_lazily_started_run(monkeypatch):
+    """A stand-in for the SDK records the calls: nothing happens before the first write, both
+    sinks log into one run, x-axes are declared once, media keys follow
+    ``<split>/batch_<index>/<artifact>``, the last close finishes the run, an asynchronous sink
+    survives a failing service, and a missing SDK is an error that names the extra."""
+    import sys
+    import types
+
+    from agentgarten_b200.infra.callbacks import wandb as sinks
+
+    calls = []
+    fake = types.ModuleType("wandb")
+    fake.run = None
+
+    def init(**kwargs):
+        calls.append(("init", kwargs))
+        fake.run = object()
+
+    def finish():
+        calls.append(("finish",))
+        fake.run = None
+
+    fake.init, fake.finish = init, finish
+    fake.login = lambda **kwargs: calls.append(("login", kwargs))
+    fake.define_metric = lambda pattern, step_metric: calls.append(("axis", pattern, step_metric))
+    fake.log = lambda payload, step: calls.append(("log", dict(payload), step))
+    fake.Image = lambda array: ("image", tuple(array.shape))
+    fake.Video = lambda data, format: ("video", format)
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    monkeypatch.setenv("WANDB_API_KEY", "k")
+
+    metrics = sinks.WandbMetricSink("proj", "grp", "run-1", "offline", step_metrics={"val/*": "val/step"})
+    media = sinks.WandbArtifactWriter("proj", group="grp", name="run-1", mode="offline", fps=4)
+    assert calls == [] and metrics.step_metrics == {"val/*": "val/step"} and media.fps == 4
+    metrics.write({"train/loss": 1.5}, iteration=3)
+    assert [c[0] for c in calls] == ["login", "init", "axis", "log"]
+    assert calls[1][1] == {"project": "proj", "group": "grp", "name": "run-1", "mode": "offline"}
+    assert calls[3] == ("log", {"train/loss": 1.5}, 3)
+    clip = torch.zeros(2, 3, 2, 8, 8)
+    media.write({"sample": clip, "still": torch.zeros(1, 3, 8, 8)}, output_dir="unused", split="validation",
+                iteration=4, rank=0, sample_batch_index=7)
+    assert [c[0] for c in calls].count("init") == 1
+    logged = calls[-1]
+    assert logged[0] == "log" and logged[2] == 4
+    assert set(logged[1]) == {"validation/batch_0007/sample/000", "validation/batch_0007/sample/001",
+                              "validation/batch_0007/still"}
+    assert logged[1]["validation/batch_0007/sample/000"] == ("video", "mp4")
+    assert logged[1]["validation/batch_0007/still"][0] == "image"
+    metrics.close()
+    assert ("finish",) not in calls          # the media writer still holds the run
+    media.close()
+    assert calls[-1] == ("finish",)
+    metrics.write({"train/loss": 2.0}, iteration=5)   # closed sinks stay quiet
+    assert calls[-1] == ("finish",)
+
+    # asynchronous writes: a service that fails once silences the sink, close() still returns
+    fake.log = lambda payload, step: (_ for _ in ()).throw(ConnectionError("service down"))
+    background = sinks.WandbMetricSink("proj", async_write=True)
+    background.write({"a": 1.0}, iteration=1)
+    background.write({"a": 2.0}, iteration=2)
+    background.close()
+    assert isinstance(background._worker_error, ConnectionError) and fake.run is None
+    background.write({"a": 3.0}, iteration=3)
+
+    monkeypatch.setitem(sys.modules, "wandb", None)    # import wandb -> ModuleNotFoundError
+    import pytest
+
+    with pytest.raises(ModuleNotFoundError, match=r"wm\[wandb\]"):
+        sinks.WandbMetricSink("proj").write({"a": 1.0}, iteration=1)
