@@ -35,7 +35,9 @@ def media_artifact_filename(*, artifact_name: str, iteration: int, rank: int, sa
                             extension: str, batch_index: int | None = None) -> str:
     numbers = (int(sample_batch_index),) + (() if batch_index is None else (int(batch_index),))
     tail = "_".join(f"{n:02d}" for n in numbers)
-    joiner = "@" if any(n >= 100 for n in numbers) else "_"
+    # as the reference writes them: the indices follow the name directly, with an "@" in between
+    # only when an index needs three digits (``wm/infra/callbacks/media.py:112-129``)
+    joiner = "@" if any(n >= 100 for n in numbers) else ""
     return f"Iter{int(iteration):09d}_Rank{int(rank):04d}_{_safe(artifact_name)}{joiner}{tail}.{extension}"
 
 

@@ -306,3 +306,40 @@ def test_checkpoints_interchange_with_the_reference(tmp_path):
     assert (theirs / "latest").read_text() == (mine / "latest").read_text()
     assert sorted(p.name for p in (theirs / "iter_000000002").iterdir()) == \
         sorted(p.name for p in (mine / "iter_000000002").iterdir())
+
+
+def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
+    """One probe file (``baseline/function_probe.py``) runs in the reference's process and in this
+    one: rectified-flow utilities and the UniPC solver, learning-rate factors, geometry
+    preprocessing with its seeded augmentations, media conversion and file names, history window,
+    phase clock, stream positions, seeded discriminator and LoRA initialisation are equal bit for
+    bit; the restructured VAE (channels-last, in-place causal history) agrees to rounding."""
+    import importlib.util
+
+    path = tmp_path / "functions.pt"
+    done = subprocess.run([sys.executable, str(ROOT / "baseline" / "function_probe.py"), str(path)],
+                          capture_output=True, text=True, timeout=900, env=reference_env(),
+                          cwd=str(ROOT / "baseline"))
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(path, weights_only=False)
+    spec = importlib.util.spec_from_file_location("function_probe", ROOT / "baseline" / "function_probe.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    ours = module.collect()
+    errors = {key: value for key, value in {**theirs, **ours}.items() if key.endswith("/error")}
+    assert not errors, errors
+    assert sorted(ours) == sorted(theirs)
+    assert len(ours) > 90
+    for key, want in theirs.items():
+        got = ours[key]
+        if not torch.is_tensor(want):
+            assert got == want, (key, got, want)
+            continue
+        assert torch.is_tensor(got) and got.shape == want.shape and got.dtype == want.dtype, key
+        if key.startswith("vae/"):
+            assert torch.allclose(got, want, atol=2e-5, rtol=1e-5), (key, float((got - want).abs().max()))
+        else:
+            assert torch.equal(torch.nan_to_num(got), torch.nan_to_num(want)), \
+                (key, float((torch.nan_to_num(got.double()) - torch.nan_to_num(want.double())).abs().max()))
+            if want.is_floating_point():
+                assert torch.equal(torch.isnan(got), torch.isnan(want)), key

@@ -193,7 +193,7 @@ def test_geometry_config_validation_and_stretch():
 def test_media_names_and_uint8_conversion():
     name = media_artifact_filename(artifact_name="comparison grid", iteration=12, rank=3,
                                    sample_batch_index=1, extension="mp4", batch_index=0)
-    assert name.startswith("Iter000000012_Rank0003_") and name.endswith("_01_00.mp4") and " " not in name
+    assert name == "Iter000000012_Rank0003_comparison_grid01_00.mp4"
     wide = media_artifact_filename(artifact_name="x", iteration=1, rank=0, sample_batch_index=120, extension="jpg")
     assert "@120" in wide
     video = torch.stack([torch.full((3, 2, 4, 4), -1.0), torch.full((3, 2, 4, 4), 1.0)])
