@@ -9,8 +9,11 @@ section that cannot run in one tree records ``"<section>/error"`` instead of sto
 Covered: rectified-flow utilities and the UniPC solver, learning-rate factors, geometry
 preprocessing and its seeded augmentations, media conversion and file names, the history window,
 the phase clock of the distillation recipe, the stream position policy, seeded initialisation of
-the discriminator head and of LoRA adapters, and the Wan 2.2 VAE (encode / decode of a small clip
-with shared random weights).
+the discriminator head and of LoRA adapters, the synthetic dataset and the stateful loader, a
+whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the metric callback,
+the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
+eviction, a prompt change and reference images, and the Wan 2.2 VAE (encode / decode of a small
+clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -178,6 +181,248 @@ def _seeded_modules(out: dict) -> None:
     out["lora/forward"] = tower.to_out(tower.to_q(torch.ones(3, 16))).detach()
 
 
+def _data(out: dict) -> None:
+    from wm.data.loader import StatefulDataLoader
+    from wm.data.video import SyntheticVideoDataset
+
+    dataset = SyntheticVideoDataset(length=11, num_frames=3, height=8, width=12, fps=12.0)
+    sample = dataset[4]
+    for key, value in sample.items():
+        out[f"data/sample/{key}"] = value
+    out["data/length"] = len(dataset)
+
+    class Indices(torch.utils.data.Dataset):
+        def __len__(self) -> int:
+            return 11
+
+        def __getitem__(self, index: int):
+            return {"index": torch.tensor(index)}
+
+    def order(loader, count):
+        seen, iterator = [], iter(loader)
+        for _ in range(count):
+            try:
+                seen.append(next(iterator)["index"].tolist())
+            except StopIteration:
+                seen.append("end")
+                iterator = iter(loader)
+        return seen
+
+    loader = StatefulDataLoader(Indices(), batch_size=2, shuffle=True, seed=5, num_workers=0, pin_memory=False)
+    out["data/len"] = len(loader)
+    out["data/signature"] = sorted((k, str(v)) for k, v in loader.resume_signature().items())
+    out["data/order"] = order(loader, 9)
+    cursor = dict(loader.state_dict())
+    out["data/cursor"] = sorted(cursor.items())
+    resumed = StatefulDataLoader(Indices(), batch_size=2, shuffle=True, seed=5, num_workers=0, pin_memory=False)
+    resumed.load_state_dict(cursor)
+    out["data/resumed"] = order(resumed, 4)
+    out["data/continued"] = order(loader, 4)
+    wrapped = StatefulDataLoader(Indices(), batch_size=2, shuffle=False, seed=5, num_workers=0, pin_memory=False,
+                                 drop_last=False)
+    wrapped.load_state_dict({"epoch": 1, "batch_offset": 8})
+    out["data/wrapped_cursor"] = sorted(wrapped.state_dict().items())
+    out["data/keep_last"] = order(wrapped, 7)
+
+
+def _training_loop(out: dict) -> None:
+    import json
+    import tempfile
+    from pathlib import Path
+
+    from wm.data.loader import StatefulDataLoader
+    from wm.infra.callbacks import CallbackGroup, GradClipMonitor, ScalarMetricCallback
+    from wm.infra.model import Model
+    from wm.infra.optim import LinearWarmup
+    from wm.infra.trainer import Trainer
+
+    class Toy(Model):
+        def __init__(self) -> None:
+            super().__init__(optimizer_parameter_groups=[{"patterns": r".*\.bias", "lr": 0.05}])
+            g = torch.Generator().manual_seed(61)
+            self.body, self.head = torch.nn.Linear(6, 4), torch.nn.Linear(4, 1)
+            with torch.no_grad():
+                for parameter in self.parameters():
+                    parameter.copy_(torch.randn(parameter.shape, generator=g) * 0.5)
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def _score(self, batch):
+            error = self.head(torch.tanh(self.body(batch["x"]))) - batch["y"]
+            loss = error.square().mean()
+            return {"metrics/mse": loss.detach(), "metrics/abs": error.abs().mean().detach(),
+                    "note": "not a metric"}, loss
+
+        def training_step(self, data_batch, iteration):
+            return self._score(data_batch)
+
+        def validation_step(self, data_batch, iteration):
+            return self._score(data_batch)
+
+        def sample(self, data_batch, **sampling_options):
+            return {}
+
+    class Rows(torch.utils.data.Dataset):
+        def __init__(self, count: int, seed: int) -> None:
+            g = torch.Generator().manual_seed(seed)
+            self.x, self.y = torch.randn(count, 6, generator=g), torch.randn(count, 1, generator=g) * 3.0
+
+        def __len__(self) -> int:
+            return len(self.x)
+
+        def __getitem__(self, index: int):
+            return {"x": self.x[index], "y": self.y[index], "sample_index": index}
+
+    class Sink:
+        def __init__(self) -> None:
+            self.rows = []
+
+        def write(self, metrics, *, iteration):
+            self.rows.append((int(iteration), sorted((str(k), float(v)) for k, v in metrics.items())))
+
+    model, sink = Toy(), Sink()
+    groups = model._group_trainable_parameters()
+    out["loop/groups"] = [(sorted(k for k in group if k != "params"), [tuple(p.shape) for p in group["params"]])
+                          for group in groups]
+    optimizer = torch.optim.SGD(groups, lr=0.2, momentum=0.5)
+    scheduler = torch.optim.lr_scheduler.LambdaLR(optimizer, lr_lambda=LinearWarmup(warmup_steps=4, start_factor=0.25))
+    model.optimizer_dict, model.scheduler_dict = {"net": optimizer}, {"net": scheduler}
+    with tempfile.TemporaryDirectory() as scratch:
+        monitor = GradClipMonitor(max_norm=0.75, spike_threshold=2.0, spike_ratio=1.5, warmup_updates=2,
+                              ema_decay=0.5, output_dir=scratch, sample_keys=("sample_index",))
+        metrics = ScalarMetricCallback(every_n=2, sinks=[sink])
+        group = CallbackGroup(config=None, trainer=None)
+        group._callbacks.extend([monitor, metrics])
+        trainer = Trainer(grad_accum_steps=2, callbacks=group, device=torch.device("cpu"))
+        train = StatefulDataLoader(Rows(13, 71), batch_size=2, shuffle=True, seed=9, num_workers=0, pin_memory=False)
+        held_out = StatefulDataLoader(Rows(6, 72), batch_size=2, shuffle=False, seed=9, num_workers=0,
+                                      pin_memory=False)
+        torch.manual_seed(8)
+        done = trainer.train(model, train, held_out, grad_scaler=torch.amp.GradScaler(device="cpu", enabled=False),
+                             max_iterations=7, validation_interval=3, max_val_steps=2, validate_at_start=True)
+        out["loop/iterations"] = int(done)
+        out["loop/spike_files"] = sorted(p.name for p in Path(scratch).rglob("*.json"))
+        spikes = []
+        for path in sorted(Path(scratch).rglob("*.json")):
+            event = json.loads(path.read_text())
+            spikes.append(sorted((k, v) for k, v in event.items() if k not in ("timestamp", "time", "host")))
+        out["loop/spikes"] = repr(spikes)
+    out["loop/metrics"] = sink.rows
+    out["loop/cursor"] = sorted(train.state_dict().items())
+    out["loop/lr"] = [float(group["lr"]) for group in optimizer.param_groups]
+    for name, value in model.state_dict().items():
+        out[f"loop/state/{name}"] = value
+
+
+def _tiny_decoders(out: dict) -> None:
+    import tempfile
+    from pathlib import Path
+
+    from wm.codecs import TAEW22SuperDecoder
+    from wm.codecs._taehv.taehv import TAEHV, StreamingTAEHV
+
+    def seeded(arch: str) -> TAEHV:
+        model = TAEHV(None, arch_name=arch).float().eval()
+        g = torch.Generator().manual_seed(81)
+        with torch.no_grad():
+            for name, tensor in sorted(model.state_dict().items()):
+                if tensor.is_floating_point():
+                    spread = (1.0 / max(1, tensor[0].numel())) ** 0.5 if tensor.ndim > 1 else 0.02
+                    tensor.copy_(torch.randn(tensor.shape, generator=g) * spread)
+        return model
+
+    g = torch.Generator().manual_seed(82)
+    latent = torch.randn(1, 3, 48, 4, 6, generator=g)           # N, T, C, H, W
+    frames = torch.rand(1, 9, 3, 32, 48, generator=g)
+    with torch.no_grad():
+        for arch in ("taew2_2", "taew2_2_super"):
+            model = seeded(arch)
+            out[f"tiny/{arch}/keys"] = sorted(model.state_dict())
+            out[f"tiny/{arch}/decode/parallel"] = model.decode_video(latent, parallel=True, show_progress_bar=False)
+            out[f"tiny/{arch}/decode/sequential"] = model.decode_video(latent, parallel=False,
+                                                                       show_progress_bar=False)
+            if arch == "taew2_2":
+                out["tiny/encode"] = model.encode_video(frames, parallel=True, show_progress_bar=False)
+                out["tiny/encode/sequential"] = model.encode_video(frames, parallel=False, show_progress_bar=False)
+                stream = StreamingTAEHV(model)
+                pieces = []
+                for index in range(latent.shape[1]):
+                    piece = stream.decode(latent[:, index:index + 1])
+                    while piece is not None:
+                        pieces.append(piece)
+                        piece = stream.decode()
+                pieces.extend(stream.flush_decoder())
+                out["tiny/stream"] = torch.cat(pieces, dim=1)
+        with tempfile.TemporaryDirectory() as scratch:
+            path = Path(scratch) / "taew2_2_super.pth"
+            torch.save(seeded("taew2_2_super").state_dict(), path)
+            decoder = TAEW22SuperDecoder(path)
+            clip = latent.transpose(1, 2).contiguous()           # N, 48, T, H, W
+            out["tiny/super/decode"] = decoder.decode(clip)
+            running = decoder.stream("cpu")
+            out["tiny/super/stream/0"] = running.decode(clip[:, :, :1])
+            out["tiny/super/stream/1"] = running.decode(clip[:, :, 1:])
+            running.reset()
+            out["tiny/super/stream/again"] = running.decode(clip[:, :, :2])
+
+
+def _streams(out: dict) -> None:
+    import os
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import batch_of, seeded_, tiny_config
+
+    from wm.codecs import Wan22VAECodec
+    from wm.models.flow import rf_interpolate
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+    from wm.networks.cosmos3.network import Cosmos3Condition
+    from wm.networks.cosmos3.reference import denoise_with_references
+    from wm.networks.cosmos3.streaming import Cosmos3Stream, StreamPolicy
+
+    config = tiny_config()
+    net = build_network(config, init_device="cpu").float().eval()
+    seeded_(net, 0)
+    cond = Cosmos3Conditioner(config=config, codec=Wan22VAECodec(pretrained_path="unused", decoder=None),
+                              geometry_noise_sigma=0.0, init_device="cpu", empty_prompt_ids=(3, 4, 5)).float()
+    seeded_(cond.text_encoder, 1)
+    batch = cond.encode(batch_of(13), training=False)
+    condition = cond.condition(batch)
+    other = cond.condition(cond.encode(batch_of(13, seed=4), training=False))
+    latent = batch["latent"]
+    noise = torch.randn(latent.shape, generator=torch.Generator().manual_seed(5))
+
+    def part(source, lo: int, hi: int) -> Cosmos3Condition:
+        return Cosmos3Condition(text=source.text, depth=source.depth[:, :, lo:hi],
+                                normal=source.normal[:, :, lo:hi], fps=source.fps)
+
+    with torch.no_grad():
+        for rope in ("absolute", "contiguous", "top_aligned"):
+            stream = Cosmos3Stream(net, StreamPolicy(block_frames=4, sink_frames=1, history_frames=4, rope=rope,
+                                                     train_frames=13))
+            stream.start(latent[:, :, :1], part(condition, 0, 1))
+            for block in range(3):
+                lo, hi = 1 + 4 * block, 5 + 4 * block
+                noisy = rf_interpolate(latent[:, :, lo:hi], noise[:, :, lo:hi], torch.tensor([0.6]))
+                if block == 2:
+                    stream.update_text(other.text)                  # a new prompt mid-stream
+                out[f"streams/{rope}/velocity/{block}"] = stream.denoise(noisy, torch.tensor([0.6]),
+                                                                         part(condition, lo, hi))
+                if block == 1 and rope == "top_aligned":
+                    references = [latent[:, :, 9:10], latent[:, :, 12:13]]
+                    out["streams/references"] = denoise_with_references(
+                        stream, noisy, torch.tensor([0.6]), part(condition, lo, hi), references)
+                    out["streams/no_references"] = denoise_with_references(
+                        stream, noisy, torch.tensor([0.6]), part(condition, lo, hi), [])
+                stream.commit(latent[:, :, lo:hi], part(condition, lo, hi))
+            out[f"streams/{rope}/keys"] = torch.stack([key.clone() for key in stream.keys])
+            out[f"streams/{rope}/values"] = torch.stack([value.clone() for value in stream.values])
+            stream.reset()
+            stream.start(latent[:, :, 1:2], part(condition, 1, 2))
+            out[f"streams/{rope}/restart"] = stream.denoise(noise[:, :, 2:6], torch.tensor([0.9]),
+                                                           part(condition, 2, 6))
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -210,7 +455,8 @@ def _vae(out: dict) -> None:
 
 
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
-            "seeded_modules": _seeded_modules, "vae": _vae}
+            "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
+            "tiny_decoders": _tiny_decoders, "streams": _streams, "vae": _vae}
 
 
 def collect(sections=None) -> dict:

@@ -310,15 +310,19 @@ def test_checkpoints_interchange_with_the_reference(tmp_path):
 
 def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     """One probe file (``baseline/function_probe.py``) runs in the reference's process and in this
-    one: rectified-flow utilities and the UniPC solver, learning-rate factors, geometry
-    preprocessing with its seeded augmentations, media conversion and file names, history window,
-    phase clock, stream positions, seeded discriminator and LoRA initialisation are equal bit for
-    bit; the restructured VAE (channels-last, in-place causal history) agrees to rounding."""
+    one.  Equal bit for bit: rectified-flow utilities and the UniPC solver, learning-rate factors,
+    geometry preprocessing with its seeded augmentations, media conversion and file names, history
+    window, phase clock, stream positions, seeded discriminator and LoRA initialisation, the
+    synthetic dataset and the stateful loader's order and cursor, a whole ``Trainer.train`` run on
+    a toy model (parameter groups, clipping and spike events, metric names and values at every
+    flush, validation, scheduler), and streams in all three position modes with eviction, a new
+    prompt mid-stream and reference images.  Equal to rounding: the restructured codecs (Wan 2.2
+    VAE, tiny decoders) and a stream restarted on its kept arenas."""
     import importlib.util
 
     path = tmp_path / "functions.pt"
     done = subprocess.run([sys.executable, str(ROOT / "baseline" / "function_probe.py"), str(path)],
-                          capture_output=True, text=True, timeout=900, env=reference_env(),
+                          capture_output=True, text=True, timeout=1800, env=reference_env(),
                           cwd=str(ROOT / "baseline"))
     assert done.returncode == 0, done.stderr[-3000:]
     theirs = torch.load(path, weights_only=False)
@@ -329,15 +333,19 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     errors = {key: value for key, value in {**theirs, **ours}.items() if key.endswith("/error")}
     assert not errors, errors
     assert sorted(ours) == sorted(theirs)
-    assert len(ours) > 90
+    assert len(ours) > 150
+
+    def to_rounding(key: str) -> bool:
+        return key.startswith(("vae/", "tiny/")) or key.endswith("/restart")
+
     for key, want in theirs.items():
         got = ours[key]
         if not torch.is_tensor(want):
             assert got == want, (key, got, want)
             continue
         assert torch.is_tensor(got) and got.shape == want.shape and got.dtype == want.dtype, key
-        if key.startswith("vae/"):
-            assert torch.allclose(got, want, atol=2e-5, rtol=1e-5), (key, float((got - want).abs().max()))
+        if to_rounding(key):
+            assert torch.allclose(got, want, atol=5e-5, rtol=1e-5), (key, float((got - want).abs().max()))
         else:
             assert torch.equal(torch.nan_to_num(got), torch.nan_to_num(want)), \
                 (key, float((torch.nan_to_num(got.double()) - torch.nan_to_num(want.double())).abs().max()))
