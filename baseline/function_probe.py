@@ -12,8 +12,8 @@ the phase clock of the distillation recipe, the stream position policy, seeded i
 the discriminator head and of LoRA adapters, the synthetic dataset and the stateful loader, a
 whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the metric callback,
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
-eviction, a prompt change and reference images, and the Wan 2.2 VAE (encode / decode of a small
-clip with shared random weights).
+eviction, a prompt change and reference images, ``sample()`` of the three objectives, and the
+Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -423,6 +423,83 @@ def _streams(out: dict) -> None:
                                                            part(condition, 2, 6))
 
 
+def _sampling(out: dict) -> None:
+    """``sample()`` of the three objectives on small towers, with a stand-in for the codec."""
+    import os
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import batch_of, seeded_, tiny_config
+
+    from wm.codecs import Wan22VAECodec
+    from wm.infra.parallel import ParallelConfig
+    from wm.models.autoregressive import AutoregressiveModel
+    from wm.models.diffusion import DiffusionModel
+    from wm.models.dmd import DMDModel
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+
+    def pixels(latent: torch.Tensor) -> torch.Tensor:
+        """Stands in for the VAE decoder (no weights here): three latent channels as 'pixels'."""
+        return (latent[:, :3] * 0.25).repeat_interleave(2, dim=-1)
+
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+
+    def conditioner():
+        made = Cosmos3Conditioner(config=config, geometry_noise_sigma=0.0, init_device="cpu",
+                                  empty_prompt_ids=(3, 4, 5),
+                                  codec=Wan22VAECodec(pretrained_path="unused", decoder=None))
+        made.codec.decode = pixels
+        return made
+
+    def finish(model):
+        model.parallelize("cpu")
+        seeded_(model.conditioner.text_encoder, 1)
+        return model.eval()
+
+    def record(label: str, panels) -> None:
+        out[f"sampling/{label}/panels"] = sorted(panels)
+        for name, value in panels.items():
+            out[f"sampling/{label}/{name}"] = value
+
+    def data_for(model, frames: int, seed: int):
+        batch = batch_of(frames, seed=seed)
+        batch["sample_id"] = torch.tensor([17])
+        batch["depth_video"] = torch.rand(1, 3, frames, 4, 4, generator=torch.Generator().manual_seed(seed))
+        return model.prepare_data_batch(batch)
+
+    net = build_network(config, init_device="cpu")
+    seeded_(net, 0)
+    bidirectional = finish(DiffusionModel(net=net, conditioner=conditioner(), parallel=plain,
+                                          conditioner_parallel=plain,
+                                          sampling={"num_steps": 3, "guidance": 2.0, "seed": 4}))
+    record("bidirectional", bidirectional.sample(data_for(bidirectional, 5, 11)))
+    record("bidirectional/plain", bidirectional.sample(data_for(bidirectional, 5, 11), guidance=1.0, seed=9))
+    try:
+        bidirectional.sample(data_for(bidirectional, 5, 11), steps=3)
+    except TypeError as error:
+        out["sampling/unknown_option"] = str(error)
+    for mode in ("teacher_forcing", "diffusion_forcing"):
+        net = build_network(config, init_device="cpu")
+        seeded_(net, 0)
+        model = finish(AutoregressiveModel(net=net, conditioner=conditioner(), mode=mode, block_frames=4,
+                                           parallel=plain, conditioner_parallel=plain))
+        out[f"sampling/{mode}/defaults"] = sorted((k, repr(v)) for k, v in model.sampling.items())
+        record(mode, model.sample(data_for(model, 9, 12), num_steps=2, guidance=1.5))
+        record(f"{mode}/window", model.sample(data_for(model, 9, 12), num_steps=2, guidance=1.0, sink_blocks=0,
+                                              recent_blocks=1))
+    towers = [build_network(config, init_device="cpu") for _ in range(3)]
+    for index, tower in enumerate(towers):
+        seeded_(tower, 20 + index)
+    distilled = finish(DMDModel(student=towers[0], real_score=towers[1], fake_score=towers[2],
+                                conditioner=conditioner(), block_frames=4, student_parallel=plain,
+                                score_parallel=plain, seed=3))
+    out["sampling/dmd/defaults"] = sorted((k, repr(v)) for k, v in distilled.sampling.items())
+    record("dmd", distilled.sample(data_for(distilled, 9, 13)))
+    kept = distilled.checkpoint_model_state_dict(dict(distilled.state_dict()))
+    out["sampling/dmd/saved_roles"] = sorted({key.split(".")[0] for key in kept})
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -456,7 +533,7 @@ def _vae(out: dict) -> None:
 
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
-            "tiny_decoders": _tiny_decoders, "streams": _streams, "vae": _vae}
+            "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "vae": _vae}
 
 
 def collect(sections=None) -> dict:
