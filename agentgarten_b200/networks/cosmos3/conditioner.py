@@ -64,7 +64,8 @@ class _Prompts:
         encoded = []
         for prompt in prompts:
             ids = self.tokenizer.apply_chat_template([{"role": "user", "content": prompt}], tokenize=True,
-                                                     add_generation_prompt=True, return_dict=False)
+                                                     add_generation_prompt=True, add_vision_id=False,
+                                                     return_dict=False)
             ids = ids.flatten().tolist() if torch.is_tensor(ids) else list(ids)
             encoded.append(ids[: self.max_tokens])
         longest = max(len(ids) for ids in encoded)

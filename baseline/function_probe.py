@@ -12,8 +12,8 @@ the phase clock of the distillation recipe, the stream position policy, seeded i
 the discriminator head and of LoRA adapters, the synthetic dataset and the stateful loader, a
 whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the metric callback,
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
-eviction, a prompt change and reference images, ``sample()`` of the three objectives, and the
-Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
+through the conditioner, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -500,6 +500,86 @@ def _sampling(out: dict) -> None:
     out["sampling/dmd/saved_roles"] = sorted({key.split(".")[0] for key in kept})
 
 
+def _conditioner_raw(out: dict) -> None:
+    """Raw batches through the conditioner: pixels, captions with their suffix, the negative
+    prompt, the geometry pipeline and its latent noise; the VAE encoder and the tokenizer are
+    replaced by simple deterministic stand-ins (no weights, no vocabulary files here)."""
+    import json
+    import os
+    import tempfile
+    from pathlib import Path
+
+    import transformers
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import seeded_, tiny_config
+
+    from wm.codecs import Wan22VAECodec
+    from wm.networks.cosmos3 import Cosmos3Conditioner
+    from wm.networks.cosmos3.geometry import GeometryAugmentationConfig
+
+    class Characters:
+        def apply_chat_template(self, messages, **options):
+            assert options == {"tokenize": True, "add_generation_prompt": True, "add_vision_id": False,
+                               "return_dict": False}, options
+            return [3 + ord(c) % 120 for c in messages[0]["content"]]
+
+    transformers.AutoTokenizer.from_pretrained = staticmethod(lambda *args, **kwargs: Characters())
+
+    def encode(pixels: torch.Tensor) -> torch.Tensor:
+        n, c, t, h, w = pixels.shape
+        low = torch.nn.functional.adaptive_avg_pool3d(pixels.float(), (1 + (t - 1) // 4, h // 16, w // 16))
+        return low.repeat(1, 16, 1, 1, 1).to(pixels.dtype)
+
+    g = torch.Generator().manual_seed(91)
+    raw = {
+        "video": torch.randint(0, 256, (2, 5, 3, 64, 96), generator=g, dtype=torch.uint8),
+        "depth": torch.rand(2, 5, 1, 64, 96, generator=g) * 20.0 + 0.5,
+        "normal": torch.randint(0, 256, (2, 5, 3, 64, 96), generator=g, dtype=torch.uint8),
+        "caption": ["  a red cube on a table ", "camera pans left."],
+        "fps": torch.tensor([16.0, 24.0]), "sample_id": torch.tensor([5, 6]),
+        "depth_scale": torch.tensor([1.0, 3.0]),
+        "depth_scale_jitter_eligible": torch.tensor([True, False]),
+        "depth_scale_jitter_bounds": torch.tensor([[0.5, 2.0], [0.5, 2.0]]),
+    }
+    augmentation = GeometryAugmentationConfig(
+        modality_dropout_probability=0.3, spatial_probability=1.0, spatial_max_scale=1.1,
+        spatial_max_shift_fraction=0.05, texture_suppression_probability=0.5, texture_downsample_min=1.5,
+        texture_downsample_max=2.5)
+    with tempfile.TemporaryDirectory() as scratch:
+        negative = Path(scratch) / "negative.json"
+        negative.write_text(json.dumps({"avoid": ["blur", "noise"], "style": "none."}))
+        conditioner = Cosmos3Conditioner(
+            config=tiny_config(), codec=Wan22VAECodec(pretrained_path="unused", decoder=None),
+            geometry_augmentation=augmentation, geometry_noise_sigma=0.4, empty_prompt_ids=(3, 4, 5),
+            tokenizer_path="unused", negative_prompt_path=str(negative), max_text_tokens=40, init_device="cpu")
+        conditioner.codec.encode = encode
+        seeded_(conditioner.text_encoder, 1)
+        conditioner = conditioner.float()
+        for training in (True, False):
+            label = "train" if training else "eval"
+            torch.manual_seed(13)
+            encoded = conditioner.encode({key: (value.clone() if torch.is_tensor(value) else list(value))
+                                          for key, value in raw.items()}, training=training)
+            out[f"raw/{label}/keys"] = sorted(encoded)
+            for key, value in encoded.items():
+                if torch.is_tensor(value):
+                    out[f"raw/{label}/{key}"] = value
+            condition = conditioner.condition(encoded, drop=torch.tensor([False, True]))
+            out[f"raw/{label}/depth"] = condition.depth
+            out[f"raw/{label}/normal"] = condition.normal
+            out[f"raw/{label}/text_valid"] = condition.text.valid_lengths
+            out[f"raw/{label}/text_keys"] = torch.stack(list(condition.text.keys))
+            if not training:
+                unwanted = conditioner.condition(encoded, negative=True)
+                out["raw/eval/negative_valid"] = unwanted.text.valid_lengths
+                out["raw/eval/negative_keys"] = torch.stack(list(unwanted.text.keys))
+                panels = conditioner.visuals(encoded)
+                out["raw/eval/panels"] = sorted(panels)
+                for name, value in panels.items():
+                    out[f"raw/eval/panel/{name}"] = value
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -533,7 +613,8 @@ def _vae(out: dict) -> None:
 
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
-            "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "vae": _vae}
+            "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
+            "vae": _vae}
 
 
 def collect(sections=None) -> dict:
