@@ -611,6 +611,50 @@ def _vae(out: dict) -> None:
         out["vae/single_frame"] = vae.encode(clip[:, :, :1], (0.0, 1.0), temporal_window=4)
 
 
+def artifact_exchange(save_to: str, load_from: str | None = None) -> dict:
+    """Export a small seeded student + text tower with ``save_artifact``; when ``load_from`` names
+    an export (of either tree), inspect and load it and return what came out."""
+    import os
+    from pathlib import Path
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import seeded_, tiny_config
+
+    from wm.inference.cosmos3 import (Cosmos3Artifact, Cosmos3ArtifactSpec, inspect_artifact, load_artifact,
+                                      save_artifact)
+    from wm.networks.cosmos3 import build_network
+    from wm.networks.cosmos3.network import Cosmos3TextEncoder
+
+    config = tiny_config()
+    lora = {"rank": 4, "alpha": 8.0, "dropout": 0.0, "target_modules": ["to_q", "to_out"]}
+    student = build_network(config, init_device="cpu", lora=lora).float()
+    text = Cosmos3TextEncoder(config).float()
+    seeded_(student, 30)
+    seeded_(text, 31)
+    spec = Cosmos3ArtifactSpec(checkpoint=Path(save_to), config=config, student=(), text=(),
+                               tokenizer_path=Path(save_to) / "tokenizer", prompt_pixel_frames=13, iteration=42,
+                               lora=lora)
+    root = save_artifact(Cosmos3Artifact(student, text, spec), save_to)
+    out: dict = {"saved/files": sorted(p.name for p in Path(root).iterdir()),
+                 "saved/student_keys": sorted(student.state_dict()), "saved/text_keys": sorted(text.state_dict())}
+    if load_from is not None:
+        found = inspect_artifact(load_from)
+        out["loaded/iteration"] = found.iteration
+        out["loaded/frames"] = found.prompt_pixel_frames
+        out["loaded/lora"] = sorted((k, repr(v)) for k, v in dict(found.lora).items())
+        out["loaded/tokenizer"] = Path(found.tokenizer_path).name
+        out["loaded/config"] = sorted((k, repr(v)) for k, v in vars(found.config).items()) \
+            if hasattr(found.config, "__dict__") else repr(found.config)
+        loaded = load_artifact(found, device="cpu", dtype=torch.float32)
+        out["loaded/report"] = sorted((k, repr(v)) for k, v in loaded.report.items()
+                                      if k not in ("checkpoint_path", "und_checkpoint_path", "implementation"))
+        for name, value in loaded.student.state_dict().items():
+            out[f"loaded/student/{name}"] = value
+        for name, value in loaded.context_encoder.state_dict().items():
+            out[f"loaded/text/{name}"] = value
+    return out
+
+
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
@@ -630,4 +674,7 @@ def collect(sections=None) -> dict:
 
 
 if __name__ == "__main__":
-    torch.save(collect(sys.argv[2:] or None), sys.argv[1])
+    if len(sys.argv) > 2 and sys.argv[2] == "artifact":   # <out> artifact <save_to> [<load_from>]
+        torch.save(artifact_exchange(*sys.argv[3:5]), sys.argv[1])
+    else:
+        torch.save(collect(sys.argv[2:] or None), sys.argv[1])

@@ -355,3 +355,37 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
                 (key, float((torch.nan_to_num(got.double()) - torch.nan_to_num(want.double())).abs().max()))
             if want.is_floating_point():
                 assert torch.equal(torch.isnan(got), torch.isnan(want)), key
+
+
+def test_exported_artifacts_interchange_with_the_reference(tmp_path):
+    """``save_artifact`` of either tree is read by ``inspect_artifact`` / ``load_artifact`` of the
+    other: same files, same manifest, every tensor of the student (with declared LoRA) and of the
+    text tower equal, iteration, caption horizon and LoRA declaration carried over."""
+    import importlib.util
+    import json
+
+    spec = importlib.util.spec_from_file_location("function_probe", ROOT / "baseline" / "function_probe.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    ours_dir, theirs_dir = tmp_path / "ours", tmp_path / "theirs"
+    saved = module.artifact_exchange(str(ours_dir))
+    path = tmp_path / "exchange.pt"
+    done = subprocess.run([sys.executable, str(ROOT / "baseline" / "function_probe.py"), str(path), "artifact",
+                           str(theirs_dir), str(ours_dir)], capture_output=True, text=True, timeout=900,
+                          env=reference_env(), cwd=str(ROOT / "baseline"))
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(path, weights_only=False)           # the reference read this package's export
+    ours = module.artifact_exchange(str(tmp_path / "again"), str(theirs_dir))   # and the reverse
+    assert saved["saved/files"] == theirs["saved/files"] == ["config.yaml", "manifest.json",
+                                                             "student.safetensors", "und.safetensors"]
+    assert json.loads((ours_dir / "manifest.json").read_text()) == json.loads((theirs_dir / "manifest.json").read_text())
+    for key in ("saved/student_keys", "saved/text_keys", "loaded/iteration", "loaded/frames", "loaded/lora",
+                "loaded/tokenizer", "loaded/report"):
+        assert ours[key] == theirs[key], key
+    assert ours["loaded/iteration"] == 42 and ours["loaded/frames"] == 13
+    assert set(theirs["loaded/config"]) <= set(ours["loaded/config"])   # this package has two more options
+    tensors = [key for key in theirs if key.startswith(("loaded/student/", "loaded/text/"))]
+    assert len(tensors) > 40 and sorted(tensors) == sorted(k for k in ours if k.startswith(("loaded/student/",
+                                                                                             "loaded/text/")))
+    for key in tensors:
+        assert torch.equal(ours[key], theirs[key]), key
