@@ -42,28 +42,42 @@ def media_artifact_filename(*, artifact_name: str, iteration: int, rank: int, sa
 
 
 def _canonical(video: Tensor, layout: str) -> Tensor:
-    """→ ``[B, C, T, H, W]``; a 4-D tensor is a batch of images."""
+    """-> ``[B, 3, T, H, W]``; a 4-D tensor is one clip without its batch axis (``CTHW`` / ``TCHW``)."""
+    shape = tuple(video.shape)
+    problem = f"media tensor must contain RGB video in BCTHW/CTHW or BTCHW/TCHW layout, got {shape}"
+    if video.ndim not in (4, 5):
+        raise ValueError(problem)
+    if layout not in ("BCTHW", "BTCHW"):
+        raise ValueError(f"unsupported media layout: {layout!r}")
     if video.ndim == 4:
-        video = video.unsqueeze(2 if layout == "BCTHW" else 1)
-    if video.ndim != 5:
-        raise ValueError(f"expected a 4-D or 5-D media tensor, got {tuple(video.shape)}")
-    return video if layout == "BCTHW" else video.permute(0, 2, 1, 3, 4)
+        video = video.unsqueeze(0)
+    if layout == "BTCHW":
+        video = video.permute(0, 2, 1, 3, 4)
+    if video.shape[1] != 3:
+        raise ValueError(problem)
+    return video
 
 
 def _to_uint8(video: Tensor, float_range: str, chunk: int) -> Tensor:
-    """``[C, T, H, W]`` → CPU uint8 ``[T, H, W, 3]``, converted ``chunk`` frames at a time."""
+    """``[3, T, H, W]`` -> CPU uint8 ``[T, H, W, 3]``, converted ``chunk`` frames at a time so that
+    a long clip never holds a second full-size copy on the device."""
     c, t, h, w = video.shape
+    if c != 3:
+        raise ValueError(f"media tensor must have three RGB channels, got {c}")
+    if chunk <= 0:
+        raise ValueError("frame_chunk_size must be positive")
+    if video.dtype != torch.uint8 and not video.is_floating_point():
+        raise TypeError(f"media tensor must be floating point or uint8, got {video.dtype}")
+    if float_range not in ("minus_one_one", "zero_one"):
+        raise ValueError(f"unsupported floating-point range: {float_range!r}")
     out = torch.empty((t, h, w, 3), dtype=torch.uint8)
     for lo in range(0, t, chunk):
-        part = video[:, lo:lo + chunk]
+        part = video[:, lo:lo + chunk].detach()
         if part.dtype != torch.uint8:
             part = part.float()
             part = (part + 1.0) * 127.5 if float_range == "minus_one_one" else part * 255.0
             part = part.round().clamp_(0, 255).to(torch.uint8)
-        part = part.permute(1, 2, 3, 0).cpu()
-        if c == 1:
-            part = part.expand(-1, -1, -1, 3)
-        out[lo:lo + part.shape[0]].copy_(part[..., :3])
+        out[lo:lo + part.shape[1]].copy_(part.permute(1, 2, 3, 0).cpu())
     return out
 
 
@@ -157,17 +171,35 @@ class ImageVideoArtifactWriter:
             yield b, batch, grid
 
     def _artifacts(self, value: Any) -> Iterator[tuple[str, int, int, Tensor]]:
-        named = value if isinstance(value, Mapping) else {"sample": value}
-        if self.grid_layout is not None and all(k in named for k in self.grid_layout):
+        """``(name, index in batch, batch size, uint8 [T, H, W, 3])`` of everything to be written:
+        the grid first when all its panels are present, then (unless a grid was built and single
+        artifacts are switched off) every entry by sorted key.  Names are made file-safe and kept
+        distinct; an entry that is not a tensor is an error (reference
+        ``wm/infra/callbacks/media.py:248-317``)."""
+        named = {"sample": value} if torch.is_tensor(value) else value
+        if not isinstance(named, Mapping):
+            raise TypeError("image/video sample must be a tensor or a mapping of tensors")
+        taken: set[str] = set()
+        with_grid = self.grid_layout is not None and all(key in named for key in self.grid_layout)
+        if with_grid:
+            title = _safe(self.grid_name)
+            taken.add(title)
             for b, batch, grid in self._grids(named):
-                yield self.grid_name, b, batch, grid
-        if self.save_individual_artifacts or self.grid_layout is None:
-            for name, tensor in named.items():
-                if not torch.is_tensor(tensor):
-                    continue
-                clips = _clips_uint8(tensor, self.layout, self.float_range, self.frame_chunk_size)
-                for b, pixels in enumerate(clips):
-                    yield str(name), b, len(clips), pixels
+                yield title, b, batch, grid
+            if not self.save_individual_artifacts:
+                return
+        for key in sorted(named, key=str):
+            tensor = named[key]
+            if not torch.is_tensor(tensor):
+                raise TypeError(f"media artifact {key!r} is not a tensor")
+            stem = name = _safe(key)
+            attempt = 2
+            while name in taken:
+                name, attempt = f"{stem}_{attempt}", attempt + 1
+            taken.add(name)
+            clips = _clips_uint8(tensor, self.layout, self.float_range, self.frame_chunk_size)
+            for b, pixels in enumerate(clips):
+                yield name, b, len(clips), pixels
 
     # --------------------------------------------------------------------- writing
     def _publish(self, jobs: Sequence[tuple[Tensor, str]]) -> None:

@@ -13,7 +13,7 @@ the discriminator head and of LoRA adapters, the synthetic dataset and the state
 whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the metric callback,
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
 eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
-through the conditioner, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+through the conditioner, periodic sampling with the media writer's files and rules, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -580,6 +580,99 @@ def _conditioner_raw(out: dict) -> None:
                     out[f"raw/eval/panel/{name}"] = value
 
 
+def _sampling_callback(out: dict) -> None:
+    """Periodic sampling inside a training run: which batches are sampled and with which options,
+    that sampling leaves the training random streams alone, and the files the media writer leaves
+    (single-frame artifacts as PNG, so that no video encoder is involved)."""
+    import hashlib
+    import tempfile
+    from pathlib import Path
+
+    from wm.data.loader import StatefulDataLoader
+    from wm.infra.callbacks import CallbackGroup, ImageVideoArtifactWriter, PeriodicSampleCallback
+    from wm.infra.model import Model
+    from wm.infra.trainer import Trainer
+
+    calls = []
+
+    class Toy(Model):
+        def __init__(self) -> None:
+            super().__init__()
+            self.scale = torch.nn.Parameter(torch.tensor(0.5))
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def training_step(self, data_batch, iteration):
+            noise = torch.rand(())                          # consumes the global stream
+            loss = ((self.scale * data_batch["x"]).mean() - noise).square()
+            return {"metrics/noise": noise}, loss
+
+        def validation_step(self, data_batch, iteration):
+            return self.training_step(data_batch, iteration)
+
+        def sample(self, data_batch, **sampling_options):
+            calls.append((bool(self.training), sorted((k, repr(v)) for k, v in sampling_options.items()),
+                          data_batch["sample_index"].tolist()))
+            torch.rand(3)                                   # must not disturb training
+            base = data_batch["x"].reshape(-1, 1, 1, 1, 1).expand(-1, 3, 1, 6, 8) * 0.1
+            ramp = torch.linspace(-1, 1, 8).view(1, 1, 1, 1, 8)
+            return {"depth": base + ramp, "normal": base - ramp, "ground_truth": base * ramp,
+                    "sample": (base + 0.3 * ramp).clamp(-1, 1), "comparison": base * 0.5}
+
+    class Rows(torch.utils.data.Dataset):
+        def __len__(self) -> int:
+            return 8
+
+        def __getitem__(self, index: int):
+            return {"x": torch.tensor(float(index)), "sample_index": torch.tensor(index),
+                    "validation_sample_seed": torch.tensor(100 + index)}
+
+    model = Toy()
+    optimizer = torch.optim.SGD(model.parameters(), lr=0.01)
+    model.optimizer_dict = {"net": optimizer}
+    model.scheduler_dict = {"net": torch.optim.lr_scheduler.LambdaLR(optimizer, lr_lambda=lambda step: 1.0)}
+    with tempfile.TemporaryDirectory() as scratch:
+        def writer():
+            return ImageVideoArtifactWriter(image_format="png", grid_layout=["depth", "normal", "ground_truth", "sample"],
+                                            grid_name="comparison", save_individual_artifacts=True)
+
+        group = CallbackGroup(config=None, trainer=None)
+        group._callbacks.extend([
+            PeriodicSampleCallback(2, str(Path(scratch) / "held_out"), writer(), source="validation", max_batches=2,
+                                   sampling_options={"steps": 4}),
+            PeriodicSampleCallback(3, str(Path(scratch) / "seen"), writer(), source="train", seed_batch_key=None,
+                                   sampling_options={"steps": 2})])
+        trainer = Trainer(grad_accum_steps=1, callbacks=group, device=torch.device("cpu"))
+        torch.manual_seed(21)
+        trainer.train(model, StatefulDataLoader(Rows(), batch_size=2, shuffle=True, seed=1, num_workers=0,
+                                                pin_memory=False),
+                      StatefulDataLoader(Rows(), batch_size=2, shuffle=False, seed=1, num_workers=0, pin_memory=False),
+                      grad_scaler=torch.amp.GradScaler(device="cpu", enabled=False), max_iterations=6,
+                      validation_interval=2, max_val_steps=3, validate_at_start=True)
+        files = sorted(str(p.relative_to(scratch)) for p in Path(scratch).rglob("*") if p.is_file())
+        out["sampler/files"] = files
+        out["sampler/digests"] = [hashlib.sha256((Path(scratch) / name).read_bytes()).hexdigest() for name in files]
+        # the artifact rules on their own: refusals, name clashes, a grid whose panels are missing
+        plain = ImageVideoArtifactWriter(image_format="png", grid_layout=["a", "b", "c"], grid_name="a",
+                                         save_individual_artifacts=False)
+        image = torch.zeros(2, 3, 1, 4, 4)
+        for label, value in (("text", {"a": image, "note": "text"}), ("number", 3.0),
+                             ("partial_grid", {"a": image, "b": image}), ("tensor", image),
+                             ("unbatched", image[0]), ("images", image[:, :, 0]), ("gray", image[:, :1]),
+                             ("integers", image.long()), ("two_dims", image[0, 0, 0]),
+                             ("clash", {"a": image, "b": image + 0.5, "c": image - 0.5, "a/": image})):
+            target = Path(scratch) / "rules" / label
+            try:
+                plain.write(value, output_dir=str(target), split="validation", iteration=1, rank=2)
+                out[f"sampler/rules/{label}"] = sorted(p.name for p in target.rglob("*") if p.is_file())
+            except Exception as error:
+                out[f"sampler/rules/{label}"] = f"{type(error).__name__}: {error}"
+    out["sampler/calls"] = calls
+    out["sampler/scale"] = model.scale.detach().clone()
+    out["sampler/next_random"] = torch.rand(2)
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -658,7 +751,7 @@ def artifact_exchange(save_to: str, load_from: str | None = None) -> dict:
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
-            "vae": _vae}
+            "sampling_callback": _sampling_callback, "vae": _vae}
 
 
 def collect(sections=None) -> dict:

@@ -371,7 +371,7 @@ def test_wandb_sinks_share_one_lazily_started_run(monkeypatch):
     assert calls[1][1] == {"project": "proj", "group": "grp", "name": "run-1", "mode": "offline"}
     assert calls[3] == ("log", {"train/loss": 1.5}, 3)
     clip = torch.zeros(2, 3, 2, 8, 8)
-    media.write({"sample": clip, "still": torch.zeros(1, 3, 8, 8)}, output_dir="unused", split="validation",
+    media.write({"sample": clip, "still": torch.zeros(3, 1, 8, 8)}, output_dir="unused", split="validation",
                 iteration=4, rank=0, sample_batch_index=7)
     assert [c[0] for c in calls].count("init") == 1
     logged = calls[-1]
