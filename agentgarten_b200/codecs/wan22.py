@@ -47,6 +47,8 @@ LATENT_STD = (
     0.6885, 0.6165, 0.8454, 0.4978, 0.5759, 0.3523, 0.7135, 0.6804, 0.5833, 1.4146, 0.8986, 0.5659,
     0.7069, 0.5338, 0.4889, 0.4917, 0.4069, 0.4999, 0.6866, 0.4093, 0.5709, 0.6065, 0.6415, 0.4944,
     0.5726, 1.2042, 0.5458, 1.6887, 0.3971, 1.0600, 0.3943, 0.5537, 0.5444, 0.4089, 0.7468, 0.7744)
+# the names the reference module gives the same tables
+WAN22_LATENTS_MEAN, WAN22_LATENTS_STD = LATENT_MEAN, LATENT_STD
 
 _HISTORY = 2  # frames of left context a temporal kernel of three needs
 

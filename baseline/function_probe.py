@@ -13,7 +13,8 @@ the discriminator head and of LoRA adapters, the synthetic dataset and the state
 whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the metric callback,
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
 eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
-through the conditioner, periodic sampling with the media writer's files and rules, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+through the conditioner, periodic sampling with the media writer's files and rules, the codec wrapper's surface, the
+objective base class, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -673,6 +674,147 @@ def _sampling_callback(out: dict) -> None:
     out["sampler/next_random"] = torch.rand(2)
 
 
+def _codec_surface(out: dict) -> None:
+    """What the codec wrapper promises without weights: factors, frame arithmetic, the latent
+    normalisation tables, the encoder window rule, refusals, and the hand-over to a tiny decoder."""
+    from wm.codecs import Wan22VAECodec, wan22
+
+    class Tiny:
+        def decode(self, latent):
+            return latent[:, :3] + 1.0
+
+    codec = Wan22VAECodec("unused", dtype="float32", decoder=Tiny())
+    out["codec/factors"] = [codec.spatial_compression_factor, codec.latent_channels,
+                            codec.temporal_compression_factor, str(codec.dtype)]
+    out["codec/latent_frames"] = [codec.latent_frames(n) for n in (1, 2, 5, 81, 93, 241)]
+    out["codec/pixel_frames"] = [codec.pixel_frames(n) for n in (1, 2, 21, 61)]
+    mean, inverse = codec._normalization(torch.device("cpu"))
+    out["codec/mean"], out["codec/inverse_std"] = mean, inverse
+    out["codec/tables"] = [tuple(wan22.WAN22_LATENTS_MEAN), tuple(wan22.WAN22_LATENTS_STD)]
+    out["codec/window"] = [codec._encode_window(shape) for shape in ((240, 416), (256, 256), (480, 832),
+                                                                     (640, 640), (720, 1280), (641, 2000))]
+    out["codec/handed_over"] = codec.decode(torch.ones(1, 48, 2, 2, 2))
+    for label, call in (("encode", lambda: codec.encode(torch.ones(1, 3, 1, 16, 16, dtype=torch.int32))),
+                        ("decode", lambda: codec.decode(torch.ones(1, 48, 1, 2, 2, dtype=torch.int64)))):
+        try:
+            call()
+        except Exception as error:
+            out[f"codec/refusal/{label}"] = f"{type(error).__name__}: {error}"
+    half = Wan22VAECodec("unused", device="cpu", temporal_compression_factor=8)
+    out["codec/other"] = [str(half.dtype), half.latent_frames(17), half.pixel_frames(3),
+                          str(half.preferred_device)]
+
+
+def _model_base(out: dict) -> None:
+    """The objective base class: trainable patterns over aliased parameters, parameter groups with
+    the decay split, bindings of two roles with their refusals, cadence, and a two-closure step
+    through the trainer (two roles updated in one step, gradients synchronised on the last)."""
+    from wm.infra.callbacks import CallbackGroup
+    from wm.infra.model import Model
+    from wm.infra.trainer import Trainer
+
+    class Twin(Model):
+        def __init__(self, **options) -> None:
+            super().__init__(**options)
+            g = torch.Generator().manual_seed(3)
+            self.left, self.right = torch.nn.Linear(4, 4), torch.nn.Linear(4, 4)
+            self.tied = torch.nn.Linear(4, 4, bias=False)
+            self.tied.weight = self.left.weight                 # one tensor, two names
+            self.norm = torch.nn.LayerNorm(4)
+            with torch.no_grad():
+                for parameter in self.parameters():
+                    parameter.copy_(torch.randn(parameter.shape, generator=g))
+            self.active = ("a", "b")
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def get_optimizer_names(self, iteration):
+            return self.active
+
+        def training_step_closures(self, data_batch, iteration):
+            yield "a", lambda: ({"metrics/a": torch.tensor(1.0)}, self.left(data_batch).square().mean()), False
+            yield "b", lambda: ({"metrics/b": torch.tensor(2.0)}, self.right(data_batch).abs().mean()), True
+
+        def sample(self, data_batch, **sampling_options):
+            return None
+
+    def live(model):
+        return sorted(name for name, p in model.named_parameters(remove_duplicate=False) if p.requires_grad)
+
+    model = Twin()
+    model.configure_trainable_parameters([r"tied\.weight", r"norm\..*"])
+    out["base/live/alias"] = live(model)
+    model.configure_trainable_parameters(r"right\.(weight|bias)")
+    out["base/live/string"] = live(model)
+    model.configure_trainable_parameters(None)
+    out["base/live/none"] = live(model)
+    model.configure_trainable_parameters([r".*"], module=model.norm)
+    out["base/live/module"] = live(model)
+    model.requires_grad_(True)
+
+    def shapes(groups):
+        return [(sorted((k, repr(v)) for k, v in group.items() if k != "params"),
+                 [tuple(p.shape) for p in group["params"]]) for group in groups]
+
+    out["base/groups/plain"] = shapes(Twin()._group_trainable_parameters())
+    out["base/groups/split"] = shapes(Twin(optimizer_split_decay_groups=True)._group_trainable_parameters())
+    declared = Twin(optimizer_parameter_groups=[
+        {"patterns": [r"tied\.weight"], "lr": 0.5}, {"patterns": r".*bias", "weight_decay": 0.0},
+        {"patterns": r"nothing", "lr": 9.0}], optimizer_split_decay_groups=True)
+    out["base/groups/declared"] = shapes(declared._group_trainable_parameters())
+    out["base/cadence"] = [bool(model.is_cadence_due(i, n)) for i in (0, 1, 4, 8) for n in (None, 0, 4)]
+
+    first = torch.optim.SGD([model.left.weight, model.left.bias], lr=0.1)
+    second = torch.optim.SGD([model.right.weight, model.right.bias], lr=0.2)
+    constant = lambda step: 1.0   # noqa: E731
+    model.optimizer_dict = {"a": first, "b": second}
+    model.scheduler_dict = {"a": torch.optim.lr_scheduler.LambdaLR(first, constant),
+                            "b": torch.optim.lr_scheduler.LambdaLR(second, constant)}
+    out["base/bindings"] = [binding.name for binding in model.get_optimizer_bindings(0)]
+
+    def refusal(label):
+        try:
+            model.get_optimizer_bindings(0)
+            out[f"base/refusal/{label}"] = "accepted"
+        except Exception as error:
+            out[f"base/refusal/{label}"] = f"{type(error).__name__}: {error}"
+
+    model.active = ()
+    refusal("none")
+    model.active = ("a", "a")
+    refusal("twice")
+    model.active = ("a", "c")
+    refusal("unknown")
+    model.active = ("a", "b")
+    model.scheduler_dict["b"] = torch.optim.lr_scheduler.LambdaLR(first, constant)
+    refusal("foreign_scheduler")
+    overlapping = torch.optim.SGD([model.left.weight, model.right.bias], lr=0.1)
+    model.optimizer_dict["b"] = overlapping
+    model.scheduler_dict["b"] = torch.optim.lr_scheduler.LambdaLR(overlapping, constant)
+    refusal("shared_parameter")
+    model.optimizer_dict["b"] = second
+    model.scheduler_dict["b"] = torch.optim.lr_scheduler.LambdaLR(second, constant)
+
+    trainer = Trainer(grad_accum_steps=2, callbacks=CallbackGroup(config=None, trainer=None),
+                      device=torch.device("cpu"))
+    scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+    g = torch.Generator().manual_seed(4)
+    steps = []
+    for micro in range(4):
+        result = trainer.training_step(model, scaler, torch.randn(3, 4, generator=g), iteration=micro // 2,
+                                       grad_accum_step=micro % 2)
+        steps.append((float(result.loss), result.grad_accum_step, bool(result.did_update),
+                      sorted(result.output_batch)))
+    out["base/steps"] = steps
+    for name, value in model.state_dict().items():
+        out[f"base/state/{name}"] = value
+    try:
+        trainer.training_step(model, scaler, torch.randn(3, 4, generator=g), iteration=3, grad_accum_step=2)
+    except Exception as error:
+        out["base/refusal/accum_step"] = f"{type(error).__name__}: {error}"
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -751,7 +893,8 @@ def artifact_exchange(save_to: str, load_from: str | None = None) -> dict:
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
-            "sampling_callback": _sampling_callback, "vae": _vae}
+            "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
+            "vae": _vae}
 
 
 def collect(sections=None) -> dict:
