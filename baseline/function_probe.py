@@ -815,6 +815,51 @@ def _model_base(out: dict) -> None:
         out["base/refusal/accum_step"] = f"{type(error).__name__}: {error}"
 
 
+def _history_windows(out: dict) -> None:
+    """Block-causal passes under a bounded history (sink + recent blocks), in both forcing modes,
+    and the cached rollout under the same window; ``forward`` with several known frames and
+    feature taps."""
+    import os
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import batch_of, seeded_, tiny_config
+
+    from wm.codecs import Wan22VAECodec
+    from wm.models.flow import rf_interpolate
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+    from wm.protocols import HistoryWindow
+
+    config = tiny_config()
+    net = build_network(config, init_device="cpu").float().eval()
+    seeded_(net, 0)
+    cond = Cosmos3Conditioner(config=config, codec=Wan22VAECodec(pretrained_path="unused", decoder=None),
+                              geometry_noise_sigma=0.0, init_device="cpu", empty_prompt_ids=(3, 4, 5)).float()
+    seeded_(cond.text_encoder, 1)
+    batch = cond.encode(batch_of(13), training=False)
+    condition = cond.condition(batch)
+    latent = batch["latent"]
+    noise = torch.randn(latent.shape, generator=torch.Generator().manual_seed(5))
+    sigma = torch.tensor([[0.9] * 4 + [0.5] * 4 + [0.2] * 4])
+    targets = rf_interpolate(latent[:, :, 1:], noise[:, :, 1:], sigma)
+    with torch.no_grad():
+        for label, window in (("sink1_recent1", HistoryWindow(sink_blocks=1, recent_blocks=1)),
+                              ("recent1", HistoryWindow(sink_blocks=0, recent_blocks=1)),
+                              ("everything", HistoryWindow())):
+            out[f"window/{label}/diffusion"] = net.forward_ar(latent[:, :, :1], targets, sigma, condition,
+                                                              block_frames=4, history=window)
+            out[f"window/{label}/teacher"] = net.forward_ar(latent[:, :, :1], targets, sigma, condition,
+                                                            block_frames=4, clean=latent[:, :, 1:], history=window)
+            cache = net.prefill(latent[:, :, :1], condition, history=window)
+            for block in range(3):
+                lo, hi = 4 * block, 4 * block + 4
+                out[f"window/{label}/cached/{block}"] = net.denoise(cache, targets[:, :, lo:hi],
+                                                                    sigma[:, lo])
+                cache = net.commit(cache, latent[:, :, 1 + lo:1 + hi])
+        flat = rf_interpolate(latent, noise, torch.tensor([0.6]))
+        flat[:, :, :3] = latent[:, :, :3]
+        out["window/known3"] = net(flat, torch.tensor([0.6]), condition, known_frames=3)
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -894,7 +939,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "vae": _vae}
+            "history_windows": _history_windows, "vae": _vae}
 
 
 def collect(sections=None) -> dict:

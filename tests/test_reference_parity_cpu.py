@@ -324,7 +324,9 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     wrapper's promises without weights; the objective base class (trainable patterns over aliased
     parameters, parameter groups, bindings and their refusals, a two-role step).  Equal
     to rounding: the restructured codecs (Wan 2.2 VAE, tiny decoders), a stream restarted on its
-    kept arenas, and the sampled latents (a few solver steps through the no-gradient operators)."""
+    kept arenas, the sampled latents (a few solver steps through the no-gradient operators) and
+    block-causal passes under bounded history windows (rows of all chunks of a layer go through
+    the row-wise operators together here)."""
     import importlib.util
 
     path = tmp_path / "functions.pt"
@@ -340,10 +342,10 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     errors = {key: value for key, value in {**theirs, **ours}.items() if key.endswith("/error")}
     assert not errors, errors
     assert sorted(ours) == sorted(theirs)
-    assert len(ours) > 270
+    assert len(ours) > 285
 
     def to_rounding(key: str) -> bool:
-        return key.startswith(("vae/", "tiny/")) or key.endswith("/restart") \
+        return key.startswith(("vae/", "tiny/", "window/")) or key.endswith("/restart") \
             or (key.startswith("sampling/") and key.endswith("/sample"))
 
     for key, want in theirs.items():
