@@ -14,7 +14,7 @@ whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
 eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
 through the conditioner, periodic sampling with the media writer's files and rules, the codec wrapper's surface, the
-objective base class, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+objective base class, bounded history windows, weight overlays at start-up, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -860,6 +860,93 @@ def _history_windows(out: dict) -> None:
         out["window/known3"] = net(flat, torch.tensor([0.6]), condition, known_frames=3)
 
 
+def _initializations(out: dict) -> None:
+    """``train.model_initializations``: overlays from a released-weights directory (safetensors,
+    source prefix and key patterns, one or several destinations, the resume subset) and from a
+    checkpoint written by the same tree, applied to a model with several roles; the plan they are
+    coalesced into; refusals for keys that do not fit."""
+    import tempfile
+    import warnings
+    from pathlib import Path
+
+    from safetensors.torch import save_file
+
+    from wm.infra.checkpoint import DistributedCheckpointer
+    from wm.infra.checkpoint.plan import plan_model_initializations
+    from wm.infra.model import Model
+
+    class Tower(torch.nn.Module):
+        def __init__(self) -> None:
+            super().__init__()
+            self.layers = torch.nn.ModuleList(torch.nn.Linear(3, 3) for _ in range(2))
+            self.head = torch.nn.Linear(3, 2)
+
+    class Roles(Model):
+        def __init__(self) -> None:
+            super().__init__()
+            self.student, self.fake, self.frozen = Tower(), Tower(), Tower()
+            with torch.no_grad():
+                for parameter in self.parameters():
+                    parameter.fill_(-1.0)
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def sample(self, data_batch, **sampling_options):
+            return None
+
+    g = torch.Generator().manual_seed(77)
+    released = {f"net.{name}": torch.randn(value.shape, generator=g) for name, value in Tower().state_dict().items()}
+    released["net.unrelated.weight"] = torch.zeros(2)
+    entries = {
+        "layers_student": {"path": "RELEASED", "model_key_prefix": "student", "source_model_key_prefix": "net",
+                           "source_model_key_patterns": [r"layers\..*"]},
+        "layers_fake": {"path": "RELEASED", "model_key_prefix": "fake", "source_model_key_prefix": "net",
+                        "source_model_key_patterns": [r"layers\..*"]},
+        "frozen": {"path": "RELEASED", "model_key_prefixes": ["frozen"], "source_model_key_prefix": "net",
+                   "source_model_key_patterns": [r"layers\..*", r"head\..*"],
+                   "resume_model_key_prefixes": ["frozen"]},
+        "skipped": {"path": None, "model_key_prefix": "student"},
+    }
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        for resume in (False, True):
+            plan = plan_model_initializations(entries, resume=resume)
+            out[f"init/plan/{resume}"] = [sorted((k, repr(v)) for k, v in item.load_kwargs().items()) for item in plan]
+        with tempfile.TemporaryDirectory() as scratch:
+            directory = Path(scratch) / "released"
+            directory.mkdir()
+            save_file(released, str(directory / "model.safetensors"))
+            located = {label: {**entry, "path": None if entry["path"] is None else str(directory)}
+                       for label, entry in entries.items()}
+            saver = DistributedCheckpointer(Path(scratch) / "checkpoints")
+            for resume in (False, True):
+                model = Roles()
+                saver.initialize_model(model, located, resume=resume)
+                for name, value in model.state_dict().items():
+                    out[f"init/{'resume' if resume else 'fresh'}/{name}"] = value
+            # a checkpoint of this tree as the source of another role
+            model = Roles()
+            saver.initialize_model(model, located, resume=False)
+            optimizer = torch.optim.SGD(model.parameters(), lr=0.1)
+            scheduler = torch.optim.lr_scheduler.LambdaLR(optimizer, lambda step: 1.0)
+            saver.save(model, {"net": optimizer}, {"net": scheduler}, None, iteration=3)
+            saver.finalize()
+            out["init/latest"] = (Path(scratch) / "checkpoints" / "latest").read_text()
+            other = Roles()
+            saver.initialize_model(other, {"from_run": {
+                "path": str(Path(scratch) / "checkpoints" / "iter_000000003"), "model_key_prefix": "fake",
+                "source_model_key_prefix": "student"}}, resume=False)
+            for name, value in other.state_dict().items():
+                out[f"init/from_run/{name}"] = value
+            try:
+                saver.initialize_model(Roles(), {"bad": {"path": str(directory), "model_key_prefix": "student",
+                                                          "source_model_key_prefix": "missing"}}, resume=False)
+                out["init/refusal"] = "accepted"
+            except Exception as error:
+                out["init/refusal"] = type(error).__name__
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -939,7 +1026,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "vae": _vae}
+            "history_windows": _history_windows, "initializations": _initializations, "vae": _vae}
 
 
 def collect(sections=None) -> dict:
