@@ -71,16 +71,31 @@ class FusedAdam(torch.optim.Optimizer):
     # ------------------------------------------------------------------ validation
     @staticmethod
     def _check_group(group: dict[str, Any]) -> None:
-        lr, eps, wd = _f(group["lr"]), _f(group["eps"]), _f(group["weight_decay"])
-        b1, b2 = (_f(b) for b in group["betas"])
-        if lr < 0:
-            raise ValueError(f"Invalid learning rate: {lr}")
-        if eps < 0:
-            raise ValueError(f"Invalid epsilon: {eps}")
-        if not 0.0 <= b1 < 1.0 or not 0.0 <= b2 < 1.0:
-            raise ValueError(f"Invalid betas: {(b1, b2)}")
-        if wd < 0:
-            raise ValueError(f"Invalid weight_decay: {wd}")
+        """Every hyper-parameter is one finite number (a Python scalar or a one-element tensor);
+        rates, epsilon and decay are not negative, both betas lie in [0, 1).  The messages are the
+        reference's (``wm/infra/optim/fused_adam.py:130-158``)."""
+        import math
+
+        def number(name: str, value: Any) -> float:
+            if torch.is_tensor(value) and value.numel() != 1:
+                raise ValueError(f"FusedAdam {name} must be a scalar")
+            try:
+                result = _f(value)
+            except (TypeError, ValueError, OverflowError) as error:
+                raise ValueError(f"FusedAdam {name} must be a finite scalar") from error
+            if not math.isfinite(result):
+                raise ValueError(f"FusedAdam {name} must be finite")
+            return result
+
+        for name in ("lr", "eps", "weight_decay"):
+            if number(name, group[name]) < 0:
+                raise ValueError(f"FusedAdam {name} must be non-negative")
+        betas = group["betas"]
+        if isinstance(betas, (str, bytes)) or not hasattr(betas, "__len__") or len(betas) != 2:
+            raise ValueError("FusedAdam betas must contain two scalars")
+        for position, beta in enumerate(betas, start=1):
+            if not 0.0 <= number(f"beta{position}", beta) < 1.0:
+                raise ValueError(f"FusedAdam beta{position} must be in [0, 1)")
 
     # ----------------------------------------------------------------------- state
     def _init_state(self, p: torch.Tensor, beta1: float, beta2: float) -> dict[str, Any]:

@@ -14,7 +14,7 @@ whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
 eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
 through the conditioner, periodic sampling with the media writer's files and rules, the codec wrapper's surface, the
-objective base class, bounded history windows, weight overlays at start-up, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+objective base class, bounded history windows, weight overlays at start-up, the optimizer's CPU path, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -947,6 +947,58 @@ def _initializations(out: dict) -> None:
                 out["init/refusal"] = type(error).__name__
 
 
+def _fused_adam(out: dict) -> None:
+    """The optimizer on the CPU path: Adam and AdamW, without first or second moment, FP32 master
+    weights under bf16 parameters, per-group options, bias correction off, a state dict that is
+    saved and loaded back; construction refusals."""
+    from wm.infra.optim import FusedAdam
+
+    def parameters(dtype):
+        g = torch.Generator().manual_seed(15)
+        made = [torch.nn.Parameter(torch.randn(shape, generator=g).to(dtype)) for shape in ((5, 3), (3,), (2, 2, 2))]
+        return made, g
+
+    variants = {
+        "adamw": dict(lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1, adam_w_mode=True),
+        "adam_l2": dict(lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1, adam_w_mode=False),
+        "no_first_moment": dict(lr=2e-3, betas=(0.0, 0.999), eps=1e-8),
+        "no_second_moment": dict(lr=2e-3, betas=(0.9, 0.0), eps=1e-3),
+        "no_bias_correction": dict(lr=1e-2, betas=(0.8, 0.9), eps=1e-6, bias_correction=False),
+        "master": dict(lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.01, use_te_capturable_kernel=True,
+                       master_weights=True),
+    }
+    for label, options in variants.items():
+        dtype = torch.bfloat16 if label == "master" else torch.float32
+        made, g = parameters(dtype)
+        groups = [{"params": made[:2]}, {"params": made[2:], "lr": options["lr"] * 0.5, "weight_decay": 0.0}]
+        optimizer = FusedAdam(groups, **options)
+        for step in range(4):
+            for parameter in made:
+                parameter.grad = torch.randn(parameter.shape, generator=g).to(dtype) * (1.0 + step)
+            optimizer.step()
+            if step == 1:
+                saved = optimizer.state_dict()
+                optimizer.load_state_dict(saved)        # the state survives its own round trip
+        for index, parameter in enumerate(made):
+            out[f"adam/{label}/parameter/{index}"] = parameter.detach().float()
+        state = optimizer.state_dict()["state"]
+        out[f"adam/{label}/state_fields"] = [sorted(state[index]) for index in sorted(state)]
+        for index in sorted(state):
+            for field, value in sorted(state[index].items()):
+                if torch.is_tensor(value):
+                    out[f"adam/{label}/state/{index}/{field}"] = value.detach().float().reshape(-1)
+                    out[f"adam/{label}/state_dtype/{index}/{field}"] = str(value.dtype)
+    made, _ = parameters(torch.float32)
+    for label, options in (("amsgrad", dict(amsgrad=True)), ("master_without_kernel", dict(master_weights=True)),
+                           ("negative_lr", dict(lr=-1.0)), ("beta_one", dict(betas=(1.0, 0.9))),
+                           ("three_betas", dict(betas=(0.9, 0.9, 0.9)))):
+        try:
+            FusedAdam(made, **options)
+            out[f"adam/refusal/{label}"] = "accepted"
+        except Exception as error:
+            out[f"adam/refusal/{label}"] = f"{type(error).__name__}: {error}"
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1026,7 +1078,8 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "vae": _vae}
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam,
+            "vae": _vae}
 
 
 def collect(sections=None) -> dict:
