@@ -30,29 +30,28 @@ __all__ = [
     "build_network",
 ]
 
-_GEN_ATTN = r"layers\.\d+\.self_attn\.(add_q_proj|add_k_proj|add_v_proj|to_add_out|norm_added_q|norm_added_k)\.weight"
-GEN_KEYS = (
-    _GEN_ATTN,
-    r"layers\.\d+\.(input_layernorm_moe_gen|post_attention_layernorm_moe_gen)\.weight",
-    r"layers\.\d+\.mlp_moe_gen\.(gate|up|down)_proj\.weight",
-    r"norm_moe_gen\.weight",
-    r"proj_(in|out)\.(weight|bias)",
-    r"time_embedder\.linear_[12]\.(weight|bias)",
-    r"geometry_modality_embed",
-    r"first_frame_reference_embed",
-)
+# The patterns end up verbatim in resolved configuration files (``source_model_key_patterns``),
+# so they are spelled exactly as the reference spells them.
 TEXT_ENCODER_KEYS = (
     r"embed_tokens\.weight",
-    r"layers\.\d+\.self_attn\.(to_q|to_k|to_v|to_out|norm_q|norm_k)\.weight",
-    r"layers\.\d+\.(input_layernorm|post_attention_layernorm)\.weight",
-    r"layers\.\d+\.mlp\.(gate|up|down)_proj\.weight",
+    r"layers\.\d+\.self_attn\.(?:to_q|to_k|to_v|to_out|norm_q|norm_k)\.weight",
+    r"layers\.\d+\.(?:input_layernorm|post_attention_layernorm)\.weight",
+    r"layers\.\d+\.mlp\.(?:gate|up|down)_proj\.weight",
 )
-LORA_ATTENTION_MODULES = (
-    r"layers\.\d+\.self_attn\.(add_q_proj|add_k_proj|add_v_proj|to_add_out)",
+GEN_KEYS = (
+    r"layers\.\d+\.self_attn\.(?:add_[qkv]_proj|to_add_out|norm_added_[qk])\.weight",
+    r"layers\.\d+\.(?:input_layernorm_moe_gen|post_attention_layernorm_moe_gen)\.weight",
+    r"layers\.\d+\.mlp_moe_gen\.(?:gate|up|down)_proj\.weight",
+    r"norm_moe_gen\.weight",
+    r"proj_(?:in|out)\.(?:weight|bias)",
+    r"time_embedder\.linear_[12]\.(?:weight|bias)",
+    r"geometry_modality_embed",       # trained checkpoints only; absent from the released one
+    r"first_frame_reference_embed",
 )
+LORA_ATTENTION_MODULES = (r"layers\.\d+\.self_attn\.(?:add_[qkv]_proj|to_add_out)",)
 LORA_ATTENTION_MLP_MODULES = (
     *LORA_ATTENTION_MODULES,
-    r"layers\.\d+\.mlp_moe_gen\.(gate|up|down)_proj",
+    r"layers\.\d+\.mlp_moe_gen\.(?:gate|up|down)_proj",
 )
 # Token ids of an empty user message after the chat template (text dropout / default negative).
 COSMOS3_EMPTY_PROMPT_IDS: tuple[int, ...] = (151644, 872, 198, 151645, 198, 151644, 77091, 198)

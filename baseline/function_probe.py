@@ -999,6 +999,47 @@ def _fused_adam(out: dict) -> None:
             out[f"adam/refusal/{label}"] = f"{type(error).__name__}: {error}"
 
 
+def _constants(out: dict) -> None:
+    """Tables and defaults that users and checkpoints depend on: key patterns of the released
+    weights, LoRA module lists, the empty prompt, configuration defaults, the distillation
+    endpoints, and the building blocks of the recipes."""
+    import dataclasses
+
+    from wm.models import dmd
+    from wm.networks import cosmos3
+    from wm.networks.cosmos3.geometry import GeometryAugmentationConfig
+    from wm.networks.cosmos3.streaming import StreamPolicy
+
+    def plain(value):
+        if dataclasses.is_dataclass(value) and not isinstance(value, type):
+            return sorted((f.name, repr(getattr(value, f.name))) for f in dataclasses.fields(value))
+        if isinstance(value, dict):
+            return sorted((str(k), repr(v)) for k, v in value.items())
+        if isinstance(value, (list, tuple, set, frozenset)):
+            return [repr(v) for v in value]
+        return repr(value)
+
+    for name in ("TEXT_ENCODER_KEYS", "GEN_KEYS", "LORA_ATTENTION_MODULES", "LORA_MLP_MODULES"):
+        if hasattr(cosmos3, name):
+            out[f"constants/cosmos3/{name}"] = plain(getattr(cosmos3, name))
+    out["constants/cosmos3/names"] = sorted(n for n in dir(cosmos3) if n.isupper() and not n.startswith("_"))
+    out["constants/config"] = plain(cosmos3.Cosmos3Config())
+    out["constants/stream_policy"] = plain(StreamPolicy())
+    out["constants/geometry"] = plain(GeometryAugmentationConfig())
+    out["constants/dmd/endpoints"] = plain(dmd.RCM_ENDPOINTS)
+    out["constants/dmd/gan"] = plain(dmd.GANConfig())
+    from wm.networks.cosmos3 import conditioner
+
+    out["constants/empty_prompt"] = plain(conditioner.COSMOS3_EMPTY_PROMPT_IDS)
+    try:
+        from wm.configs.experiments import cosmos3 as recipes
+
+        for name in ("GEOMETRY_AUGMENTATION", "LORA_TRAINABLE", "RELEASED_TRANSFORMER"):
+            out[f"constants/recipes/{name}"] = plain(getattr(recipes, name))
+    except Exception as error:
+        out["constants/recipes"] = f"{type(error).__name__}: {error}"
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1078,7 +1119,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants,
             "vae": _vae}
 
 

@@ -326,7 +326,9 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     of ``train.model_initializations`` (released-weights directory, key patterns, several
     destinations, the resume subset, a run's checkpoint as source) and their plan; the optimizer
     on its CPU path (Adam / AdamW, without first or second moment, FP32 master weights under bf16
-    parameters, per-group options, state round trip, refusals).  Equal
+    parameters, per-group options, state round trip, refusals); the tables users and checkpoints
+    depend on (key patterns of the released weights, LoRA module lists, configuration defaults,
+    distillation endpoints, recipe constants).  Equal
     to rounding: the restructured codecs (Wan 2.2 VAE, tiny decoders), a stream restarted on its
     kept arenas, the sampled latents (a few solver steps through the no-gradient operators) and
     block-causal passes under bounded history windows (rows of all chunks of a layer go through
@@ -346,7 +348,7 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     errors = {key: value for key, value in {**theirs, **ours}.items() if key.endswith("/error")}
     assert not errors, errors
     assert sorted(ours) == sorted(theirs)
-    assert len(ours) > 470
+    assert len(ours) > 480
 
     def to_rounding(key: str) -> bool:
         return key.startswith(("vae/", "tiny/", "window/")) or key.endswith("/restart") \
@@ -354,6 +356,9 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
 
     for key, want in theirs.items():
         got = ours[key]
+        if key == "constants/config":   # this package's network has two more options (AdaLN variant)
+            assert set(want) <= set(got), (key, sorted(set(want) - set(got)))
+            continue
         if not torch.is_tensor(want):
             assert got == want, (key, got, want)
             continue
