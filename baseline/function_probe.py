@@ -1040,6 +1040,46 @@ def _constants(out: dict) -> None:
         out["constants/recipes"] = f"{type(error).__name__}: {error}"
 
 
+def _recipes(out: dict) -> None:
+    """The configuration tree of every recipe before resolution (targets, constants, callbacks,
+    optimizer and scheduler settings, initialisations), flattened to ``path = value`` lines with
+    the package root of ``_target_`` strings normalised."""
+    import importlib
+    from collections.abc import Mapping
+
+    def flatten(node, prefix, lines):
+        if isinstance(node, Mapping) or (hasattr(node, "items") and hasattr(node, "keys")):
+            for key in node.keys():
+                try:
+                    child = node._get_node(key)._value() if False else dict.__getitem__(node, key)
+                except Exception:
+                    try:
+                        child = node.get(key) if not hasattr(node, "_raw") else node._raw(key)
+                    except Exception:
+                        child = "<unreadable>"
+                flatten(child, f"{prefix}.{key}" if prefix else str(key), lines)
+        elif isinstance(node, (list, tuple)) or type(node).__name__ in ("ListConfig", "LazyList"):
+            for index, child in enumerate(list(node)):
+                flatten(child, f"{prefix}[{index}]", lines)
+        else:
+            text = repr(node) if not isinstance(node, str) else node
+            if isinstance(node, str):
+                for root in ("agentgarten_b200.", "wm."):
+                    if text.startswith(root):
+                        text = "<package>." + text[len(root):]
+            lines.append(f"{prefix} = {text}")
+
+    for name in ("bidirectional", "ar_teacher_forcing", "ar_diffusion_forcing", "dmd", "dmd_gan", "dmd_gan_exact",
+                 "dmd_gan_lora"):
+        try:
+            module = importlib.import_module(f"wm.configs.experiments.cosmos3.{name}")
+            lines: list[str] = []
+            flatten(module.build_config(), "", lines)
+            out[f"recipes/{name}"] = sorted(lines)
+        except Exception as error:
+            out[f"recipes/{name}"] = f"{type(error).__name__}: {error}"
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1119,7 +1159,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes,
             "vae": _vae}
 
 

@@ -7,6 +7,7 @@ updated parameters.
 """
 
 import os
+import re
 import subprocess
 import sys
 from pathlib import Path
@@ -308,6 +309,16 @@ def test_checkpoints_interchange_with_the_reference(tmp_path):
         sorted(p.name for p in (mine / "iter_000000002").iterdir())
 
 
+# Lines of a flattened recipe that may differ: options this package adds (AdaLN variant of the
+# network, random weights for synthetic runs, the flat optimizer engine, the limit on skipped
+# updates), classes that live in another module of this package, and default factories, which the
+# reference's lazy call records as a placeholder and this package's as their value.
+RECIPE_EXTENSIONS = re.compile(
+    r"(geometry_mode|timestep_conditioning|special_tokens|codec\.architecture|random_init_seed|\.flat = None"
+    r"|process_group = None|max_consecutive_skipped_updates|compile_options = <factory>|parallel\._target_"
+    r"|gan\._target_)")
+
+
 def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     """One probe file (``baseline/function_probe.py``) runs in the reference's process and in this
     one.  Equal bit for bit: rectified-flow utilities and the UniPC solver, learning-rate factors,
@@ -328,7 +339,8 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     on its CPU path (Adam / AdamW, without first or second moment, FP32 master weights under bf16
     parameters, per-group options, state round trip, refusals); the tables users and checkpoints
     depend on (key patterns of the released weights, LoRA module lists, configuration defaults,
-    distillation endpoints, recipe constants).  Equal
+    distillation endpoints, recipe constants) and the configuration trees of all seven recipes
+    (every line, up to the options this package adds).  Equal
     to rounding: the restructured codecs (Wan 2.2 VAE, tiny decoders), a stream restarted on its
     kept arenas, the sampled latents (a few solver steps through the no-gradient operators) and
     block-causal passes under bounded history windows (rows of all chunks of a layer go through
@@ -348,7 +360,7 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     errors = {key: value for key, value in {**theirs, **ours}.items() if key.endswith("/error")}
     assert not errors, errors
     assert sorted(ours) == sorted(theirs)
-    assert len(ours) > 480
+    assert len(ours) > 490
 
     def to_rounding(key: str) -> bool:
         return key.startswith(("vae/", "tiny/", "window/")) or key.endswith("/restart") \
@@ -358,6 +370,11 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
         got = ours[key]
         if key == "constants/config":   # this package's network has two more options (AdaLN variant)
             assert set(want) <= set(got), (key, sorted(set(want) - set(got)))
+            continue
+        if key.startswith("recipes/"):
+            assert isinstance(want, list) and isinstance(got, list), (key, want if isinstance(want, str) else got)
+            stray = sorted(line for line in set(want) ^ set(got) if not RECIPE_EXTENSIONS.search(line))
+            assert not stray and len(got) > 250, (key, stray[:10])
             continue
         if not torch.is_tensor(want):
             assert got == want, (key, got, want)
