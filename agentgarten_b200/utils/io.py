@@ -73,7 +73,8 @@ def encode_image(pixels: np.ndarray, *, file_format: str, **options: Any) -> Byt
     from PIL import Image
 
     buffer = BytesIO()
-    Image.fromarray(np.ascontiguousarray(pixels)).save(buffer, format=file_format, **options)
+    name = "JPEG" if file_format.lower() in ("jpg", "jpeg") else file_format.upper()  # Pillow's names
+    Image.fromarray(np.ascontiguousarray(pixels)).save(buffer, format=name, **options)
     buffer.seek(0)
     return buffer
 

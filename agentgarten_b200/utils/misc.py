@@ -8,7 +8,8 @@ from __future__ import annotations
 import contextlib
 import os
 import random
-from collections.abc import Callable, Iterator, Mapping
+from collections import defaultdict
+from collections.abc import Callable, Iterator, Mapping, Sequence
 from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 from typing import Any
@@ -28,25 +29,30 @@ __all__ = [
 
 
 def map_tensors(value: Any, transform: Callable[[torch.Tensor], torch.Tensor]) -> Any:
-    """Apply ``transform`` to every tensor of a nested container.
+    """Rebuild a nested container with ``transform`` applied to every tensor.
 
-    Containers whose leaves all come back unchanged are returned as the same object, so
-    callers can test ``result is value`` to see whether anything moved.
+    A tensor object that occurs several times is transformed once and stays one object in the
+    result (a batch that shares a tensor between two keys still shares it after a device move).
+    Mappings and sequences come back as their own types (default dictionaries keep their
+    factory, named tuples their fields); strings, byte strings and ranges are leaves.
+    Reference: ``wm/infra/utils.py:30-52``.
     """
+    done: dict[int, torch.Tensor] = {}
 
     def visit(item: Any) -> Any:
         if isinstance(item, torch.Tensor):
-            return transform(item)
+            if id(item) not in done:
+                done[id(item)] = transform(item)
+            return done[id(item)]
         if isinstance(item, Mapping):
-            out = {key: visit(child) for key, child in item.items()}
-            same = all(out[key] is item[key] for key in item)
-            return item if same else type(item)(out) if isinstance(item, dict) else out
+            children = {key: visit(child) for key, child in item.items()}
+            if isinstance(item, defaultdict):
+                return type(item)(item.default_factory, children)
+            return type(item)(children)
         if isinstance(item, tuple) and hasattr(item, "_fields"):
-            out = [visit(child) for child in item]
-            return item if all(a is b for a, b in zip(out, item)) else type(item)(*out)
-        if isinstance(item, (list, tuple)):
-            out = [visit(child) for child in item]
-            return item if all(a is b for a, b in zip(out, item)) else type(item)(out)
+            return type(item)(*(visit(child) for child in item))
+        if isinstance(item, Sequence) and not isinstance(item, (str, bytes, bytearray, range)):
+            return type(item)([visit(child) for child in item])
         return item
 
     return visit(value)

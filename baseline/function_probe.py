@@ -1080,6 +1080,73 @@ def _recipes(out: dict) -> None:
             out[f"recipes/{name}"] = f"{type(error).__name__}: {error}"
 
 
+def _utilities(out: dict) -> None:
+    """Tree mapping of tensors, seeding, the mode / gradient-flag guards, atomic file helpers,
+    image encoding and the random-state capture of a single process."""
+    import collections
+    import random
+    import tempfile
+    from pathlib import Path
+
+    import numpy as np
+
+    from wm.infra import io
+    from wm.infra.rng_state import (capture_distributed_rng_state, isolated_rng, restore_distributed_rng_state,
+                                    validate_distributed_rng_state)
+    from wm.infra.utils import frozen_parameters, map_tensors, preserve_training_mode, set_random_seed, to
+
+    Pair = collections.namedtuple("Pair", "left right")
+    shared = torch.arange(4.0)
+    tree = {"a": shared, "b": [shared, Pair(torch.ones(2), "text")], "c": collections.defaultdict(list, {"k": shared}),
+            "d": (1, 2.5, None, b"bytes", range(3)), "e": collections.OrderedDict(z=torch.zeros(1))}
+    mapped = map_tensors(tree, lambda tensor: tensor * 2)
+    out["util/map/types"] = [type(mapped).__name__, type(mapped["b"]).__name__, type(mapped["b"][1]).__name__,
+                             type(mapped["c"]).__name__, type(mapped["d"]).__name__, type(mapped["e"]).__name__,
+                             repr(mapped["d"]), repr(mapped["c"].default_factory)]
+    out["util/map/shared"] = [mapped["a"] is mapped["b"][0], mapped["a"] is mapped["c"]["k"]]
+    out["util/map/values"] = torch.cat([mapped["a"], mapped["b"][1].left, mapped["e"]["z"]])
+    moved = to({"x": torch.zeros(2, 3, 4, 5), "y": torch.ones(2, dtype=torch.int64)}, device="cpu",
+               dtype=torch.float64, memory_format=torch.channels_last)
+    out["util/to"] = [str(moved["x"].dtype), str(moved["y"].dtype),
+                      bool(moved["x"].is_contiguous(memory_format=torch.channels_last))]
+    set_random_seed(1234)
+    out["util/seeded"] = [random.random(), float(np.random.rand()), float(torch.rand(()))]
+    module = torch.nn.Sequential(torch.nn.Linear(2, 2), torch.nn.Dropout(0.5))
+    module[1].eval()
+    module[0].weight.requires_grad_(False)
+    with preserve_training_mode(module), frozen_parameters(module):
+        module.eval()
+        inside = [p.requires_grad for p in module.parameters()]
+    out["util/guards"] = [inside, [p.requires_grad for p in module.parameters()],
+                          [m.training for m in module.modules()]]
+    with tempfile.TemporaryDirectory() as scratch:
+        target = io.join_path(scratch, "deep", "file.txt")
+        io.atomic_put_text("héllo\n", target)
+        io.atomic_put(b"\x00\x01", io.join_path(scratch, "deep", "file.bin"))
+        out["util/io"] = [io.exists(target), io.get_text(target), io.get(io.join_path(scratch, "deep", "file.bin")),
+                          io.exists(io.join_path(scratch, "missing")),
+                          sorted(p.name for p in (Path(scratch) / "deep").iterdir())]
+    pixels = (np.arange(6 * 8 * 3) % 251).astype(np.uint8).reshape(6, 8, 3)
+    out["util/png"] = io.encode_image(pixels, file_format="png").getvalue()
+    out["util/jpg"] = io.encode_image(pixels, file_format="jpg", quality=80).getvalue()
+    set_random_seed(77)
+    state = capture_distributed_rng_state()
+    validate_distributed_rng_state(state)
+    out["util/rng/keys"] = sorted(state)
+    first = [random.random(), float(np.random.rand()), float(torch.rand(()))]
+    with isolated_rng():
+        random.random(), np.random.rand(), torch.rand(3)
+    second = [random.random(), float(np.random.rand()), float(torch.rand(()))]
+    restore_distributed_rng_state(state)
+    again = [random.random(), float(np.random.rand()), float(torch.rand(()))]
+    out["util/rng/draws"] = [first, second, again]
+    try:
+        validate_distributed_rng_state({"rank_00000001": {}})
+        out["util/rng/refusal"] = "accepted"
+    except Exception as error:
+        out["util/rng/refusal"] = type(error).__name__
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1159,7 +1226,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities,
             "vae": _vae}
 
 

@@ -276,3 +276,15 @@ def test_public_signatures_follow_the_reference():
         pytest.skip("the reference package is not installed under baseline/_ref")
     problems = _reference_signature_problems(root)
     assert not problems, "\n".join(problems)
+
+
+def test_relocated_modules_are_reachable_with_from_imports():
+    """``from wm.infra import io`` style imports of the four modules that live elsewhere in this
+    package, next to the dotted form."""
+    import wm.infra.io as dotted
+    from wm.infra import io, log, parallel, utils
+
+    assert io is dotted and callable(io.atomic_put) and callable(log.info)
+    assert callable(utils.map_tensors) and hasattr(parallel, "ParallelConfig")
+    with pytest.raises(ImportError):
+        from wm.infra import nothing_of_that_name  # noqa: F401
