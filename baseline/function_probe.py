@@ -14,7 +14,8 @@ whole ``Trainer.train`` run on a toy model with the clip / spike monitor and the
 the tiny decoders (parallel, sequential, streamed), streams in all three position modes with
 eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
 through the conditioner, periodic sampling with the media writer's files and rules, the codec wrapper's surface, the
-objective base class, bounded history windows, weight overlays at start-up, the optimizer's CPU path, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+objective base class, bounded history windows, weight overlays at start-up, the optimizer's CPU path, constants and recipe trees, utilities,
+clipping helpers, lazy calls, the metric callback's corner cases, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -1147,6 +1148,96 @@ def _utilities(out: dict) -> None:
         out["util/rng/refusal"] = type(error).__name__
 
 
+def _runtime_misc(out: dict) -> None:
+    """Gradient clipping helpers (groups, an unlimited norm, non-finite gradients, shared
+    parameters), lazy calls and their instantiation rules, rank helpers without a process group,
+    and the metric callback's handling of odd step outputs and of a failing sink."""
+    import fractions
+
+    from wm.infra import distributed
+    from wm.infra.callbacks import ScalarMetricCallback
+    from wm.infra.callbacks.grad_clip import clip_grad_norm_, clip_grad_norm_groups_
+    from wm.infra.config import LazyCall, instantiate
+
+    def parameters(values):
+        made = []
+        for value in values:
+            parameter = torch.nn.Parameter(torch.zeros(len(value)))
+            parameter.grad = torch.tensor(value)
+            made.append(parameter)
+        return made
+
+    a, b, c = parameters([[3.0, 4.0], [12.0], [0.0, 0.0]])
+    frozen = torch.nn.Parameter(torch.zeros(1), requires_grad=False)
+    bare = torch.nn.Parameter(torch.zeros(1))
+    total, roles = clip_grad_norm_groups_({"first": [a, frozen, bare], "second": [b, a, c]}, 6.5)
+    out["clip/total"], out["clip/roles"] = total, sorted((k, float(v)) for k, v in roles.items())
+    out["clip/grads"] = torch.cat([a.grad, b.grad, c.grad])
+    a, b = parameters([[3.0, 4.0], [12.0]])
+    out["clip/observe"] = clip_grad_norm_([a, b], float("inf"))
+    out["clip/observe/grads"] = torch.cat([a.grad, b.grad])
+    a, b = parameters([[float("nan"), 1.0], [2.0]])
+    out["clip/nonfinite"] = clip_grad_norm_([a, b], 1.0)
+    out["clip/nonfinite/grads"] = torch.cat([a.grad, b.grad])
+    out["clip/nothing"] = repr(clip_grad_norm_groups_({"x": [frozen, bare]}, 1.0))
+    for label, bound in (("negative", -1.0), ("nan", float("nan"))):
+        try:
+            clip_grad_norm_([a], bound)
+            out[f"clip/refusal/{label}"] = "accepted"
+        except Exception as error:
+            out[f"clip/refusal/{label}"] = f"{type(error).__name__}: {error}"
+
+    lazy = LazyCall(fractions.Fraction)(numerator=3, denominator=4)
+    out["lazy/keys"] = sorted(str(k) for k in lazy)
+    out["lazy/target"] = lazy["_target_"]
+    out["lazy/value"] = str(instantiate(lazy))
+    out["lazy/override"] = str(instantiate(lazy, denominator=5))
+    nested = {"_target_": "builtins.dict", "inner": LazyCall(fractions.Fraction)(numerator=1, denominator=2),
+              "plain": [1, {"_target_": "builtins.int", "_recursive_": True}]}
+    built = instantiate(nested)
+    out["lazy/nested"] = [type(built).__name__, str(built["inner"]), repr(list(built["plain"]))]
+    kept = instantiate({"_target_": "builtins.dict", "_recursive_": False,
+                        "inner": {"_target_": "builtins.int"}})
+    out["lazy/not_recursive"] = repr(dict(kept["inner"]))
+    out["lazy/passthrough"] = [repr(instantiate(3)), repr(instantiate([1, "x"])), repr(instantiate({"k": (1, 2)}))]
+    for label, config in (("missing_module", {"_target_": "no_such_package.thing"}),
+                          ("missing_name", {"_target_": "builtins.no_such_name"}),
+                          ("not_a_string", {"_target_": 3}), ("not_callable", {"_target_": "math.pi"})):
+        try:
+            instantiate(config)
+            out[f"lazy/refusal/{label}"] = "accepted"
+        except Exception as error:
+            out[f"lazy/refusal/{label}"] = type(error).__name__
+    try:
+        LazyCall(3)
+    except Exception as error:
+        out["lazy/refusal/target"] = type(error).__name__
+
+    out["ranks"] = [distributed.get_rank(), distributed.get_world_size(), distributed.get_local_rank(),
+                    distributed.get_local_world_size(), bool(distributed.is_rank0())]
+
+    class Sink:
+        def __init__(self, broken: bool) -> None:
+            self.broken, self.rows = broken, []
+
+        def write(self, metrics, *, iteration):
+            if self.broken:
+                raise OSError("disk full")
+            self.rows.append((int(iteration), sorted((k, round(float(v), 6)) for k, v in metrics.items())))
+
+    good, bad = Sink(False), Sink(True)
+    callback = ScalarMetricCallback(every_n=2, sinks=[bad, None, good])
+    model = torch.nn.Linear(1, 1)
+    for iteration in range(1, 5):
+        outputs = {"metrics/ok": torch.tensor(float(iteration)), "metrics/nan": torch.tensor(float("nan")),
+                   "metrics/vector": torch.ones(2), "metrics/text": "skip", "metrics/number": 2.0 * iteration,
+                   "other": torch.tensor(9.0)}
+        callback.on_training_step_batch_end(model, {}, outputs, torch.tensor(0.5 * iteration), iteration=iteration - 1)
+        callback.on_training_step_end(model, {}, outputs, torch.tensor(0.5 * iteration), iteration=iteration)
+    out["metrics/rows"] = good.rows
+    out["metrics/sinks_left"] = len([sink for sink in callback.sinks])
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1226,7 +1317,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc,
             "vae": _vae}
 
 
