@@ -1313,6 +1313,70 @@ def artifact_exchange(save_to: str, load_from: str | None = None) -> dict:
     return out
 
 
+def ddp_exchange() -> dict:
+    """Run under a two-rank Gloo launch: loss closures through the data-parallel wrapper with two
+    micro-batches per update.  Gradients stay local after the first micro-batch and are averaged
+    over the ranks by the last backward pass; every rank ends with the same parameters."""
+    import torch.distributed as dist
+
+    from wm.infra import distributed
+    from wm.infra.callbacks import CallbackGroup
+    from wm.infra.model import Model
+    from wm.infra.trainer import Trainer
+
+    distributed.init(device="cpu", backend="gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+
+    class Toy(Model):
+        def __init__(self) -> None:
+            super().__init__()
+            g = torch.Generator().manual_seed(3)
+            self.body = torch.nn.Linear(3, 2)
+            with torch.no_grad():
+                for parameter in self.parameters():
+                    parameter.copy_(torch.randn(parameter.shape, generator=g))
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def training_step(self, data_batch, iteration):
+            loss = (self.body(data_batch["x"]) - data_batch["y"]).square().mean()
+            return {"metrics/mse": loss.detach()}, loss
+
+        def sample(self, data_batch, **sampling_options):
+            return None
+
+    model = Toy()
+    wrapped = distributed.wrap_ddp(model, device="cpu")
+    optimizer = torch.optim.SGD(model.parameters(), lr=0.1)
+    model.optimizer_dict = {"net": optimizer}
+    model.scheduler_dict = {"net": torch.optim.lr_scheduler.LambdaLR(optimizer, lambda step: 1.0)}
+    trainer = Trainer(grad_accum_steps=2, callbacks=CallbackGroup(config=None, trainer=None),
+                      device=torch.device("cpu"))
+    scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+    g = torch.Generator().manual_seed(100 + rank)
+    record: dict = {"wrapped": type(wrapped).__name__, "root": type(getattr(wrapped, "training_model", None)).__name__}
+    for micro in range(4):
+        batch = {"x": torch.randn(5, 3, generator=g), "y": torch.randn(5, 2, generator=g)}
+        result = trainer.training_step(wrapped, scaler, batch, iteration=micro // 2, grad_accum_step=micro % 2)
+        gradient = None if model.body.weight.grad is None else model.body.weight.grad.clone()
+        gathered: list = [None] * world
+        dist.all_gather_object(gathered, {"loss": float(result.loss), "updated": bool(result.did_update),
+                                          "gradient": gradient, "weight": model.body.weight.detach().clone()})
+        record[f"micro/{micro}"] = gathered
+    dist.barrier()
+    out: dict = {"ddp/wrapped": record["wrapped"], "ddp/root": record["root"]}
+    for micro in range(4):
+        rows = record[f"micro/{micro}"]
+        out[f"ddp/{micro}/losses"] = [row["loss"] for row in rows]
+        out[f"ddp/{micro}/updated"] = [row["updated"] for row in rows]
+        out[f"ddp/{micro}/weights"] = torch.stack([row["weight"] for row in rows])
+        if rows[0]["gradient"] is not None:
+            out[f"ddp/{micro}/gradients"] = torch.stack([row["gradient"] for row in rows])
+    distributed.destroy_process_group()
+    return out if rank == 0 else {}
+
+
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
@@ -1336,5 +1400,9 @@ def collect(sections=None) -> dict:
 if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[2] == "artifact":   # <out> artifact <save_to> [<load_from>]
         torch.save(artifact_exchange(*sys.argv[3:5]), sys.argv[1])
+    elif len(sys.argv) > 2 and sys.argv[2] == "ddp":      # under a two-rank launch; rank 0 writes
+        found = ddp_exchange()
+        if found:
+            torch.save(found, sys.argv[1])
     else:
         torch.save(collect(sys.argv[2:] or None), sys.argv[1])

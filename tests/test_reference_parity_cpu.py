@@ -424,3 +424,31 @@ def test_exported_artifacts_interchange_with_the_reference(tmp_path):
                                                                                              "loaded/text/")))
     for key in tensors:
         assert torch.equal(ours[key], theirs[key]), key
+
+
+def test_data_parallel_wrapper_equals_the_reference(tmp_path):
+    """Two Gloo ranks in each tree: loss closures through ``wrap_ddp`` with two micro-batches per
+    update.  Losses, the local gradients after the first micro-batch, the averaged ones after the
+    last, and the parameters after every step are equal bit for bit between the trees; inside a
+    tree the ranks end every update with the same parameters."""
+    results = []
+    for label, env, port in (("theirs", reference_env(), 29721),
+                             ("ours", dict(os.environ, PYTHONPATH=str(ROOT), AGB200_DISABLE_NATIVE="1"), 29722)):
+        env = {k: v for k, v in env.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+        env["OMP_NUM_THREADS"] = "2"
+        path = tmp_path / f"{label}.pt"
+        done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                               "--master-addr", "127.0.0.1", "--master-port", str(port),
+                               str(ROOT / "baseline" / "function_probe.py"), str(path), "ddp"],
+                              capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT / "baseline"))
+        assert done.returncode == 0 and path.exists(), done.stderr[-3000:]
+        results.append(torch.load(path, weights_only=False))
+    theirs, ours = results
+    assert sorted(theirs) == sorted(ours) and len(ours) == 16
+    for key, want in theirs.items():
+        got = ours[key]
+        assert torch.equal(got, want) if torch.is_tensor(want) else got == want, key
+    assert ours["ddp/0/updated"] == [False, False] and ours["ddp/1/updated"] == [True, True]
+    assert not torch.equal(ours["ddp/0/gradients"][0], ours["ddp/0/gradients"][1])     # still local
+    for micro in (1, 3):
+        assert torch.equal(ours[f"ddp/{micro}/weights"][0], ours[f"ddp/{micro}/weights"][1])
