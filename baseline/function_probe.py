@@ -1377,6 +1377,89 @@ def ddp_exchange() -> dict:
     return out if rank == 0 else {}
 
 
+def transport_exchange() -> dict:
+    """Run under a four-rank Gloo launch with context-parallel groups of two: micro-batch ``i`` is
+    read and prepared by group member ``i % 2`` and handed to the other one together with the
+    owner's random state; an early end and a failing dataset reach every rank."""
+    import random
+
+    import numpy as np
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from wm.infra import distributed
+    from wm.infra.batch_transport import fetch_batch, prepare_batch
+    from wm.infra.model import ContextParallelContext
+
+    distributed.init(device="cpu", backend="gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mesh = init_device_mesh("cpu", (world // 2, 2), mesh_dim_names=("dp", "cp"))
+    context = ContextParallelContext(mesh["cp"])
+    record: dict = {"context": [context.size, context.rank, context.leader_global_rank, context.artifact_rank,
+                                [list(group) for group in context.groups], bool(context.is_leader),
+                                context.checkpoint_topology()]}
+
+    def batches():
+        for index in range(3):
+            yield {"x": torch.full((2, 3), float(10 * rank + index)), "ids": [rank, index],
+                   "nested": {"y": torch.arange(4) + rank, "name": f"clip-{rank}-{index}"}}
+
+    def prepare(batch):
+        # consumes the owner's random streams: the others must continue from the same point
+        batch = dict(batch)
+        batch["noise"] = torch.rand(2) + random.random() + float(np.random.rand())
+        return batch
+
+    random.seed(100 + rank)
+    np.random.seed(200 + rank)
+    torch.manual_seed(300 + rank)
+    iterator = batches()
+    steps = []
+    for index in range(4):
+        batch, exhausted, owner = fetch_batch(context, iterator, sequence_index=index)
+        if exhausted:
+            steps.append("end")
+            break
+        shared = prepare_batch(context, batch, owner_rank=owner, prepare=prepare)
+        steps.append({"owner": owner, "x": shared["x"], "ids": shared["ids"], "y": shared["nested"]["y"],
+                      "name": shared["nested"]["name"], "noise": shared["noise"],
+                      "after": [random.random(), float(np.random.rand()), float(torch.rand(()))]})
+    record["steps"] = steps
+
+    def failing():
+        yield {"x": torch.zeros(1)}
+        if rank == 3:
+            raise ValueError("corrupt sample")
+        yield {"x": torch.zeros(1)}
+
+    iterator = failing()
+    fetch_batch(context, iterator, sequence_index=1)      # member 1 of every group reads its first item
+    try:
+        fetch_batch(context, iterator, sequence_index=3)  # and its second: rank 3 fails
+        record["failure"] = "none"
+    except RuntimeError as error:
+        record["failure"] = ("rank 3" in str(error), "corrupt sample" in str(error))
+    gathered: list = [None] * world
+    dist.all_gather_object(gathered, record)
+    dist.barrier()
+    distributed.destroy_process_group()
+    if rank != 0:
+        return {}
+    out: dict = {}
+    for member, seen in enumerate(gathered):
+        out[f"transport/{member}/context"] = repr(seen["context"])
+        out[f"transport/{member}/failure"] = repr(seen["failure"])
+        out[f"transport/{member}/steps"] = len(seen["steps"])
+        for index, step in enumerate(seen["steps"]):
+            if step == "end":
+                out[f"transport/{member}/{index}"] = "end"
+                continue
+            out[f"transport/{member}/{index}/meta"] = repr((step["owner"], step["ids"], step["name"], step["after"]))
+            out[f"transport/{member}/{index}/tensors"] = torch.cat([step["x"].reshape(-1), step["y"].float(),
+                                                                    step["noise"]])
+    return out
+
+
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
@@ -1400,6 +1483,10 @@ def collect(sections=None) -> dict:
 if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[2] == "artifact":   # <out> artifact <save_to> [<load_from>]
         torch.save(artifact_exchange(*sys.argv[3:5]), sys.argv[1])
+    elif len(sys.argv) > 2 and sys.argv[2] == "transport":   # under a four-rank launch; rank 0 writes
+        found = transport_exchange()
+        if found:
+            torch.save(found, sys.argv[1])
     elif len(sys.argv) > 2 and sys.argv[2] == "ddp":      # under a two-rank launch; rank 0 writes
         found = ddp_exchange()
         if found:

@@ -452,3 +452,33 @@ def test_data_parallel_wrapper_equals_the_reference(tmp_path):
     assert not torch.equal(ours["ddp/0/gradients"][0], ours["ddp/0/gradients"][1])     # still local
     for micro in (1, 3):
         assert torch.equal(ours[f"ddp/{micro}/weights"][0], ours[f"ddp/{micro}/weights"][1])
+
+
+def test_batch_transport_equals_the_reference(tmp_path):
+    """Four Gloo ranks in context-parallel groups of two, in each tree: which member reads which
+    micro-batch, the tensors, nested structure and random state the other member receives, the
+    common end of the data, and a dataset failure on one rank that every rank reports."""
+    results = []
+    for label, env, port in (("theirs", reference_env(), 29723),
+                             ("ours", dict(os.environ, PYTHONPATH=str(ROOT), AGB200_DISABLE_NATIVE="1"), 29724)):
+        env = {k: v for k, v in env.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+        env["OMP_NUM_THREADS"] = "2"
+        path = tmp_path / f"{label}.pt"
+        done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
+                               "--master-addr", "127.0.0.1", "--master-port", str(port),
+                               str(ROOT / "baseline" / "function_probe.py"), str(path), "transport"],
+                              capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT / "baseline"))
+        assert done.returncode == 0 and path.exists(), done.stderr[-3000:]
+        results.append(torch.load(path, weights_only=False))
+    theirs, ours = results
+    assert sorted(theirs) == sorted(ours) and len(ours) == 44
+    for key, want in theirs.items():
+        got = ours[key]
+        assert torch.equal(got, want) if torch.is_tensor(want) else got == want, key
+    assert all(ours[f"transport/{member}/failure"] == "(True, True)" for member in range(4))
+    # both members of a group hold the same prepared batch and continue with the same streams
+    for pair in ((0, 1), (2, 3)):
+        for step in range(3):
+            for part in ("meta", "tensors"):
+                a, b = (ours[f"transport/{member}/{step}/{part}"] for member in pair)
+                assert torch.equal(a, b) if torch.is_tensor(a) else a == b, (pair, step, part)
