@@ -15,7 +15,8 @@ the tiny decoders (parallel, sequential, streamed), streams in all three positio
 eviction, a prompt change and reference images, ``sample()`` of the three objectives, raw batches
 through the conditioner, periodic sampling with the media writer's files and rules, the codec wrapper's surface, the
 objective base class, bounded history windows, weight overlays at start-up, the optimizer's CPU path, constants and recipe trees, utilities,
-clipping helpers, lazy calls, the metric callback's corner cases, and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
+clipping helpers, lazy calls, the metric callback's corner cases, resume under a changed recipe,
+and the Wan 2.2 VAE (encode / decode of a small clip with shared random weights).
 """
 
 from __future__ import annotations
@@ -1238,6 +1239,108 @@ def _runtime_misc(out: dict) -> None:
     out["metrics/sinks_left"] = len([sink for sink in callback.sinks])
 
 
+def _resume_rules(out: dict) -> None:
+    """Resume under a changed recipe: the current learning rates, schedule and optimizer options
+    win, progress (update counts, moments) is restored, parameters that had no optimizer state get
+    none, selected components only, and the iteration and data cursor come back."""
+    import tempfile
+    import warnings
+    from pathlib import Path
+
+    from wm.data.loader import StatefulDataLoader
+    from wm.infra.checkpoint import DistributedCheckpointer
+    from wm.infra.model import Model
+    from wm.infra.optim import FusedAdam, LinearWarmup
+
+    class Toy(Model):
+        def __init__(self, seed: int) -> None:
+            super().__init__()
+            g = torch.Generator().manual_seed(seed)
+            self.used, self.unused = torch.nn.Linear(3, 3), torch.nn.Linear(3, 1)
+            with torch.no_grad():
+                for parameter in self.parameters():
+                    parameter.copy_(torch.randn(parameter.shape, generator=g))
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def sample(self, data_batch, **sampling_options):
+            return None
+
+    class Rows(torch.utils.data.Dataset):
+        def __len__(self) -> int:
+            return 10
+
+        def __getitem__(self, index: int):
+            return {"index": torch.tensor(index)}
+
+    def job(seed: int, lr: float, warmup: int, betas):
+        model = Toy(seed)
+        optimizer = FusedAdam(model.parameters(), lr=lr, betas=betas, eps=1e-8, weight_decay=0.0)
+        scheduler = torch.optim.lr_scheduler.LambdaLR(optimizer, LinearWarmup(warmup_steps=warmup, start_factor=0.5))
+        loader = StatefulDataLoader(Rows(), batch_size=2, shuffle=True, seed=4, num_workers=0, pin_memory=False)
+        return model, optimizer, scheduler, loader
+
+    def steps(model, optimizer, scheduler, count: int, seed: int):
+        g = torch.Generator().manual_seed(seed)
+        for _ in range(count):
+            optimizer.zero_grad(set_to_none=True)
+            model.used(torch.randn(4, 3, generator=g)).square().mean().backward()   # `unused` gets no gradient
+            optimizer.step()
+            scheduler.step()
+
+    with warnings.catch_warnings(), tempfile.TemporaryDirectory() as scratch:
+        warnings.simplefilter("ignore")
+        model, optimizer, scheduler, loader = job(1, 0.01, 4, (0.9, 0.99))
+        steps(model, optimizer, scheduler, 3, 50)
+        iterator = iter(loader)
+        next(iterator), next(iterator)
+        saver = DistributedCheckpointer(Path(scratch) / "checkpoints")
+        saver.save(model, {"net": optimizer}, {"net": scheduler}, None, iteration=3, dataloader=loader,
+                   runtime_metadata={"note": "first run"})
+        saver.finalize()
+        out["resume/files"] = sorted(str(p.relative_to(scratch)) for p in Path(scratch).rglob("*")
+                                     if p.is_file() and "tensor" not in p.parts)
+
+        fresh, new_optimizer, new_scheduler, new_loader = job(2, 0.02, 8, (0.8, 0.95))
+        result = DistributedCheckpointer(Path(scratch) / "checkpoints").load(
+            fresh, {"net": new_optimizer}, {"net": new_scheduler}, None, path="latest", dataloader=new_loader,
+            runtime_metadata={"note": "second run"})
+        out["resume/iteration"] = int(result.iteration)
+        out["resume/cursor"] = sorted(new_loader.state_dict().items())
+        group = new_optimizer.param_groups[0]
+        out["resume/options"] = [float(group["lr"]), tuple(float(b) for b in group["betas"]), float(group["initial_lr"])]
+        out["resume/schedule"] = [int(new_scheduler.last_epoch), [float(v) for v in new_scheduler.get_last_lr()]]
+        state = new_optimizer.state_dict()["state"]
+        out["resume/state_of"] = sorted(state)
+        for index in sorted(state):
+            for name, value in sorted(state[index].items()):
+                if torch.is_tensor(value):
+                    out[f"resume/state/{index}/{name}"] = value.detach().float().reshape(-1)
+        for name, value in fresh.state_dict().items():
+            out[f"resume/model/{name}"] = value
+        steps(fresh, new_optimizer, new_scheduler, 2, 51)
+        for name, value in fresh.state_dict().items():
+            out[f"resume/continued/{name}"] = value
+        out["resume/continued_lr"] = [float(v) for v in new_scheduler.get_last_lr()]
+
+        only_model, other_optimizer, other_scheduler, _ = job(3, 0.05, 2, (0.9, 0.99))
+        result = DistributedCheckpointer(Path(scratch) / "checkpoints").load(
+            only_model, {"net": other_optimizer}, {"net": other_scheduler}, None, path="latest",
+            components=("model",))
+        out["resume/model_only"] = [int(result.iteration), len(other_optimizer.state_dict()["state"]),
+                                    int(other_scheduler.last_epoch)]
+        out["resume/model_only/weight"] = only_model.used.weight.detach().clone()
+        nothing = DistributedCheckpointer(Path(scratch) / "checkpoints").load(
+            Toy(4), {}, {}, None, path=None)
+        out["resume/nothing"] = int(nothing.iteration)
+        try:
+            DistributedCheckpointer(Path(scratch) / "elsewhere").load(Toy(4), {}, {}, None, path="latest")
+            out["resume/no_pointer"] = "accepted"
+        except Exception as error:
+            out["resume/no_pointer"] = type(error).__name__
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1464,7 +1567,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules,
             "vae": _vae}
 
 
