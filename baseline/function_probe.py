@@ -1341,6 +1341,56 @@ def _resume_rules(out: dict) -> None:
             out["resume/no_pointer"] = type(error).__name__
 
 
+def _batched_network(out: dict) -> None:
+    """Two samples with prompts of different lengths and different frame rates through the text
+    tower and the generation tower (bidirectional and block-causal), feature taps, patch helpers."""
+    import os
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import seeded_, tiny_config
+
+    from wm.codecs import Wan22VAECodec
+    from wm.models.flow import rf_interpolate
+    from wm.networks.cosmos3 import Cosmos3Conditioner, build_network
+    from wm.networks.cosmos3 import network as network_module
+
+    config = tiny_config()
+    net = build_network(config, init_device="cpu").float().eval()
+    seeded_(net, 0)
+    cond = Cosmos3Conditioner(config=config, codec=Wan22VAECodec(pretrained_path="unused", decoder=None),
+                              geometry_noise_sigma=0.0, init_device="cpu", empty_prompt_ids=(3, 4, 5)).float()
+    seeded_(cond.text_encoder, 1)
+    g = torch.Generator().manual_seed(61)
+    shape = (2, 48, 5, 8, 8)
+    ids = torch.randint(3, 128, (2, 14), generator=g)
+    mask = torch.ones(2, 14, dtype=torch.bool)
+    mask[1, 6:] = False
+    batch = {"latent": torch.randn(shape, generator=g), "depth_latent": torch.randn(shape, generator=g),
+             "normal_latent": torch.randn(shape, generator=g), "text_input_ids": ids,
+             "text_attention_mask": mask, "fps": torch.tensor([16.0, 30.0])}
+    encoded = cond.encode(batch, training=False)
+    with torch.no_grad():
+        condition = cond.condition(encoded)
+        out["batched/text_valid"] = condition.text.valid_lengths
+        out["batched/text_keys"] = torch.stack(list(condition.text.keys))
+        out["batched/text_values"] = torch.stack(list(condition.text.values))
+        dropped = cond.condition(encoded, drop=torch.tensor([True, False]))
+        out["batched/dropped_valid"] = dropped.text.valid_lengths
+        latent = encoded["latent"]
+        noise = torch.randn(latent.shape, generator=g)
+        sigma = torch.tensor([0.7, 0.2])
+        noisy = rf_interpolate(latent, noise, sigma)
+        noisy[:, :, :1] = latent[:, :, :1]
+        out["batched/forward"] = net(noisy, sigma, condition, known_frames=1)
+        block_sigma = torch.tensor([[0.9] * 4, [0.4] * 4])
+        targets = rf_interpolate(latent[:, :, 1:], noise[:, :, 1:], block_sigma)
+        out["batched/forward_ar"] = net.forward_ar(latent[:, :, :1], targets, block_sigma, condition, block_frames=4)
+        patches = network_module.patchify(latent[:, :, :2], config.patch_size)
+        out["batched/patchify"] = patches
+        out["batched/unpatchify"] = network_module.unpatchify(patches, channels=48, grid=(4, 4),
+                                                               patch_size=config.patch_size)
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1567,7 +1617,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules, "batched_network": _batched_network,
             "vae": _vae}
 
 
