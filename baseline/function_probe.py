@@ -1613,6 +1613,81 @@ def transport_exchange() -> dict:
     return out
 
 
+def run_exchange(save_to: str, load_from: str | None = None) -> dict:
+    """Lay out a small training run (checkpoint of a bidirectional model, its resolved
+    configuration, the released text tower it was initialised from) under ``save_to``; when
+    ``load_from`` names such a run (of either tree), inspect its checkpoint and load it for
+    serving."""
+    import dataclasses
+    import os
+    from pathlib import Path
+
+    import yaml
+    from safetensors.torch import save_file
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from reference_probe import seeded_, tiny_config
+
+    from wm.codecs import Wan22VAECodec
+    from wm.inference.cosmos3 import inspect_artifact, load_artifact
+    from wm.infra.checkpoint import DistributedCheckpointer
+    from wm.infra.parallel import ParallelConfig
+    from wm.models.diffusion import DiffusionModel
+    from wm.networks.cosmos3 import TEXT_ENCODER_KEYS, Cosmos3Conditioner, build_network
+
+    config = tiny_config()
+    plain = ParallelConfig(parameter_dtype="float32", fully_shard=False, activation_checkpointing="none",
+                           compile=False)
+    model = DiffusionModel(net=build_network(config, init_device="cpu"),
+                           conditioner=Cosmos3Conditioner(config=config, geometry_noise_sigma=0.0, init_device="cpu",
+                                                          empty_prompt_ids=(3, 4, 5),
+                                                          codec=Wan22VAECodec(pretrained_path="unused", decoder=None)),
+                           parallel=plain, conditioner_parallel=plain)
+    model.parallelize("cpu")
+    seeded_(model.net, 40)
+    seeded_(model.conditioner.text_encoder, 41)
+    run = Path(save_to)
+    released = run / "released" / "transformer"
+    released.mkdir(parents=True, exist_ok=True)
+    save_file({key: value.detach().clone() for key, value in model.conditioner.text_encoder.state_dict().items()},
+              str(released / "model.safetensors"))
+    optimizer = torch.optim.SGD([p for p in model.net.parameters() if p.requires_grad], lr=0.1)
+    scheduler = torch.optim.lr_scheduler.LambdaLR(optimizer, lambda step: 1.0)
+    saver = DistributedCheckpointer(run / "checkpoints")
+    saver.save(model, {"net": optimizer}, {"net": scheduler}, None, iteration=5)
+    saver.finalize()
+    topology = {f.name: getattr(config, f.name) for f in dataclasses.fields(config)}
+    topology = {k: (list(v) if isinstance(v, tuple) else v) for k, v in topology.items()}
+    resolved = {
+        "model": {"net": {"config": topology, "lora": None},
+                  "conditioner": {"tokenizer_path": "released/tokenizer"}},
+        "dataloader_val": {"dataset": {"num_frames": 9}},
+        "train": {"model_initializations": {"text": {
+            "path": "released/transformer", "model_key_prefix": "conditioner.text_encoder",
+            "source_model_key_prefix": "", "source_model_key_patterns": list(TEXT_ENCODER_KEYS)}}},
+    }
+    (run / "config.yaml").write_text(yaml.safe_dump(resolved))
+    out: dict = {"run/files": sorted(str(p.relative_to(run)) for p in run.rglob("*")
+                                     if p.is_file() and "tensor" not in p.parts)}
+    if load_from is not None:
+        source = Path(load_from)
+        spec = inspect_artifact(source / "checkpoints" / "iter_000000005")
+        out["run/spec"] = [spec.iteration, spec.prompt_pixel_frames, repr(spec.lora),
+                           [(Path(s.path).name, s.prefix, tuple(s.patterns)) for s in spec.student],
+                           [(Path(s.path).name, s.prefix, len(s.patterns)) for s in spec.text],
+                           Path(spec.tokenizer_path).name]
+        seen = []
+        artifact = load_artifact(spec, device="cpu", dtype=torch.float32,
+                                 progress=lambda label, done, total: seen.append((label, done, total)))
+        out["run/progress"] = seen
+        for name, value in artifact.student.state_dict().items():
+            out[f"run/student/{name}"] = value
+        for name, value in artifact.context_encoder.state_dict().items():
+            out[f"run/text/{name}"] = value
+        out["run/frozen"] = not any(p.requires_grad for p in artifact.student.parameters())
+    return out
+
+
 SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "policies": _policies,
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
@@ -1636,6 +1711,8 @@ def collect(sections=None) -> dict:
 if __name__ == "__main__":
     if len(sys.argv) > 2 and sys.argv[2] == "artifact":   # <out> artifact <save_to> [<load_from>]
         torch.save(artifact_exchange(*sys.argv[3:5]), sys.argv[1])
+    elif len(sys.argv) > 2 and sys.argv[2] == "run":          # <out> run <save_to> [<load_from>]
+        torch.save(run_exchange(*sys.argv[3:5]), sys.argv[1])
     elif len(sys.argv) > 2 and sys.argv[2] == "transport":   # under a four-rank launch; rank 0 writes
         found = transport_exchange()
         if found:

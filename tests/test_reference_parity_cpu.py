@@ -484,3 +484,29 @@ def test_batch_transport_equals_the_reference(tmp_path):
             for part in ("meta", "tensors"):
                 a, b = (ours[f"transport/{member}/{step}/{part}"] for member in pair)
                 assert torch.equal(a, b) if torch.is_tensor(a) else a == b, (pair, step, part)
+
+
+def test_training_runs_are_served_by_either_tree(tmp_path):
+    """A run directory (checkpoint, resolved configuration, the released text tower it names) laid
+    out by one tree is inspected and loaded for serving by the other: the same overlay order,
+    caption horizon, tokenizer location, progress reports and every tensor of both towers."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("function_probe", ROOT / "baseline" / "function_probe.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    ours_run, theirs_run = tmp_path / "ours", tmp_path / "theirs"
+    laid_out = module.run_exchange(str(ours_run))
+    path = tmp_path / "exchange.pt"
+    done = subprocess.run([sys.executable, str(ROOT / "baseline" / "function_probe.py"), str(path), "run",
+                           str(theirs_run), str(ours_run)], capture_output=True, text=True, timeout=900,
+                          env=reference_env(), cwd=str(ROOT / "baseline"))
+    assert done.returncode == 0, done.stderr[-3000:]
+    theirs = torch.load(path, weights_only=False)            # the reference served this package's run
+    ours = module.run_exchange(str(tmp_path / "again"), str(theirs_run))    # and the reverse
+    assert laid_out["run/files"] == theirs["run/files"] == ours["run/files"]
+    assert sorted(ours) == sorted(theirs) and len(ours) == 60
+    assert ours["run/spec"][:2] == [5, 9] and ours["run/frozen"] is True
+    for key, want in theirs.items():
+        got = ours[key]
+        assert torch.equal(got, want) if torch.is_tensor(want) else got == want, key
