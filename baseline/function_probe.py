@@ -1391,6 +1391,80 @@ def _batched_network(out: dict) -> None:
                                                                patch_size=config.patch_size)
 
 
+def _skipped_update(out: dict) -> None:
+    """An update whose gradients are not finite: nothing steps, the schedule does not move, the
+    gradients are cleared, the hooks fire in the documented order, and the next update goes
+    through; with the monitor attached the event is recorded and the norm is reported."""
+    import tempfile
+
+    from wm.infra.callbacks import Callback, CallbackGroup, GradClipMonitor
+    from wm.infra.model import Model
+    from wm.infra.trainer import Trainer
+
+    class Toy(Model):
+        def __init__(self) -> None:
+            super().__init__()
+            self.weight = torch.nn.Parameter(torch.tensor([1.0, -2.0, 0.5]))
+
+        def parallelize(self, device) -> None:
+            return None
+
+        def training_step(self, data_batch, iteration):
+            loss = (self.weight * data_batch["x"]).sum()
+            return {"metrics/plain": loss.detach()}, loss
+
+        def sample(self, data_batch, **sampling_options):
+            return None
+
+    class Recorder(Callback):
+        def __init__(self) -> None:
+            super().__init__()
+            self.events = []
+
+        def on_training_step_start(self, model, data_batch, iteration=0):
+            self.events.append(("start", iteration))
+
+        def on_before_optimizer_step(self, model_ddp, optimizer, scheduler, grad_scaler, iteration=0):
+            self.events.append(("before_step", iteration))
+
+        def on_optimizer_step_skipped(self, model_ddp, optimizer_names, iteration=0):
+            self.events.append(("skipped", tuple(optimizer_names), iteration))
+
+        def on_after_optimizer_step(self, model_ddp, optimizer_name, optimizer, scheduler, iteration=0):
+            self.events.append(("after_step", optimizer_name, iteration))
+
+        def on_before_zero_grad(self, model_ddp, optimizer, scheduler, iteration=0):
+            self.events.append(("before_zero_grad", iteration))
+
+        def on_training_step_batch_end(self, model, data_batch, output_batch, loss, iteration=0):
+            self.events.append(("batch_end", iteration, sorted(output_batch)))
+
+        def on_training_step_end(self, model, data_batch, output_batch, loss, iteration=0):
+            self.events.append(("step_end", iteration))
+
+    with tempfile.TemporaryDirectory() as scratch:
+        model, recorder = Toy(), Recorder()
+        monitor = GradClipMonitor(max_norm=10.0, spike_threshold=None, spike_ratio=None, output_dir=scratch)
+        optimizer = torch.optim.SGD(model.parameters(), lr=0.1)
+        scheduler = torch.optim.lr_scheduler.LambdaLR(optimizer, lambda step: 1.0 / (1 + step))
+        model.optimizer_dict, model.scheduler_dict = {"net": optimizer}, {"net": scheduler}
+        group = CallbackGroup(config=None, trainer=None)
+        group._callbacks.extend([monitor, recorder])
+        trainer = Trainer(grad_accum_steps=1, callbacks=group, device=torch.device("cpu"))
+        scaler = torch.amp.GradScaler(device="cpu", enabled=False)
+        rows = []
+        for iteration, batch in enumerate((torch.tensor([1.0, 2.0, 3.0]), torch.tensor([1.0, float("inf"), 3.0]),
+                                           torch.tensor([0.5, 0.5, 0.5]))):
+            result = trainer.training_step(model, scaler, {"x": batch}, iteration=iteration)
+            rows.append((bool(result.did_update), bool(result.found_nonfinite), result.grad_accum_step,
+                         sorted(result.output_batch), model.weight.grad is None, int(scheduler.last_epoch),
+                         [round(float(v), 6) for v in model.weight.detach()]))
+        out["skip/rows"] = rows
+        out["skip/events"] = recorder.events
+        out["skip/reported"] = sorted((k, round(float(v), 6)) for k, v in result.output_batch.items()
+                                      if k.startswith("metrics/"))
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1692,7 +1766,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules, "batched_network": _batched_network,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules, "batched_network": _batched_network, "skipped_update": _skipped_update,
             "vae": _vae}
 
 
