@@ -345,7 +345,9 @@ class Cosmos3Network(ParallelNetwork):
 
     def time_embedding(self, sigma: torch.Tensor) -> torch.Tensor:
         """Per-frame FP32 timestep embedding ``[B, T, D]``."""
-        scaled = sigma.float().flatten() * (1000.0 * self.config.timestep_scale)
+        # two roundings, in this order, as the reference multiplies (they differ from one product
+        # by the combined factor whenever timestep_scale is not a power of two)
+        scaled = sigma.float().flatten() * 1000.0 * self.config.timestep_scale
         return self.time_embedder(scaled).unflatten(0, tuple(sigma.shape))
 
     def geometry_frames(self, condition: "Cosmos3Condition", *, start: int, stop: int,

@@ -1385,6 +1385,11 @@ def _batched_network(out: dict) -> None:
         block_sigma = torch.tensor([[0.9] * 4, [0.4] * 4])
         targets = rf_interpolate(latent[:, :, 1:], noise[:, :, 1:], block_sigma)
         out["batched/forward_ar"] = net.forward_ar(latent[:, :, :1], targets, block_sigma, condition, block_frames=4)
+        import dataclasses
+
+        scaled = build_network(dataclasses.replace(config, timestep_scale=0.7), init_device="cpu").float().eval()
+        seeded_(scaled, 0)
+        out["batched/timestep_scale"] = scaled.embed_rgb(latent[:1, :, :3], torch.tensor([[0.123, 0.456, 0.789]]))
         patches = network_module.patchify(latent[:, :, :2], config.patch_size)
         out["batched/patchify"] = patches
         out["batched/unpatchify"] = network_module.unpatchify(patches, channels=48, grid=(4, 4),

@@ -349,9 +349,10 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     update skipped for non-finite gradients (nothing steps, hook order, the next update goes
     through).  Equal
     to rounding: the restructured codecs (Wan 2.2 VAE, tiny decoders), a stream restarted on its
-    kept arenas, the sampled latents (a few solver steps through the no-gradient operators) and
-    block-causal passes under bounded history windows and on a batch of two (rows of all chunks
-    of a layer go through the row-wise operators together here)."""
+    kept arenas, the sampled latents and block-causal passes under bounded history windows and on
+    a batch of two: these agree bit for bit in most runs, but the CPU kernels underneath do not
+    promise the same rounding for the same values at another memory alignment (two runs of the
+    reference alone can differ by 4e-7), so they are compared to 5e-5."""
     import importlib.util
 
     path = tmp_path / "functions.pt"
