@@ -1470,6 +1470,59 @@ def _skipped_update(out: dict) -> None:
                                       if k.startswith("metrics/"))
 
 
+def _refusals(out: dict) -> None:
+    """What the constructors and entry points refuse, and in which words."""
+    from wm.data.loader import StatefulDataLoader
+    from wm.infra.callbacks import GradClip, PeriodicSampleCallback
+    from wm.infra.optim import CosineDecay, LinearWarmup, LinearWarmupCosineDecay
+    from wm.infra.trainer import Trainer
+    from wm.models.dmd import GANConfig, PhaseClock
+    from wm.models.flow import FlowUniPC, RectifiedFlowSchedule, UniformShift
+    from wm.networks.cosmos3.geometry import GeometryAugmentationConfig
+    from wm.networks.cosmos3.streaming import StreamPolicy
+    from wm.networks.discriminator import DiscriminatorHead
+    from wm.protocols import HistoryWindow
+
+    cases = {
+        "policy/block": lambda: StreamPolicy(block_frames=0),
+        "policy/sink": lambda: StreamPolicy(sink_frames=-1),
+        "policy/history": lambda: StreamPolicy(block_frames=4, sink_frames=5, history_frames=6),
+        "policy/rope": lambda: StreamPolicy(rope="sideways"),
+        "policy/train_frames": lambda: StreamPolicy(block_frames=4, sink_frames=1, history_frames=8, train_frames=4),
+        "window/negative": lambda: HistoryWindow(sink_blocks=-1),
+        "clock/zero": lambda: PhaseClock(fake_score_updates_per_student=0),
+        "gan/kind": lambda: GANConfig(regularization="imaginary"),
+        "gan/weight": lambda: GANConfig(regularization_weight=-1.0),
+        "schedule/shift": lambda: RectifiedFlowSchedule(shift=0.0),
+        "schedule/kind": lambda: RectifiedFlowSchedule(train_distribution="triangular"),
+        "uniform/shift": lambda: UniformShift(float("nan")),
+        "geometry/probability": lambda: GeometryAugmentationConfig(spatial_probability=1.5),
+        "geometry/scale": lambda: GeometryAugmentationConfig(spatial_max_scale=0.5),
+        "geometry/range": lambda: GeometryAugmentationConfig(texture_downsample_min=2.0, texture_downsample_max=1.0),
+        "geometry/selection": lambda: GeometryAugmentationConfig(modality_selection="neither"),
+        "head/layers": lambda: DiscriminatorHead(hidden_size=8, feature_layers=(1, 1), num_heads=2),
+        "head/heads": lambda: DiscriminatorHead(hidden_size=10, feature_layers=(1,), num_heads=4),
+        "head/sign": lambda: DiscriminatorHead(hidden_size=8, feature_layers=(1,), num_heads=2, initial_logit_sign=0.5),
+        "lr/cosine": lambda: CosineDecay(decay_steps=0),
+        "lr/min_factor": lambda: CosineDecay(decay_steps=10, min_factor=1.5),
+        "lr/both": lambda: LinearWarmupCosineDecay(warmup_steps=10, decay_steps=5),
+        "lr/warmup": lambda: LinearWarmup(warmup_steps=10, start_factor=-0.1),
+        "clip/bound": lambda: GradClip(max_norm=-1.0),
+        "trainer/accum": lambda: Trainer(grad_accum_steps=0),
+        "sampler/source": lambda: PeriodicSampleCallback(1, "out", None, source="test"),
+        "sampler/batches": lambda: PeriodicSampleCallback(1, "out", None, max_batches=-1),
+        "loader/cursor": lambda: StatefulDataLoader([1, 2, 3], batch_size=1, num_workers=0, pin_memory=False
+                                                    ).load_state_dict({"epoch": -1, "batch_offset": 0}),
+        "solver/steps": lambda: FlowUniPC(0, shift=1.0).run(torch.zeros(1), lambda x, s: x),
+    }
+    for label, make in cases.items():
+        try:
+            made = make()
+            out[f"refusal/{label}"] = f"accepted: {type(made).__name__}"
+        except Exception as error:
+            out[f"refusal/{label}"] = f"{type(error).__name__}: {error}"
+
+
 def _vae(out: dict) -> None:
     from wm.codecs import wan22
 
@@ -1771,7 +1824,7 @@ SECTIONS = {"flow": _flow, "lr": _lr, "geometry": _geometry, "media": _media, "p
             "seeded_modules": _seeded_modules, "data": _data, "training_loop": _training_loop,
             "tiny_decoders": _tiny_decoders, "streams": _streams, "sampling": _sampling, "conditioner_raw": _conditioner_raw,
             "sampling_callback": _sampling_callback, "codec_surface": _codec_surface, "model_base": _model_base,
-            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules, "batched_network": _batched_network, "skipped_update": _skipped_update,
+            "history_windows": _history_windows, "initializations": _initializations, "fused_adam": _fused_adam, "constants": _constants, "recipes": _recipes, "utilities": _utilities, "runtime_misc": _runtime_misc, "resume_rules": _resume_rules, "batched_network": _batched_network, "skipped_update": _skipped_update, "refusals": _refusals,
             "vae": _vae}
 
 

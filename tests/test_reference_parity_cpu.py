@@ -347,7 +347,7 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     schedule and options win, progress comes back, no state is invented, components can be
     selected, the data cursor returns); the text tower on two prompts of different lengths; an
     update skipped for non-finite gradients (nothing steps, hook order, the next update goes
-    through).  Equal
+    through); what thirty constructors and entry points refuse, and in which words.  Equal
     to rounding: the restructured codecs (Wan 2.2 VAE, tiny decoders), a stream restarted on its
     kept arenas, the sampled latents and block-causal passes under bounded history windows and on
     a batch of two: these agree bit for bit in most runs, but the CPU kernels underneath do not
@@ -368,7 +368,7 @@ def test_pure_and_seeded_functions_equal_the_reference(tmp_path):
     errors = {key: value for key, value in {**theirs, **ours}.items() if key.endswith("/error")}
     assert not errors, errors
     assert sorted(ours) == sorted(theirs)
-    assert len(ours) > 568
+    assert len(ours) > 600
 
     def to_rounding(key: str) -> bool:
         return key.startswith(("vae/", "tiny/", "window/", "batched/forward")) or key.endswith("/restart") \
